@@ -1,0 +1,212 @@
+"""Mixture-of-experts layer: router -> dispatch -> grouped SwiGLU experts -> combine.
+
+Semantics follow torchtitan/models/common/moe/moe.py:24-579:
+
+* ``GroupedExperts``: 3-D parameters ``w1[E,H,D] w2[E,D,H] w3[E,H,D]`` (names kept for
+  checkpoints), output ``(silu(x w1^T) * x w3^T) w2^T`` per expert group (:24-127).
+* ``TokenChoiceTopKRouter``: gate in fp32, softmax or sigmoid scores, ``expert_bias`` added
+  only for *choosing* experts, optional node-limited routing (keep ``num_limited_groups``
+  groups ranked by the sum of their top-2 scores), ``route_norm`` and ``route_scale``, a
+  round-robin debug mode, and a per-expert token histogram (:130-326).
+* ``MoE``: shared experts as one wide FeedForward, ``score_before_experts`` (scale the routed
+  rows) or after (weighted sum over the k copies in fp32), persistent ``expert_bias`` and
+  non-persistent ``tokens_per_expert`` buffers (:373-579).
+
+Structure differs: the (token, slot) pairs are placed by a counting sort (``ops.moe_sort``)
+and all movement of rows goes through a *dispatcher* object owned by ``GroupedExperts``
+(``LocalDispatcher`` here; expert parallel installs its own in ``parallel/ep.py``), so the
+layer body has no distributed code and no host synchronisation.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Literal
+
+import torch
+import torch.nn as nn
+
+from torchtitan_b200 import ops
+from torchtitan_b200.ops import reference as ref
+from torchtitan_b200.protocols.module import Module
+
+from ..feed_forward import FeedForward
+from ..linear import Linear
+
+
+def _moe_ops():
+    from torchtitan_b200.ops import moe_ops
+
+    return moe_ops
+
+
+class LocalDispatcher:
+    """All experts live on this rank: dispatch = gather rows in expert order."""
+
+    def dispatch(self, x, order, counts, top_k: int):
+        return _moe_ops().gather_rows(x, order, top_k), counts, None
+
+    def combine(self, y, ctx):
+        return y
+
+
+class GroupedExperts(Module):
+    def __init__(self, *, dim: int, hidden_dim: int, num_experts: int, use_grouped_mm: bool):
+        super().__init__()
+        self.num_experts = num_experts
+        self.w1 = nn.Parameter(torch.empty(num_experts, hidden_dim, dim))
+        self.w2 = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
+        self.w3 = nn.Parameter(torch.empty(num_experts, hidden_dim, dim))
+        self.use_grouped_mm = use_grouped_mm
+        self.dispatcher = LocalDispatcher()
+
+    def local_weights(self):
+        w = []
+        for p in (self.w1, self.w2, self.w3):
+            w.append(p.to_local() if hasattr(p, "to_local") else p)
+        return w
+
+    def forward(self, x, num_tokens_per_expert):
+        """``x`` [rows, D] grouped by (local) expert, ``num_tokens_per_expert`` [E_local]."""
+        w1, w2, w3 = self.local_weights()
+        mo = _moe_ops()
+        h = ops.swiglu(mo.grouped_linear(x, w1, num_tokens_per_expert), mo.grouped_linear(x, w3, num_tokens_per_expert))
+        return mo.grouped_linear(h, w2, num_tokens_per_expert)
+
+    def init_weights(self, **kwargs) -> None:
+        init_std = kwargs.get("init_std")
+        assert init_std is not None
+        nn.init.trunc_normal_(self.w1, mean=0.0, std=0.02)
+        nn.init.trunc_normal_(self.w2, mean=0.0, std=init_std)
+        nn.init.trunc_normal_(self.w3, mean=0.0, std=init_std)
+
+
+class TokenChoiceTopKRouter(Module):
+    def __init__(self, *, dim: int, num_experts: int, num_expert_groups: int | None,
+                 num_limited_groups: int | None, top_k: int, score_func: Literal["softmax", "sigmoid"],
+                 route_norm: bool, route_scale: float, gate_bias: bool, _debug_force_load_balance: bool = False):
+        super().__init__()
+        self.gate = Linear.Config(bias=gate_bias).build(in_features=dim, out_features=num_experts)
+        self.num_experts = num_experts
+        self.num_expert_groups = num_expert_groups
+        self.num_limited_groups = num_limited_groups
+        self.top_k = top_k
+        self.score_func = score_func
+        self.route_norm = route_norm
+        self.route_scale = route_scale
+        self._debug_force_load_balance = _debug_force_load_balance
+
+    def forward(self, x, expert_bias=None):
+        """``x`` [T, D] -> (top_scores [T,k] fp32, expert indices [T,k], tokens per expert [E])."""
+        return _moe_ops().route(
+            x, self.gate.weight, self.gate.bias, expert_bias,
+            top_k=self.top_k, score_func=self.score_func, route_norm=self.route_norm,
+            route_scale=self.route_scale, num_expert_groups=self.num_expert_groups,
+            num_limited_groups=self.num_limited_groups, force_balance=self._debug_force_load_balance,
+        )
+
+    def init_weights(self, **kwargs) -> None:
+        init_std = kwargs.get("init_std")
+        assert init_std is not None
+        self.gate.init_weights(init_std=init_std)
+
+
+class TokenReorderer(Module):
+    """Orders the T*k (token, slot) pairs by expert (stable)."""
+
+    def __init__(self, *, num_experts: int, top_k: int):
+        super().__init__()
+        self.num_experts, self.top_k = num_experts, top_k
+
+    def forward(self, top_scores, selected_experts_indices):
+        order, counts = _moe_ops().sort_by_expert(selected_experts_indices, self.num_experts)
+        return top_scores.reshape(-1)[order], order, counts
+
+    def init_weights(self, **kwargs) -> None:
+        return None
+
+
+class MoE(Module):
+    @dataclass(kw_only=True, slots=True)
+    class Config(Module.Config):
+        num_experts: int = 8
+        num_shared_experts: int = 1
+        score_func: Literal["softmax", "sigmoid"] = "sigmoid"
+        route_norm: bool = False
+        route_scale: float = 1.0
+        gate_bias: bool = False
+        score_before_experts: bool = True
+        top_k: int = 1
+        num_expert_groups: int | None = None
+        num_limited_groups: int | None = None
+        use_grouped_mm: bool = True
+        load_balance_coeff: float | None = 1e-3
+        aux_loss_coeff: float = 0.0
+        """*B200 addition*: weight of a switch-style auxiliary load-balance loss
+        ``E * sum_e(fraction_e * mean_prob_e)`` whose gradient is injected at the router; 0 = off."""
+        _debug_force_load_balance: bool = False
+        hidden_dim: int = 0
+
+    def __init__(self, config: Config, *, dim: int):
+        super().__init__()
+        E, H = config.num_experts, config.hidden_dim
+        self.experts = GroupedExperts(dim=dim, hidden_dim=H, num_experts=E, use_grouped_mm=config.use_grouped_mm)
+        self.router = TokenChoiceTopKRouter(
+            dim=dim, num_experts=E, num_expert_groups=config.num_expert_groups,
+            num_limited_groups=config.num_limited_groups, top_k=config.top_k, score_func=config.score_func,
+            route_norm=config.route_norm, route_scale=config.route_scale, gate_bias=config.gate_bias,
+            _debug_force_load_balance=config._debug_force_load_balance,
+        )
+        self.reorderer = TokenReorderer(num_experts=E, top_k=config.top_k)
+        self.shared_experts = (
+            FeedForward.Config(hidden_dim=H * config.num_shared_experts).build(dim=dim)
+            if config.num_shared_experts > 0 else None
+        )
+        self.score_before_experts = config.score_before_experts
+        self.load_balance_coeff = config.load_balance_coeff
+        self.aux_loss_coeff = config.aux_loss_coeff
+        if self.load_balance_coeff is not None:
+            assert self.load_balance_coeff > 0.0
+            self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32), persistent=True)
+        else:
+            self.expert_bias = None
+        self.register_buffer("tokens_per_expert", torch.zeros(E, dtype=torch.float32), persistent=False)
+
+    def forward(self, x):
+        bs, slen, dim = x.shape
+        x = x.reshape(-1, dim)
+        k = self.router.top_k
+        top_scores, idx, counts = self.router(x, self.expert_bias)
+        with torch.no_grad():
+            self.tokens_per_expert.add_(counts.to(self.tokens_per_expert.dtype))
+        if self.aux_loss_coeff > 0.0 and self.training:
+            x = _moe_ops().inject_aux_loss(x, self.router.gate.weight, counts, self.aux_loss_coeff, k)
+        scores_sorted, order, counts_sorted = self.reorderer(top_scores, idx)
+
+        disp = self.experts.dispatcher
+        routed_in, local_counts, ctx = disp.dispatch(x, order, counts_sorted, k)
+        if self.score_before_experts:
+            routed_in = _moe_ops().scale_rows(routed_in, scores_sorted, disp, ctx)
+        routed_out = self.experts(routed_in, local_counts)
+        routed_out = disp.combine(routed_out, ctx)
+
+        shared = self.shared_experts(x) if self.shared_experts is not None else None
+        weights = None if self.score_before_experts else top_scores
+        out = _moe_ops().scatter_combine(routed_out, order, weights, x.shape[0], k)
+        if shared is not None:
+            out = out + shared
+        return out.reshape(bs, slen, dim)
+
+    def init_weights(self, **kwargs) -> None:
+        init_std = kwargs.get("init_std")
+        buffer_device = kwargs.get("buffer_device")
+        assert init_std is not None
+        assert isinstance(buffer_device, torch.device)
+        self.experts.init_weights(init_std=init_std)
+        self.router.init_weights(init_std=init_std)
+        if self.shared_experts is not None:
+            self.shared_experts.init_weights(init_std=init_std)
+        with torch.device(buffer_device):
+            self.tokens_per_expert = torch.zeros(self.experts.num_experts, dtype=torch.float32)
+            if self.load_balance_coeff is not None:
+                self.expert_bias = torch.zeros(self.experts.num_experts, dtype=torch.float32)

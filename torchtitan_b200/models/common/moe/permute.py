@@ -1,0 +1,52 @@
+"""Index generation for regrouping all-to-all output by local expert.
+
+After expert-parallel dispatch a rank holds rows ordered ``[source rank][local expert]``;
+grouped GEMMs want ``[local expert][source rank]`` with every expert's block padded to a
+multiple of ``alignment`` rows. ``generate_permute_indices`` returns, for each padded output
+row, the input row it copies from (or -1 for padding).
+
+Parity: torchtitan/models/common/moe/kernels.py:108-218 (CPU definition ``fill_indices_cpu``
+and the wrapper's contract: int32 counts ``[ranks * experts_per_rank]``, output of length
+``max_len`` filled with -1, ``m_sizes``/``m_offsets`` per local expert). The CUDA version is a
+single counting kernel in ``csrc/moe.cu``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def fill_indices_cpu(tokens_per_expert_group, start_index_values, write_offsets,
+                     experts_per_rank: int, num_ranks: int, max_len: int):
+    out = torch.full((max_len,), -1, dtype=torch.int32)
+    for e in range(experts_per_rank):
+        w = int(write_offsets[e])
+        for r in range(num_ranks):
+            i = r * experts_per_rank + e
+            n = int(tokens_per_expert_group[i])
+            s = int(start_index_values[i])
+            if n > 0:
+                end = min(w + n, max_len)
+                out[w:end] = torch.arange(s, s + (end - w), dtype=torch.int32)
+            w += n
+    return out
+
+
+def generate_permute_indices(tokens_per_expert_group, experts_per_rank: int, num_ranks: int,
+                             max_len: int, alignment: int, use_cpu: bool | None = None):
+    """Returns (permuted_indices [max_len] int32, m_sizes [experts_per_rank] int32,
+    m_offsets [experts_per_rank] int32 = inclusive cumsum of m_sizes)."""
+    t = tokens_per_expert_group
+    start_index_values = torch.cumsum(t, 0) - t
+    total_per_expert = t.view(num_ranks, experts_per_rank).sum(0)
+    total_per_expert = torch.clamp_min(total_per_expert, alignment)
+    m_sizes = ((total_per_expert + alignment - 1) // alignment * alignment).to(torch.int32)
+    m_offsets = torch.cumsum(m_sizes, 0)
+    write_offsets = m_offsets - m_sizes
+    if t.is_cuda and not use_cpu:
+        from torchtitan_b200.ops import cuda_ops
+
+        idx = cuda_ops.moe_fill_indices(t, start_index_values, write_offsets, experts_per_rank, num_ranks, max_len)
+    else:
+        idx = fill_indices_cpu(t.cpu(), start_index_values.cpu(), write_offsets.cpu(), experts_per_rank, num_ranks, max_len).to(t.device)
+    return idx, m_sizes, m_offsets.to(torch.int32)

@@ -1,0 +1,167 @@
+"""Activation checkpointing: ``full``, ``selective`` by layer frequency, ``selective`` per op.
+
+Parity: torchtitan/distributed/activation_checkpoint.py:27-260. Per-op policy (:105-135): ops on
+the save list are kept, except that only every *second* matmul is kept; matmuls whose weight
+shape matches a Linear named in ``per_op_sac_force_recompute_mm_shapes_by_fqns`` are always
+recomputed (and do not advance the counter); device-to-host copies are always kept. The save list
+(torchtitan/models/llama3/parallelize.py:44-60) contains matmuls, attention outputs, max
+reductions and collective results (reduce-scatter / all-to-all outputs are saved rather than
+re-communicated).
+
+Built differently: a block's ``forward`` is wrapped in place (no wrapper module, so parameter
+names do not change), and the policy recognises both the ATen ops of the CPU path and this
+framework's ``tt_b200::*`` custom ops of the CUDA path.
+"""
+
+from __future__ import annotations
+
+import functools
+import os
+from collections import defaultdict
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import CheckpointPolicy, checkpoint, create_selective_checkpoint_contexts
+
+from torchtitan_b200.tools.logging import logger
+
+_layer_sac_count = 0
+
+
+def _resolve(names):
+    out = set()
+    for ns, name in names:
+        pkt = getattr(getattr(torch.ops, ns, None), name, None)
+        if pkt is None:
+            continue
+        try:
+            out.add(pkt.default)
+        except AttributeError:
+            pass
+    return out
+
+
+def default_op_sac_save_list() -> set:
+    """Compute-heavy ops whose outputs are kept for backward."""
+    aten = torch.ops.aten
+    ops = {
+        aten.mm.default, aten.linear.default, aten.addmm.default, aten.bmm.default,
+        aten._scaled_dot_product_efficient_attention.default,
+        aten._scaled_dot_product_flash_attention.default,
+        aten._scaled_dot_product_cudnn_attention.default,
+        aten._scaled_dot_product_attention_math.default,
+        aten._scaled_dot_product_flash_attention_for_cpu.default,
+        aten.max.default,
+    }
+    ops |= _resolve([
+        ("_c10d_functional", "reduce_scatter_tensor"), ("_c10d_functional", "all_to_all_single"),
+        ("tt_b200", "gemm"), ("tt_b200", "attention_fwd"), ("tt_b200", "grouped_gemm"),
+        ("tt_b200", "tp_reduce_scatter"), ("tt_b200", "ep_all_to_all"),
+    ])
+    return ops
+
+
+def _mm_ops() -> set:
+    aten = torch.ops.aten
+    return {aten.mm.default, aten.linear.default} | _resolve([("tt_b200", "gemm")])
+
+
+def _wrap_forward(module: nn.Module, ac_config, context_fn=None) -> nn.Module:
+    inner = module.forward
+    kwargs = dict(use_reentrant=False, preserve_rng_state=ac_config.preserve_rng_state,
+                  determinism_check=ac_config.determinism_check, debug=ac_config.debug)
+    if context_fn is not None:
+        kwargs["context_fn"] = context_fn
+
+    @functools.wraps(inner)
+    def forward(*args, **kw):
+        if not torch.is_grad_enabled():
+            return inner(*args, **kw)
+        prev = torch.utils.checkpoint._enable_checkpoint_early_stop if hasattr(torch.utils.checkpoint, "_enable_checkpoint_early_stop") else None
+        with torch.utils.checkpoint.set_checkpoint_early_stop(ac_config.early_stop):
+            return checkpoint(inner, *args, **kwargs, **kw)
+
+    module.forward = forward
+    module._ac_recomputes_forward = True
+    return module
+
+
+def _apply_full_ac(module, ac_config):
+    return _wrap_forward(module, ac_config)
+
+
+def _apply_layer_sac(module, ac_config):
+    global _layer_sac_count
+    _layer_sac_count += 1
+    freq = int(ac_config.selective_ac_option)
+    if not freq or _layer_sac_count % freq == 0:
+        return _wrap_forward(module, ac_config)
+    return module
+
+
+def _apply_op_sac(module, ac_config, *, base_fqn=None, op_sac_save_list=None):
+    save_list = op_sac_save_list or default_op_sac_save_list()
+    mm_ops = _mm_ops()
+    force = set()
+    for fqn, sub in module.named_modules():
+        full = f"{base_fqn}.{fqn}" if base_fqn is not None else fqn
+        if not any(f in full for f in ac_config.per_op_sac_force_recompute_mm_shapes_by_fqns):
+            continue
+        if not isinstance(sub, nn.Linear):
+            raise ValueError(f"per_op_sac_force_recompute_mm_shapes_by_fqns expected to match a nn.Linear, but got: {sub}")
+        out_f, in_f = sub.weight.shape
+        force.add((in_f, out_f))
+
+    def make_policy(meta):
+        def policy(ctx, func, *args, **kwargs):
+            if (func == torch.ops.aten._to_copy.default and "cuda" in str(args[0].device)
+                    and str(kwargs.get("device", "")) == "cpu"):
+                return CheckpointPolicy.MUST_SAVE
+            key = "recompute_mm_count" if ctx.is_recompute else "forward_mm_count"
+            if func in mm_ops:
+                w = args[1].shape
+                if func != torch.ops.aten.mm.default:  # linear-style ops carry the weight as [out, in]
+                    w = torch.Size((w[1], w[0]))
+                if tuple(w) in force:
+                    return CheckpointPolicy.PREFER_RECOMPUTE
+                meta[key] += 1
+            keep = func in save_list and not (func in mm_ops and meta[key] % 2 == 0)
+            return CheckpointPolicy.MUST_SAVE if keep else CheckpointPolicy.PREFER_RECOMPUTE
+
+        return policy
+
+    def context_fn():
+        return create_selective_checkpoint_contexts(make_policy(defaultdict(int)))
+
+    return _wrap_forward(module, ac_config, context_fn=context_fn)
+
+
+def _apply_ac_to_transformer_block(module, ac_config, *, base_fqn=None, model_compile_enabled=False, op_sac_save_list=None):
+    if ac_config.mode not in ("full", "selective"):
+        raise ValueError(f"Invalid AC mode: {ac_config.mode}. Valid modes: ('full', 'selective')")
+    if ac_config.mode == "full":
+        return _apply_full_ac(module, ac_config)
+    opt = ac_config.selective_ac_option
+    if opt == "op":
+        return _apply_op_sac(module, ac_config, base_fqn=base_fqn, op_sac_save_list=op_sac_save_list)
+    if opt.isdigit():
+        return _apply_layer_sac(module, ac_config)
+    raise ValueError(
+        f"Invalid selective AC option: {opt}. Valid options: 'op' or a positive int representing layer frequency"
+    )
+
+
+def apply_ac(model: nn.Module, ac_config, *, model_compile_enabled: bool = False, op_sac_save_list=None,
+             base_folder: str = "") -> None:
+    if ac_config.mode == "memory_budget":
+        raise NotImplementedError(
+            "activation_checkpoint.mode=memory_budget relies on a graph partitioner; this framework has no "
+            "tracing compiler. Use 'selective' (op or layer frequency) or 'full'."
+        )
+    layers = model.get_submodule("layers")
+    for layer_id, block in layers.named_children():
+        _apply_ac_to_transformer_block(
+            block, ac_config, base_fqn=f"layers.{layer_id}", model_compile_enabled=model_compile_enabled,
+            op_sac_save_list=op_sac_save_list,
+        )
+    logger.info(f"Applied {ac_config.mode} activation checkpointing to the model")

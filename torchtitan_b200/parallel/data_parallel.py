@@ -1,0 +1,84 @@
+"""Apply FSDP / HSDP / DDP to a decoder the way the reference groups parameters
+(torchtitan/models/llama3/parallelize.py:340-405): one unit for ``tok_embeddings``, one per
+transformer block, one for ``[norm, output]`` (kept gathered after forward because backward
+starts there), and a root unit for anything left."""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from torchtitan_b200.tools.logging import logger
+
+from .fsdp import MixedPrecisionPolicy, fully_shard, replicate
+from .fsdp_policy import get_fsdp_reshard_after_forward_policy
+
+
+def make_comm(dp_mesh, parallelism):
+    """Pick the transport for FSDP collectives: NVLink peer-memory kernels when every rank of the
+    shard mesh is a CUDA device of this host and the option is on, else c10d."""
+    if parallelism is not None and not getattr(parallelism, "fused_fsdp_collectives", True):
+        return None
+    if not torch.cuda.is_available() or dp_mesh is None:
+        return None
+    try:
+        from .nvlink_comm import NvlinkComm
+
+        return NvlinkComm.maybe_create(dp_mesh)
+    except ImportError:
+        return None
+
+
+def _compute_copy_bytes(model: nn.Module, dtype: torch.dtype) -> int:
+    return sum(p.numel() for p in model.parameters()) * torch.empty((), dtype=dtype).element_size()
+
+
+def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype: torch.dtype, pp_enabled: bool,
+               cpu_offload: bool = False, reshard_after_forward_policy: str = "default", parallelism=None,
+               extra_groups: dict | None = None):
+    mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
+    if cpu_offload:
+        raise NotImplementedError("training.enable_cpu_offload is not supported by this FSDP runtime")
+    reshard = get_fsdp_reshard_after_forward_policy(
+        reshard_after_forward_policy, pp_enabled, param_bytes=_compute_copy_bytes(model, param_dtype)
+    )
+    comm = make_comm(dp_mesh, parallelism)
+    kw = dict(mesh=dp_mesh, mp_policy=mp, comm=comm)
+    if getattr(model, "tok_embeddings", None) is not None:
+        fully_shard(model.tok_embeddings, **kw, reshard_after_forward=reshard)
+    for block in model.layers.values():
+        fully_shard(block, **kw, reshard_after_forward=reshard)
+    if getattr(model, "norm", None) is not None and getattr(model, "output", None) is not None:
+        fully_shard([model.norm, model.output], **kw, reshard_after_forward=reshard_after_forward_policy == "always")
+    fully_shard(model, **kw, reshard_after_forward=reshard)
+    logger.info(f"FSDP units: reshard_after_forward={reshard}, transport={'nvlink' if comm is not None else 'c10d'}")
+    return model
+
+
+def apply_replicate(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype: torch.dtype):
+    mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
+    kw = dict(mesh=dp_mesh, mp_policy=mp)
+    if getattr(model, "tok_embeddings", None) is not None:
+        replicate(model.tok_embeddings, **kw)
+    for block in model.layers.values():
+        replicate(block, **kw)
+    if getattr(model, "norm", None) is not None and getattr(model, "output", None) is not None:
+        replicate([model.norm, model.output], **kw)
+    replicate(model, **kw)
+    logger.info("Applied replicate to the model")
+    return model
+
+
+def apply_single_device_units(model: nn.Module, param_dtype: torch.dtype, reduce_dtype: torch.dtype):
+    """One GPU, no data parallelism: still use the unit machinery (fp32 master + bf16 compute
+    copy in flat buffers, fused optimizer), with a shard world of one and no collectives."""
+    mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
+    kw = dict(mesh=None, mp_policy=mp, reshard_after_forward=False)
+    if getattr(model, "tok_embeddings", None) is not None:
+        fully_shard(model.tok_embeddings, **kw)
+    for block in model.layers.values():
+        fully_shard(block, **kw)
+    if getattr(model, "norm", None) is not None and getattr(model, "output", None) is not None:
+        fully_shard([model.norm, model.output], **kw)
+    fully_shard(model, **kw)
+    return model

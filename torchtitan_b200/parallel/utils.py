@@ -1,0 +1,254 @@
+"""Distributed helpers: process-group start-up, determinism, scalar reductions, gradient
+clipping, train context.
+
+Parity: torchtitan/distributed/utils.py:30-543 -- ``dist_sum/max/mean`` (:30-58),
+``set_determinism`` (one seed broadcast from rank 0, made distinct per pipeline stage;
+deterministic algorithm switches, :92-207), ``init_distributed`` (NCCL or ``cuda:nccl,cpu:gloo``
+with Flight-Recorder environment, fake backend for dry runs, :251-363), ``set_pg_timeouts``
+(:366-394), ``clip_grad_norm_`` (total norm over sharded gradients, extra reduction over
+pipeline stages, :397-543), ``maybe_enable_amp`` (:228-248).
+"""
+
+from __future__ import annotations
+
+import contextlib
+import math
+import os
+from datetime import timedelta
+
+import torch
+import torch.distributed as dist
+from torch.distributed.tensor import DTensor
+
+from torchtitan_b200.tools.logging import logger
+from torchtitan_b200.tools.utils import device_module, device_type
+
+__all__ = [
+    "dist_sum", "dist_max", "dist_mean", "set_determinism", "init_distributed", "set_pg_timeouts",
+    "clip_grad_norm_", "maybe_enable_amp", "get_train_context", "create_context_parallel_ctx",
+]
+
+
+def _reduce(x, op, mesh, extra=None) -> float:
+    if isinstance(x, DTensor):
+        x = x.full_tensor()
+    x = x.detach().clone().float()
+    if mesh is not None:
+        dist.all_reduce(x, op=op, group=mesh.get_group() if hasattr(mesh, "get_group") else mesh)
+    if extra is not None:
+        dist.all_reduce(x, op=op, group=extra.get_group())
+    return x.item()
+
+
+def dist_sum(x: torch.Tensor, mesh, extra_pg=None) -> float:
+    return _reduce(x, dist.ReduceOp.SUM, mesh, extra_pg)
+
+
+def dist_max(x: torch.Tensor, mesh, extra_pg=None) -> float:
+    return _reduce(x, dist.ReduceOp.MAX, mesh, extra_pg)
+
+
+def dist_mean(x: torch.Tensor, mesh, extra_pg=None) -> float:
+    n = (mesh.size() if mesh is not None else 1) * (extra_pg.size() if extra_pg is not None else 1)
+    return _reduce(x, dist.ReduceOp.SUM, mesh, extra_pg) / n
+
+
+def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_seed_mesh_dims: list[str] | None = None) -> None:
+    """Same seed on all ranks except along ``distinct_seed_mesh_dims`` (default: pipeline)."""
+    distinct_seed_mesh_dims = ["pp"] if distinct_seed_mesh_dims is None else distinct_seed_mesh_dims
+    if debug_config.deterministic:
+        logger.info("Deterministic algorithm enabled (expect perf degradation).")
+        torch.use_deterministic_algorithms(True, warn_only=debug_config.deterministic_warn_only)
+        torch.backends.cudnn.deterministic = True
+        torch.backends.cudnn.benchmark = False
+        os.environ["CUBLAS_WORKSPACE_CONFIG"] = ":4096:8"
+    if debug_config.detect_anomaly:
+        torch.autograd.set_detect_anomaly(True, check_nan=False)
+    seed = debug_config.seed
+    world = parallel_dims.world_size
+    if seed is None:
+        t = torch.get_rng_state()[:8].to(device) if world > 1 and dist.is_initialized() else torch.get_rng_state()[:8]
+        if world > 1 and dist.is_initialized():
+            dist.broadcast(t, src=0)
+        seed = int(t.to("cpu").view(torch.uint64).item() % (2**63))
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    offset = 0
+    mult = 1
+    for name in distinct_seed_mesh_dims:
+        size = parallel_dims.dim_size(name)
+        if size > 1:
+            offset += parallel_dims.coordinate(name, rank) * mult
+            mult *= size
+    seed = (seed + offset) % 2**64
+    logger.debug(f"rank {rank}: seed {seed}")
+    torch.manual_seed(seed)
+    os.environ["PYTHONHASHSEED"] = str(seed % 2**32)
+
+
+def _flight_recorder_env(comm_config, base_folder: str) -> None:
+    def setdefault(k, v):
+        if k in os.environ:
+            logger.warning(f"ENV[{k}] = {os.environ[k]} will be overridden to {v} based on job config")
+        os.environ[k] = v
+
+    setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "3")
+    if comm_config.trace_buf_size > 0:
+        setdefault("TORCH_FR_BUFFER_SIZE", str(comm_config.trace_buf_size))
+        setdefault("TORCH_NCCL_DUMP_ON_TIMEOUT", "1")
+        dump_dir = os.path.join(base_folder, comm_config.save_traces_folder)
+        os.makedirs(dump_dir, exist_ok=True)
+        setdefault("TORCH_FR_DUMP_TEMP_FILE", os.path.join(dump_dir, comm_config.save_traces_file_prefix))
+
+
+def init_distributed(comm_config, enable_cpu_backend: bool = False, base_folder: str = "", ranks: list[int] | None = None) -> int:
+    """Start the default process group and return the world size."""
+    if comm_config.mode in ("fake_backend", "local_tensor"):
+        from torch.testing._internal.distributed.fake_pg import FakeStore
+
+        world = int(os.environ.get("NGPU", os.environ.get("WORLD_SIZE", "1")))
+        dist.init_process_group("fake", rank=0, world_size=world, store=FakeStore())
+        return world
+    if not ("RANK" in os.environ and "WORLD_SIZE" in os.environ):
+        # single process without a launcher
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29555")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        os.environ.setdefault("LOCAL_RANK", "0")
+    if device_type == "cuda":
+        _flight_recorder_env(comm_config, base_folder)
+        backend = "cuda:nccl,cpu:gloo" if enable_cpu_backend else "nccl"
+    else:
+        backend = "gloo"
+    kwargs = {}
+    if ranks is not None:
+        kwargs["_ranks"] = ranks
+    dist.init_process_group(backend=backend, timeout=timedelta(seconds=comm_config.init_timeout_seconds), **kwargs)
+    return dist.get_world_size()
+
+
+def set_pg_timeouts(timeout: timedelta, parallel_dims) -> None:
+    """Tighten collective timeouts after the first step (all ranks meet at a barrier first)."""
+    logger.info(f"Synchronizing and adjusting timeout for all ProcessGroups to {timeout}")
+    if device_type == "cuda":
+        device_module.synchronize()
+    dist.barrier(device_ids=[device_module.current_device()] if device_type == "cuda" else None)
+    if device_type == "cuda":
+        device_module.synchronize()
+    groups = [None] + [g for g in parallel_dims._groups.values() if g is not dist.group.WORLD]
+    for g in groups:
+        try:
+            dist.distributed_c10d._set_pg_timeout(timeout, g)
+        except Exception as e:  # gloo groups do not support changing the timeout
+            logger.debug(f"could not set timeout on {g}: {e}")
+
+
+def maybe_enable_amp(parallel_dims, mixed_precision_param: str, dev_type: str):
+    """FSDP handles mixed precision itself; without it (DDP / single device) use autocast."""
+    if parallel_dims.fsdp_enabled:
+        logger.info("Mixed precision training is handled by fully_shard")
+        return contextlib.nullcontext()
+    if parallel_dims.tp_enabled or parallel_dims.pp_enabled:
+        logger.warning("Mixed precision training with TP or PP is only supported when FSDP/HSDP/CP is enabled.")
+        logger.info("Mixed precision training is disabled")
+        return contextlib.nullcontext()
+    from torchtitan_b200.config import TORCH_DTYPE_MAP
+
+    logger.info("Mixed precision training is handled by AMP")
+    return torch.autocast(dev_type, dtype=TORCH_DTYPE_MAP[mixed_precision_param])
+
+
+def get_train_context(enable_loss_parallel: bool):
+    """Context factory entered around forward+loss+backward. Loss parallel is applied by the
+    vocab-parallel loss op itself in this framework, so the context only carries the flag."""
+
+    @contextlib.contextmanager
+    def ctx():
+        from torchtitan_b200.parallel import tp as _tp
+
+        prev = _tp.LOSS_PARALLEL.enabled
+        _tp.LOSS_PARALLEL.enabled = enable_loss_parallel
+        try:
+            yield
+        finally:
+            _tp.LOSS_PARALLEL.enabled = prev
+
+    return ctx
+
+
+def _local(t):
+    return t._local_tensor if isinstance(t, DTensor) else t
+
+
+@torch.no_grad()
+def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, error_if_nonfinite: bool = False,
+                    foreach: bool | None = None, pp_mesh=None, ep_enabled: bool = False) -> torch.Tensor:
+    """Clip the global gradient norm of (sharded) parameters; returns the total norm.
+
+    Each rank computes the norm of its *local* shards; the partial norms are combined over every
+    mesh dimension on which a gradient is sharded (read from the DTensor placements; tagged
+    tensor/expert-parallel shards add their groups) and over pipeline stages. FSDP units
+    contribute one fused sum-of-squares launch over their flat gradient shard.
+    """
+    from torchtitan_b200.ops import optim_ops
+    from torchtitan_b200.parallel.fsdp import FSDPUnit
+
+    if isinstance(parameters, torch.Tensor):
+        parameters = [parameters]
+    params = [p for p in parameters if p.grad is not None]
+    if not params:
+        return torch.tensor(0.0)
+    norm_type = float(norm_type)
+    inf = math.isinf(norm_type)
+    # group local partial norms by the set of process groups over which they must be summed
+    buckets: dict[tuple, list] = {}
+    group_objs: dict[int, object] = {}
+    units_done: dict[int, FSDPUnit] = {}
+    for p in params:
+        g = p.grad
+        groups = []
+        if isinstance(g, DTensor):
+            for i, pl in enumerate(g.placements):
+                if pl.is_shard() or pl.is_partial():
+                    groups.append(g.device_mesh.get_group(i))
+        for extra in getattr(p, "_extra_norm_groups", ()):  # TP / EP shards kept as local tensors
+            groups.append(extra)
+        key = tuple(sorted(id(x) for x in groups))
+        for x in groups:
+            group_objs[id(x)] = x
+        buckets.setdefault(key, []).append(_local(g))
+    device = _local(params[0].grad).device
+    total = torch.zeros((), dtype=torch.float32, device=device)
+    for key, grads in buckets.items():
+        if inf:
+            part = torch.stack([g.detach().abs().max().float() if g.numel() else torch.zeros((), device=device) for g in grads]).max()
+        elif norm_type == 2.0:
+            part = torch.zeros((), dtype=torch.float32, device=device)
+            for g in grads:
+                if g.numel():
+                    part = part + optim_ops.sumsq(g.reshape(-1) if g.is_contiguous() else g.contiguous().view(-1))
+        else:
+            part = torch.stack([torch.linalg.vector_norm(g.float(), norm_type) ** norm_type for g in grads if g.numel()]).sum() \
+                if any(g.numel() for g in grads) else torch.zeros((), device=device)
+        for gid in key:
+            dist.all_reduce(part, op=dist.ReduceOp.MAX if inf else dist.ReduceOp.SUM, group=group_objs[gid])
+        total = torch.maximum(total, part) if inf else total + part
+    if pp_mesh is not None:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX if inf else dist.ReduceOp.SUM, group=pp_mesh.get_group())
+    total_norm = total if inf else total ** (1.0 / norm_type)
+    if error_if_nonfinite and not torch.isfinite(total_norm):
+        raise RuntimeError(f"The total norm of order {norm_type} for gradients is non-finite")
+    coef = torch.clamp(max_norm / (total_norm + 1e-6), max=1.0)
+    seen = set()
+    for p in params:
+        g = _local(p.grad)
+        base = g.untyped_storage().data_ptr()
+        if (base, g.storage_offset(), g.numel()) in seen:
+            continue
+        seen.add((base, g.storage_offset(), g.numel()))
+        g.mul_(coef.to(g.dtype))
+    return total_norm
+
+
+def create_context_parallel_ctx(*args, **kwargs):
+    raise NotImplementedError("context parallel is applied by parallel.cp.apply_cp_to_attention_module")

@@ -1,0 +1,35 @@
+"""``ModelSpec``: everything the Trainer needs to know about one model flavor.
+
+Parity: torchtitan/protocols/model_spec.py:28-51.
+"""
+
+from collections.abc import Callable
+from dataclasses import dataclass
+from typing import Any
+
+import torch.nn as nn
+
+from .model import BaseModel
+from .state_dict_adapter import BaseStateDictAdapter
+
+ParallelizeFunction = Callable[..., nn.Module]
+PipeliningFunction = Callable[..., tuple]
+LossFunctionBuilder = Callable[..., Callable]
+PostOptimizerBuildFn = Callable[..., None]
+
+
+@dataclass
+class ModelSpec:
+    name: str
+    flavor: str
+    model: BaseModel.Config
+    parallelize_fn: ParallelizeFunction
+    pipelining_fn: PipeliningFunction | None
+    build_loss_fn: LossFunctionBuilder
+    post_optimizer_build_fn: PostOptimizerBuildFn | None = None
+    state_dict_adapter: type[BaseStateDictAdapter] | None = None
+
+
+@dataclass
+class FaultTolerantModelSpec(ModelSpec):
+    fragment_fn: Callable[..., Any] | None = None
