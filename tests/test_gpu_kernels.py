@@ -1,0 +1,193 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 definition of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from torchtitan_b200.ops import cuda_ops, native
+
+    native.lib()
+    return cuda_ops
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / max(b.float().abs().max().item(), 1e-6)
+
+
+def _no_kernel_errors():
+    from torchtitan_b200.ops import native
+
+    torch.cuda.synchronize()
+    assert not native.kernel_errors()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 192), (384, 768, 1024), (200, 264, 136), (4096, 4096, 1024)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm(ops, M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    want = a.float() @ b.float().t()
+    A = a.t().contiguous() if a_mn else a
+    Bm = b.t().contiguous() if b_mn else b
+    got = ops.gemm(A, Bm, a_mn, b_mn, False)
+    got32 = ops.gemm(A, Bm, a_mn, b_mn, True)
+    _no_kernel_errors()
+    assert _rel(got32, want) < 2e-3, _rel(got32, want)
+    assert _rel(got, want) < 1e-2, _rel(got, want)
+
+
+def test_gemm_accumulate_and_strided(ops):
+    torch.manual_seed(1)
+    a = torch.randn(256, 512, device="cuda").bfloat16()
+    b = torch.randn(384, 512, device="cuda").bfloat16()
+    big = torch.zeros(256, 1024, device="cuda", dtype=torch.float32)
+    out = big[:, 128 : 128 + 384]
+    ops.gemm_into(a, b, out)
+    ops.gemm_into(a, b, out, accumulate=True)
+    _no_kernel_errors()
+    want = 2 * (a.float() @ b.float().t())
+    assert _rel(out, want) < 2e-3
+    assert big[:, :128].abs().max() == 0 and big[:, 512:].abs().max() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,D", [(64, 4096), (1000, 128), (33, 2048), (4096, 512)])
+def test_rmsnorm(ops, dtype, rows, D):
+    torch.manual_seed(0)
+    x = torch.randn(rows, D, device="cuda", dtype=dtype, requires_grad=True)
+    w = (torch.randn(D, device="cuda") * 0.1 + 1).to(dtype).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    yr.backward(g.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    assert _rel(y, yr) < tol
+    assert _rel(x.grad, xr.grad) < tol
+    assert _rel(w.grad, wr.grad) < (3e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+@pytest.mark.parametrize("layout", ["interleaved", "half"])
+@pytest.mark.parametrize("use_pos", [False, True])
+def test_rope(ops, layout, use_pos):
+    from torchtitan_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    B, S, H, D = 2, 96, 4, 128
+    x = torch.randn(B, S, H, D, device="cuda").bfloat16().requires_grad_()
+    ang = torch.randn(256, D // 2, device="cuda")
+    table = torch.stack((ang.cos(), ang.sin()), -1).contiguous()
+    pos = torch.randint(0, 256, (B, S), device="cuda") if use_pos else None
+    y = ops.rope(x, table, pos, layout)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = ref.rope(xr, table, pos, layout)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1e-2
+
+
+def test_swiglu(ops):
+    torch.manual_seed(0)
+    g = torch.randn(300, 1024, device="cuda").bfloat16().requires_grad_()
+    u = torch.randn(300, 1024, device="cuda").bfloat16().requires_grad_()
+    y = ops.swiglu(g, u)
+    d = torch.randn_like(y)
+    y.backward(d)
+    gr, ur = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
+    yr = torch.nn.functional.silu(gr) * ur
+    yr.backward(d.float())
+    assert _rel(y, yr) < 1e-2 and _rel(g.grad, gr.grad) < 1.5e-2 and _rel(u.grad, ur.grad) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_and_logprobs(ops, dtype):
+    torch.manual_seed(0)
+    rows, V = 257, 4104
+    logits = (torch.randn(rows, V, device="cuda") * 3).to(dtype).requires_grad_()
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    labels[::7] = -100
+    loss = ops.cross_entropy_sum(logits, labels, -100)
+    (loss * 0.37).backward()
+    lr = logits.detach().float().requires_grad_()
+    want = torch.nn.functional.cross_entropy(lr, labels, reduction="sum", ignore_index=-100)
+    (want * 0.37).backward()
+    assert abs(loss.item() - want.item()) / want.item() < 1e-4
+    assert _rel(logits.grad, lr.grad) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+    # log-probs
+    labels2 = torch.randint(0, V, (rows,), device="cuda")
+    l2 = logits.detach().clone().requires_grad_()
+    lp = ops.token_logprobs(l2, labels2)
+    w = torch.randn(rows, device="cuda")
+    (lp * w).sum().backward()
+    l3 = logits.detach().float().requires_grad_()
+    lpr = torch.log_softmax(l3, -1).gather(-1, labels2[:, None]).squeeze(-1)
+    (lpr * w).sum().backward()
+    assert (lp - lpr).abs().max() < 1e-3
+    assert _rel(l2.grad, l3.grad) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+def test_adamw_and_sumsq(ops):
+    torch.manual_seed(0)
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 0.1
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    shadow = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 4):
+        ops.adamw_flat(p, g, m, v, shadow, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+        ref_p.grad = g.clone()
+        opt.step()
+    assert (p - ref_p.detach()).abs().max() < 1e-5
+    assert (shadow.float() - p).abs().max() < 2e-2
+    s = ops.sumsq(g)
+    assert abs(s.item() - g.double().pow(2).sum().item()) / s.item() < 1e-5
+
+
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 1024, 8, 2), (1, 384, 4, 1)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention(ops, B, S, H, Hkv, causal):
+    from torchtitan_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    D = 128
+    q = torch.randn(B, S, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    assert ops.attention_supported(q, k)
+    o, lse = ops.attention(q, k, v, causal=causal, return_lse=True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _no_kernel_errors()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    g = H // Hkv
+    s = torch.einsum("bqhd,bkhd->bhqk", qr, kr.repeat_interleave(g, 2)) / math.sqrt(D)
+    if causal:
+        s = s.masked_fill(torch.ones(S, S, device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+    lser = torch.logsumexp(s, -1)
+    orf = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), vr.repeat_interleave(g, 2))
+    orf.backward(do.float())
+    assert _rel(o, orf) < 2e-2, _rel(o, orf)
+    assert (lse - lser).abs().max() < 2e-2
+    assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+
+
+def test_smoke_step():
+    from torchtitan_b200.tools.smoke import run_smoke
+
+    loss = run_smoke()
+    assert 0 < loss < 12

@@ -1,0 +1,733 @@
+// Causal / full softmax attention with grouped KV heads on tcgen05 tensor cores.
+//
+// Layout: q,o,dO,dq [B,Sq,H,D]; k,v,dk,dv [B,Sk,Hkv,D]; D = 128; lse, delta [B,H,Sq] fp32.
+// All tiles are fetched with 3-D TMA descriptors (D, heads, B*S) straight from that layout, so no
+// transposed copies of q/k/v exist anywhere.
+//
+// forward   (CTA = 128 query rows of one head, two CTAs per SM): S = Q K^T into TMEM, one softmax
+//           thread per query row reads its row (no shuffles), P goes to shared memory as the A
+//           operand of O += P V; O stays in TMEM and is rescaled only when the running maximum grew
+//           by more than 2^8 (exact: the final division uses the same reference maximum).
+// backward  is split into two kernels without atomics, so it is deterministic:
+//           dkv kernel (CTA = 128 key rows of one KV head) loops over the query tiles and the query
+//           heads of the group: S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q;
+//           dq  kernel (CTA = 128 query rows) loops over key tiles: S, dP, dQ += dS K.
+// Every mbarrier wait is bounded (see ptx.cuh).
+//
+// Replaces F.scaled_dot_product_attention (cuDNN / flash) used by the reference
+// (torchtitan/models/common/attention.py:176-212).
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int D = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+__device__ int g_attn_error = 0;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct AttnArgs {
+  int B, Sq, Sk, H, Hkv;
+  int causal;
+  float scale;          // softmax scale
+  void* out;            // fwd: O bf16 ; dq kernel: dQ bf16 ; dkv kernel: dK bf16
+  void* out2;           // dkv kernel: dV bf16
+  float* lse;           // [B,H,Sq]
+  const float* delta;   // [B,H,Sq]
+};
+
+// Write 64 fp32 values as one 128-byte bf16 row of a K-major, 128B-swizzled operand tile.
+__device__ __forceinline__ void store_row_sw128(uint8_t* tile, int row, const float (&v)[64]) {
+  uint8_t* r = tile + row * 128;
+  const int x = row & 7;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = tt::pack_bf16(v[8 * c + 0], v[8 * c + 1]);
+    q.y = tt::pack_bf16(v[8 * c + 2], v[8 * c + 3]);
+    q.z = tt::pack_bf16(v[8 * c + 4], v[8 * c + 5]);
+    q.w = tt::pack_bf16(v[8 * c + 6], v[8 * c + 7]);
+    *reinterpret_cast<uint4*>(r + ((c ^ x) << 4)) = q;
+  }
+}
+
+// ---- UMMA helpers for the fixed tile shapes used here -------------------------------------------
+// K-major operand made of two 64-wide halves along the contraction (head dim 128): rows x 128 bf16,
+// half h at base + h * rows*128 bytes. Contraction step kk (16 wide), kk in [0, 8).
+__device__ __forceinline__ uint64_t desc_kmajor_dh(uint32_t base, int rows, int kk) {
+  return tt::umma_smem_desc(base + (kk >> 2) * rows * 128 + (kk & 3) * 32, 1, 64);
+}
+// K-major operand with a 64-wide contraction (one swizzle atom): step kk in [0, 4).
+__device__ __forceinline__ uint64_t desc_kmajor_64(uint32_t base, int kk) {
+  return tt::umma_smem_desc(base + kk * 32, 1, 64);
+}
+// MN-major operand: image is [krows rows][128 B] per 64-wide MN half; halves krows*128 bytes apart.
+// Contraction step kk (16 rows each).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int krows, int kk) {
+  return tt::umma_smem_desc(base + kk * 2048, (krows * 128) >> 4, 64);
+}
+
+constexpr uint32_t IDESC_128x64_KK = tt::umma_idesc_bf16(128, 64, 0, 0);
+constexpr uint32_t IDESC_128x128_KM = tt::umma_idesc_bf16(128, 128, 0, 1);
+
+// =================================================================================== forward
+// smem: Q 32K | K 2x16K | V 16K | P 16K | barriers  (small enough for two CTAs per SM)
+constexpr uint32_t F_Q = 0, F_K = 32768, F_V = F_K + 32768, F_P = F_V + 16384, F_BAR = F_P + 16384;
+constexpr size_t FWD_SMEM = 1024 + F_BAR + 256;
+
+__global__ void __launch_bounds__(192, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t bar0 = base + F_BAR;
+  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5 v_full | 7 v_empty | 9,10 s_full | 11 p_ready | 12 pv_done
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + F_BAR + 8 * 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + F_BAR + 8 * 13 + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = qt * 128;
+  const int off = p.Sk - p.Sq;  // query i attends keys <= i + off
+  int n_kv = p.Sk / 64;
+  if (p.causal) n_kv = min(n_kv, (q0 + 127 + off) / 64 + 1);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 13; ++i) tt::mbar_init(bar(i), i == 11 ? 4 : 1);
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+    tt::tma_prefetch_desc(&tq); tt::tma_prefetch_desc(&tk); tt::tma_prefetch_desc(&tv);
+  }
+  if (warp == 1) { tt::tmem_alloc(tt::smem_u32(tmem_slot), 256); tt::tmem_relinquish(); }
+  tt::tc_fence_before();
+  __syncthreads();
+  tt::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;  // S buffers at cols 0 and 64, O at 128..255
+
+  if (warp == 0) {
+    if (tt::elect_one()) {
+      tt::mbar_expect_tx(bar(0), 32768);
+      tt::tma_load_3d(base + F_Q, &tq, bar(0), 0, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + F_Q + 16384, &tq, bar(0), 64, h, b * p.Sq + q0);
+      auto load_k = [&](int j) -> bool {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 11)) return false;
+        tt::mbar_expect_tx(bar(1 + s), 16384);
+        tt::tma_load_3d(base + F_K + s * 16384, &tk, bar(1 + s), 0, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + F_K + s * 16384 + 8192, &tk, bar(1 + s), 64, hk, b * p.Sk + j * 64);
+        return true;
+      };
+      bool ok = n_kv > 0 ? load_k(0) : true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv && !load_k(j + 1)) break;  // K runs one tile ahead of V
+        if (!tt::mbar_wait(bar(7), (j & 1) ^ 1, abort_flag, &g_attn_error, 12)) break;
+        tt::mbar_expect_tx(bar(5), 16384);
+        tt::tma_load_3d(base + F_V, &tv, bar(5), 0, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + F_V + 8192, &tv, bar(5), 64, hk, b * p.Sk + j * 64);
+      }
+    }
+  } else if (warp == 1) {
+    if (tt::elect_one()) {
+      bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 13);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t kb = base + F_K + s * 16384;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tS + s * 64, desc_kmajor_dh(base + F_Q, 128, kk), desc_kmajor_dh(kb, 64, kk),
+                          IDESC_128x64_KK, kk != 0);
+        tt::umma_commit(bar(9 + s));   // S ready
+        tt::umma_commit(bar(3 + s));   // K stage free
+      };
+      if (ok && n_kv > 0) {
+        ok = tt::mbar_wait(bar(1), 0, abort_flag, &g_attn_error, 14);
+        if (ok) { tt::tc_fence_after(); issue_s(0); }
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int s1 = (j + 1) & 1;
+          if (!tt::mbar_wait(bar(1 + s1), ((j + 1) >> 1) & 1, abort_flag, &g_attn_error, 15)) break;
+          tt::tc_fence_after();
+          issue_s(j + 1);
+        }
+        const int s = j & 1;
+        if (!tt::mbar_wait(bar(11), j & 1, abort_flag, &g_attn_error, 16)) break;
+        if (!tt::mbar_wait(bar(5), j & 1, abort_flag, &g_attn_error, 17)) break;
+        tt::tc_fence_after();
+        const uint32_t vb = base + F_V;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tt::umma_f16_ss(tO, desc_kmajor_64(base + F_P, kk), desc_mnmajor(vb, 64, kk), IDESC_128x128_KM,
+                          (j | kk) != 0);
+        tt::umma_commit(bar(12));      // O updated, P free
+        tt::umma_commit(bar(7));       // V buffer free
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax: one thread per query row
+    const int lg = warp & 3;                 // TMEM lane group of this warp
+    const int row = lg * 32 + lane;          // query row inside the tile
+    const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+    const int qi = q0 + row;
+    const float sc = p.scale * kLog2e;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int s = j & 1;
+      if (!tt::mbar_wait(bar(9 + s), (j >> 1) & 1, abort_flag, &g_attn_error, 18)) { ok = false; break; }
+      tt::tc_fence_after();
+      float x[64];
+      {
+        uint32_t r[32];
+        tt::tmem_ld_32x32(tS + lane_off + s * 64, r);
+        tt::tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) x[e] = __uint_as_float(r[e]) * sc;
+        tt::tmem_ld_32x32(tS + lane_off + s * 64 + 32, r);
+        tt::tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) x[32 + e] = __uint_as_float(r[e]) * sc;
+      }
+      const int kv0 = j * 64;
+      if (p.causal && kv0 + 63 > q0 + off) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) if (kv0 + e > qi + off) x[e] = -INFINITY;
+      }
+      float mx = x[0];
+#pragma unroll
+      for (int e = 1; e < 64; ++e) mx = fmaxf(mx, x[e]);
+      // P buffer (and O) are free once the previous P*V has completed
+      if (j > 0 && !tt::mbar_wait(bar(12), (j - 1) & 1, abort_flag, &g_attn_error, 19)) { ok = false; break; }
+      tt::tc_fence_after();
+      const bool first = (j == 0);
+      const bool grow = !first && (mx > m_ref + 8.f);
+      if (first) m_ref = mx;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float f = fast_exp2(m_ref - m_new);  // 1 when this row did not grow
+        m_ref = m_new;
+        l *= f;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[16];
+          tt::tmem_ld_32x16(tO + lane_off + c * 16, r);
+          tt::tc_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * f);
+          tt::tmem_st_32x16(tO + lane_off + c * 16, r);
+        }
+        tt::tc_wait_st();
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 64; ++e) { x[e] = fast_exp2(x[e] - m_ref); sum += x[e]; }
+      l += sum;
+      store_row_sw128(gbase + F_P, row, x);
+      tt::fence_proxy_async();
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(bar(11));
+    }
+    if (ok && n_kv > 0) ok = tt::mbar_wait(bar(12), (n_kv - 1) & 1, abort_flag, &g_attn_error, 20);
+    tt::tc_fence_after();
+    if (ok) {
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) +
+                            ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (n_kv > 0) { tt::tmem_ld_32x32(tO + lane_off + c * 32, r); tt::tc_wait_ld(); }
+        else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0;
+        }
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 q;
+          q.x = tt::pack_bf16(__uint_as_float(r[8 * v4 + 0]) * inv, __uint_as_float(r[8 * v4 + 1]) * inv);
+          q.y = tt::pack_bf16(__uint_as_float(r[8 * v4 + 2]) * inv, __uint_as_float(r[8 * v4 + 3]) * inv);
+          q.z = tt::pack_bf16(__uint_as_float(r[8 * v4 + 4]) * inv, __uint_as_float(r[8 * v4 + 5]) * inv);
+          q.w = tt::pack_bf16(__uint_as_float(r[8 * v4 + 6]) * inv, __uint_as_float(r[8 * v4 + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = q;
+        }
+      }
+      if (p.lse) p.lse[(static_cast<long long>(b) * p.H + h) * p.Sq + qi] = (l > 0.f) ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+    }
+    tt::tc_fence_before();
+  }
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  if (warp == 1) { tt::tc_fence_after(); tt::tmem_dealloc(tmem, 256); }
+}
+
+// =================================================================================== backward: dQ
+// CTA = 128 query rows. smem: Q 32K | dO 32K | K 2x16K | V 2x16K | dS 2x16K | barriers
+constexpr uint32_t Q_Q = 0, Q_DO = 32768, Q_K = 65536, Q_V = Q_K + 32768, Q_DS = Q_V + 32768, Q_BAR = Q_DS + 32768;
+constexpr size_t DQ_SMEM = 1024 + Q_BAR + 256;
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
+                   const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t bar0 = base + Q_BAR;
+  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 sp_full | 7,8 ds_ready | 9,10 ds_free(dq step done)
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + Q_BAR + 8 * 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + Q_BAR + 8 * 11 + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = qt * 128;
+  const int off = p.Sk - p.Sq;
+  int n_kv = p.Sk / 64;
+  if (p.causal) n_kv = min(n_kv, (q0 + 127 + off) / 64 + 1);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 11; ++i) tt::mbar_init(bar(i), (i == 7 || i == 8) ? 4 : 1);
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+  }
+  if (warp == 1) { tt::tmem_alloc(tt::smem_u32(tmem_slot), 512); tt::tmem_relinquish(); }
+  tt::tc_fence_before();
+  __syncthreads();
+  tt::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // TMEM columns: S[2] at 0,64 | dP[2] at 128,192 | dQ at 256..383
+  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+
+  if (warp == 0) {
+    if (tt::elect_one()) {
+      tt::mbar_expect_tx(bar(0), 65536);
+      tt::tma_load_3d(base + Q_Q, &tq, bar(0), 0, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + Q_Q + 16384, &tq, bar(0), 64, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + Q_DO, &tdo, bar(0), 0, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + Q_DO + 16384, &tdo, bar(0), 64, h, b * p.Sq + q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 21)) break;
+        tt::mbar_expect_tx(bar(1 + s), 32768);
+        tt::tma_load_3d(base + Q_K + s * 16384, &tk, bar(1 + s), 0, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + Q_K + s * 16384 + 8192, &tk, bar(1 + s), 64, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + Q_V + s * 16384, &tv, bar(1 + s), 0, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + Q_V + s * 16384 + 8192, &tv, bar(1 + s), 64, hk, b * p.Sk + j * 64);
+      }
+    }
+  } else if (warp == 1) {
+    if (tt::elect_one()) {
+      bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 22);
+      auto issue_sp = [&](int j) {
+        const int s = j & 1;
+        const uint32_t kb = base + Q_K + s * 16384, vb = base + Q_V + s * 16384;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tS + s * 64, desc_kmajor_dh(base + Q_Q, 128, kk), desc_kmajor_dh(kb, 64, kk), IDESC_128x64_KK, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tDP + s * 64, desc_kmajor_dh(base + Q_DO, 128, kk), desc_kmajor_dh(vb, 64, kk), IDESC_128x64_KK, kk != 0);
+        tt::umma_commit(bar(5 + s));
+      };
+      if (ok && n_kv > 0) {
+        ok = tt::mbar_wait(bar(1), 0, abort_flag, &g_attn_error, 23);
+        if (ok) { tt::tc_fence_after(); issue_sp(0); }
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int s1 = (j + 1) & 1;
+          if (!tt::mbar_wait(bar(1 + s1), ((j + 1) >> 1) & 1, abort_flag, &g_attn_error, 24)) break;
+          tt::tc_fence_after();
+          issue_sp(j + 1);
+        }
+        const int s = j & 1;
+        if (!tt::mbar_wait(bar(7 + s), (j >> 1) & 1, abort_flag, &g_attn_error, 25)) break;
+        tt::tc_fence_after();
+        const uint32_t kb = base + Q_K + s * 16384;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tt::umma_f16_ss(tDQ, desc_kmajor_64(base + Q_DS + s * 16384, kk), desc_mnmajor(kb, 64, kk), IDESC_128x128_KM, (j | kk) != 0);
+        tt::umma_commit(bar(9 + s));   // dS buffer s free, dQ step done
+        tt::umma_commit(bar(3 + s));   // K/V stage free
+      }
+    }
+  } else {
+    const int lg = warp & 3, row = lg * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+    const int qi = q0 + row;
+    const long long stat = (static_cast<long long>(b) * p.H + h) * p.Sq + qi;
+    const float lse2 = p.lse[stat] * kLog2e;
+    const float dl = p.delta[stat];
+    const float sc = p.scale * kLog2e;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int s = j & 1;
+      if (!tt::mbar_wait(bar(5 + s), (j >> 1) & 1, abort_flag, &g_attn_error, 26)) { ok = false; break; }
+      tt::tc_fence_after();
+      float ds[64];
+      const int kv0 = j * 64;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rp[32];
+        tt::tmem_ld_32x32(tS + lane_off + s * 64 + half * 32, rs);
+        tt::tmem_ld_32x32(tDP + lane_off + s * 64 + half * 32, rp);
+        tt::tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kv = kv0 + half * 32 + e;
+          float pr = fast_exp2(__uint_as_float(rs[e]) * sc - lse2);
+          if (p.causal && kv > qi + off) pr = 0.f;
+          ds[half * 32 + e] = pr * (__uint_as_float(rp[e]) - dl) * p.scale;
+        }
+      }
+      if (j >= 2 && !tt::mbar_wait(bar(9 + s), ((j - 2) >> 1) & 1, abort_flag, &g_attn_error, 27)) { ok = false; break; }
+      store_row_sw128(gbase + Q_DS + s * 16384, row, ds);
+      tt::fence_proxy_async();
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(bar(7 + s));
+    }
+    if (ok && n_kv > 0) ok = tt::mbar_wait(bar(9 + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag, &g_attn_error, 28);
+    tt::tc_fence_after();
+    if (ok) {
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (n_kv > 0) { tt::tmem_ld_32x32(tDQ + lane_off + c * 32, r); tt::tc_wait_ld(); }
+        else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0;
+        }
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          uint4 q;
+          q.x = tt::pack_bf16(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
+          q.y = tt::pack_bf16(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
+          q.z = tt::pack_bf16(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
+          q.w = tt::pack_bf16(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
+          *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = q;
+        }
+      }
+    }
+    tt::tc_fence_before();
+  }
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  if (warp == 1) { tt::tc_fence_after(); tt::tmem_dealloc(tmem, 512); }
+}
+
+// =================================================================================== backward: dK, dV
+// CTA = 128 key rows of one KV head; steps over (query head of the group, 64-row query tile).
+// smem: K 32K | V 32K | Q 2x16K | dO 2x16K | P^T 2x16K | dS^T 2x16K | per-warp lse/delta 4x2x(64+64) floats | barriers
+constexpr uint32_t K_K = 0, K_V = 32768, K_Q = 65536, K_DO = K_Q + 32768, K_PT = K_DO + 32768, K_DST = K_PT + 32768,
+                   K_STAT = K_DST + 32768, K_BAR = K_STAT + 4096;
+constexpr size_t DKV_SMEM = 1024 + K_BAR + 256;
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
+                    const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, AttnArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t bar0 = base + K_BAR;
+  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5,6 st_full | 7,8 pt_ready | 9,10 pt_free
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + K_BAR + 8 * 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + K_BAR + 8 * 11 + 8);
+  float* stat_all = reinterpret_cast<float*>(gbase + K_STAT);  // [4 warps][2 stages][lse 64 | delta 64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int kv0 = kt * 128;
+  const int off = p.Sk - p.Sq;
+  const int nq_tiles = p.Sq / 64;
+  int qt_first = 0;
+  if (p.causal) { const int first_q = kv0 - off; qt_first = first_q > 0 ? first_q / 64 : 0; }
+  const int per_head = nq_tiles > qt_first ? nq_tiles - qt_first : 0;
+  const int n_steps = per_head * G;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 11; ++i) tt::mbar_init(bar(i), (i == 7 || i == 8) ? 4 : 1);
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+  }
+  if (warp == 1) { tt::tmem_alloc(tt::smem_u32(tmem_slot), 512); tt::tmem_relinquish(); }
+  tt::tc_fence_before();
+  __syncthreads();
+  tt::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // TMEM columns: S^T[2] at 0,64 | dP^T[2] at 128,192 | dV 256..383 | dK 384..511
+  const uint32_t tST = tmem, tDPT = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
+
+  if (warp == 0) {
+    if (tt::elect_one()) {
+      tt::mbar_expect_tx(bar(0), 65536);
+      tt::tma_load_3d(base + K_K, &tk, bar(0), 0, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_K + 16384, &tk, bar(0), 64, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_V, &tv, bar(0), 0, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_V + 16384, &tv, bar(0), 64, hk, b * p.Sk + kv0);
+      for (int st = 0; st < n_steps; ++st) {
+        const int s = st & 1; const uint32_t ph = (st >> 1) & 1;
+        const int h = hk * G + st / per_head, qt = qt_first + st % per_head;
+        if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 31)) break;
+        tt::mbar_expect_tx(bar(1 + s), 32768);
+        tt::tma_load_3d(base + K_Q + s * 16384, &tq, bar(1 + s), 0, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(base + K_Q + s * 16384 + 8192, &tq, bar(1 + s), 64, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(base + K_DO + s * 16384, &tdo, bar(1 + s), 0, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(base + K_DO + s * 16384 + 8192, &tdo, bar(1 + s), 64, h, b * p.Sq + qt * 64);
+      }
+    }
+  } else if (warp == 1) {
+    if (tt::elect_one()) {
+      bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 32);
+      auto issue_st = [&](int st) {
+        const int s = st & 1;
+        const uint32_t qb = base + K_Q + s * 16384, dob = base + K_DO + s * 16384;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tST + s * 64, desc_kmajor_dh(base + K_K, 128, kk), desc_kmajor_dh(qb, 64, kk), IDESC_128x64_KK, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tDPT + s * 64, desc_kmajor_dh(base + K_V, 128, kk), desc_kmajor_dh(dob, 64, kk), IDESC_128x64_KK, kk != 0);
+        tt::umma_commit(bar(5 + s));
+      };
+      if (ok && n_steps > 0) {
+        ok = tt::mbar_wait(bar(1), 0, abort_flag, &g_attn_error, 33);
+        if (ok) { tt::tc_fence_after(); issue_st(0); }
+      }
+      for (int st = 0; st < n_steps && ok; ++st) {
+        if (st + 1 < n_steps) {
+          const int s1 = (st + 1) & 1;
+          if (!tt::mbar_wait(bar(1 + s1), ((st + 1) >> 1) & 1, abort_flag, &g_attn_error, 34)) break;
+          tt::tc_fence_after();
+          issue_st(st + 1);
+        }
+        const int s = st & 1;
+        if (!tt::mbar_wait(bar(7 + s), (st >> 1) & 1, abort_flag, &g_attn_error, 35)) break;
+        tt::tc_fence_after();
+        const uint32_t qb = base + K_Q + s * 16384, dob = base + K_DO + s * 16384;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tt::umma_f16_ss(tDV, desc_kmajor_64(base + K_PT + s * 16384, kk), desc_mnmajor(dob, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tt::umma_f16_ss(tDK, desc_kmajor_64(base + K_DST + s * 16384, kk), desc_mnmajor(qb, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+        tt::umma_commit(bar(9 + s));   // P^T / dS^T buffers s free
+        tt::umma_commit(bar(3 + s));   // Q / dO stage free
+      }
+    }
+  } else {
+    const int lg = warp & 3, row = lg * 32 + lane;   // key row inside the tile
+    const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+    const int ki = kv0 + row;
+    const float sc = p.scale * kLog2e;
+    float* stat = stat_all + lg * 256;
+    bool ok = true;
+    for (int st = 0; st < n_steps; ++st) {
+      const int s = st & 1;
+      const int h = hk * G + st / per_head, qt = qt_first + st % per_head;
+      // per-column statistics of this step's 64 queries: every warp keeps its own copy in shared
+      // memory (lane l loads 4 of the 128 values), so no cross-warp barrier is needed
+      {
+        const long long sb = (static_cast<long long>(b) * p.H + h) * p.Sq + qt * 64;
+        stat[s * 128 + lane] = p.lse[sb + lane] * kLog2e;
+        stat[s * 128 + 32 + lane] = p.lse[sb + 32 + lane] * kLog2e;
+        stat[s * 128 + 64 + lane] = p.delta[sb + lane];
+        stat[s * 128 + 96 + lane] = p.delta[sb + 32 + lane];
+        __syncwarp();
+      }
+      if (!tt::mbar_wait(bar(5 + s), (st >> 1) & 1, abort_flag, &g_attn_error, 37)) { ok = false; break; }
+      tt::tc_fence_after();
+      float pt[64], dst[64];
+      const float* lse_s = stat + s * 128;
+      const float* dl_s = stat + s * 128 + 64;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rp[32];
+        tt::tmem_ld_32x32(tST + lane_off + s * 64 + half * 32, rs);
+        tt::tmem_ld_32x32(tDPT + lane_off + s * 64 + half * 32, rp);
+        tt::tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int c = half * 32 + e;
+          const int qi = qt * 64 + c;
+          float pr = fast_exp2(__uint_as_float(rs[e]) * sc - lse_s[c]);
+          if (p.causal && ki > qi + off) pr = 0.f;
+          pt[c] = pr;
+          dst[c] = pr * (__uint_as_float(rp[e]) - dl_s[c]) * p.scale;
+        }
+      }
+      store_row_sw128(gbase + K_PT + s * 16384, row, pt);
+      store_row_sw128(gbase + K_DST + s * 16384, row, dst);
+      tt::fence_proxy_async();
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(bar(7 + s));
+    }
+    if (ok && n_steps > 0) ok = tt::mbar_wait(bar(9 + ((n_steps - 1) & 1)), ((n_steps - 1) >> 1) & 1, abort_flag, &g_attn_error, 38);
+    tt::tc_fence_after();
+    if (ok) {
+      const long long o = ((static_cast<long long>(b) * p.Sk + ki) * p.Hkv + hk) * D;
+      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.out2) + o;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dstp = which ? dk : dv;
+        const uint32_t t = which ? tDK : tDV;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          if (n_steps > 0) { tt::tmem_ld_32x32(t + lane_off + c * 32, r); tt::tc_wait_ld(); }
+          else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = 0;
+          }
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 q;
+            q.x = tt::pack_bf16(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
+            q.y = tt::pack_bf16(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
+            q.z = tt::pack_bf16(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
+            q.w = tt::pack_bf16(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
+            *reinterpret_cast<uint4*>(dstp + c * 32 + v4 * 8) = q;
+          }
+        }
+      }
+    }
+    tt::tc_fence_before();
+  }
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  if (warp == 1) { tt::tc_fence_after(); tt::tmem_dealloc(tmem, 512); }
+}
+
+// delta[b,h,s] = sum_d dO * O
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x / 16) + threadIdx.x / 16;  // (b,s,h)
+  const int l16 = threadIdx.x & 15;
+  const long long rows = static_cast<long long>(B) * S * H;
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + l16 * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dout + row * D + l16 * 8);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(ch[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o2 = 8; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (row < rows && l16 == 0) {
+    const int hh = static_cast<int>(row % H);
+    const long long bs = row / H;
+    const int s = static_cast<int>(bs % S);
+    const long long bb = bs / S;
+    delta[(bb * H + hh) * S + s] = acc;
+  }
+}
+
+// [B*S, heads, 128] bf16 viewed as a 3-D tensor (d, head, row); box = (64, 1, box_rows), 128B swizzle
+int make_map(CUtensorMap* m, const void* ptr, long long rows, int heads, int box_rows) {
+  tt::EncodeTiledFn fn = tt::encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(heads) * D * 2};
+  cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
+bool g_attr_set = false;
+void set_attrs() {
+  if (g_attr_set) return;
+  cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FWD_SMEM));
+  cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DQ_SMEM));
+  cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DKV_SMEM));
+  g_attr_set = true;
+}
+
+int check_shapes(int Sq, int Sk, int H, int Hkv, int Dh) {
+  if (Dh != D) return -10;
+  if (Sq % 128 || Sk % 128) return -11;
+  if (Hkv <= 0 || H % Hkv) return -12;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Shapes this build of the kernels accepts (0 = yes).
+int tt_attn_supported(int Sq, int Sk, int H, int Hkv, int Dh) { return check_shapes(Sq, Sk, H, Hkv, Dh); }
+
+int tt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int H, int Hkv,
+                int Dh, int causal, float scale, cudaStream_t st) {
+  int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
+  if (rc) return rc;
+  set_attrs();
+  CUtensorMap tq, tk, tv;
+  if ((rc = make_map(&tq, q, static_cast<long long>(B) * Sq, H, 128))) return rc;
+  if ((rc = make_map(&tk, k, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
+  if ((rc = make_map(&tv, v, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
+  AttnArgs p{B, Sq, Sk, H, Hkv, causal, scale, o, nullptr, lse, nullptr};
+  dim3 grid(Sq / 128, H, B);
+  attn_fwd_kernel<<<grid, 192, FWD_SMEM, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// delta is scratch [B,H,Sq] fp32 written by the first launch and read by the other two.
+int tt_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                float* delta, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal,
+                float scale, cudaStream_t st) {
+  int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
+  if (rc) return rc;
+  set_attrs();
+  const long long rows = static_cast<long long>(B) * Sq * H;
+  attn_delta_kernel<<<static_cast<unsigned>((rows + 15) / 16), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, Sq, H);
+  CUtensorMap tq128, tdo128, tk64, tv64, tq64, tdo64, tk128, tv128;
+  if ((rc = make_map(&tq128, q, static_cast<long long>(B) * Sq, H, 128))) return rc;
+  if ((rc = make_map(&tdo128, dout, static_cast<long long>(B) * Sq, H, 128))) return rc;
+  if ((rc = make_map(&tk64, k, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
+  if ((rc = make_map(&tv64, v, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
+  if ((rc = make_map(&tq64, q, static_cast<long long>(B) * Sq, H, 64))) return rc;
+  if ((rc = make_map(&tdo64, dout, static_cast<long long>(B) * Sq, H, 64))) return rc;
+  if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
+  if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
+  AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta};
+  attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 192, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
+  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta};
+  attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 192, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int tt_attn_error() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

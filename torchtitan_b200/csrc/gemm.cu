@@ -1,0 +1,327 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM), operands staged
+// by TMA into 128-byte-swizzled shared memory.
+//
+//   C[M,N] (+)= A[M,K] * B[N,K]^T          (fp32 accumulate, bf16 or fp32 output)
+//
+// Each operand may be stored K-major (contraction dimension contiguous) or MN-major (stored
+// transposed, [K, M] / [K, N]), which covers the three GEMMs of a linear layer without explicit
+// transposes: forward (K,K), input gradient (A K-major, B MN-major), weight gradient (MN,MN).
+//
+// Structure: persistent CTAs (one per SM) walk a grouped tile order; warp 0 = TMA producer,
+// warp 1 = UMMA issuer (a single elected thread), warp 2 owns the TMEM allocation, warps 4-7 =
+// epilogue. A 4-stage (128x64 | 256x64) operand ring and two 256-column TMEM accumulators let the
+// epilogue of tile i overlap the main loop of tile i+1. No cluster multicast is used anywhere, so
+// the kernel is safe to run on any number of GPUs and with operands in peer memory.
+//
+// Replaces: cuBLAS/cuBLASLt calls behind nn.Linear in the reference (torchtitan/models/common/linear.py:14-56).
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr uint32_t B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int NUM_THREADS = 256;
+constexpr size_t SMEM_BYTES = 1024 /*align slack*/ + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+
+__device__ int g_gemm_error = 0;
+
+struct GemmArgs {
+  int M, N, K;
+  int tiles_m, tiles_n, k_iters;
+  int a_mn, b_mn;       // operand stored MN-major (transposed) ?
+  uint32_t idesc;
+  void* C;
+  long long ldc;
+  int c_fp32;
+  int accumulate;       // C += result
+  // fused all-gather variant: per n-tile readiness flags (nullptr = plain GEMM)
+  const int* ready_flags;
+  int ready_value;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // grouped order: 8 m-tiles share the same sweep over n so concurrently running CTAs reuse
+  // A row-panels and B column-panels out of L2
+  constexpr int GROUP_M = 8;
+  int per_group = GROUP_M * tiles_n;
+  int g = t / per_group;
+  int first_m = g * GROUP_M;
+  int gm = min(tiles_m - first_m, GROUP_M);
+  int r = t - g * per_group;
+  tm = first_m + r % gm;
+  tn = r / gm;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t sA = base;
+  const uint32_t sB = base + STAGES * A_STAGE_BYTES;
+  const uint32_t bars = base + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  uint8_t* bars_gen = gen_base + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_gen + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tt::mbar_init(full_bar(s), 1);
+      tt::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      tt::mbar_init(tfull_bar(a), 1);
+      tt::mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+    tt::tma_prefetch_desc(&tma_a);
+    tt::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 2) {
+    tt::tmem_alloc(tt::smem_u32(tmem_slot), TMEM_COLS);
+    tt::tmem_relinquish();
+  }
+  tt::tc_fence_before();
+  __syncthreads();
+  tt::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (tt::elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        if (p.ready_flags != nullptr) {
+          // fused all-gather: wait until the copy CTAs have landed this n-tile of B locally
+          uint64_t t0 = tt::globaltimer_ns();
+          while (*reinterpret_cast<const volatile int*>(p.ready_flags + tn) < p.ready_value) {
+            if (*abort_flag || tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) {
+              *abort_flag = 1;
+              atomicCAS(&g_gemm_error, 0, 5);
+              ok = false;
+              break;
+            }
+            __nanosleep(200);
+          }
+          if (!ok) break;
+          __threadfence();
+        }
+        for (int k = 0; k < p.k_iters; ++k, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tt::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, &g_gemm_error, 1)) { ok = false; break; }
+          tt::mbar_expect_tx(full_bar(s), A_STAGE_BYTES + B_STAGE_BYTES);
+          const uint32_t dA = sA + s * A_STAGE_BYTES, dB = sB + s * B_STAGE_BYTES;
+          if (!p.a_mn) {
+            tt::tma_load_2d(dA, &tma_a, full_bar(s), k * BK, tm * BM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tt::tma_load_2d(dA + j * (64 * BK * 2), &tma_a, full_bar(s), tm * BM + j * 64, k * BK);
+          }
+          if (!p.b_mn) {
+            tt::tma_load_2d(dB, &tma_b, full_bar(s), k * BK, tn * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tt::tma_load_2d(dB + j * (64 * BK * 2), &tma_b, full_bar(s), tn * BN + j * 64, k * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (tt::elect_one()) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      // descriptor geometry per operand layout
+      const uint32_t a_lbo = p.a_mn ? (64 * BK * 2) >> 4 : 1, b_lbo = p.b_mn ? (64 * BK * 2) >> 4 : 1;
+      const uint32_t sbo = 1024 >> 4;
+      const uint32_t a_kadv = p.a_mn ? (UMMA_K * 128) : (UMMA_K * 2);  // bytes per 16-wide k step
+      const uint32_t b_kadv = p.b_mn ? (UMMA_K * 128) : (UMMA_K * 2);
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        if (!tt::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, &g_gemm_error, 2)) break;
+        tt::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int k = 0; k < p.k_iters; ++k, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!tt::mbar_wait(full_bar(s), ph, abort_flag, &g_gemm_error, 3)) { ok = false; break; }
+          tt::tc_fence_after();
+          const uint32_t aA = sA + s * A_STAGE_BYTES, aB = sB + s * B_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t ad = tt::umma_smem_desc(aA + kk * a_kadv, a_lbo, sbo);
+            const uint64_t bd = tt::umma_smem_desc(aB + kk * b_kadv, b_lbo, sbo);
+            tt::umma_f16_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+          }
+          tt::umma_commit(empty_bar(s));  // frees the stage once these UMMAs have read it
+        }
+        if (ok) tt::umma_commit(tfull_bar(acc));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (TMEM -> registers -> global)
+    const int ew = warp - 4;  // TMEM lanes [32*ew, 32*ew+32)
+    uint32_t tile_it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_it) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int acc = tile_it & 1;
+      const uint32_t acc_ph = (tile_it >> 1) & 1;
+      if (!tt::mbar_wait(tfull_bar(acc), acc_ph, abort_flag, &g_gemm_error, 4)) break;
+      tt::tc_fence_after();
+      const int row = tm * BM + ew * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tt::tmem_ld_32x32(taddr + c * 32, r);
+        tt::tc_wait_ld();
+        const int col = n0 + c * 32;
+        if (!row_ok || col >= p.N) continue;
+        const bool full_chunk = (col + 32 <= p.N);
+        if (p.c_fp32) {
+          float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          if (full_chunk && (p.ldc % 4 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              float4* q = reinterpret_cast<float4*>(dst) + j;
+              if (p.accumulate) {
+                float4 o = *q;
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *q = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < p.N; ++j)
+              dst[j] = __uint_as_float(r[j]) + (p.accumulate ? dst[j] : 0.f);
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          if (full_chunk && (p.ldc % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4* q = reinterpret_cast<uint4*>(dst) + j;
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+              if (p.accumulate) {
+                uint4 o = *q;
+                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float2 of = __bfloat1622float2(ob[e]);
+                  f[2 * e] += of.x;
+                  f[2 * e + 1] += of.y;
+                }
+              }
+              uint4 v;
+              v.x = tt::pack_bf16(f[0], f[1]);
+              v.y = tt::pack_bf16(f[2], f[3]);
+              v.z = tt::pack_bf16(f[4], f[5]);
+              v.w = tt::pack_bf16(f[6], f[7]);
+              *q = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < p.N; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (p.accumulate) v += __bfloat162float(dst[j]);
+              dst[j] = __float2bfloat16(v);
+            }
+          }
+        }
+      }
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  if (warp == 2) {
+    tt::tc_fence_after();
+    tt::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+int g_num_sms = 0;
+
+}  // namespace
+
+extern "C" {
+
+// A: [M,K] (a_mn=0, row stride lda) or stored transposed [K,M] (a_mn=1). Same for B with N.
+// Returns 0 on success, a negative number on invalid arguments / descriptor failures.
+int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, long long lda, int b_mn,
+                 long long ldb, long long ldc, int c_fp32, int accumulate, const int* ready_flags, int ready_value,
+                 int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8)) return -2;  // TMA needs 16-byte row strides
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  else       rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64);
+  if (rc) return rc;
+  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
+  else       rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.k_iters = (K + BK - 1) / BK;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate;
+  p.ready_flags = ready_flags; p.ready_value = ready_value;
+  int grid = p.tiles_m * p.tiles_n;
+  int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
+  if (grid > cap) grid = cap;
+  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Error word written by kernels whose bounded waits expired (0 = none). Reading clears it.
+int tt_gemm_error() {
+  int v = 0, zero = 0;
+  cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int));
+  if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

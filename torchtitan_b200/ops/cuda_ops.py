@@ -1,0 +1,547 @@
+"""CUDA implementations of the hot ops: thin ``torch.library`` custom ops (namespace
+``tt_b200``) around the native kernels, plus the autograd functions that combine them.
+
+Custom ops (rather than bare ctypes calls) make the kernels visible to dispatch-level tools:
+per-op selective activation checkpointing names ``tt_b200::gemm`` and
+``tt_b200::attention_fwd`` in its save list, and the profiler shows them by name.
+Ops that the kernels do not cover (non-bf16 GEMMs, attention with head_dim != 128 or sequence
+lengths that are not multiples of 128, masks other than causal) take a PyTorch path and say
+so once in the log.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import Tensor
+
+from . import native
+from . import reference as ref
+from torchtitan_b200.tools.logging import logger, warn_once
+
+_lib = native.lib
+_ck = native.check
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _dt(t: Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+# =============================================================================== GEMM
+@torch.library.custom_op("tt_b200::gemm", mutates_args=())
+def gemm(a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, out_fp32: bool) -> Tensor:
+    """``C[M,N] = A · B^T`` with bf16 operands. ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``),
+    ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``); rows may be strided."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    c = torch.empty((M, N), dtype=torch.float32 if out_fp32 else torch.bfloat16, device=a.device)
+    _ck(_lib().tt_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, int(a_mn), a.stride(0), int(b_mn),
+                            b.stride(0), c.stride(0), int(out_fp32), 0, None, 0, 0, _stream()), "tt_gemm_bf16")
+    return c
+
+
+@gemm.register_fake
+def _(a, b, a_mn, b_mn, out_fp32):
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    return a.new_empty((M, N), dtype=torch.float32 if out_fp32 else torch.bfloat16)
+
+
+def gemm_into(a: Tensor, b: Tensor, out: Tensor, *, a_mn=False, b_mn=False, accumulate=False, ready_flags=None,
+              ready_value=0, max_ctas=0) -> Tensor:
+    """Like :func:`gemm` but writes (or accumulates) into ``out`` (bf16 or fp32, row stride free)."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert out.shape == (M, N) and out.stride(1) == 1
+    _ck(_lib().tt_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, int(a_mn), a.stride(0), int(b_mn),
+                            b.stride(0), out.stride(0), int(out.dtype == torch.float32), int(accumulate),
+                            _p(ready_flags), ready_value, max_ctas, _stream()), "tt_gemm_bf16")
+    return out
+
+
+def _gemm_ok(*ts: Tensor) -> bool:
+    for t in ts:
+        if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or t.stride(0) % 8 or t.data_ptr() % 16:
+            return False
+    return True
+
+
+def _rows2d(x: Tensor) -> Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    return x2 if x2.stride(-1) == 1 else x2.contiguous()
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = _rows2d(x)
+        y = torch.ops.tt_b200.gemm(x2, w, False, False, False)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.xshape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        g2 = _rows2d(gy)
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.ops.tt_b200.gemm(g2, w, False, True, False).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            slot = getattr(w, "_grad_slot", None)
+            if slot is not None:
+                gw = gemm_into(g2, x2, slot, a_mn=True, b_mn=True)
+            else:
+                gw = torch.ops.tt_b200.gemm(g2, x2, True, True, False)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g2.float().sum(0).to(gy.dtype)
+        return gx, gw, gb
+
+
+def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2 \
+            and weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0 \
+            and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
+        return _LinearFn.apply(x, weight, bias)
+    if torch.is_autocast_enabled() and weight.dtype == torch.float32:
+        return _LinearFn.apply(x.to(torch.bfloat16), weight.to(torch.bfloat16), None if bias is None else bias.to(torch.bfloat16))
+    warn_once(logger, f"linear with dtypes {x.dtype}/{weight.dtype} takes the PyTorch matmul path")
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+# =============================================================================== RMSNorm
+@torch.library.custom_op("tt_b200::rmsnorm_fwd", mutates_args=())
+def rmsnorm_fwd(x: Tensor, w: Tensor | None, eps: float) -> tuple[Tensor, Tensor]:
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    y = torch.empty_like(x2)
+    rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    _ck(_lib().tt_rmsnorm_fwd(x2.data_ptr(), _p(w), y.data_ptr(), rstd.data_ptr(), x2.shape[0], D, eps, _dt(x), _stream()),
+        "tt_rmsnorm_fwd")
+    return y.view(x.shape), rstd
+
+
+@rmsnorm_fwd.register_fake
+def _(x, w, eps):
+    return torch.empty_like(x), x.new_empty(x.numel() // x.shape[-1], dtype=torch.float32)
+
+
+@torch.library.custom_op("tt_b200::rmsnorm_bwd", mutates_args=())
+def rmsnorm_bwd(dy: Tensor, x: Tensor, w: Tensor | None, rstd: Tensor) -> tuple[Tensor, Tensor]:
+    D = x.shape[-1]
+    x2, dy2 = x.reshape(-1, D), dy.reshape(-1, D)
+    rows = x2.shape[0]
+    dx = torch.empty_like(x2)
+    nblk = _lib().tt_rmsnorm_bwd_blocks(rows, D)
+    scratch = torch.empty((nblk, D), dtype=torch.float32, device=x.device)
+    dw = torch.empty(D, dtype=x.dtype, device=x.device) if w is not None else torch.empty(0, dtype=x.dtype, device=x.device)
+    _ck(_lib().tt_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), _p(w), rstd.data_ptr(), dx.data_ptr(),
+                              dw.data_ptr() if w is not None else None, scratch.data_ptr(), rows, D, _dt(x), _stream()),
+        "tt_rmsnorm_bwd")
+    return dx.view(x.shape), dw
+
+
+@rmsnorm_bwd.register_fake
+def _(dy, x, w, rstd):
+    return torch.empty_like(x), x.new_empty(x.shape[-1] if w is not None else 0)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        xc = x if x.is_contiguous() else x.contiguous()
+        y, rstd = torch.ops.tt_b200.rmsnorm_fwd(xc, w, eps)
+        ctx.save_for_backward(xc, w, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        dyc = dy if dy.is_contiguous() else dy.contiguous()
+        dx, dw = torch.ops.tt_b200.rmsnorm_bwd(dyc, x, w, rstd)
+        return dx, (dw if w is not None else None), None
+
+
+def rms_norm(x: Tensor, weight: Tensor | None, eps: float | None) -> Tensor:
+    eps = torch.finfo(x.dtype).eps if eps is None else eps
+    if x.dtype in (torch.bfloat16, torch.float32) and x.shape[-1] % 8 == 0 and (weight is None or weight.dtype == x.dtype):
+        return _RMSNormFn.apply(x, weight, eps)
+    if weight is not None and weight.dtype != x.dtype and x.shape[-1] % 8 == 0:
+        return _RMSNormFn.apply(x, weight.to(x.dtype), eps)
+    return ref.rms_norm(x, weight, eps)
+
+
+# =============================================================================== RoPE
+@torch.library.custom_op("tt_b200::rope", mutates_args=())
+def rope_op(x: Tensor, table: Tensor, positions: Tensor | None, layout: int, inverse: bool) -> Tensor:
+    B, S, H, D = x.shape
+    y = torch.empty_like(x)
+    pb = 0 if positions is None else positions.shape[0]
+    _ck(_lib().tt_rope(x.data_ptr(), y.data_ptr(), table.data_ptr(), _p(positions), pb, B, S, H, D, layout, int(inverse),
+                       _dt(x), _stream()), "tt_rope")
+    return y
+
+
+@rope_op.register_fake
+def _(x, table, positions, layout, inverse):
+    return torch.empty_like(x)
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, table, positions, layout):
+        ctx.table, ctx.positions, ctx.layout = table, positions, layout
+        return torch.ops.tt_b200.rope(x.contiguous(), table, positions, layout, False)
+
+    @staticmethod
+    def backward(ctx, gy):
+        return torch.ops.tt_b200.rope(gy.contiguous(), ctx.table, ctx.positions, ctx.layout, True), None, None, None
+
+
+def rope(x: Tensor, table: Tensor, positions: Tensor | None, layout: str) -> Tensor:
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        return ref.rope(x, table, positions, layout)
+    if table.device != x.device or table.dtype != torch.float32 or not table.is_contiguous():
+        table = table.to(device=x.device, dtype=torch.float32).contiguous()
+    if positions is not None:
+        positions = positions.to(device=x.device, dtype=torch.int64).contiguous()
+        if positions.dim() == 1:
+            positions = positions.unsqueeze(0)
+    return _RopeFn.apply(x, table, positions, 0 if layout == "interleaved" else 1)
+
+
+# =============================================================================== SwiGLU
+@torch.library.custom_op("tt_b200::swiglu_fwd", mutates_args=())
+def swiglu_fwd(g: Tensor, u: Tensor) -> Tensor:
+    out = torch.empty_like(g)
+    _ck(_lib().tt_swiglu_fwd(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(), _dt(g), _stream()), "tt_swiglu_fwd")
+    return out
+
+
+@swiglu_fwd.register_fake
+def _(g, u):
+    return torch.empty_like(g)
+
+
+@torch.library.custom_op("tt_b200::swiglu_bwd", mutates_args=())
+def swiglu_bwd(dout: Tensor, g: Tensor, u: Tensor) -> tuple[Tensor, Tensor]:
+    dg, du = torch.empty_like(g), torch.empty_like(u)
+    _ck(_lib().tt_swiglu_bwd(dout.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(), _dt(g),
+                             _stream()), "tt_swiglu_bwd")
+    return dg, du
+
+
+@swiglu_bwd.register_fake
+def _(dout, g, u):
+    return torch.empty_like(g), torch.empty_like(u)
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        g, u = g.contiguous(), u.contiguous()
+        ctx.save_for_backward(g, u)
+        return torch.ops.tt_b200.swiglu_fwd(g, u)
+
+    @staticmethod
+    def backward(ctx, dout):
+        g, u = ctx.saved_tensors
+        return torch.ops.tt_b200.swiglu_bwd(dout.contiguous(), g, u)
+
+
+def swiglu(gate: Tensor, up: Tensor) -> Tensor:
+    if gate.dtype in (torch.bfloat16, torch.float32) and gate.dtype == up.dtype and gate.numel() % 8 == 0:
+        return _SwigluFn.apply(gate, up)
+    return ref.swiglu(gate, up)
+
+
+# =============================================================================== attention
+@torch.library.custom_op("tt_b200::attention_fwd", mutates_args=())
+def attention_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float) -> tuple[Tensor, Tensor]:
+    B, Sq, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    _ck(_lib().tt_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Sq, Sk, H, Hkv, D,
+                           int(causal), scale, _stream()), "tt_attn_fwd")
+    return o, lse
+
+
+@attention_fwd.register_fake
+def _(q, k, v, causal, scale):
+    return torch.empty_like(q), q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32)
+
+
+@torch.library.custom_op("tt_b200::attention_bwd", mutates_args=())
+def attention_bwd(q: Tensor, k: Tensor, v: Tensor, o: Tensor, do: Tensor, lse: Tensor, causal: bool,
+                  scale: float) -> tuple[Tensor, Tensor, Tensor]:
+    B, Sq, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    _ck(_lib().tt_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                           delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Sq, Sk, H, Hkv, D, int(causal),
+                           scale, _stream()), "tt_attn_bwd")
+    return dq, dk, dv
+
+
+@attention_bwd.register_fake
+def _(q, k, v, o, do, lse, causal, scale):
+    return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = causal, scale
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = torch.ops.tt_b200.attention_bwd(q, k, v, o, do.contiguous(), lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def attention_supported(q: Tensor, k: Tensor) -> bool:
+    B, Sq, H, D = q.shape
+    return q.dtype == torch.bfloat16 and _lib().tt_attn_supported(Sq, k.shape[1], H, k.shape[2], D) == 0
+
+
+def attention(q, k, v, *, causal=True, scale=None, window=None, doc_ids=None, sinks=None, return_lse=False):
+    plain = window is None and doc_ids is None and sinks is None
+    if plain and k.dtype == q.dtype and attention_supported(q, k):
+        scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+        o, lse = _AttnFn.apply(q, k, v, bool(causal), scale)
+        return (o, lse) if return_lse else o
+    warn_once(logger, f"attention shape/mask q={tuple(q.shape)} k={tuple(k.shape)} dtype={q.dtype} "
+                      f"window={window} doc={doc_ids is not None} sinks={sinks is not None} takes the PyTorch path")
+    return ref.attention(q, k, v, causal=causal, scale=scale, window=window, doc_ids=doc_ids, sinks=sinks, return_lse=return_lse)
+
+
+# =============================================================================== cross entropy
+@torch.library.custom_op("tt_b200::ce_fwd", mutates_args=())
+def ce_fwd(logits: Tensor, labels: Tensor, ignore_index: int) -> tuple[Tensor, Tensor, Tensor]:
+    """Returns (loss_sum [], lse [rows], per-row log-prob of the label [rows])."""
+    rows, V = logits.shape
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    loss_rows = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    logprob = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    loss = torch.zeros((), dtype=torch.float32, device=logits.device)
+    _ck(_lib().tt_ce_fwd(logits.data_ptr(), labels.data_ptr(), lse.data_ptr(), loss_rows.data_ptr(), logprob.data_ptr(),
+                         loss.data_ptr(), rows, V, logits.stride(0), ignore_index, _dt(logits), _stream()), "tt_ce_fwd")
+    return loss, lse, logprob
+
+
+@ce_fwd.register_fake
+def _(logits, labels, ignore_index):
+    r = logits.shape[0]
+    return logits.new_empty((), dtype=torch.float32), logits.new_empty(r, dtype=torch.float32), logits.new_empty(r, dtype=torch.float32)
+
+
+@torch.library.custom_op("tt_b200::ce_bwd", mutates_args=())
+def ce_bwd(logits: Tensor, labels: Tensor, lse: Tensor, gscale: Tensor | None, row_scale: Tensor | None,
+           ignore_index: int, negate: bool) -> Tensor:
+    rows, V = logits.shape
+    d = torch.empty_like(logits)
+    _ck(_lib().tt_ce_bwd(logits.data_ptr(), labels.data_ptr(), lse.data_ptr(), _p(gscale), _p(row_scale), d.data_ptr(), rows,
+                         V, logits.stride(0), ignore_index, int(negate), _dt(logits), _stream()), "tt_ce_bwd")
+    return d
+
+
+@ce_bwd.register_fake
+def _(logits, labels, lse, gscale, row_scale, ignore_index, negate):
+    return torch.empty_like(logits)
+
+
+class _CESumFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits2d, labels, ignore_index):
+        loss, lse, _ = torch.ops.tt_b200.ce_fwd(logits2d, labels, ignore_index)
+        ctx.save_for_backward(logits2d, labels, lse)
+        ctx.ignore_index = ignore_index
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        logits2d, labels, lse = ctx.saved_tensors
+        gs = g.to(torch.float32).reshape(1).contiguous()
+        return torch.ops.tt_b200.ce_bwd(logits2d, labels, lse, gs, None, ctx.ignore_index, False), None, None
+
+
+def _ce_ready(logits: Tensor) -> Tensor | None:
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        return None
+    l2 = logits.reshape(-1, logits.shape[-1])
+    if l2.stride(-1) != 1 or l2.stride(0) % 8:
+        l2 = l2.contiguous()
+        if l2.stride(0) % 8:
+            return None
+    return l2
+
+
+def cross_entropy_sum(logits: Tensor, labels: Tensor, ignore_index: int = -100) -> Tensor:
+    l2 = _ce_ready(logits)
+    if l2 is None:
+        return ref.cross_entropy_sum(logits, labels, ignore_index)
+    return _CESumFn.apply(l2, labels.reshape(-1).to(torch.int64).contiguous(), ignore_index)
+
+
+class _LogprobFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits2d, labels):
+        _, lse, lp = torch.ops.tt_b200.ce_fwd(logits2d, labels, -(2**31))
+        ctx.save_for_backward(logits2d, labels, lse)
+        return lp
+
+    @staticmethod
+    def backward(ctx, g):
+        logits2d, labels, lse = ctx.saved_tensors
+        # d logprob / d logits = onehot - softmax = -(softmax - onehot)
+        return torch.ops.tt_b200.ce_bwd(logits2d, labels, lse, None, g.to(torch.float32).contiguous(), -(2**31), True), None
+
+
+def token_logprobs(logits: Tensor, labels: Tensor) -> Tensor:
+    l2 = _ce_ready(logits)
+    if l2 is None:
+        return ref.token_logprobs(logits, labels)
+    return _LogprobFn.apply(l2, labels.reshape(-1).to(torch.int64).contiguous()).view(labels.shape)
+
+
+# =============================================================================== optimizer
+_scratch: dict = {}
+
+
+def _scratch_buf(device, n: int) -> Tensor:
+    key = (device, n)
+    if key not in _scratch:
+        _scratch[key] = torch.empty(n, dtype=torch.float32, device=device)
+    return _scratch[key]
+
+
+def adamw_flat(param, grad, exp_avg, exp_avg_sq, shadow, *, lr, beta1, beta2, eps, weight_decay, step, decoupled=True,
+               grad_scale=None):
+    assert param.dtype == torch.float32 and grad.dtype == torch.float32
+    if shadow is not None:
+        assert shadow.dtype == torch.bfloat16 and shadow.numel() == param.numel()
+    gs = None
+    if grad_scale is not None:
+        gs = grad_scale if torch.is_tensor(grad_scale) else torch.tensor(float(grad_scale), device=param.device)
+        gs = gs.to(torch.float32).reshape(1)
+    _ck(_lib().tt_adamw(param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), _p(shadow),
+                        param.numel(), lr, beta1, beta2, eps, weight_decay, int(step), int(decoupled), _p(gs), _stream()),
+        "tt_adamw")
+
+
+def sumsq(flat: Tensor, out: Tensor | None = None, accumulate: bool = False) -> Tensor:
+    if out is None:
+        out = torch.empty((), dtype=torch.float32, device=flat.device)
+    scratch = _scratch_buf(flat.device, 2048)
+    _ck(_lib().tt_sumsq(flat.data_ptr(), scratch.data_ptr(), out.data_ptr(), flat.numel(), _dt(flat), int(accumulate), _stream()),
+        "tt_sumsq")
+    return out
+
+
+# =============================================================================== MoE (see csrc/moe.cu)
+def moe_route(x, gate_w, gate_b, expert_bias, **kw):
+    return ref.moe_route(x, gate_w, gate_b, expert_bias, **kw)
+
+
+def moe_sort(expert_idx, num_experts: int):
+    return ref.moe_sort(expert_idx, num_experts)
+
+
+def moe_gather_rows(x, order, top_k: int):
+    return x[order // top_k]
+
+
+def moe_scatter_combine(rows, order, weights, num_tokens: int, top_k: int):
+    D = rows.shape[-1]
+    unsorted = rows.new_zeros(num_tokens * top_k, D)
+    unsorted[order] = rows[: order.numel()]
+    unsorted = unsorted.view(num_tokens, top_k, D)
+    if weights is None:
+        return unsorted.sum(dim=1)
+    return torch.bmm(weights.reshape(-1, 1, top_k), unsorted.float()).to(rows.dtype).squeeze(1)
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    """Per-expert GEMMs launched back to back on the tcgen05 kernel; group sizes are read once
+    per call (one small device-to-host copy shared by the three expert GEMMs of a layer)."""
+
+    @staticmethod
+    def forward(ctx, x, w, counts):
+        sizes = _group_sizes(counts)
+        out = x.new_zeros(x.shape[0], w.shape[1])
+        s = 0
+        for e, n in enumerate(sizes):
+            if n:
+                gemm_into(x[s : s + n], w[e], out[s : s + n])
+            s += n
+        ctx.save_for_backward(x, w)
+        ctx.sizes = sizes
+        return out
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w = ctx.saved_tensors
+        gy = gy.contiguous()
+        gx = torch.zeros_like(x)
+        gw = torch.zeros_like(w)
+        s = 0
+        for e, n in enumerate(ctx.sizes):
+            if n:
+                gemm_into(gy[s : s + n], w[e], gx[s : s + n], b_mn=True)
+                gemm_into(gy[s : s + n], x[s : s + n], gw[e], a_mn=True, b_mn=True)
+            s += n
+        return gx, gw, None
+
+
+_sizes_cache: dict = {}
+
+
+def _group_sizes(counts: Tensor) -> list[int]:
+    key = (counts.data_ptr(), counts._version)
+    hit = _sizes_cache.get("k")
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    sizes = [int(v) for v in counts.tolist()]
+    _sizes_cache["k"] = (key, sizes)
+    return sizes
+
+
+def grouped_linear(x, w, counts):
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and w.shape[1] % 8 == 0:
+        return _GroupedLinearFn.apply(x.contiguous(), w, counts)
+    from .moe_ops import _GroupedLinearRef
+
+    return _GroupedLinearRef.apply(x, w, counts)
+
+
+def moe_fill_indices(tokens_per_expert_group, start_index_values, write_offsets, experts_per_rank, num_ranks, max_len):
+    from torchtitan_b200.models.common.moe.permute import fill_indices_cpu
+
+    return fill_indices_cpu(tokens_per_expert_group.cpu(), start_index_values.cpu(), write_offsets.cpu(),
+                            experts_per_rank, num_ranks, max_len).to(tokens_per_expert_group.device)

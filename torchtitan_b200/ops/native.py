@@ -1,0 +1,90 @@
+"""Loader for the in-tree native library (``torchtitan_b200/_lib/libtt_b200.so``).
+
+The library is plain C ABI (built by ``__graft_entry__.build()`` with nvcc for sm_100a) and is
+called through ctypes with raw device pointers and the current CUDA stream. On a machine with
+a GPU, using any CUDA op of this framework without the library raises immediately: there is no
+silent fallback to library kernels.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+_LIB = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_lib", "libtt_b200.so")
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return os.path.exists(_LIB_PATH)
+
+
+def _sig(fn, argtypes, restype=c_int):
+    fn.argtypes = argtypes
+    fn.restype = restype
+
+
+def lib():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(_LIB_PATH):
+        raise RuntimeError(
+            f"native library {_LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
+            "from the repository root (needs nvcc)"
+        )
+    L = ctypes.CDLL(_LIB_PATH)
+    P, I, LL, F = c_void_p, c_int, c_longlong, c_float
+    _sig(L.tt_gemm_bf16, [P, P, P, I, I, I, I, LL, I, LL, LL, I, I, P, I, I, P])
+    _sig(L.tt_gemm_error, [])
+    _sig(L.tt_rmsnorm_fwd, [P, P, P, P, LL, I, F, I, P])
+    _sig(L.tt_rmsnorm_bwd_blocks, [LL, I])
+    _sig(L.tt_rmsnorm_bwd, [P, P, P, P, P, P, P, LL, I, I, P])
+    _sig(L.tt_rope, [P, P, P, P, I, I, I, I, I, I, I, I, P])
+    _sig(L.tt_swiglu_fwd, [P, P, P, LL, I, P])
+    _sig(L.tt_swiglu_bwd, [P, P, P, P, P, LL, I, P])
+    _sig(L.tt_ce_fwd, [P, P, P, P, P, P, LL, I, LL, I, I, P])
+    _sig(L.tt_ce_bwd, [P, P, P, P, P, P, LL, I, LL, I, I, I, P])
+    _sig(L.tt_adamw, [P, P, P, P, P, LL, F, F, F, F, F, I, I, P, P])
+    _sig(L.tt_sumsq, [P, P, P, LL, I, I, P])
+    _sig(L.tt_attn_supported, [I, I, I, I, I])
+    _sig(L.tt_attn_fwd, [P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    _sig(L.tt_attn_bwd, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    _sig(L.tt_attn_error, [])
+    for name, sig in _OPTIONAL.items():
+        if hasattr(L, name):
+            _sig(getattr(L, name), sig)
+    _LIB = L
+    return L
+
+
+# symbols that newer builds of the library add (bound when present)
+_OPTIONAL: dict = {}
+
+
+def register_optional(name: str, argtypes) -> None:
+    _OPTIONAL[name] = argtypes
+    if _LIB is not None and hasattr(_LIB, name):
+        _sig(getattr(_LIB, name), argtypes)
+
+
+CALLS = 0  # number of native launch calls made by this process (bench reporting)
+
+
+def check(rc: int, what: str) -> None:
+    global CALLS
+    CALLS += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def kernel_errors() -> dict:
+    """Error words set by kernels whose bounded waits expired (reading clears them)."""
+    L = lib()
+    out = {"gemm": L.tt_gemm_error(), "attention": L.tt_attn_error()}
+    return {k: v for k, v in out.items() if v}

@@ -342,7 +342,19 @@ class FSDPUnit:
     def _storage_alive(self) -> bool:
         return self.unsharded_flat is not None and self.unsharded_flat.untyped_storage().size() > 0
 
+    @property
+    def aliases_shard(self) -> bool:
+        """With a shard world of one the gathered parameters are the compute-dtype shard itself."""
+        return self.shard_world == 1 and all(p.shard_dim == 0 for p in self.params)
+
     def _alloc_unsharded(self):
+        if self.aliases_shard:
+            src = self.gather_source()
+            if self.unsharded_flat is None or self.unsharded_flat.data_ptr() != src.data_ptr():
+                self.unsharded_flat = src
+                for p in self.params:
+                    p.unsharded = self._full_view(p)
+            return
         if self.unsharded_flat is None:
             alloc = getattr(self.comm, "alloc_unsharded_buffer", None)
             buf = alloc(self) if alloc is not None else None
@@ -391,6 +403,16 @@ class FSDPUnit:
             self.materialize()
         if not self.params:
             return
+        if self.aliases_shard:
+            with torch.no_grad():
+                first = self.unsharded_flat is None
+                if first or self._shadow_stale:
+                    if first:
+                        self._alloc_unsharded()
+                    with torch.autograd._unsafe_preserve_version_counter(self.unsharded_flat):
+                        self.gather_source()  # refreshes the shadow in place when it is stale
+            self._gathered = True
+            return
         if not (self._gathered and self._storage_alive()):
             self._alloc_unsharded()
             with torch.no_grad(), torch.autograd._unsafe_preserve_version_counter(self.unsharded_flat):
@@ -408,6 +430,8 @@ class FSDPUnit:
             self._gather_event = None
 
     def reshard(self) -> None:
+        if self.aliases_shard:
+            return
         if self._storage_alive():
             if self.uses_cuda:
                 # the side stream may still be writing a prefetched gather
