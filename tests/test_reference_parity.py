@@ -1,0 +1,137 @@
+"""Loss parity with the reference implementation on CPU (gloo, 2 ranks, FSDP, fp32).
+
+Config: Llama-3 debug model with 8 KV heads (dim 256, 6 layers, 16 heads, FFN 768, vocab 2048,
+RoPE theta 500000), local batch 2 x seq 512 of uniform tokens from seed 0, AdamW lr 8e-4
+betas (0.9, 0.95) wd 0.1, warmup 2 of 10 steps. Both sides start from identical weights; ours
+runs this framework's model + FSDP runtime + optimizer container + LR schedule, the other side
+runs the reference's model code with torch's ``fully_shard``, ``AdamW`` and the reference LR
+lambda. Losses must agree to rtol 1e-4 at every step.
+"""
+
+import dataclasses
+import os
+import sys
+
+import pytest
+import torch
+
+from dist_utils import run_ranks
+
+REF = "/root/reference"
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "torchtitan")), reason="reference tree not mounted")
+
+STEPS, WARMUP, BATCH, SEQ, VOCAB = 10, 2, 2, 512, 2048
+
+
+def _batches(rank: int):
+    g = torch.Generator().manual_seed(0 + rank)
+    for _ in range(STEPS):
+        x = torch.randint(0, VOCAB, (BATCH, SEQ + 1), generator=g, dtype=torch.int64)
+        yield x[:, :-1].contiguous(), x[:, 1:].contiguous()
+
+
+def _ours(rank, world, init_state):
+    import torch.distributed as dist
+
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
+    from torchtitan_b200.components.optimizer import OptimizersContainer
+    from torchtitan_b200.models.llama3 import llama3_configs
+    from torchtitan_b200.parallel import ParallelDims, fsdp
+    from torchtitan_b200.parallel.data_parallel import apply_fsdp
+    from torchtitan_b200.parallel.utils import clip_grad_norm_
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=world, cp=1, tp=1, pp=1, ep=1, etp=1, world_size=world)
+    cfg = dataclasses.replace(llama3_configs["debugmodel_gqa"])
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=SEQ)
+    torch.manual_seed(1234)
+    model = cfg.build()
+    model.init_weights()
+    if init_state is not None:
+        model.load_state_dict(init_state)
+    full_state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    apply_fsdp(model, pd.get_mesh("fsdp"), param_dtype=torch.float32, reduce_dtype=torch.float32, pp_enabled=False)
+    fsdp.materialize(model)
+    opt = OptimizersContainer.Config(lr=8e-4, beta1=0.9, beta2=0.95, weight_decay=0.1, implementation="foreach").build(model_parts=[model])
+    sched = LRSchedulersContainer.Config(warmup_steps=WARMUP).build(optimizers=opt, training_steps=STEPS)
+    losses = []
+    for x, y in _batches(rank):
+        opt.zero_grad()
+        ntok = torch.tensor(float(y.numel()))
+        dist.all_reduce(ntok)
+        loss = cross_entropy_loss(model(x), y) / ntok
+        loss.backward()
+        clip_grad_norm_(list(model.parameters()), 1.0)
+        opt.step()
+        sched.step()
+        l = loss.detach().clone()
+        dist.all_reduce(l)
+        losses.append(l.item())
+    return losses, full_state
+
+
+def _reference(rank, world, init_state):
+    sys.path.insert(0, REF)
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    from torchtitan.components.loss import cross_entropy_loss
+    from torchtitan.models.llama3 import llama3_configs
+
+    cfg = llama3_configs["debugmodel"]
+    layer = dataclasses.replace(cfg.layer, attention=dataclasses.replace(cfg.layer.attention, n_kv_heads=8))
+    cfg = dataclasses.replace(cfg, layer=layer, rope=dataclasses.replace(cfg.rope, max_seq_len=SEQ))
+    model = cfg.build()
+    model.init_weights()
+    model.load_state_dict(init_state)
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("fsdp",))
+    for blk in model.layers.values():
+        fully_shard(blk, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    # torch's FSDP averages gradients over ranks (its "no division" mode needs PREMUL_SUM, which
+    # gloo lacks); multiplying the loss by the world size (exact in fp32) gives the same sum.
+    opt = torch.optim.AdamW(model.parameters(), lr=8e-4, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+
+    def lr_lambda(step):  # the reference's warmup + linear decay with the virtual extra step
+        if step < WARMUP:
+            return float((step + 1) / (WARMUP + 1))
+        decay = STEPS - WARMUP
+        stable = STEPS + 1 - WARMUP - decay
+        if step < WARMUP + stable:
+            return 1.0
+        return 1 - float(step - WARMUP - stable) / decay
+
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lr_lambda)
+    losses = []
+    for x, y in _batches(rank):
+        opt.zero_grad()
+        ntok = torch.tensor(float(y.numel()))
+        dist.all_reduce(ntok)
+        loss = cross_entropy_loss(model(x), y) / ntok
+        (loss * world).backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        sched.step()
+        l = loss.detach().clone()
+        dist.all_reduce(l)
+        losses.append(l.item())
+    return losses
+
+
+def _both(rank, world):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    ours, state = _ours(rank, world, None)
+    ref = _reference(rank, world, state)
+    return ours, ref
+
+
+def test_loss_matches_reference_fsdp2_cpu(tmp_path):
+    out = run_ranks(_both, 2, tmp_path=tmp_path, timeout=900)
+    ours, ref = out[0]
+    assert len(ours) == STEPS
+    for a, b in zip(ours, ref):
+        assert abs(a - b) <= 1e-4 * abs(b), (ours, ref)
+    assert ours[-1] < ours[0]

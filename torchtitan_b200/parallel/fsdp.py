@@ -293,6 +293,14 @@ class FSDPUnit:
         self._materialized = True
         if not self.params:
             return
+        # nn.Module.to_empty() may have replaced plain Parameters by new objects: re-read them
+        for p in self.params:
+            m, attr = p.sites[0]
+            cur = m._parameters[attr]
+            if cur is not p.param:
+                p.param = cur
+                for m2, a2 in p.sites[1:]:
+                    m2._parameters[a2] = cur
         dev = self.device
         assert dev.type != "meta", "materialize() needs real parameters (call to_empty/init_weights first)"
         self.shard_flat = self.alloc_shard_buffer(self.orig_dtype, kind="master")
