@@ -88,8 +88,12 @@ def _dist_env():
     return rank, world, local
 
 
-def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None):
+def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, layers: int | None = None):
     from torchtitan_b200.config.manager import ConfigManager
+    from torchtitan_b200.models.llama3 import llama3_configs
+
+    if layers is not None:  # profiling aid only: a truncated model is not a benchmark result
+        llama3_configs["8B"].n_layers = layers
 
     args = [
         "--module", "llama3", "--config", "llama3_8b_synthetic",
@@ -133,7 +137,7 @@ def run_ours(args) -> dict:
     if rank == 0:
         init_logger()
     total_steps = args.warmup + 2 * args.steps + 4
-    trainer = build_trainer(args.gpus, total_steps, args.ac)
+    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers)
     dev = trainer.device
     local_bs = trainer.config.training.local_batch_size
     tokens_per_step = local_bs * SEQ_LEN * world
@@ -215,6 +219,8 @@ def run_ours(args) -> dict:
         "kernel_error_flags": errs,
         "impl": "torchtitan_b200",
     }
+    if args.layers is not None:
+        out["invalid_truncated_model_layers"] = args.layers
     trainer.close()
     return out
 
@@ -231,6 +237,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="profiling aid: truncate the model (result is not a benchmark)")
     ap.add_argument("--ac", default=None, help="override activation_checkpoint.mode (selective|full|none)")
     args = ap.parse_args()
     assert args.warmup >= 3 or os.environ.get("TT_BENCH_ALLOW_SHORT_WARMUP"), "warm-up must be at least 3 steps"

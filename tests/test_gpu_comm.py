@@ -1,0 +1,90 @@
+"""Peer-memory collective kernels, checked on one GPU by giving the kernel W local buffers as
+"peers" (flags already at the expected version, so nothing waits on another launch)."""
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr_array(tensors):
+    arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    return ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p)), arr
+
+
+@pytest.fixture(scope="module")
+def L():
+    from torchtitan_b200.ops import native
+    from torchtitan_b200.parallel import nvlink_comm  # registers the comm symbols
+
+    return native.lib()
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_allgather_and_reduce_scatter_kernels(L, W):
+    torch.manual_seed(0)
+    dev = "cuda"
+    stream = torch.cuda.current_stream().cuda_stream
+    # three "parameters": rows x inner, chunked over W ranks (one with an odd tail)
+    shapes = [(64 * W, 256), (8 * W, 40), (W, 7)]
+    segs, s_off, f_off = [], 0, 0
+    for rows, inner in shapes:
+        chunk = rows // W * inner
+        segs.append((s_off, f_off, chunk))
+        s_off += (chunk + 7) // 8 * 8
+        f_off += (W * chunk + 7) // 8 * 8
+    seg_t = torch.tensor(segs, dtype=torch.int64, device=dev)
+    shards = [torch.randn(s_off, device=dev).bfloat16() for _ in range(W)]
+    flags = [torch.full((1,), 3, dtype=torch.int32, device=dev) for _ in range(W)]
+    for my_rank in (0, W - 1):
+        dst = torch.zeros(f_off, device=dev, dtype=torch.bfloat16)
+        p, k1 = _ptr_array(shards)
+        f, k2 = _ptr_array(flags)
+        assert L.tt_allgather_pull(p, f, seg_t.data_ptr(), len(segs), dst.data_ptr(), W, my_rank, 3, 0, 4, stream) == 0
+        torch.cuda.synchronize()
+        for (so, fo, chunk) in segs:
+            want = torch.cat([sh[so : so + chunk] for sh in shards])
+            assert torch.equal(dst[fo : fo + W * chunk], want)
+    # reduce-scatter: every "peer" has a full staging buffer
+    staging = [torch.randn(f_off, device=dev).bfloat16() for _ in range(W)]
+    for my_rank in (0, W - 1):
+        out = torch.full((s_off,), 5.0, device=dev)
+        p, k1 = _ptr_array(staging)
+        f, k2 = _ptr_array(flags)
+        assert L.tt_reduce_scatter_pull(p, f, seg_t.data_ptr(), len(segs), out.data_ptr(), W, my_rank, 3, 0, 8, stream) == 0
+        assert L.tt_reduce_scatter_pull(p, f, seg_t.data_ptr(), len(segs), out.data_ptr(), W, my_rank, 3, 1, 8, stream) == 0
+        torch.cuda.synchronize()
+        for (so, fo, chunk) in segs:
+            want = sum(st[fo + my_rank * chunk : fo + (my_rank + 1) * chunk].float() for st in staging)
+            assert torch.allclose(out[so : so + chunk], 2 * want, rtol=1e-6, atol=1e-6)
+    err = (ctypes.c_int * 4)()
+    assert L.tt_comm_error(err) == 0
+
+
+def test_bounded_wait_reports_missing_flag(L):
+    """A peer flag that never reaches the expected version: the kernel gives up after the limit,
+    records {code, peer, expected, seen}, leaves the output untouched and the context usable."""
+    dev = "cuda"
+    stream = torch.cuda.current_stream().cuda_stream
+    W = 2
+    assert L.tt_comm_set_wait_ns(200_000_000) == 0  # 0.2 s
+    try:
+        shards = [torch.ones(64, device=dev).bfloat16() for _ in range(W)]
+        flags = [torch.full((1,), 7, dtype=torch.int32, device=dev), torch.full((1,), 2, dtype=torch.int32, device=dev)]
+        seg_t = torch.tensor([[0, 0, 64]], dtype=torch.int64, device=dev)
+        dst = torch.zeros(128, device=dev, dtype=torch.bfloat16)
+        p, k1 = _ptr_array(shards)
+        f, k2 = _ptr_array(flags)
+        assert L.tt_allgather_pull(p, f, seg_t.data_ptr(), 1, dst.data_ptr(), W, 0, 7, 0, 2, stream) == 0
+        torch.cuda.synchronize()
+        err = (ctypes.c_int * 4)()
+        assert L.tt_comm_error(err) == 1
+        assert (err[1], err[2], err[3]) == (1, 7, 2)
+        assert float(dst.float().abs().sum()) == 0.0
+        assert L.tt_comm_error(err) == 0  # reading cleared it
+        # the context is still healthy
+        assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+    finally:
+        L.tt_comm_set_wait_ns(20_000_000_000)

@@ -65,6 +65,9 @@ class ShardAdamW(Optimizer):
             for i, p in enumerate(u.params):
                 self._unit_of[id(p.param)] = (u, i)
         self._init_state()
+        self.has_loose_params = any(
+            id(p) not in self._unit_of for g in self.param_groups for p in g["params"]
+        )
 
     def _wrap_like(self, param, local):
         if isinstance(param, DTensor):

@@ -96,6 +96,7 @@ class _LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.xshape = x.shape
+        ctx.grad_slot = getattr(w, "_grad_slot", None)
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -106,14 +107,28 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gx = torch.ops.tt_b200.gemm(g2, w, False, True, False).view(ctx.xshape)
         if ctx.needs_input_grad[1]:
-            slot = getattr(w, "_grad_slot", None)
+            slot = ctx.grad_slot
             if slot is not None:
-                gw = gemm_into(g2, x2, slot, a_mn=True, b_mn=True)
+                # write dW straight into the unit's gradient buffer; autograd only carries a placeholder
+                gemm_into(g2, x2, slot.tensor, a_mn=True, b_mn=True, accumulate=slot.begin())
+                gw = _placeholder(w)
             else:
                 gw = torch.ops.tt_b200.gemm(g2, x2, True, True, False)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.float().sum(0).to(gy.dtype)
         return gx, gw, gb
+
+
+_placeholders: dict = {}
+
+
+def _placeholder(w: Tensor) -> Tensor:
+    """Zero-stride all-zeros tensor shaped like ``w`` (costs no memory and no launch after the first)."""
+    key = (w.device, w.dtype)
+    z = _placeholders.get(key)
+    if z is None:
+        z = _placeholders[key] = torch.zeros((), dtype=w.dtype, device=w.device)
+    return z.expand(w.shape)
 
 
 def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:

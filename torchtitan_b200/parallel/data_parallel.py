@@ -14,7 +14,7 @@ from .fsdp import MixedPrecisionPolicy, fully_shard, replicate
 from .fsdp_policy import get_fsdp_reshard_after_forward_policy
 
 
-def make_comm(dp_mesh, parallelism):
+def make_comm(dp_mesh, parallelism, model=None, param_dtype=torch.bfloat16):
     """Pick the transport for FSDP collectives: NVLink peer-memory kernels when every rank of the
     shard mesh is a CUDA device of this host and the option is on, else c10d."""
     if parallelism is not None and not getattr(parallelism, "fused_fsdp_collectives", True):
@@ -24,7 +24,7 @@ def make_comm(dp_mesh, parallelism):
     try:
         from .nvlink_comm import NvlinkComm
 
-        return NvlinkComm.maybe_create(dp_mesh)
+        return NvlinkComm.maybe_create(dp_mesh, model=model, param_dtype=param_dtype)
     except ImportError:
         return None
 
@@ -42,7 +42,7 @@ def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype
     reshard = get_fsdp_reshard_after_forward_policy(
         reshard_after_forward_policy, pp_enabled, param_bytes=_compute_copy_bytes(model, param_dtype)
     )
-    comm = make_comm(dp_mesh, parallelism)
+    comm = make_comm(dp_mesh, parallelism, model=model, param_dtype=param_dtype)
     kw = dict(mesh=dp_mesh, mp_policy=mp, comm=comm)
     if getattr(model, "tok_embeddings", None) is not None:
         fully_shard(model.tok_embeddings, **kw, reshard_after_forward=reshard)

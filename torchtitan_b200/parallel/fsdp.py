@@ -90,6 +90,24 @@ def _contig_stride(shape):
     return tuple(reversed(st))
 
 
+class GradSlot:
+    """Where a weight-gradient GEMM may write its result directly (skipping the autograd-owned
+    temporary): the fp32 gradient shard itself when the shard world is one, or a bf16 slice of the
+    NVLink staging buffer that peers reduce from. The GEMM asks :meth:`begin` whether to
+    accumulate and the unit learns through ``written`` that nothing is left to copy."""
+
+    __slots__ = ("tensor", "unit", "index")
+
+    def __init__(self, tensor, unit, index):
+        self.tensor, self.unit, self.index = tensor, unit, index
+
+    def begin(self) -> bool:
+        u = self.unit
+        acc = u._slot_accumulate or u._slot_written[self.index]
+        u._slot_written[self.index] = True
+        return acc
+
+
 class ShardComm:
     """Transport used by a unit; the unit handles streams and ordering."""
 
@@ -125,12 +143,22 @@ class C10dComm(ShardComm):
     def reduce_scatter(self, unit, grads, accumulate):
         W, g, rd = unit.shard_world, unit.shard_group, unit.reduce_dtype
         pending = []
-        for p, gr in zip(unit.params, grads):
+        for i, (p, gr) in enumerate(zip(unit.params, grads)):
             n = p.chunk_rows * p.inner
             dst = unit.grad_shard_flat[p.shard_off : p.shard_off + n]
+            if unit.slot_was_written(i):
+                # the weight-gradient GEMM wrote (or accumulated) straight into the shard; what autograd
+                # delivered is a zero-stride placeholder unless the parameter had another use (tied weights)
+                if gr is not None and any(st != 0 for st in gr.stride()):
+                    dst.add_(gr.reshape(-1))
+                continue
             if gr is None:
                 if not accumulate:
                     dst.zero_()
+                continue
+            if W == 1 and unit.replicate_group is None:
+                src = gr.reshape(-1)
+                dst.add_(src) if accumulate else dst.copy_(src)  # one fused cast-copy
                 continue
             full = unit.pack_grad(p, gr, rd)  # [W * n], reduce dtype, chunk-major
             if W == 1:
@@ -266,6 +294,10 @@ class FSDPUnit:
         self._materialized = False
         self._grad_dtensors: list = []
         self._fwd_params = None
+        self.params_version = 0  # bumped (in lockstep on all ranks) whenever the master shard changes
+        self._slots: list = []
+        self._slot_written: list = []
+        self._slot_accumulate = False
         self.is_root = False
         self.prev: FSDPUnit | None = None
         self.next: FSDPUnit | None = None
@@ -314,9 +346,30 @@ class FSDPUnit:
                 p.param.data = view
         if self.param_dtype != self.orig_dtype:
             self.shadow_flat = self.alloc_shard_buffer(self.param_dtype, kind="shadow")
+        for i, p in enumerate(self.params):
+            p.param._tt_unit = (self, i)
         self._anchor = torch.zeros((), device=dev, requires_grad=True)
         self._grad_dtensors = [None] * len(self.params)
         self._shadow_stale = True
+        self._build_grad_slots()
+
+    def _build_grad_slots(self):
+        """Direct weight-gradient destinations for 2-D parameters on CUDA (see GradSlot)."""
+        self._slots = [None] * len(self.params)
+        self._slot_written = [False] * len(self.params)
+        if not self.uses_cuda:
+            return
+        make = getattr(self.comm, "make_grad_slot", None)
+        for i, p in enumerate(self.params):
+            if len(p.full_shape) != 2 or p.shard_dim != 0 or not p.param.requires_grad:
+                continue
+            t = None
+            if make is not None:
+                t = make(self, p)
+            elif self.shard_world == 1 and self.replicate_group is None and self.grad_shard_flat.dtype == torch.float32:
+                t = self._shard_view(self.grad_shard_flat, p)
+            if t is not None:
+                self._slots[i] = GradSlot(t, self, i)
 
     def alloc_shard_buffer(self, dtype, kind: str):
         alloc = getattr(self.comm, "alloc_shard_buffer", None)
@@ -346,6 +399,7 @@ class FSDPUnit:
         """The optimizer (or a checkpoint load) changed the master shard."""
         self._shadow_stale = not shadow_is_fresh
         self._gathered = False
+        self.params_version += 1
 
     def _storage_alive(self) -> bool:
         return self.unsharded_flat is not None and self.unsharded_flat.untyped_storage().size() > 0
@@ -480,6 +534,10 @@ class FSDPUnit:
         else:
             outs = tuple(p.unsharded for p in self.params)
         self._fwd_params = outs  # the same tensor objects are re-bound for recompute in backward
+        if self._slots:
+            for o, slot in zip(outs, self._slots):
+                if slot is not None:
+                    o._grad_slot = slot
         self._bind(outs)
         return cast_result
 
@@ -513,6 +571,9 @@ class FSDPUnit:
     def _pre_backward(self, grad):
         if not self._in_backward:
             self._in_backward = True
+            first = next((p for p in self.params if p.param.requires_grad), None)
+            self._slot_accumulate = first is not None and first.param.grad is not None
+            self._slot_written = [False] * len(self.params)
             self.unshard()
             if self.prev is not None and self.prev.reshard_after_forward and not self.prev._in_backward:
                 self.prev.unshard(async_op=True)
@@ -542,9 +603,13 @@ class FSDPUnit:
         self._in_backward = False
         self._forward_active = False
         self._fwd_params = None
+        self._slot_written = [False] * len(self.params)
         self._bind_sharded()
         if self.reshard_after_forward:
             self.reshard()
+
+    def slot_was_written(self, i: int) -> bool:
+        return bool(self._slots) and self._slots[i] is not None and self._slot_written[i]
 
     def wait_for_reduce(self):
         if self._reduce_event is not None:

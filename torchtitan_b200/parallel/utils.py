@@ -182,16 +182,18 @@ def _local(t):
 
 @torch.no_grad()
 def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, error_if_nonfinite: bool = False,
-                    foreach: bool | None = None, pp_mesh=None, ep_enabled: bool = False) -> torch.Tensor:
+                    foreach: bool | None = None, pp_mesh=None, ep_enabled: bool = False,
+                    fold_into_optimizer: bool = False) -> torch.Tensor:
     """Clip the global gradient norm of (sharded) parameters; returns the total norm.
 
-    Each rank computes the norm of its *local* shards; the partial norms are combined over every
-    mesh dimension on which a gradient is sharded (read from the DTensor placements; tagged
-    tensor/expert-parallel shards add their groups) and over pipeline stages. FSDP units
-    contribute one fused sum-of-squares launch over their flat gradient shard.
+    Each rank computes the norm of its *local* shards; partial norms are summed over every mesh
+    dimension on which a gradient is sharded (read from the DTensor placements; tagged
+    tensor/expert-parallel shards add their groups) and over pipeline stages. FSDP units whose
+    gradients all live in the unit's flat shard contribute one sum-of-squares launch, and with
+    ``fold_into_optimizer`` the clip coefficient is handed to the flat-shard optimizer as a device
+    scalar instead of being multiplied into the gradients (the gradients then stay unscaled).
     """
     from torchtitan_b200.ops import optim_ops
-    from torchtitan_b200.parallel.fsdp import FSDPUnit
 
     if isinstance(parameters, torch.Tensor):
         parameters = [parameters]
@@ -200,36 +202,64 @@ def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, error_i
         return torch.tensor(0.0)
     norm_type = float(norm_type)
     inf = math.isinf(norm_type)
-    # group local partial norms by the set of process groups over which they must be summed
-    buckets: dict[tuple, list] = {}
+    device = _local(params[0].grad).device
+
+    # ---- split parameters into whole FSDP units (flat path) and loose tensors -------------------
+    flat_units, loose = [], []
+    if norm_type == 2.0:
+        by_unit: dict[int, list] = {}
+        for p in params:
+            ref = getattr(p, "_tt_unit", None)
+            if ref is None or getattr(p, "_extra_norm_groups", None):
+                loose.append(p)
+            else:
+                by_unit.setdefault(id(ref[0]), [ref[0], []])[1].append(p)
+        for unit, plist in by_unit.values():
+            owned = [q.param for q in unit.params if q.param.requires_grad]
+            whole = len(plist) == len(owned) and all(
+                _local(q.grad).untyped_storage().data_ptr() == unit.grad_shard_flat.untyped_storage().data_ptr()
+                for q in plist
+            )
+            if whole:
+                flat_units.append(unit)
+            else:
+                loose.extend(plist)
+    else:
+        loose = params
+
     group_objs: dict[int, object] = {}
-    units_done: dict[int, FSDPUnit] = {}
-    for p in params:
+    buckets: dict[tuple, list] = {}
+
+    def add(groups, tensor):
+        key = tuple(sorted(id(g) for g in groups))
+        for g in groups:
+            group_objs[id(g)] = g
+        buckets.setdefault(key, []).append(tensor)
+
+    for unit in flat_units:
+        add([unit.shard_group] if unit.shard_world > 1 else [], unit.grad_shard_flat)
+    for p in loose:
         g = p.grad
         groups = []
         if isinstance(g, DTensor):
             for i, pl in enumerate(g.placements):
                 if pl.is_shard() or pl.is_partial():
                     groups.append(g.device_mesh.get_group(i))
-        for extra in getattr(p, "_extra_norm_groups", ()):  # TP / EP shards kept as local tensors
-            groups.append(extra)
-        key = tuple(sorted(id(x) for x in groups))
-        for x in groups:
-            group_objs[id(x)] = x
-        buckets.setdefault(key, []).append(_local(g))
-    device = _local(params[0].grad).device
+        groups.extend(getattr(p, "_extra_norm_groups", ()))
+        add(groups, _local(g))
+
     total = torch.zeros((), dtype=torch.float32, device=device)
     for key, grads in buckets.items():
         if inf:
-            part = torch.stack([g.detach().abs().max().float() if g.numel() else torch.zeros((), device=device) for g in grads]).max()
+            part = torch.stack([g.abs().max().float() if g.numel() else torch.zeros((), device=device) for g in grads]).max()
         elif norm_type == 2.0:
             part = torch.zeros((), dtype=torch.float32, device=device)
             for g in grads:
                 if g.numel():
                     part = part + optim_ops.sumsq(g.reshape(-1) if g.is_contiguous() else g.contiguous().view(-1))
         else:
-            part = torch.stack([torch.linalg.vector_norm(g.float(), norm_type) ** norm_type for g in grads if g.numel()]).sum() \
-                if any(g.numel() for g in grads) else torch.zeros((), device=device)
+            terms = [torch.linalg.vector_norm(g.float(), norm_type) ** norm_type for g in grads if g.numel()]
+            part = torch.stack(terms).sum() if terms else torch.zeros((), device=device)
         for gid in key:
             dist.all_reduce(part, op=dist.ReduceOp.MAX if inf else dist.ReduceOp.SUM, group=group_objs[gid])
         total = torch.maximum(total, part) if inf else total + part
@@ -239,14 +269,18 @@ def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, error_i
     if error_if_nonfinite and not torch.isfinite(total_norm):
         raise RuntimeError(f"The total norm of order {norm_type} for gradients is non-finite")
     coef = torch.clamp(max_norm / (total_norm + 1e-6), max=1.0)
+    for unit in flat_units:
+        if fold_into_optimizer:
+            unit.pending_grad_scale = coef
+        else:
+            unit.grad_shard_flat.mul_(coef.to(unit.grad_shard_flat.dtype))
     seen = set()
-    for p in params:
+    for p in loose:
         g = _local(p.grad)
-        base = g.untyped_storage().data_ptr()
-        if (base, g.storage_offset(), g.numel()) in seen:
-            continue
-        seen.add((base, g.storage_offset(), g.numel()))
-        g.mul_(coef.to(g.dtype))
+        key = (g.untyped_storage().data_ptr(), g.storage_offset(), g.numel())
+        if key not in seen:
+            seen.add(key)
+            g.mul_(coef.to(g.dtype))
     return total_norm
 
 

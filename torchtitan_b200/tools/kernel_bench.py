@@ -1,0 +1,149 @@
+"""Micro-benchmarks of the native kernels with CUDA-event timing.
+
+    python -m torchtitan_b200.tools.kernel_bench gemm --m 8192 --n 14336 --k 4096 [--layout nn|nt|tt] [--compare]
+    python -m torchtitan_b200.tools.kernel_bench attention --seq 8192 --heads 32 --kv-heads 8 [--compare]
+    python -m torchtitan_b200.tools.kernel_bench elementwise
+
+Each case is warmed up, then timed over ``--iters`` launches on the current stream; between timed
+launches a buffer larger than L2 is overwritten so every launch starts cold. ``--compare`` also
+times the PyTorch library op (cuBLAS / SDPA) for reference. Prints one JSON line per case.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+
+class Timer:
+    def __init__(self, flush_mb: int = 256):
+        self.flush = torch.empty(flush_mb * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    def time(self, fn, iters: int, warmup: int = 3) -> float:
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(iters):
+            self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / iters
+
+
+def bench_gemm(args, timer):
+    from torchtitan_b200.ops import cuda_ops
+
+    M, N, K = args.m, args.n, args.k
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    lay = args.layout
+    a_mn, b_mn = lay in ("tt",), lay in ("nt", "tt")
+    A = a.t().contiguous() if a_mn else a
+    B = b.t().contiguous() if b_mn else b
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = timer.time(lambda: cuda_ops.gemm_into(A, B, out, a_mn=a_mn, b_mn=b_mn), args.iters)
+    res = {"case": f"gemm_{lay}", "M": M, "N": N, "K": K, "ms": ms, "tflops": 2 * M * N * K / ms / 1e9}
+    if args.compare:
+        if lay == "nn":
+            f = lambda: torch.matmul(a, b.t(), out=out)
+        elif lay == "nt":
+            f = lambda: torch.matmul(a, B, out=out)
+        else:
+            f = lambda: torch.matmul(A.t(), B, out=out)
+        ms2 = timer.time(f, args.iters)
+        res.update({"cublas_ms": ms2, "cublas_tflops": 2 * M * N * K / ms2 / 1e9, "ratio_vs_cublas": ms2 / ms})
+    return res
+
+
+def bench_attention(args, timer):
+    from torchtitan_b200.ops import cuda_ops
+
+    B, S, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, 128
+    q = torch.randn(B, S, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    scale = 1 / math.sqrt(D)
+    fwd_flops = 4 * B * H * S * S * D / 2  # causal
+    o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, True, scale)
+    do = torch.randn_like(o)
+    ms_f = timer.time(lambda: torch.ops.tt_b200.attention_fwd(q, k, v, True, scale), args.iters)
+    ms_b = timer.time(lambda: torch.ops.tt_b200.attention_bwd(q, k, v, o, do, lse, True, scale), args.iters)
+    res = {"case": "attention_causal", "B": B, "S": S, "H": H, "Hkv": Hkv, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9,
+           "bwd_ms": ms_b, "bwd_tflops_algorithmic(2.5x fwd)": 2.5 * fwd_flops / ms_b / 1e9,
+           "bwd_tflops_executed(3.5x fwd)": 3.5 * fwd_flops / ms_b / 1e9}
+    if args.compare:
+        qt, kt, vt = (t.detach().transpose(1, 2).requires_grad_() for t in (q, k, v))
+        f = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True)
+        ms_sf = timer.time(f, args.iters)
+        out = f()
+        g = torch.randn_like(out)
+        ms_sb = timer.time(lambda: torch.autograd.grad(out, (qt, kt, vt), g, retain_graph=True), args.iters)
+        res.update({"sdpa_fwd_ms": ms_sf, "sdpa_bwd_ms": ms_sb})
+    return res
+
+
+def bench_elementwise(args, timer):
+    from torchtitan_b200.ops import cuda_ops
+
+    out = []
+    rows, D = 8192, 4096
+    x = torch.randn(rows, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    ms = timer.time(lambda: torch.ops.tt_b200.rmsnorm_fwd(x, w, 1e-5), args.iters)
+    out.append({"case": "rmsnorm_fwd", "rows": rows, "D": D, "ms": ms, "GBps": 2 * x.numel() * 2 / ms / 1e6})
+    g = torch.randn(rows, 14336, device="cuda").bfloat16()
+    u = torch.randn_like(g)
+    ms = timer.time(lambda: torch.ops.tt_b200.swiglu_fwd(g, u), args.iters)
+    out.append({"case": "swiglu_fwd", "n": g.numel(), "ms": ms, "GBps": 3 * g.numel() * 2 / ms / 1e6})
+    V = 128256
+    logits = torch.randn(rows, V, device="cuda").bfloat16()
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    ms = timer.time(lambda: torch.ops.tt_b200.ce_fwd(logits, labels, -100), args.iters)
+    out.append({"case": "ce_fwd", "rows": rows, "V": V, "ms": ms, "GBps": logits.numel() * 2 / ms / 1e6})
+    n = 1 << 28
+    p = torch.randn(n, device="cuda"); gr = torch.randn(n, device="cuda"); m = torch.zeros(n, device="cuda"); vv = torch.zeros(n, device="cuda")
+    sh = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = timer.time(lambda: cuda_ops.adamw_flat(p, gr, m, vv, sh, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3), args.iters)
+    out.append({"case": "adamw", "n": n, "ms": ms, "GBps": n * (4 * 4 + 3 * 4 + 2) / ms / 1e6})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attention", "elementwise"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="nn", choices=["nn", "nt", "tt"],
+                    help="nn: x@W^T (both K-major); nt: dgrad (B stored [K,N]); tt: wgrad (both stored transposed)")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--compare", action="store_true")
+    args = ap.parse_args()
+    timer = Timer()
+    if args.what == "gemm":
+        res = [bench_gemm(args, timer)]
+    elif args.what == "attention":
+        res = [bench_attention(args, timer)]
+    else:
+        res = bench_elementwise(args, timer)
+    from torchtitan_b200.ops import native
+
+    for r in res:
+        r["kernel_errors"] = native.kernel_errors()
+        print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()

@@ -229,6 +229,10 @@ class Trainer(Stateful, Configurable):
         self.metrics_processor.optimizers = self.optimizers
         self.metrics_processor.lr_schedulers = self.lr_schedulers
 
+        from torchtitan_b200.components.optimizer import ShardAdamW
+
+        # the flat-shard optimizer can apply the clip coefficient itself (one pass less over the gradients)
+        self._fold_clip = all(isinstance(o, ShardAdamW) and not o.has_loose_params for o in self.optimizers.optimizers)
         self.step = 0
         self.ntokens_seen = 0
         self.checkpointer = config.checkpoint.build(
@@ -365,6 +369,7 @@ class Trainer(Stateful, Configurable):
         grad_norm = dist_utils.clip_grad_norm_(
             [p for m in self.model_parts for p in m.parameters()], self.config.training.max_norm,
             foreach=True, pp_mesh=pd.get_optional_mesh("pp"), ep_enabled=pd.ep_enabled,
+            fold_into_optimizer=self._fold_clip,
         )
         self.checkpointer.maybe_wait_for_staging()
         self.optimizers.step()
