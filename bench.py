@@ -238,6 +238,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: truncate the model (result is not a benchmark)")
+    ap.add_argument("--ref-compile", action="store_true", help="reference arm only: add --compile.enable")
     ap.add_argument("--ac", default=None, help="override activation_checkpoint.mode (selective|full|none)")
     args = ap.parse_args()
     assert args.warmup >= 3 or os.environ.get("TT_BENCH_ALLOW_SHORT_WARMUP"), "warm-up must be at least 3 steps"

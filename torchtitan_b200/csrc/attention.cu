@@ -57,6 +57,34 @@ __device__ __forceinline__ void store_row_sw128(uint8_t* tile, int row, const fl
   }
 }
 
+// Write 32 fp32 values as one half (64 bytes) of a 128-byte bf16 row; half = 0 (cols 0..31) or 1.
+__device__ __forceinline__ void store_halfrow_sw128(uint8_t* tile, int row, int half, const float (&v)[32]) {
+  uint8_t* r = tile + row * 128;
+  const int x = row & 7;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q;
+    q.x = tt::pack_bf16(v[8 * c + 0], v[8 * c + 1]);
+    q.y = tt::pack_bf16(v[8 * c + 2], v[8 * c + 3]);
+    q.z = tt::pack_bf16(v[8 * c + 4], v[8 * c + 5]);
+    q.w = tt::pack_bf16(v[8 * c + 6], v[8 * c + 7]);
+    *reinterpret_cast<uint4*>(r + (((half * 4 + c) ^ x) << 4)) = q;
+  }
+}
+
+// 32 fp32 TMEM columns -> 32 bf16 written to a global row segment
+__device__ __forceinline__ void store_out_32(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
+#pragma unroll
+  for (int v4 = 0; v4 < 4; ++v4) {
+    uint4 q;
+    q.x = tt::pack_bf16(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
+    q.y = tt::pack_bf16(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
+    q.z = tt::pack_bf16(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
+    q.w = tt::pack_bf16(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
+    *reinterpret_cast<uint4*>(dst + v4 * 8) = q;
+  }
+}
+
 // ---- UMMA helpers for the fixed tile shapes used here -------------------------------------------
 // K-major operand made of two 64-wide halves along the contraction (head dim 128): rows x 128 bf16,
 // half h at base + h * rows*128 bytes. Contraction step kk (16 wide), kk in [0, 8).
@@ -273,21 +301,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 }
 
 // =================================================================================== backward: dQ
-// CTA = 128 query rows. smem: Q 32K | dO 32K | K 2x16K | V 2x16K | dS 2x16K | barriers
-constexpr uint32_t Q_Q = 0, Q_DO = 32768, Q_K = 65536, Q_V = Q_K + 32768, Q_DS = Q_V + 32768, Q_BAR = Q_DS + 32768;
+// CTA = 128 query rows. smem: Q 32K | dO 32K | K/V ring NS x (16K + 16K) | dS 2x16K | barriers
+constexpr int Q_NS = 3;  // K/V stages: a stage is reloaded only after the dQ MMAs that read it have
+                         // completed, so the ring must cover TMA latency plus one full step
+constexpr uint32_t Q_Q = 0, Q_DO = 32768, Q_KV = 65536, Q_DS = Q_KV + Q_NS * 32768, Q_BAR = Q_DS + 32768;
 constexpr size_t DQ_SMEM = 1024 + Q_BAR + 256;
+// barriers
+constexpr int QB_QFULL = 0, QB_KVFULL = 1, QB_KVEMPTY = QB_KVFULL + Q_NS, QB_SPFULL = QB_KVEMPTY + Q_NS,
+              QB_DSREADY = QB_SPFULL + 2, QB_DSFREE = QB_DSREADY + 2, QB_COUNT = QB_DSFREE + 2;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                    const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, AttnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
   const uint32_t bar0 = base + Q_BAR;
-  // 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 sp_full | 7,8 ds_ready | 9,10 ds_free(dq step done)
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + Q_BAR + 8 * 11);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + Q_BAR + 8 * 11 + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + Q_BAR + 8 * QB_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + Q_BAR + 8 * QB_COUNT + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;
@@ -299,7 +331,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   if (p.causal) n_kv = min(n_kv, (q0 + 127 + off) / 64 + 1);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) tt::mbar_init(bar(i), (i == 7 || i == 8) ? 4 : 1);
+    for (int i = 0; i < QB_COUNT; ++i) tt::mbar_init(bar(i), (i >= QB_DSREADY && i < QB_DSFREE) ? 8 : 1);
     *abort_flag = 0;
     tt::mbar_fence_init();
   }
@@ -313,59 +345,56 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 
   if (warp == 0) {
     if (tt::elect_one()) {
-      tt::mbar_expect_tx(bar(0), 65536);
-      tt::tma_load_3d(base + Q_Q, &tq, bar(0), 0, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + Q_Q + 16384, &tq, bar(0), 64, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + Q_DO, &tdo, bar(0), 0, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + Q_DO + 16384, &tdo, bar(0), 64, h, b * p.Sq + q0);
+      tt::mbar_expect_tx(bar(QB_QFULL), 65536);
+      tt::tma_load_3d(base + Q_Q, &tq, bar(QB_QFULL), 0, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + Q_Q + 16384, &tq, bar(QB_QFULL), 64, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + Q_DO, &tdo, bar(QB_QFULL), 0, h, b * p.Sq + q0);
+      tt::tma_load_3d(base + Q_DO + 16384, &tdo, bar(QB_QFULL), 64, h, b * p.Sq + q0);
       for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 21)) break;
-        tt::mbar_expect_tx(bar(1 + s), 32768);
-        tt::tma_load_3d(base + Q_K + s * 16384, &tk, bar(1 + s), 0, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(base + Q_K + s * 16384 + 8192, &tk, bar(1 + s), 64, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(base + Q_V + s * 16384, &tv, bar(1 + s), 0, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(base + Q_V + s * 16384 + 8192, &tv, bar(1 + s), 64, hk, b * p.Sk + j * 64);
+        const int s = j % Q_NS; const uint32_t ph = (j / Q_NS) & 1;
+        if (!tt::mbar_wait(bar(QB_KVEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 21)) break;
+        const uint32_t kb = base + Q_KV + s * 32768, vb = kb + 16384;
+        tt::mbar_expect_tx(bar(QB_KVFULL + s), 32768);
+        tt::tma_load_3d(kb, &tk, bar(QB_KVFULL + s), 0, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(kb + 8192, &tk, bar(QB_KVFULL + s), 64, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(vb, &tv, bar(QB_KVFULL + s), 0, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(vb + 8192, &tv, bar(QB_KVFULL + s), 64, hk, b * p.Sk + j * 64);
       }
     }
   } else if (warp == 1) {
     if (tt::elect_one()) {
-      bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 22);
-      auto issue_sp = [&](int j) {
-        const int s = j & 1;
-        const uint32_t kb = base + Q_K + s * 16384, vb = base + Q_V + s * 16384;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tS + s * 64, desc_kmajor_dh(base + Q_Q, 128, kk), desc_kmajor_dh(kb, 64, kk), IDESC_128x64_KK, kk != 0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tDP + s * 64, desc_kmajor_dh(base + Q_DO, 128, kk), desc_kmajor_dh(vb, 64, kk), IDESC_128x64_KK, kk != 0);
-        tt::umma_commit(bar(5 + s));
-      };
-      if (ok && n_kv > 0) {
-        ok = tt::mbar_wait(bar(1), 0, abort_flag, &g_attn_error, 23);
-        if (ok) { tt::tc_fence_after(); issue_sp(0); }
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          const int s1 = (j + 1) & 1;
-          if (!tt::mbar_wait(bar(1 + s1), ((j + 1) >> 1) & 1, abort_flag, &g_attn_error, 24)) break;
-          tt::tc_fence_after();
-          issue_sp(j + 1);
-        }
-        const int s = j & 1;
-        if (!tt::mbar_wait(bar(7 + s), (j >> 1) & 1, abort_flag, &g_attn_error, 25)) break;
+      bool ok = tt::mbar_wait(bar(QB_QFULL), 0, abort_flag, &g_attn_error, 22);
+      auto issue_sp = [&](int j) -> bool {
+        const int s = j % Q_NS, t2 = j & 1;
+        if (!tt::mbar_wait(bar(QB_KVFULL + s), (j / Q_NS) & 1, abort_flag, &g_attn_error, 23)) return false;
         tt::tc_fence_after();
-        const uint32_t kb = base + Q_K + s * 16384;
+        const uint32_t kb = base + Q_KV + s * 32768, vb = kb + 16384;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tS + t2 * 64, desc_kmajor_dh(base + Q_Q, 128, kk), desc_kmajor_dh(kb, 64, kk), IDESC_128x64_KK, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tDP + t2 * 64, desc_kmajor_dh(base + Q_DO, 128, kk), desc_kmajor_dh(vb, 64, kk), IDESC_128x64_KK, kk != 0);
+        tt::umma_commit(bar(QB_SPFULL + t2));
+        return true;
+      };
+      if (ok && n_kv > 0) ok = issue_sp(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv && !issue_sp(j + 1)) break;
+        const int s = j % Q_NS, t2 = j & 1;
+        if (!tt::mbar_wait(bar(QB_DSREADY + t2), (j >> 1) & 1, abort_flag, &g_attn_error, 25)) break;
+        tt::tc_fence_after();
+        const uint32_t kb = base + Q_KV + s * 32768;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tDQ, desc_kmajor_64(base + Q_DS + s * 16384, kk), desc_mnmajor(kb, 64, kk), IDESC_128x128_KM, (j | kk) != 0);
-        tt::umma_commit(bar(9 + s));   // dS buffer s free, dQ step done
-        tt::umma_commit(bar(3 + s));   // K/V stage free
+          tt::umma_f16_ss(tDQ, desc_kmajor_64(base + Q_DS + t2 * 16384, kk), desc_mnmajor(kb, 64, kk), IDESC_128x128_KM, (j | kk) != 0);
+        tt::umma_commit(bar(QB_DSFREE + t2));   // dS buffer free, dQ step done
+        tt::umma_commit(bar(QB_KVEMPTY + s));   // K/V stage free
       }
     }
   } else {
-    const int lg = warp & 3, row = lg * 32 + lane;
+    // 8 softmax warps: lane group = warp & 3 (query row), column half = (warp - 2) >> 2
+    const int lg = warp & 3, row = lg * 32 + lane, half = (warp - 2) >> 2;
     const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
     const int qi = q0 + row;
     const long long stat = (static_cast<long long>(b) * p.H + h) * p.Sq + qi;
@@ -374,53 +403,43 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const float sc = p.scale * kLog2e;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      const int s = j & 1;
-      if (!tt::mbar_wait(bar(5 + s), (j >> 1) & 1, abort_flag, &g_attn_error, 26)) { ok = false; break; }
+      const int t2 = j & 1;
+      if (!tt::mbar_wait(bar(QB_SPFULL + t2), (j >> 1) & 1, abort_flag, &g_attn_error, 26)) { ok = false; break; }
       tt::tc_fence_after();
-      float ds[64];
-      const int kv0 = j * 64;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      float ds[32];
+      const int kv0 = j * 64 + half * 32;
+      {
         uint32_t rs[32], rp[32];
-        tt::tmem_ld_32x32(tS + lane_off + s * 64 + half * 32, rs);
-        tt::tmem_ld_32x32(tDP + lane_off + s * 64 + half * 32, rp);
+        tt::tmem_ld_32x32(tS + lane_off + t2 * 64 + half * 32, rs);
+        tt::tmem_ld_32x32(tDP + lane_off + t2 * 64 + half * 32, rp);
         tt::tc_wait_ld();
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          const int kv = kv0 + half * 32 + e;
           float pr = fast_exp2(__uint_as_float(rs[e]) * sc - lse2);
-          if (p.causal && kv > qi + off) pr = 0.f;
-          ds[half * 32 + e] = pr * (__uint_as_float(rp[e]) - dl) * p.scale;
+          if (p.causal && kv0 + e > qi + off) pr = 0.f;
+          ds[e] = pr * (__uint_as_float(rp[e]) - dl) * p.scale;
         }
       }
-      if (j >= 2 && !tt::mbar_wait(bar(9 + s), ((j - 2) >> 1) & 1, abort_flag, &g_attn_error, 27)) { ok = false; break; }
-      store_row_sw128(gbase + Q_DS + s * 16384, row, ds);
+      if (j >= 2 && !tt::mbar_wait(bar(QB_DSFREE + t2), ((j - 2) >> 1) & 1, abort_flag, &g_attn_error, 27)) { ok = false; break; }
+      store_halfrow_sw128(gbase + Q_DS + t2 * 16384, row, half, ds);
       tt::fence_proxy_async();
       tt::tc_fence_before();
       __syncwarp();
-      if (lane == 0) tt::mbar_arrive(bar(7 + s));
+      if (lane == 0) tt::mbar_arrive(bar(QB_DSREADY + t2));
     }
-    if (ok && n_kv > 0) ok = tt::mbar_wait(bar(9 + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag, &g_attn_error, 28);
+    if (ok && n_kv > 0) ok = tt::mbar_wait(bar(QB_DSFREE + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag, &g_attn_error, 28);
     tt::tc_fence_after();
     if (ok) {
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t r[32];
         if (n_kv > 0) { tt::tmem_ld_32x32(tDQ + lane_off + c * 32, r); tt::tc_wait_ld(); }
         else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) r[e] = 0;
         }
-#pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          uint4 q;
-          q.x = tt::pack_bf16(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
-          q.y = tt::pack_bf16(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
-          q.z = tt::pack_bf16(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
-          q.w = tt::pack_bf16(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
-          *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = q;
-        }
+        store_out_32(orow + c * 32, r);
       }
     }
     tt::tc_fence_before();
@@ -432,23 +451,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 
 // =================================================================================== backward: dK, dV
 // CTA = 128 key rows of one KV head; steps over (query head of the group, 64-row query tile).
-// smem: K 32K | V 32K | Q 2x16K | dO 2x16K | P^T 2x16K | dS^T 2x16K | per-warp lse/delta 4x2x(64+64) floats | barriers
-constexpr uint32_t K_K = 0, K_V = 32768, K_Q = 65536, K_DO = K_Q + 32768, K_PT = K_DO + 32768, K_DST = K_PT + 32768,
-                   K_STAT = K_DST + 32768, K_BAR = K_STAT + 4096;
+// smem: K 32K | V 32K | Q/dO ring NS x (16K + 16K) | P^T 2x16K | dS^T 2x16K | barriers
+// (per-query lse / delta are read straight from global memory: warp-uniform, L1-resident loads)
+constexpr int K_NS = 3;
+constexpr uint32_t K_K = 0, K_V = 32768, K_QDO = 65536, K_PT = K_QDO + K_NS * 32768, K_DST = K_PT + 32768,
+                   K_BAR = K_DST + 32768;
 constexpr size_t DKV_SMEM = 1024 + K_BAR + 256;
+constexpr int KB_KVFULL = 0, KB_QFULL = 1, KB_QEMPTY = KB_QFULL + K_NS, KB_STFULL = KB_QEMPTY + K_NS,
+              KB_PTREADY = KB_STFULL + 2, KB_PTFREE = KB_PTREADY + 2, KB_COUNT = KB_PTFREE + 2;
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                     const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, AttnArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
   const uint32_t bar0 = base + K_BAR;
-  // 0 kv_full | 1,2 q_full | 3,4 q_empty | 5,6 st_full | 7,8 pt_ready | 9,10 pt_free
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + K_BAR + 8 * 11);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + K_BAR + 8 * 11 + 8);
-  float* stat_all = reinterpret_cast<float*>(gbase + K_STAT);  // [4 warps][2 stages][lse 64 | delta 64]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + K_BAR + 8 * KB_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + K_BAR + 8 * KB_COUNT + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -462,7 +483,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   const int n_steps = per_head * G;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) tt::mbar_init(bar(i), (i == 7 || i == 8) ? 4 : 1);
+    for (int i = 0; i < KB_COUNT; ++i) tt::mbar_init(bar(i), (i >= KB_PTREADY && i < KB_PTFREE) ? 8 : 1);
     *abort_flag = 0;
     tt::mbar_fence_init();
   }
@@ -476,110 +497,102 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 
   if (warp == 0) {
     if (tt::elect_one()) {
-      tt::mbar_expect_tx(bar(0), 65536);
-      tt::tma_load_3d(base + K_K, &tk, bar(0), 0, hk, b * p.Sk + kv0);
-      tt::tma_load_3d(base + K_K + 16384, &tk, bar(0), 64, hk, b * p.Sk + kv0);
-      tt::tma_load_3d(base + K_V, &tv, bar(0), 0, hk, b * p.Sk + kv0);
-      tt::tma_load_3d(base + K_V + 16384, &tv, bar(0), 64, hk, b * p.Sk + kv0);
+      tt::mbar_expect_tx(bar(KB_KVFULL), 65536);
+      tt::tma_load_3d(base + K_K, &tk, bar(KB_KVFULL), 0, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_K + 16384, &tk, bar(KB_KVFULL), 64, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_V, &tv, bar(KB_KVFULL), 0, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_V + 16384, &tv, bar(KB_KVFULL), 64, hk, b * p.Sk + kv0);
       for (int st = 0; st < n_steps; ++st) {
-        const int s = st & 1; const uint32_t ph = (st >> 1) & 1;
+        const int s = st % K_NS; const uint32_t ph = (st / K_NS) & 1;
         const int h = hk * G + st / per_head, qt = qt_first + st % per_head;
-        if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 31)) break;
-        tt::mbar_expect_tx(bar(1 + s), 32768);
-        tt::tma_load_3d(base + K_Q + s * 16384, &tq, bar(1 + s), 0, h, b * p.Sq + qt * 64);
-        tt::tma_load_3d(base + K_Q + s * 16384 + 8192, &tq, bar(1 + s), 64, h, b * p.Sq + qt * 64);
-        tt::tma_load_3d(base + K_DO + s * 16384, &tdo, bar(1 + s), 0, h, b * p.Sq + qt * 64);
-        tt::tma_load_3d(base + K_DO + s * 16384 + 8192, &tdo, bar(1 + s), 64, h, b * p.Sq + qt * 64);
+        if (!tt::mbar_wait(bar(KB_QEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 31)) break;
+        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
+        tt::mbar_expect_tx(bar(KB_QFULL + s), 32768);
+        tt::tma_load_3d(qb, &tq, bar(KB_QFULL + s), 0, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(qb + 8192, &tq, bar(KB_QFULL + s), 64, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(dob, &tdo, bar(KB_QFULL + s), 0, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(dob + 8192, &tdo, bar(KB_QFULL + s), 64, h, b * p.Sq + qt * 64);
       }
     }
   } else if (warp == 1) {
     if (tt::elect_one()) {
-      bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 32);
-      auto issue_st = [&](int st) {
-        const int s = st & 1;
-        const uint32_t qb = base + K_Q + s * 16384, dob = base + K_DO + s * 16384;
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tST + s * 64, desc_kmajor_dh(base + K_K, 128, kk), desc_kmajor_dh(qb, 64, kk), IDESC_128x64_KK, kk != 0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tDPT + s * 64, desc_kmajor_dh(base + K_V, 128, kk), desc_kmajor_dh(dob, 64, kk), IDESC_128x64_KK, kk != 0);
-        tt::umma_commit(bar(5 + s));
-      };
-      if (ok && n_steps > 0) {
-        ok = tt::mbar_wait(bar(1), 0, abort_flag, &g_attn_error, 33);
-        if (ok) { tt::tc_fence_after(); issue_st(0); }
-      }
-      for (int st = 0; st < n_steps && ok; ++st) {
-        if (st + 1 < n_steps) {
-          const int s1 = (st + 1) & 1;
-          if (!tt::mbar_wait(bar(1 + s1), ((st + 1) >> 1) & 1, abort_flag, &g_attn_error, 34)) break;
-          tt::tc_fence_after();
-          issue_st(st + 1);
-        }
-        const int s = st & 1;
-        if (!tt::mbar_wait(bar(7 + s), (st >> 1) & 1, abort_flag, &g_attn_error, 35)) break;
+      bool ok = tt::mbar_wait(bar(KB_KVFULL), 0, abort_flag, &g_attn_error, 32);
+      auto issue_st = [&](int st) -> bool {
+        const int s = st % K_NS, t2 = st & 1;
+        if (!tt::mbar_wait(bar(KB_QFULL + s), (st / K_NS) & 1, abort_flag, &g_attn_error, 33)) return false;
         tt::tc_fence_after();
-        const uint32_t qb = base + K_Q + s * 16384, dob = base + K_DO + s * 16384;
+        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tST + t2 * 64, desc_kmajor_dh(base + K_K, 128, kk), desc_kmajor_dh(qb, 64, kk), IDESC_128x64_KK, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tDPT + t2 * 64, desc_kmajor_dh(base + K_V, 128, kk), desc_kmajor_dh(dob, 64, kk), IDESC_128x64_KK, kk != 0);
+        tt::umma_commit(bar(KB_STFULL + t2));
+        return true;
+      };
+      if (ok && n_steps > 0) ok = issue_st(0);
+      for (int st = 0; st < n_steps && ok; ++st) {
+        if (st + 1 < n_steps && !issue_st(st + 1)) break;
+        const int s = st % K_NS, t2 = st & 1;
+        if (!tt::mbar_wait(bar(KB_PTREADY + t2), (st >> 1) & 1, abort_flag, &g_attn_error, 35)) break;
+        tt::tc_fence_after();
+        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tDV, desc_kmajor_64(base + K_PT + s * 16384, kk), desc_mnmajor(dob, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+          tt::umma_f16_ss(tDV, desc_kmajor_64(base + K_PT + t2 * 16384, kk), desc_mnmajor(dob, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tDK, desc_kmajor_64(base + K_DST + s * 16384, kk), desc_mnmajor(qb, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
-        tt::umma_commit(bar(9 + s));   // P^T / dS^T buffers s free
-        tt::umma_commit(bar(3 + s));   // Q / dO stage free
+          tt::umma_f16_ss(tDK, desc_kmajor_64(base + K_DST + t2 * 16384, kk), desc_mnmajor(qb, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+        tt::umma_commit(bar(KB_PTFREE + t2));   // P^T / dS^T buffers free
+        tt::umma_commit(bar(KB_QEMPTY + s));    // Q / dO stage free
       }
     }
   } else {
-    const int lg = warp & 3, row = lg * 32 + lane;   // key row inside the tile
+    // 8 softmax warps: lane group = warp & 3 (key row), column half = (warp - 2) >> 2 (32 queries each)
+    const int lg = warp & 3, row = lg * 32 + lane, half = (warp - 2) >> 2;
     const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
     const int ki = kv0 + row;
     const float sc = p.scale * kLog2e;
-    float* stat = stat_all + lg * 256;
     bool ok = true;
     for (int st = 0; st < n_steps; ++st) {
-      const int s = st & 1;
+      const int t2 = st & 1;
       const int h = hk * G + st / per_head, qt = qt_first + st % per_head;
-      // per-column statistics of this step's 64 queries: every warp keeps its own copy in shared
-      // memory (lane l loads 4 of the 128 values), so no cross-warp barrier is needed
-      {
-        const long long sb = (static_cast<long long>(b) * p.H + h) * p.Sq + qt * 64;
-        stat[s * 128 + lane] = p.lse[sb + lane] * kLog2e;
-        stat[s * 128 + 32 + lane] = p.lse[sb + 32 + lane] * kLog2e;
-        stat[s * 128 + 64 + lane] = p.delta[sb + lane];
-        stat[s * 128 + 96 + lane] = p.delta[sb + 32 + lane];
-        __syncwarp();
-      }
-      if (!tt::mbar_wait(bar(5 + s), (st >> 1) & 1, abort_flag, &g_attn_error, 37)) { ok = false; break; }
+      const int qbase = qt * 64 + half * 32;
+      const float* lse_g = p.lse + (static_cast<long long>(b) * p.H + h) * p.Sq + qbase;
+      const float* dl_g = p.delta + (static_cast<long long>(b) * p.H + h) * p.Sq + qbase;
+      if (!tt::mbar_wait(bar(KB_STFULL + t2), (st >> 1) & 1, abort_flag, &g_attn_error, 37)) { ok = false; break; }
       tt::tc_fence_after();
-      float pt[64], dst[64];
-      const float* lse_s = stat + s * 128;
-      const float* dl_s = stat + s * 128 + 64;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      float pt[32], dst[32];
+      {
         uint32_t rs[32], rp[32];
-        tt::tmem_ld_32x32(tST + lane_off + s * 64 + half * 32, rs);
-        tt::tmem_ld_32x32(tDPT + lane_off + s * 64 + half * 32, rp);
+        tt::tmem_ld_32x32(tST + lane_off + t2 * 64 + half * 32, rs);
+        tt::tmem_ld_32x32(tDPT + lane_off + t2 * 64 + half * 32, rp);
         tt::tc_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int c = half * 32 + e;
-          const int qi = qt * 64 + c;
-          float pr = fast_exp2(__uint_as_float(rs[e]) * sc - lse_s[c]);
-          if (p.causal && ki > qi + off) pr = 0.f;
-          pt[c] = pr;
-          dst[c] = pr * (__uint_as_float(rp[e]) - dl_s[c]) * p.scale;
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_g) + e4);
+          const float4 d4 = __ldg(reinterpret_cast<const float4*>(dl_g) + e4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e4 * 4 + u;
+            float pr = fast_exp2(__uint_as_float(rs[e]) * sc - ls[u] * kLog2e);
+            if (p.causal && ki > qbase + e + off) pr = 0.f;
+            pt[e] = pr;
+            dst[e] = pr * (__uint_as_float(rp[e]) - dd[u]) * p.scale;
+          }
         }
       }
-      store_row_sw128(gbase + K_PT + s * 16384, row, pt);
-      store_row_sw128(gbase + K_DST + s * 16384, row, dst);
+      if (st >= 2 && !tt::mbar_wait(bar(KB_PTFREE + t2), ((st - 2) >> 1) & 1, abort_flag, &g_attn_error, 36)) { ok = false; break; }
+      store_halfrow_sw128(gbase + K_PT + t2 * 16384, row, half, pt);
+      store_halfrow_sw128(gbase + K_DST + t2 * 16384, row, half, dst);
       tt::fence_proxy_async();
       tt::tc_fence_before();
       __syncwarp();
-      if (lane == 0) tt::mbar_arrive(bar(7 + s));
+      if (lane == 0) tt::mbar_arrive(bar(KB_PTREADY + t2));
     }
-    if (ok && n_steps > 0) ok = tt::mbar_wait(bar(9 + ((n_steps - 1) & 1)), ((n_steps - 1) >> 1) & 1, abort_flag, &g_attn_error, 38);
+    if (ok && n_steps > 0) ok = tt::mbar_wait(bar(KB_PTFREE + ((n_steps - 1) & 1)), ((n_steps - 1) >> 1) & 1, abort_flag, &g_attn_error, 38);
     tt::tc_fence_after();
     if (ok) {
       const long long o = ((static_cast<long long>(b) * p.Sk + ki) * p.Hkv + hk) * D;
@@ -590,22 +603,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         __nv_bfloat16* dstp = which ? dk : dv;
         const uint32_t t = which ? tDK : tDV;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = half * 2; c < half * 2 + 2; ++c) {
           uint32_t r[32];
           if (n_steps > 0) { tt::tmem_ld_32x32(t + lane_off + c * 32, r); tt::tc_wait_ld(); }
           else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) r[e] = 0;
           }
-#pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint4 q;
-            q.x = tt::pack_bf16(__uint_as_float(r[8 * v4 + 0]), __uint_as_float(r[8 * v4 + 1]));
-            q.y = tt::pack_bf16(__uint_as_float(r[8 * v4 + 2]), __uint_as_float(r[8 * v4 + 3]));
-            q.z = tt::pack_bf16(__uint_as_float(r[8 * v4 + 4]), __uint_as_float(r[8 * v4 + 5]));
-            q.w = tt::pack_bf16(__uint_as_float(r[8 * v4 + 6]), __uint_as_float(r[8 * v4 + 7]));
-            *reinterpret_cast<uint4*>(dstp + c * 32 + v4 * 8) = q;
-          }
+          store_out_32(dstp + c * 32, r);
         }
       }
     }
@@ -717,9 +722,9 @@ int tt_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta};
-  attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 192, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
+  attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 320, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
   AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta};
-  attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 192, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
+  attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 320, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

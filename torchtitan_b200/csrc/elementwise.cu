@@ -178,31 +178,51 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, T* __r
 // ============================================================================ RoPE
 // x [B,S,H,D]; table [maxS, D/2] float2 (cos, sin); pos (optional) int64 [pos_batch(1|B), S].
 // layout 0: pairs (2i, 2i+1); layout 1: pairs (i, i + D/2). inverse: rotate by -angle (backward).
+// Vectorised: one thread rotates 8 consecutive elements (interleaved layout: 4 pairs) or 8 elements
+// of the first half together with their partners in the second half (half layout: 8 pairs).
 template <typename T>
 __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const float2* __restrict__ table,
                             const long long* __restrict__ pos, int pos_batch, int B, int S, int H, int D,
-                            int layout, int inverse, long long total_pairs) {
+                            int layout, int inverse, long long total_items) {
   const int half = D / 2;
-  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_pairs;
+  const int per_row = layout == 0 ? D / 8 : half / 8;  // work items per (b,s,h) row
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_items;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int i = static_cast<int>(idx % half);
-    const long long bsh = idx / half;
+    const int c = static_cast<int>(idx % per_row);
+    const long long bsh = idx / per_row;
     const long long bs = bsh / H;
     const int s = static_cast<int>(bs % S);
     const int b = static_cast<int>(bs / S);
-    const long long p = pos ? pos[(pos_batch == 1 ? 0 : static_cast<long long>(b) * S) + s] : s;
-    float2 cs = table[p * half + i];
-    if (inverse) cs.y = -cs.y;
+    const long long ps = pos ? pos[(pos_batch == 1 ? 0 : static_cast<long long>(b) * S) + s] : s;
     const T* xr = x + bsh * D;
     T* yr = y + bsh * D;
-    float a, c;
-    int ia, ic;
-    if (layout == 0) { ia = 2 * i; ic = 2 * i + 1; } else { ia = i; ic = i + half; }
-    if constexpr (sizeof(T) == 2) { a = __bfloat162float(xr[ia]); c = __bfloat162float(xr[ic]); }
-    else { a = xr[ia]; c = xr[ic]; }
-    const float oa = a * cs.x - c * cs.y, oc = a * cs.y + c * cs.x;
-    if constexpr (sizeof(T) == 2) { yr[ia] = __float2bfloat16(oa); yr[ic] = __float2bfloat16(oc); }
-    else { yr[ia] = oa; yr[ic] = oc; }
+    const float sgn = inverse ? -1.f : 1.f;
+    if (layout == 0) {
+      Vec8<T> v; v.load(xr + c * 8);
+      float f[8], o[8]; v.to_float(f);
+      const float2* t = table + ps * half + c * 4;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 cs = t[i];
+        const float sn = cs.y * sgn;
+        o[2 * i] = f[2 * i] * cs.x - f[2 * i + 1] * sn;
+        o[2 * i + 1] = f[2 * i] * sn + f[2 * i + 1] * cs.x;
+      }
+      v.from_float(o); v.store(yr + c * 8);
+    } else {
+      Vec8<T> va, vb; va.load(xr + c * 8); vb.load(xr + half + c * 8);
+      float fa[8], fb[8], oa[8], ob[8]; va.to_float(fa); vb.to_float(fb);
+      const float2* t = table + ps * half + c * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 cs = t[i];
+        const float sn = cs.y * sgn;
+        oa[i] = fa[i] * cs.x - fb[i] * sn;
+        ob[i] = fa[i] * sn + fb[i] * cs.x;
+      }
+      va.from_float(oa); vb.from_float(ob);
+      va.store(yr + c * 8); vb.store(yr + half + c * 8);
+    }
   }
 }
 
@@ -435,7 +455,8 @@ int tt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
 
 int tt_rope(const void* x, void* y, const float* table, const long long* pos, int pos_batch, int B, int S, int H, int D,
             int layout, int inverse, int dtype, cudaStream_t st) {
-  const long long pairs = static_cast<long long>(B) * S * H * (D / 2);
+  if (D % 16) return -1;
+  const long long pairs = static_cast<long long>(B) * S * H * (layout == 0 ? D / 8 : D / 16);
   const int grid = grid_for(pairs, 256);
   if (dtype == 0) rope_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (const float2*)table, pos, pos_batch, B, S, H, D, layout, inverse, pairs);
   else rope_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (float*)y, (const float2*)table, pos, pos_batch, B, S, H, D, layout, inverse, pairs);

@@ -41,8 +41,16 @@ def _resolve(names):
     return out
 
 
+def _ensure_custom_ops_registered() -> None:
+    """The ``tt_b200::*`` ops are defined when ``ops.cuda_ops`` is imported; do that before their
+    names are looked up so the policy can recognise them."""
+    if torch.cuda.is_available():
+        from torchtitan_b200.ops import cuda_ops  # noqa: F401
+
+
 def default_op_sac_save_list() -> set:
     """Compute-heavy ops whose outputs are kept for backward."""
+    _ensure_custom_ops_registered()
     aten = torch.ops.aten
     ops = {
         aten.mm.default, aten.linear.default, aten.addmm.default, aten.bmm.default,
@@ -62,6 +70,7 @@ def default_op_sac_save_list() -> set:
 
 
 def _mm_ops() -> set:
+    _ensure_custom_ops_registered()
     aten = torch.ops.aten
     return {aten.mm.default, aten.linear.default} | _resolve([("tt_b200", "gemm")])
 
