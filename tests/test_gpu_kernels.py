@@ -43,6 +43,27 @@ def test_gemm(ops, M, N, K, a_mn, b_mn):
     assert _rel(got, want) < 1e-2, _rel(got, want)
 
 
+@pytest.mark.parametrize("pair", [0, 1])
+def test_gemm_both_tile_kernels(ops, pair):
+    from torchtitan_b200.ops import native
+
+    native.lib().tt_gemm_set_pair(pair)
+    try:
+        torch.manual_seed(2)
+        for (M, N, K) in [(512, 768, 320), (1000, 520, 264)]:
+            a = torch.randn(M, K, device="cuda").bfloat16()
+            b = torch.randn(N, K, device="cuda").bfloat16()
+            want = a.float() @ b.float().t()
+            for a_mn, b_mn in [(False, False), (False, True), (True, True)]:
+                A = a.t().contiguous() if a_mn else a
+                Bm = b.t().contiguous() if b_mn else b
+                got = ops.gemm(A, Bm, a_mn, b_mn, True)
+                _no_kernel_errors()
+                assert _rel(got, want) < 2e-3, (M, N, K, a_mn, b_mn, _rel(got, want))
+    finally:
+        native.lib().tt_gemm_set_pair(1)
+
+
 def test_gemm_accumulate_and_strided(ops):
     torch.manual_seed(1)
     a = torch.randn(256, 512, device="cuda").bfloat16()

@@ -58,6 +58,63 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gm;
 }
 
+// Write 32 consecutive accumulator columns of one output row (bf16 or fp32, optional C += ...).
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
+  const bool full_chunk = (col + 32 <= p.N);
+        if (p.c_fp32) {
+          float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          if (full_chunk && (p.ldc % 4 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              float4* q = reinterpret_cast<float4*>(dst) + j;
+              if (p.accumulate) {
+                float4 o = *q;
+                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              }
+              *q = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < p.N; ++j)
+              dst[j] = __uint_as_float(r[j]) + (p.accumulate ? dst[j] : 0.f);
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          if (full_chunk && (p.ldc % 8 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4* q = reinterpret_cast<uint4*>(dst) + j;
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+              if (p.accumulate) {
+                uint4 o = *q;
+                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float2 of = __bfloat1622float2(ob[e]);
+                  f[2 * e] += of.x;
+                  f[2 * e + 1] += of.y;
+                }
+              }
+              uint4 v;
+              v.x = tt::pack_bf16(f[0], f[1]);
+              v.y = tt::pack_bf16(f[2], f[3]);
+              v.z = tt::pack_bf16(f[4], f[5]);
+              v.w = tt::pack_bf16(f[6], f[7]);
+              *q = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < p.N; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (p.accumulate) v += __bfloat162float(dst[j]);
+              dst[j] = __float2bfloat16(v);
+            }
+          }
+        }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -203,59 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tt::tc_wait_ld();
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
-        const bool full_chunk = (col + 32 <= p.N);
-        if (p.c_fp32) {
-          float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
-          if (full_chunk && (p.ldc % 4 == 0)) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-              float4* q = reinterpret_cast<float4*>(dst) + j;
-              if (p.accumulate) {
-                float4 o = *q;
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              *q = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < p.N; ++j)
-              dst[j] = __uint_as_float(r[j]) + (p.accumulate ? dst[j] : 0.f);
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
-          if (full_chunk && (p.ldc % 8 == 0)) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4* q = reinterpret_cast<uint4*>(dst) + j;
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
-              if (p.accumulate) {
-                uint4 o = *q;
-                const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 of = __bfloat1622float2(ob[e]);
-                  f[2 * e] += of.x;
-                  f[2 * e + 1] += of.y;
-                }
-              }
-              uint4 v;
-              v.x = tt::pack_bf16(f[0], f[1]);
-              v.y = tt::pack_bf16(f[2], f[3]);
-              v.z = tt::pack_bf16(f[4], f[5]);
-              v.w = tt::pack_bf16(f[6], f[7]);
-              *q = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < p.N; ++j) {
-              float v = __uint_as_float(r[j]);
-              if (p.accumulate) v += __bfloat162float(dst[j]);
-              dst[j] = __float2bfloat16(v);
-            }
-          }
-        }
+        store_chunk(p, row, col, r);
       }
       tt::tc_fence_before();
       __syncwarp();
@@ -272,7 +277,154 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs on neighbouring SMs share one 256x256 output tile. Each CTA stages its
+// own 128 rows of A and *half* of the B tile; one UMMA (M = 256) issued by the leader reads both
+// halves, so every CTA moves 32 KB instead of 48 KB per k-step from L2 and the ring gets 6 stages.
+// Accumulators: each CTA's TMEM holds its 128 rows x 256 columns (two buffers).
+namespace pair {
+constexpr int TM = 256, TN = 256;
+constexpr int PSTAGES = 6;
+constexpr uint32_t PA_BYTES = 128 * BK * 2, PB_BYTES = 128 * BK * 2;  // per CTA per stage
+constexpr size_t PSMEM_BYTES = 1024 + PSTAGES * (PA_BYTES + PB_BYTES) + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t sA = base, sB = base + PSTAGES * PA_BYTES;
+  const uint32_t bars = base + PSTAGES * (PA_BYTES + PB_BYTES);
+  uint8_t* bars_gen = gen_base + PSTAGES * (PA_BYTES + PB_BYTES);
+  auto full_bar = [&](int s) { return bars + 8u * s; };                       // used in the leader only
+  auto empty_bar = [&](int s) { return bars + 8u * (PSTAGES + s); };          // one per CTA
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * PSTAGES + a); };      // one per CTA
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * PSTAGES + 2 + a); }; // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_gen + 8 * (2 * PSTAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * (2 * PSTAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tt::cluster_ctarank();  // 0 = leader
+  const int num_tiles = p.tiles_m * p.tiles_n;  // in 256x256 tiles
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) { tt::mbar_init(full_bar(s), 1); tt::mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { tt::mbar_init(tfull_bar(a), 1); tt::mbar_init(tempty_bar(a), 8); }
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+    tt::tma_prefetch_desc(&tma_a);
+    tt::tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 2) { tt::tmem_alloc_pair(tt::smem_u32(tmem_slot), TMEM_COLS); tt::tmem_relinquish_pair(); }
+  tt::tc_fence_before();
+  tt::cluster_sync();  // barriers of both CTAs are initialised before anyone signals across
+  tt::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (tt::elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * TM + rank * 128, n0 = tn * TN + rank * 128;
+        for (int k = 0; k < p.k_iters; ++k, ++it) {
+          const int s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1;
+          if (!tt::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, &g_gemm_error, 11)) { ok = false; break; }
+          const uint32_t fb = tt::mapa(full_bar(s), 0);  // the leader's barrier collects both CTAs' bytes
+          if (rank == 0) tt::mbar_expect_tx(full_bar(s), 2 * (PA_BYTES + PB_BYTES));
+          const uint32_t dA = sA + s * PA_BYTES, dB = sB + s * PB_BYTES;
+          if (!p.a_mn) {
+            tt::tma_load_2d_pair(dA, &tma_a, fb, k * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tt::tma_load_2d_pair(dA + j * (64 * BK * 2), &tma_a, fb, m0 + j * 64, k * BK);
+          }
+          if (!p.b_mn) {
+            tt::tma_load_2d_pair(dB, &tma_b, fb, k * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tt::tma_load_2d_pair(dB + j * (64 * BK * 2), &tma_b, fb, n0 + j * 64, k * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ------------------------------------------------------------ UMMA issuer (leader CTA only)
+    if (tt::elect_one()) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      const uint32_t a_lbo = p.a_mn ? (64 * BK * 2) >> 4 : 1, b_lbo = p.b_mn ? (64 * BK * 2) >> 4 : 1;
+      const uint32_t sbo = 1024 >> 4;
+      const uint32_t a_kadv = p.a_mn ? (UMMA_K * 128) : (UMMA_K * 2);
+      const uint32_t b_kadv = p.b_mn ? (UMMA_K * 128) : (UMMA_K * 2);
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_it) {
+        const int acc = tile_it & 1;
+        const uint32_t acc_ph = (tile_it >> 1) & 1;
+        if (!tt::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, &g_gemm_error, 12)) break;
+        tt::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TN;
+        for (int k = 0; k < p.k_iters; ++k, ++it) {
+          const int s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1;
+          if (!tt::mbar_wait(full_bar(s), ph, abort_flag, &g_gemm_error, 13)) { ok = false; break; }
+          tt::tc_fence_after();
+          const uint32_t aA = sA + s * PA_BYTES, aB = sB + s * PB_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t ad = tt::umma_smem_desc(aA + kk * a_kadv, a_lbo, sbo);
+            const uint64_t bd = tt::umma_smem_desc(aB + kk * b_kadv, b_lbo, sbo);
+            tt::umma_f16_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+          }
+          tt::umma_commit_pair(empty_bar(s), 3);  // frees this stage in both CTAs
+        }
+        if (ok) tt::umma_commit_pair(tfull_bar(acc), 3);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int ew = warp - 4;
+    uint32_t tile_it = 0;
+    const uint32_t leader_tempty0 = tt::mapa(tempty_bar(0), 0), leader_tempty1 = tt::mapa(tempty_bar(1), 0);
+    for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_it) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int acc = tile_it & 1;
+      const uint32_t acc_ph = (tile_it >> 1) & 1;
+      if (!tt::mbar_wait(tfull_bar(acc), acc_ph, abort_flag, &g_gemm_error, 14)) break;
+      tt::tc_fence_after();
+      const int row = tm * TM + rank * 128 + ew * 32 + lane;
+      const int n0 = tn * TN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * TN;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        uint32_t r[32];
+        tt::tmem_ld_32x32(taddr + c * 32, r);
+        tt::tc_wait_ld();
+        const int col = n0 + c * 32;
+        if (!row_ok || col >= p.N) continue;
+        store_chunk(p, row, col, r);
+      }
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive_cluster(acc ? leader_tempty1 : leader_tempty0);
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  tt::cluster_sync();  // nobody leaves while its partner may still touch its shared memory or TMEM
+  if (warp == 2) { tt::tc_fence_after(); tt::tmem_dealloc_pair(tmem_base, TMEM_COLS); }
+}
+}  // namespace pair
+
 int g_num_sms = 0;
+bool g_pair_enabled = true;
 
 }  // namespace
 
@@ -291,30 +443,47 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
   }
+  // CTA-pair kernel for everything large enough to fill 256x256 tiles (no fused-gather flags there)
+  const bool use_pair = g_pair_enabled && ready_flags == nullptr && M >= 256 && N >= 256;
+  const int box_n = use_pair ? 128 : BN;
   CUtensorMap ta, tb;
   int rc;
   if (!a_mn) rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
   else       rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64);
   if (rc) return rc;
-  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
+  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, box_n, BK);
   else       rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
   GemmArgs p;
   p.M = M; p.N = N; p.K = K;
-  p.tiles_m = (M + BM - 1) / BM;
-  p.tiles_n = (N + BN - 1) / BN;
   p.k_iters = (K + BK - 1) / BK;
   p.a_mn = a_mn; p.b_mn = b_mn;
-  p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate;
   p.ready_flags = ready_flags; p.ready_value = ready_value;
-  int grid = p.tiles_m * p.tiles_n;
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
-  if (grid > cap) grid = cap;
-  gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  if (use_pair) {
+    p.tiles_m = (M + pair::TM - 1) / pair::TM;
+    p.tiles_n = (N + pair::TN - 1) / pair::TN;
+    p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, a_mn, b_mn);
+    int clusters = p.tiles_m * p.tiles_n;
+    if (clusters > cap / 2) clusters = cap / 2;
+    if (clusters < 1) clusters = 1;
+    pair::gemm_bf16_pair_kernel<<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+  } else {
+    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_n = (N + BN - 1) / BN;
+    p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
+    int grid = p.tiles_m * p.tiles_n;
+    if (grid > cap) grid = cap;
+    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// Select between the single-CTA (0) and CTA-pair (1, default) tile kernels; for tests and benchmarks.
+int tt_gemm_set_pair(int enabled) { g_pair_enabled = enabled != 0; return 0; }
 
 // Error word written by kernels whose bounded waits expired (0 = none). Reading clears it.
 int tt_gemm_error() {

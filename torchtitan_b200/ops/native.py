@@ -42,6 +42,7 @@ def lib():
     P, I, LL, F = c_void_p, c_int, c_longlong, c_float
     _sig(L.tt_gemm_bf16, [P, P, P, I, I, I, I, LL, I, LL, LL, I, I, P, I, I, P])
     _sig(L.tt_gemm_error, [])
+    _sig(L.tt_gemm_set_pair, [I])
     _sig(L.tt_rmsnorm_fwd, [P, P, P, P, LL, I, F, I, P])
     _sig(L.tt_rmsnorm_bwd_blocks, [LL, I])
     _sig(L.tt_rmsnorm_bwd, [P, P, P, P, P, P, P, LL, I, I, P])

@@ -130,8 +130,13 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--single-cta", action="store_true", help="gemm: force the single-CTA tile kernel")
     args = ap.parse_args()
     timer = Timer()
+    if args.single_cta:
+        from torchtitan_b200.ops import native as _n
+
+        _n.lib().tt_gemm_set_pair(0)
     if args.what == "gemm":
         res = [bench_gemm(args, timer)]
     elif args.what == "attention":
