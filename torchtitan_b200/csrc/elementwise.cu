@@ -529,3 +529,47 @@ extern "C" int tt_sumsq(const void* x, float* scratch, float* out, long long n, 
   finish_sumsq_kernel<<<1, 256, 0, st>>>(scratch, out, grid, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ============================================================================ allocation-free entry
+// See tt_noalloc.h. The RMSNorm backward needs [blocks, D] fp32 partial sums for dW. Callers that
+// may not allocate device memory get them from this file-scope array instead of a caller buffer.
+namespace {
+constexpr int kNoAllocMaxD = 4096;
+constexpr int kNoAllocMaxBlocks = 2 * kSMs;  // upper bound of tt_rmsnorm_bwd_blocks()
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxBlocks * kNoAllocMaxD];  // 4.6 MiB per GPU
+constexpr int kNoAllocMaxDevices = 64;
+float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};  // device address of the array, per device
+}  // namespace
+
+extern "C" {
+
+int tt_rmsnorm_bwd_noalloc_max_dim() { return kNoAllocMaxD; }
+
+const char* tt_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -20: return "tt_rmsnorm_bwd_noalloc: D exceeds the built-in scratch (max 4096) or is not a multiple of 8";
+    case -21: return "tt_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed for the built-in scratch array";
+    case -22: return "tt_rmsnorm_bwd_noalloc: device ordinal out of range";
+    default: return "tt_rmsnorm_bwd_noalloc: kernel launch failed";
+  }
+}
+
+int tt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
+                           long long rows, int D, int dtype, cudaStream_t st) {
+  if (D > kNoAllocMaxD || D <= 0 || (D % 8)) return -20;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return -22;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the kernels need its device address, which
+    // differs per device, so it is looked up once per device with that device current.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return -21;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  // Every launched block overwrites its whole [D] row of partials and the column sum reads exactly
+  // those rows, so nothing has to be cleared between calls.
+  return tt_rmsnorm_bwd(dy, x, w, rstd, dx, dw, g_noalloc_ptr[dev], rows, D, dtype, st);
+}
+
+}  // extern "C"
