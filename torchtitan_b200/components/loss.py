@@ -16,6 +16,11 @@ LossFunction = Callable[..., torch.Tensor]
 
 
 def cross_entropy_loss(pred: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    group = getattr(pred, "_tp_vocab_sharded", None)
+    if group is not None:  # logits are sharded over the vocabulary (tensor parallel + loss parallel)
+        from torchtitan_b200.parallel.tp import vocab_parallel_cross_entropy_sum
+
+        return vocab_parallel_cross_entropy_sum(pred, labels, group, IGNORE_INDEX)
     return ops.cross_entropy_sum(pred, labels, IGNORE_INDEX)
 
 

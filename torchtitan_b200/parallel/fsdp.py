@@ -76,6 +76,7 @@ class _P:
     full_off: int  # element offset of the whole parameter in the unsharded buffer
     full_numel: int
     unsharded: torch.Tensor | None = None
+    tp_spec: tuple | None = None  # ("shard"|"replicate", dim, group) when tensor parallel tagged the parameter
 
 
 def _round_up(x: int, m: int) -> int:
@@ -274,8 +275,10 @@ class FSDPUnit:
                         pass
             for m, attr in sites:
                 m._parameters[attr] = new_param
+            tp_pl = getattr(param, "_tp_placement", None)
+            tp_spec = (tp_pl[0], tp_pl[1], getattr(param, "_tp_group", None)) if tp_pl is not None else None
             self.params.append(_P(sites, fqn, new_param, shape, dim, rows, chunk, inner, local_rows,
-                                  s_off, sn, f_off, fn))
+                                  s_off, sn, f_off, fn, tp_spec=tp_spec))
             s_off += sn
             f_off += fn
         self.shard_numel, self.unsharded_numel = s_off, f_off
@@ -582,6 +585,12 @@ class FSDPUnit:
         return grad
 
     def _post_backward(self, grads):
+        # parameters replicated over tensor parallel saw only a sequence shard: sum their gradients
+        for i, p in enumerate(self.params):
+            if p.tp_spec is not None and p.tp_spec[0] == "replicate" and grads[i] is not None:
+                g = grads[i] if grads[i].is_contiguous() else grads[i].contiguous()
+                dist.all_reduce(g, group=p.tp_spec[2])
+                grads[i] = g
         first = next((p for p in self.params if p.param.requires_grad), None)
         accumulate = first is not None and first.param.grad is not None
         with torch.no_grad():

@@ -147,7 +147,10 @@ class Trainer(Stateful, Configurable):
             self.dp_degree, self.dp_rank = 1, 0
 
         self.gc_handler = utils.GarbageCollection(gc_freq=config.training.gc_freq, debug=config.training.gc_debug)
-        dist_utils.set_determinism(pd, self.device, config.debug, distinct_seed_mesh_dims=["pp"])
+        # locally sharded (TP / EP) parameters are plain tensors: ranks along those dimensions need their
+        # own random streams; replicated parameters are broadcast afterwards (tp.finalize_tp)
+        seed_dims = ["pp"] + (["tp"] if pd.tp_enabled else []) + (["ep"] if pd.ep_enabled else [])
+        dist_utils.set_determinism(pd, self.device, config.debug, distinct_seed_mesh_dims=seed_dims)
         config.maybe_log()
 
         # ---- data ---------------------------------------------------------------------
@@ -279,6 +282,10 @@ class Trainer(Stateful, Configurable):
             model.init_weights(buffer_device=self.device if self.config.training.enable_cpu_offload else None)
         model.train()
         fsdp.materialize(model)
+        if self.parallel_dims.tp_enabled or self.parallel_dims.ep_enabled:
+            from torchtitan_b200.parallel.tp import finalize_tp
+
+            finalize_tp(model)
 
     def init_distributed(self) -> ParallelDims:
         c = self.config
