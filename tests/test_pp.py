@@ -1,0 +1,99 @@
+"""Pipeline parallel: stage layout, schedule validity (no deadlock, every action once) and
+numerical equality with the single-process model on 2 CPU ranks."""
+
+import dataclasses
+
+import pytest
+import torch
+
+from dist_utils import run_ranks
+from torchtitan_b200.parallel.pp import (
+    build_actions, generate_llm_fqn_per_model_part, stage_indices_for_rank, validate_actions,
+)
+
+
+def test_fqn_layout_balanced():
+    parts = generate_llm_fqn_per_model_part(4, 6, 1, 1)
+    assert parts[0][0] == "tok_embeddings" and parts[-1][-2:] == ["norm", "output"]
+    layers = [f for p in parts for f in p if f.startswith("layers.")]
+    assert layers == [f"layers.{i}" for i in range(6)]
+    assert generate_llm_fqn_per_model_part(1, 2)[0] == ["tok_embeddings", "layers.0", "layers.1", "norm", "output"]
+    with pytest.raises(ValueError):
+        generate_llm_fqn_per_model_part(20, 2)
+
+
+@pytest.mark.parametrize("schedule,pp,spr,style", [
+    ("GPipe", 4, 1, "loop"), ("1F1B", 4, 1, "loop"), ("1F1B", 2, 1, "loop"), ("Interleaved1F1B", 2, 2, "loop"),
+    ("Interleaved1F1B", 4, 2, "loop"), ("LoopedBFS", 2, 3, "loop"), ("ZBVZeroBubble", 2, 2, "v"), ("DualPipeV", 4, 2, "v"),
+])
+@pytest.mark.parametrize("n_mb", [4, 8, 5])
+def test_schedules_are_complete_and_deadlock_free(schedule, pp, spr, style, n_mb):
+    num_stages = pp * spr
+    ranks = build_actions(schedule, pp, num_stages, n_mb, style)
+    validate_actions(ranks, pp, num_stages, n_mb, style)
+    for r, acts in enumerate(ranks):
+        stages = stage_indices_for_rank(r, pp, num_stages, style)
+        assert sorted((a.stage, a.kind, a.mb) for a in acts) == sorted(
+            (s, k, m) for s in stages for k in "FB" for m in range(n_mb))
+
+
+def _worker(rank, world, schedule):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.config import ActivationCheckpointConfig, CompileConfig, ParallelismConfig, TrainingConfig
+    from torchtitan_b200.models.llama3 import llama3_configs
+    from torchtitan_b200.models.llama3.parallelize import parallelize_llama
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.parallel.pp import pipeline_llm
+    from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=1, pp=world, ep=1, etp=1, world_size=world)
+    cfg = dataclasses.replace(llama3_configs["debugmodel_gqa"], n_layers=4)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=32)
+    torch.manual_seed(3)
+    ref = cfg.build()
+    ref.init_weights()
+    B = 4
+    x = torch.randint(0, cfg.vocab_size, (B, 33))
+    inp, lab = x[:, :-1], x[:, 1:]
+    training = TrainingConfig(local_batch_size=B, seq_len=32)
+    par = ParallelismConfig(pipeline_parallel_degree=world, pipeline_parallel_schedule=schedule, pipeline_parallel_microbatch_size=1)
+    sched, parts, first, last = pipeline_llm(
+        ref, parallel_dims=pd, training=training, model_converters=ModelConvertersContainer.Config(), parallelism=par,
+        compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="/tmp",
+        device=torch.device("cpu"), model_config=cfg, parallelize_fn=parallelize_llama, loss_fn=cross_entropy_loss,
+    )
+    losses = [] if last else None
+    scale = torch.tensor(1.0 / lab.numel())
+    if first:
+        sched.step(inp, target=lab if last else None, losses=losses, loss_scale=scale)
+    else:
+        sched.step(target=lab if last else None, losses=losses, loss_scale=scale)
+    ref_loss = cross_entropy_loss(ref(inp), lab) / lab.numel()
+    ref_loss.backward()
+    out = {"ref": ref_loss.item(), "loss": float(torch.stack(losses).sum()) if last else None, "grad_err": 0.0}
+    ref_grads = dict(ref.named_parameters())
+    for part in parts:
+        for name, p in part.named_parameters():
+            out["grad_err"] = max(out["grad_err"], (p.grad - ref_grads[name].grad).abs().max().item())
+    # forward-only evaluation through the same stages
+    ev = [] if last else None
+    if first:
+        sched.eval(inp, target=lab if last else None, losses=ev)
+    else:
+        sched.eval(target=lab if last else None, losses=ev)
+    out["eval"] = float(torch.stack(ev).sum()) / lab.numel() if last else None
+    return out
+
+
+@pytest.mark.parametrize("schedule", ["1F1B", "Interleaved1F1B", "ZBVZeroBubble"])
+def test_pp2_matches_single_process(tmp_path, schedule):
+    res = run_ranks(_worker, 2, schedule, tmp_path=tmp_path)
+    got = [o for o in res if o["loss"] is not None]
+    assert got, res
+    for o in got:
+        assert abs(o["loss"] - o["ref"]) < 1e-5, o
+        assert abs(o["eval"] - o["ref"]) < 1e-5, o
+    assert max(o["grad_err"] for o in res) < 1e-5, res

@@ -1,3 +1,434 @@
-"""placeholder"""
-def pipeline_llm(*a, **k):
-    raise NotImplementedError
+"""Pipeline parallelism: FQN-based stage split, schedules and the P2P runtime.
+
+What it reproduces from torchtitan/distributed/pipeline_parallel.py:48-513: the model is split by
+fully-qualified module names (``module_fqns_per_model_part`` or an automatic layout in which the
+embedding and the output layer count as ``first/last_stage_less_layers`` layers), every stage is a
+deep copy of the meta model with the other modules removed (``layers`` keeps its string keys,
+missing top-level modules become ``None`` and are skipped by ``Decoder.forward``), stages are placed
+on ranks in loop order (``stage = rank + i * pp``) or V order for ``ZBVZeroBubble`` / ``DualPipeV``,
+each stage is parallelised with the model's own ``parallelize_fn``, and
+``n_microbatches = local_batch_size / pipeline_parallel_microbatch_size``.
+
+The runtime is this framework's own (the reference uses ``torch.distributed.pipelining``): a
+schedule is a per-rank list of actions ``(stage, F|B, microbatch)``; activations and their gradients
+travel by asynchronous NCCL/gloo point-to-point messages; every stage output keeps its autograd graph
+until its backward action. Schedules: ``GPipe``, ``1F1B``, ``Interleaved1F1B`` / ``LoopedBFS`` (two or
+more stages per rank), ``ZBVZeroBubble`` and ``DualPipeV`` (V placement; input- and weight-gradient
+work is not split, so they run as a V-shaped interleaved 1F1B), and CSV files with one line of
+actions per rank (``0F0,0F1,0B0,...``).
+"""
+
+from __future__ import annotations
+
+import copy
+import csv
+import math
+import re
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from torchtitan_b200.tools.logging import logger
+
+__all__ = ["pipeline_llm", "generate_llm_fqn_per_model_part", "pipeline_module_split", "PipelineSchedule",
+           "build_actions", "SCHEDULES"]
+
+SINGLE_STAGE = {"GPipe", "1F1B"}
+MULTI_STAGE = {"Interleaved1F1B", "LoopedBFS", "InterleavedZeroBubble", "ZBVZeroBubble", "DualPipeV"}
+V_STYLE = {"ZBVZeroBubble", "DualPipeV"}
+SCHEDULES = SINGLE_STAGE | MULTI_STAGE
+
+
+# ------------------------------------------------------------------------------------ stage layout
+def generate_llm_fqn_per_model_part(num_stages: int, num_layers: int, input_weight: int = 1, output_weight: int = 1):
+    """Split ``tok_embeddings, layers.0..L-1, norm, output`` into ``num_stages`` FQN lists; the
+    embedding weighs ``input_weight`` layers and norm+output ``output_weight`` layers."""
+    if num_stages < 1:
+        raise ValueError("Number of stages must be at least 1")
+    if num_stages == 1:
+        return [["tok_embeddings"] + [f"layers.{i}" for i in range(num_layers)] + ["norm", "output"]]
+    effective = num_layers + input_weight + output_weight
+    if num_stages > effective:
+        raise ValueError(f"Number of stages ({num_stages}) cannot be greater than effective layers ({effective})")
+    base, extra = divmod(effective, num_stages)
+    if base <= input_weight and num_stages > 1 and base < input_weight:
+        raise ValueError(f"Not enough layers for the first stage: {base} per stage vs input weight {input_weight}")
+    out, cur = [], 0
+    for s in range(num_stages):
+        budget = base + (1 if s < extra else 0)
+        names = []
+        if s == 0:
+            names.append("tok_embeddings")
+            budget -= input_weight
+        if s == num_stages - 1:
+            budget -= output_weight
+        budget = max(budget, 0)
+        if s == num_stages - 1:
+            budget = num_layers - cur
+        for _ in range(budget):
+            if cur < num_layers:
+                names.append(f"layers.{cur}")
+                cur += 1
+        if s == num_stages - 1:
+            names += ["norm", "output"]
+        out.append(names)
+    return out
+
+
+def _build_stage(whole: nn.Module, fqns: list[str]) -> nn.Module:
+    model = copy.deepcopy(whole)
+    keep = set(fqns)
+    for name, child in list(model.named_children()):
+        if isinstance(child, (nn.ModuleDict, nn.ModuleList)):
+            wanted = {f.split(".", 1)[1] for f in keep if f.startswith(name + ".")}
+            if isinstance(child, nn.ModuleDict):
+                for k in list(child.keys()):
+                    if k not in wanted:
+                        del child[k]
+            else:
+                setattr(model, name, nn.ModuleList([m for i, m in enumerate(child) if str(i) in wanted]))
+        elif name not in keep:
+            setattr(model, name, None)
+    return model
+
+
+def stage_indices_for_rank(pp_rank: int, pp: int, num_stages: int, style: str) -> tuple[int, ...]:
+    per = num_stages // pp
+    if style == "loop":
+        return tuple(pp_rank + s * pp for s in range(per))
+    assert per == 2, f"v schedules assume 2 stages per rank, got {per}"
+    return (pp_rank, num_stages - 1 - pp_rank)
+
+
+def stage_to_rank(stage: int, pp: int, num_stages: int, style: str) -> int:
+    if style == "loop":
+        return stage % pp
+    return stage if stage < pp else num_stages - 1 - stage
+
+
+def pipeline_module_split(whole: nn.Module, pp_rank: int, pp: int, schedule: str, module_names_per_stage):
+    style = "v" if schedule in V_STYLE else "loop"
+    num_stages = len(module_names_per_stage)
+    idx = stage_indices_for_rank(pp_rank, pp, num_stages, style)
+    parts = [_build_stage(whole, module_names_per_stage[i]) for i in idx]
+    for i in idx:
+        logger.info(f"PP rank {pp_rank} is building stage_idx {i} with modules {module_names_per_stage[i]}")
+    return idx, parts, style
+
+
+# ------------------------------------------------------------------------------------ schedules
+@dataclass(frozen=True)
+class Action:
+    stage: int
+    kind: str  # "F" or "B"
+    mb: int
+
+
+def _parse_action(tok: str) -> Action:
+    m = re.fullmatch(r"(\d+)([FBIW]|BW)(\d+)", tok.strip())
+    if not m:
+        raise ValueError(f"cannot parse pipeline action '{tok}'")
+    kind = m.group(2)
+    if kind in ("I", "BW"):
+        kind = "B"  # input-gradient / fused backward both run the whole stage backward here
+    return Action(int(m.group(1)), kind, int(m.group(3)))
+
+
+def load_csv_actions(path: str) -> list[list[Action]]:
+    rows = []
+    with open(path, newline="") as f:
+        for row in csv.reader(f):
+            acts = [_parse_action(t) for t in row if t.strip()]
+            rows.append([a for a in acts if a.kind in ("F", "B")])  # separate weight-grad steps are no-ops
+    return rows
+
+
+def build_actions(schedule: str, pp: int, num_stages: int, n_mb: int, style: str = "loop") -> list[list[Action]]:
+    """Per-rank ordered action lists."""
+    ranks: list[list[Action]] = [[] for _ in range(pp)]
+    my_stages = [stage_indices_for_rank(r, pp, num_stages, style) for r in range(pp)]
+    if schedule == "GPipe":
+        for r in range(pp):
+            s = my_stages[r][0]
+            ranks[r] = [Action(s, "F", m) for m in range(n_mb)] + [Action(s, "B", m) for m in range(n_mb)]
+        return ranks
+    if schedule == "1F1B":
+        for r in range(pp):
+            s = my_stages[r][0]
+            warm = min(pp - r, n_mb)
+            acts = [Action(s, "F", m) for m in range(warm)]
+            f, b = warm, 0
+            while b < n_mb:
+                acts.append(Action(s, "B", b)); b += 1
+                if f < n_mb:
+                    acts.append(Action(s, "F", f)); f += 1
+            ranks[r] = acts
+        return ranks
+    # multi-stage schedules: breadth-first rounds of pp micro-batches per local stage (interleaved 1F1B order
+    # for the forward sweep, mirrored for backward); correct for loop and V placement.
+    for r in range(pp):
+        stages = my_stages[r]
+        fwd = []
+        for m0 in range(0, n_mb, pp):
+            for s in stages:
+                for m in range(m0, min(m0 + pp, n_mb)):
+                    fwd.append(Action(s, "F", m))
+        bwd = []
+        for m0 in range(0, n_mb, pp):
+            for s in reversed(stages):
+                for m in range(m0, min(m0 + pp, n_mb)):
+                    bwd.append(Action(s, "B", m))
+        if schedule == "LoopedBFS":
+            ranks[r] = fwd + bwd
+            continue
+        # 1F1B steady state: after a warm-up of forwards alternate one backward / one forward
+        n_local = len(stages)
+        warm = min(len(fwd), (n_local - 1) * pp + 2 * (pp - 1 - r) + 1) if style == "loop" else min(len(fwd), n_local * pp)
+        acts = fwd[:warm]
+        fi, bi = warm, 0
+        while bi < len(bwd):
+            acts.append(bwd[bi]); bi += 1
+            if fi < len(fwd):
+                acts.append(fwd[fi]); fi += 1
+        ranks[r] = acts
+    return ranks
+
+
+def validate_actions(ranks: list[list[Action]], pp: int, num_stages: int, n_mb: int, style: str) -> None:
+    """Simulate the schedule with blocking receives and asynchronous sends; raise on deadlock."""
+    done = set()
+    pos = [0] * len(ranks)
+    progressed = True
+    while progressed:
+        progressed = False
+        for r, acts in enumerate(ranks):
+            while pos[r] < len(acts):
+                a = acts[pos[r]]
+                if a.kind == "F":
+                    ready = a.stage == 0 or (a.stage - 1, "F", a.mb) in done
+                else:
+                    ready = (a.stage, "F", a.mb) in done and (a.stage == num_stages - 1 or (a.stage + 1, "B", a.mb) in done)
+                if not ready:
+                    break
+                done.add((a.stage, a.kind, a.mb))
+                pos[r] += 1
+                progressed = True
+    if any(pos[r] < len(ranks[r]) for r in range(len(ranks))):
+        raise RuntimeError(f"pipeline schedule deadlocks: progress {pos} of {[len(a) for a in ranks]}")
+
+
+# ------------------------------------------------------------------------------------ runtime
+_DTYPES = [torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int64]
+
+
+class PipelineSchedule:
+    """Executes one rank's action list. Messages between two ranks are FIFO and untagged (NCCL), so
+    the receiver consumes them in the *sender's* order, which it derives from the global schedule,
+    and parks early arrivals until the action that needs them runs."""
+
+    def __init__(self, *, stages: dict[int, nn.Module], all_actions: list[list[Action]], pp_group, pp_rank: int, pp: int,
+                 num_stages: int, n_microbatches: int, loss_fn, style: str, device):
+        self.stages, self.all_actions = stages, all_actions
+        self.group, self.rank, self.pp = pp_group, pp_rank, pp
+        self.num_stages, self.n_mb, self.loss_fn, self.style, self.device = num_stages, n_microbatches, loss_fn, style, device
+        self._meta: dict = {}
+        self.has_first = 0 in stages
+        self.has_last = (num_stages - 1) in stages
+
+    def _rank_of(self, stage: int) -> int:
+        return stage_to_rank(stage, self.pp, self.num_stages, self.style)
+
+    def _inbound_orders(self, actions_per_rank) -> dict[int, list]:
+        """For every peer: the (kind, dst_stage, mb) messages it sends to this rank, in its order."""
+        orders: dict[int, list] = {}
+        for r, acts in enumerate(actions_per_rank):
+            if r == self.rank:
+                continue
+            seq = []
+            for a in acts:
+                if a.kind == "F" and a.stage < self.num_stages - 1 and self._rank_of(a.stage + 1) == self.rank:
+                    seq.append(("act", a.stage + 1, a.mb))
+                if a.kind == "B" and a.stage > 0 and self._rank_of(a.stage - 1) == self.rank:
+                    seq.append(("grad", a.stage - 1, a.mb))
+            orders[r] = seq
+        return orders
+
+    # ---- point to point -------------------------------------------------------------------------
+    def _send(self, t: torch.Tensor, kind: str, dst_stage: int, pending: list):
+        dst = dist.get_global_rank(self.group, self._rank_of(dst_stage))
+        key = ("sent", kind, dst_stage)
+        if key not in self._meta:
+            meta = torch.zeros(8, dtype=torch.int64)
+            meta[0] = t.dim()
+            meta[1 : 1 + t.dim()] = torch.tensor(list(t.shape))
+            meta[7] = _DTYPES.index(t.dtype)
+            dist.send(meta.to(self.device), dst, group=self.group)
+            self._meta[key] = True
+        t = t.contiguous()
+        pending.append((dist.isend(t, dst, group=self.group), t))
+
+    def _recv(self, kind: str, dst_stage: int, mb: int, src_stage: int) -> torch.Tensor:
+        peer = self._rank_of(src_stage)
+        want = (kind, dst_stage, mb)
+        box = self._inbox.setdefault(peer, {})
+        src = dist.get_global_rank(self.group, peer)
+        while want not in box:
+            cur = self._cursor.get(peer, 0)
+            order = self._orders[peer]
+            assert cur < len(order), f"pipeline rank {self.rank}: {want} never sent by rank {peer}"
+            k, st, m = order[cur]
+            self._cursor[peer] = cur + 1
+            mkey = ("recv", k, st)
+            if mkey not in self._meta:
+                meta = torch.zeros(8, dtype=torch.int64, device=self.device)
+                dist.recv(meta, src, group=self.group)
+                meta = meta.cpu()
+                nd = int(meta[0])
+                self._meta[mkey] = (tuple(int(v) for v in meta[1 : 1 + nd]), _DTYPES[int(meta[7])])
+            shape, dtype = self._meta[mkey]
+            buf = torch.empty(shape, dtype=dtype, device=self.device)
+            dist.recv(buf, src, group=self.group)
+            box[(k, st, m)] = buf
+        return box.pop(want)
+
+    # ---- one optimizer step worth of micro-batches --------------------------------------------------
+    def _run(self, actions_per_rank, args, kwargs, target, losses, loss_scale, train: bool):
+        n = self.n_mb
+        self._orders = self._inbound_orders(actions_per_rank)
+        self._cursor, self._inbox, self._local_grads = {}, {}, {}
+        inputs_mb = None
+        bs = None
+        if self.has_first:
+            assert args, "the first pipeline stage needs the model input"
+            bs = args[0].shape[0]
+            inputs_mb = list(torch.tensor_split(args[0], n, dim=0)) if n > 1 else [args[0]]
+        elif target is not None:
+            bs = target.shape[0]
+        kw_mb = []
+        for m in range(n):
+            kw = {}
+            for k, v in kwargs.items():
+                if torch.is_tensor(v) and n > 1 and v.dim() > 0 and bs is not None and v.shape[0] == bs:
+                    kw[k] = torch.tensor_split(v, n, dim=0)[m]
+                else:
+                    kw[k] = v
+            kw_mb.append(kw)
+        target_mb = None
+        if target is not None:
+            target_mb = list(torch.tensor_split(target, n, dim=0)) if n > 1 else [target]
+        saved: dict = {}
+        pending: list = []
+        for a in actions_per_rank[self.rank]:
+            mod = self.stages[a.stage]
+            first, last = a.stage == 0, a.stage == self.num_stages - 1
+            if a.kind == "F":
+                if first:
+                    x = inputs_mb[a.mb]
+                elif (a.stage - 1) in self.stages:
+                    x = saved[(a.stage - 1, a.mb)][1].detach()
+                else:
+                    x = self._recv("act", a.stage, a.mb, a.stage - 1)
+                if not first and train:
+                    x.requires_grad_(True)
+                with torch.set_grad_enabled(train):
+                    out = mod(x, **kw_mb[a.mb])
+                    if last:
+                        loss_sum = self.loss_fn(out, target_mb[a.mb])
+                        val = loss_sum * loss_scale if loss_scale is not None else loss_sum
+                        if losses is not None:
+                            losses.append(val.detach().reshape(()))
+                        out = val
+                saved[(a.stage, a.mb)] = (x, out)
+                if not last and (a.stage + 1) not in self.stages:
+                    self._send(out.detach(), "act", a.stage + 1, pending)
+            else:
+                x, out = saved.pop((a.stage, a.mb))
+                if last:
+                    out.backward()
+                else:
+                    if (a.stage + 1) in self.stages:
+                        g = self._local_grads.pop((a.stage, a.mb))
+                    else:
+                        g = self._recv("grad", a.stage, a.mb, a.stage + 1)
+                    torch.autograd.backward(out, g)
+                if not first:
+                    gx = x.grad
+                    if (a.stage - 1) in self.stages:
+                        self._local_grads[(a.stage - 1, a.mb)] = gx
+                    else:
+                        self._send(gx, "grad", a.stage - 1, pending)
+            pending = [(w, t) for (w, t) in pending if not w.is_completed()]
+        for w, _ in pending:
+            w.wait()
+
+    def step(self, *args, target=None, losses=None, loss_scale=None, return_outputs: bool = False, **kwargs):
+        self._run(self.all_actions, args, kwargs, target, losses, loss_scale, train=True)
+
+    def eval(self, *args, target=None, losses=None, **kwargs):
+        fwd_only = [[a for a in acts if a.kind == "F"] for acts in self.all_actions]
+        with torch.no_grad():
+            self._run(fwd_only, args, kwargs, target, losses, None, train=False)
+
+
+# ------------------------------------------------------------------------------------ entry point
+def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters, parallelism, compile_config, ac_config,
+                 dump_folder: str, device, model_config, parallelize_fn, loss_fn):
+    pp_mesh = parallel_dims.get_mesh("pp")
+    pp, pp_rank = pp_mesh.size(), pp_mesh.get_local_rank()
+    schedule = parallelism.pipeline_parallel_schedule
+    csv_path = parallelism.pipeline_parallel_schedule_csv
+    if schedule not in SCHEDULES and not csv_path:
+        raise ValueError(f"Unknown pipeline schedule {schedule}; supported: {sorted(SCHEDULES)}")
+    single = schedule in SINGLE_STAGE
+    if not hasattr(model_config, "n_layers"):
+        raise ValueError("Model does not have n_layers attribute.")
+    num_layers = model_config.n_layers
+    in_w = parallelism.pipeline_parallel_first_stage_less_layers
+    out_w = parallelism.pipeline_parallel_last_stage_less_layers
+    per_stage = parallelism.pipeline_parallel_layers_per_stage
+    fqns = parallelism.module_fqns_per_model_part
+    if fqns is None:
+        if per_stage is not None:
+            num_stages = math.ceil((num_layers + in_w + out_w) / per_stage)
+            if num_stages % pp != 0:
+                raise ValueError(
+                    f"Number of virtual stages ({num_stages}) must be divisible by pipeline parallel size ({pp}). "
+                    f"Model has {num_layers} layers with pipeline_parallel_layers_per_stage={per_stage}."
+                )
+            spr = num_stages // pp
+            if single and spr != 1:
+                raise ValueError(f"Single stage schedule requires exactly 1 stage per rank, but got {spr} stages per rank.")
+            if not single and spr < 2:
+                raise ValueError(f"Multi-stage schedule requires at least 2 stages per rank, but got {spr} stages per rank.")
+        else:
+            num_stages = pp * (1 if single else 2)
+        fqns = generate_llm_fqn_per_model_part(num_stages, num_layers, in_w, out_w)
+    num_stages = len(fqns)
+    idx, parts, style = pipeline_module_split(model, pp_rank, pp, schedule, fqns)
+    for i, m in enumerate(parts):
+        parts[i] = parallelize_fn(
+            m, parallel_dims=parallel_dims, training=training, model_converters=model_converters, parallelism=parallelism,
+            compile_config=compile_config, ac_config=ac_config, dump_folder=dump_folder,
+        )
+    mbs = parallelism.pipeline_parallel_microbatch_size
+    if training.local_batch_size % mbs != 0:
+        raise ValueError(f"Batch size {training.local_batch_size} must be divisible by microbatch_size {mbs}.")
+    n_mb = training.local_batch_size // mbs
+    if n_mb < num_stages:
+        logger.warning(
+            f"Number of microbatches ({n_mb}) is less than the total number of stages ({num_stages}) which may result in a bubble in the pipeline."
+        )
+    if csv_path:
+        all_actions = load_csv_actions(csv_path)
+        assert len(all_actions) == pp, f"CSV schedule has {len(all_actions)} rows for {pp} pipeline ranks"
+    else:
+        all_actions = build_actions(schedule, pp, num_stages, n_mb, style)
+    validate_actions(all_actions, pp, num_stages, n_mb, style)
+    sched = PipelineSchedule(
+        stages=dict(zip(idx, parts)), all_actions=all_actions, pp_group=pp_mesh.get_group(), pp_rank=pp_rank, pp=pp,
+        num_stages=num_stages, n_microbatches=n_mb, loss_fn=loss_fn, style=style, device=device,
+    )
+    logger.info(f"Using pipeline schedule {schedule if not csv_path else csv_path} with {n_mb} microbatches and {num_stages} stages.")
+    return sched, parts, sched.has_first, sched.has_last
