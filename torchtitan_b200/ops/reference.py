@@ -77,7 +77,8 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
     """
     B, S, H, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
-    plain = window is None and doc_ids is None and sinks is None and not return_lse
+    # SDPA's is_causal mask is top-left aligned; with Sq != Sk we need the bottom-right alignment
+    plain = window is None and doc_ids is None and sinks is None and not return_lse and (not causal or S == Sk)
     if plain:
         out = F.scaled_dot_product_attention(
             q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
