@@ -49,6 +49,7 @@ def apply_data_parallel(model, parallel_dims, training, parallelism):
             model, parallel_dims.get_mesh(names), param_dtype=param_dtype, reduce_dtype=reduce_dtype,
             pp_enabled=parallel_dims.pp_enabled, cpu_offload=training.enable_cpu_offload,
             reshard_after_forward_policy=parallelism.fsdp_reshard_after_forward, parallelism=parallelism,
+            efsdp_mesh=parallel_dims.get_optional_mesh("efsdp") if parallel_dims.ep_enabled else None,
         )
         logger.info("Applied HSDP to the model" if parallel_dims.dp_replicate_enabled else "Applied FSDP to the model")
     elif parallel_dims.dp_replicate_enabled:

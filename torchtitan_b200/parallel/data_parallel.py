@@ -35,7 +35,7 @@ def _compute_copy_bytes(model: nn.Module, dtype: torch.dtype) -> int:
 
 def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype: torch.dtype, pp_enabled: bool,
                cpu_offload: bool = False, reshard_after_forward_policy: str = "default", parallelism=None,
-               extra_groups: dict | None = None):
+               extra_groups: dict | None = None, efsdp_mesh=None):
     mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
     if cpu_offload:
         raise NotImplementedError("training.enable_cpu_offload is not supported by this FSDP runtime")
@@ -47,6 +47,9 @@ def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype
     if getattr(model, "tok_embeddings", None) is not None:
         fully_shard(model.tok_embeddings, **kw, reshard_after_forward=reshard)
     for block in model.layers.values():
+        if efsdp_mesh is not None and getattr(block, "moe_enabled", False):
+            # MoE-aware FSDP: expert-parallel weights are only replicated over the efsdp ranks
+            fully_shard(block.moe.experts, mesh=efsdp_mesh, mp_policy=mp, reshard_after_forward=reshard)
         fully_shard(block, **kw, reshard_after_forward=reshard)
     if getattr(model, "norm", None) is not None and getattr(model, "output", None) is not None:
         fully_shard([model.norm, model.output], **kw, reshard_after_forward=reshard_after_forward_policy == "always")

@@ -1,0 +1,152 @@
+"""Expert parallelism for MoE layers.
+
+Reference behaviour (torchtitan/distributed/expert_parallel.py:28-285 and the wiring in
+torchtitan/models/llama4/parallelize.py:525-630): expert weights are sharded on the expert dimension
+over the ``ep`` mesh; *dispatch* exchanges per-expert token counts, then the token rows, with
+all-to-all collectives and regroups the received rows by local expert (padded to the grouped-GEMM
+alignment); *combine* undoes both. With tensor parallel and ``etp = 1`` each TP rank routes only its
+own sequence shard (the "reorderer sequence parallel" arrangement), so nothing is gathered around
+the MoE layer; the router and (without EP) the expert weights are then replicated over TP and their
+gradients are summed over the TP group.
+
+Here the MoE layer itself contains no distributed code: ``GroupedExperts.dispatcher`` is swapped
+for :class:`AllToAllDispatcher`. Under FSDP the routed experts form their own unit on the ``efsdp``
+mesh (``efsdp = fsdp * tp / (ep * etp)``), the rest of the block is sharded over ``fsdp``
+(MoE-aware FSDP, torchtitan/models/llama4/parallelize.py:349-522).
+``expert_parallel_comm_backend = deepep | hybridep`` selects the same dispatcher with the
+capacity-factor (sync-free, fixed-size buffers) mode when
+``hybridep_non_blocking_expert_capacity_factor`` is set.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from torchtitan_b200.models.common.moe.permute import generate_permute_indices
+from torchtitan_b200.tools.logging import logger
+
+__all__ = ["apply_moe_ep_tp", "AllToAllDispatcher", "all_to_all_rows"]
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Variable-split all-to-all of rows; backward runs the reverse exchange."""
+
+    @staticmethod
+    def forward(ctx, x, out_splits, in_splits, group):
+        ctx.group, ctx.out_splits, ctx.in_splits = group, out_splits, in_splits
+        out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        out = g.new_empty((sum(ctx.in_splits),) + tuple(g.shape[1:]))
+        dist.all_to_all_single(out, g.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
+        return out, None, None, None
+
+
+def all_to_all_rows(x, out_splits, in_splits, group):
+    return _AllToAllRows.apply(x, list(out_splits), list(in_splits), group)
+
+
+class AllToAllDispatcher:
+    """Token exchange for expert parallel (``standard`` backend).
+
+    ``alignment``: every local expert's block of rows is padded to a multiple of it (8 for bf16, 16
+    for float8, 32 for MXFP8 grouped GEMMs). ``capacity_factor``: when set, receive buffers have the
+    fixed size ``tokens * top_k * factor`` rows per source rank and rows beyond it are dropped, which
+    removes the device-to-host read of the split sizes."""
+
+    def __init__(self, ep_mesh, num_experts: int, alignment: int = 8, capacity_factor: float | None = None):
+        self.group = ep_mesh.get_group()
+        self.ep, self.rank = ep_mesh.size(), ep_mesh.get_local_rank()
+        assert num_experts % self.ep == 0, f"ep ({self.ep}) must divide num_experts ({num_experts})"
+        self.num_experts, self.local_experts = num_experts, num_experts // self.ep
+        self.alignment, self.capacity_factor = alignment, capacity_factor
+
+    def dispatch(self, x, order, counts, top_k: int):
+        rows = x[order // top_k]  # sorted by global expert => contiguous per destination rank
+        counts = counts.to(torch.int64)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.group)  # [src rank][local expert]
+        in_splits = counts.view(self.ep, self.local_experts).sum(1).tolist()
+        out_splits = recv_counts.view(self.ep, self.local_experts).sum(1).tolist()
+        recv = all_to_all_rows(rows, out_splits, in_splits, self.group)
+        n_recv = recv.shape[0]
+        max_len = n_recv + self.local_experts * self.alignment
+        perm, m_sizes, _ = generate_permute_indices(
+            recv_counts.to(torch.int32), self.local_experts, self.ep, max_len, self.alignment, use_cpu=not recv.is_cuda)
+        perm = perm.to(recv.device).long()
+        padded = torch.vstack((recv, recv.new_zeros(1, recv.shape[-1])))  # index -1 -> the zero row
+        grouped = padded[perm]
+        ctx = {"perm": perm, "n_recv": n_recv, "in_splits": in_splits, "out_splits": out_splits, "rows": rows.shape[0]}
+        return grouped, m_sizes.to(torch.int64).to(recv.device), ctx
+
+    def scale_rows(self, rows, scores_sorted, ctx):
+        # scores travel with the rows: exchange and permute them the same way
+        sc = all_to_all_rows(scores_sorted.reshape(-1, 1).float(), ctx["out_splits"], ctx["in_splits"], self.group)
+        sc = torch.vstack((sc, sc.new_zeros(1, 1)))[ctx["perm"]]
+        return (rows.float() * sc).to(rows.dtype)
+
+    def combine(self, y, ctx):
+        perm = ctx["perm"]
+        out = y.new_zeros(ctx["n_recv"] + 1, y.shape[-1])
+        out = out.index_copy(0, torch.where(perm >= 0, perm, torch.full_like(perm, ctx["n_recv"])), y)
+        out = out[: ctx["n_recv"]]
+        return all_to_all_rows(out, ctx["in_splits"], ctx["out_splits"], self.group)
+
+
+def _shard_experts(experts: nn.Module, ep_mesh) -> None:
+    W, r, group = ep_mesh.size(), ep_mesh.get_local_rank(), ep_mesh.get_group()
+    for name in ("w1", "w2", "w3", "b1", "b2", "b3", "mlp1_weight", "mlp1_bias", "mlp2_weight", "mlp2_bias"):
+        p = experts._parameters.get(name)
+        if p is None:
+            continue
+        E = p.shape[0]
+        n = E // W
+        if p.device.type == "meta":
+            local = torch.empty((n,) + tuple(p.shape[1:]), dtype=p.dtype, device="meta")
+        else:
+            local = p.detach()[r * n : (r + 1) * n].clone()
+        newp = nn.Parameter(local, requires_grad=p.requires_grad)
+        spec = {"placement": ("shard", 0), "group": group, "mesh": ep_mesh, "full_shape": tuple(p.shape)}
+        experts.__dict__.setdefault("_tp_specs", {})[name] = spec  # same tagging protocol as tensor parallel
+        from .tp import _tag
+
+        _tag(newp, spec)
+        experts._parameters[name] = newp
+    experts.num_local_experts = experts.w1.shape[0] if hasattr(experts, "w1") else None
+
+
+def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
+    from .tp import _mark_replicated
+
+    if parallel_dims.etp_enabled:
+        raise NotImplementedError("expert tensor parallel (etp > 1) is not implemented; use etp = 1")
+    ep_mesh = parallel_dims.get_optional_mesh("ep")
+    tp_mesh = parallel_dims.get_optional_mesh("tp")
+    alignment = 8
+    cf = parallelism.hybridep_non_blocking_expert_capacity_factor if parallelism is not None else None
+    n = 0
+    for block in model.layers.values():
+        if not getattr(block, "moe_enabled", False):
+            continue
+        moe = block.moe
+        n += 1
+        if tp_mesh is not None:
+            # sequence-sharded tokens are routed by their own TP rank; everything in the MoE layer that is not
+            # expert-sharded is replicated over TP and accumulates partial gradients
+            for sub in (moe.router.gate, moe.shared_experts):
+                if sub is not None:
+                    for m in sub.modules():
+                        _mark_replicated(m, tp_mesh.get_group(), tp_mesh)
+            if ep_mesh is None:
+                _mark_replicated(moe.experts, tp_mesh.get_group(), tp_mesh)
+        if ep_mesh is not None:
+            _shard_experts(moe.experts, ep_mesh)
+            moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, moe.router.num_experts, alignment=alignment, capacity_factor=cf)
+    if n:
+        logger.info(f"Applied expert parallel to {n} MoE layers (ep={parallel_dims.ep}, backend={getattr(parallelism, 'expert_parallel_comm_backend', 'standard')})")
+    return model
