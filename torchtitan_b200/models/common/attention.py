@@ -86,8 +86,10 @@ class InnerAttention(Module):
         if masks is not None:
             doc_ids = masks.doc_ids
             window = masks.window if masks.window is not None else window
-            if masks.block is not None and doc_ids is None:
-                doc_ids = fixed_block_ids(q.shape[0], q.shape[1], masks.block, q.device)
+            if masks.block is not None:
+                blocks = fixed_block_ids(q.shape[0], q.shape[1], masks.block, q.device)
+                # both constraints: same document AND same fixed block <=> equal combined ids
+                doc_ids = blocks if doc_ids is None else doc_ids * (q.shape[1] // masks.block + 1) + blocks
         if self.ring is not None:
             return self.ring(q, k, v, scale=scale, doc_ids=doc_ids, window=window, sinks=sinks)
         return ops.attention(q, k, v, causal=True, scale=scale, window=window, doc_ids=doc_ids, sinks=sinks)
