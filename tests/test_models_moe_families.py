@@ -68,3 +68,47 @@ def test_llama4_hf_round_trip():
         if "expert_bias" in k:
             continue
         assert torch.equal(back[k], v), k
+
+
+def test_deepseek_v3_debugmodel_step_and_adapter():
+    from torchtitan_b200.models.deepseek_v3 import DeepSeekV3StateDictAdapter, deepseek_v3_configs
+
+    cfg = dataclasses.replace(deepseek_v3_configs["debugmodel_flex_attn"], n_layers=3)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=64)
+    model = cfg.build()
+    model.init_weights(buffer_device=torch.device("cpu"))
+    assert not model.layers["0"].moe_enabled and model.layers["1"].moe_enabled
+    loss, missing = _step(model, cfg.vocab_size)
+    assert loss == loss and not missing, missing
+    sd = dict(model.state_dict())
+    ad = DeepSeekV3StateDictAdapter(cfg, None)
+    hf = ad.to_hf(sd)
+    assert "model.layers.1.mlp.experts.7.down_proj.weight" in hf and "model.layers.1.mlp.gate.e_score_correction_bias" in hf
+    back = ad.from_hf(hf)
+    assert set(back) == set(sd)
+    for k, v in sd.items():
+        assert torch.equal(back[k], v), k
+
+
+def test_deepseek_v3_mla_low_rank_query_and_yarn_scale():
+    from torchtitan_b200.models.common import Linear, RMSNorm
+    from torchtitan_b200.models.deepseek_v3 import Attention
+
+    a = Attention.Config(n_heads=4, q_lora_rank=32, wq_a=Linear.Config(), wq_b=Linear.Config(), q_norm=RMSNorm.Config(),
+                         kv_norm=RMSNorm.Config(), kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                         rope_factor=40.0, rope_max_seq_len=8192, rope_original_seq_len=4096, mscale=0.7).build(dim=128)
+    import math
+
+    m = 0.1 * 0.7 * math.log(40.0) + 1.0
+    assert abs(a.softmax_scale - (48**-0.5) * m * m) < 1e-9
+    assert hasattr(a, "wq_a") and not hasattr(a, "wq")
+
+
+def test_block_fp8_dequantise():
+    from torchtitan_b200.models.utils import dequantize_block_fp8
+
+    w = torch.randn(200, 300)
+    s = torch.rand(2, 3) + 0.5
+    full = s.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300]
+    q = (w / full).to(torch.float8_e4m3fn)
+    assert torch.allclose(dequantize_block_fp8(q, s), q.float() * full)

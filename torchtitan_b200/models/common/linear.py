@@ -27,8 +27,13 @@ class Linear(nn.Linear, Module):
             )
         super().__init__(config.in_features, config.out_features, bias=config.bias)
         self._init_mean, self._init_std = config.init_mean, config.init_std
+        self.quant = None  # a QuantRecipe once a quantisation converter selected this layer
 
     def forward(self, x):
+        if self.quant is not None:
+            from torchtitan_b200.ops.quant import quant_linear
+
+            return quant_linear(x, self.weight, self.bias, self.quant)
         return ops.linear(x, self.weight, self.bias)
 
     def init_weights(self, **kwargs) -> None:

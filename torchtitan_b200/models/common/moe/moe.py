@@ -59,6 +59,7 @@ class GroupedExperts(Module):
         self.w3 = nn.Parameter(torch.empty(num_experts, hidden_dim, dim))
         self.use_grouped_mm = use_grouped_mm
         self.dispatcher = LocalDispatcher()
+        self.quant = None  # a QuantRecipe once a quantisation converter selected these experts
 
     def local_weights(self):
         w = []
@@ -70,6 +71,11 @@ class GroupedExperts(Module):
         """``x`` [rows, D] grouped by (local) expert, ``num_tokens_per_expert`` [E_local]."""
         w1, w2, w3 = self.local_weights()
         mo = _moe_ops()
+        if self.quant is not None:
+            from torchtitan_b200.ops.quant import quant_grouped_linear as gl
+
+            h = ops.swiglu(gl(x, w1, num_tokens_per_expert, self.quant), gl(x, w3, num_tokens_per_expert, self.quant))
+            return gl(h, w2, num_tokens_per_expert, self.quant)
         h = ops.swiglu(mo.grouped_linear(x, w1, num_tokens_per_expert), mo.grouped_linear(x, w3, num_tokens_per_expert))
         return mo.grouped_linear(h, w2, num_tokens_per_expert)
 

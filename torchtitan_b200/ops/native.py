@@ -74,6 +74,11 @@ def register_optional(name: str, argtypes) -> None:
         _sig(getattr(_LIB, name), argtypes)
 
 
+def has(name: str) -> bool:
+    """True when the built library exports ``name`` (optional kernels of newer builds)."""
+    return available() and hasattr(lib(), name)
+
+
 CALLS = 0  # number of native launch calls made by this process (bench reporting)
 
 

@@ -26,7 +26,7 @@ def _validate_quantization(converters: list) -> None:
     kinds = {}
     for c in converters:
         owner = type(c)._owner
-        kind = getattr(owner, "_quantization_type", None)
+        kind = getattr(type(c), "_quantization_type", None) or getattr(owner, "_quantization_type", None)
         if kind is not None:
             kinds.setdefault(kind, []).append(owner.__name__)
     if len(kinds) > 1:
