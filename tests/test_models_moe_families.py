@@ -112,3 +112,42 @@ def test_block_fp8_dequantise():
     full = s.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300]
     q = (w / full).to(torch.float8_e4m3fn)
     assert torch.allclose(dequantize_block_fp8(q, s), q.float() * full)
+
+
+def test_gpt_oss_debugmodel_step_sinks_window_and_adapter():
+    from torchtitan_b200.models.gpt_oss import GptOssStateDictAdapter, gptoss_configs
+
+    cfg = dataclasses.replace(gptoss_configs["debugmodel"], n_layers=2)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=64)
+    cfg.layer.attention = dataclasses.replace(cfg.layer.attention, n_heads=8, n_kv_heads=2, head_dim=32, sliding_window_size=8)
+    cfg.rope = dataclasses.replace(cfg.rope, dim=32)
+    model = cfg.build()
+    model.init_weights(buffer_device=torch.device("cpu"))
+    assert model.layers["0"].use_sliding_attention and not model.layers["1"].use_sliding_attention
+    loss, missing = _step(model, cfg.vocab_size)
+    assert loss == loss and not missing, missing
+    assert model.layers["0"].attention.sinks.grad.abs().sum() > 0
+    sd = dict(model.state_dict())
+    ad = GptOssStateDictAdapter(cfg, None)
+    hf = ad.to_hf(sd)
+    assert "model.layers.0.self_attn.sinks" in hf and "model.layers.1.mlp.experts.gate_up_proj_blocks" in hf
+    back = ad.from_hf(hf)
+    for k, v in sd.items():
+        if "expert_bias" in k:
+            continue
+        assert torch.equal(back[k], v), k
+
+
+def test_gpt_oss_swiglu_and_mxfp4():
+    from torchtitan_b200.models.gpt_oss.moe import swiglu
+    from torchtitan_b200.models.gpt_oss.state_dict_adapter import dequantize_mxfp4
+
+    x = torch.tensor([[10.0, 9.0, -1.0, -9.0]])
+    out = swiglu(x, limit=7.0)
+    exp0 = 7.0 * torch.sigmoid(torch.tensor(1.702 * 7.0)) * (7.0 + 1)
+    exp1 = -1.0 * torch.sigmoid(torch.tensor(-1.702)) * (-7.0 + 1)
+    assert torch.allclose(out, torch.stack((exp0, exp1)).view(1, 2))
+    blocks = torch.zeros(1, 1, 16, dtype=torch.uint8)
+    blocks[0, 0, 0] = 0x2 | (0xF << 4)  # values 1.0 and -6.0
+    vals = dequantize_mxfp4(blocks, torch.tensor([[128]], dtype=torch.uint8))
+    assert vals.shape == (1, 32) and vals[0, 0] == 2.0 and vals[0, 1] == -12.0 and vals[0, 2:].abs().sum() == 0

@@ -72,3 +72,56 @@ def test_tp2_fsdp2_loss_matches(tmp_path):
     res = run_ranks(_worker, 4, True, tmp_path=tmp_path)
     for o in res:
         assert abs(o["loss"] - o["ref"]) < 1e-5, o
+
+
+def _moe_family_worker(rank, world, family):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.parallel.ep import apply_moe_ep_tp
+    from torchtitan_b200.parallel.tp import apply_tp_to_decoder, finalize_tp
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, ep=1, etp=1, world_size=world)
+    if family == "deepseek_v3":
+        from torchtitan_b200.models.deepseek_v3 import deepseek_v3_configs
+
+        cfg = dataclasses.replace(deepseek_v3_configs["debugmodel"], n_layers=2)
+    else:
+        from torchtitan_b200.models.gpt_oss import gptoss_configs
+
+        cfg = dataclasses.replace(gptoss_configs["debugmodel"], n_layers=2)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=32)
+    torch.manual_seed(11)
+    ref = cfg.build()
+    ref.init_weights(buffer_device=torch.device("cpu"))
+    model = cfg.build()
+    model.load_state_dict(ref.state_dict())
+    model.freqs_cis = ref.freqs_cis.clone()
+    apply_tp_to_decoder(model, pd.get_mesh("tp"), loss_parallel=True)
+    apply_moe_ep_tp(model, pd, None)
+    finalize_tp(model)
+    x = torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(5))
+    inp, lab = x[:, :-1], x[:, 1:]
+    masks = model.get_attention_masks(inp, None) if family == "gpt_oss" else None
+    loss = cross_entropy_loss(model(inp, masks), lab) / lab.numel()
+    loss.backward()
+    ref_loss = cross_entropy_loss(ref(inp, masks), lab) / lab.numel()
+    ref_loss.backward()
+    out = {"loss": loss.item(), "ref": ref_loss.item()}
+    g, rg = model.layers["1"].moe.router.gate.weight.grad, ref.layers["1"].moe.router.gate.weight.grad
+    out["gate"] = (g - rg).abs().max().item()
+    if family == "gpt_oss":
+        out["wo_bias"] = (model.layers["0"].attention.wo.bias.grad - ref.layers["0"].attention.wo.bias.grad).abs().max().item()
+    return out
+
+
+def test_tp2_deepseek_mla_and_moe(tmp_path):
+    for o in run_ranks(_moe_family_worker, 2, "deepseek_v3", tmp_path=tmp_path):
+        assert abs(o["loss"] - o["ref"]) < 1e-5 and o["gate"] < 1e-5, o
+
+
+def test_tp2_gpt_oss_sinks_biases_and_moe(tmp_path):
+    for o in run_ranks(_moe_family_worker, 2, "gpt_oss", tmp_path=tmp_path):
+        assert abs(o["loss"] - o["ref"]) < 1e-5 and o["gate"] < 1e-5 and o["wo_bias"] < 1e-5, o

@@ -177,6 +177,18 @@ def _shard_param(mod: nn.Module, name: str, dim: int, rank: int, world: int, gro
     mod._parameters[name] = newp
 
 
+class _ScaleFwd(torch.autograd.Function):
+    """``bias / W`` in forward, identity in backward."""
+
+    @staticmethod
+    def forward(ctx, b, W):
+        return b / W
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
 def _mark_replicated(mod: nn.Module, group, mesh) -> None:
     """Replicated parameters that only see this rank's sequence shard: their gradients are partial
     sums and must be all-reduced over the TP group (a tensor hook, or the FSDP unit when it owns them)."""
@@ -276,11 +288,29 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
     # ---- blocks --------------------------------------------------------------------------------------
     for block in model.layers.values():
         att = block.attention
-        for name in ("wq", "wk", "wv"):
-            _shard_param(getattr(att, name), "weight", 0, r, W, group, tp_mesh)
-            if getattr(att, name).bias is not None:
-                _shard_param(getattr(att, name), "bias", 0, r, W, group, tp_mesh)
+        if hasattr(att, "wkv_b"):
+            # multi-head latent attention: the per-head up-projections are column-parallel, the shared low-rank
+            # down-projections and their norms stay replicated
+            col = ("wq", "wq_b", "wkv_b")
+            for nm in ("wq_a", "wkv_a", "q_norm", "kv_norm"):
+                if getattr(att, nm, None) is not None:
+                    _mark_replicated(getattr(att, nm), group, tp_mesh)
+        else:
+            col = ("wq", "wk", "wv")
+        for name in col:
+            lin = getattr(att, name, None)
+            if lin is None:
+                continue
+            _shard_param(lin, "weight", 0, r, W, group, tp_mesh)
+            if lin.bias is not None:
+                _shard_param(lin, "bias", 0, r, W, group, tp_mesh)
         _shard_param(att.wo, "weight", 1, r, W, group, tp_mesh)
+        if att.wo.bias is not None:
+            # a row-parallel bias must enter the cross-rank sum exactly once: every rank adds bias / W. Its
+            # gradient sees the full (all-gathered) output gradient on every rank, so it needs no reduction.
+            from torchtitan_b200 import ops as _ops
+
+            _wrap(att.wo, lambda inner, x, _lin=att.wo: _ops.linear(x, _lin.weight, None) + _ScaleFwd.apply(_lin.bias, W))
         if getattr(att, "sinks", None) is not None:
             _shard_param(att, "sinks", 0, r, W, group, tp_mesh)
         for nm in ("q_norm", "k_norm"):
