@@ -1,0 +1,70 @@
+"""Regenerates the small offline test assets:
+
+* ``tokenizer/``  -- a byte-level BPE tokenizer with a 2048-entry vocabulary (``tokenizer.json`` +
+  ``tokenizer_config.json``) trained on the synthetic corpus below;
+* ``c4_test/data.json`` -- 2000 JSON-lines documents with a ``text`` field (stand-in for the C4 test split).
+
+The corpus is generated from a fixed word list with a seeded RNG, so the outputs are reproducible:
+``python tests/assets/build_assets.py``.
+"""
+
+import json
+import os
+import random
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORDS = (
+    "the of and to in is that for it as was with be by on not he this are or his from at which but have an had they "
+    "you were their one all we can her has there been if more when will would who so no out up into than them only "
+    "time some could these two may then do first any my now such like our over man me even most made after also did "
+    "many before must through years where much your way well down should because each just those people how too little "
+    "state good very make world still own see men work long get here between both life being under never day same "
+    "another know while last might us great old year off come since against go came right used take three small large "
+    "number model train token layer tensor kernel memory data batch step loss grad weight shard rank device stream "
+    "compute matrix vector attention expert router gate norm scale cache block table sum digit answer question what "
+    "please solve add numbers result equals plus minus times total value answer"
+).split()
+
+
+def make_docs(n: int, seed: int) -> list[str]:
+    rng = random.Random(seed)
+    docs = []
+    for _ in range(n):
+        sents = []
+        for _ in range(rng.randint(3, 40)):
+            k = rng.randint(4, 18)
+            words = [rng.choice(WORDS) for _ in range(k)]
+            if rng.random() < 0.3:
+                words.insert(rng.randrange(k), str(rng.randint(0, 99999)))
+            s = " ".join(words)
+            sents.append(s[0].upper() + s[1:] + rng.choice(".?!"))
+        docs.append(" ".join(sents))
+    return docs
+
+
+def main() -> None:
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+
+    docs = make_docs(2000, 1234)
+    os.makedirs(os.path.join(HERE, "c4_test"), exist_ok=True)
+    with open(os.path.join(HERE, "c4_test", "data.json"), "w") as f:
+        for d in docs:
+            f.write(json.dumps({"text": d}) + "\n")
+
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    specials = ["<|begin_of_text|>", "<|end_of_text|>", "<|pad|>"]
+    trainer = trainers.BpeTrainer(vocab_size=2048, special_tokens=specials,
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    extra = ["[ANSWER] 12345", "Question: what is the sum of the digits 1 + 2 + 3 ?"] * 50
+    tok.train_from_iterator(docs + extra, trainer)
+    os.makedirs(os.path.join(HERE, "tokenizer"), exist_ok=True)
+    tok.save(os.path.join(HERE, "tokenizer", "tokenizer.json"))
+    with open(os.path.join(HERE, "tokenizer", "tokenizer_config.json"), "w") as f:
+        json.dump({"bos_token": specials[0], "eos_token": specials[1], "pad_token": specials[2],
+                   "add_bos_token": True, "add_eos_token": False, "model_max_length": 131072}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,143 @@
+"""RL experiment on CPU: task/grader, sampler and paged attention definitions, engine-vs-trainer
+log-probability agreement, one colocated GRPO run."""
+
+import dataclasses
+import os
+
+import pytest
+import torch
+
+
+def test_sum_digits_task_and_rewards():
+    from torchtitan_b200.experiments.rl.sum_digits import SumDigitsTask, extract_answer
+
+    t = SumDigitsTask(seed=1)
+    q, a = t.create_question()
+    nums = [int(x) for x in q[q.index("[") + 1 : q.index("]")].split(",")]
+    assert int(a) == sum(int(d) for n in nums for d in str(n))
+    assert SumDigitsTask(seed=1).create_question() == (q, a)
+    assert extract_answer("so 3 + 4 = 7\n[ANSWER] 7") == 7
+    assert extract_answer("The answer is 12.") == 12
+    assert extract_answer("i think 5 then 9") == 9 and extract_answer("none") is None
+    r = t.reward_function(["[ANSWER] 7", "x [ANSWER] 7 trailing", "[ANSWER] 8"], "7")
+    assert r.tolist() == pytest.approx([1.2, 1.0, -1.0])
+
+
+def test_group_mean_advantages():
+    from torchtitan_b200.experiments.rl.grader import group_mean_advantages
+    from torchtitan_b200.experiments.rl.types import Episode
+
+    eps = [Episode(0, [1], "", [2], [0.0], reward=r, group_id=g) for r, g in ((1, "a"), (-1, "a"), (1, "b"), (1, "b"))]
+    group_mean_advantages(eps)
+    assert [e.advantage for e in eps] == [1.0, -1.0, 0.0, 0.0]
+
+
+def test_sampler_definition():
+    from torchtitan_b200.ops.serving import sample_top_p
+
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(3, 1)
+    tok, lp = sample_top_p(logits, 0.0, 1.0, torch.zeros(3))
+    assert tok.tolist() == [0, 0, 0] and torch.allclose(lp, torch.log_softmax(logits, -1)[:, 0])
+    # top_p small enough keeps only the best token whatever the draw
+    tok, _ = sample_top_p(logits, 1.0, 0.5, torch.tensor([0.0, 0.5, 0.999]))
+    assert tok.tolist() == [0, 0, 0]
+    # full nucleus: the draw walks the sorted CDF
+    p = torch.softmax(logits[0], -1)
+    tok, lp = sample_top_p(logits, 1.0, 1.0, torch.tensor([0.0, float(p[0]) + 1e-3, 0.9999]))
+    assert tok.tolist() == [0, 1, 3]
+    assert torch.allclose(lp, torch.log_softmax(logits, -1)[0, tok])
+
+
+def test_paged_decode_definition_matches_dense():
+    from torchtitan_b200.ops import reference
+    from torchtitan_b200.ops.serving import kv_cache_write, paged_attention_decode
+
+    torch.manual_seed(0)
+    B, H, Hkv, D, bs = 3, 4, 2, 16, 4
+    lens = [5, 9, 12]
+    kc, vc = torch.zeros(16, bs, Hkv, D), torch.zeros(16, bs, Hkv, D)
+    tables = torch.zeros(B, 3, dtype=torch.int32)
+    perm = torch.randperm(16).tolist()
+    outs = []
+    q = torch.randn(B, H, D)
+    for b, n in enumerate(lens):
+        blks = [perm.pop() for _ in range((n + bs - 1) // bs)]
+        tables[b, : len(blks)] = torch.tensor(blks)
+        k, v = torch.randn(n, Hkv, D), torch.randn(n, Hkv, D)
+        slots = torch.tensor([blks[t // bs] * bs + t % bs for t in range(n)], dtype=torch.int32)
+        kv_cache_write(kc, vc, k, v, slots)
+        o = reference.attention(q[b].view(1, 1, H, D), k.unsqueeze(0), v.unsqueeze(0), causal=False, scale=D**-0.5)
+        outs.append(o.view(H, D))
+    got = paged_attention_decode(q, kc, vc, tables, torch.tensor(lens, dtype=torch.int32), D**-0.5)
+    assert torch.allclose(got, torch.stack(outs), atol=1e-5)
+
+
+def _debug_spec():
+    from torchtitan_b200.models.qwen3 import model_registry
+
+    spec = model_registry("debugmodel")
+    spec.model = dataclasses.replace(spec.model, n_layers=2)
+    spec.model.rope = dataclasses.replace(spec.model.rope, max_seq_len=512)
+    return spec
+
+
+def test_engine_logprobs_match_trainer_recompute():
+    from torchtitan_b200.experiments.rl.generator import Generator, SamplingConfig
+    from torchtitan_b200.experiments.rl.losses import compute_token_log_probs_packed
+
+    torch.manual_seed(0)
+    spec = _debug_spec()
+    gen = Generator(Generator.Config(num_samples_per_prompt=3, seed=7, max_kv_blocks=256, kv_block_size=4,
+                                     sampling=SamplingConfig(temperature=1.0, top_p=0.9, max_tokens=12)),
+                    model_spec=spec, device="cpu")
+    prompts = [[1, 5, 9, 12, 7], [3, 4, 100, 200, 300, 17, 21, 9, 2]]
+    eps = gen.generate_from_ids(prompts, ["1", "2"])
+    assert len(eps) == 6 and eps[0].group_id == eps[2].group_id != eps[3].group_id
+    assert all(len(e.token_ids) == len(e.token_log_probs) <= 12 for e in eps)
+    assert gen.engine.cache.alloc.available == 256           # every block returned
+    lps = compute_token_log_probs_packed(gen.model, [e.prompt_token_ids for e in eps], [e.token_ids for e in eps], "cpu")
+    for e, lp in zip(eps, lps):
+        assert torch.allclose(torch.tensor(e.token_log_probs), lp, atol=2e-5), (e.token_log_probs, lp)
+    # samples of one prompt are not all identical at temperature 1
+    assert len({tuple(e.token_ids) for e in eps[:3]}) > 1
+
+
+def test_param_arena_double_buffer():
+    from torchtitan_b200.experiments.rl.weight_sync import ParamArena, sync_local
+
+    spec = _debug_spec()
+    a, b = spec.model.build(), spec.model.build()
+    a.init_weights()
+    b.init_weights()
+    arena = ParamArena(b)
+    before = {n: p.clone() for n, p in b.named_parameters()}
+    ptr0 = b.output.weight.data_ptr()
+    sync_local(a, arena)
+    for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.equal(p, q), n
+    assert b.output.weight.data_ptr() != ptr0 and arena.active == 1
+    assert any(not torch.equal(before[n], p) for n, p in b.named_parameters())
+
+
+def test_colocated_grpo_two_steps(tmp_path):
+    from torchtitan_b200.experiments.rl.config_registry import rl_grpo_qwen3_debug
+    from torchtitan_b200.experiments.rl.simple_grpo_sum_digits import RLTrainer
+
+    cfg = rl_grpo_qwen3_debug()
+    cfg.model_spec = _debug_spec()
+    cfg.num_steps, cfg.num_episodes_per_step, cfg.eval_samples = 2, 2, 2
+    cfg.generator.num_samples_per_prompt = 2
+    cfg.generator.sampling.max_tokens = 6
+    cfg.generator.max_kv_blocks = 512
+    cfg.generator.seed = 0
+    cfg.trainer.training.dtype = "float32"
+    cfg.hf_assets_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "assets", "tokenizer")
+    rl = RLTrainer(cfg)
+    rl.setup(device="cpu")
+    w0 = rl.generator.model.output.weight.clone()
+    hist = rl.train()
+    assert len(hist) == 2 and all(h["loss"] == h["loss"] for h in hist)
+    assert hist[0]["logprob_diff_max"] < 1e-4        # generator and trainer agree before the first update
+    assert hist[-1]["policy_version"] == 2 and rl.generator.policy_version == 2
+    assert not torch.equal(w0, rl.generator.model.output.weight)   # weights reached the generator
+    assert torch.equal(rl.generator.model.output.weight, rl.trainer.model.output.weight.to(w0.dtype))

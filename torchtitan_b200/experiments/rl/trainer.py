@@ -1,0 +1,185 @@
+"""The learning role: policy + frozen reference model, one optimizer step per batch of episodes.
+
+Parity: torchtitan/experiments/rl/unified/actors/trainer.py:41-355 (configuration sections; episodes
+sharded round-robin over data-parallel ranks; reference log-probabilities without grad; GRPO/PPO loss
+with ``kl_coef=0.1``; generator-vs-trainer log-probability check; gradient averaging over DP; clipping;
+metrics dict; ``get_weights`` returns full tensors). Differences by design: all of a rank's episodes are
+packed into one document-masked row, so a step is one forward/backward; models are built through the
+``ModelSpec`` and parallelised with the framework's own FSDP / tensor parallel.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
+from torchtitan_b200.components.optimizer import OptimizersContainer
+from torchtitan_b200.config import TORCH_DTYPE_MAP, ActivationCheckpointConfig, CommConfig, CompileConfig, ParallelismConfig, TrainingConfig
+from torchtitan_b200.config.configurable import Configurable
+from torchtitan_b200.parallel import ParallelDims
+from torchtitan_b200.parallel import utils as dist_utils
+from torchtitan_b200.tools.logging import logger
+
+from .losses import compute_policy_gradient_loss, compute_token_log_probs_packed, verify_logprob_identity
+from .types import Episode
+from .weight_sync import full_tensor
+
+
+class PolicyTrainer(Configurable):
+    @dataclass(kw_only=True, slots=True)
+    class Config(Configurable.Config):
+        optimizer: OptimizersContainer.Config = field(default_factory=OptimizersContainer.Config)
+        lr_scheduler: LRSchedulersContainer.Config = field(default_factory=LRSchedulersContainer.Config)
+        training: TrainingConfig = field(default_factory=TrainingConfig)
+        parallelism: ParallelismConfig = field(default_factory=ParallelismConfig)
+        comm: CommConfig = field(default_factory=CommConfig)
+        objective: str = "grpo"
+        """``grpo`` (sequence-level ratio against the reference model, KL penalty) or ``dapo`` (token-level
+        ratio against the generator's log-probabilities, asymmetric clipping, no KL)."""
+        kl_coef: float = 0.1
+        ppo_clip_eps: float = 0.2
+        entropy_coef: float = 0.01
+
+    def __init__(self, config: Config, *, model_spec, batch_invariant_mode: bool = False, hf_assets_path: str = "",
+                 device: torch.device | str | None = None, group=None):
+        self.config, self.model_spec = config, model_spec
+        if device is None:
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        p = config.parallelism
+        self.parallel_dims = ParallelDims(
+            dp_shard=p.data_parallel_shard_degree, dp_replicate=p.data_parallel_replicate_degree, cp=p.context_parallel_degree,
+            tp=p.tensor_parallel_degree, pp=p.pipeline_parallel_degree, ep=p.expert_parallel_degree,
+            etp=p.expert_tensor_parallel_degree, world_size=world,
+        )
+        self.sd_adapter = model_spec.state_dict_adapter(model_spec.model, hf_assets_path) if model_spec.state_dict_adapter else None
+        self.model = self._build_model(hf_assets_path, trainable=True)
+        self.model_parts = [self.model]
+        self.ref_model = self._build_model(hf_assets_path, trainable=False)
+        self._copy_weights(self.model, self.ref_model)
+        self.optimizers = config.optimizer.build(model_parts=self.model_parts)
+        self.lr_schedulers = config.lr_scheduler.build(optimizers=self.optimizers, training_steps=config.training.steps)
+        self.policy_version = 0
+        pd = self.parallel_dims
+        self.dp_size = pd.dp_replicate * pd.dp_shard
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.dp_rank = rank // pd.non_data_parallel_size
+        self.dp_enabled = pd.dp_enabled
+        # the packed row is fed to 128-token attention tiles on the GPU
+        self._pad_to = 128 * max(1, pd.tp) if self.device.type == "cuda" else max(1, pd.tp)
+
+    # ---- construction -----------------------------------------------------------------------------------
+    def _build_model(self, hf_assets_path: str, trainable: bool):
+        cfg = self.config
+        dtype = TORCH_DTYPE_MAP[cfg.training.dtype]
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(dtype)
+        try:
+            with torch.device("meta"):
+                model = self.model_spec.model.build()
+        finally:
+            torch.set_default_dtype(old)
+        pd = self.parallel_dims
+        if pd.world_size > 1:
+            model = self.model_spec.parallelize_fn(
+                model, parallel_dims=pd, training=cfg.training, model_converters=None, parallelism=cfg.parallelism,
+                compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="",
+            )
+        model.to_empty(device=self.device)
+        with torch.no_grad():
+            model.init_weights(buffer_device=self.device)
+        if pd.world_size > 1:
+            from torchtitan_b200.parallel import fsdp
+            from torchtitan_b200.parallel.tp import finalize_tp
+
+            fsdp.materialize(model)
+            if pd.tp_enabled or pd.ep_enabled:
+                finalize_tp(model)
+        if hf_assets_path and self.sd_adapter is not None and os.path.isdir(hf_assets_path) and any(
+                f.endswith(".safetensors") for f in os.listdir(hf_assets_path)):
+            self._load_initial_hf_weights(model, hf_assets_path)
+        if trainable:
+            model.train()
+        else:
+            for q in model.parameters():
+                q.requires_grad_(False)
+            model.eval()
+        return model
+
+    def _load_initial_hf_weights(self, model, checkpoint_path: str) -> None:
+        import torch.distributed.checkpoint as dcp
+        from torch.distributed.checkpoint.state_dict import StateDictOptions, set_model_state_dict
+
+        reader = self.sd_adapter.get_hf_storage_reader(checkpoint_path)
+        hf_sd = self.sd_adapter.to_hf(model.state_dict())
+        dcp.load(hf_sd, storage_reader=reader)
+        set_model_state_dict(model=model, model_state_dict=self.sd_adapter.from_hf(hf_sd), options=StateDictOptions(strict=True))
+        logger.info(f"Loaded initial weights from {checkpoint_path}")
+
+    @staticmethod
+    @torch.no_grad()
+    def _copy_weights(src, dst) -> None:
+        d = dict(dst.named_parameters())
+        for n, p in src.named_parameters():
+            a = d[n].to_local() if hasattr(d[n], "to_local") else d[n]
+            b = p.to_local() if hasattr(p, "to_local") else p
+            a.copy_(b)
+
+    # ---- endpoints ----------------------------------------------------------------------------------------
+    def get_weights(self) -> dict:
+        """Full (unsharded) tensors keyed like the model's state dict."""
+        return {k: full_tensor(v) for k, v in self.model.state_dict().items() if torch.is_tensor(v)}
+
+    def step(self, episodes: list[Episode]) -> dict:
+        cfg = self.config
+        advantages = torch.tensor([ep.advantage for ep in episodes])
+        rewards = torch.tensor([ep.reward for ep in episodes])
+        mine = list(range(self.dp_rank, len(episodes), self.dp_size))
+        gen_ids = [episodes[i].token_ids for i in mine]
+        prompt_ids = [episodes[i].prompt_token_ids for i in mine]
+        gen_lps = [episodes[i].token_log_probs for i in mine]
+        my_adv = advantages[mine]
+
+        with torch.no_grad():
+            ref_lps = compute_token_log_probs_packed(self.ref_model, prompt_ids, gen_ids, self.device, self._pad_to)
+        loss, loss_metrics, token_lps = compute_policy_gradient_loss(
+            self.model, gen_ids, prompt_ids, my_adv, ref_lps, kl_coef=cfg.kl_coef, ppo_clip_eps=cfg.ppo_clip_eps,
+            entropy_coef=cfg.entropy_coef, objective=cfg.objective, gen_token_log_probs=gen_lps, pad_to=self._pad_to,
+        )
+        check = verify_logprob_identity(gen_lps, token_lps)
+        self.optimizers.zero_grad()
+        # data-parallel mean of the per-rank losses: FSDP sums gradients, so scale by 1 / dp_size
+        (loss / self.dp_size if self.dp_enabled else loss).backward()
+        if self.dp_enabled and not self._fsdp_owns_grads():
+            for p in self.model.parameters():
+                if p.grad is not None:
+                    dist.all_reduce(p.grad, op=dist.ReduceOp.SUM, group=self.parallel_dims.get_mesh("batch").get_group()
+                                    if self.parallel_dims.get_optional_mesh("batch") is not None else None)
+        grad_norm = dist_utils.clip_grad_norm_(
+            [p for m in self.model_parts for p in m.parameters()], cfg.training.max_norm, foreach=True,
+            pp_mesh=self.parallel_dims.get_optional_mesh("pp"),
+        )
+        self.optimizers.step()
+        self.lr_schedulers.step()
+        self.policy_version += 1
+        return {
+            "loss": loss.item(), "reward_mean": rewards.mean().item(),
+            "reward_std": rewards.std().item() if len(rewards) > 1 else 0.0,
+            "advantage_mean": advantages.mean().item(), "advantage_std": advantages.std().item() if len(advantages) > 1 else 0.0,
+            "sample_completion": episodes[0].text[:80], "policy_version": self.policy_version,
+            "grad_norm": float(grad_norm), "logprob_diff_mean": check["logprob_diff_mean"],
+            "logprob_diff_max": check["logprob_diff_max"], "logprob_max_delta": check["logprob_max_delta"],
+            "logprob_bitwise_identical": check["logprob_bitwise_identical"], **loss_metrics,
+        }
+
+    def _fsdp_owns_grads(self) -> bool:
+        from torchtitan_b200.parallel import fsdp
+
+        return bool(fsdp.fsdp_units(self.model))
