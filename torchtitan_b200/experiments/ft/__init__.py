@@ -1,0 +1,9 @@
+"""Replica-group fault tolerance: each replica group is its own launcher invocation; groups find each
+other through a heartbeat/quorum service (native, ``csrc/ft/lighthouse.cpp``), average gradients over
+the replicas that are alive at each step, and a group that rejoins pulls live state from a healthy one.
+Counterpart of torchtitan/experiments/ft (which delegates these pieces to the external torchft package)."""
+
+from .lighthouse import Lighthouse, LighthouseClient, Quorum
+from .manager import FTManager, ReplicaManager
+
+__all__ = ["Lighthouse", "LighthouseClient", "Quorum", "FTManager", "ReplicaManager"]

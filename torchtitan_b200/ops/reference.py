@@ -7,6 +7,7 @@ Shapes: activations are ``[B, S, H, Dh]`` (sequence before heads) everywhere.
 
 from __future__ import annotations
 
+import functools
 import math
 
 import torch
@@ -86,12 +87,39 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
         )
         return out.transpose(1, 2)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    # the score matrix is materialised: bound it by walking the queries in chunks (recomputed in backward)
+    chunk = S
+    while B * H * chunk * Sk * 4 > (1 << 30) and chunk > 128:
+        chunk = (chunk + 1) // 2
+    outs, lses = [], []
+    for q0 in range(0, S, chunk):
+        q1 = min(S, q0 + chunk)
+        args = (q[:, q0:q1], k, v, sinks, doc_ids[:, q0:q1] if doc_ids is not None else None, doc_ids)
+        fn = functools.partial(_masked_attention_rows, q0=q0 + (Sk - S), causal=causal, scale=scale, window=window)
+        if chunk < S and torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, sinks)):
+            from torch.utils.checkpoint import checkpoint
+
+            o, l = checkpoint(fn, *args, use_reentrant=False)
+        else:
+            o, l = fn(*args)
+        outs.append(o)
+        lses.append(l)
+    out = outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
+    if return_lse:
+        return out, (lses[0] if len(lses) == 1 else torch.cat(lses, dim=2))  # lse [B,H,S]
+    return out
+
+
+def _masked_attention_rows(q, k, v, sinks, doc_q, doc_k, *, q0: int, causal: bool, scale: float, window):
+    """Rows ``q0 ... q0 + q.shape[1]`` (key-aligned positions) of masked attention; returns (out, lse)."""
+    B, S, H, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
     g = H // Hkv
     qf = q.float().transpose(1, 2)  # B,H,S,D
     kf = k.float().transpose(1, 2).repeat_interleave(g, dim=1)
     vf = v.float().transpose(1, 2).repeat_interleave(g, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale  # B,H,S,Sk
-    qi = torch.arange(S, device=q.device).view(S, 1) + (Sk - S)
+    qi = torch.arange(S, device=q.device).view(S, 1) + q0
     ki = torch.arange(Sk, device=q.device).view(1, Sk)
     mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device)
     if causal:
@@ -99,8 +127,8 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
     if window is not None:
         mask &= ki > qi - window
     mask = mask.view(1, 1, S, Sk)
-    if doc_ids is not None:
-        mask = mask & (doc_ids.view(B, 1, S, 1) == doc_ids.view(B, 1, 1, Sk))
+    if doc_q is not None:
+        mask = mask & (doc_q.view(B, 1, S, 1) == doc_k.view(B, 1, 1, Sk))
     s = s.masked_fill(~mask, float("-inf"))
     if sinks is not None:
         sink = sinks.float().view(1, H, 1, 1).expand(B, H, S, 1)
@@ -109,10 +137,7 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
         lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse.unsqueeze(-1))
     p = torch.nan_to_num(p, nan=0.0)
-    out = torch.matmul(p, vf).transpose(1, 2).to(q.dtype)
-    if return_lse:
-        return out, lse  # lse [B,H,S]
-    return out
+    return torch.matmul(p, vf).transpose(1, 2).to(q.dtype), lse
 
 
 def cross_entropy_sum(logits, labels, ignore_index: int = -100):

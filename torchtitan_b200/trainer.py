@@ -140,6 +140,7 @@ class Trainer(Stateful, Configurable):
             torch.cuda.set_device(self.device)
 
         self.parallel_dims = pd = self.init_distributed()
+        self._post_init_distributed()
         if pd.dp_enabled:
             self.dp_degree = pd.dim_size("batch")
             self.dp_rank = pd.coordinate("batch", dist.get_rank())
@@ -224,7 +225,7 @@ class Trainer(Stateful, Configurable):
         logger.info(f"{dev_type.upper()} memory usage for model: {mem.max_reserved_gib:.2f}GiB({mem.max_reserved_pct:.2f}%)")
 
         # ---- optimizer / schedule / checkpoint -----------------------------------------------------
-        self.optimizers = config.optimizer.build(model_parts=self.model_parts)
+        self.optimizers = self._build_optimizers()
         if spec.post_optimizer_build_fn is not None:
             spec.post_optimizer_build_fn(self.optimizers, self.model_parts, pd)
         self.lr_schedulers = config.lr_scheduler.build(optimizers=self.optimizers, training_steps=config.training.steps)
@@ -266,9 +267,21 @@ class Trainer(Stateful, Configurable):
             f"{config.training.seq_len}, total steps {config.training.steps} (warmup {config.lr_scheduler.warmup_steps})"
         )
 
+    # ---- extension points used by experiment trainers (fault tolerance, forge, flux) -------------
+    def _post_init_distributed(self) -> None:
+        """Runs right after the process groups exist and before anything else is built."""
+
+    def _dataloader_dp_info(self) -> tuple[int, int]:
+        """(degree, rank) by which the dataset is split; replica-group trainers widen it."""
+        return self.dp_degree, self.dp_rank
+
+    def _build_optimizers(self):
+        return self.config.optimizer.build(model_parts=self.model_parts)
+
     def _build_dataloader(self, dl_config, local_batch_size: int):
+        dp_degree, dp_rank = self._dataloader_dp_info()
         return dl_config.build(
-            dp_world_size=self.dp_degree, dp_rank=self.dp_rank, tokenizer=self.tokenizer,
+            dp_world_size=dp_degree, dp_rank=dp_rank, tokenizer=self.tokenizer,
             seq_len=self.config.training.seq_len, local_batch_size=local_batch_size,
             model_vocab_size=getattr(self.model_config, "vocab_size", None),
         )
