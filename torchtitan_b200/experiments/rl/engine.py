@@ -95,6 +95,7 @@ class GenerationEngine:
         self.cudagraph = cudagraph and self.device.type == "cuda"
         self._graphs: dict[tuple[int, int], tuple] = {}
         self.decode_steps = 0
+        self.weight_half = 0   # which half of a double-buffered parameter arena the model currently reads
 
     # ---- one pass over the blocks with cache reads/writes -----------------------------------------
     def _attention(self, att, x, positions, layer: int, meta):
@@ -233,7 +234,7 @@ class GenerationEngine:
         self.decode_steps += 1
         if not self.cudagraph:
             return self._forward(tokens, positions, meta)
-        key = (B, maxb)
+        key = (B, maxb, self.weight_half)     # captured graphs hold parameter addresses: one set per arena half
         if key not in self._graphs:
             static = {"tokens": tokens.clone(), "positions": positions.clone(),
                       "meta": {k: (v.clone() if torch.is_tensor(v) else v) for k, v in meta.items()}}

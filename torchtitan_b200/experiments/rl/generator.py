@@ -130,6 +130,9 @@ class Generator(Configurable):
                     if k in own and own[k].shape == v.shape:
                         own[k].copy_(v)
         self.policy_version = version
+        arena = getattr(self, "arena", None)
+        if arena is not None:
+            self.engine.weight_half = arena.active
 
     # ---- rollouts --------------------------------------------------------------------------------------
     def generate(self, prompt_texts: list[str], expected_answers: list[str] | None = None) -> list[Episode]:

@@ -127,13 +127,13 @@ class RLTrainer(Configurable):
             self.generator = Generator(c.generator, model_spec=c.model_spec, model_path=c.hf_assets_path,
                                        batch_invariant_mode=c.batch_invariant_mode, tokenizer=self.tokenizer, device=device)
             self.arena = ParamArena(self.generator.model)
+            self.generator.arena = self.arena
         self.grader = Grader(self.task.reward_function)
         self._sync_weights(0)
 
     def _sync_weights(self, version: int) -> None:
         if self.colocated:
-            if self.trainer.parallel_dims.world_size > 1 or True:
-                sync_local(self.trainer.model, self.arena)
+            sync_local(self.trainer.model, self.arena)
         else:
             if self.arena is not None:
                 src_model = self.trainer.model if (self.trainer is not None and dist.get_rank() == 0) else None

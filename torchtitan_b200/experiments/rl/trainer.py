@@ -87,7 +87,8 @@ class PolicyTrainer(Configurable):
         finally:
             torch.set_default_dtype(old)
         pd = self.parallel_dims
-        if pd.world_size > 1:
+        managed = pd.world_size > 1 or self.device.type == "cuda"   # one GPU: bf16 compute over fp32 master shards
+        if managed:
             model = self.model_spec.parallelize_fn(
                 model, parallel_dims=pd, training=cfg.training, model_converters=None, parallelism=cfg.parallelism,
                 compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="",
@@ -95,7 +96,7 @@ class PolicyTrainer(Configurable):
         model.to_empty(device=self.device)
         with torch.no_grad():
             model.init_weights(buffer_device=self.device)
-        if pd.world_size > 1:
+        if managed:
             from torchtitan_b200.parallel import fsdp
             from torchtitan_b200.parallel.tp import finalize_tp
 

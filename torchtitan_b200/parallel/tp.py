@@ -96,6 +96,20 @@ class _AllGatherLast(torch.autograd.Function):
         return g[..., r * ctx.n : (r + 1) * ctx.n].contiguous(), None
 
 
+class _AllReduceSum(torch.autograd.Function):
+    """Sum over the group; the gradient passes through unchanged (every rank holds the full gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        out = x.contiguous().clone()
+        dist.all_reduce(out, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
 def all_gather_seq(x, group):
     return _AllGatherSeq.apply(x, group)
 
@@ -256,8 +270,14 @@ def _wrap(module: nn.Module, fn):
 
 
 def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True, async_tp: bool = False,
-                        cp_enabled: bool = False, enable_float8_tensorwise_tp: bool = False) -> nn.Module:
+                        cp_enabled: bool = False, enable_float8_tensorwise_tp: bool = False,
+                        sequence_parallel: bool = True) -> nn.Module:
     group = tp_mesh.get_group()
+    if sequence_parallel:
+        _gather, _scatter = all_gather_seq, reduce_scatter_seq
+    else:
+        # inference plan (generation scripts): activations stay replicated, partial sums are all-reduced
+        _gather, _scatter = (lambda x, g: x), (lambda x, g: _AllReduceSum.apply(x, g))
     W, r = tp_mesh.size(), tp_mesh.get_local_rank()
     fused = None
     if async_tp and torch.cuda.is_available():
@@ -281,7 +301,7 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
             ok = (local >= 0) & (local < Vl)
             out = torch.nn.functional.embedding(local.clamp(0, Vl - 1), emb.weight)
             out = out * ok.unsqueeze(-1).to(out.dtype)
-            return reduce_scatter_seq(out, group)
+            return _scatter(out, group)
 
         _wrap(emb, emb_forward)
 
@@ -316,7 +336,7 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
         for nm in ("q_norm", "k_norm"):
             if getattr(att, nm, None) is not None:
                 _mark_replicated(getattr(att, nm), group, tp_mesh)
-        _wrap(att, lambda inner, x, *a, **k: reduce_scatter_seq(inner(all_gather_seq(x, group), *a, **k), group))
+        _wrap(att, lambda inner, x, *a, **k: _scatter(inner(_gather(x, group), *a, **k), group))
         if fused is not None:
             fused.attach_attention(att)
         ff = getattr(block, "feed_forward", None)
@@ -324,7 +344,7 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
             _shard_param(ff.w1, "weight", 0, r, W, group, tp_mesh)
             _shard_param(ff.w3, "weight", 0, r, W, group, tp_mesh)
             _shard_param(ff.w2, "weight", 1, r, W, group, tp_mesh)
-            _wrap(ff, lambda inner, x, *a, **k: reduce_scatter_seq(inner(all_gather_seq(x, group), *a, **k), group))
+            _wrap(ff, lambda inner, x, *a, **k: _scatter(inner(_gather(x, group), *a, **k), group))
             if fused is not None:
                 fused.attach_ffn(ff)
         for nm in ("attention_norm", "ffn_norm"):
@@ -341,7 +361,7 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
         LOSS_PARALLEL.group = group
 
         def out_forward(inner, x):
-            y = inner(all_gather_seq(x, group))  # [B, S, V/tp]
+            y = inner(_gather(x, group))  # [B, S, V/tp]
             if loss_parallel:
                 y._tp_vocab_sharded = group  # consumed by the loss (see components/loss.py)
                 return y
