@@ -207,6 +207,99 @@ def test_attention(ops, B, S, H, Hkv, causal):
     assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
 
 
+@pytest.mark.parametrize("kind", ["docs", "window", "docs+window", "block"])
+@pytest.mark.parametrize("B,S,H,Hkv", [(2, 512, 4, 2), (1, 1024, 4, 1)])
+def test_attention_range_masks(ops, kind, B, S, H, Hkv):
+    """Document / sliding-window / fixed-block causal masks through the flash kernel vs an fp32 masked reference."""
+    from torchtitan_b200.ops import reference as ref
+
+    torch.manual_seed(1)
+    D = 128
+    q = torch.randn(B, S, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    doc, window = None, None
+    if "docs" in kind:
+        # boundaries that fall inside tiles, on tile edges and make very short documents
+        cuts = torch.tensor([0, 5, 64, 130, 131, 300, 448][: 4 + S // 256], device="cuda")
+        doc = (torch.arange(S, device="cuda").view(1, S) >= cuts.view(-1, 1)).sum(0, keepdim=True).int().expand(B, S).contiguous()
+        if B > 1:
+            doc = doc.clone()
+            doc[1] = (torch.arange(S, device="cuda") // 200).int()
+    if "window" in kind:
+        window = 100
+    if kind == "block":
+        doc = (torch.arange(S, device="cuda") // 192).int().view(1, S).expand(B, S).contiguous()
+    o, lse = ops.attention(q, k, v, causal=True, window=window, doc_ids=doc, return_lse=True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _no_kernel_errors()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    orf, lser = ref.attention(qr, kr, vr, causal=True, window=window, doc_ids=doc, return_lse=True)
+    orf.backward(do.float())
+    assert _rel(o, orf) < 2e-2, _rel(o, orf)
+    assert (lse - lser).abs().max() < 2e-2
+    assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+
+
+@pytest.mark.parametrize("E,N,K,sizes", [
+    (4, 256, 128, [64, 0, 192, 128]),
+    (8, 768, 2048, [640, 64, 0, 128, 1024, 64, 320, 192]),
+    (3, 192, 320, [128, 64, 64]),
+])
+def test_grouped_gemm_device_offsets(ops, E, N, K, sizes):
+    """Grouped GEMM with device-side group offsets (forward, input gradient, weight gradient) vs fp32 per-expert matmuls."""
+    torch.manual_seed(0)
+    R = sum(sizes) + 64                      # trailing padding rows belong to no group
+    x = (torch.randn(R, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(E, N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    counts = torch.tensor(sizes, device="cuda", dtype=torch.int64)
+    counts._tt_aligned = 64
+    y = ops.grouped_linear(x, w, counts)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    _no_kernel_errors()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    outs, s = [], 0
+    for e, n in enumerate(sizes):
+        outs.append(xr[s : s + n] @ wr[e].t())
+        s += n
+    outs.append(xr.new_zeros(R - s, N))
+    yr = torch.cat(outs)
+    yr.backward(gy.float())
+    assert _rel(y, yr) < 2e-2, _rel(y, yr)
+    assert (y[s:] == 0).all()
+    assert _rel(x.grad, xr.grad) < 2e-2, _rel(x.grad, xr.grad)
+    assert _rel(w.grad, wr.grad) < 2e-2, _rel(w.grad, wr.grad)
+
+
+def test_moe_layer_native_grouped_path(ops):
+    """A MoE layer on the GPU (padded dispatcher + device-offset grouped GEMMs) vs the same layer in fp32 on the CPU."""
+    from torchtitan_b200.models.common.moe import MoE
+
+    kw = dict(num_experts=8, num_shared_experts=1, score_func="softmax", route_norm=True, top_k=2, hidden_dim=128,
+              score_before_experts=False)
+    torch.manual_seed(0)
+    ref_moe = MoE.Config(**kw).build(dim=128)
+    ref_moe.init_weights(init_std=0.02, buffer_device=torch.device("cpu"))
+    moe = MoE.Config(**kw).build(dim=128)
+    moe.load_state_dict(ref_moe.state_dict())
+    moe = moe.cuda().bfloat16()
+    moe.router.gate.float()
+    x = torch.randn(2, 256, 128)
+    xg = x.cuda().bfloat16().requires_grad_()
+    xr = x.bfloat16().float().requires_grad_()
+    y = moe(xg)
+    y.float().square().sum().backward()
+    _no_kernel_errors()
+    yr = ref_moe(xr)
+    yr.square().sum().backward()
+    assert _rel(y.cpu(), yr) < 5e-2, _rel(y.cpu(), yr)
+    assert _rel(xg.grad.cpu(), xr.grad) < 8e-2, _rel(xg.grad.cpu(), xr.grad)
+
+
 def test_smoke_step():
     from torchtitan_b200.tools.smoke import run_smoke
 

@@ -151,3 +151,26 @@ def test_gpt_oss_swiglu_and_mxfp4():
     blocks[0, 0, 0] = 0x2 | (0xF << 4)  # values 1.0 and -6.0
     vals = dequantize_mxfp4(blocks, torch.tensor([[128]], dtype=torch.uint8))
     assert vals.shape == (1, 32) and vals[0, 0] == 2.0 and vals[0, 1] == -12.0 and vals[0, 2:].abs().sum() == 0
+
+
+def test_padded_local_dispatcher_matches_unpadded():
+    """The 64-aligned layout (used by the device-side grouped GEMM) gives the same layer output and gradients."""
+    from torchtitan_b200.models.common.moe import MoE
+    from torchtitan_b200.models.common.moe.moe import LocalDispatcher
+
+    kw = dict(num_experts=8, num_shared_experts=1, score_func="softmax", route_norm=True, top_k=2, hidden_dim=32)
+    for before in (True, False):
+        torch.manual_seed(0)
+        a = MoE.Config(score_before_experts=before, **kw).build(dim=16)
+        a.init_weights(init_std=0.02, buffer_device=torch.device("cpu"))
+        b = MoE.Config(score_before_experts=before, **kw).build(dim=16)
+        b.load_state_dict(a.state_dict())
+        b.experts.dispatcher = LocalDispatcher(alignment=64)
+        x1 = torch.randn(2, 24, 16, requires_grad=True)
+        x2 = x1.detach().clone().requires_grad_()
+        ya, yb = a(x1), b(x2)
+        ya.square().sum().backward()
+        yb.square().sum().backward()
+        assert torch.allclose(ya, yb, atol=1e-6)
+        assert torch.allclose(x1.grad, x2.grad, atol=1e-6)
+        assert torch.allclose(a.experts.w2.grad, b.experts.w2.grad, atol=1e-6)

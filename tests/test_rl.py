@@ -41,9 +41,12 @@ def test_sampler_definition():
     # top_p small enough keeps only the best token whatever the draw
     tok, _ = sample_top_p(logits, 1.0, 0.5, torch.tensor([0.0, 0.5, 0.999]))
     assert tok.tolist() == [0, 0, 0]
-    # full nucleus: the draw walks the sorted CDF
+    # top_p = 1: plain multinomial, the draw walks the CDF in index order
     p = torch.softmax(logits[0], -1)
     tok, lp = sample_top_p(logits, 1.0, 1.0, torch.tensor([0.0, float(p[0]) + 1e-3, 0.9999]))
+    assert tok.tolist() == [0, 1, 3]
+    rev = logits.flip(-1)
+    tok, _ = sample_top_p(rev, 1.0, 1.0, torch.tensor([0.0, float(p[3]) + 1e-3, 0.9999]))
     assert tok.tolist() == [0, 1, 3]
     assert torch.allclose(lp, torch.log_softmax(logits, -1)[0, tok])
 

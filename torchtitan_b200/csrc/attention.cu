@@ -1,4 +1,5 @@
-// Causal / full softmax attention with grouped KV heads on tcgen05 tensor cores.
+// Causal / full / range-masked (document, sliding-window, fixed-block) softmax attention with grouped KV heads on
+// tcgen05 tensor cores.
 //
 // Layout: q,o,dO,dq [B,Sq,H,D]; k,v,dk,dv [B,Sk,Hkv,D]; D = 128; lse, delta [B,H,Sq] fp32.
 // All tiles are fetched with 3-D TMA descriptors (D, heads, B*S) straight from that layout, so no
@@ -40,6 +41,11 @@ struct AttnArgs {
   void* out2;           // dkv kernel: dV bf16
   float* lse;           // [B,H,Sq]
   const float* delta;   // [B,H,Sq]
+  // Optional contiguous-range masks (need Sq == Sk): query i sees keys row_lo[b,i] <= k <= i, equivalently key k is
+  // seen by queries k <= i <= col_hi[b,k]. Both arrays are non-decreasing along the sequence, which covers document
+  // masks, sliding windows and fixed blocks. Tiles wholly outside the range are skipped.
+  const int* row_lo;    // [B,Sq] or null
+  const int* col_hi;    // [B,Sk] or null
 };
 
 // Write 64 fp32 values as one 128-byte bf16 row of a K-major, 128B-swizzled operand tile.
@@ -129,6 +135,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const int off = p.Sk - p.Sq;  // query i attends keys <= i + off
   int n_kv = p.Sk / 64;
   if (p.causal) n_kv = min(n_kv, (q0 + 127 + off) / 64 + 1);
+  // range mask: the first row of the tile has the smallest lower bound, earlier key tiles are skipped
+  const int j0 = p.row_lo ? min(__ldg(p.row_lo + static_cast<long long>(b) * p.Sq + q0) / 64, n_kv) : 0;
+  n_kv -= j0;  // from here on: number of key tiles visited, tile index j means key tile j0 + j
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 13; ++i) tt::mbar_init(bar(i), i == 11 ? 4 : 1);
@@ -152,8 +161,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
         if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 11)) return false;
         tt::mbar_expect_tx(bar(1 + s), 16384);
-        tt::tma_load_3d(base + F_K + s * 16384, &tk, bar(1 + s), 0, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(base + F_K + s * 16384 + 8192, &tk, bar(1 + s), 64, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + F_K + s * 16384, &tk, bar(1 + s), 0, hk, b * p.Sk + (j0 + j) * 64);
+        tt::tma_load_3d(base + F_K + s * 16384 + 8192, &tk, bar(1 + s), 64, hk, b * p.Sk + (j0 + j) * 64);
         return true;
       };
       bool ok = n_kv > 0 ? load_k(0) : true;
@@ -161,8 +170,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         if (j + 1 < n_kv && !load_k(j + 1)) break;  // K runs one tile ahead of V
         if (!tt::mbar_wait(bar(7), (j & 1) ^ 1, abort_flag, &g_attn_error, 12)) break;
         tt::mbar_expect_tx(bar(5), 16384);
-        tt::tma_load_3d(base + F_V, &tv, bar(5), 0, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(base + F_V + 8192, &tv, bar(5), 64, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(base + F_V, &tv, bar(5), 0, hk, b * p.Sk + (j0 + j) * 64);
+        tt::tma_load_3d(base + F_V + 8192, &tv, bar(5), 64, hk, b * p.Sk + (j0 + j) * 64);
       }
     }
   } else if (warp == 1) {
@@ -209,6 +218,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
     const int qi = q0 + row;
     const float sc = p.scale * kLog2e;
+    const int lo = p.row_lo ? __ldg(p.row_lo + static_cast<long long>(b) * p.Sq + qi) : 0;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
@@ -227,10 +237,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
         for (int e = 0; e < 32; ++e) x[32 + e] = __uint_as_float(r[e]) * sc;
       }
-      const int kv0 = j * 64;
+      const int kv0 = (j0 + j) * 64;
       if (p.causal && kv0 + 63 > q0 + off) {
 #pragma unroll
         for (int e = 0; e < 64; ++e) if (kv0 + e > qi + off) x[e] = -INFINITY;
+      }
+      if (kv0 < lo) {
+#pragma unroll
+        for (int e = 0; e < 64; ++e) if (kv0 + e < lo) x[e] = -INFINITY;
       }
       float mx = x[0];
 #pragma unroll
@@ -243,7 +257,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       if (first) m_ref = mx;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mx);
-        const float f = fast_exp2(m_ref - m_new);  // 1 when this row did not grow
+        // 1 when this row did not grow; a row that has seen only masked keys so far keeps m = -inf
+        const float f = (m_new == -INFINITY) ? 1.f : fast_exp2(m_ref - m_new);
         m_ref = m_new;
         l *= f;
 #pragma unroll 1
@@ -258,8 +273,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tt::tc_wait_st();
       }
       float sum = 0.f;
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;  // all-masked row: exp2(-inf) = 0, not NaN
 #pragma unroll
-      for (int e = 0; e < 64; ++e) { x[e] = fast_exp2(x[e] - m_ref); sum += x[e]; }
+      for (int e = 0; e < 64; ++e) { x[e] = fast_exp2(x[e] - m_use); sum += x[e]; }
       l += sum;
       store_row_sw128(gbase + F_P, row, x);
       tt::fence_proxy_async();
@@ -329,6 +345,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   const int off = p.Sk - p.Sq;
   int n_kv = p.Sk / 64;
   if (p.causal) n_kv = min(n_kv, (q0 + 127 + off) / 64 + 1);
+  const int j0 = p.row_lo ? min(__ldg(p.row_lo + static_cast<long long>(b) * p.Sq + q0) / 64, n_kv) : 0;
+  n_kv -= j0;  // number of key tiles visited; tile index j means key tile j0 + j
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < QB_COUNT; ++i) tt::mbar_init(bar(i), (i >= QB_DSREADY && i < QB_DSFREE) ? 8 : 1);
@@ -355,10 +373,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         if (!tt::mbar_wait(bar(QB_KVEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 21)) break;
         const uint32_t kb = base + Q_KV + s * 32768, vb = kb + 16384;
         tt::mbar_expect_tx(bar(QB_KVFULL + s), 32768);
-        tt::tma_load_3d(kb, &tk, bar(QB_KVFULL + s), 0, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(kb + 8192, &tk, bar(QB_KVFULL + s), 64, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(vb, &tv, bar(QB_KVFULL + s), 0, hk, b * p.Sk + j * 64);
-        tt::tma_load_3d(vb + 8192, &tv, bar(QB_KVFULL + s), 64, hk, b * p.Sk + j * 64);
+        tt::tma_load_3d(kb, &tk, bar(QB_KVFULL + s), 0, hk, b * p.Sk + (j0 + j) * 64);
+        tt::tma_load_3d(kb + 8192, &tk, bar(QB_KVFULL + s), 64, hk, b * p.Sk + (j0 + j) * 64);
+        tt::tma_load_3d(vb, &tv, bar(QB_KVFULL + s), 0, hk, b * p.Sk + (j0 + j) * 64);
+        tt::tma_load_3d(vb + 8192, &tv, bar(QB_KVFULL + s), 64, hk, b * p.Sk + (j0 + j) * 64);
       }
     }
   } else if (warp == 1) {
@@ -401,13 +419,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     const float lse2 = p.lse[stat] * kLog2e;
     const float dl = p.delta[stat];
     const float sc = p.scale * kLog2e;
+    const int lo = p.row_lo ? __ldg(p.row_lo + static_cast<long long>(b) * p.Sq + qi) : 0;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int t2 = j & 1;
       if (!tt::mbar_wait(bar(QB_SPFULL + t2), (j >> 1) & 1, abort_flag, &g_attn_error, 26)) { ok = false; break; }
       tt::tc_fence_after();
       float ds[32];
-      const int kv0 = j * 64 + half * 32;
+      const int kv0 = (j0 + j) * 64 + half * 32;
       {
         uint32_t rs[32], rp[32];
         tt::tmem_ld_32x32(tS + lane_off + t2 * 64 + half * 32, rs);
@@ -416,7 +435,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           float pr = fast_exp2(__uint_as_float(rs[e]) * sc - lse2);
-          if (p.causal && kv0 + e > qi + off) pr = 0.f;
+          if ((p.causal && kv0 + e > qi + off) || kv0 + e < lo) pr = 0.f;
           ds[e] = pr * (__uint_as_float(rp[e]) - dl) * p.scale;
         }
       }
@@ -479,7 +498,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   const int nq_tiles = p.Sq / 64;
   int qt_first = 0;
   if (p.causal) { const int first_q = kv0 - off; qt_first = first_q > 0 ? first_q / 64 : 0; }
-  const int per_head = nq_tiles > qt_first ? nq_tiles - qt_first : 0;
+  // range mask: the last key of the tile is seen furthest; later query tiles are skipped
+  int qt_end = nq_tiles;
+  if (p.col_hi) qt_end = min(nq_tiles, __ldg(p.col_hi + static_cast<long long>(b) * p.Sk + kv0 + 127) / 64 + 1);
+  const int per_head = qt_end > qt_first ? qt_end - qt_first : 0;
   const int n_steps = per_head * G;
 
   if (threadIdx.x == 0) {
@@ -554,6 +576,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
     const int ki = kv0 + row;
     const float sc = p.scale * kLog2e;
+    const int hi = p.col_hi ? __ldg(p.col_hi + static_cast<long long>(b) * p.Sk + ki) : 0x7fffffff;
     bool ok = true;
     for (int st = 0; st < n_steps; ++st) {
       const int t2 = st & 1;
@@ -578,7 +601,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
           for (int u = 0; u < 4; ++u) {
             const int e = e4 * 4 + u;
             float pr = fast_exp2(__uint_as_float(rs[e]) * sc - ls[u] * kLog2e);
-            if (p.causal && ki > qbase + e + off) pr = 0.f;
+            if ((p.causal && ki > qbase + e + off) || qbase + e > hi) pr = 0.f;
             pt[e] = pr;
             dst[e] = pr * (__uint_as_float(rp[e]) - dd[u]) * p.scale;
           }
@@ -687,27 +710,51 @@ extern "C" {
 // Shapes this build of the kernels accepts (0 = yes).
 int tt_attn_supported(int Sq, int Sk, int H, int Hkv, int Dh) { return check_shapes(Sq, Sk, H, Hkv, Dh); }
 
+// row_lo (nullable, int32 [B,Sq], non-decreasing along the sequence, needs Sq == Sk): see AttnArgs.
+int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo, int B, int Sq,
+                      int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st);
+
 int tt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int H, int Hkv,
                 int Dh, int causal, float scale, cudaStream_t st) {
+  return tt_attn_fwd_range(q, k, v, o, lse, nullptr, B, Sq, Sk, H, Hkv, Dh, causal, scale, st);
+}
+
+int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo, int B, int Sq,
+                      int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st) {
   int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
   if (rc) return rc;
+  if (row_lo && Sq != Sk) return -13;
   set_attrs();
   CUtensorMap tq, tk, tv;
   if ((rc = make_map(&tq, q, static_cast<long long>(B) * Sq, H, 128))) return rc;
   if ((rc = make_map(&tk, k, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
   if ((rc = make_map(&tv, v, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
-  AttnArgs p{B, Sq, Sk, H, Hkv, causal, scale, o, nullptr, lse, nullptr};
+  AttnArgs p{B, Sq, Sk, H, Hkv, causal, scale, o, nullptr, lse, nullptr, row_lo, nullptr};
   dim3 grid(Sq / 128, H, B);
   attn_fwd_kernel<<<grid, 192, FWD_SMEM, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 // delta is scratch [B,H,Sq] fp32 written by the first launch and read by the other two.
+int tt_attn_bwd_range(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                      float* delta, void* dq, void* dk, void* dv, const int* row_lo, const int* col_hi, int B, int Sq,
+                      int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st);
+
 int tt_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
                 float* delta, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal,
                 float scale, cudaStream_t st) {
+  return tt_attn_bwd_range(q, k, v, o, dout, lse, delta, dq, dk, dv, nullptr, nullptr, B, Sq, Sk, H, Hkv, Dh, causal,
+                           scale, st);
+}
+
+// row_lo / col_hi: both null or both given (see AttnArgs).
+int tt_attn_bwd_range(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                      float* delta, void* dq, void* dk, void* dv, const int* row_lo, const int* col_hi, int B, int Sq,
+                      int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st) {
   int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
   if (rc) return rc;
+  if ((row_lo != nullptr) != (col_hi != nullptr)) return -14;
+  if (row_lo && Sq != Sk) return -13;
   set_attrs();
   const long long rows = static_cast<long long>(B) * Sq * H;
   attn_delta_kernel<<<static_cast<unsigned>((rows + 15) / 16), 256, 0, st>>>(
@@ -721,9 +768,9 @@ int tt_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   if ((rc = make_map(&tdo64, dout, static_cast<long long>(B) * Sq, H, 64))) return rc;
   if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
-  AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta};
+  AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta, row_lo, col_hi};
   attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 320, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
-  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta};
+  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta, row_lo, col_hi};
   attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 320, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

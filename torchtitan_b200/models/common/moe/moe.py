@@ -40,14 +40,52 @@ def _moe_ops():
     return moe_ops
 
 
+GROUP_ALIGN_NATIVE = 64  # contraction tile of the grouped weight-gradient kernel
+
+
 class LocalDispatcher:
-    """All experts live on this rank: dispatch = gather rows in expert order."""
+    """All experts live on this rank: dispatch = gather rows in expert order.
+
+    With ``alignment > 1`` every expert's block of rows starts at a multiple of ``alignment`` (zero rows in between),
+    which is what the device-side grouped GEMM needs; the layout is computed on the device from the counts, so there is
+    no host synchronisation. ``alignment=None`` picks 64 for CUDA bf16 inputs when the native kernel is built, else 1."""
+
+    def __init__(self, alignment: int | None = None):
+        self.alignment = alignment
+
+    def _align_for(self, x) -> int:
+        if self.alignment is not None:
+            return self.alignment
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            from torchtitan_b200.ops import native
+
+            return GROUP_ALIGN_NATIVE if native.has("tt_grouped_gemm") else 1
+        return 1
 
     def dispatch(self, x, order, counts, top_k: int):
-        return _moe_ops().gather_rows(x, order, top_k), counts, None
+        a = self._align_for(x)
+        if a <= 1:
+            return _moe_ops().gather_rows(x, order, top_k), counts, None
+        n, E = order.numel(), counts.numel()
+        c = counts.to(torch.int64)
+        padded = (c + (a - 1)) // a * a
+        starts = torch.cumsum(c, 0) - c
+        pstarts = torch.cumsum(padded, 0) - padded
+        pos = torch.arange(n, device=x.device)
+        expert = torch.searchsorted(torch.cumsum(c, 0), pos, right=True).clamp_(max=E - 1)
+        dest = pos + (pstarts - starts)[expert]
+        max_rows = (n + E * (a - 1) + a - 1) // a * a          # static upper bound on the padded row count
+        rows = x.new_zeros(max_rows, x.shape[-1]).index_copy(0, dest, _moe_ops().gather_rows(x, order, top_k))
+        pc = padded.to(counts.dtype)
+        pc._tt_aligned = a                                      # read by the CUDA grouped GEMM wrapper
+        return rows, pc, {"dest": dest, "max_rows": max_rows}
+
+    def scale_rows(self, rows, scores_sorted, ctx):
+        sc = rows.new_zeros(ctx["max_rows"], 1, dtype=torch.float32).index_copy(0, ctx["dest"], scores_sorted.reshape(-1, 1).float())
+        return (rows.float() * sc).to(rows.dtype)
 
     def combine(self, y, ctx):
-        return y
+        return y if ctx is None else y.index_select(0, ctx["dest"])
 
 
 class GroupedExperts(Module):

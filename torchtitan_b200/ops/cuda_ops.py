@@ -290,54 +290,75 @@ def swiglu(gate: Tensor, up: Tensor) -> Tensor:
 
 # =============================================================================== attention
 @torch.library.custom_op("tt_b200::attention_fwd", mutates_args=())
-def attention_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float) -> tuple[Tensor, Tensor]:
+def attention_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float,
+                  row_lo: Tensor | None = None) -> tuple[Tensor, Tensor]:
     B, Sq, H, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     o = torch.empty_like(q)
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
-    _ck(_lib().tt_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, Sq, Sk, H, Hkv, D,
-                           int(causal), scale, _stream()), "tt_attn_fwd")
+    _ck(_lib().tt_attn_fwd_range(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo), B, Sq, Sk,
+                                 H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd")
     return o, lse
 
 
 @attention_fwd.register_fake
-def _(q, k, v, causal, scale):
+def _(q, k, v, causal, scale, row_lo=None):
     return torch.empty_like(q), q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32)
 
 
 @torch.library.custom_op("tt_b200::attention_bwd", mutates_args=())
-def attention_bwd(q: Tensor, k: Tensor, v: Tensor, o: Tensor, do: Tensor, lse: Tensor, causal: bool,
-                  scale: float) -> tuple[Tensor, Tensor, Tensor]:
+def attention_bwd(q: Tensor, k: Tensor, v: Tensor, o: Tensor, do: Tensor, lse: Tensor, causal: bool, scale: float,
+                  row_lo: Tensor | None = None, col_hi: Tensor | None = None) -> tuple[Tensor, Tensor, Tensor]:
     B, Sq, H, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
-    _ck(_lib().tt_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
-                           delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Sq, Sk, H, Hkv, D, int(causal),
-                           scale, _stream()), "tt_attn_bwd")
+    _ck(_lib().tt_attn_bwd_range(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                 delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _p(row_lo), _p(col_hi), B, Sq,
+                                 Sk, H, Hkv, D, int(causal), scale, _stream()), "tt_attn_bwd")
     return dq, dk, dv
 
 
 @attention_bwd.register_fake
-def _(q, k, v, o, do, lse, causal, scale):
+def _(q, k, v, o, do, lse, causal, scale, row_lo=None, col_hi=None):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
+    def forward(ctx, q, k, v, causal, scale, row_lo=None, col_hi=None):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, causal, scale)
-        ctx.save_for_backward(q, k, v, o, lse)
+        o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, causal, scale, row_lo)
+        ctx.save_for_backward(q, k, v, o, lse, row_lo, col_hi)
         ctx.causal, ctx.scale = causal, scale
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, _dlse):
-        q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = torch.ops.tt_b200.attention_bwd(q, k, v, o, do.contiguous(), lse, ctx.causal, ctx.scale)
-        return dq, dk, dv, None, None
+        q, k, v, o, lse, row_lo, col_hi = ctx.saved_tensors
+        dq, dk, dv = torch.ops.tt_b200.attention_bwd(q, k, v, o, do.contiguous(), lse, ctx.causal, ctx.scale, row_lo, col_hi)
+        return dq, dk, dv, None, None, None, None
+
+
+def range_bounds(doc_ids: Tensor | None, window: int | None, B: int, S: int, device) -> tuple[Tensor, Tensor]:
+    """Per-query first visible key and per-key last visible query (int32 [B, S]) of a causal mask restricted to the
+    token's own document (a document is a maximal run of equal ids) and/or to a sliding window."""
+    idx = torch.arange(S, device=device, dtype=torch.int32).expand(B, S)
+    if doc_ids is not None:
+        d = doc_ids.to(device)
+        edge = d[:, 1:] != d[:, :-1]
+        one = torch.ones((B, 1), dtype=torch.bool, device=device)
+        starts = torch.where(torch.cat((one, edge), 1), idx, torch.zeros_like(idx))
+        lo = torch.cummax(starts, dim=1).values
+        ends = torch.where(torch.cat((edge, one), 1), idx, torch.full_like(idx, S - 1))
+        hi = torch.flip(torch.cummin(torch.flip(ends, (1,)), dim=1).values, (1,))
+    else:
+        lo, hi = torch.zeros_like(idx), torch.full_like(idx, S - 1)
+    if window is not None:
+        lo = torch.maximum(lo, idx - (window - 1))
+        hi = torch.minimum(hi, idx + (window - 1))
+    return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
 
 
 def attention_supported(q: Tensor, k: Tensor) -> bool:
@@ -346,10 +367,19 @@ def attention_supported(q: Tensor, k: Tensor) -> bool:
 
 
 def attention(q, k, v, *, causal=True, scale=None, window=None, doc_ids=None, sinks=None, return_lse=False):
-    plain = window is None and doc_ids is None and sinks is None
-    if plain and k.dtype == q.dtype and attention_supported(q, k):
+    """Flash attention kernel for causal / full attention and for causal attention restricted to documents and/or a
+    sliding window (contiguous key ranges); attention sinks and unsupported shapes take the PyTorch definition."""
+    ranged = window is not None or doc_ids is not None
+    ok = sinks is None and k.dtype == q.dtype and attention_supported(q, k)
+    if ok and ranged:
+        ok = bool(causal) and q.shape[1] == k.shape[1]
+    if ok:
         scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-        o, lse = _AttnFn.apply(q, k, v, bool(causal), scale)
+        if ranged:
+            lo, hi = range_bounds(doc_ids, window, q.shape[0], q.shape[1], q.device)
+            o, lse = _AttnFn.apply(q, k, v, True, scale, lo, hi)
+        else:
+            o, lse = _AttnFn.apply(q, k, v, bool(causal), scale)
         return (o, lse) if return_lse else o
     warn_once(logger, f"attention shape/mask q={tuple(q.shape)} k={tuple(k.shape)} dtype={q.dtype} "
                       f"window={window} doc={doc_ids is not None} sinks={sinks is not None} takes the PyTorch path")
@@ -547,8 +577,47 @@ def _group_sizes(counts: Tensor) -> list[int]:
     return sizes
 
 
+class _GroupedGemmFn(torch.autograd.Function):
+    """One launch per GEMM over all experts; group boundaries stay on the device (``csrc/grouped_gemm.cu``).
+    Needs every group size to be a multiple of 64 (the dispatcher pads with zero rows)."""
+
+    @staticmethod
+    def forward(ctx, x, w, offs):
+        R, K = x.shape
+        E, N, _ = w.shape
+        y = x.new_zeros(R, N)
+        _ck(_lib().tt_grouped_gemm(x.data_ptr(), w.data_ptr(), y.data_ptr(), offs.data_ptr(), R, E, N, K, 0, x.stride(0),
+                                   y.stride(0), _stream()), "tt_grouped_gemm")
+        ctx.save_for_backward(x, w, offs)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w, offs = ctx.saved_tensors
+        gy = gy.contiguous()
+        R, K = x.shape
+        E, N, _ = w.shape
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.zeros_like(x)
+            # w viewed as [E, K' = N, N' = K]: the contraction runs over w's first matrix dimension (b_mn)
+            _ck(_lib().tt_grouped_gemm(gy.data_ptr(), w.data_ptr(), gx.data_ptr(), offs.data_ptr(), R, E, K, N, 1, gy.stride(0),
+                                       gx.stride(0), _stream()), "tt_grouped_gemm(dgrad)")
+        if ctx.needs_input_grad[1]:
+            gw = torch.zeros_like(w)
+            _ck(_lib().tt_grouped_gemm_wgrad(gy.data_ptr(), x.data_ptr(), gw.data_ptr(), offs.data_ptr(), R, E, N, K,
+                                             gy.stride(0), x.stride(0), int(gw.dtype == torch.float32), _stream()),
+                "tt_grouped_gemm_wgrad")
+        return gx, gw, None
+
+
 def grouped_linear(x, w, counts):
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and w.shape[1] % 8 == 0:
+    ok = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and w.shape[1] % 8 == 0
+    aligned = getattr(counts, "_tt_aligned", 0)
+    if ok and aligned and aligned % 64 == 0 and w.shape[1] % 64 == 0 and w.shape[2] % 64 == 0 and native.has("tt_grouped_gemm"):
+        offs = torch.cumsum(counts, 0).to(torch.int32)
+        return _GroupedGemmFn.apply(x.contiguous(), w.contiguous(), offs)
+    if ok:
         return _GroupedLinearFn.apply(x.contiguous(), w, counts)
     from .moe_ops import _GroupedLinearRef
 
@@ -560,3 +629,45 @@ def moe_fill_indices(tokens_per_expert_group, start_index_values, write_offsets,
 
     return fill_indices_cpu(tokens_per_expert_group.cpu(), start_index_values.cpu(), write_offsets.cpu(),
                             experts_per_rank, num_ranks, max_len).to(tokens_per_expert_group.device)
+
+
+# =============================================================================== generation (see csrc/serving.cu)
+def kv_write(k_cache: Tensor, v_cache: Tensor, k: Tensor, v: Tensor, slots: Tensor) -> None:
+    T, Hkv, D = k.shape
+    if k.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or D != 128:
+        kc, vc = k_cache.view(-1, Hkv, D), v_cache.view(-1, Hkv, D)
+        kc.index_copy_(0, slots.long(), k.to(kc.dtype))
+        vc.index_copy_(0, slots.long(), v.to(vc.dtype))
+        return
+    k, v = k.contiguous(), v.contiguous()
+    _ck(_lib().tt_kv_write(k_cache.data_ptr(), v_cache.data_ptr(), k.data_ptr(), v.data_ptr(), slots.to(torch.int32).data_ptr(),
+                           T, Hkv, D, _stream()), "tt_kv_write")
+
+
+def paged_decode(q: Tensor, k_cache: Tensor, v_cache: Tensor, block_tables: Tensor, context_lens: Tensor, scale: float) -> Tensor:
+    B, H, D = q.shape
+    nb, bs, Hkv, _ = k_cache.shape
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or D != 128 or (H // Hkv) not in (1, 2, 4, 8):
+        raise NotImplementedError(f"paged decode kernel: bf16, head_dim 128 and 1/2/4/8 query heads per kv head (got {q.dtype}, {D}, {H}/{Hkv})")
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    bt = block_tables if block_tables.dtype == torch.int32 else block_tables.to(torch.int32)
+    cl = context_lens if context_lens.dtype == torch.int32 else context_lens.to(torch.int32)
+    _ck(_lib().tt_paged_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), bt.contiguous().data_ptr(), cl.data_ptr(),
+                               out.data_ptr(), float(scale), B, H, Hkv, D, bs, bt.shape[1], _stream()), "tt_paged_decode")
+    return out
+
+
+def sample(logits: Tensor, temperature: float, uniforms: Tensor) -> tuple[Tensor, Tensor]:
+    """Greedy (temperature <= 0) or index-order multinomial sampling; one CTA per row."""
+    B, V = logits.shape
+    if logits.dtype not in (torch.float32, torch.bfloat16):
+        logits = logits.float()
+    if logits.stride(-1) != 1:
+        logits = logits.contiguous()
+    tok = torch.empty(B, dtype=torch.int64, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    u = uniforms.to(torch.float32).contiguous()
+    _ck(_lib().tt_sample(logits.data_ptr(), u.data_ptr(), tok.data_ptr(), lp.data_ptr(), B, V, logits.stride(0), float(temperature),
+                         int(logits.dtype == torch.bfloat16), _stream()), "tt_sample")
+    return tok, lp

@@ -57,6 +57,14 @@ def lib():
     _sig(L.tt_attn_fwd, [P, P, P, P, P, I, I, I, I, I, I, I, F, P])
     _sig(L.tt_attn_bwd, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
     _sig(L.tt_attn_error, [])
+    _sig(L.tt_attn_fwd_range, [P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    _sig(L.tt_attn_bwd_range, [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    _sig(L.tt_grouped_gemm, [P, P, P, P, LL, I, I, I, I, LL, LL, P])
+    _sig(L.tt_grouped_gemm_wgrad, [P, P, P, P, LL, I, I, I, LL, LL, I, P])
+    _sig(L.tt_grouped_gemm_error, [])
+    _sig(L.tt_kv_write, [P, P, P, P, P, LL, I, I, P])
+    _sig(L.tt_paged_decode, [P, P, P, P, P, P, F, I, I, I, I, I, I, P])
+    _sig(L.tt_sample, [P, P, P, P, I, I, LL, F, I, P])
     for name, sig in _OPTIONAL.items():
         if hasattr(L, name):
             _sig(getattr(L, name), sig)
@@ -92,5 +100,5 @@ def check(rc: int, what: str) -> None:
 def kernel_errors() -> dict:
     """Error words set by kernels whose bounded waits expired (reading clears them)."""
     L = lib()
-    out = {"gemm": L.tt_gemm_error(), "attention": L.tt_attn_error()}
+    out = {"gemm": L.tt_gemm_error(), "attention": L.tt_attn_error(), "grouped_gemm": L.tt_grouped_gemm_error()}
     return {k: v for k, v in out.items() if v}

@@ -15,13 +15,6 @@ import torch
 
 from . import native
 
-for _name, _sig in (
-    ("tt_paged_decode", None),
-    ("tt_kv_write", None),
-    ("tt_sample_top_p", None),
-):
-    pass  # signatures are registered in cuda_ops when the library exports them
-
 
 def kv_cache_write(k_cache, v_cache, k, v, slots):
     """Scatter new keys/values ``[T, Hkv, D]`` into flat cache slots ``slots[T]`` (= block * block_size + offset)."""
@@ -37,7 +30,8 @@ def kv_cache_write(k_cache, v_cache, k, v, slots):
 def paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scale: float):
     """One query token per sequence: ``q [B, H, D]`` attends to the first ``context_lens[b]`` cached tokens
     of its sequence. Returns ``[B, H, D]``. GQA: query head h reads kv head ``h // (H / Hkv)``."""
-    if q.is_cuda and native.has("tt_paged_decode"):
+    if q.is_cuda and native.has("tt_paged_decode") and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and \
+            (q.shape[1] // k_cache.shape[2]) in (1, 2, 4, 8):
         from .cuda_ops import paged_decode
 
         return paged_decode(q, k_cache, v_cache, block_tables, context_lens, scale)
@@ -60,20 +54,26 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scal
 def sample_top_p(logits, temperature: float, top_p: float, uniforms):
     """Sample one token per row of ``logits [B, V]``.
 
-    ``uniforms [B]`` in [0, 1) drives the draw (inverse-CDF over the probability-sorted nucleus), so a
-    given (logits, uniform) pair always yields the same token on every device. ``temperature == 0`` is
-    greedy. Returns (tokens int64 [B], log-probabilities fp32 [B]); the log-probability is taken from the
+    ``uniforms [B]`` in [0, 1) drives the draw by inverse CDF -- over the vocabulary in index order when
+    ``top_p >= 1`` (plain multinomial sampling, no sort), over the probability-sorted nucleus otherwise -- so a
+    given (logits, uniform) pair yields the same token on every device up to rounding at CDF boundaries.
+    ``temperature == 0`` is greedy (lowest index on ties). Returns (tokens int64 [B], log-probabilities fp32 [B]); the log-probability is taken from the
     fp32 log-softmax of the *unscaled* logits, which is what the trainer recomputes."""
-    if logits.is_cuda and native.has("tt_sample_top_p"):
-        from .cuda_ops import sample_top_p as native_sample
+    if logits.is_cuda and native.has("tt_sample") and (top_p >= 1.0 or temperature <= 0.0):
+        from .cuda_ops import sample as native_sample
 
-        return native_sample(logits, temperature, top_p, uniforms)
+        return native_sample(logits, temperature, uniforms)
     lf = logits.float()
     logp_raw = torch.log_softmax(lf, dim=-1)
     if temperature <= 0.0:
         tok = lf.argmax(-1)
         return tok, logp_raw.gather(1, tok.view(-1, 1)).squeeze(1)
     probs = torch.softmax(lf / temperature, dim=-1)
+    if top_p >= 1.0:
+        cdf = probs.cumsum(-1)
+        target = uniforms.float().view(-1, 1) * cdf[:, -1:]
+        tok = (cdf <= target).sum(-1).clamp(max=logits.shape[-1] - 1)
+        return tok, logp_raw.gather(1, tok.view(-1, 1)).squeeze(1)
     sp, si = probs.sort(dim=-1, descending=True, stable=True)
     cum = sp.cumsum(-1)
     keep = (cum - sp) < top_p                    # always keeps the most likely token

@@ -82,7 +82,9 @@ class AllToAllDispatcher:
         padded = torch.vstack((recv, recv.new_zeros(1, recv.shape[-1])))  # index -1 -> the zero row
         grouped = padded[perm]
         ctx = {"perm": perm, "n_recv": n_recv, "in_splits": in_splits, "out_splits": out_splits, "rows": rows.shape[0]}
-        return grouped, m_sizes.to(torch.int64).to(recv.device), ctx
+        sizes = m_sizes.to(torch.int64).to(recv.device)
+        sizes._tt_aligned = self.alignment      # read by the CUDA grouped GEMM wrapper (needs multiples of 64)
+        return grouped, sizes, ctx
 
     def scale_rows(self, rows, scores_sorted, ctx):
         # scores travel with the rows: exchange and permute them the same way
@@ -127,7 +129,11 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
         raise NotImplementedError("expert tensor parallel (etp > 1) is not implemented; use etp = 1")
     ep_mesh = parallel_dims.get_optional_mesh("ep")
     tp_mesh = parallel_dims.get_optional_mesh("tp")
-    alignment = 8
+    from torchtitan_b200.models.common.moe.moe import GROUP_ALIGN_NATIVE
+    from torchtitan_b200.ops import native
+
+    # 64-row groups let the device-side grouped GEMM (incl. its weight-gradient form) run without host-side sizes
+    alignment = GROUP_ALIGN_NATIVE if (torch.cuda.is_available() and native.has("tt_grouped_gemm")) else 8
     cf = parallelism.hybridep_non_blocking_expert_capacity_factor if parallelism is not None else None
     n = 0
     for block in model.layers.values():
