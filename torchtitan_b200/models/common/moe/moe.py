@@ -71,14 +71,24 @@ class LocalDispatcher:
         padded = (c + (a - 1)) // a * a
         starts = torch.cumsum(c, 0) - c
         pstarts = torch.cumsum(padded, 0) - padded
-        pos = torch.arange(n, device=x.device)
-        expert = torch.searchsorted(torch.cumsum(c, 0), pos, right=True).clamp_(max=E - 1)
-        dest = pos + (pstarts - starts)[expert]
+        jpos = torch.arange(n, device=x.device)
+        expert = torch.searchsorted(torch.cumsum(c, 0), jpos, right=True).clamp_(max=E - 1)
+        dest = jpos + (pstarts - starts)[expert]                # padded row of sorted entry j
         max_rows = (n + E * (a - 1) + a - 1) // a * a          # static upper bound on the padded row count
-        rows = x.new_zeros(max_rows, x.shape[-1]).index_copy(0, dest, _moe_ops().gather_rows(x, order, top_k))
         pc = padded.to(counts.dtype)
         pc._tt_aligned = a                                      # read by the CUDA grouped GEMM wrapper
-        return rows, pc, {"dest": dest, "max_rows": max_rows}
+        ctx = {"dest": dest, "max_rows": max_rows}
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+            # one gather straight into the padded layout; `pair` / `pos` are the row <-> (token, slot) maps
+            pair = torch.full((max_rows,), -1, dtype=torch.int64, device=x.device).index_copy_(0, dest, order)
+            pos = torch.empty(n, dtype=torch.int32, device=x.device).index_copy_(0, order, dest.to(torch.int32))
+            src = torch.where(pair >= 0, pair // top_k, pair).to(torch.int32)
+            ctx.update(pair=pair, pos=pos, top_k=top_k, tokens=x.shape[0])
+            from torchtitan_b200.ops import cuda_ops
+
+            return cuda_ops.moe_gather_src(x, src, pos, top_k), pc, ctx
+        rows = x.new_zeros(max_rows, x.shape[-1]).index_copy(0, dest, _moe_ops().gather_rows(x, order, top_k))
+        return rows, pc, ctx
 
     def scale_rows(self, rows, scores_sorted, ctx):
         sc = rows.new_zeros(ctx["max_rows"], 1, dtype=torch.float32).index_copy(0, ctx["dest"], scores_sorted.reshape(-1, 1).float())
@@ -86,6 +96,14 @@ class LocalDispatcher:
 
     def combine(self, y, ctx):
         return y if ctx is None else y.index_select(0, ctx["dest"])
+
+    def combine_to_tokens(self, y, weights, ctx):
+        """Fused un-pad + un-sort + weighted sum over the k copies (CUDA bf16 path); None when not applicable."""
+        if ctx is None or "pos" not in ctx or y.dtype != torch.bfloat16:
+            return None
+        from torchtitan_b200.ops import cuda_ops
+
+        return cuda_ops.moe_combine_pos(y, ctx["pos"], ctx["pair"], weights, ctx["tokens"], ctx["top_k"])
 
 
 class GroupedExperts(Module):
@@ -232,11 +250,14 @@ class MoE(Module):
         if self.score_before_experts:
             routed_in = _moe_ops().scale_rows(routed_in, scores_sorted, disp, ctx)
         routed_out = self.experts(routed_in, local_counts)
-        routed_out = disp.combine(routed_out, ctx)
-
-        shared = self.shared_experts(x) if self.shared_experts is not None else None
         weights = None if self.score_before_experts else top_scores
-        out = _moe_ops().scatter_combine(routed_out, order, weights, x.shape[0], k)
+        fused = disp.combine_to_tokens(routed_out, weights, ctx) if hasattr(disp, "combine_to_tokens") else None
+        shared = self.shared_experts(x) if self.shared_experts is not None else None
+        if fused is not None:
+            out = fused
+        else:
+            routed_out = disp.combine(routed_out, ctx)
+            out = _moe_ops().scatter_combine(routed_out, order, weights, x.shape[0], k)
         if shared is not None:
             out = out + shared
         return out.reshape(bs, slen, dim)

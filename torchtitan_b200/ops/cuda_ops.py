@@ -510,12 +510,120 @@ def sumsq(flat: Tensor, out: Tensor | None = None, accumulate: bool = False) -> 
 
 
 # =============================================================================== MoE (see csrc/moe.cu)
-def moe_route(x, gate_w, gate_b, expert_bias, **kw):
-    return ref.moe_route(x, gate_w, gate_b, expert_bias, **kw)
+class _RouteFn(torch.autograd.Function):
+    """scores -> top-k -> (normalised, scaled) weights + histogram, one warp per token (``csrc/moe.cu``)."""
+
+    @staticmethod
+    def forward(ctx, logits, expert_bias, top_k, softmax, norm, scale):
+        T, E = logits.shape
+        top = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        idx = torch.empty(T, top_k, dtype=torch.int64, device=logits.device)
+        counts = torch.zeros(E, dtype=torch.float32, device=logits.device)
+        _ck(_lib().tt_moe_route_fwd(logits.data_ptr(), _p(expert_bias), top.data_ptr(), idx.data_ptr(), counts.data_ptr(), T, E,
+                                    top_k, int(softmax), int(norm), float(scale), _stream()), "tt_moe_route_fwd")
+        ctx.save_for_backward(logits, idx)
+        ctx.cfg = (top_k, softmax, norm, scale)
+        ctx.mark_non_differentiable(idx, counts)
+        return top, idx, counts
+
+    @staticmethod
+    def backward(ctx, gtop, _gi, _gc):
+        logits, idx = ctx.saved_tensors
+        top_k, softmax, norm, scale = ctx.cfg
+        T, E = logits.shape
+        gl = torch.empty_like(logits)
+        _ck(_lib().tt_moe_route_bwd(logits.data_ptr(), idx.data_ptr(), gtop.contiguous().float().data_ptr(), gl.data_ptr(), T, E,
+                                    top_k, int(softmax), int(norm), float(scale), _stream()), "tt_moe_route_bwd")
+        return gl, None, None, None, None, None
+
+
+def moe_route(x, gate_w, gate_b, expert_bias, *, top_k, score_func, route_norm, route_scale, num_expert_groups=None,
+              num_limited_groups=None, force_balance=False):
+    E = gate_w.shape[0]
+    if num_expert_groups is not None or force_balance or E > 256 or top_k > 16 or score_func not in ("softmax", "sigmoid"):
+        return ref.moe_route(x, gate_w, gate_b, expert_bias, top_k=top_k, score_func=score_func, route_norm=route_norm,
+                             route_scale=route_scale, num_expert_groups=num_expert_groups,
+                             num_limited_groups=num_limited_groups, force_balance=force_balance)
+    # the gate product stays in fp32 (library GEMM); everything after it is one kernel
+    logits = torch.nn.functional.linear(x.float(), gate_w.float(), None if gate_b is None else gate_b.float()).contiguous()
+    eb = None if expert_bias is None else expert_bias.float().contiguous()
+    return _RouteFn.apply(logits, eb, top_k, score_func == "softmax", bool(route_norm), float(route_scale))
 
 
 def moe_sort(expert_idx, num_experts: int):
-    return ref.moe_sort(expert_idx, num_experts)
+    """Stable counting sort of the (token, slot) pairs by expert: (order int64 [T*k], counts int64 [E])."""
+    flat = expert_idx.reshape(-1).contiguous()
+    n = flat.numel()
+    counts_f = torch.zeros(num_experts, dtype=torch.float32, device=flat.device)
+    counts_f.index_add_(0, flat, torch.ones(n, dtype=torch.float32, device=flat.device))
+    order = torch.empty(n, dtype=torch.int64, device=flat.device)
+    counts = torch.empty(num_experts, dtype=torch.int64, device=flat.device)
+    _ck(_lib().tt_moe_sort(flat.data_ptr(), counts_f.data_ptr(), order.data_ptr(), counts.data_ptr(), n, num_experts, _stream()),
+        "tt_moe_sort")
+    return order, counts
+
+
+class _GatherSrc(torch.autograd.Function):
+    """out[j] = x[src[j]] (zero row where src < 0); backward sums the k copies of each token through ``pos``."""
+
+    @staticmethod
+    def forward(ctx, x, src, pos, top_k):
+        R, D = src.numel(), x.shape[-1]
+        out = torch.empty(R, D, dtype=x.dtype, device=x.device)
+        _ck(_lib().tt_moe_gather(x.data_ptr(), src.data_ptr(), None, out.data_ptr(), R, D, _stream()), "tt_moe_gather")
+        ctx.save_for_backward(pos)
+        ctx.shape, ctx.k = x.shape, top_k
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (pos,) = ctx.saved_tensors
+        T, D = ctx.shape
+        gx = torch.empty(T, D, dtype=g.dtype, device=g.device)
+        _ck(_lib().tt_moe_combine(g.contiguous().data_ptr(), pos.data_ptr(), None, gx.data_ptr(), T, ctx.k, D, _stream()),
+            "tt_moe_combine")
+        return gx, None, None, None
+
+
+class _CombinePos(torch.autograd.Function):
+    """out[t] = sum_s w[t,s] * rows[pos[t,s]] in fp32; ``pair`` [R] is the inverse map (flat pair index per row, -1 = padding)."""
+
+    @staticmethod
+    def forward(ctx, rows, pos, pair, w, T, top_k):
+        D = rows.shape[-1]
+        out = torch.empty(T, D, dtype=rows.dtype, device=rows.device)
+        wf = None if w is None else w.float().contiguous()
+        _ck(_lib().tt_moe_combine(rows.data_ptr(), pos.data_ptr(), _p(wf), out.data_ptr(), T, top_k, D, _stream()), "tt_moe_combine")
+        ctx.save_for_backward(rows, pos, pair, wf if wf is not None else torch.empty(0, device=rows.device))
+        ctx.has_w, ctx.k = w is not None, top_k
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        rows, pos, pair, wf = ctx.saved_tensors
+        g = g.contiguous()
+        R, D = rows.shape
+        T = g.shape[0]
+        src = torch.where(pair >= 0, pair // ctx.k, pair).to(torch.int32)
+        scale = None
+        if ctx.has_w:
+            scale = torch.where(pair >= 0, wf.reshape(-1)[pair.clamp(min=0).long()], torch.zeros((), device=g.device)).contiguous()
+        grows = torch.empty_like(rows)
+        _ck(_lib().tt_moe_gather(g.data_ptr(), src.data_ptr(), _p(scale), grows.data_ptr(), R, D, _stream()), "tt_moe_gather")
+        gw = None
+        if ctx.has_w and ctx.needs_input_grad[3]:
+            gw = torch.empty(T, ctx.k, dtype=torch.float32, device=g.device)
+            _ck(_lib().tt_moe_rowdot(rows.data_ptr(), pos.data_ptr(), g.data_ptr(), gw.data_ptr(), T, ctx.k, D, _stream()),
+                "tt_moe_rowdot")
+        return grows, None, None, gw, None, None
+
+
+def moe_gather_src(x, src, pos, top_k: int):
+    return _GatherSrc.apply(x.contiguous(), src, pos, top_k)
+
+
+def moe_combine_pos(rows, pos, pair, weights, num_tokens: int, top_k: int):
+    return _CombinePos.apply(rows.contiguous(), pos, pair, weights, num_tokens, top_k)
 
 
 def moe_gather_rows(x, order, top_k: int):

@@ -65,6 +65,12 @@ def lib():
     _sig(L.tt_kv_write, [P, P, P, P, P, LL, I, I, P])
     _sig(L.tt_paged_decode, [P, P, P, P, P, P, F, I, I, I, I, I, I, P])
     _sig(L.tt_sample, [P, P, P, P, I, I, LL, F, I, P])
+    _sig(L.tt_moe_route_fwd, [P, P, P, P, P, I, I, I, I, I, F, P])
+    _sig(L.tt_moe_route_bwd, [P, P, P, P, I, I, I, I, I, F, P])
+    _sig(L.tt_moe_sort, [P, P, P, P, LL, I, P])
+    _sig(L.tt_moe_gather, [P, P, P, P, LL, I, P])
+    _sig(L.tt_moe_combine, [P, P, P, P, LL, I, I, P])
+    _sig(L.tt_moe_rowdot, [P, P, P, P, LL, I, I, P])
     for name, sig in _OPTIONAL.items():
         if hasattr(L, name):
             _sig(getattr(L, name), sig)
