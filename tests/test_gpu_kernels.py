@@ -300,6 +300,31 @@ def test_moe_layer_native_grouped_path(ops):
     assert _rel(xg.grad.cpu(), xr.grad) < 8e-2, _rel(xg.grad.cpu(), xr.grad)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (512, 768, 1024), (300, 264, 208), (4096, 4096, 2048)])
+@pytest.mark.parametrize("mode", ["tensorwise", "rowwise"])
+def test_gemm_fp8(ops, M, N, K, mode):
+    """tcgen05 float8 GEMM with epilogue scales vs the fp32 product of the dequantised operands."""
+    from torchtitan_b200.ops import quant
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda") * 2
+    b = torch.randn(N, K, device="cuda") * 0.3
+    axis = None if mode == "tensorwise" else -1
+    qa, sa = quant.quantize_fp8(a, axis)
+    qb, sb = quant.quantize_fp8(b, axis)
+    got = ops.gemm_fp8(qa, qb, sa, sb, torch.float32)
+    _no_kernel_errors()
+    want = (qa.float() * sa) @ (qb.float() * sb).t()
+    assert _rel(got, want) < 1e-3, _rel(got, want)
+    got16 = ops.gemm_fp8(qa, qb, sa, sb, torch.bfloat16)
+    assert _rel(got16, want) < 1e-2
+    # e5m2 gradients against e4m3 weights
+    qg, sg = quant.quantize_fp8(a, None, torch.float8_e5m2)
+    got = ops.gemm_fp8(qg, qb, sg, sb if mode == "tensorwise" else sb.mean(), torch.float32)
+    want = (qg.float() * sg) @ (qb.float() * (sb if mode == "tensorwise" else sb.mean())).t()
+    assert _rel(got, want) < 1e-3, _rel(got, want)
+
+
 def test_smoke_step():
     from torchtitan_b200.tools.smoke import run_smoke
 

@@ -43,6 +43,14 @@ struct GemmArgs {
   // fused all-gather variant: per n-tile readiness flags (nullptr = plain GEMM)
   const int* ready_flags;
   int ready_value;
+  // 8-bit float operands (e4m3/e5m2, both K-major): `bk` contraction elements per stage (128 instead of 64) and an
+  // epilogue that multiplies by the dequantisation scales: scale_mode 1 = one scale per tensor (pointers to scalars),
+  // 2 = one per row of A and one per row of B (= output column).
+  int fp8;
+  int bk;
+  int scale_mode;
+  const float* scale_a;
+  const float* scale_b;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -59,7 +67,27 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 // Write 32 consecutive accumulator columns of one output row (bf16 or fp32, optional C += ...).
+__device__ __forceinline__ void store_chunk_raw(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]);
+
 __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
+  if (p.scale_mode == 0) { store_chunk_raw(p, row, col, r); return; }
+  uint32_t s[32];
+  const float sa = p.scale_mode == 1 ? __ldg(p.scale_a) : __ldg(p.scale_a + row);
+  if (p.scale_mode == 1) {
+    const float f = sa * __ldg(p.scale_b);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) s[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float sb = (col + j < p.N) ? __ldg(p.scale_b + col + j) : 0.f;
+      s[j] = __float_as_uint(__uint_as_float(r[j]) * sa * sb);
+    }
+  }
+  store_chunk_raw(p, row, col, s);
+}
+
+__device__ __forceinline__ void store_chunk_raw(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
   const bool full_chunk = (col + 32 <= p.N);
         if (p.c_fp32) {
           float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
@@ -189,14 +217,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           tt::mbar_expect_tx(full_bar(s), A_STAGE_BYTES + B_STAGE_BYTES);
           const uint32_t dA = sA + s * A_STAGE_BYTES, dB = sB + s * B_STAGE_BYTES;
           if (!p.a_mn) {
-            tt::tma_load_2d(dA, &tma_a, full_bar(s), k * BK, tm * BM);
+            tt::tma_load_2d(dA, &tma_a, full_bar(s), k * p.bk, tm * BM);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
               tt::tma_load_2d(dA + j * (64 * BK * 2), &tma_a, full_bar(s), tm * BM + j * 64, k * BK);
           }
           if (!p.b_mn) {
-            tt::tma_load_2d(dB, &tma_b, full_bar(s), k * BK, tn * BN);
+            tt::tma_load_2d(dB, &tma_b, full_bar(s), k * p.bk, tn * BN);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -231,7 +259,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t ad = tt::umma_smem_desc(aA + kk * a_kadv, a_lbo, sbo);
             const uint64_t bd = tt::umma_smem_desc(aB + kk * b_kadv, b_lbo, sbo);
-            tt::umma_f16_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+            if (p.fp8) tt::umma_f8_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+            else tt::umma_f16_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
           }
           tt::umma_commit(empty_bar(s));  // frees the stage once these UMMAs have read it
         }
@@ -339,13 +368,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           if (rank == 0) tt::mbar_expect_tx(full_bar(s), 2 * (PA_BYTES + PB_BYTES));
           const uint32_t dA = sA + s * PA_BYTES, dB = sB + s * PB_BYTES;
           if (!p.a_mn) {
-            tt::tma_load_2d_pair(dA, &tma_a, fb, k * BK, m0);
+            tt::tma_load_2d_pair(dA, &tma_a, fb, k * p.bk, m0);
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tt::tma_load_2d_pair(dA + j * (64 * BK * 2), &tma_a, fb, m0 + j * 64, k * BK);
           }
           if (!p.b_mn) {
-            tt::tma_load_2d_pair(dB, &tma_b, fb, k * BK, n0);
+            tt::tma_load_2d_pair(dB, &tma_b, fb, k * p.bk, n0);
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tt::tma_load_2d_pair(dB + j * (64 * BK * 2), &tma_b, fb, n0 + j * 64, k * BK);
@@ -378,7 +407,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t ad = tt::umma_smem_desc(aA + kk * a_kadv, a_lbo, sbo);
             const uint64_t bd = tt::umma_smem_desc(aB + kk * b_kadv, b_lbo, sbo);
-            tt::umma_f16_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+            if (p.fp8) tt::umma_f8_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+            else tt::umma_f16_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
           }
           tt::umma_commit_pair(empty_bar(s), 3);  // frees this stage in both CTAs
         }
@@ -462,6 +492,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate;
   p.ready_flags = ready_flags; p.ready_value = ready_value;
+  p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
@@ -477,6 +508,55 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
     int grid = p.tiles_m * p.tiles_n;
     if (grid > cap) grid = cap;
+    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// C[M,N] = (A[M,K] . B[N,K]^T) * scales with 8-bit float operands (a_e5m2 / b_e5m2 select e5m2 instead of e4m3), both
+// K-major with row strides lda / ldb in elements (multiples of 16), fp32 accumulation, C bf16 or fp32.
+// scale_mode: 0 none, 1 per-tensor (scale_a, scale_b point to one float each), 2 per row of A / per row of B.
+int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                int c_fp32, int a_e5m2, int b_e5m2, const float* scale_a, const float* scale_b, int scale_mode,
+                cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) || (ldb % 16)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (scale_mode && (!scale_a || !scale_b)) return -5;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+  }
+  constexpr int BK8 = 128;  // one 128-byte swizzle row of 8-bit elements
+  const bool use_pair = g_pair_enabled && M >= 256 && N >= 256;
+  CUtensorMap ta, tb;
+  int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, BM, BK8);
+  if (rc) return rc;
+  rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, use_pair ? 128 : BN, BK8);
+  if (rc) return rc;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K;
+  p.k_iters = (K + BK8 - 1) / BK8;
+  p.a_mn = 0; p.b_mn = 0;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
+  p.ready_flags = nullptr; p.ready_value = 0;
+  p.fp8 = 1; p.bk = BK8; p.scale_mode = scale_mode; p.scale_a = scale_a; p.scale_b = scale_b;
+  if (use_pair) {
+    p.tiles_m = (M + pair::TM - 1) / pair::TM;
+    p.tiles_n = (N + pair::TN - 1) / pair::TN;
+    p.idesc = tt::umma_idesc_f8(pair::TM, pair::TN, a_e5m2, b_e5m2);
+    int clusters = p.tiles_m * p.tiles_n;
+    if (clusters > g_num_sms / 2) clusters = g_num_sms / 2;
+    pair::gemm_bf16_pair_kernel<<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+  } else {
+    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_n = (N + BN - 1) / BN;
+    p.idesc = tt::umma_idesc_f8(BM, BN, a_e5m2, b_e5m2);
+    int grid = p.tiles_m * p.tiles_n;
+    if (grid > g_num_sms) grid = g_num_sms;
     gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

@@ -779,3 +779,29 @@ def sample(logits: Tensor, temperature: float, uniforms: Tensor) -> tuple[Tensor
     _ck(_lib().tt_sample(logits.data_ptr(), u.data_ptr(), tok.data_ptr(), lp.data_ptr(), B, V, logits.stride(0), float(temperature),
                          int(logits.dtype == torch.bfloat16), _stream()), "tt_sample")
     return tok, lp
+
+
+# =============================================================================== float8 GEMM (csrc/gemm.cu, kind::f8f6f4)
+def gemm_fp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:
+    """``(qa [M,K] @ qb [N,K]^T) * sa * sb`` with float8 operands; ``sa``/``sb`` are scalars (tensorwise) or hold one
+    scale per row of ``qa`` / ``qb`` (rowwise). fp32 accumulation in TMEM, scales applied in the epilogue."""
+    M, K = qa.shape
+    N = qb.shape[0]
+    if K % 16 or qa.stride(-1) != 1 or qb.stride(-1) != 1:
+        acc = qa.float() @ qb.float().t()
+        return (acc * sa.reshape(-1, 1) * sb.reshape(1, -1)).to(out_dtype)
+    qa, qb = qa.contiguous(), qb.contiguous()
+    mode = 1 if (sa.numel() == 1 and sb.numel() == 1) else 2
+    sa = sa.reshape(-1).float().contiguous()
+    sb = sb.reshape(-1).float().contiguous()
+    if mode == 2:
+        if sa.numel() == 1:
+            sa = sa.expand(M).contiguous()
+        if sb.numel() == 1:
+            sb = sb.expand(N).contiguous()
+    c_fp32 = out_dtype == torch.float32
+    out = torch.empty(M, N, dtype=torch.float32 if c_fp32 else torch.bfloat16, device=qa.device)
+    _ck(_lib().tt_gemm_fp8(qa.data_ptr(), qb.data_ptr(), out.data_ptr(), M, N, K, qa.stride(0), qb.stride(0), out.stride(0),
+                           int(c_fp32), int(qa.dtype == torch.float8_e5m2), int(qb.dtype == torch.float8_e5m2), sa.data_ptr(),
+                           sb.data_ptr(), mode, _stream()), "tt_gemm_fp8")
+    return out if out.dtype == out_dtype else out.to(out_dtype)

@@ -57,7 +57,7 @@ def _fp8_mm(a: torch.Tensor, b_t: torch.Tensor, axis_mode: str, out_dtype, grad:
     qb, sb = quantize_fp8(b_t, axis)
     from . import native
 
-    if a.is_cuda and native.has("tt_gemm_fp8") and a_dtype == torch.float8_e4m3fn:
+    if a.is_cuda and native.has("tt_gemm_fp8"):
         from .cuda_ops import gemm_fp8
 
         return gemm_fp8(qa, qb, sa, sb, out_dtype)

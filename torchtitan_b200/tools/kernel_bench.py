@@ -63,6 +63,25 @@ def bench_gemm(args, timer):
     return res
 
 
+def bench_gemm_fp8(args, timer):
+    """float8 (e4m3, rowwise scales) GEMM through the tcgen05 kind::f8f6f4 path; ``--compare`` adds torch._scaled_mm."""
+    from torchtitan_b200.ops import cuda_ops, quant
+
+    M, N, K = args.m, args.n, args.k
+    qa, sa = quant.quantize_fp8(torch.randn(M, K, device="cuda"), -1)
+    qb, sb = quant.quantize_fp8(torch.randn(N, K, device="cuda"), -1)
+    ms = timer.time(lambda: cuda_ops.gemm_fp8(qa, qb, sa, sb, torch.bfloat16), args.iters)
+    res = {"case": "gemm_fp8_rowwise", "M": M, "N": N, "K": K, "ms": ms, "tflops": 2 * M * N * K / ms / 1e9}
+    if args.compare:
+        f = lambda: torch._scaled_mm(qa, qb.t(), scale_a=sa.float().view(M, 1), scale_b=sb.float().view(1, N), out_dtype=torch.bfloat16)
+        try:
+            ms2 = timer.time(f, args.iters)
+            res.update({"cublaslt_ms": ms2, "cublaslt_tflops": 2 * M * N * K / ms2 / 1e9, "ratio_vs_cublaslt": ms2 / ms})
+        except Exception as e:  # library variant not available for this shape / scaling
+            res["cublaslt_error"] = str(e)[:200]
+    return res
+
+
 def bench_attention(args, timer):
     from torchtitan_b200.ops import cuda_ops
 
@@ -118,7 +137,7 @@ def bench_elementwise(args, timer):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "elementwise"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -139,6 +158,8 @@ def main():
         _n.lib().tt_gemm_set_pair(0)
     if args.what == "gemm":
         res = [bench_gemm(args, timer)]
+    elif args.what == "gemm_fp8":
+        res = [bench_gemm_fp8(args, timer)]
     elif args.what == "attention":
         res = [bench_attention(args, timer)]
     else:
