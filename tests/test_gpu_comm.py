@@ -88,3 +88,35 @@ def test_bounded_wait_reports_missing_flag(L):
         assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
     finally:
         L.tt_comm_set_wait_ns(20_000_000_000)
+
+
+def test_fused_allgather_gemm_single_gpu_emulation(L):
+    """All-gather fused into the GEMM, with the "peers" being local buffers whose flags are already published (so no CTA
+    waits on another launch): remote slices are pulled by the copy CTAs of the same launch while the GEMM CTAs multiply."""
+    torch.manual_seed(0)
+    W, rows_local, K, N = 4, 256, 512, 768
+    M = W * rows_local
+    stream = torch.cuda.current_stream().cuda_stream
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    want = x.float() @ w.float().t()
+    for rank in (0, 2):
+        # rank r's buffer holds only its own slice; the others are garbage until pulled
+        bufs = []
+        for r in range(W):
+            b = torch.full((M, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+            b[r * rows_local : (r + 1) * rows_local] = x[r * rows_local : (r + 1) * rows_local]
+            bufs.append(b)
+        flags = [torch.full((1,), 7, dtype=torch.int32, device="cuda") for _ in range(W)]
+        ready = torch.zeros(M // 128, dtype=torch.int32, device="cuda")
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        p, k1 = _ptr_array(bufs)
+        f, k2 = _ptr_array(flags)
+        rc = L.tt_gemm_allgather_a(p, f, W, rank, 7, w.data_ptr(), out.data_ptr(), M, N, K, 0, K, N, 0, ready.data_ptr(), 1, 8, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert L.tt_gemm_error() == 0
+        assert torch.equal(bufs[rank], x)                       # the gathered operand is complete locally afterwards
+        assert (ready == 1).all()
+        err = (out.float() - want).abs().max() / want.abs().max()
+        assert err < 1e-2, err

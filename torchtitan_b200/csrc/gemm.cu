@@ -43,6 +43,17 @@ struct GemmArgs {
   // fused all-gather variant: per n-tile readiness flags (nullptr = plain GEMM)
   const int* ready_flags;
   int ready_value;
+  // fused all-gather (same launch): the last `copy_ctas` CTAs pull row panels of the gathered operand from the peers'
+  // memory over NVLink into the local buffer and publish one flag per panel; the GEMM CTAs wait for the panel they need.
+  int flags_by_m;       // ready_flags index = m-tile (A operand gathered) instead of n-tile (B operand gathered)
+  int m_rot;            // tiles visit m-panels starting at this offset (the local shard first)
+  int copy_ctas;
+  const void* gather_src[16];  // base of the gathered buffer on every rank (peer-mapped addresses)
+  const int* gather_flag[16];  // rank r's "my slice is written" version flag
+  void* gather_dst;            // local gathered buffer
+  int* panel_ready;            // local flags, one per panel (same array as ready_flags)
+  long long panel_bytes;
+  int panels_per_rank, gather_world, gather_rank, gather_expected;
   // 8-bit float operands (e4m3/e5m2, both K-major): `bk` contraction elements per stage (128 instead of 64) and an
   // epilogue that multiplies by the dequantisation scales: scale_mode 1 = one scale per tensor (pointers to scalars),
   // 2 = one per row of A and one per row of B (= output column).
@@ -67,27 +78,31 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 // Write 32 consecutive accumulator columns of one output row (bf16 or fp32, optional C += ...).
-__device__ __forceinline__ void store_chunk_raw(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]);
-
-__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
-  if (p.scale_mode == 0) { store_chunk_raw(p, row, col, r); return; }
-  uint32_t s[32];
-  const float sa = p.scale_mode == 1 ? __ldg(p.scale_a) : __ldg(p.scale_a + row);
+// 8-bit float GEMMs: multiply the accumulators by the dequantisation scales (in place, before the store).
+// `sa` is the row's scale (times the tensor scale of B in per-tensor mode), loaded once per tile row by the caller.
+__device__ __forceinline__ void apply_scales(const GemmArgs& p, float sa, int col, uint32_t (&r)[32]) {
   if (p.scale_mode == 1) {
-    const float f = sa * __ldg(p.scale_b);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) s[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sa);
+  } else if (col + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.scale_b + col) & 15) == 0) {
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const float4 sb = __ldg(reinterpret_cast<const float4*>(p.scale_b + col) + j4);
+      r[4 * j4 + 0] = __float_as_uint(__uint_as_float(r[4 * j4 + 0]) * sa * sb.x);
+      r[4 * j4 + 1] = __float_as_uint(__uint_as_float(r[4 * j4 + 1]) * sa * sb.y);
+      r[4 * j4 + 2] = __float_as_uint(__uint_as_float(r[4 * j4 + 2]) * sa * sb.z);
+      r[4 * j4 + 3] = __float_as_uint(__uint_as_float(r[4 * j4 + 3]) * sa * sb.w);
+    }
   } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const float sb = (col + j < p.N) ? __ldg(p.scale_b + col + j) : 0.f;
-      s[j] = __float_as_uint(__uint_as_float(r[j]) * sa * sb);
+      r[j] = __float_as_uint(__uint_as_float(r[j]) * sa * sb);
     }
   }
-  store_chunk_raw(p, row, col, s);
 }
 
-__device__ __forceinline__ void store_chunk_raw(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
   const bool full_chunk = (col + 32 <= p.N);
         if (p.c_fp32) {
           float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
@@ -143,6 +158,61 @@ __device__ __forceinline__ void store_chunk_raw(const GemmArgs& p, int row, int 
         }
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Copy role of the fused all-gather GEMM. Copy CTA `c` handles panels c, c + copy_ctas, ... of a list that starts with
+// the owner next to this rank, so that traffic is spread over the peers. A panel of the local slice needs no copy.
+// Plain 16-byte loads from peer memory (no multicast). Bounded waits: on expiry the error word is set and the panel is
+// left unpublished, which makes the consuming GEMM CTAs give up through their own bounded waits.
+__device__ void gather_panels(const GemmArgs& p, int c) {
+  __shared__ int s_ok;
+  const int total = p.panels_per_rank * p.gather_world;
+  for (int i = c; i < total; i += p.copy_ctas) {
+    const int hop = i / p.panels_per_rank;                       // 0 = local slice
+    const int owner = (p.gather_rank + hop) % p.gather_world;
+    const int panel = owner * p.panels_per_rank + i % p.panels_per_rank;
+    if (hop != 0) {
+      if (threadIdx.x == 0) {
+        int ok = 1;
+        const uint64_t t0 = tt::globaltimer_ns();
+        while (ld_acquire_sys(p.gather_flag[owner]) < p.gather_expected) {
+          if (tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) { atomicCAS(&g_gemm_error, 0, 6); ok = 0; break; }
+          __nanosleep(500);
+        }
+        s_ok = ok;
+      }
+      __syncthreads();
+      if (!s_ok) return;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.gather_src[owner]) + panel * p.panel_bytes);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.gather_dst) + panel * p.panel_bytes);
+      const long long n16 = p.panel_bytes / 16;
+      // 4 independent loads in flight per thread
+      long long j = threadIdx.x;
+      for (; j + 3 * NUM_THREADS < n16; j += 4 * NUM_THREADS) {
+        const uint4 a = src[j], b = src[j + NUM_THREADS], cc = src[j + 2 * NUM_THREADS], d = src[j + 3 * NUM_THREADS];
+        dst[j] = a; dst[j + NUM_THREADS] = b; dst[j + 2 * NUM_THREADS] = cc; dst[j + 3 * NUM_THREADS] = d;
+      }
+      for (; j < n16; j += NUM_THREADS) dst[j] = src[j];
+      __threadfence();
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) st_release_gpu(p.panel_ready + panel, p.ready_value);
+  }
+}
+
+template <bool FP8>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -163,6 +233,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const int gemm_ctas = static_cast<int>(gridDim.x) - p.copy_ctas;
+
+  if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
+    gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -192,13 +268,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (tt::elect_one()) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        tm = (tm + p.m_rot) % p.tiles_m;
         if (p.ready_flags != nullptr) {
           // fused all-gather: wait until the copy CTAs have landed this n-tile of B locally
           uint64_t t0 = tt::globaltimer_ns();
-          while (*reinterpret_cast<const volatile int*>(p.ready_flags + tn) < p.ready_value) {
+          while (ld_acquire_gpu(p.ready_flags + (p.flags_by_m ? tm : tn)) < p.ready_value) {
             if (*abort_flag || tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) {
               *abort_flag = 1;
               atomicCAS(&g_gemm_error, 0, 5);
@@ -217,14 +294,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           tt::mbar_expect_tx(full_bar(s), A_STAGE_BYTES + B_STAGE_BYTES);
           const uint32_t dA = sA + s * A_STAGE_BYTES, dB = sB + s * B_STAGE_BYTES;
           if (!p.a_mn) {
-            tt::tma_load_2d(dA, &tma_a, full_bar(s), k * p.bk, tm * BM);
+            tt::tma_load_2d(dA, &tma_a, full_bar(s), k * (FP8 ? 128 : BK), tm * BM);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
               tt::tma_load_2d(dA + j * (64 * BK * 2), &tma_a, full_bar(s), tm * BM + j * 64, k * BK);
           }
           if (!p.b_mn) {
-            tt::tma_load_2d(dB, &tma_b, full_bar(s), k * p.bk, tn * BN);
+            tt::tma_load_2d(dB, &tma_b, full_bar(s), k * (FP8 ? 128 : BK), tn * BN);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -243,7 +320,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t sbo = 1024 >> 4;
       const uint32_t a_kadv = p.a_mn ? (UMMA_K * 128) : (UMMA_K * 2);  // bytes per 16-wide k step
       const uint32_t b_kadv = p.b_mn ? (UMMA_K * 128) : (UMMA_K * 2);
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas, ++tile_it) {
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
         if (!tt::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, &g_gemm_error, 2)) break;
@@ -259,7 +336,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t ad = tt::umma_smem_desc(aA + kk * a_kadv, a_lbo, sbo);
             const uint64_t bd = tt::umma_smem_desc(aB + kk * b_kadv, b_lbo, sbo);
-            if (p.fp8) tt::umma_f8_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+            if constexpr (FP8) tt::umma_f8_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
             else tt::umma_f16_ss(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
           }
           tt::umma_commit(empty_bar(s));  // frees the stage once these UMMAs have read it
@@ -271,9 +348,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------------------------------------ epilogue (TMEM -> registers -> global)
     const int ew = warp - 4;  // TMEM lanes [32*ew, 32*ew+32)
     uint32_t tile_it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_it) {
+    for (int t = blockIdx.x; t < num_tiles; t += gemm_ctas, ++tile_it) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      tm = (tm + p.m_rot) % p.tiles_m;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       if (!tt::mbar_wait(tfull_bar(acc), acc_ph, abort_flag, &g_gemm_error, 4)) break;
@@ -282,6 +360,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
       const bool row_ok = row < p.M;
+      float sa = 1.f;
+      if constexpr (FP8) {
+        if (p.scale_mode == 1) sa = __ldg(p.scale_a) * __ldg(p.scale_b);
+        else if (p.scale_mode == 2 && row_ok) sa = __ldg(p.scale_a + row);
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -289,6 +372,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tt::tc_wait_ld();
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
+        if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
         store_chunk(p, row, col, r);
       }
       tt::tc_fence_before();
@@ -317,6 +401,7 @@ constexpr int PSTAGES = 6;
 constexpr uint32_t PA_BYTES = 128 * BK * 2, PB_BYTES = 128 * BK * 2;  // per CTA per stage
 constexpr size_t PSMEM_BYTES = 1024 + PSTAGES * (PA_BYTES + PB_BYTES) + 256;
 
+template <bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -368,13 +453,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           if (rank == 0) tt::mbar_expect_tx(full_bar(s), 2 * (PA_BYTES + PB_BYTES));
           const uint32_t dA = sA + s * PA_BYTES, dB = sB + s * PB_BYTES;
           if (!p.a_mn) {
-            tt::tma_load_2d_pair(dA, &tma_a, fb, k * p.bk, m0);
+            tt::tma_load_2d_pair(dA, &tma_a, fb, k * (FP8 ? 128 : BK), m0);
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tt::tma_load_2d_pair(dA + j * (64 * BK * 2), &tma_a, fb, m0 + j * 64, k * BK);
           }
           if (!p.b_mn) {
-            tt::tma_load_2d_pair(dB, &tma_b, fb, k * p.bk, n0);
+            tt::tma_load_2d_pair(dB, &tma_b, fb, k * (FP8 ? 128 : BK), n0);
           } else {
 #pragma unroll
             for (int j = 0; j < 2; ++j) tt::tma_load_2d_pair(dB + j * (64 * BK * 2), &tma_b, fb, n0 + j * 64, k * BK);
@@ -407,7 +492,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t ad = tt::umma_smem_desc(aA + kk * a_kadv, a_lbo, sbo);
             const uint64_t bd = tt::umma_smem_desc(aB + kk * b_kadv, b_lbo, sbo);
-            if (p.fp8) tt::umma_f8_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
+            if constexpr (FP8) tt::umma_f8_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
             else tt::umma_f16_ss_pair(d_tmem, ad, bd, p.idesc, (k | kk) != 0);
           }
           tt::umma_commit_pair(empty_bar(s), 3);  // frees this stage in both CTAs
@@ -431,6 +516,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       const int n0 = tn * TN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * TN;
       const bool row_ok = row < p.M;
+      float sa = 1.f;
+      if constexpr (FP8) {
+        if (p.scale_mode == 1) sa = __ldg(p.scale_a) * __ldg(p.scale_b);
+        else if (p.scale_mode == 2 && row_ok) sa = __ldg(p.scale_a + row);
+      }
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         uint32_t r[32];
@@ -438,6 +528,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         tt::tc_wait_ld();
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
+        if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
         store_chunk(p, row, col, r);
       }
       tt::tc_fence_before();
@@ -456,6 +547,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 int g_num_sms = 0;
 bool g_pair_enabled = true;
 
+void set_kernel_attrs() {
+  cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+  cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+  cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+  cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+}
+
 }  // namespace
 
 extern "C" {
@@ -472,8 +570,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
-    cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+    set_kernel_attrs();
   }
   // CTA-pair kernel for everything large enough to fill 256x256 tiles (no fused-gather flags there)
   const bool use_pair = g_pair_enabled && ready_flags == nullptr && M >= 256 && N >= 256;
@@ -493,6 +590,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate;
   p.ready_flags = ready_flags; p.ready_value = ready_value;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
+  p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr;
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
@@ -501,14 +599,14 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     int clusters = p.tiles_m * p.tiles_n;
     if (clusters > cap / 2) clusters = cap / 2;
     if (clusters < 1) clusters = 1;
-    pair::gemm_bf16_pair_kernel<<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+    pair::gemm_bf16_pair_kernel<false><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
     int grid = p.tiles_m * p.tiles_n;
     if (grid > cap) grid = cap;
-    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -527,8 +625,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
-    cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+    set_kernel_attrs();
   }
   constexpr int BK8 = 128;  // one 128-byte swizzle row of 8-bit elements
   const bool use_pair = g_pair_enabled && M >= 256 && N >= 256;
@@ -544,21 +641,75 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
   p.ready_flags = nullptr; p.ready_value = 0;
   p.fp8 = 1; p.bk = BK8; p.scale_mode = scale_mode; p.scale_a = scale_a; p.scale_b = scale_b;
+  p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_f8(pair::TM, pair::TN, a_e5m2, b_e5m2);
     int clusters = p.tiles_m * p.tiles_n;
     if (clusters > g_num_sms / 2) clusters = g_num_sms / 2;
-    pair::gemm_bf16_pair_kernel<<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+    pair::gemm_bf16_pair_kernel<true><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = (M + BM - 1) / BM;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_f8(BM, BN, a_e5m2, b_e5m2);
     int grid = p.tiles_m * p.tiles_n;
     if (grid > g_num_sms) grid = g_num_sms;
-    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    gemm_bf16_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Fused all-gather -> GEMM for sequence/tensor parallel: C[M,N] = A_full[M,K] . B[N,K]^T (or B stored [K,N] with b_mn)
+// where A_full is the concatenation over `world` ranks of row slices of M/world rows. Every rank keeps a buffer of the
+// full size at the same offset of its symmetric heap and has written its own slice; `peer_bufs[r]` is that buffer on rank
+// r as mapped here, `peer_flags[r]` the version flag rank r sets once its slice is complete (>= expected).
+// One launch: `copy_ctas` CTAs pull the remote slices panel by panel (128 rows) into `peer_bufs[rank]` while the
+// remaining CTAs multiply, starting with the local panels; a tile waits only for its own panel.
+// `panel_ready` is a local int array with M/128 entries; pass a `ready_value` larger than any used before.
+int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_flags, int world, int rank, int expected,
+                        const void* B, void* C, int M, int N, int K, int b_mn, long long ldb, long long ldc, int c_fp32,
+                        int* panel_ready, int ready_value, int copy_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > 16 || rank < 0 || rank >= world) return -6;
+  if (M % (world * BM) || (K % 8) || (ldb % 8)) return -2;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    set_kernel_attrs();
+  }
+  void* A = const_cast<void*>(peer_bufs[rank]);
+  CUtensorMap ta, tb;
+  int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, BM, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
+  else       rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K;
+  p.k_iters = (K + BK - 1) / BK;
+  p.a_mn = 0; p.b_mn = b_mn;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
+  p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
+  p.ready_flags = panel_ready; p.ready_value = ready_value; p.panel_ready = panel_ready;
+  p.flags_by_m = 1;
+  p.panels_per_rank = M / BM / world;
+  p.m_rot = rank * p.panels_per_rank;
+  p.gather_world = world; p.gather_rank = rank; p.gather_expected = expected;
+  p.gather_dst = A;
+  p.panel_bytes = static_cast<long long>(BM) * K * 2;
+  for (int r = 0; r < 16; ++r) { p.gather_src[r] = r < world ? peer_bufs[r] : nullptr; p.gather_flag[r] = r < world ? peer_flags[r] : nullptr; }
+  if (copy_ctas < 1) copy_ctas = 1;
+  if (copy_ctas > g_num_sms / 2) copy_ctas = g_num_sms / 2;
+  p.copy_ctas = world > 1 ? copy_ctas : 1;
+  int gemm_ctas = p.tiles_m * p.tiles_n;
+  if (gemm_ctas > g_num_sms - p.copy_ctas) gemm_ctas = g_num_sms - p.copy_ctas;
+  // all CTAs must be co-resident (GEMM CTAs wait on flags written by copy CTAs): one CTA per SM, grid <= SM count
+  gemm_bf16_kernel<false><<<gemm_ctas + p.copy_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

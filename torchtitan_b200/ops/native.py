@@ -72,6 +72,7 @@ def lib():
     _sig(L.tt_moe_combine, [P, P, P, P, LL, I, I, P])
     _sig(L.tt_moe_rowdot, [P, P, P, P, LL, I, I, P])
     _sig(L.tt_gemm_fp8, [P, P, P, I, I, I, LL, LL, LL, I, I, I, P, P, I, P])
+    _sig(L.tt_gemm_allgather_a, [P, P, I, I, I, P, P, I, I, I, I, LL, LL, I, P, I, I, P])
     for name, sig in _OPTIONAL.items():
         if hasattr(L, name):
             _sig(getattr(L, name), sig)

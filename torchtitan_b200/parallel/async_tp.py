@@ -1,0 +1,168 @@
+"""Asynchronous tensor parallel: the sequence all-gather fused into the GEMM that consumes it.
+
+Reference behaviour (``enable_async_tensor_parallel``, torchtitan/distributed/tensor_parallel.py:202 -> the
+symmetric-memory micro-pipeline of upstream PyTorch): decompose all-gather -> matmul into chunks so transfers hide
+behind the math. Here it is one kernel (``tt_gemm_allgather_a`` in ``csrc/gemm.cu``): every rank keeps the gathered
+activation buffer in its NVLink-mapped symmetric heap and writes its own sequence slice there; in the fused launch a few
+CTAs pull the peers' slices panel by panel (128 rows) with plain peer loads while the other CTAs run the tcgen05 GEMM,
+local panels first, each output tile waiting only for the panel it reads. The gathered activation stays in the local
+buffer, so the other projections of the block (``w3`` next to ``w1``) read it without another collective.
+
+Buffers are double-buffered per shape and versioned by a job-wide call counter; a rank overwrites a slice only after it
+has seen the peers' flags of the following version, which they publish after their own fused kernel finished reading.
+
+Backward uses the collective path (sequence all-gather for the weight gradient, reduce-scatter for the input gradient).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from torchtitan_b200.ops import native
+from torchtitan_b200.tools.logging import logger
+
+from .nvlink_comm import _PP, SymmetricHeap, _stream
+
+
+class AsyncTP:
+    COPY_CTAS = 16
+
+    def __init__(self, tp_mesh, heap_bytes: int = 1 << 30):
+        self.group = tp_mesh.get_group()
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.heap = SymmetricHeap(self.group, heap_bytes, self.device)
+        self.world, self.rank = self.heap.world, self.heap.rank
+        self.flag_off = self.heap.alloc_flag()
+        self._flag_ptrs, self._flag_keep = self.heap.peer_ptrs(self.flag_off)
+        self._bufs: dict[tuple[int, int], list] = {}
+        self.version = 0
+        self.panel_ready = torch.zeros(4096, dtype=torch.int32, device=self.device)
+        self.fused_calls = 0
+
+    @classmethod
+    def maybe_create(cls, tp_mesh):
+        if not native.available() or not native.has("tt_gemm_allgather_a"):
+            return None
+        W = tp_mesh.size()
+        me = torch.cuda.current_device()
+        ok = 2 <= W <= 16 and torch.cuda.device_count() >= W and all(
+            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=tp_mesh.get_group())
+        if int(flag.item()) == 0:
+            return None
+        return cls(tp_mesh)
+
+    # ---- buffers --------------------------------------------------------------------------------------------
+    def _buffers(self, rows: int, K: int):
+        key = (rows, K)
+        if key not in self._bufs:
+            out = []
+            for _ in range(2):
+                off = self.heap.alloc(rows * K * 2, align=1024)
+                ptrs, keep = self.heap.peer_ptrs(off)
+                out.append((off, ptrs, keep, self.heap.local_tensor(off, rows * K, torch.bfloat16).view(rows, K)))
+            self._bufs[key] = out
+        return self._bufs[key]
+
+    def supported(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
+        rows_local = x.numel() // x.shape[-1]
+        return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] == 1
+                and rows_local % 128 == 0 and x.shape[-1] % 8 == 0 and rows_local * self.world // 128 <= self.panel_ready.numel())
+
+    def ag_linear(self, x: torch.Tensor, weight: torch.Tensor):
+        """``x`` [1, S/tp, K] (this rank's sequence slice), ``weight`` [N, K] -> (gathered x [1, S, K], x_full @ weight^T)."""
+        return _AgLinear.apply(x, weight, self)
+
+    def _forward(self, x: torch.Tensor, weight: torch.Tensor):
+        L = native.lib()
+        K = x.shape[-1]
+        rows_local = x.numel() // K
+        rows = rows_local * self.world
+        N = weight.shape[0]
+        self.version += 1
+        off, ptrs, _keep, full = self._buffers(rows, K)[self.version % 2]
+        full[self.rank * rows_local : (self.rank + 1) * rows_local].copy_(x.reshape(rows_local, K))
+        native.check(L.tt_set_flag(self.heap.base + self.flag_off, self.version, _stream()), "tt_set_flag")
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
+        w = weight.contiguous()
+        native.check(L.tt_gemm_allgather_a(ptrs, ctypes.cast(self._flag_ptrs, _PP), self.world, self.rank, self.version,
+                                           w.data_ptr(), out.data_ptr(), rows, N, K, 0, w.stride(0), out.stride(0), 0,
+                                           self.panel_ready.data_ptr(), self.version, self.COPY_CTAS, _stream()),
+                     "tt_gemm_allgather_a")
+        self.fused_calls += 1
+        return full.view(1, rows, K), out.view(1, rows, N)
+
+    # ---- module hooks used by the tensor-parallel plan ---------------------------------------------------------
+    def attach_ffn(self, ff) -> None:
+        ff._async_tp = self
+
+    def attach_attention(self, att) -> None:
+        att._async_tp = None  # attention projections take the collective path
+
+
+class _AgLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, atp: AsyncTP):
+        xg, y = atp._forward(x, weight)
+        ctx.save_for_backward(x, weight)
+        ctx.atp = atp
+        ctx.mark_non_differentiable(xg)
+        # the gathered buffer is recycled two calls later: hand out a view for immediate consumers only
+        return xg, y
+
+    @staticmethod
+    def backward(ctx, _gxg, gy):
+        from .tp import all_gather_seq
+
+        x, weight = ctx.saved_tensors
+        group = ctx.atp.group
+        W = ctx.atp.world
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        gx_full = gy2 @ weight                                   # [S, K]
+        gx = torch.empty(gx_full.shape[0] // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
+        dist.reduce_scatter_tensor(gx, gx_full.contiguous(), group=group)
+        xg = all_gather_seq(x.detach(), group).reshape(-1, x.shape[-1])
+        gw = gy2.t() @ xg
+        return gx.view_as(x), gw, None
+
+
+def fused_ffn_forward(ff, x_local, group):
+    """SwiGLU feed-forward under sequence parallel with the all-gather fused into ``w1``; returns the partial-sum output
+    [1, S, D] (the caller reduce-scatters it)."""
+    from torchtitan_b200 import ops
+
+    atp: AsyncTP = ff._async_tp
+    xg, h1 = atp.ag_linear(x_local, ff.w1.weight)
+    # w3 must use xg before the buffer is recycled; it is consumed right here. For backward it re-gathers (collective).
+    h3 = _LinearOnGathered.apply(xg, x_local, ff.w3.weight, group)
+    return ff.w2(ops.swiglu(h1, h3))
+
+
+class _LinearOnGathered(torch.autograd.Function):
+    """``xg @ w^T`` where ``xg`` is a transient gathered copy of the sequence-sharded ``x``: saves only the shard."""
+
+    @staticmethod
+    def forward(ctx, xg, x_local, weight, group):
+        from torchtitan_b200 import ops
+
+        ctx.save_for_backward(x_local, weight)
+        ctx.group = group
+        with torch.no_grad():
+            return ops.linear(xg, weight, None)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from .tp import all_gather_seq
+
+        x, weight = ctx.saved_tensors
+        W = dist.get_world_size(ctx.group)
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        gx_full = gy2 @ weight
+        gx = torch.empty(gx_full.shape[0] // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
+        dist.reduce_scatter_tensor(gx, gx_full.contiguous(), group=ctx.group)
+        xg = all_gather_seq(x.detach(), ctx.group).reshape(-1, x.shape[-1])
+        return None, gx.view_as(x), gy2.t() @ xg, None

@@ -344,9 +344,19 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
             _shard_param(ff.w1, "weight", 0, r, W, group, tp_mesh)
             _shard_param(ff.w3, "weight", 0, r, W, group, tp_mesh)
             _shard_param(ff.w2, "weight", 1, r, W, group, tp_mesh)
-            _wrap(ff, lambda inner, x, *a, **k: _scatter(inner(_gather(x, group), *a, **k), group))
             if fused is not None:
                 fused.attach_ffn(ff)
+
+                def ffn_forward(inner, x, _ff=ff):
+                    if _ff._async_tp.supported(x, _ff.w1.weight):
+                        from .async_tp import fused_ffn_forward
+
+                        return _scatter(fused_ffn_forward(_ff, x, group), group)
+                    return _scatter(inner(_gather(x, group)), group)
+
+                _wrap(ff, ffn_forward)
+            else:
+                _wrap(ff, lambda inner, x, *a, **k: _scatter(inner(_gather(x, group), *a, **k), group))
         for nm in ("attention_norm", "ffn_norm"):
             if getattr(block, nm, None) is not None:
                 _mark_replicated(getattr(block, nm), group, tp_mesh)
