@@ -144,3 +144,45 @@ def test_colocated_grpo_two_steps(tmp_path):
     assert hist[-1]["policy_version"] == 2 and rl.generator.policy_version == 2
     assert not torch.equal(w0, rl.generator.model.output.weight)   # weights reached the generator
     assert torch.equal(rl.generator.model.output.weight, rl.trainer.model.output.weight.to(w0.dtype))
+
+
+def _disagg_worker(rank, world):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.experiments.rl.config_registry import rl_grpo_qwen3_debug
+    from torchtitan_b200.experiments.rl.simple_grpo_sum_digits import RLTrainer
+
+    cfg = rl_grpo_qwen3_debug()
+    cfg.model_spec = _debug_spec()
+    cfg.num_steps, cfg.num_episodes_per_step, cfg.eval_samples = 2, 2, 2
+    cfg.generator.num_samples_per_prompt = 2
+    cfg.generator.sampling.max_tokens = 5
+    cfg.generator.max_kv_blocks = 512
+    cfg.generator.seed = rank
+    cfg.trainer.training.dtype = "float32"
+    cfg.async_mode = True
+    cfg.hf_assets_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "assets", "tokenizer")
+    rl = RLTrainer(cfg)
+    rl.setup(device="cpu")
+    hist = rl.train()
+    out = {"steps": len(hist), "version": hist[-1]["policy_version"], "is_trainer": rl.trainer is not None,
+           "is_generator": rl.generator is not None, "sync_s": hist[-1]["weight_sync_s"]}
+    if rl.generator is not None:
+        out["gen_version"] = rl.generator.policy_version
+        out["w"] = rl.generator.model.output.weight.detach().clone()
+    if rl.trainer is not None:
+        out["w"] = rl.trainer.model.output.weight.detach().clone()
+    return out
+
+
+def test_disaggregated_async_grpo_three_ranks(tmp_path):
+    """1 trainer rank + 2 generator replicas over gloo: episodes are gathered, weights reach every replica."""
+    from dist_utils import run_ranks
+
+    res = run_ranks(_disagg_worker, 3, tmp_path=tmp_path)
+    assert res[0]["is_trainer"] and not res[0]["is_generator"]
+    assert all(r["is_generator"] and not r["is_trainer"] for r in res[1:])
+    assert all(r["steps"] == 2 and r["version"] == 2 for r in res)
+    for r in res[1:]:
+        assert r["gen_version"] == 2 and torch.equal(r["w"], res[0]["w"])

@@ -35,7 +35,7 @@ from .grader import Grader, group_mean_advantages
 from .sum_digits import SumDigitsTask, extract_answer
 from .trainer import PolicyTrainer
 from .types import Episode
-from .weight_sync import ParamArena, broadcast_arena, sync_local
+from .weight_sync import ParamArena, build_bare_model, full_tensor, sync_local
 
 
 class Provisioner:
@@ -122,26 +122,40 @@ class RLTrainer(Configurable):
         if self.is_trainer:
             self.trainer = PolicyTrainer(c.trainer, model_spec=c.model_spec, batch_invariant_mode=c.batch_invariant_mode,
                                          hf_assets_path=c.hf_assets_path, device=device, group=self.trainer_group)
-        if self.is_generator or (not self.colocated and rank == 0):
-            # trainer rank 0 keeps a generator-layout arena as the broadcast source
+        if self.is_generator:
             self.generator = Generator(c.generator, model_spec=c.model_spec, model_path=c.hf_assets_path,
                                        batch_invariant_mode=c.batch_invariant_mode, tokenizer=self.tokenizer, device=device)
             self.arena = ParamArena(self.generator.model)
             self.generator.arena = self.arena
+        elif rank == 0:
+            # the first trainer rank stages the generator-layout arena that is broadcast to the replicas
+            self.arena = ParamArena(build_bare_model(c.model_spec, c.generator.model_dtype, device), double_buffer=False)
         self.grader = Grader(self.task.reward_function)
         self._sync_weights(0)
 
     def _sync_weights(self, version: int) -> None:
+        """Trainer -> generator weights. Returns the time spent (seconds, host clock around a device sync)."""
+        t0 = time.perf_counter()
         if self.colocated:
             sync_local(self.trainer.model, self.arena)
         else:
+            rank = dist.get_rank()
+            if self.trainer is not None:
+                # every trainer rank takes part in un-sharding (collectives inside the trainer group); rank 0 keeps the result
+                dst = self.arena.staging() if rank == 0 else None
+                with torch.no_grad():
+                    for name, p in self.trainer.model.named_parameters():
+                        t = full_tensor(p)
+                        if dst is not None and name in dst:
+                            dst[name].copy_(t)
             if self.arena is not None:
-                src_model = self.trainer.model if (self.trainer is not None and dist.get_rank() == 0) else None
-                if self.trainer is not None and dist.get_rank() != 0:
-                    return
-                broadcast_arena(self.arena, src=0, group=self.sync_group, trainer_model=src_model)
+                dist.broadcast(self.arena.halves[self.arena.inactive], src=0, group=self.sync_group)
+                self.arena.flip()
         if self.generator is not None:
             self.generator.update(version)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.last_sync_s = time.perf_counter() - t0
 
     # ---- rollouts across generator replicas -------------------------------------------------------------------
     def _rollout(self, prompts: list[str], answers: list[str]) -> list[Episode]:
@@ -208,7 +222,7 @@ class RLTrainer(Configurable):
             dt = time.perf_counter() - t0
             lens = [len(e.token_ids) for e in episodes]
             n_ok = sum(1 for e in episodes if e.reward > 0)
-            metrics.update(step=step, time_s=dt, avg_tokens=sum(lens) / max(1, len(lens)), correct=n_ok, total=len(episodes),
+            metrics.update(step=step, time_s=dt, weight_sync_s=getattr(self, "last_sync_s", 0.0), avg_tokens=sum(lens) / max(1, len(lens)), correct=n_ok, total=len(episodes),
                            gen_tokens_per_s=sum(lens) / dt)
             self.history.append(metrics)
             logger.info(

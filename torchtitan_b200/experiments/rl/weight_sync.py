@@ -34,6 +34,28 @@ def full_tensor(p: torch.Tensor) -> torch.Tensor:
     return t
 
 
+def build_bare_model(model_spec, dtype_name: str, device) -> nn.Module:
+    """An uninitialised model in the generator's dtype and layout (no engine, no KV cache): the staging side of a sync."""
+    from torchtitan_b200.config import TORCH_DTYPE_MAP
+
+    device = torch.device(device) if device is not None else torch.device(
+        f"cuda:{torch.cuda.current_device()}" if torch.cuda.is_available() else "cpu")
+    dtype = TORCH_DTYPE_MAP[dtype_name] if device.type == "cuda" else torch.float32
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        with torch.device("meta"):
+            model = model_spec.model.build()
+    finally:
+        torch.set_default_dtype(old)
+    model.to_empty(device=device)
+    with torch.no_grad():
+        model.init_weights(buffer_device=device)     # also restores parameter tying, so both sides agree on the layout
+    for p in model.parameters():
+        p.requires_grad_(False)
+    return model
+
+
 class ParamArena:
     """All parameters of ``model`` re-seated as views of one flat buffer (two halves when double-buffered)."""
 
@@ -53,6 +75,7 @@ class ParamArena:
         with torch.no_grad():
             for (_, p), o in zip(params, self.offsets):
                 self.halves[0][o : o + p.numel()].copy_(p.reshape(-1))
+        # tied parameters (one tensor under two names) appear once in named_parameters and stay tied after re-seating
         self._seat(0)
 
     def _views(self, half: int):
