@@ -93,8 +93,12 @@ def test_bounded_wait_reports_missing_flag(L):
 def test_fused_allgather_gemm_single_gpu_emulation(L):
     """All-gather fused into the GEMM, with the "peers" being local buffers whose flags are already published (so no CTA
     waits on another launch): remote slices are pulled by the copy CTAs of the same launch while the GEMM CTAs multiply."""
+    _fused_case(L, 4, 256, 512, 768)      # whole 256-row tiles per rank: CTA-pair kernel
+    _fused_case(L, 4, 128, 320, 264)      # single-CTA tile kernel, ragged N and K
+
+
+def _fused_case(L, W, rows_local, K, N):
     torch.manual_seed(0)
-    W, rows_local, K, N = 4, 256, 512, 768
     M = W * rows_local
     stream = torch.cuda.current_stream().cuda_stream
     x = torch.randn(M, K, device="cuda").bfloat16()

@@ -273,3 +273,89 @@ int tt_comm_error(int* out4) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------ RL weight sync
+// Trainer -> generator replicas: every trainer rank casts the fp32 master shards it owns to bf16 and stores them straight
+// into the parameter arenas of all generator replicas (peer-mapped), following a precomputed list of contiguous
+// segments. One launch per sync per trainer rank; the arena version flag is published afterwards (tt_set_flag on the
+// peer-mapped flag), and a generator waits for all trainer flags (tt_wait_flags, bounded) before it swaps arenas.
+// Counterpart of get_weights (full tensors) + RPC + set_model_state_dict in the reference
+// (torchtitan/experiments/rl/unified/actors/trainer.py:226-239, actors/generator.py:307-335).
+namespace {
+
+struct PushSeg {
+  const float* src;     // fp32 source (this rank's shard of one parameter)
+  long long dst_off;    // element offset in the bf16 arena
+  long long n;          // elements
+};
+
+struct Arenas {
+  __nv_bfloat16* base[kMaxPeers];
+  int count;
+};
+
+__global__ void __launch_bounds__(256) push_cast_kernel(const PushSeg* __restrict__ segs, int nseg, Arenas dst) {
+  // grid.y = segment, grid.x = blocks striding over the segment in 8-element (16-byte bf16) chunks
+  for (int s = blockIdx.y; s < nseg; s += gridDim.y) {
+    const PushSeg sg = segs[s];
+    const bool vec = ((sg.dst_off & 7) == 0) && ((reinterpret_cast<uintptr_t>(sg.src) & 15) == 0);
+    if (vec) {
+      const long long n8 = sg.n / 8;
+      for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+           i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const float4 a = reinterpret_cast<const float4*>(sg.src)[2 * i];
+        const float4 b = reinterpret_cast<const float4*>(sg.src)[2 * i + 1];
+        uint4 v;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+        h[0] = __floats2bfloat162_rn(a.x, a.y); h[1] = __floats2bfloat162_rn(a.z, a.w);
+        h[2] = __floats2bfloat162_rn(b.x, b.y); h[3] = __floats2bfloat162_rn(b.z, b.w);
+        for (int g = 0; g < dst.count; ++g) reinterpret_cast<uint4*>(dst.base[g] + sg.dst_off)[i] = v;
+      }
+      if (blockIdx.x == 0 && threadIdx.x < (sg.n & 7)) {
+        const long long i = n8 * 8 + threadIdx.x;
+        const __nv_bfloat16 v = __float2bfloat16(sg.src[i]);
+        for (int g = 0; g < dst.count; ++g) dst.base[g][sg.dst_off + i] = v;
+      }
+    } else {
+      for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < sg.n;
+           i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const __nv_bfloat16 v = __float2bfloat16(sg.src[i]);
+        for (int g = 0; g < dst.count; ++g) dst.base[g][sg.dst_off + i] = v;
+      }
+    }
+  }
+}
+
+__global__ void wait_flags_kernel(Peers peers, int n, int expected) {
+  __shared__ int ok;
+  wait_peers(peers, n, expected, &ok);
+}
+
+}  // namespace
+
+extern "C" {
+
+// segs: device array of {const float* src, long long dst_off, long long n}; arenas: host array of peer-mapped bf16 arena
+// base pointers (one per generator replica).
+int tt_push_cast(const void* segs, int nseg, void* const* arenas, int n_arenas, cudaStream_t st) {
+  if (nseg <= 0 || n_arenas <= 0) return 0;
+  if (n_arenas > kMaxPeers) return -2;
+  Arenas a;
+  a.count = n_arenas;
+  for (int i = 0; i < kMaxPeers; ++i) a.base[i] = i < n_arenas ? static_cast<__nv_bfloat16*>(arenas[i]) : nullptr;
+  dim3 grid(32, nseg < 1024 ? nseg : 1024);
+  push_cast_kernel<<<grid, 256, 0, st>>>(static_cast<const PushSeg*>(segs), nseg, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Stream-ordered bounded wait until every flag >= expected (error word set on expiry, see tt_comm_error).
+int tt_wait_flags(const int* const* flags, int n, int expected, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (n > kMaxPeers) return -2;
+  Peers p;
+  for (int i = 0; i < kMaxPeers; ++i) { p.ptr[i] = nullptr; p.flag[i] = i < n ? flags[i] : nullptr; }
+  wait_flags_kernel<<<1, 32, 0, st>>>(p, n, expected);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // extern "C"

@@ -174,41 +174,65 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
 
 // Copy role of the fused all-gather GEMM. Copy CTA `c` handles panels c, c + copy_ctas, ... of a list that starts with
 // the owner next to this rank, so that traffic is spread over the peers. A panel of the local slice needs no copy.
-// Plain 16-byte loads from peer memory (no multicast). Bounded waits: on expiry the error word is set and the panel is
-// left unpublished, which makes the consuming GEMM CTAs give up through their own bounded waits.
-__device__ void gather_panels(const GemmArgs& p, int c) {
-  __shared__ int s_ok;
+// One thread drives a ring of bulk copies through shared memory (peer memory -> smem -> local memory, GATHER_BUFS chunks
+// of GATHER_CHUNK bytes in flight), which keeps far more bytes in flight per SM than register copies; plain (non-
+// multicast) bulk loads. Bounded waits: on expiry the error word is set and the panel is left unpublished, which makes
+// the consuming GEMM CTAs give up through their own bounded waits.
+constexpr uint32_t GATHER_CHUNK = 32768;
+constexpr int GATHER_BUFS = 5;   // 160 KB of the CTA's dynamic shared memory (+ barriers)
+
+__device__ void gather_panels(const GemmArgs& p, int c, uint8_t* smem_raw) {
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + GATHER_BUFS * GATHER_CHUNK;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  if (threadIdx.x != 0) return;           // a single thread issues everything
+  for (int i = 0; i < GATHER_BUFS; ++i) tt::mbar_init(bar(i), 1);
+  tt::mbar_fence_init();
+  int abort_local = 0;
+  uint32_t issued = 0;                    // chunks issued so far (ring position / phase)
   const int total = p.panels_per_rank * p.gather_world;
+  const uint32_t chunks = static_cast<uint32_t>((p.panel_bytes + GATHER_CHUNK - 1) / GATHER_CHUNK);
   for (int i = c; i < total; i += p.copy_ctas) {
     const int hop = i / p.panels_per_rank;                       // 0 = local slice
     const int owner = (p.gather_rank + hop) % p.gather_world;
     const int panel = owner * p.panels_per_rank + i % p.panels_per_rank;
     if (hop != 0) {
-      if (threadIdx.x == 0) {
-        int ok = 1;
-        const uint64_t t0 = tt::globaltimer_ns();
-        while (ld_acquire_sys(p.gather_flag[owner]) < p.gather_expected) {
-          if (tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) { atomicCAS(&g_gemm_error, 0, 6); ok = 0; break; }
-          __nanosleep(500);
+      const uint64_t t0 = tt::globaltimer_ns();
+      while (ld_acquire_sys(p.gather_flag[owner]) < p.gather_expected) {
+        if (tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) { atomicCAS(&g_gemm_error, 0, 6); return; }
+        __nanosleep(500);
+      }
+      const uint8_t* src = static_cast<const uint8_t*>(p.gather_src[owner]) + panel * p.panel_bytes;
+      uint8_t* dst = static_cast<uint8_t*>(p.gather_dst) + panel * p.panel_bytes;
+      // software pipeline: loads run GATHER_BUFS - 1 chunks ahead of the stores
+      uint32_t loaded = 0, stored = 0;
+      const uint32_t first = issued;
+      while (stored < chunks) {
+        while (loaded < chunks && loaded - stored < GATHER_BUFS) {
+          const uint32_t slot = (first + loaded) % GATHER_BUFS;
+          // the bulk store that last read this slot must have finished reading shared memory
+          if (first + loaded >= GATHER_BUFS) tt::bulk_store_wait_read<GATHER_BUFS - 1>();
+          const long long off = static_cast<long long>(loaded) * GATHER_CHUNK;
+          const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(GATHER_CHUNK), p.panel_bytes - off));
+          tt::mbar_expect_tx(bar(slot), bytes);
+          tt::bulk_load(base + slot * GATHER_CHUNK, src + off, bytes, bar(slot));
+          ++loaded;
         }
-        s_ok = ok;
+        const uint32_t slot = (first + stored) % GATHER_BUFS;
+        const uint32_t ph = ((first + stored) / GATHER_BUFS) & 1;
+        if (!tt::mbar_wait(bar(slot), ph, &abort_local, &g_gemm_error, 7)) return;
+        const long long off = static_cast<long long>(stored) * GATHER_CHUNK;
+        const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(GATHER_CHUNK), p.panel_bytes - off));
+        tt::fence_proxy_async();
+        tt::bulk_store(dst + off, base + slot * GATHER_CHUNK, bytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        ++stored;
       }
-      __syncthreads();
-      if (!s_ok) return;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.gather_src[owner]) + panel * p.panel_bytes);
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.gather_dst) + panel * p.panel_bytes);
-      const long long n16 = p.panel_bytes / 16;
-      // 4 independent loads in flight per thread
-      long long j = threadIdx.x;
-      for (; j + 3 * NUM_THREADS < n16; j += 4 * NUM_THREADS) {
-        const uint4 a = src[j], b = src[j + NUM_THREADS], cc = src[j + 2 * NUM_THREADS], d = src[j + 3 * NUM_THREADS];
-        dst[j] = a; dst[j + NUM_THREADS] = b; dst[j + 2 * NUM_THREADS] = cc; dst[j + 3 * NUM_THREADS] = d;
-      }
-      for (; j < n16; j += NUM_THREADS) dst[j] = src[j];
+      issued = first + chunks;
+      tt::bulk_store_wait_all();          // writes of this panel are complete before it is published
       __threadfence();
-      __syncthreads();
     }
-    if (threadIdx.x == 0) st_release_gpu(p.panel_ready + panel, p.ready_value);
+    st_release_gpu(p.panel_ready + panel, p.ready_value);
   }
 }
 
@@ -236,7 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int gemm_ctas = static_cast<int>(gridDim.x) - p.copy_ctas;
 
   if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-    gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+    gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
     return;
   }
 
@@ -420,7 +444,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = tt::cluster_ctarank();  // 0 = leader
   const int num_tiles = p.tiles_m * p.tiles_n;  // in 256x256 tiles
-  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = (static_cast<int>(gridDim.x) - p.copy_ctas) >> 1;   // clusters that multiply
+
+  if (cluster_id >= num_clusters) {
+    // fused all-gather: the trailing clusters only move data (both CTAs), see gather_panels
+    gather_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters, smem_raw);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PSTAGES; ++s) { tt::mbar_init(full_bar(s), 1); tt::mbar_init(empty_bar(s), 1); }
@@ -444,7 +475,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        tm = (tm + p.m_rot) % p.tiles_m;
         const int m0 = tm * TM + rank * 128, n0 = tn * TN + rank * 128;
+        if (p.ready_flags != nullptr) {
+          // fused all-gather of A: this CTA's 128 rows are panel 2 * tm + rank
+          const uint64_t t0 = tt::globaltimer_ns();
+          while (ld_acquire_gpu(p.ready_flags + 2 * tm + static_cast<int>(rank)) < p.ready_value) {
+            if (*abort_flag || tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) {
+              *abort_flag = 1;
+              atomicCAS(&g_gemm_error, 0, 5);
+              ok = false;
+              break;
+            }
+            __nanosleep(200);
+          }
+          if (!ok) break;
+        }
         for (int k = 0; k < p.k_iters; ++k, ++it) {
           const int s = it % PSTAGES;
           const uint32_t ph = (it / PSTAGES) & 1;
@@ -508,6 +554,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_it) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      tm = (tm + p.m_rot) % p.tiles_m;
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       if (!tt::mbar_wait(tfull_bar(acc), acc_ph, abort_flag, &g_gemm_error, 14)) break;
@@ -680,10 +727,12 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
     set_kernel_attrs();
   }
   void* A = const_cast<void*>(peer_bufs[rank]);
+  // the CTA-pair kernel needs whole 256-row tiles inside one rank's slice
+  const bool use_pair = g_pair_enabled && (M % (world * pair::TM) == 0) && N >= 256;
   CUtensorMap ta, tb;
   int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, BM, BK);
   if (rc) return rc;
-  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BN, BK);
+  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, use_pair ? 128 : BN, BK);
   else       rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
   if (rc) return rc;
   GemmArgs p;
@@ -692,24 +741,35 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
   p.a_mn = 0; p.b_mn = b_mn;
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
-  p.tiles_m = M / BM;
-  p.tiles_n = (N + BN - 1) / BN;
-  p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
   p.ready_flags = panel_ready; p.ready_value = ready_value; p.panel_ready = panel_ready;
   p.flags_by_m = 1;
   p.panels_per_rank = M / BM / world;
-  p.m_rot = rank * p.panels_per_rank;
   p.gather_world = world; p.gather_rank = rank; p.gather_expected = expected;
   p.gather_dst = A;
   p.panel_bytes = static_cast<long long>(BM) * K * 2;
   for (int r = 0; r < 16; ++r) { p.gather_src[r] = r < world ? peer_bufs[r] : nullptr; p.gather_flag[r] = r < world ? peer_flags[r] : nullptr; }
-  if (copy_ctas < 1) copy_ctas = 1;
-  if (copy_ctas > g_num_sms / 2) copy_ctas = g_num_sms / 2;
-  p.copy_ctas = world > 1 ? copy_ctas : 1;
-  int gemm_ctas = p.tiles_m * p.tiles_n;
-  if (gemm_ctas > g_num_sms - p.copy_ctas) gemm_ctas = g_num_sms - p.copy_ctas;
+  if (copy_ctas < 2) copy_ctas = 2;
+  copy_ctas &= ~1;
+  if (copy_ctas > g_num_sms / 2) copy_ctas = (g_num_sms / 2) & ~1;
+  p.copy_ctas = copy_ctas;
   // all CTAs must be co-resident (GEMM CTAs wait on flags written by copy CTAs): one CTA per SM, grid <= SM count
-  gemm_bf16_kernel<false><<<gemm_ctas + p.copy_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  if (use_pair) {
+    p.tiles_m = M / pair::TM;
+    p.tiles_n = (N + pair::TN - 1) / pair::TN;
+    p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, 0, b_mn);
+    p.m_rot = rank * (p.panels_per_rank / 2);
+    int clusters = p.tiles_m * p.tiles_n;
+    if (clusters > (g_num_sms - p.copy_ctas) / 2) clusters = (g_num_sms - p.copy_ctas) / 2;
+    pair::gemm_bf16_pair_kernel<false><<<clusters * 2 + p.copy_ctas, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+  } else {
+    p.tiles_m = M / BM;
+    p.tiles_n = (N + BN - 1) / BN;
+    p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
+    p.m_rot = rank * p.panels_per_rank;
+    int gemm_ctas = p.tiles_m * p.tiles_n;
+    if (gemm_ctas > g_num_sms - p.copy_ctas) gemm_ctas = g_num_sms - p.copy_ctas;
+    gemm_bf16_kernel<false><<<gemm_ctas + p.copy_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

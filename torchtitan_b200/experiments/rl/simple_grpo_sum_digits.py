@@ -82,6 +82,8 @@ class RLTrainer(Configurable):
         trainer: PolicyTrainer.Config = field(default_factory=PolicyTrainer.Config)
         generator: Generator.Config = field(default_factory=Generator.Config)
         async_mode: bool = False
+        peer_weight_sync: bool = True
+        """Disaggregated GPU runs: move weights with the NVLink peer-memory kernel when possible (else one arena broadcast)."""
         eval_samples: int = 20
 
     def __init__(self, config: Config):
@@ -122,22 +124,55 @@ class RLTrainer(Configurable):
         if self.is_trainer:
             self.trainer = PolicyTrainer(c.trainer, model_spec=c.model_spec, batch_invariant_mode=c.batch_invariant_mode,
                                          hf_assets_path=c.hf_assets_path, device=device, group=self.trainer_group)
+        self.peer_sync = None
+        if not self.colocated and c.peer_weight_sync and torch.cuda.is_available() and c.generator.model_dtype == "bfloat16":
+            self.peer_sync = self._maybe_peer_sync(train_ranks, device)
         if self.is_generator:
             self.generator = Generator(c.generator, model_spec=c.model_spec, model_path=c.hf_assets_path,
                                        batch_invariant_mode=c.batch_invariant_mode, tokenizer=self.tokenizer, device=device)
-            self.arena = ParamArena(self.generator.model)
+            self.arena = ParamArena(self.generator.model, alloc=self.peer_sync.alloc if self.peer_sync else None)
             self.generator.arena = self.arena
-        elif rank == 0:
+        elif rank == 0 and self.peer_sync is None:
             # the first trainer rank stages the generator-layout arena that is broadcast to the replicas
             self.arena = ParamArena(build_bare_model(c.model_spec, c.generator.model_dtype, device), double_buffer=False)
+        if self.peer_sync is not None and self.is_trainer:
+            self.peer_sync.build_plan(self.trainer.model, self._arena_offsets)
         self.grader = Grader(self.task.reward_function)
         self._sync_weights(0)
+
+    def _maybe_peer_sync(self, train_ranks, device):
+        """One symmetric heap over all ranks of the job when every GPU can map every other one; else None (broadcast path)."""
+        from torchtitan_b200.ops import native
+
+        from .weight_sync import NvlinkWeightSync, arena_layout
+
+        me = torch.cuda.current_device()
+        ok = native.available() and native.has("tt_push_cast") and dist.get_world_size() <= torch.cuda.device_count() and all(
+            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
+        # FSDP (or single-rank) trainers only: tensor-parallel shards are not dim-0 slices of the full parameter
+        p = self.config.trainer.parallelism
+        ok = ok and p.tensor_parallel_degree == 1 and p.pipeline_parallel_degree == 1
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            return None
+        with torch.device("meta"):
+            meta = self.config.model_spec.model.build()
+        if getattr(meta, "enable_weight_tying", False):
+            meta.tok_embeddings.weight = meta.output.weight
+        self._arena_offsets, numel = arena_layout(meta)
+        return NvlinkWeightSync(dist.group.WORLD, train_ranks, self.gen_ranks, numel, device or f"cuda:{me}")
 
     def _sync_weights(self, version: int) -> None:
         """Trainer -> generator weights. Returns the time spent (seconds, host clock around a device sync)."""
         t0 = time.perf_counter()
         if self.colocated:
             sync_local(self.trainer.model, self.arena)
+        elif self.peer_sync is not None:
+            if self.is_trainer:
+                self.peer_sync.push()
+            else:
+                self.peer_sync.wait_and_flip(self.arena)
         else:
             rank = dist.get_rank()
             if self.trainer is not None:

@@ -59,7 +59,8 @@ def build_bare_model(model_spec, dtype_name: str, device) -> nn.Module:
 class ParamArena:
     """All parameters of ``model`` re-seated as views of one flat buffer (two halves when double-buffered)."""
 
-    def __init__(self, model: nn.Module, double_buffer: bool = True):
+    def __init__(self, model: nn.Module, double_buffer: bool = True, alloc=None):
+        """``alloc(numel, dtype) -> flat tensor`` lets the halves live in an NVLink-mapped symmetric heap."""
         self.model = model
         params = list(dict(model.named_parameters()).items())
         self.names = [n for n, _ in params]
@@ -70,7 +71,8 @@ class ParamArena:
             off += (p.numel() + 127) // 128 * 128          # 256-byte aligned slices
         self.numel = off
         p0 = params[0][1]
-        self.halves = [torch.zeros(off, dtype=p0.dtype, device=p0.device) for _ in range(2 if double_buffer else 1)]
+        make = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=p0.device))
+        self.halves = [make(off, p0.dtype) for _ in range(2 if double_buffer else 1)]
         self.active = 0
         with torch.no_grad():
             for (_, p), o in zip(params, self.offsets):
@@ -124,3 +126,101 @@ def broadcast_arena(arena: ParamArena, src: int, group=None, trainer_model: nn.M
                 dst[name].copy_(full_tensor(p))
     dist.broadcast(arena.halves[arena.inactive], src=src, group=group)
     arena.flip()
+
+
+def arena_layout(model: nn.Module) -> tuple[dict[str, int], int]:
+    """(name -> element offset, total elements) of the arena a :class:`ParamArena` would build for ``model`` (works on
+    meta tensors: trainer ranks use it to address generator arenas they never allocate)."""
+    offsets, off = {}, 0
+    for n, p in model.named_parameters():
+        offsets[n] = off
+        off += (p.numel() + 127) // 128 * 128
+    return offsets, off
+
+
+class NvlinkWeightSync:
+    """Peer-memory weight sync: each trainer rank casts the fp32 master shards it owns to bf16 and writes them directly
+    into every generator replica's (inactive) arena half with one kernel (``tt_push_cast``), then publishes the version on
+    a flag in each generator's heap; a generator waits (stream-ordered, bounded) for all trainer flags and flips.
+
+    All ranks of the job build one symmetric heap; generator arenas are allocated from it on every rank (trainer ranks
+    leave theirs unused) so an offset addresses the same arena half everywhere. Trainer parameters must be data-parallel
+    sharded on dim 0 by the framework's FSDP runtime (or unsharded); other layouts use the broadcast path."""
+
+    def __init__(self, group, trainer_ranks: list[int], generator_ranks: list[int], arena_numel: int, device):
+        from torchtitan_b200.parallel.nvlink_comm import SymmetricHeap
+
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.trainer_ranks, self.generator_ranks = trainer_ranks, generator_ranks
+        self.heap = SymmetricHeap(group, 2 * arena_numel * 2 + (8 << 20), torch.device(device))
+        self.half_off = [self.heap.alloc(arena_numel * 2, align=1024) for _ in range(2)]
+        self.flag_off = [self.heap.alloc_flag() for _ in trainer_ranks]   # flag t: "trainer t finished version v"
+        self.arena_numel = arena_numel
+        self.version = 0
+        self._segs = None
+        self.bytes_pushed = 0
+
+    def alloc(self, numel: int, dtype) -> torch.Tensor:
+        """Allocator for ``ParamArena(alloc=...)`` on generator ranks: hands out the two heap halves in order."""
+        assert numel == self.arena_numel and dtype == torch.bfloat16
+        off = self.half_off[getattr(self, "_given", 0)]
+        self._given = getattr(self, "_given", 0) + 1
+        return self.heap.local_tensor(off, numel, dtype)
+
+    # ---- trainer side ----------------------------------------------------------------------------------------------
+    def build_plan(self, trainer_model: nn.Module, offsets: dict[str, int]) -> None:
+        from torchtitan_b200.parallel import fsdp
+
+        segs = []
+        seen = set()
+        units = fsdp.fsdp_units(trainer_model)
+        name_of = {id(p): n for n, p in trainer_model.named_parameters()}
+        for u in units:
+            r = u.shard_rank
+            for p in u.params:
+                name = name_of.get(id(p.param), p.fqn)
+                if name not in offsets or p.shard_dim != 0 or p.local_rows == 0:
+                    if name in offsets and p.shard_dim != 0:
+                        raise NotImplementedError(f"{name}: peer weight sync needs dim-0 shards")
+                    continue
+                src = u.shard_flat[p.shard_off : p.shard_off + p.local_rows * p.inner]
+                assert src.dtype == torch.float32
+                segs.append((src.data_ptr(), offsets[name] + r * p.chunk_rows * p.inner, p.local_rows * p.inner))
+                seen.add(name)
+        self._keep = units
+        t = torch.tensor(segs, dtype=torch.int64)
+        self._segs = t.to(self.heap.device)
+        self.bytes_pushed = int(sum(s[2] for s in segs)) * 2 * len(self.generator_ranks)
+        missing = [n for n in offsets if n not in seen]
+        if missing and not units:
+            raise NotImplementedError("peer weight sync needs FSDP units (fp32 master shards)")
+
+    def push(self) -> None:
+        """Trainer ranks: write version ``self.version + 1`` into the generators' inactive halves and publish it."""
+        import ctypes
+
+        from torchtitan_b200.ops import native
+        from torchtitan_b200.parallel.nvlink_comm import _stream
+
+        self.version += 1
+        half = self.version % 2
+        L = native.lib()
+        ptrs = (ctypes.c_void_p * len(self.generator_ranks))(*[self.heap.peer_base[g] + self.half_off[half] for g in self.generator_ranks])
+        native.check(L.tt_push_cast(self._segs.data_ptr(), self._segs.shape[0], ptrs, len(self.generator_ranks), _stream()), "tt_push_cast")
+        me = self.trainer_ranks.index(self.rank)
+        for g in self.generator_ranks:
+            native.check(L.tt_set_flag(self.heap.peer_base[g] + self.flag_off[me], self.version, _stream()), "tt_set_flag")
+
+    # ---- generator side -----------------------------------------------------------------------------------------------
+    def wait_and_flip(self, arena: "ParamArena") -> None:
+        import ctypes
+
+        from torchtitan_b200.ops import native
+        from torchtitan_b200.parallel.nvlink_comm import _stream
+
+        self.version += 1
+        flags = (ctypes.c_void_p * len(self.trainer_ranks))(*[self.heap.base + off for off in self.flag_off])
+        native.check(native.lib().tt_wait_flags(flags, len(self.trainer_ranks), self.version, _stream()), "tt_wait_flags")
+        target = self.version % 2
+        if arena.active != target:
+            arena.flip()
