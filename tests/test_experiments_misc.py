@@ -126,3 +126,19 @@ def test_transformers_backend_fsdp2_grads(tmp_path):
 
     for o in run_ranks(_hf_fsdp_worker, 2, tmp_path=tmp_path):
         assert o["err"] < 1e-4 and o["units"] == 4, o
+
+
+def test_autoparallel_planner_choices():
+    from torchtitan_b200.experiments.autoparallel import auto_plan
+
+    # Llama-3.1-8B on 8 GPUs: plain FSDP with parameters kept gathered, no tensor parallel
+    p = auto_plan(8.03e9, 5.79e10, 32, 4096, 8192, 1, 8)
+    assert p.tp == 1 and p.dp_shard == 8 and p.est_mem_bytes < 180e9
+    # a 70B model does not fit unsharded on one GPU: the plan must shard and stay under the memory limit
+    p70 = auto_plan(70e9, 4.5e11, 80, 8192, 8192, 1, 8)
+    assert p70.dp_shard * p70.tp == 8 and p70.est_mem_bytes < 0.92 * 180e9
+    import pytest
+
+    with pytest.raises(RuntimeError):
+        auto_plan(700e9, 4e12, 120, 16384, 8192, 1, 8)
+    assert any("tensor_parallel_degree" in o for o in p.to_overrides())
