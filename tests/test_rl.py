@@ -186,3 +186,30 @@ def test_disaggregated_async_grpo_three_ranks(tmp_path):
     assert all(r["steps"] == 2 and r["version"] == 2 for r in res)
     for r in res[1:]:
         assert r["gen_version"] == 2 and torch.equal(r["w"], res[0]["w"])
+
+
+@pytest.mark.parametrize("objective", ["grpo", "dapo"])
+def test_microbatched_policy_step_equals_full_batch(objective):
+    from torchtitan_b200.experiments.rl.trainer import PolicyTrainer
+    from torchtitan_b200.experiments.rl.types import Episode
+
+    def make(limit):
+        torch.manual_seed(0)
+        cfg = PolicyTrainer.Config(objective=objective, max_tokens_per_microbatch=limit)
+        cfg.training.dtype = "float32"
+        cfg.training.max_norm = 1e9
+        cfg.optimizer.lr = 0.0
+        return PolicyTrainer(cfg, model_spec=_debug_spec(), device="cpu")
+
+    g = torch.Generator().manual_seed(1)
+    eps = []
+    for i in range(5):
+        p = torch.randint(1, 2000, (int(torch.randint(4, 9, (1,), generator=g)),), generator=g).tolist()
+        t = torch.randint(1, 2000, (int(torch.randint(3, 12, (1,), generator=g)),), generator=g).tolist()
+        eps.append(Episode(0, p, "", t, [-7.0] * len(t), reward=float(i % 2), group_id=str(i // 2), advantage=float(i) - 2.0))
+    a, b = make(10**6), make(24)
+    ma, mb = a.step(eps), b.step(eps)
+    assert abs(ma["loss"] - mb["loss"]) < 1e-5 and abs(ma["grad_norm"] - mb["grad_norm"]) < 1e-4 * max(1.0, ma["grad_norm"])
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        if p.grad is not None:
+            assert torch.allclose(p.grad, q.grad, atol=1e-6, rtol=1e-4), n

@@ -81,19 +81,25 @@ def compute_token_log_probs(model, prompt_token_ids: list[int], gen_token_ids: l
 def compute_policy_gradient_loss(model, gen_token_ids, prompt_token_ids, advantages, ref_token_log_probs,
                                  kl_coef: float = 0.1, ppo_clip_eps: float = 0.2, entropy_coef: float = 0.01,
                                  objective: str = "grpo", gen_token_log_probs=None, clip_low: float = 0.2,
-                                 clip_high: float = 0.28, pad_to: int = 1):
+                                 clip_high: float = 0.28, pad_to: int = 1, n_seqs_total: int | None = None,
+                                 n_tokens_total: int | None = None):
+    """Loss of one (micro-)batch. ``n_seqs_total`` / ``n_tokens_total`` are the counts of the whole step when the
+    episodes are processed in several micro-batches: every mean below divides by them, so the micro-batch losses add up
+    to the loss of the full batch and gradients can simply be accumulated."""
     device = next(model.parameters()).device
     advantages = advantages.to(device)
     token_lps = compute_token_log_probs_packed(model, prompt_token_ids, gen_token_ids, device, pad_to)
     all_lps = torch.cat(token_lps)
-    entropy = -all_lps.mean()
+    n_seq = float(n_seqs_total if n_seqs_total is not None else len(token_lps))
+    n_tok = float(n_tokens_total if n_tokens_total is not None else max(1, all_lps.numel()))
+    entropy = -all_lps.sum() / n_tok
     if objective == "dapo":
         assert gen_token_log_probs is not None, "the dapo objective needs the generator's log-probabilities"
         old = torch.cat([torch.as_tensor(o, dtype=torch.float32, device=device) for o in gen_token_log_probs])
         adv = torch.cat([advantages[i].expand(len(t)) for i, t in enumerate(token_lps)])
         ratio = torch.exp(all_lps - old)
         clipped = ratio.clamp(1 - clip_low, 1 + clip_high)
-        pg_loss = -torch.min(ratio * adv, clipped * adv).mean()
+        pg_loss = -torch.min(ratio * adv, clipped * adv).sum() / n_tok
         kl_div = torch.zeros((), device=device)
         total = pg_loss - entropy_coef * entropy
     else:
@@ -104,8 +110,8 @@ def compute_policy_gradient_loss(model, gen_token_ids, prompt_token_ids, advanta
             kls.append((torch.exp(lr) - 1 - lr).mean())
         ratio = torch.exp(torch.stack(log_ratio))
         clipped = ratio.clamp(1 - ppo_clip_eps, 1 + ppo_clip_eps)
-        pg_loss = -torch.min(ratio * advantages, clipped * advantages).mean()
-        kl_div = torch.stack(kls).mean()
+        pg_loss = -torch.min(ratio * advantages, clipped * advantages).sum() / n_seq
+        kl_div = torch.stack(kls).sum() / n_seq
         total = pg_loss - entropy_coef * entropy + kl_coef * kl_div
     metrics = {
         "pg_loss": pg_loss.item(), "entropy": entropy.item(), "kl_div": kl_div.item(), "ratio_mean": ratio.mean().item(),

@@ -193,21 +193,30 @@ class RLTrainer(Configurable):
         self.last_sync_s = time.perf_counter() - t0
 
     # ---- rollouts across generator replicas -------------------------------------------------------------------
-    def _rollout(self, prompts: list[str], answers: list[str]) -> list[Episode]:
+    def _generate_local(self, prompts: list, answers: list[str] | None = None) -> list[Episode]:
+        """This rank's share of a rollout (empty on pure trainer ranks). ``prompts`` are texts or token-id lists."""
+        if self.generator is None or not self.is_generator:
+            return []
+        by_ids = bool(prompts) and not isinstance(prompts[0], str)
+        gen = self.generator.generate_from_ids if by_ids else self.generator.generate
         if self.colocated:
-            return self.generator.generate(prompts, answers)
-        rank, gens = dist.get_rank(), self.gen_ranks
-        mine: list[Episode] = []
-        if self.is_generator:
-            k = gens.index(rank)
-            idx = list(range(k, len(prompts), len(gens)))
-            eps = self.generator.generate([prompts[i] for i in idx], [answers[i] for i in idx])
-            for e in eps:   # make group ids unique across replicas
-                e.group_id = f"g{k}-{e.group_id}"
-            mine = eps
+            return gen(prompts, answers)
+        k = self.gen_ranks.index(dist.get_rank())
+        idx = list(range(k, len(prompts), len(self.gen_ranks)))
+        eps = gen([prompts[i] for i in idx], [answers[i] for i in idx] if answers else None)
+        for e in eps:   # make group ids unique across replicas
+            e.group_id = f"g{k}-{e.group_id}"
+        return eps
+
+    def _gather_episodes(self, mine: list[Episode]) -> list[Episode]:
+        if self.colocated:
+            return mine
         gathered: list = [None] * dist.get_world_size()
         dist.all_gather_object(gathered, mine)
         return [e for part in gathered for e in (part or [])]
+
+    def _rollout(self, prompts: list, answers: list[str] | None = None) -> list[Episode]:
+        return self._gather_episodes(self._generate_local(prompts, answers))
 
     def _questions(self, task: SumDigitsTask, n: int):
         prompts, answers = [], []
@@ -235,34 +244,37 @@ class RLTrainer(Configurable):
         logger.info("Evaluating pre-training baseline...")
         pre = self.evaluate()
         logger.info(f"Starting RL training for {c.num_steps} steps")
-        pending = None
+        # async mode = one step off-policy: while the trainer ranks work on batch k, the generator ranks already produce
+        # batch k + 1 with the weights of step k - 1; the blocking exchange of episodes comes after both.
+        episodes = self._rollout(*self._questions(self.task, c.num_episodes_per_step)) if c.async_mode else None
         for step in range(c.num_steps):
             t0 = time.perf_counter()
-            if c.async_mode and pending is not None:
-                episodes = pending
-            else:
+            nxt_local = None
+            if not c.async_mode:
                 episodes = self._rollout(*self._questions(self.task, c.num_episodes_per_step))
-            if c.async_mode and step + 1 < c.num_steps:
-                # issued before the policy step: these samples come from weights one version behind
-                pending = self._rollout(*self._questions(self.task, c.num_episodes_per_step))
+            elif step + 1 < c.num_steps:
+                nxt_local = self._generate_local(*self._questions(self.task, c.num_episodes_per_step))
             episodes = group_mean_advantages(self.grader.score(episodes))
             if c.log_samples:
                 _log_samples(episodes)
             metrics = self.trainer.step(episodes) if self.trainer is not None else None
+            cur = episodes
+            if nxt_local is not None:
+                episodes = self._gather_episodes(nxt_local)
             if not self.colocated:
                 box = [metrics]
                 dist.broadcast_object_list(box, src=0)
                 metrics = box[0]
             self._sync_weights(metrics["policy_version"])
             dt = time.perf_counter() - t0
-            lens = [len(e.token_ids) for e in episodes]
-            n_ok = sum(1 for e in episodes if e.reward > 0)
-            metrics.update(step=step, time_s=dt, weight_sync_s=getattr(self, "last_sync_s", 0.0), avg_tokens=sum(lens) / max(1, len(lens)), correct=n_ok, total=len(episodes),
+            lens = [len(e.token_ids) for e in cur]
+            n_ok = sum(1 for e in cur if e.reward > 0)
+            metrics.update(step=step, time_s=dt, weight_sync_s=getattr(self, "last_sync_s", 0.0), avg_tokens=sum(lens) / max(1, len(lens)), correct=n_ok, total=len(cur),
                            gen_tokens_per_s=sum(lens) / dt)
             self.history.append(metrics)
             logger.info(
                 f"Step {step:2d} | Loss: {metrics['loss']:+.4f} | Reward: {metrics['reward_mean']:+.3f} | "
-                f"Correct: {n_ok:>2}/{len(episodes)} | Avg tokens: {metrics['avg_tokens']:>3.0f} | "
+                f"Correct: {n_ok:>2}/{len(cur)} | Avg tokens: {metrics['avg_tokens']:>3.0f} | "
                 f"Logprob diff: mean={metrics['logprob_diff_mean']:.4e}, max={metrics['logprob_diff_max']:.4e} | Time: {dt:.1f}s"
             )
             if not torch.isfinite(torch.tensor(metrics["loss"])):

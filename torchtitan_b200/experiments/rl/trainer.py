@@ -43,6 +43,10 @@ class PolicyTrainer(Configurable):
         kl_coef: float = 0.1
         ppo_clip_eps: float = 0.2
         entropy_coef: float = 0.01
+        clip_low: float = 0.2
+        clip_high: float = 0.28
+        max_tokens_per_microbatch: int = 16384
+        """Episodes of a rank are packed into rows of at most this many tokens; gradients accumulate over the rows."""
 
     def __init__(self, config: Config, *, model_spec, batch_invariant_mode: bool = False, hf_assets_path: str = "",
                  device: torch.device | str | None = None, group=None):
@@ -62,8 +66,11 @@ class PolicyTrainer(Configurable):
         self.sd_adapter = model_spec.state_dict_adapter(model_spec.model, hf_assets_path) if model_spec.state_dict_adapter else None
         self.model = self._build_model(hf_assets_path, trainable=True)
         self.model_parts = [self.model]
-        self.ref_model = self._build_model(hf_assets_path, trainable=False)
-        self._copy_weights(self.model, self.ref_model)
+        self.needs_ref = config.objective != "dapo" and config.kl_coef != 0.0
+        self.ref_model = None
+        if self.needs_ref or config.objective != "dapo":
+            self.ref_model = self._build_model(hf_assets_path, trainable=False)
+            self._copy_weights(self.model, self.ref_model)
         self.optimizers = config.optimizer.build(model_parts=self.model_parts)
         self.lr_schedulers = config.lr_scheduler.build(optimizers=self.optimizers, training_steps=config.training.steps)
         self.policy_version = 0
@@ -148,16 +155,42 @@ class PolicyTrainer(Configurable):
         gen_lps = [episodes[i].token_log_probs for i in mine]
         my_adv = advantages[mine]
 
-        with torch.no_grad():
-            ref_lps = compute_token_log_probs_packed(self.ref_model, prompt_ids, gen_ids, self.device, self._pad_to)
-        loss, loss_metrics, token_lps = compute_policy_gradient_loss(
-            self.model, gen_ids, prompt_ids, my_adv, ref_lps, kl_coef=cfg.kl_coef, ppo_clip_eps=cfg.ppo_clip_eps,
-            entropy_coef=cfg.entropy_coef, objective=cfg.objective, gen_token_log_probs=gen_lps, pad_to=self._pad_to,
-        )
-        check = verify_logprob_identity(gen_lps, token_lps)
+        # micro-batches: greedy packing of this rank's episodes into rows of bounded length
+        groups, cur, cur_tok = [], [], 0
+        for j in range(len(mine)):
+            n = len(prompt_ids[j]) + len(gen_ids[j])
+            if cur and cur_tok + n > cfg.max_tokens_per_microbatch:
+                groups.append(cur)
+                cur, cur_tok = [], 0
+            cur.append(j)
+            cur_tok += n
+        if cur:
+            groups.append(cur)
+        n_seqs, n_toks = len(mine), max(1, sum(len(g) for g in gen_ids))
         self.optimizers.zero_grad()
-        # data-parallel mean of the per-rank losses: FSDP sums gradients, so scale by 1 / dp_size
-        (loss / self.dp_size if self.dp_enabled else loss).backward()
+        loss_total, token_lps, agg = 0.0, [None] * len(mine), {}
+        for gi, idx in enumerate(groups):
+            sel = lambda xs: [xs[j] for j in idx]  # noqa: E731
+            ref_lps = None
+            if self.ref_model is not None and cfg.objective != "dapo":
+                with torch.no_grad():
+                    ref_lps = compute_token_log_probs_packed(self.ref_model, sel(prompt_ids), sel(gen_ids), self.device, self._pad_to)
+            loss, m, lps = compute_policy_gradient_loss(
+                self.model, sel(gen_ids), sel(prompt_ids), my_adv[idx], ref_lps, kl_coef=cfg.kl_coef,
+                ppo_clip_eps=cfg.ppo_clip_eps, entropy_coef=cfg.entropy_coef, objective=cfg.objective,
+                gen_token_log_probs=sel(gen_lps), clip_low=cfg.clip_low, clip_high=cfg.clip_high, pad_to=self._pad_to,
+                n_seqs_total=n_seqs, n_tokens_total=n_toks,
+            )
+            # data-parallel mean of the per-rank losses: FSDP sums gradients, so scale by 1 / dp_size
+            (loss / self.dp_size if self.dp_enabled else loss).backward()
+            loss_total += loss.item()
+            for j, t in zip(idx, lps):
+                token_lps[j] = t.detach()
+            for k, v in m.items():
+                agg[k] = agg.get(k, 0.0) + (v if k in ("pg_loss", "entropy", "kl_div") else v * len(idx) / n_seqs)
+        loss_metrics = agg
+        loss = torch.tensor(loss_total)
+        check = verify_logprob_identity(gen_lps, token_lps)
         if self.dp_enabled and not self._fsdp_owns_grads():
             for p in self.model.parameters():
                 if p.grad is not None:

@@ -82,6 +82,85 @@ def bench_gemm_fp8(args, timer):
     return res
 
 
+def bench_ag_gemm(args, timer):
+    """Fused all-gather GEMM on ONE GPU: the "peers" are local buffers whose flags are already published, so the copy CTAs
+    and the GEMM CTAs of the single launch do all the work (intra-GPU copies stand in for NVLink loads)."""
+    import ctypes
+
+    from torchtitan_b200.ops import native
+
+    L = native.lib()
+    W, M, N, K = args.world, args.m, args.n, args.k
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    rows = M // W
+    bufs = []
+    for r in range(W):
+        b = torch.zeros(M, K, device="cuda", dtype=torch.bfloat16)
+        b[r * rows : (r + 1) * rows] = x[r * rows : (r + 1) * rows]
+        bufs.append(b)
+    flags = [torch.full((1,), 1 << 30, dtype=torch.int32, device="cuda") for _ in range(W)]
+    ready = torch.zeros(M // 128, dtype=torch.int32, device="cuda")
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    pa = (ctypes.c_void_p * W)(*[b.data_ptr() for b in bufs])
+    fa = (ctypes.c_void_p * W)(*[f.data_ptr() for f in flags])
+    st = torch.cuda.current_stream().cuda_stream
+    ver = [0]
+
+    def run():
+        ver[0] += 1
+        native.check(L.tt_gemm_allgather_a(pa, fa, W, 0, 1, w.data_ptr(), out.data_ptr(), M, N, K, 0, K, N, 0, ready.data_ptr(),
+                                           ver[0], args.copy_ctas, st), "tt_gemm_allgather_a")
+
+    ms = timer.time(run, args.iters)
+    err = ((out.float() - x.float() @ w.float().t()).abs().max() / (x.float() @ w.float().t()).abs().max()).item()
+    return {"case": "ag_gemm_one_gpu", "world": W, "M": M, "N": N, "K": K, "copy_ctas": args.copy_ctas, "ms": ms,
+            "tflops": 2 * M * N * K / ms / 1e9, "gathered_bytes": (W - 1) * rows * K * 2, "max_rel_err": err}
+
+
+def bench_grouped_gemm(args, timer):
+    """Grouped GEMM with device-side offsets (forward + both gradients) on a Qwen3-30B-A3B-like expert shape."""
+    from torchtitan_b200.ops import cuda_ops
+
+    E, N, K, R = args.experts, args.n, args.k, args.m
+    g = torch.Generator(device="cuda").manual_seed(0)
+    raw = torch.rand(E, device="cuda", generator=g) + 0.2
+    sizes = (raw / raw.sum() * (R - 64 * E)).long() // 64 * 64 + 64
+    counts = sizes.clone()
+    counts._tt_aligned = 64
+    rows = int(sizes.sum())
+    x = (torch.randn(rows, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(E, N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = cuda_ops.grouped_linear(x, w, counts)
+    gy = torch.randn_like(y)
+    ms_f = timer.time(lambda: cuda_ops.grouped_linear(x, w, counts), args.iters)
+
+    def fb():
+        x.grad = w.grad = None
+        cuda_ops.grouped_linear(x, w, counts).backward(gy)
+
+    ms_fb = timer.time(fb, args.iters)
+    fl = 2.0 * rows * N * K
+    return {"case": "grouped_gemm", "experts": E, "rows": rows, "N": N, "K": K, "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9,
+            "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3 * fl / ms_fb / 1e9}
+
+
+def bench_paged_decode(args, timer):
+    """Paged-KV decode attention: ``batch`` sequences of ``seq`` cached tokens; reports achieved KV read bandwidth."""
+    from torchtitan_b200.ops import cuda_ops
+
+    B, H, Hkv, D, bs, ctx = args.batch, args.heads, args.kv_heads, 128, 16, args.seq
+    nblk = B * ((ctx + bs - 1) // bs)
+    kc = torch.randn(nblk, bs, Hkv, D, device="cuda").bfloat16()
+    vc = torch.randn(nblk, bs, Hkv, D, device="cuda").bfloat16()
+    tables = torch.randperm(nblk, device="cuda").view(B, -1).int()
+    lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    q = torch.randn(B, H, D, device="cuda").bfloat16()
+    ms = timer.time(lambda: cuda_ops.paged_decode(q, kc, vc, tables, lens, D**-0.5), args.iters)
+    nbytes = 2.0 * B * ctx * Hkv * D * 2
+    return {"case": "paged_decode", "batch": B, "ctx": ctx, "H": H, "Hkv": Hkv, "ms": ms, "kv_gb_per_s": nbytes / ms / 1e6}
+
+
 def bench_attention(args, timer):
     from torchtitan_b200.ops import cuda_ops
 
@@ -137,7 +216,10 @@ def bench_elementwise(args, timer):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_fp8", "attention", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "ag_gemm", "grouped_gemm", "paged_decode", "attention", "elementwise"])
+    ap.add_argument("--world", type=int, default=4)
+    ap.add_argument("--copy-ctas", type=int, default=8)
+    ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -160,6 +242,12 @@ def main():
         res = [bench_gemm(args, timer)]
     elif args.what == "gemm_fp8":
         res = [bench_gemm_fp8(args, timer)]
+    elif args.what == "ag_gemm":
+        res = [bench_ag_gemm(args, timer)]
+    elif args.what == "grouped_gemm":
+        res = [bench_grouped_gemm(args, timer)]
+    elif args.what == "paged_decode":
+        res = [bench_paged_decode(args, timer)]
     elif args.what == "attention":
         res = [bench_attention(args, timer)]
     else:
