@@ -142,3 +142,54 @@ def test_autoparallel_planner_choices():
     with pytest.raises(RuntimeError):
         auto_plan(700e9, 4e12, 120, 16384, 8192, 1, 8)
     assert any("tensor_parallel_degree" in o for o in p.to_overrides())
+
+
+def test_vlm_data_path_and_model_step():
+    from torchtitan_b200.experiments.vlm import llama3_siglip2_configs
+    from torchtitan_b200.experiments.vlm.datasets import MultiModalCollatorNLD, SyntheticMultiModalDataset, patchify, smart_resize
+    from torchtitan_b200.experiments.vlm.model import SpecialTokens
+
+    assert smart_resize(100, 37, 16, 64) == (96, 32)
+    H, W = smart_resize(1000, 1000, 16, 64)
+    assert (H // 16) * (W // 16) <= 64
+    p, g = patchify(torch.arange(3 * 32 * 48, dtype=torch.float32).view(3, 32, 48), 16)
+    assert p.shape == (6, 768) and g[:, 1].max() == 1 and g[:, 2].max() == 2
+    assert torch.equal(p[4].view(3, 16, 16), torch.arange(3 * 32 * 48, dtype=torch.float32).view(3, 32, 48)[:, 16:32, 16:32])
+
+    st = SpecialTokens("<|image|>", 2044, "<|begin_of_image|>", 2045, "<|end_of_image|>", 2046, "<|pad|>", 2047)
+    ds = SyntheticMultiModalDataset(st, vocab=2000, seq_len=256, patch=16, max_patches=16)
+    it = iter(ds)
+    batch = [next(it) for _ in range(2)]
+    coll = MultiModalCollatorNLD(patch_dim=768, max_images_per_batch=32, max_patches_per_image=16, special_tokens=st)
+    inputs, labels = coll(batch)
+    assert inputs["input"].shape == (2, 256) and labels.shape == (2, 256)
+    n_placeholders = int((torch.tensor([b[0] for b in batch]) == st.img_id).sum())
+    n_patches = int((inputs["grid_thw"][:, :, 1:] != -1).all(-1).sum())
+    assert n_placeholders == n_patches > 0
+    assert (labels == st.img_id).sum() == 0
+
+    cfg = llama3_siglip2_configs["debugmodel"]
+    import dataclasses
+
+    cfg = dataclasses.replace(cfg, n_layers=2)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=256)
+    model = cfg.build()
+    model.init_weights()
+
+    class _Tok:
+        eos_id = 0
+
+    masks = model.get_attention_masks(inputs["input"], _Tok())
+    # make the placeholders of the (shifted) input match the images exactly: recompute from the input ids
+    keep = int((inputs["input"] == st.img_id).sum())
+    assert keep <= n_patches
+    if keep != n_patches:   # the last token of a row was a placeholder cut by the shift: drop that patch
+        gm = (inputs["grid_thw"][:, :, 1:] != -1).all(-1)
+        idx = gm.nonzero()[keep:]
+        for n_i, l_i in idx.tolist():
+            inputs["grid_thw"][n_i, l_i] = -1
+    out = model(inputs["input"], inputs["pixel_values"], inputs["grid_thw"], st, masks)
+    assert out.shape == (2, 256, cfg.vocab_size)
+    loss = torch.nn.functional.cross_entropy(out.flatten(0, 1).float(), labels.flatten(), ignore_index=-100)
+    loss.backward()
+    assert model.encoder.layers["0"].fc1.weight.grad.abs().sum() > 0 and model.projector.w2.weight.grad.abs().sum() > 0

@@ -1,0 +1,142 @@
+"""Multimodal data path: native-resolution patchification, sample packing, collation
+(torchtitan/experiments/vlm/datasets/{mm_datasets,mm_collator_nld}.py and datasets/utils/{image,packing,text}.py)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .model import SpecialTokens
+
+
+def smart_resize(h: int, w: int, patch: int, max_patches: int, merge: int = 1) -> tuple[int, int]:
+    """Closest size that is a multiple of ``patch * merge`` per side, keeps the aspect ratio and has <= ``max_patches`` patches."""
+    unit = patch * merge
+    H, W = max(unit, round(h / unit) * unit), max(unit, round(w / unit) * unit)
+    if (H // patch) * (W // patch) > max_patches:
+        scale = (max_patches * patch * patch / (h * w)) ** 0.5
+        H, W = max(unit, int(h * scale) // unit * unit), max(unit, int(w * scale) // unit * unit)
+    return H, W
+
+
+def patchify(img_chw: torch.Tensor, patch: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """[C, H, W] -> (patches [L, C*patch*patch], grid [L, 3] of (t, h, w) coordinates)."""
+    C, H, W = img_chw.shape
+    gh, gw = H // patch, W // patch
+    p = img_chw.reshape(C, gh, patch, gw, patch).permute(1, 3, 0, 2, 4).reshape(gh * gw, C * patch * patch)
+    hh, ww = torch.meshgrid(torch.arange(gh), torch.arange(gw), indexing="ij")
+    grid = torch.stack((torch.zeros_like(hh), hh, ww), dim=-1).reshape(-1, 3)
+    return p, grid
+
+
+def process_sample(text_ids_before: list[int], images: list[torch.Tensor], text_ids_after: list[int], st: SpecialTokens,
+                   patch: int, max_patches: int):
+    """One document: ``<text> (<boi> <image>*L <eoi>)* <text>``; returns (token ids, [patches], [grids])."""
+    ids, pats, grids = list(text_ids_before), [], []
+    for img in images:
+        H, W = smart_resize(img.shape[1], img.shape[2], patch, max_patches)
+        img = torch.nn.functional.interpolate(img.unsqueeze(0).float(), size=(H, W), mode="bilinear", align_corners=False)[0]
+        p, g = patchify(img, patch)
+        pats.append(p)
+        grids.append(g)
+        ids += [st.boi_id] + [st.img_id] * p.shape[0] + [st.eoi_id]
+    return ids + list(text_ids_after), pats, grids
+
+
+class SamplePacker:
+    """Greedy packing of whole samples into sequences of ``seq_len + 1`` tokens (a sample that does not fit starts the
+    next sequence; over-long samples are truncated and lose their images past the cut)."""
+
+    def __init__(self, seq_len: int, st: SpecialTokens):
+        self.seq_len, self.st = seq_len + 1, st
+        self.ids: list[int] = []
+        self.pats: list[torch.Tensor] = []
+        self.grids: list[torch.Tensor] = []
+
+    def add(self, ids, pats, grids):
+        out = None
+        if len(self.ids) + len(ids) > self.seq_len and self.ids:
+            out = self.flush()
+        if len(ids) > self.seq_len:
+            ids = ids[: self.seq_len]
+            kept = sum(1 for t in ids if t == self.st.img_id)
+            n, keep_p, keep_g = 0, [], []
+            for p, g in zip(pats, grids):
+                if n + p.shape[0] <= kept:
+                    keep_p.append(p)
+                    keep_g.append(g)
+                    n += p.shape[0]
+            ids = [t if (t != self.st.img_id or i < 0) else t for i, t in enumerate(ids)]
+            # placeholders without a complete image become padding
+            extra = kept - n
+            if extra:
+                idx = [i for i, t in enumerate(ids) if t == self.st.img_id][-extra:]
+                for i in idx:
+                    ids[i] = self.st.pad_id
+            pats, grids = keep_p, keep_g
+        self.ids += ids
+        self.pats += pats
+        self.grids += grids
+        return out
+
+    def flush(self):
+        ids = self.ids + [self.st.pad_id] * (self.seq_len - len(self.ids))
+        out = (ids, self.pats, self.grids)
+        self.ids, self.pats, self.grids = [], [], []
+        return out
+
+
+@dataclass
+class MultiModalCollatorNLD:
+    """Stack packed sequences; images of the whole batch form ``pixel_values [N, L, D]`` / ``grid_thw [N, L, 3]`` padded
+    with -1 coordinates, N padded to ``max_images_per_batch`` so that shapes are static."""
+
+    patch_dim: int
+    max_images_per_batch: int
+    max_patches_per_image: int
+    special_tokens: SpecialTokens
+
+    def __call__(self, batch):
+        st = self.special_tokens
+        toks = torch.tensor([b[0] for b in batch], dtype=torch.long)
+        N, L = self.max_images_per_batch, self.max_patches_per_image
+        pixels = torch.zeros(N, L, self.patch_dim)
+        grid = torch.full((N, L, 3), -1, dtype=torch.long)
+        n = 0
+        for _, pats, grids in batch:
+            for p, g in zip(pats, grids):
+                assert n < N, "more images in the batch than max_images_per_batch"
+                pixels[n, : p.shape[0]] = p
+                grid[n, : g.shape[0]] = g
+                n += 1
+        inputs, labels = toks[:, :-1], toks[:, 1:].clone()
+        for t in (st.pad_id, st.img_id, st.boi_id, st.eoi_id):
+            labels[labels == t] = st.ignore_id
+        return {"input": inputs, "pixel_values": pixels, "grid_thw": grid, "special_tokens": st}, labels
+
+
+class SyntheticMultiModalDataset(torch.utils.data.IterableDataset):
+    """Random text and random images of varying aspect ratio (offline stand-in for OBELICS / CC12M streams)."""
+
+    def __init__(self, st: SpecialTokens, vocab: int, seq_len: int, patch: int = 16, max_patches: int = 64, seed: int = 0,
+                 dp_rank: int = 0, dp_world_size: int = 1):
+        self.st, self.vocab, self.seq_len, self.patch, self.max_patches = st, vocab, seq_len, patch, max_patches
+        self.seed, self.rank, self.world = seed, dp_rank, dp_world_size
+
+    def __iter__(self):
+        g = torch.Generator().manual_seed(self.seed * 1000 + self.rank)
+        packer = SamplePacker(self.seq_len, self.st)
+        reserved = {self.st.img_id, self.st.boi_id, self.st.eoi_id, self.st.pad_id}
+        while True:
+            n_txt = int(torch.randint(8, 64, (1,), generator=g))
+            ids = [t for t in torch.randint(0, self.vocab, (n_txt,), generator=g).tolist() if t not in reserved]
+            imgs = []
+            for _ in range(int(torch.randint(0, 3, (1,), generator=g))):
+                h = int(torch.randint(2, 8, (1,), generator=g)) * self.patch
+                w = int(torch.randint(2, 8, (1,), generator=g)) * self.patch
+                imgs.append(torch.rand(3, h, w, generator=g))
+            sample = process_sample(ids[: n_txt // 2], imgs, ids[n_txt // 2 :], self.st, self.patch, self.max_patches)
+            out = packer.add(*sample)
+            if out is not None:
+                yield out
