@@ -75,41 +75,31 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
   for (int t0 = 0; t0 < ctx; t0 += TT) {
     const int nt = min(TT, ctx - t0);
-    // ---- scores: 16 threads per row, 8 rows per pass; all 16 row loads of a thread are issued before any is used
-    {
-      uint4 kk[TT / 8];
+    // ---- scores: 8 rows per pass, 16 threads per row
+    for (int r = tg; r < TT; r += 8) {
+      float part[G];
 #pragma unroll
-      for (int i = 0; i < TT / 8; ++i) {
-        const int r = tg + 8 * i;
-        kk[i] = make_uint4(0, 0, 0, 0);
-        if (r < nt) {
-          const int t = t0 + r;
-          const long long row = (static_cast<long long>(bt[t / block_size]) * block_size + t % block_size) * Hkv + hk;
-          kk[i] = __ldg(reinterpret_cast<const uint4*>(kc + row * HD + dl * 8));
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < TT / 8; ++i) {
-        const int r = tg + 8 * i;
-        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kk[i]);
-        float part[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) part[g] = 0.f;
+      for (int g = 0; g < G; ++g) part[g] = 0.f;
+      if (r < nt) {
+        const int t = t0 + r;
+        const long long row = (static_cast<long long>(bt[t / block_size]) * block_size + t % block_size) * Hkv + hk;
+        const uint4 kk = *reinterpret_cast<const uint4*>(kc + row * HD + dl * 8);
+        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kk);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 f = __bfloat1622float2(kh[e]);
 #pragma unroll
           for (int g = 0; g < G; ++g) part[g] += qreg[g][2 * e] * f.x + qreg[g][2 * e + 1] * f.y;
         }
+      }
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float v = part[g];
-          v += __shfl_xor_sync(0xffffffffu, v, 1);
-          v += __shfl_xor_sync(0xffffffffu, v, 2);
-          v += __shfl_xor_sync(0xffffffffu, v, 4);
-          v += __shfl_xor_sync(0xffffffffu, v, 8);
-          if (dl == 0) s_p[g][r] = (r < nt) ? v : -INFINITY;
-        }
+      for (int g = 0; g < G; ++g) {
+        float v = part[g];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        if (dl == 0) s_p[g][r] = (r < nt) ? v : -INFINITY;
       }
     }
     __syncthreads();
@@ -144,33 +134,21 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       }
     }
     __syncthreads();
-    // ---- P.V: thread owns 8 dims of 16 rows; the value loads are issued up front as well
-    {
-      uint4 vv[TT / 8];
+    // ---- P.V: 8 rows per pass, thread owns 8 dims
+    for (int r = tg; r < nt; r += 8) {
+      const int t = t0 + r;
+      const long long row = (static_cast<long long>(bt[t / block_size]) * block_size + t % block_size) * Hkv + hk;
+      const uint4 vv = *reinterpret_cast<const uint4*>(vc + row * HD + dl * 8);
+      const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vv);
+      float vf[8];
 #pragma unroll
-      for (int i = 0; i < TT / 8; ++i) {
-        const int r = tg + 8 * i;
-        vv[i] = make_uint4(0, 0, 0, 0);
-        if (r < nt) {
-          const int t = t0 + r;
-          const long long row = (static_cast<long long>(bt[t / block_size]) * block_size + t % block_size) * Hkv + hk;
-          vv[i] = __ldg(reinterpret_cast<const uint4*>(vc + row * HD + dl * 8));
-        }
-      }
+      for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(vh[e]); vf[2 * e] = f.x; vf[2 * e + 1] = f.y; }
 #pragma unroll
-      for (int i = 0; i < TT / 8; ++i) {
-        const int r = tg + 8 * i;
-        const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vv[i]);
-        float vf[8];
+      for (int g = 0; g < G; ++g) {
+        const float pr = s_p[g][r];
+        sum_part[g] += pr;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(vh[e]); vf[2 * e] = f.x; vf[2 * e + 1] = f.y; }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float pr = s_p[g][r];       // zero for rows past the context
-          sum_part[g] += pr;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[g][e] += pr * vf[e];
-        }
+        for (int e = 0; e < 8; ++e) acc[g][e] += pr * vf[e];
       }
     }
     // every thread of a row lane saw the same rows: the row-lane partial sums are combined at the end

@@ -69,6 +69,10 @@ def main() -> None:
     if a.no_cudagraph:
         cfg.generator.compile.backend = "none"
     cfg.generator.seed = 1234 + rank
+    # KV cache sized for the benchmark instead of "all free memory": sequences of this replica x longest possible length
+    n_gen = 1 if world == 1 else world - ntrain
+    seqs = -(-a.prompts // n_gen) * a.samples
+    cfg.generator.max_kv_blocks = int(seqs * (512 + a.max_new + 32) / cfg.generator.kv_block_size * 1.1) + 64
     cfg.peer_weight_sync = a.sync == "peer"
     cfg.async_mode = True
 
