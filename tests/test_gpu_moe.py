@@ -19,11 +19,11 @@ def test_router_forward_backward(E, K, func, norm):
     bias = torch.randn(E, device="cuda") * 0.01
     kw = dict(top_k=K, score_func=func, route_norm=norm, route_scale=2.5)
     top, idx, counts = cuda_ops.moe_route(x, gw, None, bias, **kw)
-    g = torch.randn_like(top)
-    top.backward(g)
+    g_expert = torch.randn(T, E, device="cuda")          # upstream gradient per (token, expert): slot order may differ
+    top.backward(g_expert.gather(1, idx))
     x2, gw2 = x.detach().clone().requires_grad_(), gw.detach().clone().requires_grad_()
     rtop, ridx, rcounts = ref.moe_route(x2, gw2, None, bias, **kw)
-    rtop.backward(g)
+    rtop.backward(g_expert.gather(1, ridx))
     # the same experts are chosen (order inside the k may differ); a near-tie at the k-th place may flip for a rare token
     same = (idx.sort(-1).values == ridx.sort(-1).values).all(-1)
     assert same.float().mean() > 0.99, same.float().mean()
