@@ -1,0 +1,88 @@
+"""``FluxTrainer``: flow-matching training step on top of the base trainer.
+
+Parity: torchtitan/models/flux/trainer.py:26-285 -- frozen T5 / CLIP encoders and autoencoder are built beside the model;
+a step encodes the batch (no grad), draws noise and a uniform time per sample, forms ``x_t = (1 - t) x + t eps``, and
+regresses the packed velocity ``eps - x`` with a sum-of-squares loss divided by the global number of latent elements."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from torchtitan_b200.parallel import utils as dist_utils
+from torchtitan_b200.trainer import Trainer
+
+from .model.autoencoder import load_ae
+from .model.hf_embedder import FluxEmbedder
+from .utils import create_position_encoding_for_latents, pack_latents, preprocess_data
+
+
+@dataclass(kw_only=True, slots=True)
+class Encoder:
+    t5_encoder: str = "google/t5-v1_1-small"
+    clip_encoder: str = "openai/clip-vit-large-patch14"
+    autoencoder_path: str = "assets/hf/FLUX.1-dev/ae.safetensors"
+    random_init: bool = False
+    """Build small randomly initialised encoders / autoencoder instead of loading checkpoints (tests, offline runs)."""
+    hidden: int = 64
+
+
+class FluxTrainer(Trainer):
+    @dataclass(kw_only=True, slots=True)
+    class Config(Trainer.Config):
+        encoder: Encoder = field(default_factory=Encoder)
+
+    def __init__(self, config: Config):
+        super().__init__(config)
+        from torchtitan_b200.config import TORCH_DTYPE_MAP
+
+        self._dtype = TORCH_DTYPE_MAP[config.training.mixed_precision_param] if self.device.type == "cuda" else torch.float32
+        e = config.encoder
+        self.autoencoder = load_ae(e.autoencoder_path, self.model_config.autoencoder_params, device=self.device, dtype=self._dtype,
+                                   random_init=e.random_init)
+        self.clip_encoder = FluxEmbedder(e.clip_encoder, random_init=e.random_init, hidden=self.model_config.vec_in_dim).to(self.device, self._dtype)
+        self.t5_encoder = FluxEmbedder(e.t5_encoder, random_init=e.random_init, hidden=self.model_config.context_in_dim).to(self.device, self._dtype)
+
+    def forward_backward_step(self, *, input_dict, labels, global_valid_tokens=None):
+        input_dict = dict(input_dict)
+        input_dict["image"] = labels
+        batch = preprocess_data(self.device, self._dtype, autoencoder=self.autoencoder, clip_encoder=self.clip_encoder,
+                                t5_encoder=self.t5_encoder, batch=input_dict)
+        target_latents = batch["img_encodings"]
+        n_local = torch.tensor(float(target_latents.numel()), device=self.device)
+        n_global = dist_utils.dist_sum(n_local, self.parallel_dims.get_mesh("batch")) if self.parallel_dims.dp_enabled else n_local
+        bsz, _, lh, lw = target_latents.shape
+        with torch.no_grad():
+            noise = torch.randn_like(target_latents)
+            t = torch.rand(bsz, device=self.device)
+            sig = t.view(-1, 1, 1, 1).to(target_latents.dtype)
+            latents = pack_latents((1 - sig) * target_latents + sig * noise)
+            target = pack_latents(noise - target_latents)
+            img_ids = create_position_encoding_for_latents(bsz, lh, lw).to(self.device)
+            txt_ids = torch.zeros(bsz, batch["t5_encodings"].shape[1], 3, device=self.device)
+        with self.train_context(), self.maybe_enable_amp:
+            pred = self.model_parts[0](img=latents, img_ids=img_ids, txt=batch["t5_encodings"], txt_ids=txt_ids,
+                                       y=batch["clip_encodings"], timesteps=t.to(latents.dtype))
+            loss = self.loss_fn(pred, target) / n_global
+        loss.backward()
+        return loss
+
+    def train_step(self, data_iterator) -> None:
+        self.optimizers.zero_grad()
+        losses = []
+        for _ in range(self.gradient_accumulation_steps):
+            input_dict, labels = next(data_iterator)
+            losses.append(self.forward_backward_step(input_dict=input_dict, labels=labels).detach())
+        grad_norm = dist_utils.clip_grad_norm_([p for m in self.model_parts for p in m.parameters()], self.config.training.max_norm,
+                                               foreach=True, pp_mesh=None)
+        self.checkpointer.maybe_wait_for_staging()
+        self.optimizers.step()
+        self.lr_schedulers.step()
+        self.last_loss = torch.stack(losses).sum()
+        self.last_grad_norm = grad_norm
+        if self.metrics_processor.should_log(self.step):
+            loss = self.last_loss
+            if self.parallel_dims.dp_enabled:
+                loss = dist_utils.dist_sum(loss, self.parallel_dims.get_mesh("batch"))
+            self.metrics_processor.log(self.step, float(loss), float(loss), float(grad_norm))
