@@ -146,7 +146,7 @@ def test_colocated_grpo_two_steps(tmp_path):
     assert torch.equal(rl.generator.model.output.weight, rl.trainer.model.output.weight.to(w0.dtype))
 
 
-def _disagg_worker(rank, world):
+def _disagg_worker(rank, world, ntrain=1):
     import torch.distributed as dist
 
     dist.init_process_group("gloo")
@@ -162,6 +162,7 @@ def _disagg_worker(rank, world):
     cfg.generator.seed = rank
     cfg.trainer.training.dtype = "float32"
     cfg.async_mode = True
+    cfg.trainer.parallelism.data_parallel_shard_degree = ntrain
     cfg.hf_assets_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "assets", "tokenizer")
     rl = RLTrainer(cfg)
     rl.setup(device="cpu")
@@ -172,7 +173,9 @@ def _disagg_worker(rank, world):
         out["gen_version"] = rl.generator.policy_version
         out["w"] = rl.generator.model.output.weight.detach().clone()
     if rl.trainer is not None:
-        out["w"] = rl.trainer.model.output.weight.detach().clone()
+        from torchtitan_b200.experiments.rl.weight_sync import full_tensor
+
+        out["w"] = full_tensor(rl.trainer.model.output.weight).detach().clone()
     return out
 
 
@@ -213,3 +216,13 @@ def test_microbatched_policy_step_equals_full_batch(objective):
     for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
         if p.grad is not None:
             assert torch.allclose(p.grad, q.grad, atol=1e-6, rtol=1e-4), n
+
+
+def test_disaggregated_fsdp_trainer_subgroup(tmp_path):
+    """2 FSDP trainer ranks (a sub-group of the job) + 1 generator rank."""
+    from dist_utils import run_ranks
+
+    res = run_ranks(_disagg_worker, 3, 2, tmp_path=tmp_path)
+    assert [r["is_trainer"] for r in res] == [True, True, False]
+    assert all(r["steps"] == 2 and r["version"] == 2 for r in res)
+    assert torch.equal(res[0]["w"], res[1]["w"]) and torch.equal(res[2]["w"], res[0]["w"])

@@ -121,9 +121,13 @@ class RLTrainer(Configurable):
             self.sync_group = dist.new_group([train_ranks[0]] + self.gen_ranks)
         logger.info(f"{len(self.gen_ranks)} generator GPUs + {self.trainer_world} trainer GPUs"
                     f"{' (colocated)' if self.colocated else ''}")
+        if not self.colocated and not self.is_trainer:
+            # take part in the creation of the trainer's process groups (a collective of the whole job)
+            PolicyTrainer.make_parallel_dims(c.trainer, self.trainer_world, train_ranks).build_mesh()
         if self.is_trainer:
             self.trainer = PolicyTrainer(c.trainer, model_spec=c.model_spec, batch_invariant_mode=c.batch_invariant_mode,
-                                         hf_assets_path=c.hf_assets_path, device=device, group=self.trainer_group)
+                                         hf_assets_path=c.hf_assets_path, device=device, group=self.trainer_group,
+                                         ranks=None if self.colocated else train_ranks)
         self.peer_sync = None
         if not self.colocated and c.peer_weight_sync and torch.cuda.is_available() and c.generator.model_dtype == "bfloat16":
             self.peer_sync = self._maybe_peer_sync(train_ranks, device)

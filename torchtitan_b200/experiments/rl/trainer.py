@@ -49,7 +49,7 @@ class PolicyTrainer(Configurable):
         """Episodes of a rank are packed into rows of at most this many tokens; gradients accumulate over the rows."""
 
     def __init__(self, config: Config, *, model_spec, batch_invariant_mode: bool = False, hf_assets_path: str = "",
-                 device: torch.device | str | None = None, group=None):
+                 device: torch.device | str | None = None, group=None, ranks: list[int] | None = None):
         self.config, self.model_spec = config, model_spec
         if device is None:
             device = f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}" if torch.cuda.is_available() else "cpu"
@@ -57,12 +57,9 @@ class PolicyTrainer(Configurable):
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
         world = dist.get_world_size(group) if dist.is_initialized() else 1
-        p = config.parallelism
-        self.parallel_dims = ParallelDims(
-            dp_shard=p.data_parallel_shard_degree, dp_replicate=p.data_parallel_replicate_degree, cp=p.context_parallel_degree,
-            tp=p.tensor_parallel_degree, pp=p.pipeline_parallel_degree, ep=p.expert_parallel_degree,
-            etp=p.expert_tensor_parallel_degree, world_size=world,
-        )
+        self.parallel_dims = self.make_parallel_dims(config, world, ranks)
+        if getattr(self.parallel_dims, "_base", None) is not None:
+            self.parallel_dims.build_mesh()              # collective with the non-trainer ranks (see make_parallel_dims)
         self.sd_adapter = model_spec.state_dict_adapter(model_spec.model, hf_assets_path) if model_spec.state_dict_adapter else None
         self.model = self._build_model(hf_assets_path, trainable=True)
         self.model_parts = [self.model]
@@ -81,6 +78,20 @@ class PolicyTrainer(Configurable):
         self.dp_enabled = pd.dp_enabled
         # the packed row is fed to 128-token attention tiles on the GPU
         self._pad_to = 128 * max(1, pd.tp) if self.device.type == "cuda" else max(1, pd.tp)
+
+    @staticmethod
+    def make_parallel_dims(config: "PolicyTrainer.Config", world: int, ranks: list[int] | None = None) -> ParallelDims:
+        """The trainer's dims over ``ranks`` of the job. When that is a strict subset, every other rank of the job must
+        build the same object and call ``build_mesh()`` once (process-group creation is a collective of the whole job)."""
+        p = config.parallelism
+        pd = ParallelDims(
+            dp_shard=p.data_parallel_shard_degree, dp_replicate=p.data_parallel_replicate_degree, cp=p.context_parallel_degree,
+            tp=p.tensor_parallel_degree, pp=p.pipeline_parallel_degree, ep=p.expert_parallel_degree,
+            etp=p.expert_tensor_parallel_degree, world_size=world,
+        )
+        if ranks is not None and dist.is_initialized() and len(ranks) != dist.get_world_size():
+            pd.set_base_ranks(ranks)
+        return pd
 
     # ---- construction -----------------------------------------------------------------------------------
     def _build_model(self, hf_assets_path: str, trainable: bool):

@@ -174,21 +174,49 @@ class ParallelDims:
 
         return device_type
 
+    # A job may give the dims only a subset of its ranks (e.g. the trainer ranks of an RL job whose other ranks generate):
+    # ``set_base_ranks`` maps grid positions 0..world_size-1 to those global ranks. Process-group creation stays a
+    # collective of the whole job, so the ranks outside the subset must call ``build_mesh()`` on an identical object
+    # (they become members of no group).
+    def set_base_ranks(self, ranks: list[int] | None) -> None:
+        assert ranks is None or len(ranks) == self.world_size
+        self._base = list(ranks) if ranks is not None else None
+        self._meshes, self._groups = {}, {}
+
+    def _global(self, ranks: list[int]) -> list[int]:
+        base = getattr(self, "_base", None)
+        return list(ranks) if base is None else [base[r] for r in ranks]
+
+    def _me(self) -> int:
+        """This process's position in the grids."""
+        base = getattr(self, "_base", None)
+        return dist.get_rank() if base is None else base.index(dist.get_rank())
+
+    def _new_group(self, granks: list[int]):
+        if getattr(self, "_base", None) is None:
+            return dist.new_group(granks)
+        key = ("sub",) + tuple(granks)            # one group per distinct rank set
+        if key not in self._groups:
+            self._groups[key] = dist.new_group(granks)
+        return self._groups[key]
+
     def _group_for(self, grid_name: str, dims: tuple[str, ...]):
         """Create (collectively, on every rank) the groups of one dimension; return mine."""
         grid = self.grids[grid_name]
         mine = None
         me = dist.get_rank()
+        whole_job = getattr(self, "_base", None) is None
         for ranks in grid.all_groups(dims):
-            key = tuple(ranks)
+            granks = self._global(ranks)
+            key = tuple(granks)
             if key not in self._groups:
-                if len(ranks) == self.world_size and ranks == list(range(self.world_size)):
+                if whole_job and len(ranks) == self.world_size and ranks == list(range(self.world_size)):
                     self._groups[key] = dist.group.WORLD
                 else:
-                    self._groups[key] = dist.new_group(ranks)
-            if me in ranks:
-                mine = (self._groups[key], ranks)
-        assert mine is not None
+                    self._groups[key] = self._new_group(granks)
+            if me in granks:
+                mine = (self._groups[key], granks)
+        assert mine is not None or getattr(self, "_base", None) is not None
         return mine
 
     def build_mesh(self):
@@ -200,7 +228,8 @@ class ParallelDims:
             f"dp_shard={self.dp_shard}, cp={self.cp}, tp={self.tp}, ep={self.ep}, etp={self.etp}"
         )
         assert dist.is_initialized(), "init_distributed() must run before build_mesh()"
-        assert dist.get_world_size() == self.world_size, (
+        base = getattr(self, "_base", None)
+        assert base is not None or dist.get_world_size() == self.world_size, (
             f"world size {dist.get_world_size()} != ParallelDims.world_size {self.world_size}"
         )
         dev = self._device_type()
@@ -212,19 +241,31 @@ class ParallelDims:
                 continue
             grid_name, dims = self._dim_home(name)
             if size == 1:  # efsdp of size 1 under EP: a one-rank group
-                pg, ranks = dist.new_group([dist.get_rank()]) if False else (None, [dist.get_rank()])
+                pg, ranks = None, [dist.get_rank()]
                 # every rank must take part in new_group calls: make them all
-                for r in range(self.world_size):
-                    g = dist.new_group([r])
+                for r in self._global(list(range(self.world_size))):
+                    g = self._new_group([r])
                     if r == dist.get_rank():
                         pg = g
             else:
-                pg, ranks = self._group_for(grid_name, dims)
+                got = self._group_for(grid_name, dims)
+                if got is None:              # this rank is outside the subset: it only took part in the creation
+                    self._meshes[name] = None
+                    continue
+                pg, ranks = got
+            if base is not None and dist.get_rank() not in base:
+                self._meshes[name] = None
+                continue
             self._meshes[name] = DeviceMesh.from_group(
                 pg, dev, mesh=torch.tensor(ranks, dtype=torch.int), mesh_dim_names=(name,)
             )
+        all_ranks = self._global(list(range(self.world_size)))
+        world_pg = dist.group.WORLD if base is None else self._new_group(all_ranks)
+        if base is not None and dist.get_rank() not in base:
+            self._world_mesh = None
+            return None
         self._world_mesh = DeviceMesh.from_group(
-            dist.group.WORLD, dev, mesh=torch.arange(self.world_size, dtype=torch.int), mesh_dim_names=("world",)
+            world_pg, dev, mesh=torch.tensor(all_ranks, dtype=torch.int), mesh_dim_names=("world",)
         )
         active = [k for k, v in self._meshes.items() if v is not None]
         logger.info(f"Successfully created meshes with active dimensions: {active}")
@@ -257,8 +298,7 @@ class ParallelDims:
                 break
         else:
             raise ValueError(f"Invalid mesh name combinations {list(dims)} (homes {homes}).")
-        me = dist.get_rank()
-        ranks = grid.group_ranks(me, dims)
+        ranks = self._global(grid.group_ranks(self._me(), dims))
         order = sorted(dims, key=grid.names.index)
         if list(order) != list(dims):
             raise ValueError(f"mesh dims must be requested in grid order {order}, got {list(dims)}")
