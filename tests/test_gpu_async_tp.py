@@ -55,6 +55,54 @@ def _worker(rank, world):
     }
 
 
+def _rs_worker(rank, world):
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    from torchtitan_b200.ops import native
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.parallel.async_tp import AsyncTP
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, ep=1, etp=1, world_size=world)
+    atp = AsyncTP.maybe_create(pd.get_mesh("tp"))
+    assert atp is not None
+    torch.manual_seed(0)
+    S, K, N = 2048, 1536, 1024
+    h_full = torch.randn(1, S, K, device="cuda").bfloat16()
+    w_full = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    ks = slice(rank * K // world, (rank + 1) * K // world)
+    h = h_full[..., ks].clone().requires_grad_()
+    w = w_full[:, ks].clone().requires_grad_()
+    assert atp.rs_supported(h, w)
+    rows = slice(rank * S // world, (rank + 1) * S // world)
+    errs = []
+    for it in range(4):                       # several calls: both staging buffers, counters keep counting
+        y = atp.linear_rs(h * (it + 1), w)
+        want = ((h_full.float() * (it + 1)) @ w_full.float().t())[:, rows]
+        errs.append(((y.float() - want).abs().max() / want.abs().max()).item())
+    g_full = torch.randn(1, S, N, device="cuda").bfloat16()
+    dist.broadcast(g_full, src=0)
+    y.backward(g_full[:, rows])
+    torch.cuda.synchronize()
+    hr = h_full.detach().float().requires_grad_()
+    wr = w_full.detach().float().requires_grad_()
+    ((hr * 4) @ wr.t()).backward(g_full.float())
+    gh_ref, gw_ref = hr.grad[..., ks], wr.grad[:, ks]
+    return {
+        "fwd": max(errs), "gemm_err": native.lib().tt_gemm_error(),
+        "gw": ((w.grad.float() - gw_ref).abs().max() / gw_ref.abs().max()).item(),
+        "gh": ((h.grad.float() - gh_ref).abs().max() / gh_ref.abs().max()).item(),
+    }
+
+
+def test_fused_linear_reduce_scatter_two_gpus(tmp_path):
+    _need_two()
+    for o in run_ranks(_rs_worker, 2, tmp_path=tmp_path):
+        assert o["gemm_err"] == 0, o
+        assert o["fwd"] < 1e-2 and o["gw"] < 2e-2 and o["gh"] < 2e-2, o
+
+
 def test_fused_allgather_linear_two_gpus(tmp_path):
     _need_two()
     for o in run_ranks(_worker, 2, tmp_path=tmp_path):

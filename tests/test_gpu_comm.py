@@ -124,3 +124,41 @@ def _fused_case(L, W, rows_local, K, N):
         assert (ready == 1).all()
         err = (out.float() - want).abs().max() / want.abs().max()
         assert err < 1e-2, err
+
+
+def test_fused_gemm_reduce_scatter_single_gpu_emulation(L):
+    """GEMM with the reduce-scatter in its epilogue, the "ranks" being local buffers. Launches run one after another and
+    none waits on a later one: all ranks but the last contribute only, the last one also reduces its own rows; the next
+    call (counters keep counting) rotates which rank goes last."""
+    if not hasattr(L, "tt_gemm_reduce_scatter"):
+        pytest.skip("library built without tt_gemm_reduce_scatter")
+    _rs_case(L, 2, 512, 256, 768)        # whole 256-row tiles per rank: CTA-pair kernel
+    _rs_case(L, 4, 128, 192, 264)        # single-CTA tile kernel, ragged N tile
+    _rs_case(L, 1, 256, 128, 512)        # one rank: staging round trip only
+
+
+def _rs_case(L, W, rows_per_rank, Kshard, N):
+    torch.manual_seed(1)
+    M = W * rows_per_rank
+    stream = torch.cuda.current_stream().cuda_stream
+    A = [torch.randn(M, Kshard, device="cuda").bfloat16() for _ in range(W)]
+    B = [(torch.randn(N, Kshard, device="cuda") * 0.1).bfloat16() for _ in range(W)]
+    parts = [a.float() @ b.float().t() for a, b in zip(A, B)]
+    want = sum(p.bfloat16().float() for p in parts)          # contributions are rounded to bf16 before the sum
+    stages = [torch.full((W, rows_per_rank, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(W)]
+    counts = [torch.zeros(W * (rows_per_rank // 128), dtype=torch.int32, device="cuda") for _ in range(W)]
+    sp, k1 = _ptr_array(stages)
+    cp, k2 = _ptr_array(counts)
+    for call in range(1, W + 1):
+        last = (call - 1) % W
+        order = [r for r in range(W) if r != last] + [last]
+        out = torch.full((rows_per_rank, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        for r in order:
+            rc = L.tt_gemm_reduce_scatter(A[r].data_ptr(), B[r].data_ptr(), sp, cp, out.data_ptr(), W, r, M, N, Kshard,
+                                          Kshard, 0, Kshard, call, 4 if r == last else 0, stream)
+            assert rc == 0
+        torch.cuda.synchronize()
+        assert L.tt_gemm_error() == 0
+        ref = want[last * rows_per_rank : (last + 1) * rows_per_rank]
+        err = (out.float() - ref).abs().max() / ref.abs().max()
+        assert err < 1e-2, (W, call, err)

@@ -54,6 +54,15 @@ struct GemmArgs {
   int* panel_ready;            // local flags, one per panel (same array as ready_flags)
   long long panel_bytes;
   int panels_per_rank, gather_world, gather_rank, gather_expected;
+  // fused reduce-scatter (same launch): the epilogue stores every output tile as bf16 into the staging slot
+  // [this rank] of the rank that owns those rows (peer-mapped stores) and bumps that owner's per-panel counter; the
+  // trailing `copy_ctas` CTAs sum the slots of this rank's own rows in rank order once all contributions arrived.
+  int rs_world, rs_rank;
+  void* rs_stage[16];          // staging buffer [world][rows_per_rank][N] bf16 on every rank (peer-mapped)
+  int* rs_count[16];           // counters [world][panels_per_rank] on every rank (peer-mapped)
+  void* rs_out;                // local result [rows_per_rank, N] bf16
+  int rs_rows_per_rank;
+  int rs_target;               // counter value that means "all warps of all column tiles of this call have stored"
   // 8-bit float operands (e4m3/e5m2, both K-major): `bk` contraction elements per stage (128 instead of 64) and an
   // epilogue that multiplies by the dequantisation scales: scale_mode 1 = one scale per tensor (pointers to scalars),
   // 2 = one per row of A and one per row of B (= output column).
@@ -102,10 +111,22 @@ __device__ __forceinline__ void apply_scales(const GemmArgs& p, float sa, int co
   }
 }
 
+__device__ __forceinline__ void store_chunk_to(const GemmArgs& p, void* Cbase, int row, int col, const uint32_t (&r)[32]);
+
 __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
+  if (p.rs_world > 0) {
+    // reduce-scatter epilogue: row -> (owner, row inside the owner's slice); slot of this rank in the owner's staging
+    const int owner = row / p.rs_rows_per_rank, local = row - owner * p.rs_rows_per_rank;
+    store_chunk_to(p, p.rs_stage[owner], p.rs_rank * p.rs_rows_per_rank + local, col, r);
+  } else {
+    store_chunk_to(p, p.C, row, col, r);
+  }
+}
+
+__device__ __forceinline__ void store_chunk_to(const GemmArgs& p, void* Cbase, int row, int col, const uint32_t (&r)[32]) {
   const bool full_chunk = (col + 32 <= p.N);
         if (p.c_fp32) {
-          float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          float* dst = reinterpret_cast<float*>(Cbase) + static_cast<long long>(row) * p.ldc + col;
           if (full_chunk && (p.ldc % 4 == 0)) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -123,7 +144,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col,
               dst[j] = __uint_as_float(r[j]) + (p.accumulate ? dst[j] : 0.f);
           }
         } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cbase) + static_cast<long long>(row) * p.ldc + col;
           if (full_chunk && (p.ldc % 8 == 0)) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -170,6 +191,60 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 }
 __device__ __forceinline__ void st_release_gpu(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// After the stores of one 128-row panel part by one epilogue warp: make them visible system-wide, then bump the owner's
+// counter for (this rank, panel).
+__device__ __forceinline__ void rs_publish(const GemmArgs& p, int first_row) {
+  const int owner = first_row / p.rs_rows_per_rank;
+  const int panel = (first_row - owner * p.rs_rows_per_rank) / BM;
+  __threadfence_system();
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0)
+    atomicAdd_system(p.rs_count[owner] + p.rs_rank * (p.rs_rows_per_rank / BM) + panel, 1);
+}
+
+// Reduce role of the fused GEMM -> reduce-scatter: aux CTA `c` handles own panels c, c + copy_ctas, ...; for each it waits
+// (bounded) until every source rank's counter reached the target, then adds the W staging slots in rank order in fp32.
+__device__ void reduce_panels(const GemmArgs& p, int c) {
+  __shared__ int s_ok;
+  const int panels = p.rs_rows_per_rank / BM;
+  const int* counts = p.rs_count[p.rs_rank];
+  const __nv_bfloat16* stage = static_cast<const __nv_bfloat16*>(p.rs_stage[p.rs_rank]);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.rs_out);
+  for (int panel = c; panel < panels; panel += p.copy_ctas) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const uint64_t t0 = tt::globaltimer_ns();
+      for (int src = 0; src < p.rs_world && ok; ++src) {
+        while (ld_acquire_sys(counts + src * panels + panel) < p.rs_target) {
+          if (tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) { atomicCAS(&g_gemm_error, 0, 8); ok = 0; break; }
+          __nanosleep(500);
+        }
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const long long slot = static_cast<long long>(p.rs_rows_per_rank) * p.N;
+    const long long base = static_cast<long long>(panel) * BM * p.N;
+    const long long n8 = static_cast<long long>(BM) * p.N / 8;
+    for (long long i = threadIdx.x; i < n8; i += NUM_THREADS) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int src = 0; src < p.rs_world; ++src) {
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + src * slot + base + i * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+      }
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+      *reinterpret_cast<uint4*>(out + base + i * 8) = o;
+    }
+    __syncthreads();
+  }
 }
 
 // Copy role of the fused all-gather GEMM. Copy CTA `c` handles panels c, c + copy_ctas, ... of a list that starts with
@@ -260,7 +335,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int gemm_ctas = static_cast<int>(gridDim.x) - p.copy_ctas;
 
   if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-    gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
+    if (p.rs_world > 0) reduce_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+    else gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
     return;
   }
 
@@ -399,6 +475,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
         store_chunk(p, row, col, r);
       }
+      if (p.rs_world > 0 && tm * BM + ew * 32 < p.M) rs_publish(p, tm * BM);
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive(tempty_bar(acc));
@@ -449,7 +526,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
   if (cluster_id >= num_clusters) {
     // fused all-gather: the trailing clusters only move data (both CTAs), see gather_panels
-    gather_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters, smem_raw);
+    if (p.rs_world > 0) reduce_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters);
+    else gather_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters, smem_raw);
     return;
   }
 
@@ -578,6 +656,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
         store_chunk(p, row, col, r);
       }
+      if (p.rs_world > 0) rs_publish(p, tm * TM + static_cast<int>(rank) * 128);
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive_cluster(acc ? leader_tempty1 : leader_tempty0);
@@ -637,7 +716,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate;
   p.ready_flags = ready_flags; p.ready_value = ready_value;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
-  p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr;
+  p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr; p.rs_world = 0;
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
@@ -688,7 +767,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
   p.ready_flags = nullptr; p.ready_value = 0;
   p.fp8 = 1; p.bk = BK8; p.scale_mode = scale_mode; p.scale_a = scale_a; p.scale_b = scale_b;
-  p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr;
+  p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr; p.rs_world = 0;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
@@ -742,7 +821,7 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
   p.ready_flags = panel_ready; p.ready_value = ready_value; p.panel_ready = panel_ready;
-  p.flags_by_m = 1;
+  p.flags_by_m = 1; p.rs_world = 0;
   p.panels_per_rank = M / BM / world;
   p.gather_world = world; p.gather_rank = rank; p.gather_expected = expected;
   p.gather_dst = A;
@@ -766,6 +845,68 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
     p.m_rot = rank * p.panels_per_rank;
+    int gemm_ctas = p.tiles_m * p.tiles_n;
+    if (gemm_ctas > g_num_sms - p.copy_ctas) gemm_ctas = g_num_sms - p.copy_ctas;
+    gemm_bf16_kernel<false><<<gemm_ctas + p.copy_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Fused GEMM -> reduce-scatter for row-parallel layers: every rank computes the partial product P = A[M,K] . B[N,K]^T (or
+// B stored [K,N] with b_mn) of its K-shard; rank r ends up with sum over ranks of P[r*M/world : (r+1)*M/world] in
+// `out` [M/world, N] bf16. `stages[r]` / `counts[r]` are rank r's staging buffer ([world][M/world][N] bf16) and counters
+// ([world][M/world/128] int32, zero at allocation, never reset) as mapped here; `call_index` counts the calls made on
+// these buffers (1, 2, ...) -- the same on every rank. Tiles owned by other ranks are computed first. `reduce_ctas`
+// CTAs of the launch (rounded up to even; 0 = none, contribute only) do the reduction.
+int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, int* const* counts, void* out, int world,
+                           int rank, int M, int N, int K, long long lda, int b_mn, long long ldb, int call_index,
+                           int reduce_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > 16 || rank < 0 || rank >= world) return -6;
+  if (M % (world * BM) || (N % 8) || (lda % 8) || (ldb % 8)) return -2;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    set_kernel_attrs();
+  }
+  const bool use_pair = g_pair_enabled && (M % (world * pair::TM) == 0) && N >= 256;
+  CUtensorMap ta, tb;
+  int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK);
+  if (rc) return rc;
+  if (!b_mn) rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, use_pair ? 128 : BN, BK);
+  else       rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  GemmArgs p;
+  p.M = M; p.N = N; p.K = K;
+  p.k_iters = (K + BK - 1) / BK;
+  p.a_mn = 0; p.b_mn = b_mn;
+  p.C = nullptr; p.ldc = N; p.c_fp32 = 0; p.accumulate = 0;
+  p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
+  p.ready_flags = nullptr; p.ready_value = 0; p.panel_ready = nullptr; p.flags_by_m = 0;
+  p.rs_world = world; p.rs_rank = rank; p.rs_out = out; p.rs_rows_per_rank = M / world;
+  for (int r = 0; r < 16; ++r) { p.rs_stage[r] = r < world ? stages[r] : nullptr; p.rs_count[r] = r < world ? counts[r] : nullptr; }
+  // reduce_ctas <= 0: contribute only (the reduction of this rank's rows is left to a later call on the same counters)
+  if (reduce_ctas < 0) reduce_ctas = 0;
+  reduce_ctas = (reduce_ctas + 1) & ~1;
+  if (reduce_ctas > g_num_sms / 2) reduce_ctas = (g_num_sms / 2) & ~1;
+  p.copy_ctas = reduce_ctas;
+  const int tiles_n_256 = (N + 255) / 256;
+  // per (source, 128-row panel): 4 epilogue warps per 256-wide column tile (both tile kernels use 256 columns)
+  p.rs_target = call_index * tiles_n_256 * 4;
+  if (use_pair) {
+    p.tiles_m = M / pair::TM;
+    p.tiles_n = (N + pair::TN - 1) / pair::TN;
+    p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, 0, b_mn);
+    p.m_rot = ((rank + 1) % world) * (p.tiles_m / world);
+    int clusters = p.tiles_m * p.tiles_n;
+    if (clusters > (g_num_sms - p.copy_ctas) / 2) clusters = (g_num_sms - p.copy_ctas) / 2;
+    pair::gemm_bf16_pair_kernel<false><<<clusters * 2 + p.copy_ctas, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+  } else {
+    p.tiles_m = M / BM;
+    p.tiles_n = (N + BN - 1) / BN;
+    p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
+    p.m_rot = ((rank + 1) % world) * (p.tiles_m / world);
     int gemm_ctas = p.tiles_m * p.tiles_n;
     if (gemm_ctas > g_num_sms - p.copy_ctas) gemm_ctas = g_num_sms - p.copy_ctas;
     gemm_bf16_kernel<false><<<gemm_ctas + p.copy_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);

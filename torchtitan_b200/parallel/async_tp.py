@@ -11,6 +11,13 @@ buffer, so the other projections of the block (``w3`` next to ``w1``) read it wi
 Buffers are double-buffered per shape and versioned by a job-wide call counter; a rank overwrites a slice only after it
 has seen the peers' flags of the following version, which they publish after their own fused kernel finished reading.
 
+The mirror image closes a row-parallel layer (``w2``, ``wo``): ``tt_gemm_reduce_scatter`` computes the partial product of
+this rank's K-shard and its epilogue stores each output tile, as bf16, straight into the staging slot of the rank that
+owns those rows (peer stores over NVLink), remote-owned tiles first; a few CTAs of the same launch add the slots of this
+rank's own rows in rank order as soon as every contribution of a 128-row panel has landed (per-panel counters bumped
+with system-scope atomics). Staging is double-buffered: a rank's call n+1 ends only after every peer contributed to
+call n+1, which they do after their call n, so the buffer of call n is free again when call n+2 starts.
+
 Backward uses the collective path (sequence all-gather for the weight gradient, reduce-scatter for the input gradient).
 """
 
@@ -41,6 +48,8 @@ class AsyncTP:
         self.version = 0
         self.panel_ready = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.fused_calls = 0
+        self._rs_bufs: dict[tuple[int, int], list] = {}
+        self.rs_calls = 0
 
     @classmethod
     def maybe_create(cls, tp_mesh):
@@ -96,6 +105,55 @@ class AsyncTP:
         self.fused_calls += 1
         return full.view(1, rows, K), out.view(1, rows, N)
 
+    # ---- GEMM -> reduce-scatter ----------------------------------------------------------------------------
+    REDUCE_CTAS = 8
+
+    def _rs_buffers(self, rows: int, N: int):
+        """Two (staging, counters) sets for outputs of ``rows`` x ``N``; each entry also counts its own calls."""
+        key = (rows, N)
+        if key not in self._rs_bufs:
+            out = []
+            panels = rows // self.world // 128
+            for _ in range(2):
+                soff = self.heap.alloc(rows * N * 2, align=1024)
+                coff = self.heap.alloc(self.world * panels * 4, align=256)
+                sp, sk = self.heap.peer_ptrs(soff)
+                cp, ck = self.heap.peer_ptrs(coff)
+                out.append({"stage": sp, "count": cp, "keep": (sk, ck), "calls": 0})
+            self._rs_bufs[key] = out
+        return self._rs_bufs[key]
+
+    def rs_supported(self, h: torch.Tensor, weight: torch.Tensor) -> bool:
+        rows = h.numel() // h.shape[-1]
+        return (native.has("tt_gemm_reduce_scatter") and h.is_cuda and h.dtype == torch.bfloat16
+                and weight.dtype == torch.bfloat16 and h.shape[0] == 1 and rows % (128 * self.world) == 0
+                and h.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0)
+
+    def linear_rs(self, h: torch.Tensor, weight: torch.Tensor):
+        """``h`` [1, S, K/tp] (this rank's feature shard), ``weight`` [N, K/tp] -> this rank's sequence slice
+        [1, S/tp, N] of ``sum over ranks (h @ weight^T)``."""
+        return _LinearRs.apply(h, weight, self)
+
+    def _forward_rs(self, h: torch.Tensor, weight: torch.Tensor):
+        L = native.lib()
+        K = h.shape[-1]
+        rows = h.numel() // K
+        N = weight.shape[0]
+        h2 = h.reshape(rows, K)
+        if h2.stride(-1) != 1 or h2.stride(0) % 8:
+            h2 = h2.contiguous()
+        w = weight.contiguous()
+        self.rs_calls += 1
+        buf = self._rs_buffers(rows, N)[self.rs_calls % 2]
+        buf["calls"] += 1
+        out = torch.empty(rows // self.world, N, dtype=torch.bfloat16, device=h.device)
+        native.check(L.tt_gemm_reduce_scatter(h2.data_ptr(), w.data_ptr(), buf["stage"], ctypes.cast(buf["count"], _PP),
+                                              out.data_ptr(), self.world, self.rank, rows, N, K, h2.stride(0), 0,
+                                              w.stride(0), buf["calls"], self.REDUCE_CTAS, _stream()),
+                     "tt_gemm_reduce_scatter")
+        self.fused_calls += 1
+        return out.view(1, rows // self.world, N)
+
     # ---- module hooks used by the tensor-parallel plan ---------------------------------------------------------
     def attach_ffn(self, ff) -> None:
         ff._async_tp = self
@@ -130,16 +188,40 @@ class _AgLinear(torch.autograd.Function):
         return gx.view_as(x), gw, None
 
 
+class _LinearRs(torch.autograd.Function):
+    """Row-parallel linear closed by the fused reduce-scatter; backward gathers the output gradient (collective)."""
+
+    @staticmethod
+    def forward(ctx, h, weight, atp: AsyncTP):
+        ctx.save_for_backward(h, weight)
+        ctx.atp = atp
+        return atp._forward_rs(h, weight)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from .tp import all_gather_seq
+
+        h, weight = ctx.saved_tensors
+        g_full = all_gather_seq(gy.contiguous(), ctx.atp.group).reshape(-1, gy.shape[-1])   # [S, N]
+        gh = (g_full @ weight).view_as(h)
+        gw = g_full.t() @ h.reshape(-1, h.shape[-1])
+        return gh, gw, None
+
+
 def fused_ffn_forward(ff, x_local, group):
     """SwiGLU feed-forward under sequence parallel with the all-gather fused into ``w1``; returns the partial-sum output
-    [1, S, D] (the caller reduce-scatters it)."""
+    [1, S, D] and False (the caller reduce-scatters it), or -- when the fused GEMM -> reduce-scatter applies to ``w2`` --
+    this rank's sequence slice [1, S/tp, D] and True."""
     from torchtitan_b200 import ops
 
     atp: AsyncTP = ff._async_tp
     xg, h1 = atp.ag_linear(x_local, ff.w1.weight)
     # w3 must use xg before the buffer is recycled; it is consumed right here. For backward it re-gathers (collective).
     h3 = _LinearOnGathered.apply(xg, x_local, ff.w3.weight, group)
-    return ff.w2(ops.swiglu(h1, h3))
+    h = ops.swiglu(h1, h3)
+    if getattr(ff.w2, "bias", None) is None and getattr(ff.w2, "quant", None) is None and atp.rs_supported(h, ff.w2.weight):
+        return atp.linear_rs(h, ff.w2.weight), True
+    return ff.w2(h), False
 
 
 class _LinearOnGathered(torch.autograd.Function):

@@ -157,10 +157,11 @@ class NvlinkComm(ShardComm):
         if int(flag.item()) == 0:
             logger.info("NVLink FSDP transport unavailable (no peer access); using c10d collectives")
             return None
-        nparams = sum(p.numel() for p in model.parameters()) if model is not None else 0
+        # a tied weight is reachable from two wrapped units and each keeps its own flat buffers: count it twice
+        nparams = sum(p.numel() for p in model.parameters(remove_duplicate=False)) if model is not None else 0
         nunits = 4 + (len(model.layers) if model is not None and hasattr(model, "layers") else 64)
         # shadow shard (2 B / W) + staging (2 B) per parameter, rounding slack per unit and per parameter
-        heap_bytes = int(2 * nparams * (1 + 1.0 / W)) + nunits * (1 << 20) + (64 << 20)
+        heap_bytes = int(2.05 * nparams * (1 + 1.0 / W)) + nunits * (1 << 20) + (64 << 20)
         return cls(mesh, heap_bytes)
 
     # ------------------------------------------------------------------ per-unit state

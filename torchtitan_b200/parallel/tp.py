@@ -351,7 +351,8 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
                     if _ff._async_tp.supported(x, _ff.w1.weight):
                         from .async_tp import fused_ffn_forward
 
-                        return _scatter(fused_ffn_forward(_ff, x, group), group)
+                        y, scattered = fused_ffn_forward(_ff, x, group)
+                        return y if scattered else _scatter(y, group)
                     return _scatter(inner(_gather(x, group)), group)
 
                 _wrap(ff, ffn_forward)

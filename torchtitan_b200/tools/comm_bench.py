@@ -3,6 +3,8 @@
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m torchtitan_b200.tools.comm_bench ag_gemm \\
         --seq 8192 --kdim 4096 --ndim 7168
 
+``gemm_rs``: row-parallel GEMM with the sequence reduce-scatter in its epilogue (``tt_gemm_reduce_scatter``) against the
+GEMM followed by NCCL reduce-scatter (``--kdim`` is the full contraction, split over the ranks).
 ``ag_gemm``: sequence all-gather fused into the consuming GEMM (``tt_gemm_allgather_a``) against NCCL all-gather followed
 by the same GEMM kernel, and against the GEMM alone on already gathered data (the lower bound). Times are CUDA events on
 the launching stream, maximum over ranks; an L2-sized buffer is overwritten between timed launches. The roofline target is
@@ -94,9 +96,55 @@ def bench_ag_gemm(args):
         }))
 
 
+def bench_gemm_rs(args):
+    """Row-parallel GEMM (K sharded) closed by a sequence reduce-scatter: one fused launch vs GEMM + NCCL."""
+    from torchtitan_b200.ops import cuda_ops, native
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.parallel.async_tp import AsyncTP
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, ep=1, etp=1, world_size=world)
+    atp = AsyncTP.maybe_create(pd.get_mesh("tp"))
+    assert atp is not None, "peer access / native library missing"
+    atp.REDUCE_CTAS = args.copy_ctas
+    S, K, N = args.seq, args.k // world, args.n          # K is the full contraction; each rank holds K / world
+    h = torch.randn(1, S, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    part = torch.empty(S, N, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(S // world, N, device="cuda", dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def fused():
+        atp._forward_rs(h, w)
+
+    def gemm_then_nccl():
+        cuda_ops.gemm_into(h.view(S, K), w, part)
+        dist.reduce_scatter_tensor(out, part)
+
+    def gemm_only():
+        cuda_ops.gemm_into(h.view(S, K), w, part)
+
+    t_fused = _time(fused, args.iters, flush)
+    t_nccl = _time(gemm_then_nccl, args.iters, flush)
+    t_gemm = _time(gemm_only, args.iters, flush)
+    peak, src = _peaks()
+    flops = 2.0 * S * N * K
+    remote_bytes = (world - 1) / world * S * N * 2
+    t_roof = max(flops / (peak * 1e12), remote_bytes / 770e9) * 1e3
+    if rank == 0:
+        print(json.dumps({
+            "case": "gemm_rs", "world": world, "S": S, "K_per_rank": K, "N": N, "reduce_ctas": args.copy_ctas,
+            "fused_ms": t_fused, "gemm_plus_nccl_reduce_scatter_ms": t_nccl, "gemm_only_ms": t_gemm,
+            "speedup_vs_nccl": t_nccl / t_fused, "roofline_ms": t_roof, "fraction_of_roofline": t_roof / t_fused,
+            "roofline_terms": {"compute_ms": flops / (peak * 1e12) * 1e3, "nvlink_ms": remote_bytes / 770e9 * 1e3,
+                               "peak_tflops": peak, "peak_source": f"of {src}"},
+            "kernel_errors": native.kernel_errors(),
+        }))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["ag_gemm"])
+    ap.add_argument("what", choices=["ag_gemm", "gemm_rs"])
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--kdim", dest="k", type=int, default=4096)
     ap.add_argument("--ndim", dest="n", type=int, default=7168)
@@ -107,7 +155,7 @@ def main():
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     try:
-        bench_ag_gemm(args)
+        (bench_ag_gemm if args.what == "ag_gemm" else bench_gemm_rs)(args)
     finally:
         dist.destroy_process_group()
 
