@@ -128,8 +128,8 @@ def _fused_case(L, W, rows_local, K, N):
 
 def test_fused_gemm_reduce_scatter_single_gpu_emulation(L):
     """GEMM with the reduce-scatter in its epilogue, the "ranks" being local buffers. Launches run one after another and
-    none waits on a later one: all ranks but the last contribute only, the last one also reduces its own rows; the next
-    call (counters keep counting) rotates which rank goes last."""
+    none waits on a later one: all ranks but the last contribute only (their own rows are left out), the last one also
+    computes and reduces its own rows; the next call (counters keep counting) rotates which rank goes last."""
     if not hasattr(L, "tt_gemm_reduce_scatter"):
         pytest.skip("library built without tt_gemm_reduce_scatter")
     _rs_case(L, 2, 512, 256, 768)        # whole 256-row tiles per rank: CTA-pair kernel
@@ -144,9 +144,9 @@ def _rs_case(L, W, rows_per_rank, Kshard, N):
     A = [torch.randn(M, Kshard, device="cuda").bfloat16() for _ in range(W)]
     B = [(torch.randn(N, Kshard, device="cuda") * 0.1).bfloat16() for _ in range(W)]
     parts = [a.float() @ b.float().t() for a, b in zip(A, B)]
-    want = sum(p.bfloat16().float() for p in parts)          # contributions are rounded to bf16 before the sum
+    want = sum(parts)
     stages = [torch.full((W, rows_per_rank, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(W)]
-    counts = [torch.zeros(W * (rows_per_rank // 128), dtype=torch.int32, device="cuda") for _ in range(W)]
+    counts = [torch.zeros(W * (rows_per_rank // 128) * ((N + 255) // 256), dtype=torch.int32, device="cuda") for _ in range(W)]
     sp, k1 = _ptr_array(stages)
     cp, k2 = _ptr_array(counts)
     for call in range(1, W + 1):
@@ -155,7 +155,7 @@ def _rs_case(L, W, rows_per_rank, Kshard, N):
         out = torch.full((rows_per_rank, N), float("nan"), device="cuda", dtype=torch.bfloat16)
         for r in order:
             rc = L.tt_gemm_reduce_scatter(A[r].data_ptr(), B[r].data_ptr(), sp, cp, out.data_ptr(), W, r, M, N, Kshard,
-                                          Kshard, 0, Kshard, call, 4 if r == last else 0, stream)
+                                          Kshard, 0, Kshard, call, 0 if r == last else 1, stream)
             assert rc == 0
         torch.cuda.synchronize()
         assert L.tt_gemm_error() == 0

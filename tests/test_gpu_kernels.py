@@ -244,6 +244,33 @@ def test_attention_range_masks(ops, kind, B, S, H, Hkv):
     assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
 
 
+@pytest.mark.parametrize("window", [None, 128])
+def test_attention_sinks(ops, window):
+    """Per-head attention sinks (a logit in the softmax denominator that carries no value), with and without a sliding
+    window, through the flash kernel vs the fp32 definition; the sink gradient comes from lse."""
+    from torchtitan_b200.ops import reference as ref
+
+    torch.manual_seed(2)
+    B, S, H, Hkv, D = 2, 512, 8, 2, 128
+    q = torch.randn(B, S, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    sinks = (torch.randn(H, device="cuda") * 2).requires_grad_()       # some above, some below the typical row maximum
+    o, lse = ops.attention(q, k, v, causal=True, window=window, sinks=sinks, return_lse=True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _no_kernel_errors()
+    qr, kr, vr, sr = (t.detach().float().requires_grad_() for t in (q, k, v, sinks))
+    orf, lser = ref.attention(qr, kr, vr, causal=True, window=window, sinks=sr, return_lse=True)
+    orf.backward(do.float())
+    assert _rel(o, orf) < 2e-2, _rel(o, orf)
+    assert (lse - lser).abs().max() < 2e-2
+    assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+    assert _rel(sinks.grad, sr.grad) < 3e-2, _rel(sinks.grad, sr.grad)
+
+
 @pytest.mark.parametrize("E,N,K,sizes", [
     (4, 256, 128, [64, 0, 192, 128]),
     (8, 768, 2048, [640, 64, 0, 128, 1024, 64, 320, 192]),

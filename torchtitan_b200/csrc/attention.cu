@@ -46,6 +46,10 @@ struct AttnArgs {
   // masks, sliding windows and fixed blocks. Tiles wholly outside the range are skipped.
   const int* row_lo;    // [B,Sq] or null
   const int* col_hi;    // [B,Sk] or null
+  // Optional attention sinks (forward only): one learned logit per query head that joins the softmax denominator and
+  // carries no value. The backward kernels need nothing extra: they rebuild the probabilities from lse, which includes
+  // the sink.
+  const float* sinks;   // [H] fp32 or null
 };
 
 // Write 64 fp32 values as one 128-byte bf16 row of a K-major, 128B-swizzled operand tile.
@@ -286,7 +290,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     if (ok && n_kv > 0) ok = tt::mbar_wait(bar(12), (n_kv - 1) & 1, abort_flag, &g_attn_error, 20);
     tt::tc_fence_after();
     if (ok) {
-      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      float o_scale = 1.f;
+      if (p.sinks != nullptr) {
+        // fold exp(sink) into the running (max, sum): the accumulated O keeps its old reference, so it is rescaled
+        // through `inv` below
+        const float s2 = __ldg(p.sinks + h) * kLog2e;
+        const float m_new = fmaxf(m_ref, s2);
+        const float f = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
+        l = l * f + fast_exp2(s2 - m_new);
+        o_scale = f;
+        m_ref = m_new;
+      }
+      const float inv = (l > 0.f) ? o_scale / l : 0.f;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) +
                             ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * D;
 #pragma unroll 1
@@ -714,6 +729,10 @@ int tt_attn_supported(int Sq, int Sk, int H, int Hkv, int Dh) { return check_sha
 int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo, int B, int Sq,
                       int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st);
 
+int tt_attn_fwd_sinks(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                      const float* sinks, int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal, float scale,
+                      cudaStream_t st);
+
 int tt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int H, int Hkv,
                 int Dh, int causal, float scale, cudaStream_t st) {
   return tt_attn_fwd_range(q, k, v, o, lse, nullptr, B, Sq, Sk, H, Hkv, Dh, causal, scale, st);
@@ -721,6 +740,13 @@ int tt_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse
 
 int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo, int B, int Sq,
                       int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st) {
+  return tt_attn_fwd_sinks(q, k, v, o, lse, row_lo, nullptr, B, Sq, Sk, H, Hkv, Dh, causal, scale, st);
+}
+
+// sinks (nullable, fp32 [H]): per-head logit added to the softmax denominator; lse includes it.
+int tt_attn_fwd_sinks(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                      const float* sinks, int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal, float scale,
+                      cudaStream_t st) {
   int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
   if (rc) return rc;
   if (row_lo && Sq != Sk) return -13;
@@ -729,7 +755,7 @@ int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, floa
   if ((rc = make_map(&tq, q, static_cast<long long>(B) * Sq, H, 128))) return rc;
   if ((rc = make_map(&tk, k, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
   if ((rc = make_map(&tv, v, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
-  AttnArgs p{B, Sq, Sk, H, Hkv, causal, scale, o, nullptr, lse, nullptr, row_lo, nullptr};
+  AttnArgs p{B, Sq, Sk, H, Hkv, causal, scale, o, nullptr, lse, nullptr, row_lo, nullptr, sinks};
   dim3 grid(Sq / 128, H, B);
   attn_fwd_kernel<<<grid, 192, FWD_SMEM, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -768,9 +794,9 @@ int tt_attn_bwd_range(const void* q, const void* k, const void* v, const void* o
   if ((rc = make_map(&tdo64, dout, static_cast<long long>(B) * Sq, H, 64))) return rc;
   if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
-  AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta, row_lo, col_hi};
+  AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta, row_lo, col_hi, nullptr};
   attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 320, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
-  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta, row_lo, col_hi};
+  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta, row_lo, col_hi, nullptr};
   attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 320, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

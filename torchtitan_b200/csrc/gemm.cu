@@ -47,6 +47,8 @@ struct GemmArgs {
   // memory over NVLink into the local buffer and publish one flag per panel; the GEMM CTAs wait for the panel they need.
   int flags_by_m;       // ready_flags index = m-tile (A operand gathered) instead of n-tile (B operand gathered)
   int m_rot;            // tiles visit m-panels starting at this offset (the local shard first)
+  int m_block;          // m-tiles per ordering block: all tiles of one block are visited before the next block (the fused
+                        // reduce-scatter sets it to the m-tiles per rank, so every peer-owned tile precedes the own ones)
   int copy_ctas;
   const void* gather_src[16];  // base of the gathered buffer on every rank (peer-mapped addresses)
   const int* gather_flag[16];  // rank r's "my slice is written" version flag
@@ -54,15 +56,18 @@ struct GemmArgs {
   int* panel_ready;            // local flags, one per panel (same array as ready_flags)
   long long panel_bytes;
   int panels_per_rank, gather_world, gather_rank, gather_expected;
-  // fused reduce-scatter (same launch): the epilogue stores every output tile as bf16 into the staging slot
-  // [this rank] of the rank that owns those rows (peer-mapped stores) and bumps that owner's per-panel counter; the
-  // trailing `copy_ctas` CTAs sum the slots of this rank's own rows in rank order once all contributions arrived.
+  // fused reduce-scatter (same launch): tiles whose rows another rank owns come first; their epilogue stores the bf16
+  // partial into slot [this rank] of the owner's staging buffer (peer-mapped stores) and bumps the owner's counter for
+  // (this rank, 128-row panel, 256-column tile). Tiles of this rank's own rows come last: their epilogue waits for the
+  // peers' counters, adds the staged partials to the fp32 accumulator in rank order and writes the final rows.
   int rs_world, rs_rank;
   void* rs_stage[16];          // staging buffer [world][rows_per_rank][N] bf16 on every rank (peer-mapped)
-  int* rs_count[16];           // counters [world][panels_per_rank] on every rank (peer-mapped)
+  int* rs_count[16];           // counters [world][panels_per_rank][tiles of 256 columns] on every rank (peer-mapped)
   void* rs_out;                // local result [rows_per_rank, N] bf16
   int rs_rows_per_rank;
-  int rs_target;               // counter value that means "all warps of all column tiles of this call have stored"
+  int rs_tiles_n;              // 256-column tiles per row panel
+  int rs_target;               // counter value that means "all 4 epilogue warps of this call have stored"
+  int rs_skip_own;             // contribute only: tiles of this rank's own rows are not computed
   // 8-bit float operands (e4m3/e5m2, both K-major): `bk` contraction elements per stage (128 instead of 64) and an
   // epilogue that multiplies by the dequantisation scales: scale_mode 1 = one scale per tensor (pointers to scalars),
   // 2 = one per row of A and one per row of B (= output column).
@@ -84,6 +89,15 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   int r = t - g * per_group;
   tm = first_m + r % gm;
   tn = r / gm;
+}
+
+// Tile t of the persistent schedule -> (tm, tn): blocks of `m_block` m-tiles one after another, the grouped order inside
+// a block, then the rotation.
+__device__ __forceinline__ void tile_coords_p(const GemmArgs& p, int t, int& tm, int& tn) {
+  const int blk_tiles = p.m_block * p.tiles_n;
+  const int blk = t / blk_tiles;
+  tile_coords(t - blk * blk_tiles, p.m_block, p.tiles_n, tm, tn);
+  tm = (tm + blk * p.m_block + p.m_rot) % p.tiles_m;
 }
 
 // Write 32 consecutive accumulator columns of one output row (bf16 or fp32, optional C += ...).
@@ -113,11 +127,48 @@ __device__ __forceinline__ void apply_scales(const GemmArgs& p, float sa, int co
 
 __device__ __forceinline__ void store_chunk_to(const GemmArgs& p, void* Cbase, int row, int col, const uint32_t (&r)[32]);
 
+template <bool RS>
 __device__ __forceinline__ void store_chunk(const GemmArgs& p, int row, int col, const uint32_t (&r)[32]) {
-  if (p.rs_world > 0) {
-    // reduce-scatter epilogue: row -> (owner, row inside the owner's slice); slot of this rank in the owner's staging
+  if constexpr (RS) {
+    // reduce-scatter epilogue: row -> (owner, row inside the owner's slice)
     const int owner = row / p.rs_rows_per_rank, local = row - owner * p.rs_rows_per_rank;
-    store_chunk_to(p, p.rs_stage[owner], p.rs_rank * p.rs_rows_per_rank + local, col, r);
+    if (owner != p.rs_rank) {
+      store_chunk_to(p, p.rs_stage[owner], p.rs_rank * p.rs_rows_per_rank + local, col, r);   // slot of this rank
+    } else {
+      // own rows: add the peers' staged partials (the caller waited for their counters) and write the result
+      float f[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = 0.f;
+      const bool full_chunk = (col + 32 <= p.N);
+      for (int src = 0; src < p.rs_world; ++src) {
+        if (src == p.rs_rank) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] += __uint_as_float(r[j]);
+          continue;
+        }
+        const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(p.rs_stage[p.rs_rank]) +
+                                  (static_cast<long long>(src) * p.rs_rows_per_rank + local) * p.N + col;
+        if (full_chunk) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 v = __ldcv(reinterpret_cast<const uint4*>(sp) + j);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x = __bfloat1622float2(h[e]);
+              f[8 * j + 2 * e] += x.x;
+              f[8 * j + 2 * e + 1] += x.y;
+            }
+          }
+        } else {
+          for (int j = 0; j < 32 && col + j < p.N; ++j) f[j] += __bfloat162float(sp[j]);
+        }
+      }
+      uint32_t o[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(f[j]);
+      store_chunk_to(p, p.rs_out, local, col, o);
+    }
   } else {
     store_chunk_to(p, p.C, row, col, r);
   }
@@ -193,58 +244,43 @@ __device__ __forceinline__ void st_release_gpu(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// After the stores of one 128-row panel part by one epilogue warp: make them visible system-wide, then bump the owner's
-// counter for (this rank, panel).
-__device__ __forceinline__ void rs_publish(const GemmArgs& p, int first_row) {
+// Reduce-scatter epilogue, once per (epilogue warp, output tile) before its stores. Rows owned by this rank: wait
+// (bounded) until every peer's counter for this panel and column tile reached the target, so that their staged partials
+// are visible. Returns false when the wait ran out (the error word is set; the tile's result is not meaningful).
+__device__ __forceinline__ bool rs_begin(const GemmArgs& p, int first_row, int tn) {
   const int owner = first_row / p.rs_rows_per_rank;
+  if (owner != p.rs_rank) return true;
   const int panel = (first_row - owner * p.rs_rows_per_rank) / BM;
+  const int panels = p.rs_rows_per_rank / BM;
+  const int lane = threadIdx.x & 31;
+  int ok = 1;
+  if (lane < p.rs_world && lane != p.rs_rank) {
+    const int* c = p.rs_count[p.rs_rank] + (lane * panels + panel) * p.rs_tiles_n + tn;
+    const uint64_t t0 = tt::globaltimer_ns();
+    while (ld_acquire_sys(c) < p.rs_target) {
+      if (tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) { atomicCAS(&g_gemm_error, 0, 8); ok = 0; break; }
+      __nanosleep(200);
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  return ok != 0;
+}
+
+// ... and once after them. Rows owned by a peer: make the stores visible system-wide, then bump the owner's counter.
+__device__ __forceinline__ void rs_end(const GemmArgs& p, int first_row, int tn) {
+  const int owner = first_row / p.rs_rows_per_rank;
+  if (owner == p.rs_rank) return;
+  const int panel = (first_row - owner * p.rs_rows_per_rank) / BM;
+  const int panels = p.rs_rows_per_rank / BM;
   __threadfence_system();
   __syncwarp();
   if ((threadIdx.x & 31) == 0)
-    atomicAdd_system(p.rs_count[owner] + p.rs_rank * (p.rs_rows_per_rank / BM) + panel, 1);
+    atomicAdd_system(p.rs_count[owner] + (p.rs_rank * panels + panel) * p.rs_tiles_n + tn, 1);
 }
 
-// Reduce role of the fused GEMM -> reduce-scatter: aux CTA `c` handles own panels c, c + copy_ctas, ...; for each it waits
-// (bounded) until every source rank's counter reached the target, then adds the W staging slots in rank order in fp32.
-__device__ void reduce_panels(const GemmArgs& p, int c) {
-  __shared__ int s_ok;
-  const int panels = p.rs_rows_per_rank / BM;
-  const int* counts = p.rs_count[p.rs_rank];
-  const __nv_bfloat16* stage = static_cast<const __nv_bfloat16*>(p.rs_stage[p.rs_rank]);
-  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.rs_out);
-  for (int panel = c; panel < panels; panel += p.copy_ctas) {
-    if (threadIdx.x == 0) {
-      int ok = 1;
-      const uint64_t t0 = tt::globaltimer_ns();
-      for (int src = 0; src < p.rs_world && ok; ++src) {
-        while (ld_acquire_sys(counts + src * panels + panel) < p.rs_target) {
-          if (tt::globaltimer_ns() - t0 > TT_WAIT_LIMIT_NS) { atomicCAS(&g_gemm_error, 0, 8); ok = 0; break; }
-          __nanosleep(500);
-        }
-      }
-      s_ok = ok;
-    }
-    __syncthreads();
-    if (!s_ok) return;
-    const long long slot = static_cast<long long>(p.rs_rows_per_rank) * p.N;
-    const long long base = static_cast<long long>(panel) * BM * p.N;
-    const long long n8 = static_cast<long long>(BM) * p.N / 8;
-    for (long long i = threadIdx.x; i < n8; i += NUM_THREADS) {
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int src = 0; src < p.rs_world; ++src) {
-        const uint4 v = *reinterpret_cast<const uint4*>(stage + src * slot + base + i * 8);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
-      }
-      uint4 o;
-      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-      *reinterpret_cast<uint4*>(out + base + i * 8) = o;
-    }
-    __syncthreads();
-  }
+// Contribute-only launches leave out the tiles of this rank's own rows (all roles skip the same tiles).
+__device__ __forceinline__ bool rs_skip_tile(const GemmArgs& p, int first_row) {
+  return p.rs_skip_own && first_row / p.rs_rows_per_rank == p.rs_rank;
 }
 
 // Copy role of the fused all-gather GEMM. Copy CTA `c` handles panels c, c + copy_ctas, ... of a list that starts with
@@ -311,7 +347,7 @@ __device__ void gather_panels(const GemmArgs& p, int c, uint8_t* smem_raw) {
   }
 }
 
-template <bool FP8>
+template <bool FP8, bool RS = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -335,8 +371,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int gemm_ctas = static_cast<int>(gridDim.x) - p.copy_ctas;
 
   if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-    if (p.rs_world > 0) reduce_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas);
-    else gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
+    gather_panels(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
     return;
   }
 
@@ -370,8 +405,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-        tm = (tm + p.m_rot) % p.tiles_m;
+        tile_coords_p(p, t, tm, tn);
+        if (RS && rs_skip_tile(p, tm * BM)) continue;
         if (p.ready_flags != nullptr) {
           // fused all-gather: wait until the copy CTAs have landed this n-tile of B locally
           uint64_t t0 = tt::globaltimer_ns();
@@ -421,6 +456,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t a_kadv = p.a_mn ? (UMMA_K * 128) : (UMMA_K * 2);  // bytes per 16-wide k step
       const uint32_t b_kadv = p.b_mn ? (UMMA_K * 128) : (UMMA_K * 2);
       for (int t = blockIdx.x; t < num_tiles && ok; t += gemm_ctas, ++tile_it) {
+        if (RS && p.rs_skip_own) {
+          int tm, tn;
+          tile_coords_p(p, t, tm, tn);
+          if (rs_skip_tile(p, tm * BM)) { --tile_it; continue; }
+        }
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
         if (!tt::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, &g_gemm_error, 2)) break;
@@ -450,8 +490,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t tile_it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gemm_ctas, ++tile_it) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      tm = (tm + p.m_rot) % p.tiles_m;
+      tile_coords_p(p, t, tm, tn);
+      if (RS && rs_skip_tile(p, tm * BM)) { --tile_it; continue; }
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       if (!tt::mbar_wait(tfull_bar(acc), acc_ph, abort_flag, &g_gemm_error, 4)) break;
@@ -465,6 +505,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (p.scale_mode == 1) sa = __ldg(p.scale_a) * __ldg(p.scale_b);
         else if (p.scale_mode == 2 && row_ok) sa = __ldg(p.scale_a + row);
       }
+      if constexpr (RS) rs_begin(p, tm * BM, tn);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -473,9 +514,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
         if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
-        store_chunk(p, row, col, r);
+        store_chunk<RS>(p, row, col, r);
       }
-      if (p.rs_world > 0 && tm * BM + ew * 32 < p.M) rs_publish(p, tm * BM);
+      if constexpr (RS) rs_end(p, tm * BM, tn);
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive(tempty_bar(acc));
@@ -502,7 +543,7 @@ constexpr int PSTAGES = 6;
 constexpr uint32_t PA_BYTES = 128 * BK * 2, PB_BYTES = 128 * BK * 2;  // per CTA per stage
 constexpr size_t PSMEM_BYTES = 1024 + PSTAGES * (PA_BYTES + PB_BYTES) + 256;
 
-template <bool FP8>
+template <bool FP8, bool RS = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -526,8 +567,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
   if (cluster_id >= num_clusters) {
     // fused all-gather: the trailing clusters only move data (both CTAs), see gather_panels
-    if (p.rs_world > 0) reduce_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters);
-    else gather_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters, smem_raw);
+    gather_panels(p, static_cast<int>(blockIdx.x) - 2 * num_clusters, smem_raw);
     return;
   }
 
@@ -552,8 +592,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-        tm = (tm + p.m_rot) % p.tiles_m;
+        tile_coords_p(p, t, tm, tn);
+        if (RS && rs_skip_tile(p, tm * TM)) continue;
         const int m0 = tm * TM + rank * 128, n0 = tn * TN + rank * 128;
         if (p.ready_flags != nullptr) {
           // fused all-gather of A: this CTA's 128 rows are panel 2 * tm + rank
@@ -601,6 +641,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       const uint32_t a_kadv = p.a_mn ? (UMMA_K * 128) : (UMMA_K * 2);
       const uint32_t b_kadv = p.b_mn ? (UMMA_K * 128) : (UMMA_K * 2);
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_it) {
+        if (RS && p.rs_skip_own) {
+          int tm, tn;
+          tile_coords_p(p, t, tm, tn);
+          if (rs_skip_tile(p, tm * TM)) { --tile_it; continue; }
+        }
         const int acc = tile_it & 1;
         const uint32_t acc_ph = (tile_it >> 1) & 1;
         if (!tt::mbar_wait(tempty_bar(acc), acc_ph ^ 1, abort_flag, &g_gemm_error, 12)) break;
@@ -631,8 +676,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     const uint32_t leader_tempty0 = tt::mapa(tempty_bar(0), 0), leader_tempty1 = tt::mapa(tempty_bar(1), 0);
     for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_it) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-      tm = (tm + p.m_rot) % p.tiles_m;
+      tile_coords_p(p, t, tm, tn);
+      if (RS && rs_skip_tile(p, tm * TM)) { --tile_it; continue; }
       const int acc = tile_it & 1;
       const uint32_t acc_ph = (tile_it >> 1) & 1;
       if (!tt::mbar_wait(tfull_bar(acc), acc_ph, abort_flag, &g_gemm_error, 14)) break;
@@ -646,6 +691,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (p.scale_mode == 1) sa = __ldg(p.scale_a) * __ldg(p.scale_b);
         else if (p.scale_mode == 2 && row_ok) sa = __ldg(p.scale_a + row);
       }
+      if constexpr (RS) rs_begin(p, tm * TM + static_cast<int>(rank) * 128, tn);
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         uint32_t r[32];
@@ -654,9 +700,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         const int col = n0 + c * 32;
         if (!row_ok || col >= p.N) continue;
         if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
-        store_chunk(p, row, col, r);
+        store_chunk<RS>(p, row, col, r);
       }
-      if (p.rs_world > 0) rs_publish(p, tm * TM + static_cast<int>(rank) * 128);
+      if constexpr (RS) rs_end(p, tm * TM + static_cast<int>(rank) * 128, tn);
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive_cluster(acc ? leader_tempty1 : leader_tempty0);
@@ -678,6 +724,8 @@ void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
   cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
   cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+  cudaFuncSetAttribute(gemm_bf16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+  cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
 }
 
 }  // namespace
@@ -720,6 +768,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, a_mn, b_mn);
     int clusters = p.tiles_m * p.tiles_n;
@@ -728,6 +777,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     pair::gemm_bf16_pair_kernel<false><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = (M + BM - 1) / BM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
     int grid = p.tiles_m * p.tiles_n;
@@ -770,6 +820,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
   p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr; p.rs_world = 0;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_f8(pair::TM, pair::TN, a_e5m2, b_e5m2);
     int clusters = p.tiles_m * p.tiles_n;
@@ -777,6 +828,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
     pair::gemm_bf16_pair_kernel<true><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = (M + BM - 1) / BM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_f8(BM, BN, a_e5m2, b_e5m2);
     int grid = p.tiles_m * p.tiles_n;
@@ -834,6 +886,7 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
   // all CTAs must be co-resident (GEMM CTAs wait on flags written by copy CTAs): one CTA per SM, grid <= SM count
   if (use_pair) {
     p.tiles_m = M / pair::TM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, 0, b_mn);
     p.m_rot = rank * (p.panels_per_rank / 2);
@@ -842,6 +895,7 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
     pair::gemm_bf16_pair_kernel<false><<<clusters * 2 + p.copy_ctas, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = M / BM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
     p.m_rot = rank * p.panels_per_rank;
@@ -855,12 +909,12 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
 // Fused GEMM -> reduce-scatter for row-parallel layers: every rank computes the partial product P = A[M,K] . B[N,K]^T (or
 // B stored [K,N] with b_mn) of its K-shard; rank r ends up with sum over ranks of P[r*M/world : (r+1)*M/world] in
 // `out` [M/world, N] bf16. `stages[r]` / `counts[r]` are rank r's staging buffer ([world][M/world][N] bf16) and counters
-// ([world][M/world/128] int32, zero at allocation, never reset) as mapped here; `call_index` counts the calls made on
-// these buffers (1, 2, ...) -- the same on every rank. Tiles owned by other ranks are computed first. `reduce_ctas`
-// CTAs of the launch (rounded up to even; 0 = none, contribute only) do the reduction.
+// ([world][M/world/128][ceil(N/256)] int32, zero at allocation, never reset) as mapped here; `call_index` counts the
+// calls made on these buffers (1, 2, ...) -- the same on every rank. Tiles owned by other ranks are computed first;
+// `contribute_only` leaves this rank's own rows out (single-GPU emulation of several ranks, launch after launch).
 int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, int* const* counts, void* out, int world,
                            int rank, int M, int N, int K, long long lda, int b_mn, long long ldb, int call_index,
-                           int reduce_ctas, cudaStream_t stream) {
+                           int contribute_only, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (world < 1 || world > 16 || rank < 0 || rank >= world) return -6;
   if (M % (world * BM) || (N % 8) || (lda % 8) || (ldb % 8)) return -2;
@@ -886,30 +940,30 @@ int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, in
   p.ready_flags = nullptr; p.ready_value = 0; p.panel_ready = nullptr; p.flags_by_m = 0;
   p.rs_world = world; p.rs_rank = rank; p.rs_out = out; p.rs_rows_per_rank = M / world;
   for (int r = 0; r < 16; ++r) { p.rs_stage[r] = r < world ? stages[r] : nullptr; p.rs_count[r] = r < world ? counts[r] : nullptr; }
-  // reduce_ctas <= 0: contribute only (the reduction of this rank's rows is left to a later call on the same counters)
-  if (reduce_ctas < 0) reduce_ctas = 0;
-  reduce_ctas = (reduce_ctas + 1) & ~1;
-  if (reduce_ctas > g_num_sms / 2) reduce_ctas = (g_num_sms / 2) & ~1;
-  p.copy_ctas = reduce_ctas;
-  const int tiles_n_256 = (N + 255) / 256;
-  // per (source, 128-row panel): 4 epilogue warps per 256-wide column tile (both tile kernels use 256 columns)
-  p.rs_target = call_index * tiles_n_256 * 4;
+  p.copy_ctas = 0;
+  p.rs_skip_own = contribute_only;
+  p.rs_tiles_n = (N + 255) / 256;      // both tile kernels use 256 columns
+  p.rs_target = call_index * 4;        // 4 epilogue warps store each (128-row panel, column tile)
   if (use_pair) {
     p.tiles_m = M / pair::TM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, 0, b_mn);
-    p.m_rot = ((rank + 1) % world) * (p.tiles_m / world);
+    p.m_block = p.tiles_m / world;
+    p.m_rot = ((rank + 1) % world) * p.m_block;
     int clusters = p.tiles_m * p.tiles_n;
-    if (clusters > (g_num_sms - p.copy_ctas) / 2) clusters = (g_num_sms - p.copy_ctas) / 2;
-    pair::gemm_bf16_pair_kernel<false><<<clusters * 2 + p.copy_ctas, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+    if (clusters > g_num_sms / 2) clusters = g_num_sms / 2;
+    pair::gemm_bf16_pair_kernel<false, true><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = M / BM;
+    p.m_block = p.tiles_m;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
-    p.m_rot = ((rank + 1) % world) * (p.tiles_m / world);
+    p.m_block = p.tiles_m / world;
+    p.m_rot = ((rank + 1) % world) * p.m_block;
     int gemm_ctas = p.tiles_m * p.tiles_n;
-    if (gemm_ctas > g_num_sms - p.copy_ctas) gemm_ctas = g_num_sms - p.copy_ctas;
-    gemm_bf16_kernel<false><<<gemm_ctas + p.copy_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+    if (gemm_ctas > g_num_sms) gemm_ctas = g_num_sms;
+    gemm_bf16_kernel<false, true><<<gemm_ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -291,18 +291,22 @@ def swiglu(gate: Tensor, up: Tensor) -> Tensor:
 # =============================================================================== attention
 @torch.library.custom_op("tt_b200::attention_fwd", mutates_args=())
 def attention_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float,
-                  row_lo: Tensor | None = None) -> tuple[Tensor, Tensor]:
+                  row_lo: Tensor | None = None, sinks: Tensor | None = None) -> tuple[Tensor, Tensor]:
     B, Sq, H, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     o = torch.empty_like(q)
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    if sinks is not None:
+        _ck(_lib().tt_attn_fwd_sinks(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo),
+                                     sinks.data_ptr(), B, Sq, Sk, H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd_sinks")
+        return o, lse
     _ck(_lib().tt_attn_fwd_range(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo), B, Sq, Sk,
                                  H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd")
     return o, lse
 
 
 @attention_fwd.register_fake
-def _(q, k, v, causal, scale, row_lo=None):
+def _(q, k, v, causal, scale, row_lo=None, sinks=None):
     return torch.empty_like(q), q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32)
 
 
@@ -326,19 +330,27 @@ def _(q, k, v, o, do, lse, causal, scale, row_lo=None, col_hi=None):
 
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale, row_lo=None, col_hi=None):
+    def forward(ctx, q, k, v, causal, scale, row_lo=None, col_hi=None, sinks=None):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, causal, scale, row_lo)
-        ctx.save_for_backward(q, k, v, o, lse, row_lo, col_hi)
+        s32 = None if sinks is None else sinks.detach().float().contiguous()
+        o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, causal, scale, row_lo, s32)
+        ctx.save_for_backward(q, k, v, o, lse, row_lo, col_hi, sinks)
         ctx.causal, ctx.scale = causal, scale
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, _dlse):
-        q, k, v, o, lse, row_lo, col_hi = ctx.saved_tensors
-        dq, dk, dv = torch.ops.tt_b200.attention_bwd(q, k, v, o, do.contiguous(), lse, ctx.causal, ctx.scale, row_lo, col_hi)
-        return dq, dk, dv, None, None, None, None
+        q, k, v, o, lse, row_lo, col_hi, sinks = ctx.saved_tensors
+        do = do.contiguous()
+        dq, dk, dv = torch.ops.tt_b200.attention_bwd(q, k, v, o, do, lse, ctx.causal, ctx.scale, row_lo, col_hi)
+        dsinks = None
+        if sinks is not None and ctx.needs_input_grad[7]:
+            # the sink has probability exp(sink - lse) and no value: d sink = - sum_i p_sink,i * (dO_i . O_i)
+            delta = (do.float() * o.float()).sum(-1).transpose(1, 2)                     # [B,H,S]
+            p_sink = torch.exp(sinks.float().view(1, -1, 1) - lse)
+            dsinks = -(p_sink * delta).sum((0, 2)).to(sinks.dtype)
+        return dq, dk, dv, None, None, None, None, dsinks
 
 
 def range_bounds(doc_ids: Tensor | None, window: int | None, B: int, S: int, device) -> tuple[Tensor, Tensor]:
@@ -368,18 +380,21 @@ def attention_supported(q: Tensor, k: Tensor) -> bool:
 
 def attention(q, k, v, *, causal=True, scale=None, window=None, doc_ids=None, sinks=None, return_lse=False):
     """Flash attention kernel for causal / full attention and for causal attention restricted to documents and/or a
-    sliding window (contiguous key ranges); attention sinks and unsupported shapes take the PyTorch definition."""
+    sliding window (contiguous key ranges), with optional per-head attention sinks; unsupported shapes take the PyTorch
+    definition."""
     ranged = window is not None or doc_ids is not None
-    ok = sinks is None and k.dtype == q.dtype and attention_supported(q, k)
+    ok = k.dtype == q.dtype and attention_supported(q, k)
+    if ok and sinks is not None:
+        ok = native.has("tt_attn_fwd_sinks")
     if ok and ranged:
         ok = bool(causal) and q.shape[1] == k.shape[1]
     if ok:
         scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
         if ranged:
             lo, hi = range_bounds(doc_ids, window, q.shape[0], q.shape[1], q.device)
-            o, lse = _AttnFn.apply(q, k, v, True, scale, lo, hi)
+            o, lse = _AttnFn.apply(q, k, v, True, scale, lo, hi, sinks)
         else:
-            o, lse = _AttnFn.apply(q, k, v, bool(causal), scale)
+            o, lse = _AttnFn.apply(q, k, v, bool(causal), scale, None, None, sinks)
         return (o, lse) if return_lse else o
     warn_once(logger, f"attention shape/mask q={tuple(q.shape)} k={tuple(k.shape)} dtype={q.dtype} "
                       f"window={window} doc={doc_ids is not None} sinks={sinks is not None} takes the PyTorch path")

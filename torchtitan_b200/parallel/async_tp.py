@@ -13,9 +13,9 @@ has seen the peers' flags of the following version, which they publish after the
 
 The mirror image closes a row-parallel layer (``w2``, ``wo``): ``tt_gemm_reduce_scatter`` computes the partial product of
 this rank's K-shard and its epilogue stores each output tile, as bf16, straight into the staging slot of the rank that
-owns those rows (peer stores over NVLink), remote-owned tiles first; a few CTAs of the same launch add the slots of this
-rank's own rows in rank order as soon as every contribution of a 128-row panel has landed (per-panel counters bumped
-with system-scope atomics). Staging is double-buffered: a rank's call n+1 ends only after every peer contributed to
+owns those rows (peer stores over NVLink), remote-owned tiles first, and bumps the owner's counter for that tile with a
+system-scope atomic; the tiles of this rank's own rows come last, and their epilogue waits for the peers' counters, adds
+the staged partials to the fp32 accumulator in rank order and writes the final rows. Staging is double-buffered: a rank's call n+1 ends only after every peer contributed to
 call n+1, which they do after their call n, so the buffer of call n is free again when call n+2 starts.
 
 Backward uses the collective path (sequence all-gather for the weight gradient, reduce-scatter for the input gradient).
@@ -106,8 +106,6 @@ class AsyncTP:
         return full.view(1, rows, K), out.view(1, rows, N)
 
     # ---- GEMM -> reduce-scatter ----------------------------------------------------------------------------
-    REDUCE_CTAS = 8
-
     def _rs_buffers(self, rows: int, N: int):
         """Two (staging, counters) sets for outputs of ``rows`` x ``N``; each entry also counts its own calls."""
         key = (rows, N)
@@ -116,7 +114,7 @@ class AsyncTP:
             panels = rows // self.world // 128
             for _ in range(2):
                 soff = self.heap.alloc(rows * N * 2, align=1024)
-                coff = self.heap.alloc(self.world * panels * 4, align=256)
+                coff = self.heap.alloc(self.world * panels * ((N + 255) // 256) * 4, align=256)
                 sp, sk = self.heap.peer_ptrs(soff)
                 cp, ck = self.heap.peer_ptrs(coff)
                 out.append({"stage": sp, "count": cp, "keep": (sk, ck), "calls": 0})
@@ -149,7 +147,7 @@ class AsyncTP:
         out = torch.empty(rows // self.world, N, dtype=torch.bfloat16, device=h.device)
         native.check(L.tt_gemm_reduce_scatter(h2.data_ptr(), w.data_ptr(), buf["stage"], ctypes.cast(buf["count"], _PP),
                                               out.data_ptr(), self.world, self.rank, rows, N, K, h2.stride(0), 0,
-                                              w.stride(0), buf["calls"], self.REDUCE_CTAS, _stream()),
+                                              w.stride(0), buf["calls"], 0, _stream()),
                      "tt_gemm_reduce_scatter")
         self.fused_calls += 1
         return out.view(1, rows // self.world, N)

@@ -106,7 +106,6 @@ def bench_gemm_rs(args):
     pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, ep=1, etp=1, world_size=world)
     atp = AsyncTP.maybe_create(pd.get_mesh("tp"))
     assert atp is not None, "peer access / native library missing"
-    atp.REDUCE_CTAS = args.copy_ctas
     S, K, N = args.seq, args.k // world, args.n          # K is the full contraction; each rank holds K / world
     h = torch.randn(1, S, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
@@ -133,7 +132,7 @@ def bench_gemm_rs(args):
     t_roof = max(flops / (peak * 1e12), remote_bytes / 770e9) * 1e3
     if rank == 0:
         print(json.dumps({
-            "case": "gemm_rs", "world": world, "S": S, "K_per_rank": K, "N": N, "reduce_ctas": args.copy_ctas,
+            "case": "gemm_rs", "world": world, "S": S, "K_per_rank": K, "N": N,
             "fused_ms": t_fused, "gemm_plus_nccl_reduce_scatter_ms": t_nccl, "gemm_only_ms": t_gemm,
             "speedup_vs_nccl": t_nccl / t_fused, "roofline_ms": t_roof, "fraction_of_roofline": t_roof / t_fused,
             "roofline_terms": {"compute_ms": flops / (peak * 1e12) * 1e3, "nvlink_ms": remote_bytes / 770e9 * 1e3,
