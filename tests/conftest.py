@@ -21,3 +21,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _own_rendezvous_port(monkeypatch):
+    """In-process single-rank trainers rendezvous on MASTER_PORT: give every test its own free port so that tests can run
+    side by side (pytest-xdist) and a lingering socket of the previous test never collides."""
+    if "MASTER_PORT" not in os.environ:
+        import socket
+
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            monkeypatch.setenv("MASTER_PORT", str(s.getsockname()[1]))
+    yield

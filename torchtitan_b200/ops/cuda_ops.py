@@ -797,12 +797,47 @@ def sample(logits: Tensor, temperature: float, uniforms: Tensor) -> tuple[Tensor
 
 
 # =============================================================================== float8 GEMM (csrc/gemm.cu, kind::f8f6f4)
+def quantize_fp8_operand(x: Tensor, rowwise: bool, dtype=torch.float8_e4m3fn):
+    """Quantise a 2-D bf16 GEMM operand ``x`` [R, K] along its last (contraction) dimension with the native kernels and
+    return (q [R, K] contiguous, scale): one scale per row (power of two) when ``rowwise`` else one per tensor.
+    ``x`` may be a transposed view of a row-major matrix: then the transposing kernels are used, so no copy of the
+    high-precision operand is made. Returns None when the layout or shape is not covered."""
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or not native.has("tt_fp8_quant_rows"):
+        return None
+    R, K = x.shape
+    e5m2 = int(dtype == torch.float8_e5m2)
+    L = _lib()
+    q = torch.empty(R, K, dtype=dtype, device=x.device)
+    if x.stride(1) == 1 and x.stride(0) % 8 == 0 and K % 8 == 0 and x.data_ptr() % 16 == 0:
+        if rowwise:
+            scale = torch.empty(R, dtype=torch.float32, device=x.device)
+            _ck(L.tt_fp8_quant_rows(x.data_ptr(), x.stride(0), R, K, q.data_ptr(), scale.data_ptr(), e5m2, 1, _stream()),
+                "tt_fp8_quant_rows")
+        else:
+            scale = torch.empty(1, dtype=torch.float32, device=x.device)
+            _ck(L.tt_fp8_quant_tensor(x.data_ptr(), x.stride(0), R, K, q.data_ptr(), scale.data_ptr(), 0, e5m2, _stream()),
+                "tt_fp8_quant_tensor")
+        return q, scale
+    if x.stride(0) == 1 and x.stride(1) % 8 == 0 and R % 8 == 0 and K % 16 == 0 and x.data_ptr() % 16 == 0:
+        # x = m^T for the row-major m [K, R]: contraction runs down the columns of m
+        if rowwise:
+            scale = torch.empty(R, dtype=torch.float32, device=x.device)
+            _ck(L.tt_fp8_quant_cols(x.data_ptr(), x.stride(1), K, R, q.data_ptr(), scale.data_ptr(), e5m2, 1, _stream()),
+                "tt_fp8_quant_cols")
+        else:
+            scale = torch.empty(1, dtype=torch.float32, device=x.device)
+            _ck(L.tt_fp8_quant_tensor(x.data_ptr(), x.stride(1), K, R, q.data_ptr(), scale.data_ptr(), 1, e5m2, _stream()),
+                "tt_fp8_quant_tensor")
+        return q, scale
+    return None
+
+
 def gemm_fp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:
     """``(qa [M,K] @ qb [N,K]^T) * sa * sb`` with float8 operands; ``sa``/``sb`` are scalars (tensorwise) or hold one
     scale per row of ``qa`` / ``qb`` (rowwise). fp32 accumulation in TMEM, scales applied in the epilogue."""
     M, K = qa.shape
     N = qb.shape[0]
-    if K % 16 or qa.stride(-1) != 1 or qb.stride(-1) != 1:
+    if K % 16:
         acc = qa.float() @ qb.float().t()
         return (acc * sa.reshape(-1, 1) * sb.reshape(1, -1)).to(out_dtype)
     qa, qb = qa.contiguous(), qb.contiguous()

@@ -53,14 +53,19 @@ def _fp8_mm(a: torch.Tensor, b_t: torch.Tensor, axis_mode: str, out_dtype, grad:
     """``a [M,K] @ b_t[N,K]^T`` with both operands quantised along K."""
     axis = None if axis_mode == "tensorwise" else -1
     a_dtype = torch.float8_e5m2 if (grad and axis_mode == "tensorwise") else torch.float8_e4m3fn
-    qa, sa = quantize_fp8(a, axis, a_dtype)
-    qb, sb = quantize_fp8(b_t, axis)
     from . import native
 
     if a.is_cuda and native.has("tt_gemm_fp8"):
-        from .cuda_ops import gemm_fp8
+        from .cuda_ops import gemm_fp8, quantize_fp8_operand
 
+        # native quantisation writes operands contiguous along the contraction whatever the view's layout
+        qa_sa = quantize_fp8_operand(a, axis is not None, a_dtype)
+        qb_sb = quantize_fp8_operand(b_t, axis is not None, torch.float8_e4m3fn)
+        qa, sa = qa_sa if qa_sa is not None else quantize_fp8(a, axis, a_dtype)
+        qb, sb = qb_sb if qb_sb is not None else quantize_fp8(b_t, axis)
         return gemm_fp8(qa, qb, sa, sb, out_dtype)
+    qa, sa = quantize_fp8(a, axis, a_dtype)
+    qb, sb = quantize_fp8(b_t, axis)
     acc = qa.float() @ qb.float().t()
     sa2 = sa if axis is None else sa.reshape(-1, 1)
     sb2 = sb if axis is None else sb.reshape(1, -1)
