@@ -84,3 +84,42 @@ def test_sampler_greedy_and_multinomial(dtype):
     assert (freq - torch.softmax(small[0], -1)).abs().max() < 0.02
     t2, _ = serving.sample_top_p(logits, 1.0, 1.0, u)
     assert torch.equal(t2, cuda_ops.sample(logits, 1.0, u)[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sampler_nucleus(dtype):
+    """top-p sampling in the kernel (bisection on the logit key, no sort) vs the sorted definition: the token lies in
+    the nucleus, sits where the index-order CDF over the nucleus crosses u, and frequencies follow the renormalised
+    distribution."""
+    from torchtitan_b200.ops import cuda_ops, native, serving
+
+    if not native.has("tt_sample_top_p"):
+        pytest.skip("library built without tt_sample_top_p")
+    torch.manual_seed(0)
+    B, V = 64, 151936
+    logits = (torch.randn(B, V, device="cuda") * 3).to(dtype)
+    u = torch.rand(B, device="cuda")
+    lf = logits.float()
+    for temp, top_p in ((1.0, 0.9), (0.7, 0.5), (1.0, 0.05)):
+        tok, lp = cuda_ops.sample(logits, temp, u, top_p)
+        probs = torch.softmax(lf.double() / temp, -1)
+        # nucleus with slack on the cut: everything the strict definition keeps at top_p - eps must contain no outsider
+        loose = serving.nucleus_mask(probs, min(1.0, top_p + 1e-4))
+        assert loose.gather(1, tok.view(-1, 1)).all()
+        keep = serving.nucleus_mask(probs, top_p)
+        cdf = (probs * keep).cumsum(-1)
+        total = cdf[:, -1]
+        hi = cdf.gather(1, tok.view(-1, 1)).squeeze(1)
+        lo = hi - (probs * keep).gather(1, tok.view(-1, 1)).squeeze(1)
+        target = u.double() * total
+        inside = (target >= lo - 2e-4) & (target <= hi + 2e-4)
+        assert inside.float().mean() > 0.95, inside.float().mean()      # rows whose cut differs by one tie may shift
+        assert (lp - torch.log_softmax(lf, -1).gather(1, tok.view(-1, 1)).squeeze(1)).abs().max() < 1e-3
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device="cuda").repeat(20000, 1)      # p = .087 .237 .644 .032
+    tok, _ = cuda_ops.sample(small, 1.0, torch.rand(20000, device="cuda"), 0.8)          # nucleus = {2, 1}
+    freq = torch.bincount(tok, minlength=4).float() / 20000
+    p = torch.softmax(small[0], -1)
+    want = torch.tensor([0.0, p[1] / (p[1] + p[2]), p[2] / (p[1] + p[2]), 0.0], device="cuda")
+    assert (freq - want).abs().max() < 0.02, freq
+    t2, _ = serving.sample_top_p(small[:8], 1.0, 0.8, torch.rand(8, device="cuda"))
+    assert set(t2.tolist()) <= {1, 2}

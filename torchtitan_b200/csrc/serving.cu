@@ -181,6 +181,14 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 // ---------------------------------------------------------------------------------------------- sampler
 // One CTA per row. mode 0: greedy (argmax, lowest index on ties); mode 1: multinomial over softmax(logits / T) by inverse
 // CDF in *index order* driven by uniforms[row]. The reported log-probability is log_softmax(raw logits)[token] in fp32.
+// top_p < 1 restricts the draw to the nucleus: the tokens whose probability is at least that of the last token needed
+// to reach a cumulative mass of top_p when taken from the most likely down (ties at that value are all kept). The cut
+// is found without sorting: bisection over the order-preserving integer key of the logit for the smallest key k with
+// sum of p over {logit > k} < top_p.
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
 template <typename T>
 __device__ __forceinline__ float ld(const T* p, long long i);
 template <>
@@ -191,7 +199,7 @@ __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, long 
 template <typename T>
 __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ logits, const float* __restrict__ uniforms, long long* __restrict__ tokens,
-              float* __restrict__ logprobs, int V, long long ld_row, float inv_temp, int mode) {
+              float* __restrict__ logprobs, int V, long long ld_row, float inv_temp, int mode, float top_p) {
   const int row = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
   const T* x = logits + row * ld_row;
   __shared__ float s_val[1024];
@@ -244,6 +252,40 @@ sample_kernel(const T* __restrict__ logits, const float* __restrict__ uniforms, 
     if (tid == 0) { tokens[row] = gidx; logprobs[row] = -__logf(raw_total); }
     return;
   }
+  uint32_t kmin = 0;       // keys >= kmin are in the nucleus (0 keeps everything)
+  if (top_p < 1.f) {
+    // Z of the tempered distribution
+    s_tot[tid] = tem;
+    __syncthreads();
+    for (int o = nthr >> 1; o > 0; o >>= 1) { if (tid < o) s_tot[tid] += s_tot[tid + o]; __syncthreads(); }
+    const float mass = top_p * s_tot[0];
+    __syncthreads();
+    // smallest key k with S(k) = sum_{key(x) > k} e(x) < mass; S is non-increasing in k and S(key(max)) = 0 < mass
+    uint32_t lo_k = 0, hi_k = order_key(gmax);
+    while (lo_k < hi_k) {
+      const uint32_t mid = lo_k + ((hi_k - lo_k) >> 1);
+      float part = 0.f;
+      for (int i = lo; i < hi; ++i) {
+        const float v = ld<T>(x, i);
+        if (order_key(v) > mid) part += __expf((v - gmax) * inv_temp);
+      }
+      s_tot[tid] = part;
+      __syncthreads();
+      for (int o = nthr >> 1; o > 0; o >>= 1) { if (tid < o) s_tot[tid] += s_tot[tid + o]; __syncthreads(); }
+      const bool below = s_tot[0] < mass;
+      __syncthreads();
+      if (below) hi_k = mid; else lo_k = mid + 1;
+    }
+    kmin = lo_k;
+    // per-thread sums restricted to the nucleus
+    tem = 0.f;
+    for (int i = lo; i < hi; ++i) {
+      const float v = ld<T>(x, i);
+      if (order_key(v) >= kmin) tem += __expf((v - gmax) * inv_temp);
+    }
+    s_sum[tid] = tem;
+    __syncthreads();
+  }
   // inclusive scan of the per-thread temperature sums (Hillis-Steele over 1024 entries)
   for (int o = 1; o < nthr; o <<= 1) {
     const float add = tid >= o ? s_sum[tid - o] : 0.f;
@@ -255,14 +297,19 @@ sample_kernel(const T* __restrict__ logits, const float* __restrict__ uniforms, 
   const float target = uniforms[row] * total;
   const float before = tid > 0 ? s_sum[tid - 1] : 0.f;
   // the owner of the crossing: before <= target < s_sum[tid]; the last non-empty thread also takes target >= total
-  const bool last_nonempty = hi > lo && (hi == V);
+  // (with a nucleus the trailing threads may hold no mass: the last thread whose inclusive sum equals the total)
+  const bool last_nonempty = hi > lo && (top_p < 1.f ? (s_sum[tid] >= total && before < total) : (hi == V));
   if (hi > lo && before <= target && (target < s_sum[tid] || last_nonempty)) {
     float run = before;
-    int pick = hi - 1;
+    int pick = -1, last_kept = -1;
     for (int i = lo; i < hi; ++i) {
-      run += __expf((ld<T>(x, i) - gmax) * inv_temp);
+      const float v = ld<T>(x, i);
+      if (order_key(v) < kmin) continue;
+      last_kept = i;
+      run += __expf((v - gmax) * inv_temp);
       if (run > target) { pick = i; break; }
     }
+    if (pick < 0) pick = last_kept >= 0 ? last_kept : hi - 1;
     tokens[row] = pick;
     logprobs[row] = (ld<T>(x, pick) - gmax) - __logf(raw_total);
   }
@@ -307,16 +354,26 @@ int tt_paged_decode(const void* q, const void* kc, const void* vc, const int* bl
 }
 
 // dtype: 0 = fp32 logits, 1 = bf16 logits. temperature <= 0 selects greedy.
+int tt_sample_top_p(const void* logits, const float* uniforms, long long* tokens, float* logprobs, int B, int V,
+                    long long ld_row, float temperature, float top_p, int dtype, cudaStream_t st);
+
 int tt_sample(const void* logits, const float* uniforms, long long* tokens, float* logprobs, int B, int V, long long ld_row,
               float temperature, int dtype, cudaStream_t st) {
+  return tt_sample_top_p(logits, uniforms, tokens, logprobs, B, V, ld_row, temperature, 1.f, dtype, st);
+}
+
+// top_p in (0, 1]: nucleus sampling (1 = the whole vocabulary).
+int tt_sample_top_p(const void* logits, const float* uniforms, long long* tokens, float* logprobs, int B, int V,
+                    long long ld_row, float temperature, float top_p, int dtype, cudaStream_t st) {
   if (B <= 0) return 0;
+  if (!(top_p > 0.f)) return -2;
   const int mode = temperature > 0.f ? 1 : 0;
   const float inv_t = mode ? 1.f / temperature : 1.f;
   if (dtype == 0)
-    sample_kernel<float><<<B, 1024, 0, st>>>(static_cast<const float*>(logits), uniforms, tokens, logprobs, V, ld_row, inv_t, mode);
+    sample_kernel<float><<<B, 1024, 0, st>>>(static_cast<const float*>(logits), uniforms, tokens, logprobs, V, ld_row, inv_t, mode, top_p);
   else
     sample_kernel<__nv_bfloat16><<<B, 1024, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), uniforms, tokens, logprobs, V,
-                                                      ld_row, inv_t, mode);
+                                                      ld_row, inv_t, mode, top_p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

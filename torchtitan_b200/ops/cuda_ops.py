@@ -781,8 +781,8 @@ def paged_decode(q: Tensor, k_cache: Tensor, v_cache: Tensor, block_tables: Tens
     return out
 
 
-def sample(logits: Tensor, temperature: float, uniforms: Tensor) -> tuple[Tensor, Tensor]:
-    """Greedy (temperature <= 0) or index-order multinomial sampling; one CTA per row."""
+def sample(logits: Tensor, temperature: float, uniforms: Tensor, top_p: float = 1.0) -> tuple[Tensor, Tensor]:
+    """Greedy (temperature <= 0) or index-order multinomial / nucleus sampling; one CTA per row."""
     B, V = logits.shape
     if logits.dtype not in (torch.float32, torch.bfloat16):
         logits = logits.float()
@@ -791,6 +791,11 @@ def sample(logits: Tensor, temperature: float, uniforms: Tensor) -> tuple[Tensor
     tok = torch.empty(B, dtype=torch.int64, device=logits.device)
     lp = torch.empty(B, dtype=torch.float32, device=logits.device)
     u = uniforms.to(torch.float32).contiguous()
+    if top_p < 1.0 and temperature > 0.0:
+        _ck(_lib().tt_sample_top_p(logits.data_ptr(), u.data_ptr(), tok.data_ptr(), lp.data_ptr(), B, V, logits.stride(0),
+                                   float(temperature), float(top_p), int(logits.dtype == torch.bfloat16), _stream()),
+            "tt_sample_top_p")
+        return tok, lp
     _ck(_lib().tt_sample(logits.data_ptr(), u.data_ptr(), tok.data_ptr(), lp.data_ptr(), B, V, logits.stride(0), float(temperature),
                          int(logits.dtype == torch.bfloat16), _stream()), "tt_sample")
     return tok, lp

@@ -54,15 +54,17 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scal
 def sample_top_p(logits, temperature: float, top_p: float, uniforms):
     """Sample one token per row of ``logits [B, V]``.
 
-    ``uniforms [B]`` in [0, 1) drives the draw by inverse CDF -- over the vocabulary in index order when
-    ``top_p >= 1`` (plain multinomial sampling, no sort), over the probability-sorted nucleus otherwise -- so a
-    given (logits, uniform) pair yields the same token on every device up to rounding at CDF boundaries.
+    ``uniforms [B]`` in [0, 1) drives the draw by inverse CDF in vocabulary index order -- over the whole vocabulary
+    when ``top_p >= 1`` (plain multinomial sampling), over the nucleus otherwise -- so a given (logits, uniform) pair
+    yields the same token on every device up to rounding at CDF boundaries. The nucleus is the set of tokens at least as
+    likely as the last token needed to reach a cumulative mass of ``top_p`` from the most likely down (ties at that
+    probability are all kept).
     ``temperature == 0`` is greedy (lowest index on ties). Returns (tokens int64 [B], log-probabilities fp32 [B]); the log-probability is taken from the
     fp32 log-softmax of the *unscaled* logits, which is what the trainer recomputes."""
-    if logits.is_cuda and native.has("tt_sample") and (top_p >= 1.0 or temperature <= 0.0):
+    if logits.is_cuda and native.has("tt_sample") and (top_p >= 1.0 or temperature <= 0.0 or native.has("tt_sample_top_p")):
         from .cuda_ops import sample as native_sample
 
-        return native_sample(logits, temperature, uniforms)
+        return native_sample(logits, temperature, uniforms, top_p)
     lf = logits.float()
     logp_raw = torch.log_softmax(lf, dim=-1)
     if temperature <= 0.0:
@@ -74,13 +76,19 @@ def sample_top_p(logits, temperature: float, top_p: float, uniforms):
         target = uniforms.float().view(-1, 1) * cdf[:, -1:]
         tok = (cdf <= target).sum(-1).clamp(max=logits.shape[-1] - 1)
         return tok, logp_raw.gather(1, tok.view(-1, 1)).squeeze(1)
-    sp, si = probs.sort(dim=-1, descending=True, stable=True)
-    cum = sp.cumsum(-1)
-    keep = (cum - sp) < top_p                    # always keeps the most likely token
-    sp = sp * keep
-    cdf = sp.cumsum(-1)
+    keep = nucleus_mask(probs, top_p)
+    cdf = (probs * keep).cumsum(-1)
     target = uniforms.float().view(-1, 1) * cdf[:, -1:]
-    pos = (cdf <= target).sum(-1).clamp(max=logits.shape[-1] - 1)
-    pos = torch.minimum(pos, keep.sum(-1) - 1)
-    tok = si.gather(1, pos.view(-1, 1)).squeeze(1)
+    tok = (cdf <= target).sum(-1)
+    last_kept = logits.shape[-1] - 1 - keep.flip(-1).float().argmax(-1)
+    tok = torch.minimum(tok, last_kept)
     return tok, logp_raw.gather(1, tok.view(-1, 1)).squeeze(1)
+
+
+def nucleus_mask(probs, top_p: float):
+    """Boolean [B, V]: tokens whose probability is >= that of the last token taken when accumulating ``top_p`` of mass
+    from the most likely token down (the most likely token is always in)."""
+    sp, _ = probs.sort(dim=-1, descending=True)
+    taken = (sp.cumsum(-1) - sp) < top_p
+    cut = torch.where(taken, sp, torch.full_like(sp, float("inf"))).amin(-1, keepdim=True)
+    return probs >= cut
