@@ -404,3 +404,25 @@ def test_fp8_linear_uses_native_quantisation(ops):
         assert _rel(x.grad, xr.grad) < 8e-2, _rel(x.grad, xr.grad)
         assert _rel(w.grad, wr.grad) < 8e-2, _rel(w.grad, wr.grad)
     _no_kernel_errors()
+
+
+def test_mxfp8_quantise_kernels(ops):
+    """Native MXFP8 quantisation (e4m3 data, one E8M0 exponent per 32 elements of the contraction, RCEIL) of an operand
+    as stored and as a transposed view: exponents and codes equal the elementwise definition."""
+    from torchtitan_b200.ops import cuda_ops
+    from torchtitan_b200.ops.quant import dequantize_mxfp8, quantize_mxfp8
+
+    torch.manual_seed(0)
+    for R, K in [(256, 1024), (136, 96)]:
+        base = (torch.randn(R, K, device="cuda") * torch.exp(torch.randn(R, 1, device="cuda") * 4)).bfloat16()
+        base[5, :64] = 0                                               # all-zero blocks take the exponent floor
+        for x in (base, (torch.randn(K, R, device="cuda") * 5).bfloat16().t()):
+            got = cuda_ops.quantize_mxfp8_operand(x)
+            assert got is not None
+            q, sc = got
+            qr, sr = quantize_mxfp8(x.contiguous())
+            assert torch.equal(sc, sr), (sc.flatten()[:8], sr.flatten()[:8])
+            assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
+            back = dequantize_mxfp8(q, sc)
+            assert _rel(back, x.float()) < 5e-2
+    _no_kernel_errors()

@@ -181,6 +181,99 @@ cast_transpose_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, 
   }
 }
 
+// ------------------------------------------------------------------------------------------- MXFP8
+// e4m3 data with one E8M0 scale (biased exponent byte) per 32 consecutive elements of the contraction dimension.
+// RCEIL: exponent = ceil(log2(amax / 448)), clamped to [-127, 127], so no element saturates.
+__device__ __forceinline__ int mx_exponent(float amax) {
+  const float v = fmaxf(amax, 448.f * 1.17549435e-38f * 0.5f) / 448.f;   // floor 2^-127 * 448, as the definition
+  const uint32_t b = __float_as_uint(v);
+  int e = static_cast<int>((b >> 23) & 0xff) - 127;
+  if ((b >> 23) == 0) e = (b == 0x00400000u) ? -127 : -126;   // subnormal quotient: exactly 2^-127, or just above it
+  else if (b & 0x007fffffu) e += 1;
+  return max(-127, min(127, e));
+}
+
+// Rows: one thread per 32-element block (64 bytes in, 32 bytes + 1 scale byte out). K % 32 == 0.
+__global__ void __launch_bounds__(256)
+mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int K, uint8_t* __restrict__ q,
+                     uint8_t* __restrict__ scales) {
+  const int kb = K / 32;
+  const long long total = static_cast<long long>(M) * kb;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / kb;
+    const int b = static_cast<int>(i - r * kb);
+    const uint4* src = reinterpret_cast<const uint4*>(x + r * ld + b * 32);
+    uint4 v[4];
+    float mx = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = src[j];
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&v[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(__bfloat162float(h[e])));
+    }
+    const int ex = mx_exponent(mx);
+    const float inv = exp2f(static_cast<float>(-ex));
+    uint8_t o[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&v[j]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float y = fminf(fmaxf(__bfloat162float(h[e]) * inv, -E4M3_MAX), E4M3_MAX);
+        o[8 * j + e] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(q + r * static_cast<long long>(K) + b * 32);
+    dst[0] = *reinterpret_cast<const uint4*>(o);
+    dst[1] = *reinterpret_cast<const uint4*>(o + 16);
+    scales[r * kb + b] = static_cast<uint8_t>(ex + 127);
+  }
+}
+
+// Columns: qT [N, M] = transpose of x [M, N], blocks of 32 along M (the contraction of the transposed operand);
+// scales [N, M/32]. Tile of 128 rows (m) x 64 columns (n): per column four 32-row blocks. M % 32 == 0, N % 8 == 0.
+__global__ void __launch_bounds__(256)
+mx_quant_cols_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N, uint8_t* __restrict__ qT,
+                     uint8_t* __restrict__ scales) {
+  __shared__ __nv_bfloat16 s_x[128][64 + 8];
+  __shared__ uint8_t s_t[64][128 + 16];
+  const int n0 = blockIdx.x * 64, m0 = blockIdx.y * 128;
+  const int c8 = threadIdx.x & 7, rl = threadIdx.x >> 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = rl + 32 * i;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m0 + r < M && n0 + c8 * 8 < N) v = *reinterpret_cast<const uint4*>(x + (m0 + r) * ld + n0 + c8 * 8);
+    *reinterpret_cast<uint4*>(&s_x[r][c8 * 8]) = v;
+  }
+  __syncthreads();
+  // thread -> (column n = tid % 64, 32-row block blk = tid / 64)
+  const int n = threadIdx.x & 63, blk = threadIdx.x >> 6;
+  float mx = 0.f;
+#pragma unroll 8
+  for (int r = 0; r < 32; ++r) mx = fmaxf(mx, fabsf(__bfloat162float(s_x[blk * 32 + r][n])));
+  const int ex = mx_exponent(mx);
+  const float inv = exp2f(static_cast<float>(-ex));
+#pragma unroll 8
+  for (int r = 0; r < 32; ++r) {
+    const float y = fminf(fmaxf(__bfloat162float(s_x[blk * 32 + r][n]) * inv, -E4M3_MAX), E4M3_MAX);
+    s_t[n][blk * 32 + r] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
+  }
+  if (n0 + n < N && m0 + blk * 32 < M)
+    scales[(n0 + n) * static_cast<long long>(M / 32) + (m0 / 32 + blk)] = static_cast<uint8_t>(ex + 127);
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int seg = threadIdx.x + 256 * i;
+    const int nn = seg >> 3, part = seg & 7;
+    if (n0 + nn < N && m0 + part * 16 < M)
+      *reinterpret_cast<uint4*>(qT + (n0 + nn) * static_cast<long long>(M) + m0 + part * 16) =
+          *reinterpret_cast<const uint4*>(&s_t[nn][part * 16]);
+  }
+}
+
 int grid_for(long long work, int block) {
   long long g = (work + block - 1) / block;
   if (g > 148 * 16) g = 148 * 16;
@@ -241,6 +334,25 @@ int tt_fp8_quant_tensor(const void* x, long long ld, int M, int N, void* q, floa
     if (e5m2) cast_kernel<true><<<g, 256, 0, st>>>(xp, ld, M, N, qp, scale_out, 0);
     else      cast_kernel<false><<<g, 256, 0, st>>>(xp, ld, M, N, qp, scale_out, 0);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// MXFP8 along the rows' contiguous dimension: q [M,K] e4m3, scales [M, K/32] E8M0 bytes.
+int tt_mxfp8_quant_rows(const void* x, long long ld, int M, int K, void* q, void* scales, cudaStream_t st) {
+  if (M <= 0 || K <= 0) return 0;
+  if (K % 32 || ld % 8) return -2;
+  mx_quant_rows_kernel<<<grid_for(static_cast<long long>(M) * (K / 32), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), ld, M, K, static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales));
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// MXFP8 of the transposed operand: qT [N,M] e4m3 and scales [N, M/32] from x [M,N] (blocks run down the columns of x).
+int tt_mxfp8_quant_cols(const void* x, long long ld, int M, int N, void* qT, void* scales, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M % 32 || N % 8 || ld % 8) return -2;
+  dim3 g((N + 63) / 64, (M + 127) / 128);
+  mx_quant_cols_kernel<<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ld, M, N, static_cast<uint8_t*>(qT),
+                                          static_cast<uint8_t*>(scales));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

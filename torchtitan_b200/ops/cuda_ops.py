@@ -837,6 +837,27 @@ def quantize_fp8_operand(x: Tensor, rowwise: bool, dtype=torch.float8_e4m3fn):
     return None
 
 
+def quantize_mxfp8_operand(x: Tensor):
+    """MXFP8-quantise a 2-D bf16 GEMM operand ``x`` [R, K] along K (blocks of 32): returns (e4m3 [R, K] contiguous,
+    uint8 E8M0 scales [R, K/32]) or None when the layout is not covered. A transposed view of a row-major matrix goes
+    through the transposing kernel (no high-precision copy)."""
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or not native.has("tt_mxfp8_quant_rows"):
+        return None
+    R, K = x.shape
+    if K % 32 or x.data_ptr() % 16:
+        return None
+    L = _lib()
+    q = torch.empty(R, K, dtype=torch.float8_e4m3fn, device=x.device)
+    sc = torch.empty(R, K // 32, dtype=torch.uint8, device=x.device)
+    if x.stride(1) == 1 and x.stride(0) % 8 == 0:
+        _ck(L.tt_mxfp8_quant_rows(x.data_ptr(), x.stride(0), R, K, q.data_ptr(), sc.data_ptr(), _stream()), "tt_mxfp8_quant_rows")
+        return q, sc
+    if x.stride(0) == 1 and x.stride(1) % 8 == 0 and R % 8 == 0:
+        _ck(L.tt_mxfp8_quant_cols(x.data_ptr(), x.stride(1), K, R, q.data_ptr(), sc.data_ptr(), _stream()), "tt_mxfp8_quant_cols")
+        return q, sc
+    return None
+
+
 def gemm_fp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:
     """``(qa [M,K] @ qb [N,K]^T) * sa * sb`` with float8 operands; ``sa``/``sb`` are scalars (tensorwise) or hold one
     scale per row of ``qa`` / ``qb`` (rowwise). fp32 accumulation in TMEM, scales applied in the epilogue."""

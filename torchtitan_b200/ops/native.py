@@ -73,6 +73,9 @@ def lib():
     _sig(L.tt_moe_rowdot, [P, P, P, P, LL, I, I, P])
     _sig(L.tt_gemm_fp8, [P, P, P, I, I, I, LL, LL, LL, I, I, I, P, P, I, P])
     _sig(L.tt_gemm_allgather_a, [P, P, I, I, I, P, P, I, I, I, I, LL, LL, I, P, I, I, P])
+    if hasattr(L, "tt_mxfp8_quant_rows"):
+        _sig(L.tt_mxfp8_quant_rows, [P, LL, I, I, P, P, P])
+        _sig(L.tt_mxfp8_quant_cols, [P, LL, I, I, P, P, P])
     if hasattr(L, "tt_sample_top_p"):
         _sig(L.tt_sample_top_p, [P, P, P, P, I, I, LL, F, F, I, P])
     if hasattr(L, "tt_fp8_quant_rows"):

@@ -127,9 +127,15 @@ def _mx_mm(a: torch.Tensor, b_t: torch.Tensor, out_dtype):
     if pad:
         a = torch.nn.functional.pad(a, (0, pad))
         b_t = torch.nn.functional.pad(b_t, (0, pad))
-    qa, sa = quantize_mxfp8(a.contiguous())
-    qb, sb = quantize_mxfp8(b_t.contiguous())
     from . import native
+
+    qa_sa = qb_sb = None
+    if a.is_cuda and native.has("tt_mxfp8_quant_rows"):
+        from .cuda_ops import quantize_mxfp8_operand
+
+        qa_sa, qb_sb = quantize_mxfp8_operand(a), quantize_mxfp8_operand(b_t)
+    qa, sa = qa_sa if qa_sa is not None else quantize_mxfp8(a.contiguous())
+    qb, sb = qb_sb if qb_sb is not None else quantize_mxfp8(b_t.contiguous())
 
     if a.is_cuda and native.has("tt_gemm_mxfp8"):
         from .cuda_ops import gemm_mxfp8
