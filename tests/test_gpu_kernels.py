@@ -323,8 +323,17 @@ def test_moe_layer_native_grouped_path(ops):
     _no_kernel_errors()
     yr = ref_moe(xr)
     yr.square().sum().backward()
-    assert _rel(y.cpu(), yr) < 5e-2, _rel(y.cpu(), yr)
-    assert _rel(xg.grad.cpu(), xr.grad) < 8e-2, _rel(xg.grad.cpu(), xr.grad)
+    # a token whose two best scores are nearly tied may be routed differently by the two gate products: compare the
+    # tokens on whose experts both sides agree (nearly all of them)
+    with torch.no_grad():
+        _, idx_g, _ = moe.router(xg.detach().reshape(-1, 128), moe.expert_bias)
+        _, idx_r, _ = ref_moe.router(xr.detach().reshape(-1, 128), ref_moe.expert_bias)
+    same = (idx_g.cpu().sort(-1).values == idx_r.sort(-1).values).all(-1)
+    assert same.float().mean() > 0.98, same.float().mean()
+    yg, yc = y.detach().cpu().reshape(-1, 128)[same], yr.detach().reshape(-1, 128)[same]
+    assert _rel(yg, yc) < 5e-2, _rel(yg, yc)
+    gg, gc = xg.grad.cpu().reshape(-1, 128)[same], xr.grad.reshape(-1, 128)[same]
+    assert _rel(gg, gc) < 8e-2, _rel(gg, gc)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (512, 768, 1024), (300, 264, 208), (4096, 4096, 2048)])
@@ -426,3 +435,24 @@ def test_mxfp8_quantise_kernels(ops):
             back = dequantize_mxfp8(q, sc)
             assert _rel(back, x.float()) < 5e-2
     _no_kernel_errors()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 512), (384, 768, 1024), (200, 328, 224), (4096, 4096, 2048)])
+def test_gemm_mxfp8_block_scaled(ops, M, N, K):
+    """Block-scaled tcgen05 MXFP8 GEMM (scales applied by the MMA) vs the fp32 product of the dequantised operands."""
+    from torchtitan_b200.ops import native, quant
+
+    if not native.has("tt_gemm_mxfp8"):
+        pytest.skip("library built without tt_gemm_mxfp8")
+    torch.manual_seed(0)
+    # rows and K blocks of very different magnitude, so that a misplaced scale shows
+    a = torch.randn(M, K, device="cuda") * torch.exp2(torch.randint(-6, 7, (M, K // 32), device="cuda").float()).repeat_interleave(32, 1)
+    b = torch.randn(N, K, device="cuda") * torch.exp2(torch.randint(-6, 7, (N, K // 32), device="cuda").float()).repeat_interleave(32, 1)
+    qa, sa = quant.quantize_mxfp8(a.bfloat16())
+    qb, sb = quant.quantize_mxfp8(b.bfloat16())
+    want = quant.dequantize_mxfp8(qa, sa) @ quant.dequantize_mxfp8(qb, sb).t()
+    got = ops.gemm_mxfp8(qa, qb, sa, sb, torch.float32)
+    _no_kernel_errors()
+    assert _rel(got, want) < 1e-3, _rel(got, want)
+    got16 = ops.gemm_mxfp8(qa, qb, sa, sb, torch.bfloat16)
+    assert _rel(got16, want) < 1e-2

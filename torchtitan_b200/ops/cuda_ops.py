@@ -858,6 +858,25 @@ def quantize_mxfp8_operand(x: Tensor):
     return None
 
 
+def gemm_mxfp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:
+    """``qa [M,K] @ qb [N,K]^T`` for MXFP8 operands (e4m3 data, E8M0 scales [rows, K/32]) on the block-scaled tensor-core
+    path: the scales are re-laid into the MMA's 512-byte chunks and applied by the MMA itself."""
+    M, K = qa.shape
+    N = qb.shape[0]
+    L = _lib()
+    qa, qb = qa.contiguous(), qb.contiguous()
+    sa, sb = sa.contiguous(), sb.contiguous()
+    swa = torch.empty(L.tt_mx_scales_bytes(M, 128, K), dtype=torch.uint8, device=qa.device)
+    swb = torch.empty(L.tt_mx_scales_bytes(N, 256, K), dtype=torch.uint8, device=qa.device)
+    _ck(L.tt_mx_swizzle_scales(sa.data_ptr(), M, K, 128, swa.data_ptr(), _stream()), "tt_mx_swizzle_scales")
+    _ck(L.tt_mx_swizzle_scales(sb.data_ptr(), N, K, 256, swb.data_ptr(), _stream()), "tt_mx_swizzle_scales")
+    c_fp32 = out_dtype == torch.float32
+    out = torch.empty(M, N, dtype=torch.float32 if c_fp32 else torch.bfloat16, device=qa.device)
+    _ck(L.tt_gemm_mxfp8(qa.data_ptr(), qb.data_ptr(), swa.data_ptr(), swb.data_ptr(), out.data_ptr(), M, N, K, qa.stride(0),
+                        qb.stride(0), out.stride(0), int(c_fp32), _stream()), "tt_gemm_mxfp8")
+    return out if out.dtype == out_dtype else out.to(out_dtype)
+
+
 def gemm_fp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:
     """``(qa [M,K] @ qb [N,K]^T) * sa * sb`` with float8 operands; ``sa``/``sb`` are scalars (tensorwise) or hold one
     scale per row of ``qa`` / ``qb`` (rowwise). fp32 accumulation in TMEM, scales applied in the epilogue."""

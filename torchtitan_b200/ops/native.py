@@ -73,6 +73,11 @@ def lib():
     _sig(L.tt_moe_rowdot, [P, P, P, P, LL, I, I, P])
     _sig(L.tt_gemm_fp8, [P, P, P, I, I, I, LL, LL, LL, I, I, I, P, P, I, P])
     _sig(L.tt_gemm_allgather_a, [P, P, I, I, I, P, P, I, I, I, I, LL, LL, I, P, I, I, P])
+    if hasattr(L, "tt_gemm_mxfp8"):
+        _sig(L.tt_gemm_mxfp8, [P, P, P, P, P, I, I, I, LL, LL, LL, I, P])
+        _sig(L.tt_mx_swizzle_scales, [P, I, I, I, P, P])
+        L.tt_mx_scales_bytes.argtypes = [I, I, I]
+        L.tt_mx_scales_bytes.restype = LL
     if hasattr(L, "tt_mxfp8_quant_rows"):
         _sig(L.tt_mxfp8_quant_rows, [P, LL, I, I, P, P, P])
         _sig(L.tt_mxfp8_quant_cols, [P, LL, I, I, P, P, P])
@@ -125,4 +130,6 @@ def kernel_errors() -> dict:
     """Error words set by kernels whose bounded waits expired (reading clears them)."""
     L = lib()
     out = {"gemm": L.tt_gemm_error(), "attention": L.tt_attn_error(), "grouped_gemm": L.tt_grouped_gemm_error()}
+    if hasattr(L, "tt_gemm_mx_error"):
+        out["gemm_mx"] = L.tt_gemm_mx_error()
     return {k: v for k, v in out.items() if v}
