@@ -106,6 +106,15 @@ def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, lay
     return cfg.build()
 
 
+def _sac_mm_policy(trainer) -> str:
+    from torchtitan_b200.parallel import ac
+
+    mode = trainer.config.activation_checkpoint.per_op_sac_mm_policy
+    if mode == "auto":
+        return "all (auto: memory allows)" if ac._AUTO_KEEP_ALL else "every second (auto: memory bound)"
+    return mode
+
+
 def max_over_ranks(x: float) -> float:
     import torch
     import torch.distributed as dist
@@ -206,7 +215,8 @@ def run_ours(args) -> dict:
         "config": {
             "model": "Llama-3.1-8B", "global_batch": local_bs * world, "seq_len": SEQ_LEN,
             "parallelism": f"fsdp{world}" if world > 1 else "single-gpu (fp32 master + bf16 compute copy)",
-            "activation_checkpoint": f"{trainer.config.activation_checkpoint.mode}/{trainer.config.activation_checkpoint.selective_ac_option}",
+            "activation_checkpoint": f"{trainer.config.activation_checkpoint.mode}/{trainer.config.activation_checkpoint.selective_ac_option}"
+                                     f" (matmul outputs kept: {_sac_mm_policy(trainer)})",
             "optimizer": "AdamW fused over flat shards, grad clip 1.0",
             "l2_between_iterations": "inputs and weights (16 GB bf16 + activations) exceed the 126 MB L2; no explicit flush",
             "per_gpu": {"tokens_per_sec": value / world, "mfu_pct_of_2.25PF": 100 * flops_per_token * value / world / 2.25e15,

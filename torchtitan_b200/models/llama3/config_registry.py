@@ -101,6 +101,8 @@ def llama3_8b_synthetic() -> Trainer.Config:
     cfg.profiling = ProfilingConfig()
     cfg.metrics = MetricsProcessor.Config(log_freq=10)
     cfg.lr_scheduler = LRSchedulersContainer.Config(warmup_steps=200, decay_ratio=0.1, decay_type="linear")
+    # per-op SAC keeps every matmul output when the device has the room (sharded runs on 180 GB parts do)
+    cfg.activation_checkpoint.per_op_sac_mm_policy = "auto"
     return cfg
 
 

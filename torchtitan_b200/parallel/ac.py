@@ -108,6 +108,24 @@ def _apply_layer_sac(module, ac_config):
     return module
 
 
+_AUTO_KEEP_ALL: bool | None = None
+
+
+def _auto_keep_all_mm() -> bool:
+    """Decided once, at the first checkpointed forward (parameters, gradients and optimizer state are resident by then):
+    keep every matmul output when more than 35 % of the device memory is still free."""
+    global _AUTO_KEEP_ALL
+    if _AUTO_KEEP_ALL is None:
+        if torch.cuda.is_available():
+            free, total = torch.cuda.mem_get_info()
+            reusable = torch.cuda.memory_reserved() - torch.cuda.memory_allocated()   # cached blocks count as free
+            _AUTO_KEEP_ALL = (free + reusable) > 0.35 * total
+        else:
+            _AUTO_KEEP_ALL = False
+        logger.info(f"per-op SAC matmul policy (auto): {'all matmul outputs kept' if _AUTO_KEEP_ALL else 'every second matmul kept'}")
+    return _AUTO_KEEP_ALL
+
+
 def _apply_op_sac(module, ac_config, *, base_fqn=None, op_sac_save_list=None):
     save_list = op_sac_save_list or default_op_sac_save_list()
     mm_ops = _mm_ops()
@@ -121,7 +139,16 @@ def _apply_op_sac(module, ac_config, *, base_fqn=None, op_sac_save_list=None):
         out_f, in_f = sub.weight.shape
         force.add((in_f, out_f))
 
+    mm_mode = getattr(ac_config, "per_op_sac_mm_policy", "every_second")
+
+    def keep_all_mm() -> bool:
+        if mm_mode != "auto":
+            return mm_mode == "all"
+        return _auto_keep_all_mm()
+
     def make_policy(meta):
+        keep_all = keep_all_mm()
+
         def policy(ctx, func, *args, **kwargs):
             if (func == torch.ops.aten._to_copy.default and "cuda" in str(args[0].device)
                     and str(kwargs.get("device", "")) == "cpu"):
@@ -134,7 +161,7 @@ def _apply_op_sac(module, ac_config, *, base_fqn=None, op_sac_save_list=None):
                 if tuple(w) in force:
                     return CheckpointPolicy.PREFER_RECOMPUTE
                 meta[key] += 1
-            keep = func in save_list and not (func in mm_ops and meta[key] % 2 == 0)
+            keep = func in save_list and not (func in mm_ops and not keep_all and meta[key] % 2 == 0)
             return CheckpointPolicy.MUST_SAVE if keep else CheckpointPolicy.PREFER_RECOMPUTE
 
         return policy

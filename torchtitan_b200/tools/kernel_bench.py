@@ -82,6 +82,29 @@ def bench_gemm_fp8(args, timer):
     return res
 
 
+def bench_gemm_mxfp8(args, timer):
+    """MXFP8 GEMM on the block-scaled tcgen05 path (scales applied by the MMA), plus the quantise kernels that feed it
+    (bf16 -> e4m3 + E8M0, as stored and transposed) and the float8 rowwise quantise kernel, in GB/s of bf16 input."""
+    from torchtitan_b200.ops import cuda_ops
+
+    M, N, K = args.m, args.n, args.k
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    qa, sa = cuda_ops.quantize_mxfp8_operand(a)
+    qb, sb = cuda_ops.quantize_mxfp8_operand(b)
+    ms = timer.time(lambda: cuda_ops.gemm_mxfp8(qa, qb, sa, sb, torch.bfloat16), args.iters)
+    res = {"case": "gemm_mxfp8_block_scaled", "M": M, "N": N, "K": K, "ms": ms, "tflops": 2 * M * N * K / ms / 1e9}
+    at = torch.randn(K, M, device="cuda").bfloat16().t()
+    for name, fn in (("mx_quant_rows", lambda: cuda_ops.quantize_mxfp8_operand(a)),
+                     ("mx_quant_transposed", lambda: cuda_ops.quantize_mxfp8_operand(at)),
+                     ("fp8_quant_rows", lambda: cuda_ops.quantize_fp8_operand(a, True)),
+                     ("fp8_quant_transposed", lambda: cuda_ops.quantize_fp8_operand(at, True))):
+        t = timer.time(fn, args.iters)
+        res[name + "_ms"] = t
+        res[name + "_gbs_in"] = M * K * 2 / t / 1e6
+    return res
+
+
 def bench_ag_gemm(args, timer):
     """Fused all-gather GEMM on ONE GPU: the "peers" are local buffers whose flags are already published, so the copy CTAs
     and the GEMM CTAs of the single launch do all the work (intra-GPU copies stand in for NVLink loads)."""
@@ -216,7 +239,7 @@ def bench_elementwise(args, timer):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "gemm_fp8", "ag_gemm", "grouped_gemm", "paged_decode", "attention", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "gemm_fp8", "gemm_mxfp8", "ag_gemm", "grouped_gemm", "paged_decode", "attention", "elementwise"])
     ap.add_argument("--world", type=int, default=4)
     ap.add_argument("--copy-ctas", type=int, default=8)
     ap.add_argument("--experts", type=int, default=16)
@@ -242,6 +265,8 @@ def main():
         res = [bench_gemm(args, timer)]
     elif args.what == "gemm_fp8":
         res = [bench_gemm_fp8(args, timer)]
+    elif args.what == "gemm_mxfp8":
+        res = [bench_gemm_mxfp8(args, timer)]
     elif args.what == "ag_gemm":
         res = [bench_ag_gemm(args, timer)]
     elif args.what == "grouped_gemm":
