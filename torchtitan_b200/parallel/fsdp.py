@@ -447,7 +447,8 @@ class FSDPUnit:
         """Gradient of a whole parameter -> flat ``[W * chunk * inner]`` in ``dtype``."""
         W, n = self.shard_world, p.chunk_rows * p.inner
         if len(p.full_shape) == 0:
-            return g.reshape(1).to(dtype)
+            # a 0-dim parameter is replicated: every rank's chunk receives the sum over ranks
+            return g.reshape(1).to(dtype).repeat(W)
         if p.shard_dim == 0:
             if p.rows == W * p.chunk_rows:
                 return g.reshape(-1).to(dtype)

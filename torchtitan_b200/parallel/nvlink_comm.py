@@ -176,7 +176,7 @@ class NvlinkComm(ShardComm):
 
     def supports(self, unit: FSDPUnit) -> bool:
         return (unit.param_dtype == torch.bfloat16 and unit.orig_dtype == torch.float32 and unit.shard_world == self.world
-                and all(p.shard_dim == 0 for p in unit.params))
+                and all(p.shard_dim == 0 and len(p.full_shape) > 0 for p in unit.params))
 
     def alloc_shard_buffer(self, unit: FSDPUnit, dtype, kind: str):
         if kind != "shadow" or not self.supports(unit):
