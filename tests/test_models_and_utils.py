@@ -1,0 +1,174 @@
+"""Dense model families on CPU (forward shapes, determinism of initialisation, RoPE variants, attention masks, Hugging Face
+state-dict adapters) and small utilities (model: the reference's tests/unit_tests/test_rope.py, test_module.py,
+test_state_dict_adapter-style checks in scripts/checkpoint_conversion, test_utils)."""
+
+import dataclasses
+import gc
+
+import pytest
+import torch
+
+
+def _tiny(family: str, flavor: str):
+    import importlib
+
+    mod = importlib.import_module(f"torchtitan_b200.models.{family}")
+    cfg = dataclasses.replace(getattr(mod, f"{family}_configs")[flavor])
+    return cfg
+
+
+@pytest.mark.parametrize("family,flavor", [("llama3", "debugmodel"), ("llama3", "debugmodel_gqa"), ("qwen3", "debugmodel")])
+def test_dense_models_forward_backward_and_init_is_seeded(family, flavor):
+    cfg = _tiny(family, flavor)
+    torch.manual_seed(0)
+    a = cfg.build()
+    a.init_weights()
+    torch.manual_seed(0)
+    b = cfg.build()
+    b.init_weights()
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert torch.equal(p, q), n
+        assert torch.isfinite(p).all()
+    tok = torch.randint(0, cfg.vocab_size, (2, 24))
+    out = a(tok)
+    assert out.shape == (2, 24, cfg.vocab_size)
+    out.float().logsumexp(-1).mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in a.parameters() if p.requires_grad)
+    # causal: changing a later token leaves earlier logits untouched
+    tok2 = tok.clone()
+    tok2[:, -1] = (tok2[:, -1] + 1) % cfg.vocab_size
+    assert torch.allclose(a(tok2)[:, :-1], out[:, :-1].detach(), atol=1e-5)
+
+
+def test_model_flop_and_parameter_accounting():
+    cfg = _tiny("llama3", "debugmodel")
+    m = cfg.build()
+    nparams, flops = cfg.get_nparams_and_flops(m, seq_len=128)
+    assert nparams == sum(p.numel() for p in m.parameters())
+    # 6 * (non-embedding parameters) + attention term
+    emb = m.tok_embeddings.weight.numel()
+    assert flops > 6 * (nparams - emb)
+
+
+def test_rope_layouts_rotate_pairs_and_keep_norms():
+    from torchtitan_b200.models.common.rope import RoPE, apply_rotary_emb
+
+    for backend in ("complex", "cos_sin"):
+        rope = RoPE(RoPE.Config(dim=16, max_seq_len=64, theta=10000.0, backend=backend))
+        q = torch.randn(2, 10, 4, 16)
+        k = torch.randn(2, 10, 2, 16)
+        rq, rk = apply_rotary_emb(q, k, rope.cache, layout=rope.layout)
+        assert rq.shape == q.shape and rk.shape == k.shape
+        assert torch.allclose(rq.norm(dim=-1), q.norm(dim=-1), atol=1e-4)      # rotations preserve length
+        assert torch.allclose(rq[:, 0], q[:, 0], atol=1e-6)                     # position 0 is the identity
+        # relative property: <R_m q, R_n k> depends on m - n only
+        pos = torch.tensor([[3, 7]])
+        pos2 = pos + 11
+        a, b = torch.randn(1, 1, 1, 16), torch.randn(1, 1, 1, 16)
+        qa, _ = apply_rotary_emb(a.expand(1, 2, 1, 16), a.expand(1, 2, 1, 16), rope.cache, positions=pos, layout=rope.layout)
+        kb, _ = apply_rotary_emb(b.expand(1, 2, 1, 16), b.expand(1, 2, 1, 16), rope.cache, positions=pos, layout=rope.layout)
+        qa2, _ = apply_rotary_emb(a.expand(1, 2, 1, 16), a.expand(1, 2, 1, 16), rope.cache, positions=pos2, layout=rope.layout)
+        kb2, _ = apply_rotary_emb(b.expand(1, 2, 1, 16), b.expand(1, 2, 1, 16), rope.cache, positions=pos2, layout=rope.layout)
+        d1 = (qa[0, 0, 0] * kb[0, 1, 0]).sum()
+        d2 = (qa2[0, 0, 0] * kb2[0, 1, 0]).sum()
+        assert torch.allclose(d1, d2, atol=1e-4)
+
+
+def test_rope_scaling_variants_change_only_low_frequencies():
+    from torchtitan_b200.models.common.rope import RoPE
+
+    base = RoPE(RoPE.Config(dim=64, max_seq_len=128, theta=500000.0))
+    llama = RoPE(RoPE.Config(dim=64, max_seq_len=128, theta=500000.0, scaling="llama", scaling_factor=8.0,
+                             original_max_position_embeddings=64))
+    f0, _ = base.inv_freq()
+    f1, _ = llama.inv_freq()
+    assert torch.allclose(f0[:2], f1[:2])                       # the fastest frequencies are untouched
+    assert (f1[-4:] < f0[-4:]).all()                            # the slowest are stretched
+    with pytest.raises(NotImplementedError):
+        RoPE(RoPE.Config(dim=64, max_seq_len=128, backend="cos_sin", scaling="llama"))
+
+
+def test_document_masks_block_attention_across_documents():
+    from torchtitan_b200 import ops
+    from torchtitan_b200.models.common.attention import create_varlen_metadata_for_document, document_ids, fixed_block_ids
+
+    eos = 9
+    tok = torch.tensor([[1, 2, eos, 3, 4, 5, eos, 6], [eos, 1, 2, 3, 4, eos, 5, 6]])
+    ids = document_ids(tok, eos)
+    assert ids.tolist() == [[0, 0, 0, 1, 1, 1, 1, 2], [0, 1, 1, 1, 1, 1, 2, 2]]
+    meta = create_varlen_metadata_for_document(tok, eos)
+    assert meta.cu_seqlens.tolist() == [0, 3, 7, 8, 9, 14, 16] and meta.max_seqlen == 5
+    assert fixed_block_ids(1, 6, 4).tolist() == [[0, 0, 0, 0, 1, 1]]
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(2, 8, 2, 16) for _ in range(3))
+    out = ops.attention(q, k, v, causal=True, doc_ids=ids)
+    # a document's outputs do not change when another document's values change
+    v2 = v.clone()
+    v2[0, :3] += 5.0
+    out2 = ops.attention(q, k, v2, causal=True, doc_ids=ids)
+    assert torch.allclose(out[0, 3:], out2[0, 3:], atol=1e-6) and not torch.allclose(out[0, :3], out2[0, :3])
+    # sliding window: a key further back than the window has no influence
+    w = ops.attention(q, k, v, causal=True, window=2)
+    v3 = v.clone()
+    v3[:, 0] += 5.0
+    w3 = ops.attention(q, k, v3, causal=True, window=2)
+    assert torch.allclose(w[:, 2:], w3[:, 2:], atol=1e-6)
+
+
+@pytest.mark.parametrize("family,flavor", [("llama3", "debugmodel_gqa"), ("qwen3", "debugmodel")])
+def test_hf_state_dict_adapter_round_trip(family, flavor):
+    import importlib
+
+    cfg = _tiny(family, flavor)
+    m = cfg.build()
+    m.init_weights()
+    sd = {k: v.detach().clone() for k, v in m.state_dict().items()}
+    mod = importlib.import_module(f"torchtitan_b200.models.{family}.state_dict_adapter")
+    cls = next(getattr(mod, n) for n in dir(mod) if n.endswith("StateDictAdapter") and n != "StateDictAdapter" and "MoE" not in n)
+    ad = cls(cfg, None)
+    hf = ad.to_hf(sd)
+    assert all(k.startswith(("model.", "lm_head.")) for k in hf), list(hf)[:5]
+    assert any("self_attn.q_proj.weight" in k for k in hf) and any("mlp.down_proj.weight" in k for k in hf)
+    back = ad.from_hf(hf)
+    assert set(back) == set(sd)
+    for k in sd:
+        assert torch.equal(back[k], sd[k]), k
+
+
+def test_llama_rope_permutation_matches_hf_rotate_half():
+    """The q/k projection rows are permuted between the interleaved layout used here and the half-rotated layout of
+    Hugging Face checkpoints: scores must agree between the two conventions."""
+    from torchtitan_b200.models.llama3.state_dict_adapter import Llama3StateDictAdapter
+
+    n_heads, hd, dim = 2, 8, 16
+    w = torch.randn(n_heads * hd, dim)
+    hf = Llama3StateDictAdapter._to_hf_layout(w, n_heads)
+    assert torch.equal(Llama3StateDictAdapter._from_hf_layout(hf, n_heads), w)
+    x = torch.randn(5, dim)
+    ours = (x @ w.t()).view(5, n_heads, hd // 2, 2)             # pairs (2i, 2i+1)
+    theirs = (x @ hf.t()).view(5, n_heads, 2, hd // 2)           # halves (i, i + hd/2)
+    assert torch.allclose(ours[..., 0], theirs[:, :, 0], atol=1e-6) and torch.allclose(ours[..., 1], theirs[:, :, 1], atol=1e-6)
+
+
+def test_peak_flops_table_memory_monitor_and_gc():
+    from torchtitan_b200.components.metrics import build_device_memory_monitor
+    from torchtitan_b200.tools.utils import Color, GarbageCollection, NoColor, get_peak_flops
+
+    assert get_peak_flops("NVIDIA B200") == 2.25e15
+    assert get_peak_flops("NVIDIA H100 80GB HBM3") == 989e12
+    assert get_peak_flops("some unknown device") == 312e12
+    mon = build_device_memory_monitor()
+    st = mon.get_peak_stats()
+    assert st.max_reserved_gib >= 0 and 0 <= st.max_reserved_pct <= 100
+    assert set(vars(NoColor)) >= {n for n in vars(Color) if not n.startswith("_")}
+    was = gc.isenabled()
+    try:
+        h = GarbageCollection(gc_freq=2)
+        assert not gc.isenabled()
+        h.run(1)
+        h.run(2)
+        with pytest.raises(AssertionError):
+            GarbageCollection(gc_freq=0)
+    finally:
+        if was:
+            gc.enable()
