@@ -440,7 +440,7 @@ def test_mxfp8_quantise_kernels(ops):
             assert torch.equal(sc, sr), (sc.flatten()[:8], sr.flatten()[:8])
             assert torch.equal(q.view(torch.uint8), qr.view(torch.uint8))
             back = dequantize_mxfp8(q, sc)
-            assert _rel(back, x.float()) < 5e-2
+            assert _rel(back, x.float()) < 7e-2       # e4m3 keeps 3 mantissa bits: up to 2^-4 of the block maximum
     _no_kernel_errors()
 
 
