@@ -94,3 +94,108 @@ def test_ep2_fsdp_model_loss_and_grad_norm(tmp_path):
     for o in run_ranks(_model_worker, 2, tmp_path=tmp_path):
         assert abs(o["loss"] - o["ref"]) < 1e-5, o
         assert abs(o["norm"] - o["ref_norm"]) < 1e-4 * max(1.0, o["ref_norm"]), o
+
+
+def _etp_worker(rank, world):
+    """tp = etp = 2, ep = 2 on 4 ranks: experts split [ep: expert index] x [etp: hidden]; every rank feeds its own tokens."""
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.models.common.moe import MoE
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.parallel.ep import AllToAllDispatcher, _shard_experts, _shard_experts_hidden
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=2, cp=1, tp=2, pp=1, ep=2, etp=2, world_size=world)
+    ep_mesh, etp_mesh = pd.get_mesh("ep"), pd.get_mesh("etp")
+    assert sorted(dist.get_process_group_ranks(etp_mesh.get_group())) == sorted(dist.get_process_group_ranks(pd.get_mesh("tp").get_group()))
+    kw = dict(num_experts=8, num_shared_experts=1, score_func="softmax", route_norm=True, top_k=2, hidden_dim=32,
+              score_before_experts=False)
+    torch.manual_seed(0)
+    ref = MoE.Config(**kw).build(dim=16)
+    ref.init_weights(init_std=0.02, buffer_device=torch.device("cpu"))
+    moe = MoE.Config(**kw).build(dim=16)
+    moe.load_state_dict({k: v.clone() for k, v in ref.state_dict().items()})
+    _shard_experts(moe.experts, ep_mesh)
+    moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, 8, alignment=8)
+    _shard_experts_hidden(moe.experts, etp_mesh)
+    moe._etp_group = etp_mesh.get_group()
+    assert tuple(moe.experts.w1.shape) == (4, 16, 16) and tuple(moe.experts.w2.shape) == (4, 16, 16)
+    xs = [torch.randn(2, 12, 16, generator=torch.Generator().manual_seed(10 + r)) for r in range(world)]
+    x = xs[rank].clone().requires_grad_()
+    y = moe(x)
+    y.pow(2).sum().backward()
+    xr = [t.clone().requires_grad_() for t in xs]
+    yr = [ref(t) for t in xr]
+    sum(t.pow(2).sum() for t in yr).backward()
+    e, h = ep_mesh.get_local_rank(), etp_mesh.get_local_rank()
+    es, hs = slice(4 * e, 4 * e + 4), slice(16 * h, 16 * h + 16)
+    # the gate and the shared experts are replicated over tp: their gradients are partial per rank and summed by the
+    # tensor-parallel gradient hooks, which this layer-level test applies by hand
+    gate = moe.router.gate.weight.grad.clone()
+    dist.all_reduce(gate)
+    return {
+        "y": (y - yr[rank]).abs().max().item(),
+        "dx": (x.grad - xr[rank].grad).abs().max().item(),
+        "dw1": (moe.experts.w1.grad - ref.experts.w1.grad[es, hs]).abs().max().item(),
+        "dw2": (moe.experts.w2.grad - ref.experts.w2.grad[es, :, hs]).abs().max().item(),
+        "dw3": (moe.experts.w3.grad - ref.experts.w3.grad[es, hs]).abs().max().item(),
+        "dgate": (gate - ref.router.gate.weight.grad).abs().max().item(),
+    }
+
+
+def test_expert_tensor_parallel_matches_single_process(tmp_path):
+    for o in run_ranks(_etp_worker, 4, tmp_path=tmp_path):
+        assert max(o.values()) < 2e-5, o
+
+
+def _etp_model_worker(rank, world):
+    import dataclasses
+
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.config import ActivationCheckpointConfig, CompileConfig, ParallelismConfig, TrainingConfig
+    from torchtitan_b200.models.qwen3 import qwen3_configs
+    from torchtitan_b200.models.qwen3.parallelize import parallelize_qwen3
+    from torchtitan_b200.parallel import ParallelDims, fsdp
+    from torchtitan_b200.parallel import utils as dist_utils
+    from torchtitan_b200.parallel.tp import finalize_tp
+    from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=2, cp=1, tp=2, pp=1, ep=2, etp=2, world_size=world)
+    cfg = dataclasses.replace(qwen3_configs["debugmodel_moe"], n_layers=2)
+    torch.manual_seed(3)
+    ref = cfg.build()
+    ref.init_weights()
+    model = cfg.build()
+    model.load_state_dict({k: v.detach().clone() for k, v in ref.state_dict().items()})
+    parallelize_qwen3(
+        model, parallel_dims=pd, training=TrainingConfig(local_batch_size=2, seq_len=32, dtype="float32",
+                                                         mixed_precision_param="float32", mixed_precision_reduce="float32"),
+        model_converters=ModelConvertersContainer.Config(), parallelism=ParallelismConfig(tensor_parallel_degree=2,
+                                                                                          expert_parallel_degree=2,
+                                                                                          expert_tensor_parallel_degree=2),
+        compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="")
+    fsdp.materialize(model)
+    finalize_tp(model)
+    # the two ranks of a tp group share a batch; dp rank = rank // 2
+    dp = rank // 2
+    xs = [torch.randint(0, cfg.vocab_size, (2, 33), generator=torch.Generator().manual_seed(50 + r)) for r in range(2)]
+    ntok = sum(x[:, 1:].numel() for x in xs)
+    x = xs[dp]
+    loss = cross_entropy_loss(model(x[:, :-1]), x[:, 1:]) / ntok
+    loss.backward()
+    ref_loss = sum(cross_entropy_loss(ref(t[:, :-1]), t[:, 1:]) for t in xs) / ntok
+    ref_loss.backward()
+    tot = loss.detach().clone()
+    dist.all_reduce(tot, group=pd.get_mesh("fsdp").get_group())
+    ref_norm = torch.nn.utils.get_total_norm([p.grad for p in ref.parameters() if p.grad is not None])
+    norm = dist_utils.clip_grad_norm_(list(model.parameters()), 1e9, ep_enabled=True)
+    return {"loss": tot.item(), "ref": ref_loss.item(), "norm": float(norm), "ref_norm": float(ref_norm)}
+
+
+def test_etp_model_loss_and_grad_norm(tmp_path):
+    for o in run_ranks(_etp_model_worker, 4, tmp_path=tmp_path):
+        assert abs(o["loss"] - o["ref"]) < 2e-5, o
+        assert abs(o["norm"] - o["ref_norm"]) < 1e-4 * max(1.0, o["ref_norm"]), o

@@ -233,10 +233,26 @@ class MoE(Module):
         else:
             self.expert_bias = None
         self.register_buffer("tokens_per_expert", torch.zeros(E, dtype=torch.float32), persistent=False)
+        # expert tensor parallel (set by parallel/ep.py): the experts' hidden dimension is split over this group, whose
+        # ranks hold different sequence shards. The routed path then runs on the group's gathered tokens and its partial
+        # sums are reduce-scattered back; the shared experts stay on the local shard.
+        self._etp_group = None
 
     def forward(self, x):
         bs, slen, dim = x.shape
         x = x.reshape(-1, dim)
+        if self._etp_group is None:
+            out = self._routed(x)
+        else:
+            from torchtitan_b200.parallel.ep import gather_rows, reduce_scatter_rows
+
+            out = reduce_scatter_rows(self._routed(gather_rows(x, self._etp_group)), self._etp_group)
+        if self.shared_experts is not None:
+            out = out + self.shared_experts(x)
+        return out.reshape(bs, slen, dim)
+
+    def _routed(self, x):
+        """Router -> dispatch -> experts -> combine on tokens ``x`` [T, dim]."""
         k = self.router.top_k
         top_scores, idx, counts = self.router(x, self.expert_bias)
         with torch.no_grad():
@@ -252,15 +268,10 @@ class MoE(Module):
         routed_out = self.experts(routed_in, local_counts)
         weights = None if self.score_before_experts else top_scores
         fused = disp.combine_to_tokens(routed_out, weights, ctx) if hasattr(disp, "combine_to_tokens") else None
-        shared = self.shared_experts(x) if self.shared_experts is not None else None
         if fused is not None:
-            out = fused
-        else:
-            routed_out = disp.combine(routed_out, ctx)
-            out = _moe_ops().scatter_combine(routed_out, order, weights, x.shape[0], k)
-        if shared is not None:
-            out = out + shared
-        return out.reshape(bs, slen, dim)
+            return fused
+        routed_out = disp.combine(routed_out, ctx)
+        return _moe_ops().scatter_combine(routed_out, order, weights, x.shape[0], k)
 
     def init_weights(self, **kwargs) -> None:
         init_std = kwargs.get("init_std")

@@ -122,13 +122,96 @@ def _shard_experts(experts: nn.Module, ep_mesh) -> None:
     experts.num_local_experts = experts.w1.shape[0] if hasattr(experts, "w1") else None
 
 
+class _GatherRows(torch.autograd.Function):
+    """Concatenate the ranks' row blocks [T, D] -> [W * T, D]; backward sums the ranks' gradients of each block."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        W = dist.get_world_size(group)
+        x = x.contiguous()
+        out = x.new_empty((W * x.shape[0],) + tuple(x.shape[1:]))
+        dist.all_gather_into_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        W = dist.get_world_size(ctx.group)
+        g = g.contiguous()
+        out = g.new_empty((g.shape[0] // W,) + tuple(g.shape[1:]))
+        dist.reduce_scatter_tensor(out, g, group=ctx.group)
+        return out, None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    """Sum the ranks' [W * T, D] partial results and keep this rank's block [T, D]; backward gathers."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        W = dist.get_world_size(group)
+        x = x.contiguous()
+        out = x.new_empty((x.shape[0] // W,) + tuple(x.shape[1:]))
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        W = dist.get_world_size(ctx.group)
+        g = g.contiguous()
+        out = g.new_empty((W * g.shape[0],) + tuple(g.shape[1:]))
+        dist.all_gather_into_tensor(out, g, group=ctx.group)
+        return out, None
+
+
+def gather_rows(x, group):
+    return _GatherRows.apply(x, group)
+
+
+def reduce_scatter_rows(x, group):
+    return _ReduceScatterRows.apply(x, group)
+
+
+def _shard_experts_hidden(experts: nn.Module, etp_mesh) -> None:
+    """Expert tensor parallel: split every expert's hidden dimension over ``etp_mesh`` (``w1``/``w3`` [E, H, D] by rows,
+    ``w2`` [E, D, H] by columns), so a rank produces partial sums of the expert outputs.
+    Parity: ExpertTensorParallel, torchtitan/distributed/expert_parallel.py (2-D expert sharding [ep, etp])."""
+    W, r, group = etp_mesh.size(), etp_mesh.get_local_rank(), etp_mesh.get_group()
+    if not all(hasattr(experts, n) for n in ("w1", "w2", "w3")) or any(
+            experts._parameters.get(n) is not None for n in ("mlp1_weight", "mlp1_bias", "b1")):
+        raise NotImplementedError("expert tensor parallel covers SwiGLU experts without biases (w1 / w2 / w3)")
+    for name, dim in (("w1", 1), ("w3", 1), ("w2", 2)):
+        p = experts._parameters[name]
+        assert p.shape[dim] % W == 0, f"{name}: hidden size {p.shape[dim]} not divisible by etp={W}"
+        n = p.shape[dim] // W
+        if p.device.type == "meta":
+            shape = list(p.shape)
+            shape[dim] = n
+            local = torch.empty(shape, dtype=p.dtype, device="meta")
+        else:
+            local = p.detach().narrow(dim, r * n, n).clone()
+        newp = nn.Parameter(local, requires_grad=p.requires_grad)
+        prev = experts.__dict__.get("_tp_specs", {}).get(name)
+        groups = ((prev["group"],) if prev is not None else ()) + (group,)
+        spec = {"placement": ("shard", dim), "group": group, "mesh": etp_mesh,
+                "full_shape": tuple(prev["full_shape"] if prev is not None else p.shape), "norm_groups": groups,
+                "outer": prev}
+        experts.__dict__.setdefault("_tp_specs", {})[name] = spec
+        from .tp import _tag
+
+        _tag(newp, spec)
+        newp._extra_norm_groups = groups       # the squared norm is a partial sum over both the ep and the etp group
+        experts._parameters[name] = newp
+
+
 def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
     from .tp import _mark_replicated
 
-    if parallel_dims.etp_enabled:
-        raise NotImplementedError("expert tensor parallel (etp > 1) is not implemented; use etp = 1")
     ep_mesh = parallel_dims.get_optional_mesh("ep")
     tp_mesh = parallel_dims.get_optional_mesh("tp")
+    etp_mesh = parallel_dims.get_optional_mesh("etp") if parallel_dims.etp_enabled else None
+    if parallel_dims.etp_enabled and tp_mesh is None:
+        raise ValueError("expert tensor parallel needs tensor parallel (etp must equal tp)")
     from torchtitan_b200.models.common.moe.moe import GROUP_ALIGN_NATIVE
     from torchtitan_b200.ops import native
 
@@ -153,6 +236,11 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
         if ep_mesh is not None:
             _shard_experts(moe.experts, ep_mesh)
             moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, moe.router.num_experts, alignment=alignment, capacity_factor=cf)
+        if etp_mesh is not None:
+            if moe.aux_loss_coeff > 0.0:
+                raise NotImplementedError("the auxiliary load-balance loss is not supported with expert tensor parallel")
+            _shard_experts_hidden(moe.experts, etp_mesh)
+            moe._etp_group = etp_mesh.get_group()
     if n:
         logger.info(f"Applied expert parallel to {n} MoE layers (ep={parallel_dims.ep}, backend={getattr(parallelism, 'expert_parallel_comm_backend', 'standard')})")
     return model

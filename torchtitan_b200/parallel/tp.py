@@ -169,7 +169,8 @@ def _tag(p, spec) -> None:
     p._tp_group, p._tp_mesh = spec["group"], spec["mesh"]
     p._tp_full_shape = spec.get("full_shape")
     if spec["placement"][0] == "shard":
-        p._extra_norm_groups = (spec["group"],)  # its squared norm is a partial sum over the TP group
+        # its squared norm is a partial sum over the TP group (over several groups for 2-D expert shards)
+        p._extra_norm_groups = tuple(spec.get("norm_groups") or (spec["group"],))
 
 
 def _shard_param(mod: nn.Module, name: str, dim: int, rank: int, world: int, group, mesh) -> None:
