@@ -133,6 +133,7 @@ def test_fused_gemm_reduce_scatter_single_gpu_emulation(L):
     if not hasattr(L, "tt_gemm_reduce_scatter"):
         pytest.skip("library built without tt_gemm_reduce_scatter")
     _rs_case(L, 2, 512, 256, 768)        # whole 256-row tiles per rank: CTA-pair kernel
+    _rs_case(L, 2, 256, 128, 328)        # CTA-pair kernel, ragged last column tile (72 columns)
     _rs_case(L, 4, 128, 192, 264)        # single-CTA tile kernel, ragged N tile
     _rs_case(L, 1, 256, 128, 512)        # one rank: staging round trip only
 

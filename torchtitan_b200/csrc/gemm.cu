@@ -542,6 +542,11 @@ constexpr int TM = 256, TN = 256;
 constexpr int PSTAGES = 6;
 constexpr uint32_t PA_BYTES = 128 * BK * 2, PB_BYTES = 128 * BK * 2;  // per CTA per stage
 constexpr size_t PSMEM_BYTES = 1024 + PSTAGES * (PA_BYTES + PB_BYTES) + 256;
+// The fused reduce-scatter stages the rows it sends to a peer in shared memory (32 rows x 128 columns bf16 per epilogue
+// warp, 16-byte columns XOR-swizzled by the row) so that every warp-wide store covers two whole 256-byte row segments:
+// NVLink then carries full packets instead of one 16-byte write per lane.
+constexpr uint32_t RS_STAGE_PER_WARP = 32 * 256;
+constexpr size_t PSMEM_RS_BYTES = PSMEM_BYTES + 4 * RS_STAGE_PER_WARP;
 
 template <bool FP8, bool RS = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -692,15 +697,59 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         else if (p.scale_mode == 2 && row_ok) sa = __ldg(p.scale_a + row);
       }
       if constexpr (RS) rs_begin(p, tm * TM + static_cast<int>(rank) * 128, tn);
+      bool staged = false;
+      if constexpr (RS) {
+        const int first_row = tm * TM + static_cast<int>(rank) * 128;
+        const int owner = first_row / p.rs_rows_per_rank;
+        if (owner != p.rs_rank) {
+          // rows of a peer: TMEM -> bf16 -> swizzled shared memory -> row-contiguous stores into the owner's staging slot
+          staged = true;
+          uint8_t* stg = bars_gen + 256 + ew * RS_STAGE_PER_WARP;
+          const int local0 = first_row - owner * p.rs_rows_per_rank + ew * 32;   // first of this warp's 32 rows
+          __nv_bfloat16* dst_base = static_cast<__nv_bfloat16*>(p.rs_stage[owner]) +
+                                    (static_cast<long long>(p.rs_rank) * p.rs_rows_per_rank + local0) * p.N;
 #pragma unroll 1
-      for (int c = 0; c < TN / 32; ++c) {
-        uint32_t r[32];
-        tt::tmem_ld_32x32(taddr + c * 32, r);
-        tt::tc_wait_ld();
-        const int col = n0 + c * 32;
-        if (!row_ok || col >= p.N) continue;
-        if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
-        store_chunk<RS>(p, row, col, r);
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tt::tmem_ld_32x32(taddr + half * 128 + c * 32, r);
+              tt::tc_wait_ld();
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 q;
+                q.x = tt::pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                q.y = tt::pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                q.z = tt::pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                q.w = tt::pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                const int c16 = c * 4 + v;
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((c16 ^ (lane & 7)) << 4)) = q;
+              }
+            }
+            __syncwarp();
+            const int c16 = lane & 15;
+            const int gcol = n0 + half * 128 + c16 * 8;
+#pragma unroll 4
+            for (int r2 = 0; r2 < 16; ++r2) {
+              const int rr = r2 * 2 + (lane >> 4);
+              const uint4 q = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((c16 ^ (rr & 7)) << 4));
+              if (gcol < p.N) *reinterpret_cast<uint4*>(dst_base + static_cast<long long>(rr) * p.N + gcol) = q;
+            }
+            __syncwarp();
+          }
+        }
+      }
+      if (!staged) {
+#pragma unroll 1
+        for (int c = 0; c < TN / 32; ++c) {
+          uint32_t r[32];
+          tt::tmem_ld_32x32(taddr + c * 32, r);
+          tt::tc_wait_ld();
+          const int col = n0 + c * 32;
+          if (!row_ok || col >= p.N) continue;
+          if constexpr (FP8) { if (p.scale_mode) apply_scales(p, sa, col, r); }
+          store_chunk<RS>(p, row, col, r);
+        }
       }
       if constexpr (RS) rs_end(p, tm * TM + static_cast<int>(rank) * 128, tn);
       tt::tc_fence_before();
@@ -725,7 +774,7 @@ void set_kernel_attrs() {
   cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
   cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
   cudaFuncSetAttribute(gemm_bf16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
-  cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_BYTES));
+  cudaFuncSetAttribute(pair::gemm_bf16_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pair::PSMEM_RS_BYTES));
 }
 
 }  // namespace
@@ -953,7 +1002,7 @@ int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, in
     p.m_rot = ((rank + 1) % world) * p.m_block;
     int clusters = p.tiles_m * p.tiles_n;
     if (clusters > g_num_sms / 2) clusters = g_num_sms / 2;
-    pair::gemm_bf16_pair_kernel<false, true><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
+    pair::gemm_bf16_pair_kernel<false, true><<<clusters * 2, NUM_THREADS, pair::PSMEM_RS_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = M / BM;
     p.m_block = p.tiles_m;
