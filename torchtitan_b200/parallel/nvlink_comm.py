@@ -158,7 +158,7 @@ class NvlinkComm(ShardComm):
             logger.info("NVLink FSDP transport unavailable (no peer access); using c10d collectives")
             return None
         # a tied weight is reachable from two wrapped units and each keeps its own flat buffers: count it twice
-        nparams = sum(p.numel() for p in model.parameters(remove_duplicate=False)) if model is not None else 0
+        nparams = sum(p.numel() for _, p in model.named_parameters(remove_duplicate=False)) if model is not None else 0
         nunits = 4 + (len(model.layers) if model is not None and hasattr(model, "layers") else 64)
         # shadow shard (2 B / W) + staging (2 B) per parameter, rounding slack per unit and per parameter
         heap_bytes = int(2.05 * nparams * (1 + 1.0 / W)) + nunits * (1 << 20) + (64 << 20)
