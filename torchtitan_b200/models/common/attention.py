@@ -162,10 +162,18 @@ class GQAttention(BaseAttention):
 
     def forward(self, x, rope_cache, attention_masks: AttentionMasksType | None, positions=None):
         bs, seqlen, _ = x.shape
-        # -1 for the head count: tensor parallel shards the projections by heads
-        xq = self.wq(x).view(bs, seqlen, -1, self.head_dim)
-        xk = self.wk(x).view(bs, seqlen, -1, self.head_dim)
-        xv = self.wv(x).view(bs, seqlen, -1, self.head_dim)
+        # asynchronous tensor parallel (parallel/tp.py): ``x`` is this rank's sequence shard, the projections gather it
+        # inside the GEMM and ``wo`` reduce-scatters inside its GEMM
+        fused_tp = self.__dict__.get("_fused_tp_call")
+        if fused_tp is not None:
+            q2, k2, v2 = fused_tp.project(self, x)
+            seqlen = q2.shape[1]
+            xq, xk, xv = (t.view(bs, seqlen, -1, self.head_dim) for t in (q2, k2, v2))
+        else:
+            # -1 for the head count: tensor parallel shards the projections by heads
+            xq = self.wq(x).view(bs, seqlen, -1, self.head_dim)
+            xk = self.wk(x).view(bs, seqlen, -1, self.head_dim)
+            xv = self.wv(x).view(bs, seqlen, -1, self.head_dim)
         if self.q_norm is not None:
             xq, xk = self.q_norm(xq), self.k_norm(xk)
         if self.use_rope:
@@ -177,6 +185,8 @@ class GQAttention(BaseAttention):
         else:
             assert isinstance(attention_masks, AttentionMasks), attention_masks
         out = self.inner_attention(xq, xk, xv, masks=attention_masks, scale=self.scaling)
+        if fused_tp is not None:
+            return fused_tp.output(self, out.reshape(bs, seqlen, -1))
         return self.wo(out.reshape(bs, seqlen, -1))
 
     def init_weights(self, init_std: float = 0.02, **kwargs) -> None:

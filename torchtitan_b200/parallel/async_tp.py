@@ -157,7 +157,28 @@ class AsyncTP:
         ff._async_tp = self
 
     def attach_attention(self, att) -> None:
-        att._async_tp = None  # attention projections take the collective path
+        """Grouped-query attention without biases: ``wq`` gathers the sequence inside its GEMM, ``wk`` / ``wv`` read the
+        gathered copy, ``wo`` reduce-scatters inside its GEMM. Other attention forms keep the collective path."""
+        plain = all(hasattr(att, n) for n in ("wq", "wk", "wv", "wo")) and not hasattr(att, "wkv_b") and all(
+            getattr(getattr(att, n), "bias", None) is None and getattr(getattr(att, n), "quant", None) is None
+            for n in ("wq", "wk", "wv", "wo"))
+        att._async_tp = self if plain else None
+
+    def attention_supported(self, att, x_local: torch.Tensor) -> bool:
+        if getattr(att, "_async_tp", None) is not self or not self.supported(x_local, att.wq.weight):
+            return False
+        rows = x_local.shape[1] * self.world
+        return (native.has("tt_gemm_reduce_scatter") and rows % (128 * self.world) == 0
+                and att.wo.weight.dtype == torch.bfloat16 and att.wo.weight.shape[0] % 8 == 0 and att.wo.weight.shape[1] % 8 == 0)
+
+    def project(self, att, x_local):
+        xg, q = self.ag_linear(x_local, att.wq.weight)
+        k = _LinearOnGathered.apply(xg, x_local, att.wk.weight, self.group)
+        v = _LinearOnGathered.apply(xg, x_local, att.wv.weight, self.group)
+        return q, k, v
+
+    def output(self, att, o):
+        return self.linear_rs(o, att.wo.weight)
 
 
 class _AgLinear(torch.autograd.Function):

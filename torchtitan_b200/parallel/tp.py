@@ -337,9 +337,20 @@ def apply_tp_to_decoder(model: nn.Module, tp_mesh, *, loss_parallel: bool = True
         for nm in ("q_norm", "k_norm"):
             if getattr(att, nm, None) is not None:
                 _mark_replicated(getattr(att, nm), group, tp_mesh)
-        _wrap(att, lambda inner, x, *a, **k: _scatter(inner(_gather(x, group), *a, **k), group))
         if fused is not None:
             fused.attach_attention(att)
+
+        def att_forward(inner, x, *a, _att=att, **k):
+            atp = _att.__dict__.get("_async_tp")
+            if atp is not None and atp.attention_supported(_att, x):
+                _att.__dict__["_fused_tp_call"] = atp
+                try:
+                    return inner(x, *a, **k)             # gathers and reduce-scatters inside its GEMMs
+                finally:
+                    _att.__dict__.pop("_fused_tp_call", None)
+            return _scatter(inner(_gather(x, group), *a, **k), group)
+
+        _wrap(att, att_forward)
         ff = getattr(block, "feed_forward", None)
         if ff is not None and not getattr(block, "moe_enabled", False):
             _shard_param(ff.w1, "weight", 0, r, W, group, tp_mesh)
