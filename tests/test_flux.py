@@ -79,3 +79,84 @@ def test_flux_trainer_steps_on_cpu(tmp_path, monkeypatch):
 
     assert os.path.getsize(path) > 0
     tr.close()
+
+
+def _make_image_data(root, n=7):
+    import io
+    import json
+    import tarfile
+
+    import numpy as np
+    from PIL import Image
+
+    folder, wds = root / "folder", root / "wds"
+    folder.mkdir()
+    wds.mkdir()
+    rows = []
+    tars = [tarfile.open(wds / f"shard-{i:03d}.tar", "w") for i in range(2)]
+    for i in range(n):
+        arr = (np.random.RandomState(i).rand(40 + 3 * i, 56, 3) * 255).astype("uint8")
+        im = Image.fromarray(arr)
+        im.save(folder / f"img{i}.png")
+        rows.append({"file_name": f"img{i}.png", "captions" if i % 2 else "text": [f"a picture number {i}"] if i % 2 else f"a picture number {i}"})
+        buf = io.BytesIO()
+        im.save(buf, format="JPEG")
+        for name, data in ((f"{i:05d}.jpg", buf.getvalue()), (f"{i:05d}.txt", f"caption {i}".encode())):
+            info = tarfile.TarInfo(name)
+            info.size = len(data)
+            tars[i % 2].addfile(info, io.BytesIO(data))
+    (folder / "broken.png").write_bytes(b"not an image")
+    rows.append({"file_name": "broken.png", "text": "unreadable"})
+    with open(folder / "metadata.jsonl", "w") as f:
+        f.write("\n".join(json.dumps(r) for r in rows))
+    for t in tars:
+        t.close()
+    return folder, wds
+
+
+def test_image_caption_datasets_folder_and_webdataset(tmp_path):
+    from torchtitan_b200.models.flux.flux_datasets import FluxDataLoader
+    from torchtitan_b200.models.flux.tokenizer import FluxTestTokenizer, build_flux_tokenizer
+
+    folder, wds = _make_image_data(tmp_path)
+    tok = FluxTestTokenizer(max_length=8, vocab_size=100)
+    ids = tok.encode(["a b c", ""])
+    assert ids.shape == (2, 8) and ids[0, 3] == 99 and ids[1, 0] == 99 and (ids[1, 1:] == 0).all()
+    assert torch.equal(tok.encode("a b c"), ids[:1])
+    t5, clip = build_flux_tokenizer(t5_path=None, clip_path=str(tmp_path / "missing"), t5_max_length=16, clip_max_length=8)
+    assert t5.encode("x").shape == (1, 16) and clip.encode("x").shape == (1, 8)
+
+    def loader(name, path, rank=0, world=1, **kw):
+        cfg = FluxDataLoader.Config(dataset=name, dataset_path=str(path), img_size=32, t5_max_length=16, clip_max_length=8,
+                                    classifier_free_guidance_prob=0.0, test_tokenizer=True, infinite=False, **kw)
+        return FluxDataLoader(cfg, dp_world_size=world, dp_rank=rank, local_batch_size=2)
+
+    batches = list(loader("coco-validation", folder))
+    assert len(batches) == 3                                             # 7 readable images -> 3 full batches of 2
+    inp, img = batches[0]
+    assert img.shape == (2, 3, 32, 32) and float(img.min()) >= -1 and float(img.max()) <= 1
+    assert inp["t5_tokens"].shape == (2, 1, 16) and inp["clip_tokens"].shape == (2, 1, 8)
+    assert inp["prompt"] == ["a picture number 0", "a picture number 1"]
+    # web-dataset shards, split over two data-parallel ranks by shard
+    r0 = [p for b in loader("cc12m-wds", wds, 0, 2) for p in b[0]["prompt"]]
+    r1 = [p for b in loader("cc12m-wds", wds, 1, 2) for p in b[0]["prompt"]]
+    assert r0 == ["caption 0", "caption 2", "caption 4", "caption 6"] and r1 == ["caption 1", "caption 3"]
+    # resume: the state counts consumed samples
+    dl = loader("cc12m-test", folder)
+    it = iter(dl)
+    next(it)
+    state = dl.state_dict()
+    want = next(it)[0]["prompt"]
+    dl2 = loader("cc12m-test", folder)
+    dl2.load_state_dict(state)
+    assert next(iter(dl2))[0]["prompt"] == want
+    # classifier-free guidance drops prompts
+    dropped = [p for b in loader("cc12m-test", folder).__class__(
+        FluxDataLoader.Config(dataset="cc12m-test", dataset_path=str(folder), img_size=32, t5_max_length=16, clip_max_length=8,
+                              classifier_free_guidance_prob=1.0, test_tokenizer=True, infinite=False),
+        dp_world_size=1, dp_rank=0, local_batch_size=1) for p in b[0]["prompt"]]
+    assert dropped and all(p == "" for p in dropped)
+    import pytest
+
+    with pytest.raises(FileNotFoundError):
+        loader("cc12m-test", tmp_path / "nowhere")
