@@ -160,3 +160,31 @@ def test_image_caption_datasets_folder_and_webdataset(tmp_path):
 
     with pytest.raises(FileNotFoundError):
         loader("cc12m-test", tmp_path / "nowhere")
+
+
+def test_flux_hf_adapter_splits_fused_projections_and_round_trips():
+    from torchtitan_b200.models.flux.config_registry import flux_debugmodel
+    from torchtitan_b200.models.flux.model.state_dict_adapter import FluxStateDictAdapter
+
+    cfg = flux_debugmodel().model_spec.model
+    model = cfg.build()
+    sd = {k: torch.randn_like(v) for k, v in model.state_dict().items()}
+    ad = FluxStateDictAdapter(cfg, None)
+    hf = ad.to_hf(sd)
+    h = cfg.hidden_size
+    assert hf["transformer_blocks.0.attn.to_k.weight"].shape == (h, h)
+    assert torch.equal(hf["transformer_blocks.0.attn.to_k.weight"], sd["double_blocks.0.img_attn.qkv.weight"][h : 2 * h])
+    assert torch.equal(hf["transformer_blocks.1.attn.add_v_proj.bias"], sd["double_blocks.1.txt_attn.qkv.bias"][2 * h :])
+    assert torch.equal(hf["single_transformer_blocks.0.proj_mlp.weight"], sd["single_blocks.0.linear1.weight"][3 * h :])
+    # the final modulation stores (shift, scale) here and (scale, shift) there
+    w = sd["final_layer.adaLN_modulation.1.weight"]
+    assert torch.equal(hf["norm_out.linear.weight"], torch.cat((w[h:], w[:h])))
+    assert "x_embedder.weight" in hf and "time_text_embed.timestep_embedder.linear_1.bias" in hf
+    back = ad.from_hf(hf)
+    assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) for k in sd)
+    import pytest
+
+    with pytest.raises(KeyError):
+        ad.from_hf({"transformer_blocks.0.attn.to_q.weight": torch.zeros(h, h)})
+    with pytest.raises(KeyError):
+        ad.to_hf({"unknown.weight": torch.zeros(1)})

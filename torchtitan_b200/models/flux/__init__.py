@@ -5,6 +5,7 @@ from torchtitan_b200.components.loss import build_mse_loss
 from torchtitan_b200.protocols.model_spec import ModelSpec
 
 from .flux_datasets import FluxDataLoader
+from .model.state_dict_adapter import FluxStateDictAdapter
 from .model.autoencoder import AutoEncoderParams
 from .model.model import FluxModel
 from .parallelize import parallelize_flux
@@ -26,4 +27,4 @@ flux_configs = {
 
 def model_registry(flavor: str) -> ModelSpec:
     return ModelSpec(name="flux", flavor=flavor, model=flux_configs[flavor], parallelize_fn=parallelize_flux, pipelining_fn=None,
-                     build_loss_fn=build_mse_loss, post_optimizer_build_fn=None, state_dict_adapter=None)
+                     build_loss_fn=build_mse_loss, post_optimizer_build_fn=None, state_dict_adapter=FluxStateDictAdapter)
