@@ -95,16 +95,19 @@ def test_fused_allgather_gemm_single_gpu_emulation(L):
     waits on another launch): remote slices are pulled by the copy CTAs of the same launch while the GEMM CTAs multiply."""
     _fused_case(L, 4, 256, 512, 768)      # whole 256-row tiles per rank: CTA-pair kernel
     _fused_case(L, 4, 128, 320, 264)      # single-CTA tile kernel, ragged N and K
+    _fused_case(L, 2, 256, 512, 768, b_mn=True)   # weight read as [contraction, output]: the backward form
+    _fused_case(L, 2, 128, 192, 320, b_mn=True)
 
 
-def _fused_case(L, W, rows_local, K, N):
+def _fused_case(L, W, rows_local, K, N, b_mn=False):
     torch.manual_seed(0)
     M = W * rows_local
     stream = torch.cuda.current_stream().cuda_stream
     x = torch.randn(M, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
     want = x.float() @ w.float().t()
-    for rank in (0, 2):
+    wb = w.t().contiguous() if b_mn else w                  # [K, N] when read as [contraction, output]
+    for rank in (0, W - 1):
         # rank r's buffer holds only its own slice; the others are garbage until pulled
         bufs = []
         for r in range(W):
@@ -116,7 +119,8 @@ def _fused_case(L, W, rows_local, K, N):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         p, k1 = _ptr_array(bufs)
         f, k2 = _ptr_array(flags)
-        rc = L.tt_gemm_allgather_a(p, f, W, rank, 7, w.data_ptr(), out.data_ptr(), M, N, K, 0, K, N, 0, ready.data_ptr(), 1, 8, stream)
+        rc = L.tt_gemm_allgather_a(p, f, W, rank, 7, wb.data_ptr(), out.data_ptr(), M, N, K, int(b_mn), wb.stride(0), N, 0,
+                                   ready.data_ptr(), 1, 8, stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert L.tt_gemm_error() == 0
@@ -136,15 +140,17 @@ def test_fused_gemm_reduce_scatter_single_gpu_emulation(L):
     _rs_case(L, 2, 256, 128, 328)        # CTA-pair kernel, ragged last column tile (72 columns)
     _rs_case(L, 4, 128, 192, 264)        # single-CTA tile kernel, ragged N tile
     _rs_case(L, 1, 256, 128, 512)        # one rank: staging round trip only
+    _rs_case(L, 2, 256, 192, 512, b_mn=True)     # weight read as [contraction, output]: the backward form
 
 
-def _rs_case(L, W, rows_per_rank, Kshard, N):
+def _rs_case(L, W, rows_per_rank, Kshard, N, b_mn=False):
     torch.manual_seed(1)
     M = W * rows_per_rank
     stream = torch.cuda.current_stream().cuda_stream
     A = [torch.randn(M, Kshard, device="cuda").bfloat16() for _ in range(W)]
     B = [(torch.randn(N, Kshard, device="cuda") * 0.1).bfloat16() for _ in range(W)]
     parts = [a.float() @ b.float().t() for a, b in zip(A, B)]
+    Bm = [b.t().contiguous() for b in B] if b_mn else B      # [Kshard, N] when read as [contraction, output]
     want = sum(parts)
     stages = [torch.full((W, rows_per_rank, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(W)]
     counts = [torch.zeros(W * (rows_per_rank // 128) * ((N + 255) // 256), dtype=torch.int32, device="cuda") for _ in range(W)]
@@ -155,8 +161,8 @@ def _rs_case(L, W, rows_per_rank, Kshard, N):
         order = [r for r in range(W) if r != last] + [last]
         out = torch.full((rows_per_rank, N), float("nan"), device="cuda", dtype=torch.bfloat16)
         for r in order:
-            rc = L.tt_gemm_reduce_scatter(A[r].data_ptr(), B[r].data_ptr(), sp, cp, out.data_ptr(), W, r, M, N, Kshard,
-                                          Kshard, 0, Kshard, call, 0 if r == last else 1, stream)
+            rc = L.tt_gemm_reduce_scatter(A[r].data_ptr(), Bm[r].data_ptr(), sp, cp, out.data_ptr(), W, r, M, N, Kshard,
+                                          Kshard, int(b_mn), Bm[r].stride(0), call, 0 if r == last else 1, stream)
             assert rc == 0
         torch.cuda.synchronize()
         assert L.tt_gemm_error() == 0

@@ -18,7 +18,10 @@ system-scope atomic; the tiles of this rank's own rows come last, and their epil
 the staged partials to the fp32 accumulator in rank order and writes the final rows. Staging is double-buffered: a rank's call n+1 ends only after every peer contributed to
 call n+1, which they do after their call n, so the buffer of call n is free again when call n+2 starts.
 
-Backward uses the collective path (sequence all-gather for the weight gradient, reduce-scatter for the input gradient).
+Backward reuses both kernels with the weight read as the [contraction, output] operand: the input gradient of a
+column-parallel layer is a GEMM -> reduce-scatter, that of a row-parallel layer an all-gather -> GEMM whose gathered
+output gradient also feeds the weight-gradient GEMM. Only the re-gather of the saved sequence shard for the weight
+gradients of column-parallel layers is a plain collective.
 """
 
 from __future__ import annotations
@@ -80,18 +83,21 @@ class AsyncTP:
     def supported(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
         rows_local = x.numel() // x.shape[-1]
         return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[0] == 1
-                and rows_local % 128 == 0 and x.shape[-1] % 8 == 0 and rows_local * self.world // 128 <= self.panel_ready.numel())
+                and rows_local % 128 == 0 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+                and rows_local * self.world // 128 <= self.panel_ready.numel())
 
     def ag_linear(self, x: torch.Tensor, weight: torch.Tensor):
         """``x`` [1, S/tp, K] (this rank's sequence slice), ``weight`` [N, K] -> (gathered x [1, S, K], x_full @ weight^T)."""
         return _AgLinear.apply(x, weight, self)
 
-    def _forward(self, x: torch.Tensor, weight: torch.Tensor):
+    def _forward(self, x: torch.Tensor, weight: torch.Tensor, b_mn: bool = False):
+        """Fused gather of ``x`` + GEMM with ``weight`` [N, K] (or stored [K, N] with ``b_mn``, as in the input-gradient
+        GEMM of a row-parallel layer)."""
         L = native.lib()
         K = x.shape[-1]
         rows_local = x.numel() // K
         rows = rows_local * self.world
-        N = weight.shape[0]
+        N = weight.shape[1] if b_mn else weight.shape[0]
         self.version += 1
         off, ptrs, _keep, full = self._buffers(rows, K)[self.version % 2]
         full[self.rank * rows_local : (self.rank + 1) * rows_local].copy_(x.reshape(rows_local, K))
@@ -99,7 +105,7 @@ class AsyncTP:
         out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
         w = weight.contiguous()
         native.check(L.tt_gemm_allgather_a(ptrs, ctypes.cast(self._flag_ptrs, _PP), self.world, self.rank, self.version,
-                                           w.data_ptr(), out.data_ptr(), rows, N, K, 0, w.stride(0), out.stride(0), 0,
+                                           w.data_ptr(), out.data_ptr(), rows, N, K, int(b_mn), w.stride(0), out.stride(0), 0,
                                            self.panel_ready.data_ptr(), self.version, self.COPY_CTAS, _stream()),
                      "tt_gemm_allgather_a")
         self.fused_calls += 1
@@ -132,11 +138,11 @@ class AsyncTP:
         [1, S/tp, N] of ``sum over ranks (h @ weight^T)``."""
         return _LinearRs.apply(h, weight, self)
 
-    def _forward_rs(self, h: torch.Tensor, weight: torch.Tensor):
+    def _forward_rs(self, h: torch.Tensor, weight: torch.Tensor, b_mn: bool = False):
         L = native.lib()
         K = h.shape[-1]
         rows = h.numel() // K
-        N = weight.shape[0]
+        N = weight.shape[1] if b_mn else weight.shape[0]
         h2 = h.reshape(rows, K)
         if h2.stride(-1) != 1 or h2.stride(0) % 8:
             h2 = h2.contiguous()
@@ -146,7 +152,7 @@ class AsyncTP:
         buf["calls"] += 1
         out = torch.empty(rows // self.world, N, dtype=torch.bfloat16, device=h.device)
         native.check(L.tt_gemm_reduce_scatter(h2.data_ptr(), w.data_ptr(), buf["stage"], ctypes.cast(buf["count"], _PP),
-                                              out.data_ptr(), self.world, self.rank, rows, N, K, h2.stride(0), 0,
+                                              out.data_ptr(), self.world, self.rank, rows, N, K, h2.stride(0), int(b_mn),
                                               w.stride(0), buf["calls"], 0, _stream()),
                      "tt_gemm_reduce_scatter")
         self.fused_calls += 1
@@ -173,8 +179,8 @@ class AsyncTP:
 
     def project(self, att, x_local):
         xg, q = self.ag_linear(x_local, att.wq.weight)
-        k = _LinearOnGathered.apply(xg, x_local, att.wk.weight, self.group)
-        v = _LinearOnGathered.apply(xg, x_local, att.wv.weight, self.group)
+        k = _LinearOnGathered.apply(xg, x_local, att.wk.weight, self.group, self)
+        v = _LinearOnGathered.apply(xg, x_local, att.wv.weight, self.group, self)
         return q, k, v
 
     def output(self, att, o):
@@ -196,15 +202,29 @@ class _AgLinear(torch.autograd.Function):
         from .tp import all_gather_seq
 
         x, weight = ctx.saved_tensors
-        group = ctx.atp.group
-        W = ctx.atp.world
+        atp = ctx.atp
+        group, W = atp.group, atp.world
         gy2 = gy.reshape(-1, gy.shape[-1])
-        gx_full = gy2 @ weight                                   # [S, K]
-        gx = torch.empty(gx_full.shape[0] // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
-        dist.reduce_scatter_tensor(gx, gx_full.contiguous(), group=group)
+        gx = _input_grad_rs(atp, gy2, weight)
         xg = all_gather_seq(x.detach(), group).reshape(-1, x.shape[-1])
         gw = gy2.t() @ xg
         return gx.view_as(x), gw, None
+
+
+def _input_grad_rs(atp: "AsyncTP", gy2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``reduce_scatter_rows(gy2 @ weight)`` for a column-parallel layer's input gradient: the fused GEMM ->
+    reduce-scatter when the shapes allow (``weight`` [N, K] is read as the [contraction, output] operand), else the
+    collective."""
+    W = atp.world
+    gy2 = gy2 if gy2.is_contiguous() else gy2.contiguous()
+    rows = gy2.shape[0]
+    if (native.has("tt_gemm_reduce_scatter") and gy2.is_cuda and gy2.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and rows % (128 * W) == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0):
+        return atp._forward_rs(gy2.view(1, rows, -1), weight, b_mn=True).view(rows // W, weight.shape[1])
+    gx_full = gy2 @ weight
+    gx = torch.empty(rows // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
+    dist.reduce_scatter_tensor(gx, gx_full.contiguous(), group=atp.group)
+    return gx
 
 
 class _LinearRs(torch.autograd.Function):
@@ -221,7 +241,15 @@ class _LinearRs(torch.autograd.Function):
         from .tp import all_gather_seq
 
         h, weight = ctx.saved_tensors
-        g_full = all_gather_seq(gy.contiguous(), ctx.atp.group).reshape(-1, gy.shape[-1])   # [S, N]
+        atp = ctx.atp
+        gy = gy.contiguous()
+        if atp.supported(gy, weight):
+            # all-gather of the output gradient fused into the input-gradient GEMM; the gathered copy feeds the weight gradient
+            g_full, gh = atp._forward(gy, weight, b_mn=True)
+            g_full = g_full.reshape(-1, gy.shape[-1])
+            gw = g_full.t() @ h.reshape(-1, h.shape[-1])
+            return gh.view_as(h), gw, None
+        g_full = all_gather_seq(gy, atp.group).reshape(-1, gy.shape[-1])                       # [S, N]
         gh = (g_full @ weight).view_as(h)
         gw = g_full.t() @ h.reshape(-1, h.shape[-1])
         return gh, gw, None
@@ -236,7 +264,7 @@ def fused_ffn_forward(ff, x_local, group):
     atp: AsyncTP = ff._async_tp
     xg, h1 = atp.ag_linear(x_local, ff.w1.weight)
     # w3 must use xg before the buffer is recycled; it is consumed right here. For backward it re-gathers (collective).
-    h3 = _LinearOnGathered.apply(xg, x_local, ff.w3.weight, group)
+    h3 = _LinearOnGathered.apply(xg, x_local, ff.w3.weight, group, atp)
     h = ops.swiglu(h1, h3)
     if getattr(ff.w2, "bias", None) is None and getattr(ff.w2, "quant", None) is None and atp.rs_supported(h, ff.w2.weight):
         return atp.linear_rs(h, ff.w2.weight), True
@@ -247,11 +275,12 @@ class _LinearOnGathered(torch.autograd.Function):
     """``xg @ w^T`` where ``xg`` is a transient gathered copy of the sequence-sharded ``x``: saves only the shard."""
 
     @staticmethod
-    def forward(ctx, xg, x_local, weight, group):
+    def forward(ctx, xg, x_local, weight, group, atp=None):
         from torchtitan_b200 import ops
 
         ctx.save_for_backward(x_local, weight)
         ctx.group = group
+        ctx.atp = atp
         with torch.no_grad():
             return ops.linear(xg, weight, None)
 
@@ -262,8 +291,11 @@ class _LinearOnGathered(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         W = dist.get_world_size(ctx.group)
         gy2 = gy.reshape(-1, gy.shape[-1])
-        gx_full = gy2 @ weight
-        gx = torch.empty(gx_full.shape[0] // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
-        dist.reduce_scatter_tensor(gx, gx_full.contiguous(), group=ctx.group)
+        if ctx.atp is not None:
+            gx = _input_grad_rs(ctx.atp, gy2, weight)
+        else:
+            gx_full = gy2 @ weight
+            gx = torch.empty(gx_full.shape[0] // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
+            dist.reduce_scatter_tensor(gx, gx_full.contiguous(), group=ctx.group)
         xg = all_gather_seq(x.detach(), ctx.group).reshape(-1, x.shape[-1])
-        return None, gx.view_as(x), gy2.t() @ xg, None
+        return None, gx.view_as(x), gy2.t() @ xg, None, None
