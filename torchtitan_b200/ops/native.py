@@ -73,6 +73,15 @@ def lib():
     _sig(L.tt_moe_rowdot, [P, P, P, P, LL, I, I, P])
     _sig(L.tt_gemm_fp8, [P, P, P, I, I, I, LL, LL, LL, I, I, I, P, P, I, P])
     _sig(L.tt_gemm_allgather_a, [P, P, I, I, I, P, P, I, I, I, I, LL, LL, I, P, I, I, P])
+    if hasattr(L, "tt_ep_push"):
+        _sig(L.tt_ep_publish_counts, [P, P, P, I, I, I, I, P])
+        _sig(L.tt_ep_build_maps, [P, P, I, I, I, I, I, I, I, P, P, P, P, P, P, P, I, P])
+        _sig(L.tt_ep_push, [P, P, I, P, P, P, P, I, I, I, P])
+        _sig(L.tt_ep_wait, [P, I, P])
+        _sig(L.tt_ep_error, [P])
+        L.tt_ep_set_wait_ns.argtypes = [ctypes.c_ulonglong]
+        L.tt_ep_set_wait_ns.restype = None
+        _sig(L.tt_ep_push_ctas, [])
     if hasattr(L, "tt_gemm_mxfp8"):
         _sig(L.tt_gemm_mxfp8, [P, P, P, P, P, I, I, I, LL, LL, LL, I, P])
         _sig(L.tt_mx_swizzle_scales, [P, I, I, I, P, P])
@@ -132,4 +141,8 @@ def kernel_errors() -> dict:
     out = {"gemm": L.tt_gemm_error(), "attention": L.tt_attn_error(), "grouped_gemm": L.tt_grouped_gemm_error()}
     if hasattr(L, "tt_gemm_mx_error"):
         out["gemm_mx"] = L.tt_gemm_mx_error()
+    if hasattr(L, "tt_ep_error"):
+        e4 = (ctypes.c_int * 4)()
+        if L.tt_ep_error(e4) == 1:
+            out["ep"] = tuple(e4)
     return {k: v for k, v in out.items() if v}

@@ -218,6 +218,15 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
     # 64-row groups let the device-side grouped GEMM (incl. its weight-gradient form) run without host-side sizes
     alignment = GROUP_ALIGN_NATIVE if (torch.cuda.is_available() and native.has("tt_grouped_gemm")) else 8
     cf = parallelism.hybridep_non_blocking_expert_capacity_factor if parallelism is not None else None
+    # 'deepep' / 'hybridep' select the peer-memory dispatch / combine kernels (no external library); they need every rank
+    # of the expert-parallel group on one NVLink domain, else the collective dispatcher is used
+    nvlink_ep = False
+    if ep_mesh is not None and getattr(parallelism, "expert_parallel_comm_backend", "standard") in ("deepep", "hybridep"):
+        from .nvlink_ep import NvlinkDispatcher
+
+        nvlink_ep = NvlinkDispatcher.available(ep_mesh)
+        if not nvlink_ep:
+            logger.info("expert_parallel_comm_backend: peer-memory dispatch unavailable here; using all-to-all collectives")
     n = 0
     for block in model.layers.values():
         if not getattr(block, "moe_enabled", False):
@@ -235,7 +244,14 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
                 _mark_replicated(moe.experts, tp_mesh.get_group(), tp_mesh)
         if ep_mesh is not None:
             _shard_experts(moe.experts, ep_mesh)
-            moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, moe.router.num_experts, alignment=alignment, capacity_factor=cf)
+            if nvlink_ep and not moe.score_before_experts:
+                from .nvlink_ep import NvlinkDispatcher
+
+                moe.experts.dispatcher = NvlinkDispatcher(ep_mesh, moe.router.num_experts, alignment=GROUP_ALIGN_NATIVE,
+                                                          capacity_factor=cf)
+            else:
+                moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, moe.router.num_experts, alignment=alignment,
+                                                            capacity_factor=cf)
         if etp_mesh is not None:
             if moe.aux_loss_coeff > 0.0:
                 raise NotImplementedError("the auxiliary load-balance loss is not supported with expert tensor parallel")

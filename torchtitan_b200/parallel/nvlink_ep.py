@@ -1,0 +1,178 @@
+"""Expert-parallel dispatch / combine over NVLink peer memory (``csrc/ep.cu``): permutation and all-to-all in one kernel,
+counts exchanged through peer memory, group offsets kept on the device -- no collective library call and no device-to-host
+read on the path. Drop-in for :class:`parallel.ep.AllToAllDispatcher` (same ``dispatch`` / ``combine`` contract).
+
+The receive buffer has a fixed capacity of ``capacity_factor x`` the rows a rank sends (plus alignment padding); rows that
+do not fit are dropped and reported through ``native.kernel_errors()``. Received rows are copied out of the symmetric buffer
+(which is recycled two calls later) into an ordinary tensor, with the padding rows zeroed in the same pass.
+Parity: the DeepEP / HybridEP backends of the reference (torchtitan/distributed/deepep, hybridep: NVLink buffers, fused
+permute, optional fixed-capacity non-blocking mode), without the external library."""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from torchtitan_b200.ops import native
+
+from .nvlink_comm import _PP, SymmetricHeap, _stream
+
+_I32 = torch.int32
+
+
+class _Shared:
+    """Buffers and call counters shared by all MoE layers of one expert-parallel group with the same (rows, width)."""
+
+    def __init__(self, heap: SymmetricHeap, n: int, D: int, E: int, cap: int):
+        self.heap, self.n, self.D, self.E, self.cap = heap, n, D, E, cap
+        W = heap.world
+        self.recv, self.ret, self.table, self.flags, self.arrive = [], [], [], [], {"fwd": [], "rev": []}
+        for _ in range(2):
+            self.recv.append(self._buf(cap * D * 2, cap * D, torch.bfloat16, (cap, D)))
+            self.ret.append(self._buf(n * D * 2, n * D, torch.bfloat16, (n, D)))
+            self.table.append(self._buf(W * E * 4, W * E, _I32, (W, E)))
+            self.flags.append(self._buf(W * 4, W, _I32, (W,)))
+            for d in ("fwd", "rev"):
+                self.arrive[d].append(self._buf(4, 1, _I32, (1,)))
+        self.dispatch_calls = 0
+        self.dir_calls = {"fwd": 0, "rev": 0}
+        self.ctas = native.lib().tt_ep_push_ctas()
+
+    def _buf(self, nbytes, numel, dtype, shape):
+        off = self.heap.alloc(nbytes, align=1024)
+        ptrs, keep = self.heap.peer_ptrs(off)
+        return {"local": self.heap.local_tensor(off, numel, dtype).view(shape), "peers": ptrs, "keep": keep,
+                "ptr": self.heap.base + off}
+
+
+class _Exchange(torch.autograd.Function):
+    """``direction == "fwd"``: this rank's rows (optionally gathered through ``in_index``) -> the owners' expert-grouped
+    buffers, returns this rank's received rows [cap, D]; ``"rev"``: received-layout rows -> the sources' sorted order,
+    returns [n, D]. Backward is the opposite direction."""
+
+    @staticmethod
+    def forward(ctx, rows, in_index, maps, sh: _Shared, direction: str):
+        ctx.maps, ctx.sh, ctx.direction = maps, sh, direction
+        ctx.in_index, ctx.in_rows = in_index, rows.shape[0]
+        return _exchange(rows, in_index, maps, sh, direction)
+
+    @staticmethod
+    def backward(ctx, g):
+        sh, maps = ctx.sh, ctx.maps
+        back = "rev" if ctx.direction == "fwd" else "fwd"
+        out = _exchange(g.contiguous(), None, maps, sh, back)
+        if ctx.direction == "fwd" and ctx.in_index is not None:
+            # rows were gathered through in_index: add the gradients of the copies of each source row
+            gx = g.new_zeros(ctx.in_rows, g.shape[-1])
+            gx.index_add_(0, ctx.in_index.long(), out)
+            return gx, None, None, None, None
+        return out, None, None, None, None
+
+
+def _exchange(rows, in_index, maps, sh: _Shared, direction: str):
+    L = native.lib()
+    W = sh.heap.world
+    sh.dir_calls[direction] += 1
+    par = sh.dir_calls[direction] % 2
+    per_parity_calls = (sh.dir_calls[direction] + 1) // 2 if par else sh.dir_calls[direction] // 2   # calls on this buffer
+    arrive = sh.arrive[direction][par]
+    if direction == "fwd":
+        n_in = maps["n"] if in_index is not None else rows.shape[0]
+        native.check(L.tt_ep_push(rows.data_ptr(), in_index.data_ptr() if in_index is not None else None, n_in,
+                                  maps["dst_rank"].data_ptr(), maps["dst_row"].data_ptr(), sh.recv[par]["peers"],
+                                  arrive["peers"], W, sh.D, sh.cap, _stream()), "tt_ep_push")
+        native.check(L.tt_ep_wait(arrive["ptr"], per_parity_calls * W * sh.ctas, _stream()), "tt_ep_wait")
+        valid = (maps["rev_rank"] >= 0).unsqueeze(1)
+        return torch.where(valid, sh.recv[par]["local"], torch.zeros((), dtype=torch.bfloat16, device=rows.device))
+    native.check(L.tt_ep_push(rows.data_ptr(), None, sh.cap, maps["rev_rank"].data_ptr(), maps["rev_row"].data_ptr(),
+                              sh.ret[par]["peers"], arrive["peers"], W, sh.D, sh.n, _stream()), "tt_ep_push")
+    native.check(L.tt_ep_wait(arrive["ptr"], per_parity_calls * W * sh.ctas, _stream()), "tt_ep_wait")
+    out = sh.ret[par]["local"].clone()
+    dropped = maps["dst_rank"] < 0                      # rows that did not fit a receive buffer come back as zeros
+    return torch.where(dropped.unsqueeze(1), torch.zeros((), dtype=out.dtype, device=out.device), out)
+
+
+class NvlinkDispatcher:
+    _heaps: dict = {}
+    _shared: dict = {}
+
+    def __init__(self, ep_mesh, num_experts: int, alignment: int = 64, capacity_factor: float | None = None,
+                 heap_bytes: int = 3 << 30):
+        self.group = ep_mesh.get_group()
+        self.ep, self.rank = ep_mesh.size(), ep_mesh.get_local_rank()
+        assert num_experts % self.ep == 0, f"ep ({self.ep}) must divide num_experts ({num_experts})"
+        self.num_experts, self.local_experts = num_experts, num_experts // self.ep
+        self.alignment = alignment
+        self.capacity_factor = capacity_factor if capacity_factor is not None else 2.0
+        self.heap_bytes = heap_bytes
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._mesh, self._fallback = ep_mesh, None
+
+    @classmethod
+    def available(cls, ep_mesh) -> bool:
+        if not (torch.cuda.is_available() and native.available() and native.has("tt_ep_push")):
+            return False
+        W = ep_mesh.size()
+        me = torch.cuda.current_device()
+        ok = 2 <= W <= 16 and torch.cuda.device_count() >= W and all(
+            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=ep_mesh.get_group())
+        return bool(int(flag.item()))
+
+    def _state(self, n: int, D: int) -> _Shared:
+        gid = id(self.group)
+        if gid not in NvlinkDispatcher._heaps:
+            NvlinkDispatcher._heaps[gid] = SymmetricHeap(self.group, self.heap_bytes, self.device)
+        key = (gid, n, D, self.num_experts)
+        if key not in NvlinkDispatcher._shared:
+            cap = int(n * self.capacity_factor) + self.local_experts * self.alignment
+            cap = (cap + self.alignment - 1) // self.alignment * self.alignment
+            NvlinkDispatcher._shared[key] = _Shared(NvlinkDispatcher._heaps[gid], n, D, self.num_experts, cap)
+            dist.barrier(group=self.group)
+        return NvlinkDispatcher._shared[key]
+
+    def dispatch(self, x, order, counts, top_k: int):
+        if x.dtype != torch.bfloat16 or x.shape[-1] % 8:
+            # the peer-memory kernels move bf16 rows of a multiple of 8 elements: anything else takes the collectives
+            if self._fallback is None:
+                from .ep import AllToAllDispatcher
+
+                self._fallback = AllToAllDispatcher(self._mesh, self.num_experts, alignment=self.alignment)
+            rows, sizes, ctx = self._fallback.dispatch(x, order, counts, top_k)
+            ctx["fallback"] = True
+            return rows, sizes, ctx
+        L = native.lib()
+        n, D = order.numel(), x.shape[-1]
+        sh = self._state(n, D)
+        sh.dispatch_calls += 1
+        par = sh.dispatch_calls % 2
+        version = (sh.dispatch_calls + 1) // 2 if par else sh.dispatch_calls // 2      # dispatches on this count table
+        W, E, dev = self.ep, self.num_experts, x.device
+        c64 = counts.to(torch.int64).contiguous()
+        native.check(L.tt_ep_publish_counts(c64.data_ptr(), sh.table[par]["peers"], sh.flags[par]["peers"], W, self.rank, E,
+                                            version, _stream()), "tt_ep_publish_counts")
+        maps = {"n": n, "dst_rank": torch.empty(n, dtype=_I32, device=dev), "dst_row": torch.empty(n, dtype=_I32, device=dev),
+                "rev_rank": torch.empty(sh.cap, dtype=_I32, device=dev), "rev_row": torch.empty(sh.cap, dtype=_I32, device=dev),
+                "offs": torch.empty(self.local_experts, dtype=_I32, device=dev), "info": torch.empty(2, dtype=_I32, device=dev)}
+        native.check(L.tt_ep_build_maps(sh.table[par]["ptr"], sh.flags[par]["ptr"], W, self.rank, E, self.alignment, n, sh.cap,
+                                        version, maps["dst_rank"].data_ptr(),
+                                        maps["dst_row"].data_ptr(), maps["rev_rank"].data_ptr(), maps["rev_row"].data_ptr(),
+                                        maps["offs"].data_ptr(), maps["info"].data_ptr(), None, D, _stream()),
+                     "tt_ep_build_maps")
+        src_index = (order // top_k).to(_I32).contiguous()
+        recv = _Exchange.apply(x.contiguous(), src_index, maps, sh, "fwd")
+        offs = maps["offs"].to(torch.int64)
+        sizes = offs - torch.cat((offs.new_zeros(1), offs[:-1]))
+        sizes._tt_aligned = self.alignment
+        return recv, sizes, {"maps": maps, "sh": sh}
+
+    def scale_rows(self, rows, scores_sorted, ctx):
+        raise NotImplementedError("the NVLink dispatcher applies the routing scores after the experts (score_before_experts=False)")
+
+    def combine(self, y, ctx):
+        if ctx.get("fallback"):
+            return self._fallback.combine(y, ctx)
+        return _Exchange.apply(y.contiguous(), None, ctx["maps"], ctx["sh"], "rev")

@@ -231,7 +231,9 @@ def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, error_i
     buckets: dict[tuple, list] = {}
 
     def add(groups, tensor):
-        key = tuple(sorted(id(g) for g in groups))
+        # the reductions of a bucket run group after group: every rank must walk them in the same order, so keep the
+        # order in which the parameter lists them (placements first, then tagged groups) -- never an order by object id
+        key = tuple(id(g) for g in groups)
         for g in groups:
             group_objs[id(g)] = g
         buckets.setdefault(key, []).append(tensor)
