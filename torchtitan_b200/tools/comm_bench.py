@@ -3,6 +3,7 @@
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m torchtitan_b200.tools.comm_bench ag_gemm \\
         --seq 8192 --kdim 4096 --ndim 7168
 
+``ep``: expert-parallel dispatch + combine round trip, peer-memory kernels (``csrc/ep.cu``) vs all-to-all collectives.
 ``gemm_rs``: row-parallel GEMM with the sequence reduce-scatter in its epilogue (``tt_gemm_reduce_scatter``) against the
 GEMM followed by NCCL reduce-scatter (``--kdim`` is the full contraction, split over the ranks).
 ``ag_gemm``: sequence all-gather fused into the consuming GEMM (``tt_gemm_allgather_a``) against NCCL all-gather followed
@@ -141,20 +142,60 @@ def bench_gemm_rs(args):
         }))
 
 
+def bench_ep(args):
+    """Expert-parallel dispatch + combine round trip (forward): the peer-memory kernels vs all-to-all collectives with their
+    device-to-host read of the split sizes. Tokens per rank = --seq, width = --kdim, experts = --experts, top-k = --topk."""
+    from torchtitan_b200.ops import native
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.parallel.ep import AllToAllDispatcher
+    from torchtitan_b200.parallel.nvlink_ep import NvlinkDispatcher
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pd = ParallelDims(dp_replicate=1, dp_shard=world, cp=1, tp=1, pp=1, ep=world, etp=1, world_size=world)
+    mesh = pd.get_mesh("ep")
+    assert NvlinkDispatcher.available(mesh), "peer access / native library missing"
+    T, D, E, k = args.seq, args.k, args.experts, args.topk
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    x = torch.randn(T, D, device="cuda", generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda", generator=g)[:k] for _ in range(64)]).repeat(T // 64 + 1, 1)[:T]
+    order = torch.argsort(idx.flatten(), stable=True)
+    counts = torch.bincount(idx.flatten(), minlength=E)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    res = {}
+    for name, disp in (("nvlink", NvlinkDispatcher(mesh, E, alignment=64)), ("all_to_all", AllToAllDispatcher(mesh, E, alignment=64))):
+        def round_trip():
+            with torch.no_grad():
+                rows, sizes, ctx = disp.dispatch(x, order, counts, k)
+                return disp.combine(rows, ctx)
+        back = round_trip()
+        assert torch.equal(back, x[order // k]), name            # every row comes home unchanged
+        res[name + "_ms"] = _time(round_trip, args.iters, flush)
+    n = T * k
+    remote = (world - 1) / world * n * D * 2 * 2                  # bytes this rank sends (dispatch) + gets back (combine)
+    if rank == 0:
+        print(json.dumps({
+            "case": "ep_dispatch_combine", "world": world, "tokens_per_rank": T, "top_k": k, "experts": E, "width": D,
+            **res, "speedup_vs_all_to_all": res["all_to_all_ms"] / res["nvlink_ms"],
+            "nvlink_roofline_ms": remote / 2 / 770e9 * 1e3 * 2, "rows": n, "kernel_errors": native.kernel_errors(),
+        }))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["ag_gemm", "gemm_rs"])
+    ap.add_argument("what", choices=["ag_gemm", "gemm_rs", "ep"])
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--kdim", dest="k", type=int, default=4096)
     ap.add_argument("--ndim", dest="n", type=int, default=7168)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--copy-ctas", type=int, default=16)
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--topk", type=int, default=8)
     args = ap.parse_args()
     rank = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     try:
-        (bench_ag_gemm if args.what == "ag_gemm" else bench_gemm_rs)(args)
+        {"ag_gemm": bench_ag_gemm, "gemm_rs": bench_gemm_rs, "ep": bench_ep}[args.what](args)
     finally:
         dist.destroy_process_group()
 
