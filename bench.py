@@ -88,7 +88,8 @@ def _dist_env():
     return rank, world, local
 
 
-def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, layers: int | None = None):
+def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, layers: int | None = None,
+                  extra: list[str] | None = None):
     from torchtitan_b200.config.manager import ConfigManager
     from torchtitan_b200.models.llama3 import llama3_configs
 
@@ -102,6 +103,7 @@ def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, lay
     ]
     if ac_mode:
         args += ["--activation_checkpoint.mode", ac_mode]
+    args += list(extra or [])
     cfg = ConfigManager().parse_args(args)
     return cfg.build()
 
@@ -146,7 +148,7 @@ def run_ours(args) -> dict:
     if rank == 0:
         init_logger()
     total_steps = args.warmup + 2 * args.steps + 4
-    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers)
+    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers, args.override)
     dev = trainer.device
     local_bs = trainer.config.training.local_batch_size
     tokens_per_step = local_bs * SEQ_LEN * world
@@ -231,6 +233,8 @@ def run_ours(args) -> dict:
     }
     if args.layers is not None:
         out["invalid_truncated_model_layers"] = args.layers
+    if args.override:
+        out["config"]["overrides"] = list(args.override)
     trainer.close()
     return out
 
@@ -247,6 +251,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--override", type=lambda v: v.split(), default=[], help="extra config flags for experiments as one "
+                    "string, e.g. --override='--parallelism.fsdp_reshard_after_forward never' (recorded in the JSON line)")
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: truncate the model (result is not a benchmark)")
     ap.add_argument("--ref-compile", action="store_true", help="reference arm only: add --compile.enable")
     ap.add_argument("--ac", default=None, help="override activation_checkpoint.mode (selective|full|none)")
