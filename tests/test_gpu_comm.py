@@ -136,6 +136,11 @@ def test_fused_gemm_reduce_scatter_single_gpu_emulation(L):
     computes and reduces its own rows; the next call (counters keep counting) rotates which rank goes last."""
     if not hasattr(L, "tt_gemm_reduce_scatter"):
         pytest.skip("library built without tt_gemm_reduce_scatter")
+    for mode in (0, 1):                  # peer-owned tiles first / interleaved tile order
+        L.tt_gemm_rs_set_interleave(mode)
+        _rs_case(L, 2, 512, 256, 768)
+        _rs_case(L, 4, 128, 192, 264)
+    L.tt_gemm_rs_set_interleave(-1)
     _rs_case(L, 2, 512, 256, 768)        # whole 256-row tiles per rank: CTA-pair kernel
     _rs_case(L, 2, 256, 128, 328)        # CTA-pair kernel, ragged last column tile (72 columns)
     _rs_case(L, 4, 128, 192, 264)        # single-CTA tile kernel, ragged N tile

@@ -47,6 +47,8 @@ struct GemmArgs {
   // memory over NVLink into the local buffer and publish one flag per panel; the GEMM CTAs wait for the panel they need.
   int flags_by_m;       // ready_flags index = m-tile (A operand gathered) instead of n-tile (B operand gathered)
   int m_rot;            // tiles visit m-panels starting at this offset (the local shard first)
+  int m_interleave;     // 1: visit the blocks round-robin (tile j of every block before tile j + 1 of any), which spreads the
+                        // peer-bound stores of the fused reduce-scatter over the whole launch instead of its first part
   int m_block;          // m-tiles per ordering block: all tiles of one block are visited before the next block (the fused
                         // reduce-scatter sets it to the m-tiles per rank, so every peer-owned tile precedes the own ones)
   int copy_ctas;
@@ -94,9 +96,17 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // Tile t of the persistent schedule -> (tm, tn): blocks of `m_block` m-tiles one after another, the grouped order inside
 // a block, then the rotation.
 __device__ __forceinline__ void tile_coords_p(const GemmArgs& p, int t, int& tm, int& tn) {
-  const int blk_tiles = p.m_block * p.tiles_n;
-  const int blk = t / blk_tiles;
-  tile_coords(t - blk * blk_tiles, p.m_block, p.tiles_n, tm, tn);
+  int blk, local;
+  if (p.m_interleave) {
+    const int nblk = p.tiles_m / p.m_block;
+    local = t / nblk;
+    blk = t - local * nblk;
+  } else {
+    const int blk_tiles = p.m_block * p.tiles_n;
+    blk = t / blk_tiles;
+    local = t - blk * blk_tiles;
+  }
+  tile_coords(local, p.m_block, p.tiles_n, tm, tn);
   tm = (tm + blk * p.m_block + p.m_rot) % p.tiles_m;
 }
 
@@ -767,6 +777,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
 int g_num_sms = 0;
 bool g_pair_enabled = true;
+int g_rs_interleave = -1;   // -1: by the burst estimate, 0 / 1: forced (tests)
 
 void set_kernel_attrs() {
   cudaFuncSetAttribute(gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
@@ -817,7 +828,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
-    p.m_block = p.tiles_m;
+    p.m_block = p.tiles_m; p.m_interleave = 0;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, a_mn, b_mn);
     int clusters = p.tiles_m * p.tiles_n;
@@ -826,7 +837,7 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     pair::gemm_bf16_pair_kernel<false><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = (M + BM - 1) / BM;
-    p.m_block = p.tiles_m;
+    p.m_block = p.tiles_m; p.m_interleave = 0;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, a_mn, b_mn);
     int grid = p.tiles_m * p.tiles_n;
@@ -869,7 +880,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
   p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr; p.rs_world = 0;
   if (use_pair) {
     p.tiles_m = (M + pair::TM - 1) / pair::TM;
-    p.m_block = p.tiles_m;
+    p.m_block = p.tiles_m; p.m_interleave = 0;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_f8(pair::TM, pair::TN, a_e5m2, b_e5m2);
     int clusters = p.tiles_m * p.tiles_n;
@@ -877,7 +888,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
     pair::gemm_bf16_pair_kernel<true><<<clusters * 2, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = (M + BM - 1) / BM;
-    p.m_block = p.tiles_m;
+    p.m_block = p.tiles_m; p.m_interleave = 0;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_f8(BM, BN, a_e5m2, b_e5m2);
     int grid = p.tiles_m * p.tiles_n;
@@ -935,7 +946,7 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
   // all CTAs must be co-resident (GEMM CTAs wait on flags written by copy CTAs): one CTA per SM, grid <= SM count
   if (use_pair) {
     p.tiles_m = M / pair::TM;
-    p.m_block = p.tiles_m;
+    p.m_block = p.tiles_m; p.m_interleave = 0;
     p.tiles_n = (N + pair::TN - 1) / pair::TN;
     p.idesc = tt::umma_idesc_bf16(pair::TM, pair::TN, 0, b_mn);
     p.m_rot = rank * (p.panels_per_rank / 2);
@@ -944,7 +955,7 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
     pair::gemm_bf16_pair_kernel<false><<<clusters * 2 + p.copy_ctas, NUM_THREADS, pair::PSMEM_BYTES, stream>>>(ta, tb, p);
   } else {
     p.tiles_m = M / BM;
-    p.m_block = p.tiles_m;
+    p.m_block = p.tiles_m; p.m_interleave = 0;
     p.tiles_n = (N + BN - 1) / BN;
     p.idesc = tt::umma_idesc_bf16(BM, BN, 0, b_mn);
     p.m_rot = rank * p.panels_per_rank;
@@ -991,6 +1002,15 @@ int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, in
   for (int r = 0; r < 16; ++r) { p.rs_stage[r] = r < world ? stages[r] : nullptr; p.rs_count[r] = r < world ? counts[r] : nullptr; }
   p.copy_ctas = 0;
   p.rs_skip_own = contribute_only;
+  // Peer-owned tiles come first, so (world - 1) / world of the output crosses NVLink during the first part of the launch.
+  // When that burst would need more than ~400 GB/s, interleave peer-owned and own tiles instead (own tile j then waits
+  // for the peers' tile j, which they compute in the same round).
+  {
+    const double t_gemm = 2.0 * M * static_cast<double>(N) * K / 1.5e15;
+    const double bytes = static_cast<double>(world - 1) / world * M * static_cast<double>(N) * 2.0;
+    const bool burst = world > 1 && bytes / (t_gemm * (world - 1) / world) > 400e9;
+    p.m_interleave = g_rs_interleave < 0 ? (burst ? 1 : 0) : g_rs_interleave;
+  }
   p.rs_tiles_n = (N + 255) / 256;      // both tile kernels use 256 columns
   p.rs_target = call_index * 4;        // 4 epilogue warps store each (128-row panel, column tile)
   if (use_pair) {
@@ -1016,6 +1036,10 @@ int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, in
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// Tile order of the fused reduce-scatter: -1 = choose by the NVLink burst estimate, 0 = peer-owned tiles first, 1 =
+// interleaved; for tests and benchmarks.
+void tt_gemm_rs_set_interleave(int mode) { g_rs_interleave = mode; }
 
 // Select between the single-CTA (0) and CTA-pair (1, default) tile kernels; for tests and benchmarks.
 int tt_gemm_set_pair(int enabled) { g_pair_enabled = enabled != 0; return 0; }
