@@ -34,3 +34,8 @@ def _own_rendezvous_port(monkeypatch):
             s.bind(("127.0.0.1", 0))
             monkeypatch.setenv("MASTER_PORT", str(s.getsockname()[1]))
     yield
+    # an in-process trainer test must not leave its default process group to the next test
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()

@@ -10,7 +10,10 @@ import torch
 
 
 def _trainer(tmp_path, steps, extra=(), config="llama3_debugmodel_synthetic"):
+    from dist_utils import free_port
     from torchtitan_b200.config.manager import ConfigManager
+
+    os.environ["MASTER_PORT"] = str(free_port())            # every (re)initialised process group gets its own rendezvous port
 
     args = [
         "--module", "llama3", "--config", config, "--dump_folder", str(tmp_path),
@@ -50,9 +53,12 @@ def _run(tr, n=None):
 
 @pytest.fixture()
 def single_rank(monkeypatch):
+    import torch.distributed as dist
+
+    if dist.is_initialized():          # an earlier in-process trainer test of this worker may have left its group behind
+        dist.destroy_process_group()
     monkeypatch.setenv("LOCAL_RANK", "0")
     yield
-    import torch.distributed as dist
 
     if dist.is_initialized():
         dist.destroy_process_group()
