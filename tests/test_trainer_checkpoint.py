@@ -147,3 +147,36 @@ def test_validation_and_gradient_accumulation(tmp_path, single_rank):
     tr.validator.validate(tr.model_parts, tr.step)
     tr.close()
     assert len(losses) == 2
+
+
+def test_last_step_export_in_hf_format_and_reload(tmp_path, single_rank):
+    """The final model-only checkpoint can be written as Hugging Face safetensors (names converted by the model's
+    state-dict adapter) and a new run can start from it through ``initial_load_in_hf``."""
+    import glob
+
+    import torch.distributed as dist
+    from safetensors import safe_open
+
+    ck = ["--checkpoint.enable", "--checkpoint.interval", "100", "--checkpoint.folder", "ckpt",
+          "--checkpoint.last_save_model_only", "True", "--checkpoint.last_save_in_hf", "True"]
+    tr = _trainer(tmp_path, 2, ck)
+    _run(tr)
+    w = tr.model_parts[0].layers["0"].attention.wq.weight.detach().clone()
+    out = tr.model_parts[0].output.weight.detach().clone()
+    tr.close()
+    dist.destroy_process_group()
+    files = glob.glob(str(tmp_path / "ckpt" / "step-2" / "*.safetensors"))
+    assert files
+    names = set()
+    for f in files:
+        with safe_open(f, "pt") as sf:
+            names |= set(sf.keys())
+    assert "model.embed_tokens.weight" in names and "model.layers.0.self_attn.q_proj.weight" in names and "lm_head.weight" in names
+    fresh = _trainer(tmp_path / "second", 2, ["--checkpoint.enable", "--checkpoint.folder", "ckpt2",
+                                               "--checkpoint.initial_load_path", str(tmp_path / "ckpt" / "step-2"),
+                                               "--checkpoint.initial_load_in_hf", "True"])
+    assert fresh.checkpointer.load(step=-1)
+    assert fresh.step == 0                                    # model only: the run starts from step 0 with these weights
+    assert torch.equal(fresh.model_parts[0].output.weight.detach(), out)
+    assert torch.allclose(fresh.model_parts[0].layers["0"].attention.wq.weight.detach(), w)
+    fresh.close()
