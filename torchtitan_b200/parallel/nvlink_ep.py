@@ -89,9 +89,9 @@ def _exchange(rows, in_index, maps, sh: _Shared, direction: str):
     native.check(L.tt_ep_push(rows.data_ptr(), None, sh.cap, maps["rev_rank"].data_ptr(), maps["rev_row"].data_ptr(),
                               sh.ret[par]["peers"], arrive["peers"], W, sh.D, sh.n, _stream()), "tt_ep_push")
     native.check(L.tt_ep_wait(arrive["ptr"], per_parity_calls * W * sh.ctas, _stream()), "tt_ep_wait")
-    out = sh.ret[par]["local"].clone()
     dropped = maps["dst_rank"] < 0                      # rows that did not fit a receive buffer come back as zeros
-    return torch.where(dropped.unsqueeze(1), torch.zeros((), dtype=out.dtype, device=out.device), out)
+    ret = sh.ret[par]["local"]                          # copied out of the symmetric buffer in the same pass
+    return torch.where(dropped.unsqueeze(1), torch.zeros((), dtype=ret.dtype, device=ret.device), ret)
 
 
 class NvlinkDispatcher:
