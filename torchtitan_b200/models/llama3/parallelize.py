@@ -54,6 +54,8 @@ def apply_data_parallel(model, parallel_dims, training, parallelism):
         logger.info("Applied HSDP to the model" if parallel_dims.dp_replicate_enabled else "Applied FSDP to the model")
     elif parallel_dims.dp_replicate_enabled:
         apply_replicate(model, parallel_dims.get_mesh("dp_replicate"), param_dtype=param_dtype, reduce_dtype=reduce_dtype)
-    elif torch.cuda.is_available() and training.dtype == "float32" and not parallel_dims.tp_enabled and not parallel_dims.pp_enabled:
+    elif torch.cuda.is_available() and training.dtype == "float32" and not parallel_dims.pp_enabled:
+        # no data-parallel sharding (one GPU, or tensor parallel only): the same units with a shard world of one keep an
+        # fp32 master and a bf16 compute copy, so the bf16 kernels and the flat-shard optimizer still apply
         apply_single_device_units(model, param_dtype=param_dtype, reduce_dtype=reduce_dtype)
         logger.info("Applied single-device mixed-precision units to the model")

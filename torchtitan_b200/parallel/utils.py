@@ -148,6 +148,13 @@ def maybe_enable_amp(parallel_dims, mixed_precision_param: str, dev_type: str):
     if parallel_dims.fsdp_enabled:
         logger.info("Mixed precision training is handled by fully_shard")
         return contextlib.nullcontext()
+    if parallel_dims.tp_enabled and not parallel_dims.pp_enabled and dev_type == "cuda":
+        from torchtitan_b200.config import TORCH_DTYPE_MAP
+
+        # tensor parallel without data-parallel sharding on a GPU: the model runs on single-device mixed-precision units
+        # (bf16 compute copies of fp32 masters); autocast covers the inputs that are still fp32
+        logger.info("Mixed precision training is handled by single-device units and AMP")
+        return torch.autocast(dev_type, dtype=TORCH_DTYPE_MAP[mixed_precision_param])
     if parallel_dims.tp_enabled or parallel_dims.pp_enabled:
         logger.warning("Mixed precision training with TP or PP is only supported when FSDP/HSDP/CP is enabled.")
         logger.info("Mixed precision training is disabled")
