@@ -206,9 +206,25 @@ class _AgLinear(torch.autograd.Function):
         group, W = atp.group, atp.world
         gy2 = gy.reshape(-1, gy.shape[-1])
         gx = _input_grad_rs(atp, gy2, weight)
-        xg = all_gather_seq(x.detach(), group).reshape(-1, x.shape[-1])
-        gw = gy2.t() @ xg
+        gw = gy2.t() @ _regather(atp, x)
         return gx.view_as(x), gw, None
+
+
+def _regather(atp: "AsyncTP", x: torch.Tensor) -> torch.Tensor:
+    """The sequence-gathered copy of the saved shard ``x`` for a weight gradient. The projections that read the same
+    input (``wq`` / ``wk`` / ``wv``, ``w1`` / ``w3``) run their backward one after another: the last gathered copy is kept
+    and reused while the same tensor (same storage, same version) is asked for, so it is gathered once per group."""
+    from .tp import all_gather_seq
+
+    key = (x.data_ptr(), x._version, tuple(x.shape))
+    hit = atp.__dict__.get("_regather_cache")
+    if hit is not None and hit[0] == key:
+        return hit[2]
+    xg = all_gather_seq(x.detach(), atp.group).reshape(-1, x.shape[-1])
+    # the entry keeps ``x`` itself: while it is held its memory cannot be handed to another tensor, so an equal address
+    # (with an equal version) can only be the same activation
+    atp.__dict__["_regather_cache"] = (key, x, xg)
+    return xg
 
 
 def _input_grad_rs(atp: "AsyncTP", gy2: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -293,6 +309,7 @@ class _LinearOnGathered(torch.autograd.Function):
         gy2 = gy.reshape(-1, gy.shape[-1])
         if ctx.atp is not None:
             gx = _input_grad_rs(ctx.atp, gy2, weight)
+            return None, gx.view_as(x), gy2.t() @ _regather(ctx.atp, x), None, None
         else:
             gx_full = gy2 @ weight
             gx = torch.empty(gx_full.shape[0] // W, gx_full.shape[1], dtype=gx_full.dtype, device=gx_full.device)
