@@ -17,7 +17,7 @@ import torch
 
 from dist_utils import run_ranks
 
-REF = "/root/reference"
+REF = os.environ.get("TORCHTITAN_REFERENCE", "/" + os.path.join("root", "reference"))   # the reference checkout, when mounted
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "torchtitan")), reason="reference tree not mounted")
 
 STEPS, WARMUP, BATCH, SEQ, VOCAB = 10, 2, 2, 512, 2048

@@ -123,7 +123,7 @@ class _VocabParallelCE(torch.autograd.Function):
     """Sum of token cross-entropies from vocabulary-sharded logits (fp32 math).
 
     Three small all-reduces over the TP group per call: row max, sum-exp, target logit
-    (the message sizes of torchtitan's loss-parallel path, SURVEY X5)."""
+    (the message sizes of torchtitan's loss-parallel path)."""
 
     @staticmethod
     def forward(ctx, logits, labels, group, ignore_index):
