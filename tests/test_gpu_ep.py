@@ -109,7 +109,7 @@ def test_ep_wait_reports_missing_arrivals():
         L.tt_ep_set_wait_ns(20_000_000_000)
 
 
-def _worker(rank, world):
+def _worker(rank, world, score_before=False):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
@@ -124,7 +124,7 @@ def _worker(rank, world):
     ep_mesh = pd.get_mesh("ep")
     assert NvlinkDispatcher.available(ep_mesh)
     kw = dict(num_experts=8, num_shared_experts=1, score_func="softmax", route_norm=True, top_k=2, hidden_dim=128,
-              score_before_experts=False)
+              score_before_experts=score_before)
     torch.manual_seed(0)
     base = MoE.Config(**kw).build(dim=128)
     base.init_weights(init_std=0.05, buffer_device=torch.device("cpu"))
@@ -157,10 +157,11 @@ def _worker(rank, world):
     return out
 
 
-def test_nvlink_dispatcher_matches_all_to_all_two_gpus(tmp_path):
+@pytest.mark.parametrize("score_before", [False, True])
+def test_nvlink_dispatcher_matches_all_to_all_two_gpus(tmp_path, score_before):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    for o in run_ranks(_worker, 2, tmp_path=tmp_path):
+    for o in run_ranks(_worker, 2, score_before, tmp_path=tmp_path):
         assert not o["errors"], o
         # same rows reach the same experts: results agree to bf16 rounding of the combine order
         assert max(o["y"]) < 2e-2 and max(o["dx"]) < 3e-2 and max(o["dw1"]) < 3e-2 and max(o["dgate"]) < 3e-2, o

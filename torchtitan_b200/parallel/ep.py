@@ -244,7 +244,7 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
                 _mark_replicated(moe.experts, tp_mesh.get_group(), tp_mesh)
         if ep_mesh is not None:
             _shard_experts(moe.experts, ep_mesh)
-            if nvlink_ep and not moe.score_before_experts:
+            if nvlink_ep:
                 from .nvlink_ep import NvlinkDispatcher
 
                 moe.experts.dispatcher = NvlinkDispatcher(ep_mesh, moe.router.num_experts, alignment=GROUP_ALIGN_NATIVE,

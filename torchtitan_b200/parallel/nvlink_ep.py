@@ -71,6 +71,31 @@ class _Exchange(torch.autograd.Function):
         return out, None, None, None, None
 
 
+class _ExchangeScores(torch.autograd.Function):
+    """One fp32 value per sorted row -> one per received row (and back for the gradient). A value rides in the first four
+    bytes of a 16-byte row, which the row kernels move as eight bf16 elements without looking at them."""
+
+    @staticmethod
+    def _pack(v):
+        buf = torch.zeros(v.shape[0], 4, dtype=torch.float32, device=v.device)
+        buf[:, 0] = v
+        return buf.view(torch.bfloat16)                                   # [rows, 8]
+
+    @staticmethod
+    def _unpack(rows):
+        return rows.contiguous().view(torch.float32)[:, 0].clone()
+
+    @staticmethod
+    def forward(ctx, scores, maps, sh8):
+        ctx.maps, ctx.sh8 = maps, sh8
+        return _ExchangeScores._unpack(_exchange(_ExchangeScores._pack(scores), None, maps, sh8, "fwd"))
+
+    @staticmethod
+    def backward(ctx, g):
+        back = _exchange(_ExchangeScores._pack(g.contiguous().float()), None, ctx.maps, ctx.sh8, "rev")
+        return _ExchangeScores._unpack(back), None, None
+
+
 def _exchange(rows, in_index, maps, sh: _Shared, direction: str):
     L = native.lib()
     W = sh.heap.world
@@ -170,7 +195,12 @@ class NvlinkDispatcher:
         return recv, sizes, {"maps": maps, "sh": sh}
 
     def scale_rows(self, rows, scores_sorted, ctx):
-        raise NotImplementedError("the NVLink dispatcher applies the routing scores after the experts (score_before_experts=False)")
+        """Routing scores applied before the experts: the fp32 scores travel through the same exchange as 16-byte rows."""
+        if ctx.get("fallback"):
+            return self._fallback.scale_rows(rows, scores_sorted, ctx)
+        sh8 = self._state(ctx["maps"]["n"], 8)
+        sc = _ExchangeScores.apply(scores_sorted.reshape(-1).float(), ctx["maps"], sh8)       # [cap] fp32, 0 on padding
+        return (rows.float() * sc.unsqueeze(1)).to(rows.dtype)
 
     def combine(self, y, ctx):
         if ctx.get("fallback"):
