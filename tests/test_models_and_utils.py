@@ -172,3 +172,25 @@ def test_peak_flops_table_memory_monitor_and_gc():
     finally:
         if was:
             gc.enable()
+
+
+def test_profiler_writes_traces_on_schedule_and_is_off_by_default(tmp_path):
+    import glob
+
+    from torchtitan_b200.tools.profiling import ProfilingConfig, maybe_enable_memory_snapshot, maybe_enable_profiling
+
+    with maybe_enable_profiling(ProfilingConfig(), base_folder=str(tmp_path)) as prof:
+        assert prof is None
+    cfg = ProfilingConfig(enable_profiling=True, profile_freq=3, profiler_warmup=1, profiler_active=1)
+    with maybe_enable_profiling(cfg, global_step=0, base_folder=str(tmp_path), leaf_folder="leaf") as prof:
+        for _ in range(6):
+            torch.randn(64, 64) @ torch.randn(64, 64)
+            prof.step()
+    traces = sorted(glob.glob(str(tmp_path / "profile_traces" / "iteration_*" / "leaf" / "rank0_trace.json")))
+    assert len(traces) == 2, traces                           # one trace per period of profile_freq steps
+    with pytest.raises(AssertionError):
+        with maybe_enable_profiling(ProfilingConfig(enable_profiling=True, profile_freq=2, profiler_warmup=3),
+                                    base_folder=str(tmp_path)):
+            pass
+    with maybe_enable_memory_snapshot(ProfilingConfig(enable_memory_snapshot=True), base_folder=str(tmp_path)) as snap:
+        assert snap is None or torch.cuda.is_available()      # memory snapshots need a CUDA device
