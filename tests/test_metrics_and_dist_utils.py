@@ -123,3 +123,20 @@ def test_clip_grad_norm_over_shards_matches_unsharded(tmp_path, norm_type):
     for o in run_ranks(_clip_worker, 2, norm_type, tmp_path=tmp_path):
         assert o["total"] == pytest.approx(o["want"], rel=1e-5)
         assert o["err"] < 1e-5
+
+
+def test_seed_dtensor_rng_skips_cpu_meshes_and_forwards_cuda_ones(monkeypatch):
+    """The DTensor tracker is created through ``manual_seed`` (no start-up broadcast over the default group)."""
+    import types
+
+    import torch.distributed.tensor._random as dtensor_random
+
+    from torchtitan_b200.parallel import utils as dist_utils
+
+    seen = []
+    monkeypatch.setattr(dtensor_random, "manual_seed", lambda seed, mesh: seen.append((seed, mesh.device_type)))
+    dist_utils.seed_dtensor_rng(None, 3)
+    dist_utils.seed_dtensor_rng(types.SimpleNamespace(device_type="cpu"), 3)
+    assert seen == []
+    dist_utils.seed_dtensor_rng(types.SimpleNamespace(device_type="cuda"), 2**63 + 5)
+    assert seen == [(5, "cuda")]

@@ -226,3 +226,19 @@ def test_disaggregated_fsdp_trainer_subgroup(tmp_path):
     assert [r["is_trainer"] for r in res] == [True, True, False]
     assert all(r["steps"] == 2 and r["version"] == 2 for r in res)
     assert torch.equal(res[0]["w"], res[1]["w"]) and torch.equal(res[2]["w"], res[0]["w"])
+
+
+def test_plan_microbatches_gives_every_rank_the_same_count():
+    """Reference: torchtitan/experiments/rl/actors/trainer.py (micro-batching of a rank's episodes). With a sharded
+    model every forward is a collective, so ranks with less to do split or repeat micro-batches."""
+    from torchtitan_b200.experiments.rl.trainer import plan_microbatches
+
+    lens = [[100, 100, 100, 100], [10, 10, 10, 10], [390]]
+    plans = [plan_microbatches(lens, r, cap=200) for r in range(3)]
+    assert plans[0] == ([[0, 1], [2, 3]], 2)
+    assert plans[1] == ([[0, 1], [2, 3]], 2)             # one greedy group, split in two
+    assert plans[2] == ([[0], [0]], 1)                   # nothing to split: a zero-weight repeat
+    for r, (groups, n_real) in enumerate(plans):
+        assert sorted(j for g in groups[:n_real] for j in g) == list(range(len(lens[r])))
+    with pytest.raises(ValueError):
+        plan_microbatches([[1], []], 1, cap=8)

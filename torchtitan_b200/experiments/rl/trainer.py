@@ -29,6 +29,39 @@ from .types import Episode
 from .weight_sync import full_tensor
 
 
+def _greedy_pack(lengths: list[int], cap: int) -> list[list[int]]:
+    groups, cur, tok = [], [], 0
+    for j, n in enumerate(lengths):
+        if cur and tok + n > cap:
+            groups.append(cur)
+            cur, tok = [], 0
+        cur.append(j)
+        tok += n
+    if cur:
+        groups.append(cur)
+    return groups
+
+
+def plan_microbatches(lengths_by_rank: list[list[int]], rank: int, cap: int) -> tuple[list[list[int]], int]:
+    """Micro-batches (lists of local episode indices) for ``rank`` such that every rank runs the same number of them.
+
+    Each rank's episodes are packed greedily under ``cap`` tokens; a rank with fewer micro-batches than the largest count
+    splits its biggest ones, and when it has no episode left to split it repeats its first micro-batch (the caller gives
+    the repeats zero weight). Returns ``(groups, n_real)``: ``groups[n_real:]`` are the repeats."""
+    target = max(len(_greedy_pack(l, cap)) for l in lengths_by_rank)
+    groups = _greedy_pack(lengths_by_rank[rank], cap)
+    if not groups:
+        raise ValueError(f"data-parallel rank {rank} has no episode: need at least one episode per trainer rank")
+    while len(groups) < target:
+        k = max(range(len(groups)), key=lambda i: len(groups[i]))
+        if len(groups[k]) < 2:
+            break
+        g = groups.pop(k)
+        groups[k:k] = [g[: len(g) // 2], g[len(g) // 2:]]
+    n_real = len(groups)
+    return groups + [groups[0]] * (target - n_real), n_real
+
+
 class PolicyTrainer(Configurable):
     @dataclass(kw_only=True, slots=True)
     class Config(Configurable.Config):
@@ -60,6 +93,12 @@ class PolicyTrainer(Configurable):
         self.parallel_dims = self.make_parallel_dims(config, world, ranks)
         if getattr(self.parallel_dims, "_base", None) is not None:
             self.parallel_dims.build_mesh()              # collective with the non-trainer ranks (see make_parallel_dims)
+        if world > 1 and self.device.type == "cuda":
+            # one seed for the trainer ranks, agreed inside their own group: DTensor's default start-up sync is a
+            # broadcast over the whole job, which the generator ranks never enter
+            t = torch.tensor([torch.initial_seed() % 2**62], dtype=torch.int64, device=self.device)
+            dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            dist_utils.seed_dtensor_rng(self.parallel_dims.world_mesh, int(t.item()))
         self.sd_adapter = model_spec.state_dict_adapter(model_spec.model, hf_assets_path) if model_spec.state_dict_adapter else None
         self.model = self._build_model(hf_assets_path, trainable=True)
         self.model_parts = [self.model]
@@ -166,21 +205,17 @@ class PolicyTrainer(Configurable):
         gen_lps = [episodes[i].token_log_probs for i in mine]
         my_adv = advantages[mine]
 
-        # micro-batches: greedy packing of this rank's episodes into rows of bounded length
-        groups, cur, cur_tok = [], [], 0
-        for j in range(len(mine)):
-            n = len(prompt_ids[j]) + len(gen_ids[j])
-            if cur and cur_tok + n > cfg.max_tokens_per_microbatch:
-                groups.append(cur)
-                cur, cur_tok = [], 0
-            cur.append(j)
-            cur_tok += n
-        if cur:
-            groups.append(cur)
+        # micro-batches: greedy packing of this rank's episodes into rows of bounded length. Every forward/backward of a
+        # sharded model is a collective of the data-parallel group, so all its ranks must run the SAME number of them:
+        # each rank plans the packing of every rank (all hold the full episode list) and matches the largest count.
+        lens = [[len(episodes[i].prompt_token_ids) + len(episodes[i].token_ids) for i in range(r, len(episodes), self.dp_size)]
+                for r in range(self.dp_size)]
+        groups, n_real = plan_microbatches(lens, self.dp_rank, cfg.max_tokens_per_microbatch)
         n_seqs, n_toks = len(mine), max(1, sum(len(g) for g in gen_ids))
         self.optimizers.zero_grad()
         loss_total, token_lps, agg = 0.0, [None] * len(mine), {}
         for gi, idx in enumerate(groups):
+            real = gi < n_real       # the rest repeat a micro-batch with zero weight, only to keep the collectives paired
             sel = lambda xs: [xs[j] for j in idx]  # noqa: E731
             ref_lps = None
             if self.ref_model is not None and cfg.objective != "dapo":
@@ -193,6 +228,9 @@ class PolicyTrainer(Configurable):
                 n_seqs_total=n_seqs, n_tokens_total=n_toks,
             )
             # data-parallel mean of the per-rank losses: FSDP sums gradients, so scale by 1 / dp_size
+            if not real:
+                (loss * 0.0).backward()
+                continue
             (loss / self.dp_size if self.dp_enabled else loss).backward()
             loss_total += loss.item()
             for j, t in zip(idx, lps):

@@ -24,7 +24,7 @@ from torchtitan_b200.tools.logging import logger
 from torchtitan_b200.tools.utils import device_module, device_type
 
 __all__ = [
-    "dist_sum", "dist_max", "dist_mean", "set_determinism", "init_distributed", "set_pg_timeouts",
+    "dist_sum", "dist_max", "dist_mean", "set_determinism", "seed_dtensor_rng", "init_distributed", "set_pg_timeouts",
     "clip_grad_norm_", "maybe_enable_amp", "get_train_context", "create_context_parallel_ctx",
 ]
 
@@ -83,6 +83,24 @@ def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_
     logger.debug(f"rank {rank}: seed {seed}")
     torch.manual_seed(seed)
     os.environ["PYTHONHASHSEED"] = str(seed % 2**32)
+    if world > 1 and dist.is_initialized() and torch.device(device).type == "cuda":
+        seed_dtensor_rng(parallel_dims.world_mesh, seed)
+
+
+def seed_dtensor_rng(mesh, seed: int) -> None:
+    """Create DTensor's random-number tracker for ``mesh`` with ``seed`` and WITHOUT its start-up broadcast.
+
+    The first random op on a DTensor otherwise builds the tracker with a broadcast of rank 0's generator state over the
+    default process group. When the mesh covers only part of the job (trainer ranks beside generator ranks), the other
+    ranks never enter that broadcast and it pairs up with whatever collective they issue next. Every rank of ``mesh``
+    must pass the same ``seed`` (ranks that differ along a pipeline dimension pass their own). A mesh on the CPU has no
+    tracker and needs none.
+    """
+    import torch.distributed.tensor._random as dtensor_random
+
+    if mesh is None or mesh.device_type != "cuda":
+        return
+    dtensor_random.manual_seed(seed % 2**63, mesh)
 
 
 def _flight_recorder_env(comm_config, base_folder: str) -> None:
