@@ -202,6 +202,42 @@ def test_full_and_layer_frequency_checkpointing_preserve_gradients():
         ac._apply_ac_to_transformer_block(net.layers["0"], ActivationCheckpointConfig(mode="none"))
 
 
+def test_memory_budget_mixes_block_plans_and_preserves_gradients(tmp_path):
+    """Reference: torchtitan/distributed/activation_checkpoint.py:216-230 hands the budget to the compiler's partitioner;
+    here the same knob picks a per-block plan from a ladder (full / per-op / none)."""
+    from torchtitan_b200.config import ActivationCheckpointConfig
+    from torchtitan_b200.parallel import ac
+
+    assert ac.plan_memory_budget(4, 0.0) == ["full"] * 4
+    assert ac.plan_memory_budget(4, 1.0) == ["none"] * 4
+    assert ac.plan_memory_budget(4, 0.22) == ["full", "op_every_second", "full", "op_every_second"]
+    assert ac.plan_memory_budget(8, 0.5).count("op_all") == 3           # 0.40 + 3/8 * 0.25 <= 0.5
+    shares = {n: m for n, m, _ in ac._BUDGET_LADDER}
+    prev = -1.0
+    for i in range(11):                                                   # monotone in the budget, never above it
+        pl = ac.plan_memory_budget(6, i / 10)
+        mean = sum(shares[x] for x in pl) / 6
+        assert prev <= mean <= max(i / 10, shares["full"]) + 1e-9
+        prev = mean
+    with pytest.raises(ValueError):
+        ac.plan_memory_budget(4, 1.5)
+
+    torch.manual_seed(0)
+    ref = _Net()
+    tok = torch.randint(0, 50, (2, 8))
+    ref(tok).square().mean().backward()
+    for budget in (0.0, 0.3, 0.6, 1.0):
+        net = copy.deepcopy(ref)
+        net.zero_grad()
+        ac.apply_ac(net, ActivationCheckpointConfig(mode="memory_budget", memory_budget=budget,
+                                                    visualize_memory_budget_pareto=True), base_folder=str(tmp_path))
+        net(tok).square().mean().backward()
+        for (n1, p1), (_, p2) in zip(net.named_parameters(), ref.named_parameters()):
+            assert torch.allclose(p1.grad, p2.grad, atol=1e-6), (budget, n1)
+    rows = (tmp_path / "memory_budget_pareto.csv").read_text().strip().splitlines()
+    assert rows[0] == "budget,resident_share,recompute_share" and len(rows) == 22
+
+
 # ------------------------------------------------------------------------------------------ optimizer container
 def test_optimizers_container_steps_and_round_trips_flattened_state():
     from torchtitan_b200.components.optimizer import OptimizersContainer

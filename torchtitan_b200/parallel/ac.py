@@ -1,4 +1,4 @@
-"""Activation checkpointing: ``full``, ``selective`` by layer frequency, ``selective`` per op.
+"""Activation checkpointing: ``full``, ``selective`` by layer frequency, ``selective`` per op, ``memory_budget``.
 
 Parity: torchtitan/distributed/activation_checkpoint.py:27-260. Per-op policy (:105-135): ops on
 the save list are kept, except that only every *second* matmul is kept; matmuls whose weight
@@ -187,13 +187,74 @@ def _apply_ac_to_transformer_block(module, ac_config, *, base_fqn=None, model_co
     )
 
 
+# Plans a block can take under ``memory_budget``, from cheapest in memory to cheapest in recompute: (name, share of the
+# block's no-checkpoint activation bytes that stays resident, share of the block's forward that backward runs again).
+# The shares are nominal figures for a dense pre-norm transformer block in bf16 (block input only / matmul outputs,
+# attention output and every second matmul / all matmul outputs / everything); they order the plans and set the mix, and
+# the planner needs no trace of the model.
+_BUDGET_LADDER = (("full", 0.04, 1.0), ("op_every_second", 0.40, 0.55), ("op_all", 0.65, 0.15), ("none", 1.0, 0.0))
+
+
+def plan_memory_budget(n_blocks: int, budget: float) -> list[str]:
+    """One plan name per block such that the mean resident share is the largest reachable value <= ``budget``.
+
+    The reference hands ``memory_budget`` to the partitioner of its tracing compiler, which solves a knapsack over the
+    ops of the traced graph (torchtitan/distributed/activation_checkpoint.py:216-230). Without a tracer the same knob is
+    served per block: the two neighbouring plans of the ladder around ``budget`` are mixed, the costlier-in-memory one
+    on as many blocks as the budget allows, spread evenly over depth so that pipeline stages get the same mix."""
+    if not 0.0 <= budget <= 1.0:
+        raise ValueError(f"activation_checkpoint.memory_budget must be in [0, 1], got {budget}")
+    shares = [x[1] for x in _BUDGET_LADDER]
+    if budget <= shares[0]:
+        return [_BUDGET_LADDER[0][0]] * n_blocks
+    hi = next(i for i, sh in enumerate(shares) if sh >= budget)
+    lo = hi - 1
+    n_hi = int((budget - shares[lo]) / (shares[hi] - shares[lo]) * n_blocks + 1e-9)
+    plans = [_BUDGET_LADDER[lo][0]] * n_blocks
+    for k in range(n_hi):                                   # evenly spaced positions
+        plans[int((k + 0.5) * n_blocks / n_hi)] = _BUDGET_LADDER[hi][0]
+    return plans
+
+
+def _apply_memory_budget(model, ac_config, *, op_sac_save_list=None, base_folder: str = "") -> None:
+    import copy
+
+    blocks = list(model.get_submodule("layers").named_children())
+    plans = plan_memory_budget(len(blocks), float(ac_config.memory_budget))
+
+    def variant(**kw):
+        c = copy.copy(ac_config)
+        for k, v in kw.items():
+            setattr(c, k, v)
+        return c
+
+    for (layer_id, block), plan in zip(blocks, plans):
+        if plan == "full":
+            _apply_full_ac(block, ac_config)
+        elif plan in ("op_every_second", "op_all"):
+            cfg = variant(mode="selective", selective_ac_option="op",
+                          per_op_sac_mm_policy="all" if plan == "op_all" else "every_second")
+            _apply_op_sac(block, cfg, base_fqn=f"layers.{layer_id}", op_sac_save_list=op_sac_save_list)
+    counts = {name: plans.count(name) for name, _, _ in _BUDGET_LADDER if name in plans}
+    logger.info(f"Applied memory_budget={ac_config.memory_budget} activation checkpointing: {counts}")
+    if ac_config.visualize_memory_budget_pareto and base_folder:
+        # the trade-off curve of the ladder for this depth: budget -> resident share, recomputed share of the forward
+        os.makedirs(base_folder, exist_ok=True)
+        path = os.path.join(base_folder, "memory_budget_pareto.csv")
+        share = {n: (m, r) for n, m, r in _BUDGET_LADDER}
+        with open(path, "w") as f:
+            f.write("budget,resident_share,recompute_share\n")
+            for i in range(21):
+                pl = plan_memory_budget(len(blocks), i / 20)
+                f.write(f"{i / 20:.2f},{sum(share[x][0] for x in pl) / len(pl):.4f},{sum(share[x][1] for x in pl) / len(pl):.4f}\n")
+        logger.info(f"memory-budget trade-off table written to {path}")
+
+
 def apply_ac(model: nn.Module, ac_config, *, model_compile_enabled: bool = False, op_sac_save_list=None,
              base_folder: str = "") -> None:
     if ac_config.mode == "memory_budget":
-        raise NotImplementedError(
-            "activation_checkpoint.mode=memory_budget relies on a graph partitioner; this framework has no "
-            "tracing compiler. Use 'selective' (op or layer frequency) or 'full'."
-        )
+        _apply_memory_budget(model, ac_config, op_sac_save_list=op_sac_save_list, base_folder=base_folder)
+        return
     layers = model.get_submodule("layers")
     for layer_id, block in layers.named_children():
         _apply_ac_to_transformer_block(
