@@ -87,6 +87,9 @@ class InnerAttention(Module):
             doc_ids = masks.doc_ids
             window = masks.window if masks.window is not None else window
             if masks.block is not None:
+                if self.ring is not None:
+                    raise NotImplementedError("fixed-block attention masks are built from local positions; "
+                                              "context parallel serves document, window and sink masks")
                 blocks = fixed_block_ids(q.shape[0], q.shape[1], masks.block, q.device)
                 # both constraints: same document AND same fixed block <=> equal combined ids
                 doc_ids = blocks if doc_ids is None else doc_ids * (q.shape[1] // masks.block + 1) + blocks

@@ -73,7 +73,8 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
     """Softmax attention on ``[B,S,H,Dh]`` tensors with grouped KV heads.
 
     ``window``: sliding window size (a query sees keys in (i-window, i]).
-    ``doc_ids``: int tensor [B,S]; tokens attend only inside their own document.
+    ``doc_ids``: int tensor [B,Sk], one id per key; tokens attend only inside their own document. With fewer queries
+    than keys the queries are the LAST ``Sq`` positions (the same bottom-right alignment as the causal mask).
     ``sinks``: per-head learned logit [H] joining the softmax denominator only.
     """
     B, S, H, D = q.shape
@@ -94,7 +95,7 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
     outs, lses = [], []
     for q0 in range(0, S, chunk):
         q1 = min(S, q0 + chunk)
-        args = (q[:, q0:q1], k, v, sinks, doc_ids[:, q0:q1] if doc_ids is not None else None, doc_ids)
+        args = (q[:, q0:q1], k, v, sinks, doc_ids[:, Sk - S + q0 : Sk - S + q1] if doc_ids is not None else None, doc_ids)
         fn = functools.partial(_masked_attention_rows, q0=q0 + (Sk - S), causal=causal, scale=scale, window=window)
         if chunk < S and torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, sinks)):
             from torch.utils.checkpoint import checkpoint

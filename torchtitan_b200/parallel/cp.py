@@ -12,7 +12,8 @@ The attention itself (``RingAttention``) supports both rotate methods of
 
 * ``allgather``: K and V shards are gathered once; each local query chunk then attends its whole
   causal prefix in a single kernel call (the kernel handles ``Sq != Sk`` with a causal offset), so no
-  partial results have to be merged. Backward reduce-scatters dK/dV to their owners.
+  partial results have to be merged. Backward reduce-scatters dK/dV to their owners. Document masks, sliding windows
+  and attention sinks are served by this method (the per-token document ids are gathered alongside).
 * ``alltoall``: K/V blocks travel around the ring in ``cp-1`` point-to-point steps; partial outputs are
   merged with their log-sum-exp in fp32; backward runs the ring again with the final (merged)
   statistics, dK/dV travelling with their block.
@@ -229,24 +230,46 @@ class RingAttention:
         assert rotate_method in ("allgather", "alltoall")
         self.method, self.balanced = rotate_method, load_balancer is not None
 
+    def _gather_ids(self, ids):
+        """Per-token ids of the whole sequence in global order, from every rank's local shard ``[B, S_local]``."""
+        W = self.cp
+        parts = [torch.empty_like(ids) for _ in range(W)]
+        dist.all_gather(parts, ids.contiguous(), group=self.group)
+        if not self.balanced:
+            return torch.cat(parts, dim=1)
+        c = ids.shape[1] // 2
+        chunks = [None] * (2 * W)
+        for j, p in enumerate(parts):
+            chunks[j], chunks[2 * W - 1 - j] = p[:, :c], p[:, c:]
+        return torch.cat(chunks, dim=1)
+
     def __call__(self, q, k, v, *, scale=None, doc_ids=None, window=None, sinks=None):
-        if doc_ids is not None or window is not None or sinks is not None:
-            raise NotImplementedError("context parallel supports plain causal attention (no document / window / sink masks)")
+        """``doc_ids`` are this rank's shard of the per-token document ids. Masks (documents, sliding window, sinks) need
+        every query to see its whole key set in one softmax, which the ``allgather`` method gives; the ring method
+        merges partial softmaxes and serves plain causal attention only."""
+        masked = doc_ids is not None or window is not None or sinks is not None
+        if masked and self.method == "alltoall":
+            raise NotImplementedError("context parallel with document / window / sink masks needs "
+                                      "parallelism.context_parallel_rotate_method='allgather'")
         scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.shape[-1])
         if self.method == "alltoall":
             return _RingPass.apply(q, k, v, self.group, scale, self.balanced)
         K = _AllGatherKV.apply(k, self.group, self.balanced)
         V = _AllGatherKV.apply(v, self.group, self.balanced)
+        docs = self._gather_ids(doc_ids) if doc_ids is not None else None
         W, r = self.cp, self.rank
-        if not self.balanced:
-            c = q.shape[1]
-            return ops.attention(q, K[:, : (r + 1) * c], V[:, : (r + 1) * c], causal=True, scale=scale)
-        c = q.shape[1] // 2
+        c = q.shape[1] if not self.balanced else q.shape[1] // 2
+        owned = (r,) if not self.balanced else (r, 2 * W - 1 - r)
         outs = []
-        for qi, a in enumerate((r, 2 * W - 1 - r)):
+        for qi, a in enumerate(owned):
             end = (a + 1) * c
-            outs.append(ops.attention(q[:, qi * c : (qi + 1) * c], K[:, :end], V[:, :end], causal=True, scale=scale))
-        return torch.cat(outs, dim=1)
+            # a sliding window never looks further back than window - 1 keys before the chunk's first query
+            start = max(0, a * c - (window - 1)) if window is not None else 0
+            kw = {}
+            if masked:
+                kw = dict(window=window, sinks=sinks, doc_ids=docs[:, start:end] if docs is not None else None)
+            outs.append(ops.attention(q[:, qi * c : (qi + 1) * c], K[:, start:end], V[:, start:end], causal=True, scale=scale, **kw))
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
 
 
 def apply_cp_to_attention_module(attention_modules, cp_mesh, attn_backend: str = "sdpa", *, rotate_method: str = "allgather",
