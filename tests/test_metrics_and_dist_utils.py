@@ -140,3 +140,22 @@ def test_seed_dtensor_rng_skips_cpu_meshes_and_forwards_cuda_ones(monkeypatch):
     assert seen == []
     dist_utils.seed_dtensor_rng(types.SimpleNamespace(device_type="cuda"), 2**63 + 5)
     assert seen == [(5, "cuda")]
+
+
+def test_trainer_raises_when_a_kernel_reports_an_expired_wait(monkeypatch):
+    import types
+
+    import torch
+
+    from torchtitan_b200.ops import native
+    from torchtitan_b200.trainer import Trainer
+
+    fake = types.SimpleNamespace(device=torch.device("cuda"), step=7)
+    monkeypatch.setattr(native, "available", lambda: True)
+    monkeypatch.setattr(native, "kernel_errors", lambda: {})
+    Trainer._raise_on_kernel_errors(fake)                         # nothing reported: no error
+    monkeypatch.setattr(native, "kernel_errors", lambda: {"gemm": 4})
+    with pytest.raises(RuntimeError, match="step 7.*gemm"):
+        Trainer._raise_on_kernel_errors(fake)
+    fake.device = torch.device("cpu")
+    Trainer._raise_on_kernel_errors(fake)                         # CPU runs have no kernels to ask

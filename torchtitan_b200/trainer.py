@@ -414,6 +414,22 @@ class Trainer(Stateful, Configurable):
             global_ntokens = self.ntokens_seen
         extra = {"n_tokens_seen": global_ntokens, "lr": lr}
         self.metrics_processor.log(self.step, global_avg_loss, global_max_loss, float(grad_norm), extra_metrics=extra)
+        self._raise_on_kernel_errors()
+
+    def _raise_on_kernel_errors(self) -> None:
+        """The CUDA kernels of this framework bound every wait (peer flags, mbarriers, arrival counters); one that gives
+        up sets a bit in its family's error word and returns, so the step finishes with wrong numbers instead of
+        hanging. The words are read here, at log steps (the host has just synchronised for the loss)."""
+        if self.device.type != "cuda":
+            return
+        from torchtitan_b200.ops import native
+
+        if not native.available():
+            return
+        errs = native.kernel_errors()
+        if errs:
+            raise RuntimeError(f"step {self.step}: a kernel gave up on a bounded wait (family -> error word): {errs}. "
+                               "The results of the steps since the last log are not trustworthy.")
 
     # ------------------------------------------------------------------ loop
     @record
