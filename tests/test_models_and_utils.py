@@ -5,6 +5,8 @@ test_state_dict_adapter-style checks in scripts/checkpoint_conversion, test_util
 import dataclasses
 import gc
 
+import os
+
 import pytest
 import torch
 
@@ -188,6 +190,14 @@ def test_profiler_writes_traces_on_schedule_and_is_off_by_default(tmp_path):
             prof.step()
     traces = sorted(glob.glob(str(tmp_path / "profile_traces" / "iteration_*" / "leaf" / "rank0_trace.json")))
     assert len(traces) == 2, traces                           # one trace per period of profile_freq steps
+    # repeat = 1 records a single cycle, skip_first delays it
+    cfg = ProfilingConfig(enable_profiling=True, profile_freq=3, profiler_warmup=1, profiler_active=1, profiler_repeat=1,
+                          profiler_skip_first=2, save_traces_folder="once")
+    with maybe_enable_profiling(cfg, global_step=0, base_folder=str(tmp_path)) as prof:
+        for _ in range(12):
+            torch.randn(64, 64) @ torch.randn(64, 64)
+            prof.step()
+    assert sorted(os.listdir(tmp_path / "once")) == ["iteration_5"]
     with pytest.raises(AssertionError):
         with maybe_enable_profiling(ProfilingConfig(enable_profiling=True, profile_freq=2, profiler_warmup=3),
                                     base_folder=str(tmp_path)):

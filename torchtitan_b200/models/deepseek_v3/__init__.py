@@ -12,7 +12,7 @@ from .model import Attention, DeepSeekV3Model, DeepSeekV3TransformerBlock
 from .parallelize import parallelize_deepseekv3
 from .state_dict_adapter import DeepSeekV3StateDictAdapter
 
-__all__ = ["DeepSeekV3Model", "deepseek_v3_configs", "model_registry", "parallelize_deepseekv3", "Attention"]
+__all__ = ["DeepSeekV3Model", "deepseek_v3_configs", "deepseekv3_configs", "model_registry", "parallelize_deepseekv3", "Attention"]
 
 
 def _rope() -> RoPE.Config:
@@ -58,6 +58,7 @@ deepseek_v3_configs = {
                     moe=_moe(hidden_dim=2048, num_experts=256, num_shared_experts=1, top_k=8, num_expert_groups=8,
                              num_limited_groups=4, score_func="sigmoid", route_norm=True, route_scale=2.5)),
 }
+deepseekv3_configs = deepseek_v3_configs      # the spelling of torchtitan/models/deepseek_v3/__init__.py
 
 
 def model_registry(flavor: str) -> ModelSpec:

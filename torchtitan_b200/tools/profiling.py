@@ -28,6 +28,12 @@ class ProfilingConfig:
     profile_freq: int = 10
     profiler_active: int = 1
     profiler_warmup: int = 3
+    profiler_repeat: int | None = None
+    """How many wait/warm-up/active cycles to record (unset: every cycle until the run ends)."""
+    profiler_skip_first: int | None = None
+    """Steps to ignore before the first cycle starts."""
+    profiler_skip_first_wait: int | None = None
+    """Non-zero: the first cycle starts with its warm-up instead of its wait."""
     enable_memory_snapshot: bool = False
     save_memory_snapshot_folder: str = "memory_snapshot"
     experimental_cuda_device_timestamps: bool = False
@@ -56,6 +62,8 @@ def maybe_enable_profiling(config: ProfilingConfig, *, global_step: int = 0, bas
 
     wait = freq - (active + warmup)
     assert wait >= 0, "profile_freq must be >= profiler_active + profiler_warmup"
+    cycle = {k: v for k, v in (("repeat", config.profiler_repeat), ("skip_first", config.profiler_skip_first),
+                                ("skip_first_wait", config.profiler_skip_first_wait)) if v is not None}
     acts = [torch.profiler.ProfilerActivity.CPU]
     if torch.cuda.is_available():
         acts.append(torch.profiler.ProfilerActivity.CUDA)
@@ -63,7 +71,7 @@ def maybe_enable_profiling(config: ProfilingConfig, *, global_step: int = 0, bas
     os.makedirs(trace_dir, exist_ok=True)
     with torch.profiler.profile(
         activities=acts,
-        schedule=torch.profiler.schedule(wait=wait, warmup=warmup, active=active),
+        schedule=torch.profiler.schedule(wait=wait, warmup=warmup, active=active, **cycle),
         on_trace_ready=on_ready,
         record_shapes=True,
     ) as prof:
