@@ -29,6 +29,7 @@ How it is built differs:
 
 from __future__ import annotations
 
+import functools
 import math
 from dataclasses import dataclass, field
 from typing import Callable
@@ -537,7 +538,9 @@ class FSDPUnit:
             outs = _UnitGather.apply(self, self._anchor)
         else:
             outs = tuple(p.unsharded for p in self.params)
-        self._fwd_params = outs  # the same tensor objects are re-bound for recompute in backward
+        # the same tensor objects are re-bound for recompute in backward; with several forwards in flight before the
+        # first backward (pipeline micro-batches) each backward needs ITS forward's tensors, so the output hooks carry them
+        self._fwd_params = outs
         if self._slots:
             for o, slot in zip(outs, self._slots):
                 if slot is not None:
@@ -551,18 +554,20 @@ class FSDPUnit:
         self._forward_active = False
         self._bind_sharded()
         if self._needs_grad():
-            self._hook_outputs(output)
+            self._hook_outputs(output, self._fwd_params)
         if self.reshard_after_forward:
             self.reshard()
         if self.mp.output_dtype is not None and torch.is_tensor(output):
             output = output.to(self.mp.output_dtype)
         return output
 
-    def _hook_outputs(self, output):
+    def _hook_outputs(self, output, fwd_params):
+        hook = functools.partial(self._pre_backward, fwd_params)
+
         def visit(o):
             if torch.is_tensor(o):
                 if o.requires_grad:
-                    o.register_hook(self._pre_backward)
+                    o.register_hook(hook)
             elif isinstance(o, (list, tuple)):
                 for x in o:
                     visit(x)
@@ -572,7 +577,7 @@ class FSDPUnit:
 
         visit(output)
 
-    def _pre_backward(self, grad):
+    def _pre_backward(self, fwd_params, grad):
         if not self._in_backward:
             self._in_backward = True
             first = next((p for p in self.params if p.param.requires_grad), None)
@@ -581,7 +586,7 @@ class FSDPUnit:
             self.unshard()
             if self.prev is not None and self.prev.reshard_after_forward and not self.prev._in_backward:
                 self.prev.unshard(async_op=True)
-            self._bind(self._fwd_params if self._fwd_params is not None else tuple(p.unsharded for p in self.params))
+            self._bind(fwd_params if fwd_params is not None else tuple(p.unsharded for p in self.params))
             _BackwardEnd.register(self)
         return grad
 
