@@ -66,5 +66,19 @@ def main() -> None:
                    "add_bos_token": True, "add_eos_token": False, "model_max_length": 131072}, f, indent=1)
 
 
+def write_custom_schedule() -> None:
+    """``custom_schedule.csv``: one row per pipeline rank, actions ``<stage><F|B><micro-batch>``, for 2 ranks with 2 looped
+    stages each and 8 micro-batches (what ``--parallelism.pipeline_parallel_schedule_csv`` reads): the interleaved 1F1B
+    order spelled out action by action."""
+    from torchtitan_b200.parallel.pp import build_actions, validate_actions
+
+    rows = build_actions("Interleaved1F1B", 2, 4, 8, "loop")
+    validate_actions(rows, 2, 4, 8, "loop")
+    with open(os.path.join(HERE, "custom_schedule.csv"), "w") as f:
+        for acts in rows:
+            f.write(",".join(f"{a.stage}{a.kind}{a.mb}" for a in acts) + "\n")
+
+
 if __name__ == "__main__":
     main()
+    write_custom_schedule()

@@ -50,7 +50,8 @@ def build_features_test_list() -> list[T]:
            [f"{PP} 4", f"{SCHED} Interleaved1F1B", "--parallelism.pipeline_parallel_layers_per_stage 1"]],
           "PP looped 1F1B", "pp_looped_1f1b", ngpu=4),
         T([[f"{PP} 2", f"{SCHED} PipelineScheduleMulti",
-            "--parallelism.pipeline_parallel_schedule_csv ./tests/assets/custom_schedule.csv"]],
+            "--parallelism.pipeline_parallel_schedule_csv ./tests/assets/custom_schedule.csv",
+            "--training.local_batch_size 8"]],        # the file is written for 8 micro-batches
           "PP with a schedule read from a CSV file", "pp_custom_csv", ngpu=2),
         T([["--optimizer.name AdamW", "--optimizer.implementation foreach"]], "Foreach optimizer", "optimizer_foreach", ngpu=2),
         T([[f"{SHARD} 1", f"{REPL} 4"]], "DDP", "ddp", ngpu=4),

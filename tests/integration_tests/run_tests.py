@@ -38,7 +38,19 @@ def command(case: OverrideDefinitions, i: int, dump: str, extra: list[str]) -> t
     """Environment additions and argv of override set ``i``; ``{dump}`` in a flag expands to the case's dump folder."""
     env = {"NGPU": str(case.ngpu), "MODULE": case.module, "CONFIG": case.config, "LOG_RANK": "0"}
     flags = [f.replace("{dump}", dump) for f in case.flags(i)]
-    return env, [os.path.join(_REPO, "run_train.sh"), "--dump_folder", dump, *flags, *extra]
+    return env, [os.path.join(_REPO, "run_train.sh"), "--dump_folder", dump, *flags, *_without(extra, flags)]
+
+
+def _without(extra: list[str], flags: list[str]) -> list[str]:
+    """``extra`` minus the options the case sets itself (the case wins): an option is a ``--name`` and the values after it."""
+    mine = {f.split("=")[0] for f in flags if f.startswith("--")}
+    out, keep = [], True
+    for tok in extra:
+        if tok.startswith("--"):
+            keep = tok.split("=")[0] not in mine
+        if keep:
+            out.append(tok)
+    return out
 
 
 def validate(case: OverrideDefinitions, extra: list[str] = ()) -> None:

@@ -32,6 +32,9 @@ def test_selection_and_command_line():
     assert env["NGPU"] == "2" and env["MODULE"] == "llama3" and argv[0].endswith("run_train.sh")
     assert argv[1:] == ["--dump_folder", "/out/n", "--checkpoint.enable", "--checkpoint.initial_load_path", "/out/n/hf/step-10",
                         "--training.steps", "2"]
+    # an option the case sets itself is not overridden by the extras
+    _, argv = run_tests.command(OverrideDefinitions([["--training.steps 20"]], "d", "n"), 0, "/o", ["--training.steps", "2", "--x", "1"])
+    assert argv[3:] == ["--training.steps", "20", "--x", "1"]
     with pytest.raises(SystemExit):
         run_tests.select("no_such_suite", "all", 8, False)
     with pytest.raises(AssertionError):
