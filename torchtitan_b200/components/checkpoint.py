@@ -62,9 +62,17 @@ class ModelWrapper(Stateful):
         self.cache_state_dict = self._get_state_dict()
 
     def _get_state_dict(self) -> dict[str, Any]:
+        """Tensor- and expert-parallel shards appear with their full logical shape (``parallel/global_view.py``): the
+        checkpoint does not depend on the layout that wrote it."""
+        from torchtitan_b200.parallel.global_view import global_view, is_outer_sharded
+
         out: dict[str, Any] = {}
         for part in self.model:
-            out.update(part.state_dict())
+            sd = part.state_dict()
+            for name, p in part.named_parameters(remove_duplicate=False):
+                if name in sd and is_outer_sharded(p):
+                    sd[name] = global_view(p)
+            out.update(sd)
         return out
 
     def state_dict(self) -> dict[str, Any]:
@@ -72,10 +80,22 @@ class ModelWrapper(Stateful):
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         from torchtitan_b200.parallel.fsdp import fsdp_units
+        from torchtitan_b200.parallel.global_view import is_outer_sharded, local_of
 
         for part in self.model:
             own = part.state_dict()
             sub = {k: v for k, v in state_dict.items() if k in own}
+            with torch.no_grad():
+                for name, p in part.named_parameters(remove_duplicate=False):
+                    if name in sub and is_outer_sharded(p):
+                        # a full-shape view: its local piece has this rank's layout (a distributed-checkpoint load has
+                        # usually written it in place already, then this copy is a no-op)
+                        src, dst = local_of(sub.pop(name)), local_of(p)
+                        if tuple(src.shape) != tuple(dst.shape):
+                            raise ValueError(f"{name}: cannot load a tensor of local shape {tuple(src.shape)} into a "
+                                             f"shard of shape {tuple(dst.shape)}")
+                        if src.data_ptr() != dst.data_ptr():
+                            dst.copy_(src)
             part.load_state_dict(sub, strict=False)
             for u in fsdp_units(part):
                 u.mark_params_updated()

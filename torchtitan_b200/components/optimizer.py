@@ -234,11 +234,42 @@ class OptimizersContainer(Optimizer, Stateful, Configurable):
         for opt in self.optimizers:
             opt.zero_grad(*args, **kwargs)
 
+    def _outer_sharded_params(self) -> dict:
+        from torchtitan_b200.parallel.global_view import is_outer_sharded
+
+        return {n: p for m in self.model_parts for n, p in m.named_parameters(remove_duplicate=False) if is_outer_sharded(p)}
+
     def state_dict(self) -> dict[str, Any]:
+        """Flattened (``state.<fqn>.<name>``, ``param_groups.<fqn>.<option>``). States of tensor- / expert-parallel shards
+        appear with the parameter's full logical shape, like the parameters themselves in the model state dict."""
+        from torchtitan_b200.parallel.global_view import global_view
+
         fn = functools.partial(get_optimizer_state_dict, options=StateDictOptions(flatten_optimizer_state_dict=True))
-        return {k: v for sd in map(fn, self.model_parts, self.optimizers) for k, v in sd.items()}
+        out = {k: v for sd in map(fn, self.model_parts, self.optimizers) for k, v in sd.items()}
+        sharded = self._outer_sharded_params()
+        if sharded:
+            for k, v in out.items():
+                if k.startswith("state.") and torch.is_tensor(v):
+                    fqn = k[len("state."):].rsplit(".", 1)[0]
+                    if fqn in sharded:
+                        out[k] = global_view(sharded[fqn], v)
+        return out
 
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        from torchtitan_b200.parallel.global_view import local_of
+
+        sharded = self._outer_sharded_params()
+        if sharded:
+            # back from full-shape views to tensors laid out like the parameter on this rank
+            state_dict = dict(state_dict)
+            for k, v in state_dict.items():
+                if k.startswith("state.") and torch.is_tensor(v):
+                    fqn = k[len("state."):].rsplit(".", 1)[0]
+                    p = sharded.get(fqn)
+                    if p is not None and v.dim() > 0:
+                        local = local_of(v)
+                        state_dict[k] = (DTensor.from_local(local, p.device_mesh, p.placements, run_check=False, shape=p.shape,
+                                                            stride=p.stride()) if isinstance(p, DTensor) else local)
         fn = functools.partial(
             set_optimizer_state_dict, optim_state_dict=state_dict,
             options=StateDictOptions(flatten_optimizer_state_dict=True),

@@ -168,6 +168,13 @@ def _tag(p, spec) -> None:
     p._tp_placement = spec["placement"]
     p._tp_group, p._tp_mesh = spec["group"], spec["mesh"]
     p._tp_full_shape = spec.get("full_shape")
+    # every sharding applied to the full tensor, outermost first: (dim, mesh) -- what a checkpoint view needs
+    chain, s = [], spec
+    while s is not None:
+        if s["placement"][0] == "shard":
+            chain.append((s["placement"][1], s["mesh"]))
+        s = s.get("outer")
+    p._tp_chain = tuple(reversed(chain))
     if spec["placement"][0] == "shard":
         # its squared norm is a partial sum over the TP group (over several groups for 2-D expert shards)
         p._extra_norm_groups = tuple(spec.get("norm_groups") or (spec["group"],))
