@@ -30,7 +30,7 @@ def build_model_tests_list() -> list[T]:
         T([[]], "DeepSeek V3 with document masks", "deepseek_v3_flex", ngpu=2, module="deepseek_v3",
           config="deepseek_v3_debugmodel_flex_attn"),
         T([[f"{SHARD} 2", f"{TP} 2"]], "Qwen3 FSDP + TP", "qwen3_fsdp+tp", ngpu=4, **qw),
-        T([[f"{PP} 2", f"{SHARD} 2"]], "Qwen3 PP + FSDP", "qwen3_pp+fsdp", ngpu=4, **qw),
+        T([[f"{SHARD} 2", f"{CP} 2"]], "Qwen3 FSDP + CP", "qwen3_fsdp+cp", ngpu=4, **qw),   # tied weights: no PP for this flavor
         T([[f"{SHARD} 4", f"{EP} 2"]], "Qwen3 MoE FSDP + EP", "qwen3_moe_fsdp+ep", ngpu=4, **qm),
         T([[f"{SHARD} 2", f"{TP} 2", f"{EP} 2", f"{ETP} 1"]], "Qwen3 MoE FSDP + TP + EP", "qwen3_moe_fsdp+tp+ep", ngpu=4, **qm),
         T([[f"{SHARD} 2", f"{EP} 2", "--parallelism.expert_parallel_comm_backend deepep"]],

@@ -87,11 +87,12 @@ def _model_worker(rank, world):
     ref_norm = torch.nn.utils.get_total_norm([p.grad for p in ref.parameters() if p.grad is not None])
     norm = dist_utils.clip_grad_norm_(list(model.parameters()), 1e9, ep_enabled=True)
     return {"loss": tot.item(), "ref": ref_loss.item(), "norm": float(norm) if norm is not None else -1.0,
-            "ref_norm": float(ref_norm)}
+            "ref_norm": float(ref_norm), "view_diff": _checkpoint_view_diff(model, ref)}
 
 
 def test_ep2_fsdp_model_loss_and_grad_norm(tmp_path):
     for o in run_ranks(_model_worker, 2, tmp_path=tmp_path):
+        assert o["view_diff"] == 0.0, o
         assert abs(o["loss"] - o["ref"]) < 1e-5, o
         assert abs(o["norm"] - o["ref_norm"]) < 1e-4 * max(1.0, o["ref_norm"]), o
 
@@ -192,10 +193,25 @@ def _etp_model_worker(rank, world):
     dist.all_reduce(tot, group=pd.get_mesh("fsdp").get_group())
     ref_norm = torch.nn.utils.get_total_norm([p.grad for p in ref.parameters() if p.grad is not None])
     norm = dist_utils.clip_grad_norm_(list(model.parameters()), 1e9, ep_enabled=True)
-    return {"loss": tot.item(), "ref": ref_loss.item(), "norm": float(norm), "ref_norm": float(ref_norm)}
+    return {"loss": tot.item(), "ref": ref_loss.item(), "norm": float(norm), "ref_norm": float(ref_norm),
+            "view_diff": _checkpoint_view_diff(model, ref)}
+
+
+def _checkpoint_view_diff(model, ref) -> float:
+    """What a checkpoint sees (full logical tensors rebuilt from this layout's shards) against the unsharded model."""
+    from torchtitan_b200.components.checkpoint import ModelWrapper
+
+    want = ref.state_dict()
+    worst = 0.0
+    for k, v in ModelWrapper(model).state_dict().items():
+        assert tuple(v.shape) == tuple(want[k].shape), (k, tuple(v.shape), tuple(want[k].shape))
+        got = v.full_tensor() if hasattr(v, "full_tensor") else v
+        worst = max(worst, (got.float() - want[k].float()).abs().max().item())
+    return worst
 
 
 def test_etp_model_loss_and_grad_norm(tmp_path):
     for o in run_ranks(_etp_model_worker, 4, tmp_path=tmp_path):
+        assert o["view_diff"] == 0.0, o                    # tp x ep x etp x fsdp shards reassemble to the full tensors
         assert abs(o["loss"] - o["ref"]) < 2e-5, o
         assert abs(o["norm"] - o["ref_norm"]) < 1e-4 * max(1.0, o["ref_norm"]), o
