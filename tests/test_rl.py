@@ -146,7 +146,7 @@ def test_colocated_grpo_two_steps(tmp_path):
     assert torch.equal(rl.generator.model.output.weight, rl.trainer.model.output.weight.to(w0.dtype))
 
 
-def _disagg_worker(rank, world, ntrain=1):
+def _disagg_worker(rank, world, ntrain=1, tp=1):
     import torch.distributed as dist
 
     dist.init_process_group("gloo")
@@ -162,7 +162,8 @@ def _disagg_worker(rank, world, ntrain=1):
     cfg.generator.seed = rank
     cfg.trainer.training.dtype = "float32"
     cfg.async_mode = True
-    cfg.trainer.parallelism.data_parallel_shard_degree = ntrain
+    cfg.trainer.parallelism.data_parallel_shard_degree = ntrain // tp
+    cfg.trainer.parallelism.tensor_parallel_degree = tp
     cfg.hf_assets_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "assets", "tokenizer")
     rl = RLTrainer(cfg)
     rl.setup(device="cpu")
@@ -226,6 +227,74 @@ def test_disaggregated_fsdp_trainer_subgroup(tmp_path):
     assert [r["is_trainer"] for r in res] == [True, True, False]
     assert all(r["steps"] == 2 and r["version"] == 2 for r in res)
     assert torch.equal(res[0]["w"], res[1]["w"]) and torch.equal(res[2]["w"], res[0]["w"])
+
+
+def test_disaggregated_tensor_parallel_trainer(tmp_path):
+    """2 tensor-parallel trainer ranks + 1 generator: the generator receives the FULL weights, reassembled from the shards
+    (the layout of the reference's default RL configurations: trainer TP 2)."""
+    from dist_utils import run_ranks
+
+    res = run_ranks(_disagg_worker, 3, 2, 2, tmp_path=tmp_path)
+    assert [r["is_trainer"] for r in res] == [True, True, False]
+    assert all(r["steps"] == 2 and r["version"] == 2 for r in res)
+    assert res[2]["w"].shape == res[0]["w"].shape and torch.equal(res[2]["w"], res[0]["w"]) and torch.equal(res[0]["w"], res[1]["w"])
+
+
+def _policy_step_worker(rank, world, tp):
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("gloo")
+    from torchtitan_b200.experiments.rl.trainer import PolicyTrainer
+    from torchtitan_b200.experiments.rl.types import Episode
+    from torchtitan_b200.experiments.rl.weight_sync import full_tensor
+
+    torch.manual_seed(0)
+    cfg = PolicyTrainer.Config(objective="grpo")
+    cfg.training.dtype = "float32"
+    cfg.training.max_norm = 1e9
+    cfg.optimizer.lr = 1e-3
+    cfg.parallelism.tensor_parallel_degree = tp
+    cfg.parallelism.data_parallel_shard_degree = world // tp
+    tr = PolicyTrainer(cfg, model_spec=_debug_spec(), device="cpu")
+    # identical starting weights on every layout: take them from a seeded single-process model
+    torch.manual_seed(11)
+    src = _debug_spec().model.build()
+    src.init_weights()
+    from torchtitan_b200.components.checkpoint import ModelWrapper
+
+    for model in (tr.model, tr.ref_model):
+        sd = ModelWrapper(model).state_dict()
+        with torch.no_grad():
+            for k, v in sd.items():
+                if hasattr(v, "device_mesh"):
+                    from torch.distributed.tensor import distribute_tensor
+
+                    v._local_tensor.copy_(distribute_tensor(src.state_dict()[k], v.device_mesh, v.placements)._local_tensor)
+                else:
+                    v.copy_(src.state_dict()[k])
+        from torchtitan_b200.parallel import fsdp
+
+        for u in fsdp.fsdp_units(model):
+            u.mark_params_updated()
+    g = torch.Generator().manual_seed(1)
+    eps = []
+    for i in range(4):
+        p = torch.randint(1, 2000, (6,), generator=g).tolist()
+        t = torch.randint(1, 2000, (7,), generator=g).tolist()
+        eps.append(Episode(0, p, "", t, [-7.0] * len(t), reward=float(i % 2), group_id=str(i // 2), advantage=float(i) - 1.5))
+    m = tr.step(eps)
+    return {"loss": m["loss"], "grad_norm": m["grad_norm"], "w": full_tensor(tr.model.layers["0"].attention.wq.weight).clone()}
+
+
+def test_tensor_parallel_policy_step_matches_single_process(tmp_path):
+    from dist_utils import run_ranks
+
+    one = _policy_step_worker(0, 1, 1)
+    for o in run_ranks(_policy_step_worker, 2, 2, tmp_path=tmp_path):
+        assert abs(o["loss"] - one["loss"]) < 1e-5, (o["loss"], one["loss"])
+        assert abs(o["grad_norm"] - one["grad_norm"]) < 1e-4 * max(1.0, one["grad_norm"])
+        assert torch.allclose(o["w"], one["w"], atol=1e-6)
 
 
 def test_plan_microbatches_gives_every_rank_the_same_count():

@@ -146,8 +146,13 @@ class PolicyTrainer(Configurable):
         pd = self.parallel_dims
         managed = pd.world_size > 1 or self.device.type == "cuda"   # one GPU: bf16 compute over fp32 master shards
         if managed:
+            # the policy loss reads per-token log-probabilities of arbitrary labels: it needs the whole vocabulary on
+            # every rank, so the output projection gathers its tensor-parallel shards (no loss parallel)
+            import dataclasses
+
+            par = dataclasses.replace(cfg.parallelism, disable_loss_parallel=True) if pd.tp_enabled else cfg.parallelism
             model = self.model_spec.parallelize_fn(
-                model, parallel_dims=pd, training=cfg.training, model_converters=None, parallelism=cfg.parallelism,
+                model, parallel_dims=pd, training=cfg.training, model_converters=None, parallelism=par,
                 compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="",
             )
         model.to_empty(device=self.device)
@@ -193,7 +198,8 @@ class PolicyTrainer(Configurable):
     # ---- endpoints ----------------------------------------------------------------------------------------
     def get_weights(self) -> dict:
         """Full (unsharded) tensors keyed like the model's state dict."""
-        return {k: full_tensor(v) for k, v in self.model.state_dict().items() if torch.is_tensor(v)}
+        params = dict(self.model.named_parameters(remove_duplicate=False))   # the parameter objects carry the sharding tags
+        return {k: full_tensor(params.get(k, v)) for k, v in self.model.state_dict().items() if torch.is_tensor(v)}
 
     def step(self, episodes: list[Episode]) -> dict:
         cfg = self.config

@@ -22,16 +22,13 @@ import torch.nn as nn
 
 
 def full_tensor(p: torch.Tensor) -> torch.Tensor:
-    """The unsharded value of a (possibly FSDP- or tensor-parallel-sharded) parameter."""
-    spec = getattr(p, "_tp_spec", None)
-    t = p.full_tensor() if hasattr(p, "full_tensor") else p
-    t = t.detach()
-    if spec is not None and spec["placement"][0] == "shard":
-        group, dim = spec["group"], spec["placement"][1]
-        parts = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
-        dist.all_gather(parts, t.contiguous(), group=group)
-        t = torch.cat(parts, dim=dim)
-    return t
+    """The unsharded value of a (possibly FSDP-, tensor- or expert-parallel-sharded) parameter: a collective of every
+    group the parameter is sharded over."""
+    from torchtitan_b200.parallel.global_view import global_view
+
+    v = global_view(p)
+    t = v.full_tensor() if hasattr(v, "full_tensor") else v
+    return t.detach()
 
 
 def build_bare_model(model_spec, dtype_name: str, device) -> nn.Module:
