@@ -72,9 +72,16 @@ def main(argv=None) -> dict:
     if a.checkpoint:
         import torch.distributed.checkpoint as dcp
 
-        sd = model.state_dict()
+        from torchtitan_b200.components.checkpoint import ModelWrapper
+        from torchtitan_b200.parallel.tp import finalize_tp
+
+        if world > 1:
+            finalize_tp(model)                       # re-attach the sharding tags that to_empty() dropped
+        wrapper = ModelWrapper(model)                # tensor-parallel shards appear with their full shape, as saved
+        sd = wrapper.state_dict()
         t0 = time.monotonic()
         dcp.load(sd, checkpoint_id=a.checkpoint)
+        wrapper.load_state_dict(sd)
         logger.info(f"Finished loading checkpoint in {time.monotonic() - t0:.2f} seconds.")
     ids = torch.tensor(tokenizer.encode(a.prompt, add_bos=True, add_eos=False), dtype=torch.long, device=device)
     ids = ids.view(1, -1).repeat(a.batch_size, 1)
