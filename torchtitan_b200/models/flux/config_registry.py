@@ -9,6 +9,7 @@ from torchtitan_b200.config import ActivationCheckpointConfig, TrainingConfig
 from . import model_registry
 from .flux_datasets import FluxDataLoader
 from .trainer import Encoder, FluxTrainer
+from .validate import FluxValidator
 
 
 def flux_debugmodel() -> FluxTrainer.Config:
@@ -19,6 +20,8 @@ def flux_debugmodel() -> FluxTrainer.Config:
         training=TrainingConfig(local_batch_size=4, seq_len=16, steps=10, max_norm=2.0),
         encoder=Encoder(random_init=True), checkpoint=CheckpointManager.Config(interval=10, last_save_model_only=False),
         activation_checkpoint=ActivationCheckpointConfig(mode="full"),
+        validator=FluxValidator.Config(steps=2, timesteps=2, freq=5, dataloader=FluxDataLoader.Config(
+            dataset="synthetic", img_size=64, t5_max_length=16, clip_max_length=16)),
     )
 
 

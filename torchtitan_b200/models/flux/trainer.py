@@ -16,6 +16,7 @@ from torchtitan_b200.trainer import Trainer
 from .model.autoencoder import load_ae
 from .model.hf_embedder import FluxEmbedder
 from .utils import create_position_encoding_for_latents, pack_latents, preprocess_data
+from .validate import FluxValidator
 
 
 @dataclass(kw_only=True, slots=True)
@@ -32,6 +33,7 @@ class FluxTrainer(Trainer):
     @dataclass(kw_only=True, slots=True)
     class Config(Trainer.Config):
         encoder: Encoder = field(default_factory=Encoder)
+        validator: FluxValidator.Config = field(default_factory=FluxValidator.Config)
 
     def __init__(self, config: Config):
         super().__init__(config)
@@ -43,6 +45,8 @@ class FluxTrainer(Trainer):
                                    random_init=e.random_init)
         self.clip_encoder = FluxEmbedder(e.clip_encoder, random_init=e.random_init, hidden=self.model_config.vec_in_dim).to(self.device, self._dtype)
         self.t5_encoder = FluxEmbedder(e.t5_encoder, random_init=e.random_init, hidden=self.model_config.context_in_dim).to(self.device, self._dtype)
+        if self.validator is not None:
+            self.validator.attach(self)
 
     def forward_backward_step(self, *, input_dict, labels, global_valid_tokens=None):
         input_dict = dict(input_dict)
