@@ -119,6 +119,13 @@ def main(argv: list[str] | None = None) -> int:
     for name, why in skipped:
         print(f"skipped {name}: {why}")
     os.makedirs(a.output_dir, exist_ok=True)
+    lighthouse = None
+    if a.test_suite == "ft" and cases and not a.dry_run and not os.environ.get("TT_LIGHTHOUSE"):
+        # fault-tolerant jobs register with a quorum service: run one for the duration of the suite
+        from torchtitan_b200.experiments.ft.lighthouse import Lighthouse
+
+        lighthouse = Lighthouse()
+        os.environ["TT_LIGHTHOUSE"] = lighthouse.address
     failed = []
     for c in cases:
         validate(c, extra)
@@ -133,6 +140,9 @@ def main(argv: list[str] | None = None) -> int:
                 raise
             print(f"FAILED  {c.test_name}: {e}", flush=True)
             failed.append(c.test_name)
+    if lighthouse is not None:
+        lighthouse.shutdown()
+        os.environ.pop("TT_LIGHTHOUSE", None)
     if failed:
         print(f"{len(failed)} failed: {failed}")
     return 1 if failed else 0

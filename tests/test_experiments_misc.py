@@ -193,3 +193,36 @@ def test_vlm_data_path_and_model_step():
     loss = torch.nn.functional.cross_entropy(out.flatten(0, 1).float(), labels.flatten(), ignore_index=-100)
     loss.backward()
     assert model.encoder.layers["0"].fc1.weight.grad.abs().sum() > 0 and model.projector.w2.weight.grad.abs().sum() > 0
+
+
+def test_vlm_loader_feeds_the_model_and_resumes():
+    """The loader the job configuration builds: placeholders and patches stay one to one after the label shift, and a
+    restored loader continues with the next batch."""
+    from torchtitan_b200.experiments.vlm import llama3_siglip2_configs
+    from torchtitan_b200.experiments.vlm.datasets import MMDataLoader
+
+    cfg = MMDataLoader.Config(max_patches_per_image=16, max_images_per_batch=64)
+    dl = cfg.build(dp_world_size=1, dp_rank=0, tokenizer=None, seq_len=128, local_batch_size=2, model_vocab_size=2048)
+    it = iter(dl)
+    batches = [next(it) for _ in range(3)]
+    st = dl.special_tokens
+    assert (st.img_id, st.pad_id) == (2044, 2047)
+    for inputs, labels in batches:
+        assert inputs["input"].shape == (2, 128) and labels.shape == (2, 128)
+        assert int((inputs["input"] == st.img_id).sum()) == int((inputs["grid_thw"][:, :, 1:] != -1).all(-1).sum())
+    dl2 = cfg.build(dp_world_size=1, dp_rank=0, tokenizer=None, seq_len=128, local_batch_size=2, model_vocab_size=2048)
+    dl2.load_state_dict({"batches": 2})
+    again, _ = next(iter(dl2))
+    assert torch.equal(again["input"], batches[2][0]["input"])
+    import dataclasses
+
+    mc = dataclasses.replace(llama3_siglip2_configs["debugmodel"], n_layers=1)
+    mc.rope = dataclasses.replace(mc.rope, max_seq_len=128)
+    model = mc.build()
+    model.init_weights()
+    inputs, labels = batches[0]
+    import types
+
+    masks = model.get_attention_masks(inputs["input"], types.SimpleNamespace(eos_id=0))
+    out = model(inputs["input"], inputs["pixel_values"], inputs["grid_thw"], inputs["special_tokens"], masks)
+    assert out.shape == (2, 128, mc.vocab_size)

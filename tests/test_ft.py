@@ -112,6 +112,52 @@ def test_replicas_average_survive_a_death_and_heal_a_late_joiner():
         lh.shutdown()
 
 
+def _group_member(lh_addr, replica, rank, init_file, q):
+    """One rank of a two-rank replica group (its own gloo group inside the replica, as a training job has)."""
+    try:
+        import torch.distributed as dist
+
+        dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=2)
+        m = _mk(lh_addr, f"g{replica}", min_replica_size=2, rank=rank, world_size=2)
+        got = []
+        for _ in range(3):
+            qm = m.start_quorum()
+            g = torch.full((2,), float((replica + 1) * 10 + rank))
+            m.allreduce(g, average=True)
+            if m.should_commit():
+                got.append((len(qm.replica_ids), g[0].item()))
+        q.put((replica, rank, got))
+        m.shutdown()
+        dist.destroy_process_group()
+    except Exception:  # pragma: no cover
+        import traceback
+
+        q.put((replica, rank, "ERR " + traceback.format_exc()))
+
+
+def test_replica_groups_of_two_ranks_average_rank_by_rank(tmp_path):
+    """Local rank r of every replica group forms its own cross-replica group (torchft's layout: the replicate dimension
+    is managed per shard rank), all through one rendezvous store."""
+    from torchtitan_b200.experiments.ft import Lighthouse
+
+    lh = Lighthouse(heartbeat_timeout_ms=2000, join_timeout_ms=6000)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    try:
+        ps = [ctx.Process(target=_group_member, args=(lh.address, rep, r, str(tmp_path / f"init{rep}"), q))
+              for rep in range(2) for r in range(2)]
+        for p in ps:
+            p.start()
+        res = [q.get(timeout=90) for _ in ps]
+        for p in ps:
+            p.join(timeout=30)
+        for replica, rank, got in res:
+            assert not isinstance(got, str), got
+            assert got == [(2, 15.0 + rank)] * 3, (replica, rank, got)      # (10 + r + 20 + r) / 2
+    finally:
+        lh.shutdown()
+
+
 class _FakeManager:
     """Two in-process 'replicas' averaged synchronously (no sockets): enough to test the semi-sync algebra."""
 

@@ -99,11 +99,10 @@ class ReplicaManager:
     def _reconfigure(self, q: Quorum) -> None:
         n, me = len(q.replica_ids), q.rank_of(self.replica_id)
         host, port = q.addresses[0].rsplit(":", 1)
-        # one store per replica-group rank: hosted by the first replica's rank 0 (+ local rank offset)
-        is_master = me == 0
+        # one rendezvous store for the whole quorum, hosted by rank 0 of the first replica; local rank r of every replica
+        # meets its peers (rank r of the other replicas) under its own prefix and forms its own cross-replica group
+        is_master = me == 0 and self.rank == 0
         port = int(port)
-        if self.rank != 0:
-            raise NotImplementedError("cross-replica groups for local ranks > 0 need one store port per local rank")
         if is_master and self._store is None:
             self._store = dist.TCPStore(host, port, is_master=True, wait_for_workers=False, timeout=self.timeout)
             store = self._store
@@ -111,7 +110,7 @@ class ReplicaManager:
             store = self._store
         else:
             store = dist.TCPStore(host, port, is_master=False, timeout=self.timeout)
-        store = dist.PrefixStore(f"q{q.quorum_id}", store)
+        store = dist.PrefixStore(f"q{q.quorum_id}/r{self.rank}", store)
         if self.backend == "nccl":
             opts = dist.ProcessGroupNCCL.Options()
             opts._timeout = self.timeout

@@ -7,6 +7,8 @@ from dataclasses import dataclass
 
 import torch
 
+from torchtitan_b200.components.dataloader import BaseDataLoader
+
 from .model import SpecialTokens
 
 
@@ -111,6 +113,15 @@ class MultiModalCollatorNLD:
                 grid[n, : g.shape[0]] = g
                 n += 1
         inputs, labels = toks[:, :-1], toks[:, 1:].clone()
+        # the shift drops the last token of every row; where that token was an image placeholder, drop the patch it stood
+        # for as well (the last patch of the row's last image), so placeholders and patches stay one to one
+        n = 0
+        for b, (_, pats, _) in enumerate(batch):
+            n += len(pats)
+            if len(pats) and int(toks[b, -1]) == st.img_id:
+                valid = (grid[n - 1, :, 1:] != -1).all(-1).nonzero()
+                if valid.numel():
+                    grid[n - 1, int(valid[-1])] = -1
         for t in (st.pad_id, st.img_id, st.boi_id, st.eoi_id):
             labels[labels == t] = st.ignore_id
         return {"input": inputs, "pixel_values": pixels, "grid_thw": grid, "special_tokens": st}, labels
@@ -140,3 +151,52 @@ class SyntheticMultiModalDataset(torch.utils.data.IterableDataset):
             out = packer.add(*sample)
             if out is not None:
                 yield out
+
+
+class MMDataLoader(BaseDataLoader):
+    """Packed multimodal batches for the trainer: ``({"input", "pixel_values", "grid_thw", "special_tokens"}, labels)``.
+
+    Reference: torchtitan/experiments/vlm/datasets/mm_datasets.py (the loader built from the job configuration). The
+    ``synthetic`` dataset needs no files; its special tokens take the last four ids of the model's vocabulary."""
+
+    @dataclass(kw_only=True, slots=True)
+    class Config(BaseDataLoader.Config):
+        dataset: str = "synthetic"
+        patch_size: int = 16
+        max_patches_per_image: int = 64
+        max_images_per_batch: int = 32
+        seed: int = 0
+
+    def __init__(self, config: Config, *, dp_world_size: int, dp_rank: int, tokenizer=None, seq_len: int, local_batch_size: int,
+                 model_vocab_size: int | None = None, **kwargs):
+        if config.dataset != "synthetic":
+            raise ValueError(f"vlm dataset {config.dataset!r} is not available offline; supported: ['synthetic']")
+        self.config, self.batch_size = config, local_batch_size
+        try:
+            st = SpecialTokens.from_tokenizer(tokenizer)
+        except Exception:
+            v = model_vocab_size or 2048
+            st = SpecialTokens("<|image|>", v - 4, "<|begin_of_image|>", v - 3, "<|end_of_image|>", v - 2, "<|pad|>", v - 1)
+        self.special_tokens = st
+        vocab = min(i for i in (st.img_id, st.boi_id, st.eoi_id, st.pad_id))
+        self.dataset = SyntheticMultiModalDataset(st, vocab=vocab, seq_len=seq_len, patch=config.patch_size,
+                                                  max_patches=config.max_patches_per_image, seed=config.seed, dp_rank=dp_rank,
+                                                  dp_world_size=dp_world_size)
+        self.collate = MultiModalCollatorNLD(patch_dim=3 * config.patch_size ** 2, max_images_per_batch=config.max_images_per_batch,
+                                             max_patches_per_image=config.max_patches_per_image, special_tokens=st)
+        self._batches = 0
+
+    def __iter__(self):
+        it = iter(self.dataset)
+        for _ in range(self._batches * self.batch_size):          # resume: the stream is a pure function of (seed, rank)
+            next(it)
+        while True:
+            batch = [next(it) for _ in range(self.batch_size)]
+            self._batches += 1
+            yield self.collate(batch)
+
+    def state_dict(self):
+        return {"batches": self._batches}
+
+    def load_state_dict(self, state_dict):
+        self._batches = int(state_dict.get("batches", 0)) if state_dict else 0
