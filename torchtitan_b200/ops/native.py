@@ -148,4 +148,8 @@ def kernel_errors() -> dict:
         e4 = (ctypes.c_int * 4)()
         if L.tt_ep_error(e4) == 1:
             out["ep"] = tuple(e4)
+    if hasattr(L, "tt_comm_error"):                      # peer-memory collectives of the FSDP / weight-sync transports
+        c4 = (ctypes.c_int * 4)()
+        if L.tt_comm_error(c4) != 0:
+            out["comm"] = tuple(c4)                          # (code, peer, expected version, version seen)
     return {k: v for k, v in out.items() if v}
