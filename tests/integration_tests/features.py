@@ -59,6 +59,9 @@ def build_features_test_list() -> list[T]:
         T([[f"{CP} 4", "--parallelism.context_parallel_rotate_method allgather"]], "CP (allgather)", "cp_allgather", ngpu=4),
         T([[f"{CP} 4", "--parallelism.context_parallel_rotate_method alltoall"]], "CP (alltoall)", "cp_alltoall", ngpu=4),
         T([[f"{CP} 2"]], "CP with document masks", "cp_document_masks", ngpu=2, config="llama3_debugmodel_flex_attn"),
+        T([[f"{PP} 2", f"{SCHED} 1F1B"]], "PP with document masks", "pp_document_masks", ngpu=2, config="llama3_debugmodel_flex_attn"),
+        T([[f"{PP} 2", f"{SCHED} Interleaved1F1B"]], "PP with packed-document attention", "pp_varlen", ngpu=2,
+          config="llama3_debugmodel_varlen_attn"),
         T([[f"{SHARD} 2", f"{REPL} 2", f"{TP} 2"]], "HSDP + TP", "hsdp+tp", ngpu=8),
         T([[f"{SHARD} 2", f"{CP} 2"]], "FSDP + CP", "fsdp+cp", ngpu=4),
         T([[f"{SHARD} 1", f"{REPL} 2", f"{CP} 2"]], "HSDP + CP (without dp_shard)", "hsdp+cp_without_dp_shard", ngpu=4),

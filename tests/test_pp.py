@@ -97,3 +97,20 @@ def test_pp2_matches_single_process(tmp_path, schedule):
         assert abs(o["loss"] - o["ref"]) < 1e-5, o
         assert abs(o["eval"] - o["ref"]) < 1e-5, o
     assert max(o["grad_err"] for o in res) < 1e-5, res
+
+
+def test_keyword_arguments_are_cut_per_micro_batch():
+    """Mask records travel to every stage as keyword arguments; each micro-batch must see its own rows."""
+    from torchtitan_b200.models.common.attention import AttentionMasks
+    from torchtitan_b200.parallel.pp import _batch_size_hint, _micro_batch_of
+
+    doc = torch.arange(4 * 6).view(4, 6)
+    masks = AttentionMasks(doc_ids=doc, cu_seqlens=torch.tensor([0, 24]), max_seqlen=24, window=3)
+    kw = {"attention_masks": {"rope": masks, "nope": AttentionMasks()}, "positions": torch.arange(6).view(1, 6), "flag": True}
+    assert _batch_size_hint(kw) == 4
+    got = [{k: _micro_batch_of(v, 2, m, 4) for k, v in kw.items()} for m in range(2)]
+    assert torch.equal(got[1]["attention_masks"]["rope"].doc_ids, doc[2:]) and got[1]["attention_masks"]["rope"].window == 3
+    assert got[0]["attention_masks"]["rope"].cu_seqlens is None            # packed boundaries no longer describe the rows
+    assert got[0]["attention_masks"]["nope"].doc_ids is None
+    assert got[0]["positions"].shape == (1, 6) and got[0]["flag"] is True
+    assert _micro_batch_of(masks, 1, 0, 4) is masks

@@ -223,6 +223,45 @@ def validate_actions(ranks: list[list[Action]], pp: int, num_stages: int, n_mb: 
 _DTYPES = [torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int64]
 
 
+def _micro_batch_of(v, n: int, m: int, bs: int | None):
+    """Micro-batch ``m`` of ``n`` of a keyword argument: tensors whose leading dimension is the batch are cut, containers
+    (dicts, mask records) are walked, everything else is passed whole."""
+    import dataclasses
+
+    if n <= 1 or bs is None:
+        return v
+    if torch.is_tensor(v):
+        return torch.tensor_split(v, n, dim=0)[m] if v.dim() > 0 and v.shape[0] == bs else v
+    if isinstance(v, dict):
+        return {k: _micro_batch_of(x, n, m, bs) for k, x in v.items()}
+    if dataclasses.is_dataclass(v) and not isinstance(v, type):
+        changes = {}
+        for f in dataclasses.fields(v):
+            x = getattr(v, f.name)
+            if torch.is_tensor(x) and x.dim() > 1 and x.shape[0] == bs:
+                changes[f.name] = torch.tensor_split(x, n, dim=0)[m]
+        if changes:
+            # packed boundaries describe the whole batch: the per-row ids carry the same information
+            for name in ("cu_seqlens", "max_seqlen"):
+                if hasattr(v, name) and name not in changes:
+                    changes[name] = None
+            return dataclasses.replace(v, **changes)
+    return v
+
+
+def _batch_size_hint(kwargs) -> int | None:
+    import dataclasses
+
+    for v in kwargs.values():
+        for x in (v.values() if isinstance(v, dict) else (v,)):
+            if dataclasses.is_dataclass(x) and not isinstance(x, type):
+                for f in dataclasses.fields(x):
+                    t = getattr(x, f.name)
+                    if torch.is_tensor(t) and t.dim() > 1:
+                        return t.shape[0]
+    return None
+
+
 class PipelineSchedule:
     """Executes one rank's action list. Messages between two ranks are FIFO and untagged (NCCL), so
     the receiver consumes them in the *sender's* order, which it derives from the global schedule,
@@ -306,15 +345,9 @@ class PipelineSchedule:
             inputs_mb = list(torch.tensor_split(args[0], n, dim=0)) if n > 1 else [args[0]]
         elif target is not None:
             bs = target.shape[0]
-        kw_mb = []
-        for m in range(n):
-            kw = {}
-            for k, v in kwargs.items():
-                if torch.is_tensor(v) and n > 1 and v.dim() > 0 and bs is not None and v.shape[0] == bs:
-                    kw[k] = torch.tensor_split(v, n, dim=0)[m]
-                else:
-                    kw[k] = v
-            kw_mb.append(kw)
+        if bs is None:
+            bs = _batch_size_hint(kwargs)            # a middle stage sees neither the tokens nor the labels
+        kw_mb = [{k: _micro_batch_of(v, n, m, bs) for k, v in kwargs.items()} for m in range(n)]
         target_mb = None
         if target is not None:
             target_mb = list(torch.tensor_split(target, n, dim=0)) if n > 1 else [target]
