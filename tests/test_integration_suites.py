@@ -45,4 +45,3 @@ def test_one_case_runs_end_to_end_on_cpu_ranks(tmp_path):
     rc = run_tests.main([str(tmp_path), "--test_suite", "features", "--test_name", "fsdp_reshard_always", "--ngpu", "2", "--cpu",
                          "--extra", "--training.steps 3 --training.local_batch_size 2 --training.seq_len 64"])
     assert rc == 0
-    assert os.path.isdir(tmp_path / "fsdp_reshard_always")
