@@ -29,6 +29,10 @@ def build_features_test_list() -> list[T]:
            [CKPT, "--checkpoint.initial_load_path {dump}/hf_checkpoint/step-10", "--checkpoint.initial_load_model_only",
             "--checkpoint.initial_load_in_hf"]],
           "Checkpoint: model-only save and load in the Hugging Face definition and format", "model_only_hf_checkpoint"),
+        T([[CKPT, "--checkpoint.folder hf_checkpoint", "--checkpoint.last_save_model_only", "--checkpoint.last_save_in_hf", f"{TP} 2"],
+           [CKPT, "--checkpoint.initial_load_path {dump}/hf_checkpoint/step-10", "--checkpoint.initial_load_model_only",
+            "--checkpoint.initial_load_in_hf"]],
+          "Checkpoint: Hugging Face export written under TP, loaded under plain FSDP", "hf_checkpoint_across_layouts"),
         T([[CKPT, "--checkpoint.last_save_model_only"]], "Checkpoint: model-only save in fp32", "last_save_model_only_fp32"),
         T([[CKPT, "--checkpoint.last_save_model_only", "--checkpoint.export_dtype bfloat16"]],
           "Checkpoint: model-only save in bf16", "last_save_model_only_bf16"),
