@@ -84,7 +84,10 @@ def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_
     torch.manual_seed(seed)
     os.environ["PYTHONHASHSEED"] = str(seed % 2**32)
     if world > 1 and dist.is_initialized() and torch.device(device).type == "cuda":
-        seed_dtensor_rng(parallel_dims.world_mesh, seed)
+        try:
+            seed_dtensor_rng(parallel_dims.world_mesh, seed)
+        except Exception as e:      # every rank of the job is here, so DTensor's own lazy start-up sync also works
+            logger.warning(f"DTensor RNG tracker not pre-seeded ({type(e).__name__}: {e}); falling back to its start-up sync")
 
 
 def seed_dtensor_rng(mesh, seed: int) -> None:
