@@ -22,11 +22,12 @@ def build_autoparallel_test_list() -> list[T]:
 
 
 def build_transformers_backend_test_list() -> list[T]:
-    # wrapped Hugging Face models take the data-parallel layouts; tensor / pipeline / context parallel over an arbitrary
-    # Hugging Face module tree are not built here (the cases of the reference that use them have no counterpart)
+    # wrapped Hugging Face models take data-parallel layouts and tensor parallel; pipeline / context parallel over an
+    # arbitrary Hugging Face module tree are not built here
     h = dict(module="transformers_modeling_backend", config="transformers_modeling_backend_debugmodel")
     return [T([[]], "Hugging Face model, FSDP", "hf_fsdp", ngpu=2, **h),
             T([[f"{SHARD} 2", "--parallelism.data_parallel_replicate_degree 2"]], "Hugging Face model, HSDP", "hf_hsdp", ngpu=4, **h),
+            T([[f"{SHARD} 2", f"{TP} 2"]], "Hugging Face model, FSDP + TP", "hf_fsdp+tp", ngpu=4, **h),
             T([["--checkpoint.enable"], ["--checkpoint.enable", "--training.steps 20"]], "Hugging Face model, save and resume",
               "hf_checkpoint", ngpu=2, **h)]
 

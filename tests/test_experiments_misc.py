@@ -121,6 +121,57 @@ def _hf_fsdp_worker(rank, world):
     return {"err": (full - ref.output.weight.grad).abs().max().item(), "units": len(fsdp.fsdp_units(model))}
 
 
+def _hf_tp_worker(rank, world):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.checkpoint import ModelWrapper
+    from torchtitan_b200.config import ActivationCheckpointConfig, ParallelismConfig, TrainingConfig
+    from torchtitan_b200.experiments.transformers_modeling_backend import model_registry
+    from torchtitan_b200.parallel import ParallelDims
+
+    spec = model_registry("debugmodel")
+    spec.model.overrides = dict(spec.model.overrides, num_hidden_layers=2)
+    torch.manual_seed(0)
+    ref = spec.model.build()
+    ref.init_weights()
+    model = spec.model.build()
+    model.load_state_dict(ref.state_dict())
+    pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=world, pp=1, ep=1, etp=1, world_size=world)
+    tr = TrainingConfig(mixed_precision_param="float32", mixed_precision_reduce="float32")
+    spec.parallelize_fn(model, parallel_dims=pd, training=tr, model_converters=None,
+                        parallelism=ParallelismConfig(tensor_parallel_degree=world), compile_config=None,
+                        ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="")
+    x = torch.randint(0, 2048, (2, 16), generator=torch.Generator().manual_seed(5))
+    out = model(x)
+    out.float().logsumexp(-1).sum().backward()
+    want = ref(x)
+    want.float().logsumexp(-1).sum().backward()
+    blk, rblk = model.layers["0"], ref.layers["0"]
+    n = rblk.self_attn.q_proj.weight.shape[0] // world
+    k = rblk.mlp.down_proj.weight.shape[1] // world
+    sd = ModelWrapper(model).state_dict()
+    key = next(kk for kk in sd if kk.endswith("layers.0.self_attn.q_proj.weight"))
+    return {
+        "out": (out - want).abs().max().item(),
+        "q": (blk.self_attn.q_proj.weight.grad - rblk.self_attn.q_proj.weight.grad[rank * n:(rank + 1) * n]).abs().max().item(),
+        "down": (blk.mlp.down_proj.weight.grad - rblk.mlp.down_proj.weight.grad[:, rank * k:(rank + 1) * k]).abs().max().item(),
+        "norm": (blk.input_layernorm.weight.grad - rblk.input_layernorm.weight.grad).abs().max().item(),
+        "emb": (model.tok_embeddings.weight.grad - ref.tok_embeddings.weight.grad).abs().max().item(),
+        "ckpt_shape": tuple(sd[key].shape), "full_shape": tuple(rblk.self_attn.q_proj.weight.shape),
+    }
+
+
+def test_transformers_backend_tensor_parallel_matches_single_process(tmp_path):
+    """Reference: torchtitan/experiments/transformers_modeling_backend/parallelize.py (tensor-parallel plan for wrapped
+    Hugging Face decoders)."""
+    from dist_utils import run_ranks
+
+    for o in run_ranks(_hf_tp_worker, 2, tmp_path=tmp_path):
+        assert max(o[k] for k in ("out", "q", "down", "norm", "emb")) < 1e-4, o
+        assert o["ckpt_shape"] == o["full_shape"], o          # checkpoints see the full projection
+
+
 def test_transformers_backend_fsdp2_grads(tmp_path):
     from dist_utils import run_ranks
 

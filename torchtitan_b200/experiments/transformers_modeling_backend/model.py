@@ -48,11 +48,10 @@ class HFTransformerModel(BaseModel):
             if os.path.exists(cand):
                 self.hf_config_path = cand
             par = trainer_config.parallelism
-            for name, deg in (("tensor", par.tensor_parallel_degree), ("context", par.context_parallel_degree),
-                              ("pipeline", par.pipeline_parallel_degree)):
+            for name, deg in (("context", par.context_parallel_degree), ("pipeline", par.pipeline_parallel_degree)):
                 if deg > 1:
                     raise NotImplementedError(f"{name} parallel is not available for wrapped Hugging Face models; "
-                                              "use FSDP / HSDP (data_parallel_shard_degree / data_parallel_replicate_degree)")
+                                              "use FSDP / HSDP and tensor parallel")
 
         def hf_config(self):
             from transformers import AutoConfig, CONFIG_MAPPING

@@ -1,6 +1,7 @@
 """Activation checkpointing + FSDP/HSDP for wrapped Hugging Face decoders (one unit per decoder layer, one for
 [norm, lm_head], one for the rest). Parity: torchtitan/experiments/transformers_modeling_backend/parallelize.py:41-400,
-minus the tensor/context/pipeline plans (rejected in the model configuration)."""
+plus tensor parallel for the usual decoder layout (``self_attn.{q,k,v,o}_proj``, ``mlp.{gate,up,down}_proj``); context and
+pipeline plans are rejected in the model configuration."""
 
 from __future__ import annotations
 
@@ -25,8 +26,74 @@ def _checkpoint_layer(layer: nn.Module) -> None:
     layer.forward = forward
 
 
+class _CopyToTensorParallel(torch.autograd.Function):
+    """Identity in forward; backward sums the input gradient over the group (each rank back-propagated through its own
+    slice of the heads / hidden units)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def apply_tp_to_hf_decoder(model: nn.Module, tp_mesh) -> None:
+    """Megatron-style tensor parallel over the module names most Hugging Face decoders share: q/k/v and gate/up projections
+    are split by output features (whole heads), ``o_proj`` / ``down_proj`` by input features with a sum of the partial
+    outputs. Hugging Face attention reshapes with ``-1`` heads, so it runs unchanged on its slice of the heads. Norms,
+    embeddings and the output head stay replicated (activations are replicated: no sequence parallel here).
+    Reference: torchtitan/experiments/transformers_modeling_backend/parallelize.py (its tensor-parallel plan)."""
+    from torchtitan_b200.parallel.tp import _AllReduceSum, _shard_param, _wrap
+
+    W, r, group = tp_mesh.size(), tp_mesh.get_local_rank(), tp_mesh.get_group()
+    cfg = model.hf_config
+    kv = getattr(cfg, "num_key_value_heads", None) or cfg.num_attention_heads
+    if cfg.num_attention_heads % W or kv % W:
+        raise ValueError(f"tensor parallel degree {W} must divide the head counts ({cfg.num_attention_heads} / {kv})")
+
+    def region(mod, cols, rows):
+        for name in cols + rows:
+            if not hasattr(mod, name):
+                raise NotImplementedError(f"tensor parallel for wrapped Hugging Face models expects a `{name}` projection in "
+                                          f"{type(mod).__name__}")
+        for name in cols:
+            lin = getattr(mod, name)
+            _shard_param(lin, "weight", 0, r, W, group, tp_mesh)
+            if lin.bias is not None:
+                _shard_param(lin, "bias", 0, r, W, group, tp_mesh)
+            lin.out_features //= W
+        for name in rows:
+            lin = getattr(mod, name)
+            if lin.bias is not None:
+                raise NotImplementedError(f"{name}: a bias on a row-parallel projection is not supported")
+            _shard_param(lin, "weight", 1, r, W, group, tp_mesh)
+            lin.in_features //= W
+
+        def fwd(inner, hidden_states, *a, **k):
+            out = inner(_CopyToTensorParallel.apply(hidden_states, group), *a, **k)
+            if isinstance(out, tuple):
+                return (_AllReduceSum.apply(out[0], group),) + tuple(out[1:])
+            return _AllReduceSum.apply(out, group)
+
+        _wrap(mod, fwd)
+
+    for layer in model.layers.values():
+        region(layer.self_attn, ["q_proj", "k_proj", "v_proj"], ["o_proj"])
+        region(layer.mlp, ["gate_proj", "up_proj"], ["down_proj"])
+    logger.info(f"Applied tensor parallel (degree {W}) to the wrapped Hugging Face model")
+
+
 def parallelize_hf_transformers(model: nn.Module, *, parallel_dims, training, model_converters, parallelism, compile_config,
                                 ac_config, dump_folder: str):
+    if parallel_dims.tp_enabled:
+        apply_tp_to_hf_decoder(model, parallel_dims.get_mesh("tp"))
     layers = list(model.layers.values())
     if ac_config.mode == "full":
         for layer in layers:
