@@ -90,6 +90,10 @@ def run(args) -> dict:
     f1.record()
     sync()
     e2e_ms = max_ranks(f0.elapsed_time(f1)) / args.steps
+    if getattr(args, "kernel_table", None):
+        from bench import write_kernel_table
+
+        write_kernel_table(args.kernel_table, lambda: step(host_iter), rank)
     value = tokens_per_step / (dev_ms / 1e3)
     out = {
         "metric": "llama3_8b_train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

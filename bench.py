@@ -137,6 +137,32 @@ def barrier_sync():
     torch.cuda.synchronize()
 
 
+def write_kernel_table(path: str, step_fn, rank: int) -> None:
+    """Run one more step under the PyTorch profiler (device activities only) and write the time per kernel name,
+    largest first, as text. The figures are in-situ durations (clocks and caches as in training); they are a
+    breakdown, not a benchmark value."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn()
+        torch.cuda.synchronize()
+    if rank != 0:
+        return
+    rows: dict[str, list[float]] = {}
+    for ev in prof.events():
+        if ev.device_type is not None and str(ev.device_type).endswith("CUDA"):
+            r = rows.setdefault(ev.name, [0.0, 0])
+            r[0] += ev.device_time_total if hasattr(ev, "device_time_total") else ev.cuda_time_total
+            r[1] += 1
+    total = sum(v[0] for v in rows.values()) or 1.0
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        f.write(f"# device time of one step by kernel (us); total {total:.0f} us\n")
+        for name, (us, n) in sorted(rows.items(), key=lambda kv: -kv[1][0])[:60]:
+            f.write(f"{us:12.0f} {100 * us / total:6.2f}% {n:6d}  {name[:150]}\n")
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -231,6 +257,8 @@ def run_ours(args) -> dict:
         "kernel_error_flags": errs,
         "impl": "torchtitan_b200",
     }
+    if args.kernel_table:
+        write_kernel_table(args.kernel_table, lambda: step(host_iter), rank)
     if args.layers is not None:
         out["invalid_truncated_model_layers"] = args.layers
     if args.override:
@@ -255,6 +283,8 @@ def main():
                     "string, e.g. --override='--parallelism.fsdp_reshard_after_forward never' (recorded in the JSON line)")
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: truncate the model (result is not a benchmark)")
     ap.add_argument("--ref-compile", action="store_true", help="reference arm only: add --compile.enable")
+    ap.add_argument("--kernel-table", default=None, help="after the timed regions, run one more step under the PyTorch "
+                    "profiler and write the device time per kernel name to this file")
     ap.add_argument("--ac", default=None, help="override activation_checkpoint.mode (selective|full|none)")
     args = ap.parse_args()
     assert args.warmup >= 3 or os.environ.get("TT_BENCH_ALLOW_SHORT_WARMUP"), "warm-up must be at least 3 steps"

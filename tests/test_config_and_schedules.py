@@ -131,11 +131,11 @@ def _lrs(total, **kw):
 
 def test_lr_warmup_then_linear_decay_to_zero():
     lrs, _, _ = _lrs(10, warmup_steps=2, decay_type="linear")
-    assert lrs[0] == pytest.approx(1 / 3) and lrs[1] == pytest.approx(2 / 3)
-    assert lrs[2] == pytest.approx(1.0)
-    assert lrs[3] == pytest.approx(1.0)                       # the schedule holds the peak for one step
-    assert all(a > b for a, b in zip(lrs[3:], lrs[4:]))       # then strictly decreasing
-    assert lrs[-1] > 0.0
+    assert lrs[0] == pytest.approx(1 / 2) and lrs[1] == pytest.approx(1.0)   # the last warm-up step is at the peak
+    assert lrs[2] == pytest.approx(1.0)                       # one stable step (the virtual extra step)
+    assert all(a > b for a, b in zip(lrs[2:], lrs[3:]))       # then strictly decreasing
+    assert lrs[3] == pytest.approx(1 - 1 / 8)
+    assert lrs[-1] == pytest.approx(1 - 7 / 8) and lrs[-1] > 0.0
 
 
 def test_lr_warmup_stable_decay_with_floor_and_shapes():

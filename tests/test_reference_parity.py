@@ -4,8 +4,12 @@ Config: Llama-3 debug model with 8 KV heads (dim 256, 6 layers, 16 heads, FFN 76
 RoPE theta 500000), local batch 2 x seq 512 of uniform tokens from seed 0, AdamW lr 8e-4
 betas (0.9, 0.95) wd 0.1, warmup 2 of 10 steps. Both sides start from identical weights; ours
 runs this framework's model + FSDP runtime + optimizer container + LR schedule, the other side
-runs the reference's model code with torch's ``fully_shard``, ``AdamW`` and the reference LR
-lambda. Losses must agree to rtol 1e-4 at every step.
+runs the reference's model code with torch's ``fully_shard``, ``AdamW`` and the reference's own
+``LRSchedulersContainer``. Losses must agree to rtol 1e-4 at every step. A second test compares
+the learning-rate multipliers of the two schedulers step by step.
+
+The reference is taken from ``$TORCHTITAN_REFERENCE`` (a checkout) or from the offline install
+under ``baseline/_ref``; without either the tests are skipped.
 """
 
 import dataclasses
@@ -17,7 +21,8 @@ import torch
 
 from dist_utils import run_ranks
 
-REF = os.environ.get("TORCHTITAN_REFERENCE", "/" + os.path.join("root", "reference"))   # the reference checkout, when mounted
+_HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("TORCHTITAN_REFERENCE") or os.path.join(os.path.dirname(_HERE), "baseline", "_ref")
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "torchtitan")), reason="reference tree not mounted")
 
 STEPS, WARMUP, BATCH, SEQ, VOCAB = 10, 2, 2, 512, 2048
@@ -91,18 +96,10 @@ def _reference(rank, world, init_state):
     fully_shard(model, mesh=mesh)
     # torch's FSDP averages gradients over ranks (its "no division" mode needs PREMUL_SUM, which
     # gloo lacks); multiplying the loss by the world size (exact in fp32) gives the same sum.
+    from torchtitan.components.lr_scheduler import LRSchedulersContainer as RefSchedulers
+
     opt = torch.optim.AdamW(model.parameters(), lr=8e-4, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
-
-    def lr_lambda(step):  # the reference's warmup + linear decay with the virtual extra step
-        if step < WARMUP:
-            return float((step + 1) / (WARMUP + 1))
-        decay = STEPS - WARMUP
-        stable = STEPS + 1 - WARMUP - decay
-        if step < WARMUP + stable:
-            return 1.0
-        return 1 - float(step - WARMUP - stable) / decay
-
-    sched = torch.optim.lr_scheduler.LambdaLR(opt, lr_lambda)
+    sched = RefSchedulers.Config(warmup_steps=WARMUP).build(optimizers=[opt], training_steps=STEPS)
     losses = []
     for x, y in _batches(rank):
         opt.zero_grad()
@@ -135,3 +132,31 @@ def test_loss_matches_reference_fsdp2_cpu(tmp_path):
     for a, b in zip(ours, ref):
         assert abs(a - b) <= 1e-4 * abs(b), (ours, ref)
     assert ours[-1] < ours[0]
+
+
+@pytest.mark.parametrize("kind", ["linear", "sqrt", "cosine"])
+@pytest.mark.parametrize("decay_ratio,floor", [(None, 0.0), (0.3, 0.0), (0.25, 0.1), (None, 0.2)])
+def test_lr_multipliers_match_the_reference_scheduler_step_by_step(kind, decay_ratio, floor):
+    """Same multiplier at every step as the reference's own ``LRSchedulersContainer`` (built through its Config)."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from torchtitan.components.lr_scheduler import LRSchedulersContainer as RefSchedulers
+
+    from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
+
+    total, warmup = 100, 10
+    kw = dict(warmup_steps=warmup, decay_ratio=decay_ratio, decay_type=kind, min_lr_factor=floor)
+
+    def curve(container_cls):
+        opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+        sched = container_cls.Config(**kw).build(optimizers=[opt], training_steps=total)
+        out = []
+        for _ in range(total):
+            out.append(opt.param_groups[0]["lr"])
+            opt.step()
+            sched.step()
+        return out
+
+    ours, ref = curve(LRSchedulersContainer), curve(RefSchedulers)
+    assert ours == pytest.approx(ref, rel=1e-12, abs=1e-15)
+    assert ours[0] == pytest.approx(1 / warmup) and ours[warmup - 1] == pytest.approx(1.0)

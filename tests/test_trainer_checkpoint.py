@@ -180,3 +180,22 @@ def test_last_step_export_in_hf_format_and_reload(tmp_path, single_rank):
     assert torch.equal(fresh.model_parts[0].output.weight.detach(), out)
     assert torch.allclose(fresh.model_parts[0].layers["0"].attention.wq.weight.detach(), w)
     fresh.close()
+
+
+def test_no_checkpoint_is_written_after_a_kernel_gave_up(tmp_path, single_rank):
+    """A kernel error word that shows up between log steps stops the run before the step's checkpoint is written (the
+    interval is not a multiple of the log frequency, so only the check in front of the save can catch it)."""
+    ck = ["--checkpoint.enable", "--checkpoint.interval", "3", "--checkpoint.folder", "ckpt", "--metrics.log_freq", "100"]
+    tr = _trainer(tmp_path, 8, ck)
+    seen = []
+
+    def fake_words(sync=False):
+        seen.append((tr.step, sync))
+        return {"comm": 1} if tr.step >= 6 else {}
+
+    tr._kernel_error_words = fake_words
+    with pytest.raises(RuntimeError, match="gave up on a bounded wait"):
+        tr.train()
+    tr.close()
+    assert sorted(os.listdir(tmp_path / "ckpt")) == ["step-3"]          # step-6 was never written
+    assert (3, True) in seen and (6, True) in seen                       # checked (with a sync) right before both saves

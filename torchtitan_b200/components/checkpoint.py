@@ -338,6 +338,10 @@ class CheckpointManager(Configurable):
             out.update(src[MODEL].state_dict())
         return out
 
+    def will_save(self, curr_step: int, last_step: bool = False) -> bool:
+        """Whether :meth:`save` would write a checkpoint for this step (the trainer checks the kernels' error words first)."""
+        return self._should_save(curr_step, last_step)
+
     def _should_save(self, curr_step: int, last_step: bool = False) -> bool:
         if not self.enable or self.load_only:
             return False

@@ -3,12 +3,13 @@
 Parity: torchtitan/components/lr_scheduler.py:50-228. The multiplier at step ``s``
 (``LambdaLR`` semantics, ``s`` = number of ``step()`` calls so far):
 
-* warmup: ``(s + 1) / (warmup_steps + 1)``;
+* warmup: ``(s + 1) / warmup_steps`` (the last warm-up step already runs at the full rate);
 * stable: 1 for ``stable_steps = total + 1 - warmup - decay`` steps (the ``+ 1`` is a virtual
   last step so the rate never reaches ``min_lr_factor`` exactly inside training);
 * decay over ``decay_steps = decay_ratio * total`` (or everything after warmup when
-  ``decay_ratio is None``): progress ``1 - (s - warmup - stable) / decay`` shaped ``linear``,
-  ``sqrt`` or ``cosine``, then mapped to ``[min_lr_factor, 1]``.
+  ``decay_ratio is None``): progress ``(s + 1 - warmup - stable) / decay``, remaining fraction
+  ``1 - progress`` (``linear``), ``1 - sqrt(progress)`` (``sqrt``) or the cosine half period
+  (``cosine``), then mapped to ``[min_lr_factor, 1]``.
 
 ``total`` defaults to ``training.steps``; too-long warmup/decay are clipped with a warning.
 Only the first scheduler's state is checkpointed (all are identical).
@@ -31,16 +32,17 @@ __all__ = ["LRSchedulersContainer", "wsd_multiplier"]
 
 def wsd_multiplier(step: int, *, warmup: int, stable: int, decay: int, kind: str, floor: float) -> float:
     if step < warmup:
-        return float((step + 1) / (warmup + 1))
+        return float((step + 1) / warmup)
     if step < warmup + stable:
         return 1.0
-    progress = 1.0 - float(step - warmup - stable) / max(decay, 1)
+    assert decay != 0, "decay_steps must not be zero to reach the decay phase"
+    progress = float(step + 1 - warmup - stable) / decay
     if kind == "linear":
-        f = progress
+        f = 1.0 - progress
     elif kind == "sqrt":
-        f = 1.0 - math.sqrt(max(1.0 - progress, 0.0))
+        f = 1.0 - math.sqrt(progress)
     elif kind == "cosine":
-        f = 0.5 * (1.0 + math.cos(math.pi * (1.0 - progress)))
+        f = 0.5 * (1.0 + math.cos(math.pi * progress))
     else:
         raise ValueError(f"unknown lr decay type {kind}")
     return floor + (1.0 - floor) * f

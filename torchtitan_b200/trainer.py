@@ -369,13 +369,20 @@ class Trainer(Stateful, Configurable):
         lr = self.lr_schedulers.schedulers[0].get_last_lr()[0]
 
         microbatches = []
-        local_valid = 0
+        host_valid, dev_valid = 0, None
         for _ in range(self.gradient_accumulation_steps):
             input_dict, labels = next(data_iterator)
-            local_valid += int((labels != IGNORE_INDEX).sum())
+            n = (labels != IGNORE_INDEX).sum()
+            if labels.device.type == "cpu":
+                host_valid += int(n)           # host tensor: counting it is not a device synchronisation
+            else:
+                dev_valid = n if dev_valid is None else dev_valid + n
             microbatches.append((input_dict, labels))
-        # the denominator stays on the device: no host sync in the step
-        global_valid_tokens = torch.tensor(float(local_valid), dtype=torch.float32, device=self.device)
+        # the denominator is built and stays on the device: no device -> host read anywhere in the step
+        local_valid = torch.tensor(float(host_valid), dtype=torch.float32, device=self.device)
+        if dev_valid is not None:
+            local_valid = local_valid + dev_valid.to(torch.float32)
+        global_valid_tokens = local_valid.clone()
         if pd.dp_enabled:
             dist.all_reduce(global_valid_tokens, group=pd.get_mesh("batch").get_group())
 
@@ -403,7 +410,9 @@ class Trainer(Stateful, Configurable):
         if pd.dp_cp_enabled:
             loss = loss.detach()
             loss_mesh = pd.get_optional_mesh("loss")
-            local_avg = loss * global_valid_tokens / max(local_valid * max(pd.cp, 1), 1)
+            # this rank's loss sum over the valid tokens of its own batch, as in the reference
+            # (torchtitan/trainer.py:764-768)
+            local_avg = loss * global_valid_tokens / torch.clamp(local_valid, min=1.0)
             global_avg_loss = dist_utils.dist_sum(loss, loss_mesh)
             global_max_loss = dist_utils.dist_max(local_avg, loss_mesh)
             global_ntokens = dist_utils.dist_sum(
@@ -416,17 +425,24 @@ class Trainer(Stateful, Configurable):
         self.metrics_processor.log(self.step, global_avg_loss, global_max_loss, float(grad_norm), extra_metrics=extra)
         self._raise_on_kernel_errors()
 
-    def _raise_on_kernel_errors(self) -> None:
-        """The CUDA kernels of this framework bound every wait (peer flags, mbarriers, arrival counters); one that gives
-        up sets a bit in its family's error word and returns, so the step finishes with wrong numbers instead of
-        hanging. The words are read here, at log steps (the host has just synchronised for the loss)."""
+    def _kernel_error_words(self, sync: bool = False) -> dict:
+        """Error words of the native kernel families that are set ({} on CPU or without the native library)."""
         if self.device.type != "cuda":
-            return
+            return {}
         from torchtitan_b200.ops import native
 
         if not native.available():
-            return
-        errs = native.kernel_errors()
+            return {}
+        if sync:
+            torch.cuda.synchronize()
+        return native.kernel_errors()
+
+    def _raise_on_kernel_errors(self, sync: bool = False) -> None:
+        """The CUDA kernels of this framework bound every wait (peer flags, mbarriers, arrival counters); one that gives
+        up sets a bit in its family's error word and returns, so the step finishes with wrong numbers instead of
+        hanging. The words are read at log steps (the host has just synchronised for the loss) and, with ``sync``,
+        before every checkpoint save and validation pass, so that no checkpoint is written from such a step."""
+        errs = self._kernel_error_words(sync)
         if errs:
             raise RuntimeError(f"step {self.step}: a kernel gave up on a bounded wait (family -> error word): {errs}. "
                                "The results of the steps since the last log are not trustworthy.")
@@ -457,8 +473,13 @@ class Trainer(Stateful, Configurable):
                     ev[1].record()
                     self._pending_step_events = getattr(self, "_pending_step_events", []) + [ev]
                     self._drain_step_events()
-                self.checkpointer.save(self.step, last_step=(self.step == config.training.steps))
-                if self.validator is not None and self.validator.should_validate(self.step):
+                last = self.step == config.training.steps
+                will_validate = self.validator is not None and self.validator.should_validate(self.step)
+                if will_validate or self.checkpointer.will_save(self.step, last_step=last):
+                    # a kernel that gave up on a bounded wait leaves wrong numbers behind: never persist or score them
+                    self._raise_on_kernel_errors(sync=True)
+                self.checkpointer.save(self.step, last_step=last)
+                if will_validate:
                     self.validator.validate(self.model_parts, self.step)
                 if prof is not None:
                     prof.step()
