@@ -339,3 +339,23 @@ def test_optimizers_in_backward_frees_gradients_as_it_goes():
     for p, q in zip(net.parameters(), ref.parameters()):
         assert torch.allclose(p, q, atol=1e-6)
         assert p.grad is None
+
+
+def test_nvlink_staging_wait_is_needed_only_between_micro_batches_of_one_step():
+    """The peer-memory transport waits for the peers' "read done" flags before a unit's next backward only when a
+    reduce-scatter of that unit happened since the last optimizer step (host-side decision, no GPU needed)."""
+    from types import SimpleNamespace
+
+    from torchtitan_b200.parallel.nvlink_comm import NvlinkComm
+
+    comm = NvlinkComm.__new__(NvlinkComm)
+    unit = SimpleNamespace(params_version=3)
+    comm._units = {}
+    assert not comm.needs_staging_wait(unit)                       # unknown unit
+    st = {"staging": object(), "grad_version": 0, "rs_params_version": None}
+    comm._units[id(unit)] = st
+    assert not comm.needs_staging_wait(unit)                       # nothing reduced yet
+    st.update(grad_version=1, rs_params_version=3)
+    assert comm.needs_staging_wait(unit)                           # second micro-batch of the same optimizer step
+    unit.params_version = 4                                        # the optimizer ran: all-gather flags order the reuse
+    assert not comm.needs_staging_wait(unit)

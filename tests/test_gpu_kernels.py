@@ -20,6 +20,26 @@ def _rel(a, b):
     return (a.float() - b.float()).abs().max().item() / max(b.float().abs().max().item(), 1e-6)
 
 
+def _close(a, b, rtol, atol_frac):
+    """Per-element check: |a - b| <= atol + rtol * |b| with atol a fraction of the reference's RMS, so that errors on
+    small-magnitude elements are seen too (a max-over-max ratio hides them)."""
+    a, b = a.float(), b.float()
+    atol = atol_frac * b.pow(2).mean().sqrt().item()
+    bad = (a - b).abs() > atol + rtol * b.abs()
+    return bad.float().mean().item()
+
+
+@pytest.fixture(params=["fused", "split"])
+def bwd_form(request):
+    """Run a test once with the fused attention backward (default) and once with the deterministic two-kernel form."""
+    from torchtitan_b200.ops import cuda_ops
+
+    old = cuda_ops.ATTN_BWD_FUSED
+    cuda_ops.ATTN_BWD_FUSED = request.param == "fused"
+    yield request.param
+    cuda_ops.ATTN_BWD_FUSED = old
+
+
 def _no_kernel_errors():
     from torchtitan_b200.ops import native
 
@@ -41,6 +61,8 @@ def test_gemm(ops, M, N, K, a_mn, b_mn):
     _no_kernel_errors()
     assert _rel(got32, want) < 2e-3, _rel(got32, want)
     assert _rel(got, want) < 1e-2, _rel(got, want)
+    assert _close(got32, want, rtol=1e-3, atol_frac=1e-3) == 0.0      # per element, fp32 output
+    assert _close(got, want, rtol=8e-3, atol_frac=4e-3) == 0.0        # per element, bf16 output (one rounding)
 
 
 @pytest.mark.parametrize("pair", [0, 1])
@@ -79,7 +101,7 @@ def test_gemm_accumulate_and_strided(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,D", [(64, 4096), (1000, 128), (33, 2048), (4096, 512)])
+@pytest.mark.parametrize("rows,D", [(64, 4096), (1000, 128), (33, 2048), (4096, 512), (16, 16384)])
 def test_rmsnorm(ops, dtype, rows, D):
     torch.manual_seed(0)
     x = torch.randn(rows, D, device="cuda", dtype=dtype, requires_grad=True)
@@ -177,9 +199,9 @@ def test_adamw_and_sumsq(ops):
     assert abs(s.item() - g.double().pow(2).sum().item()) / s.item() < 1e-5
 
 
-@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 1024, 8, 2), (1, 384, 4, 1)])
+@pytest.mark.parametrize("B,S,H,Hkv", [(1, 128, 2, 2), (2, 256, 4, 2), (1, 1024, 8, 2), (1, 384, 4, 1), (1, 2048, 4, 1)])
 @pytest.mark.parametrize("causal", [True, False])
-def test_attention(ops, B, S, H, Hkv, causal):
+def test_attention(ops, B, S, H, Hkv, causal, bwd_form):
     from torchtitan_b200.ops import reference as ref
 
     torch.manual_seed(0)
@@ -205,11 +227,14 @@ def test_attention(ops, B, S, H, Hkv, causal):
     assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
     assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
     assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+    # per element: bf16 outputs of fp32-accumulated sums are within a few bf16 ulps (2^-8) of the fp32 result
+    for got, want in ((o, orf), (q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert _close(got, want, rtol=2e-2, atol_frac=2e-2) < 1e-4
 
 
 @pytest.mark.parametrize("kind", ["docs", "window", "docs+window", "block"])
 @pytest.mark.parametrize("B,S,H,Hkv", [(2, 512, 4, 2), (1, 1024, 4, 1)])
-def test_attention_range_masks(ops, kind, B, S, H, Hkv):
+def test_attention_range_masks(ops, kind, B, S, H, Hkv, bwd_form):
     """Document / sliding-window / fixed-block causal masks through the flash kernel vs an fp32 masked reference."""
     from torchtitan_b200.ops import reference as ref
 

@@ -659,6 +659,367 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   if (warp == 1) { tt::tc_fence_after(); tt::tmem_dealloc(tmem, 512); }
 }
 
+// =================================================================================== backward: fused dK, dV and dQ
+// One pass over the (key tile, query tile) pairs instead of two: the CTA of a key tile also forms that pair's share of
+// dQ, so S^T and dP^T are computed once per pair (5 MMAs per pair instead of 4 + 3 in the two-kernel form above).
+//   dQ^T[d, q] = K^T[d, keys] * dS^T[keys, q]      (A = the K tile read MN-major, B = the dS^T tile read MN-major)
+// lands in TMEM with the head dimension on the lanes. Four drain warps move it through a 16 KB shared-memory staging
+// tile ([32 queries][128 d] fp32, two halves per step) and add it to the fp32 dQ accumulator in global memory with bulk
+// reduce-add copies (cp.reduce.async.bulk ... add.f32, one 512-byte row per copy): the memory system adds whole lines,
+// which per-element atomics do far slower. The sum over key tiles is formed by those additions, in no fixed order: the
+// low bits of dQ differ from run to run (the two-kernel form stays available for deterministic runs). A small kernel
+// converts the accumulator to bf16 afterwards.
+// S^T / dP^T are single-buffered in TMEM but released as soon as the softmax warps hold them in registers, so the
+// MMAs of step st + 1 start while step st is still in the softmax. P^T is single-buffered in shared memory (its MMA,
+// dV, is the first of a step's second group and frees it early); dS^T is double-buffered.
+// smem: K 32K | V 32K | Q/dO ring 3 x 32K | P^T 16K | dQ staging 16K | dS^T 2 x 16K | barriers.
+// TMEM columns: S^T 0..63 | dP^T 64..127 | dQ^T 128..191 | dV 256..383 | dK 384..511.
+constexpr int FB_KVFULL = 0, FB_QFULL = 1, FB_QEMPTY = FB_QFULL + K_NS, FB_STFULL = FB_QEMPTY + K_NS,
+              FB_STFREE = FB_STFULL + 1, FB_PTREADY = FB_STFREE + 1, FB_PTFREE = FB_PTREADY + 2,
+              FB_DQFULL = FB_PTFREE + 2, FB_DQFREE = FB_DQFULL + 1, FB_PFREE = FB_DQFREE + 1, FB_COUNT = FB_PFREE + 1;
+constexpr uint32_t K_DQS = K_PT + 16384;   // dQ staging tile (second half of the two-kernel form's P^T double buffer)
+constexpr uint32_t IDESC_128x64_MM = tt::umma_idesc_bf16(128, 64, 1, 1);
+constexpr int FUSED_THREADS = 448;   // TMA, MMA, 8 softmax warps, 4 drain warps
+
+struct FusedExtra {
+  const float* lse2;     // [B,H,Sq] -lse * log2(e)
+  const float* delta_s;  // [B,H,Sq] -delta * scale
+  float* dq_acc;         // [B,Sq,H,D] fp32, zero on entry
+  int dq_mode;           // 0: tiled TMA reduce-add through shared memory; 1: one atomic add per element; 2: dQ dropped (timing aid)
+};
+
+// Tiled reduce-add of a shared-memory box into a 3-D fp32 tensor in global memory (one instruction per box).
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, uint32_t src_smem, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Two fp32 lanes per instruction (sm_100 packed math): halves the issue slots of the softmax arithmetic.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d)
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return *reinterpret_cast<float2*>(&d);
+}
+// 32 atomic adds, one query row apart (QS floats; 0 = the run-time stride): with a compile-time stride the offsets are
+// immediates and no address arithmetic is issued.
+template <int QS>
+__device__ __forceinline__ void red_rows(float* dst, long long qstride, const uint32_t (&r)[32]) {
+#pragma unroll
+  for (int c = 0; c < 32; ++c) atomicAdd(dst + c * (QS ? static_cast<long long>(QS) : qstride), __uint_as_float(r[c]));
+}
+
+__global__ void __launch_bounds__(FUSED_THREADS, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
+                      const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                      const __grid_constant__ CUtensorMap tdq, AttnArgs p, FusedExtra x) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t bar0 = base + K_BAR;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + K_BAR + 8 * FB_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + K_BAR + 8 * FB_COUNT + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the KV head is the fastest block index: under a causal mask the blocks run from the heaviest key tile (all
+  // queries) to the lightest, over all heads, so the SMs finish close together
+  const int hk = blockIdx.x, kt = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int kv0 = kt * 128;
+  const int off = p.Sk - p.Sq;
+  const int nq_tiles = p.Sq / 64;
+  int qt_first = 0;
+  if (p.causal) { const int first_q = kv0 - off; qt_first = first_q > 0 ? first_q / 64 : 0; }
+  int qt_end = nq_tiles;
+  if (p.col_hi) qt_end = min(nq_tiles, __ldg(p.col_hi + static_cast<long long>(b) * p.Sk + kv0 + 127) / 64 + 1);
+  const int per_head = qt_end > qt_first ? qt_end - qt_first : 0;
+  const int n_steps = per_head * G;
+  // step st <-> (query head h, query tile qt): every role walks the same sequence with counters (no divisions)
+  int h = hk * G, qt = qt_first;
+  auto next_step = [&]() { if (++qt == qt_end) { qt = qt_first; ++h; } };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < FB_COUNT; ++i) {
+      uint32_t cnt = 1;
+      if (i == FB_STFREE || (i >= FB_PTREADY && i < FB_PTFREE)) cnt = 8;   // one arrival per softmax warp
+      if (i == FB_DQFREE) cnt = 4;                                         // one per drain warp
+      tt::mbar_init(bar(i), cnt);
+    }
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+  }
+  if (warp == 1) { tt::tmem_alloc(tt::smem_u32(tmem_slot), 512); tt::tmem_relinquish(); }
+  tt::tc_fence_before();
+  __syncthreads();
+  tt::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tST = tmem, tDPT = tmem + 64, tDQT = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
+
+  if (warp == 0) {
+    if (tt::elect_one()) {
+      tt::mbar_expect_tx(bar(FB_KVFULL), 65536);
+      tt::tma_load_3d(base + K_K, &tk, bar(FB_KVFULL), 0, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_K + 16384, &tk, bar(FB_KVFULL), 64, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_V, &tv, bar(FB_KVFULL), 0, hk, b * p.Sk + kv0);
+      tt::tma_load_3d(base + K_V + 16384, &tv, bar(FB_KVFULL), 64, hk, b * p.Sk + kv0);
+      for (int st = 0; st < n_steps; ++st, next_step()) {
+        const int s = st % K_NS; const uint32_t ph = (st / K_NS) & 1;
+        if (!tt::mbar_wait(bar(FB_QEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 41)) break;
+        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
+        tt::mbar_expect_tx(bar(FB_QFULL + s), 32768);
+        tt::tma_load_3d(qb, &tq, bar(FB_QFULL + s), 0, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(qb + 8192, &tq, bar(FB_QFULL + s), 64, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(dob, &tdo, bar(FB_QFULL + s), 0, h, b * p.Sq + qt * 64);
+        tt::tma_load_3d(dob + 8192, &tdo, bar(FB_QFULL + s), 64, h, b * p.Sq + qt * 64);
+      }
+    }
+  } else if (warp == 1) {
+    if (tt::elect_one()) {
+      bool ok = tt::mbar_wait(bar(FB_KVFULL), 0, abort_flag, &g_attn_error, 42);
+      // S^T and dP^T of step st; the TMEM buffers must have been read out by the softmax warps of step st - 1
+      auto issue_st = [&](int st) -> bool {
+        const int s = st % K_NS;
+        if (!tt::mbar_wait(bar(FB_QFULL + s), (st / K_NS) & 1, abort_flag, &g_attn_error, 43)) return false;
+        if (st > 0 && !tt::mbar_wait(bar(FB_STFREE), (st - 1) & 1, abort_flag, &g_attn_error, 44)) return false;
+        tt::tc_fence_after();
+        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tST, desc_kmajor_dh(base + K_K, 128, kk), desc_kmajor_dh(qb, 64, kk), IDESC_128x64_KK, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tDPT, desc_kmajor_dh(base + K_V, 128, kk), desc_kmajor_dh(dob, 64, kk), IDESC_128x64_KK, kk != 0);
+        tt::umma_commit(bar(FB_STFULL));
+        return true;
+      };
+      if (ok && n_steps > 0) ok = issue_st(0);
+      for (int st = 0; st < n_steps && ok; ++st) {
+        if (st + 1 < n_steps && !issue_st(st + 1)) break;
+        const int s = st % K_NS, t2 = st & 1;
+        if (!tt::mbar_wait(bar(FB_PTREADY + t2), (st >> 1) & 1, abort_flag, &g_attn_error, 45)) break;
+        if (st > 0 && !tt::mbar_wait(bar(FB_DQFREE), (st - 1) & 1, abort_flag, &g_attn_error, 46)) break;
+        tt::tc_fence_after();
+        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
+        const uint32_t ptb = base + K_PT, dstb = base + K_DST + t2 * 16384;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tt::umma_f16_ss(tDV, desc_kmajor_64(ptb, kk), desc_mnmajor(dob, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+        tt::umma_commit(bar(FB_PFREE));         // P^T buffer free for the next step's softmax
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tt::umma_f16_ss(tDK, desc_kmajor_64(dstb, kk), desc_mnmajor(qb, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tt::umma_f16_ss(tDQT, desc_mnmajor(base + K_K, 128, kk), desc_mnmajor(dstb, 128, kk), IDESC_128x64_MM, kk != 0);
+        tt::umma_commit(bar(FB_DQFULL));        // dQ^T of this step complete
+        tt::umma_commit(bar(FB_PTFREE + t2));   // dS^T buffer free
+        tt::umma_commit(bar(FB_QEMPTY + s));    // Q / dO stage free
+      }
+    }
+  } else if (warp < 10) {
+    // 8 softmax warps: lane group = warp & 3 (key row), column half = (warp - 2) >> 2 (32 queries each)
+    const int lg = warp & 3, row = lg * 32 + lane, half = (warp - 2) >> 2;
+    const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+    const int ki = kv0 + row;
+    const float sc = p.scale * kLog2e;
+    const int hi = p.col_hi ? __ldg(p.col_hi + static_cast<long long>(b) * p.Sk + ki) : 0x7fffffff;
+    bool ok = true;
+    const float2 sc2 = make_float2(sc, sc), scale2 = make_float2(p.scale, p.scale);
+    for (int st = 0; st < n_steps; ++st, next_step()) {
+      const int t2 = st & 1;
+      const int qbase = qt * 64 + half * 32;
+      const float* lse_g = x.lse2 + (static_cast<long long>(b) * p.H + h) * p.Sq + qbase;
+      const float* dl_g = x.delta_s + (static_cast<long long>(b) * p.H + h) * p.Sq + qbase;
+      if (!tt::mbar_wait(bar(FB_STFULL), st & 1, abort_flag, &g_attn_error, 47)) { ok = false; break; }
+      tt::tc_fence_after();
+      uint32_t rs[32], rp[32];
+      tt::tmem_ld_32x32(tST + lane_off + half * 32, rs);
+      tt::tmem_ld_32x32(tDPT + lane_off + half * 32, rp);
+      tt::tc_wait_ld();
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(bar(FB_STFREE));      // the next step's S^T / dP^T may overwrite TMEM now
+      // only tiles that touch the diagonal (or a range bound) need per-element masks: two versions of the loop
+      const bool masked = (p.causal && kv0 + 127 > qt * 64 + off) || p.col_hi != nullptr;
+      uint32_t pp[16], dd[16];   // packed bf16 pairs: P^T and dS^T of this thread's 32 queries
+      if (!masked) {
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_g) + e4);   // -lse * log2(e)
+          const float4 d4 = __ldg(reinterpret_cast<const float4*>(dl_g) + e4);    // -delta * scale
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int e = e4 * 4 + 2 * u;
+            const float2 xx = ffma2(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), sc2,
+                                    u ? make_float2(l4.z, l4.w) : make_float2(l4.x, l4.y));
+            const float2 pr = make_float2(fast_exp2(xx.x), fast_exp2(xx.y));
+            const float2 tt2 = ffma2(make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1])), scale2,
+                                     u ? make_float2(d4.z, d4.w) : make_float2(d4.x, d4.y));
+            const float2 ds = fmul2(pr, tt2);
+            pp[2 * e4 + u] = tt::pack_bf16(pr.x, pr.y);
+            dd[2 * e4 + u] = tt::pack_bf16(ds.x, ds.y);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_g) + e4);
+          const float4 d4 = __ldg(reinterpret_cast<const float4*>(dl_g) + e4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pr[4], ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e4 * 4 + u;
+            pr[u] = fast_exp2(fmaf(__uint_as_float(rs[e]), sc, ls[u]));
+            if ((p.causal && ki > qbase + e + off) || qbase + e > hi) pr[u] = 0.f;
+            ds[u] = pr[u] * fmaf(__uint_as_float(rp[e]), p.scale, dl[u]);
+          }
+          pp[2 * e4] = tt::pack_bf16(pr[0], pr[1]); pp[2 * e4 + 1] = tt::pack_bf16(pr[2], pr[3]);
+          dd[2 * e4] = tt::pack_bf16(ds[0], ds[1]); dd[2 * e4 + 1] = tt::pack_bf16(ds[2], ds[3]);
+        }
+      }
+      if (st >= 1 && !tt::mbar_wait(bar(FB_PFREE), (st - 1) & 1, abort_flag, &g_attn_error, 51)) { ok = false; break; }
+      if (st >= 2 && !tt::mbar_wait(bar(FB_PTFREE + t2), ((st - 2) >> 1) & 1, abort_flag, &g_attn_error, 48)) { ok = false; break; }
+      {
+        uint8_t* prow = gbase + K_PT + row * 128;
+        uint8_t* drow = gbase + K_DST + t2 * 16384 + row * 128;
+        const int xr = row & 7;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int chunk = ((half * 4 + c) ^ xr) << 4;
+          *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+          *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+        }
+      }
+      tt::fence_proxy_async();
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(bar(FB_PTREADY + t2));
+    }
+    if (ok && n_steps > 0) ok = tt::mbar_wait(bar(FB_PTFREE + ((n_steps - 1) & 1)), ((n_steps - 1) >> 1) & 1, abort_flag, &g_attn_error, 49);
+    tt::tc_fence_after();
+    if (ok) {
+      const long long o = ((static_cast<long long>(b) * p.Sk + ki) * p.Hkv + hk) * D;
+      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.out2) + o;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dstp = which ? dk : dv;
+        const uint32_t t = which ? tDK : tDV;
+#pragma unroll 1
+        for (int c = half * 2; c < half * 2 + 2; ++c) {
+          uint32_t r[32];
+          if (n_steps > 0) { tt::tmem_ld_32x32(t + lane_off + c * 32, r); tt::tc_wait_ld(); }
+          else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = 0;
+          }
+          store_out_32(dstp + c * 32, r);
+        }
+      }
+    }
+    tt::tc_fence_before();
+  } else {
+    // 4 drain warps: lane = head-dim index d of dQ^T; add this step's [64 queries x 128 d] to the fp32 accumulator
+    const int lg = warp & 3, d = lg * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
+    float* stage = reinterpret_cast<float*>(gbase + K_DQS);
+    const uint32_t stage_u32 = base + K_DQS;
+    const long long qstride = static_cast<long long>(p.H) * D;
+    const bool issuer = (warp == 10) && lane == 0;   // issues (and tracks) the tiled reduce copies
+    for (int st = 0; st < n_steps; ++st, next_step()) {
+      if (!tt::mbar_wait(bar(FB_DQFULL), st & 1, abort_flag, &g_attn_error, 50)) break;
+      tt::tc_fence_after();
+      float* dst0 = x.dq_acc + ((static_cast<long long>(b) * p.Sq + qt * 64) * p.H + h) * D + d;
+#pragma unroll 1
+      for (int hq = 0; hq < 2; ++hq) {
+        uint32_t r[32];
+        tt::tmem_ld_32x32(tDQT + lane_off + hq * 32, r);
+        tt::tc_wait_ld();
+        if (hq == 1) {
+          tt::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tt::mbar_arrive(bar(FB_DQFREE));   // dQ^T is in registers: the next step's MMA may overwrite it
+        }
+        if (x.dq_mode == 0) {
+          if (issuer) tt::bulk_store_wait_read<0>();         // the previous half's copy has read the staging tile
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < 32; ++c) stage[c * D + d] = __uint_as_float(r[c]);
+          tt::fence_proxy_async();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (issuer) {
+            tma_reduce_add_3d(&tdq, stage_u32, 0, h, b * p.Sq + qt * 64 + hq * 32);
+            tt::tma_store_commit();
+          }
+        } else if (x.dq_mode == 1) {
+          float* dst = dst0 + hq * 32 * qstride;
+          if (p.H == 32) red_rows<32 * D>(dst, qstride, r);
+          else if (p.H == 16) red_rows<16 * D>(dst, qstride, r);
+          else if (p.H == 64) red_rows<64 * D>(dst, qstride, r);
+          else red_rows<0>(dst, qstride, r);
+        }
+      }
+    }
+    if (issuer) tt::bulk_store_wait_all();                  // all additions have been performed before the kernel ends
+    tt::tc_fence_before();
+  }
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  if (warp == 1) { tt::tc_fence_after(); tt::tmem_dealloc(tmem, 512); }
+}
+
+// -delta[b,h,s] * scale (delta = sum_d dO * O) and -lse * log2(e): the addends of the fused backward's two FMAs
+__global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                 const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta_s,
+                                 float scale, int B, int S, int H) {
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x / 16) + threadIdx.x / 16;  // (b,s,h)
+  const int l16 = threadIdx.x & 15;
+  const long long rows = static_cast<long long>(B) * S * H;
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + l16 * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dout + row * D + l16 * 8);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 xx = __bfloat1622float2(ah[i]), y = __bfloat1622float2(ch[i]);
+      acc += xx.x * y.x + xx.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o2 = 8; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (row < rows && l16 == 0) {
+    const int hh = static_cast<int>(row % H);
+    const long long bs = row / H;
+    const int s = static_cast<int>(bs % S);
+    const long long bb = bs / S;
+    const long long i = (bb * H + hh) * S + s;
+    delta_s[i] = -acc * scale;
+    lse2[i] = -lse[i] * kLog2e;
+  }
+}
+
+// fp32 dQ accumulator -> bf16
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long n8) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(acc)[2 * i], c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+    uint4 v;
+    v.x = tt::pack_bf16(a.x, a.y); v.y = tt::pack_bf16(a.z, a.w);
+    v.z = tt::pack_bf16(c.x, c.y); v.w = tt::pack_bf16(c.z, c.w);
+    reinterpret_cast<uint4*>(dq)[i] = v;
+  }
+}
+
 // delta[b,h,s] = sum_d dO * O
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                   float* __restrict__ delta, int B, int S, int H) {
@@ -703,11 +1064,13 @@ int make_map(CUtensorMap* m, const void* ptr, long long rows, int heads, int box
 }
 
 bool g_attr_set = false;
+int g_dq_mode = 0;
 void set_attrs() {
   if (g_attr_set) return;
   cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FWD_SMEM));
   cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DQ_SMEM));
   cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DKV_SMEM));
+  cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DKV_SMEM));
   g_attr_set = true;
 }
 
@@ -798,6 +1161,53 @@ int tt_attn_bwd_range(const void* q, const void* k, const void* v, const void* o
   attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 320, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
   AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta, row_lo, col_hi, nullptr};
   attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 320, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Debug / measurement knob: how the fused backward adds dQ (see FusedExtra::dq_mode). Mode 2 drops dQ.
+void tt_attn_set_dq_mode(int mode) { g_dq_mode = mode; }
+
+// Fused backward (see attn_bwd_fused_kernel). scratch: fp32 [2 * B*H*Sq] (written here); dq_acc: fp32 [B,Sq,H,D] that the
+// caller has zeroed (on the same stream). dQ's low bits are not reproducible from run to run.
+int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                      float* scratch, float* dq_acc, void* dq, void* dk, void* dv, const int* row_lo, const int* col_hi,
+                      int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal, float scale, cudaStream_t st) {
+  int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
+  if (rc) return rc;
+  if ((row_lo != nullptr) != (col_hi != nullptr)) return -14;
+  if (row_lo && Sq != Sk) return -13;
+  set_attrs();
+  const long long rows = static_cast<long long>(B) * Sq * H;
+  float* lse2 = scratch;
+  float* delta_s = scratch + rows;
+  attn_prep_kernel<<<static_cast<unsigned>((rows + 15) / 16), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, lse2, delta_s, scale, B, Sq, H);
+  CUtensorMap tq64, tdo64, tk128, tv128;
+  if ((rc = make_map(&tq64, q, static_cast<long long>(B) * Sq, H, 64))) return rc;
+  if ((rc = make_map(&tdo64, dout, static_cast<long long>(B) * Sq, H, 64))) return rc;
+  if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
+  if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
+  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), nullptr, row_lo, col_hi, nullptr};
+  FusedExtra x{lse2, delta_s, dq_acc, g_dq_mode};
+  // the fp32 dQ accumulator as a 3-D tensor (d, head, row); box = (128, 1, 32) fp32 rows, no swizzle
+  CUtensorMap tdq;
+  {
+    tt::EncodeTiledFn fn = tt::encode_tiled_fn();
+    if (!fn) return -1;
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B) * Sq};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 4, static_cast<cuuint64_t>(H) * D * 4};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(D), 1, 32};
+    cuuint32_t es[3] = {1, 1, 1};
+    CUresult r = fn(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -static_cast<int>(r) - 1000;
+  }
+  attn_bwd_fused_kernel<<<dim3(Hkv, Sk / 128, B), FUSED_THREADS, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, tdq, pk, x);
+  const long long n8 = rows * D / 8;
+  long long cblocks = (n8 + 255) / 256;
+  if (cblocks > 148 * 16) cblocks = 148 * 16;
+  attn_dq_convert_kernel<<<static_cast<unsigned>(cblocks), 256, 0, st>>>(
+      dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -439,6 +439,16 @@ int tt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   if (D % 8) return -1;
   const int grid = tt_rmsnorm_bwd_blocks(rows, D);
   const size_t sm = (32 + D) * sizeof(float);
+  if (sm > 227 * 1024) return -5;       // D above ~58k: the per-block dW row no longer fits in shared memory
+  if (sm > 48 * 1024) {
+    // rows wider than 12256 elements (e.g. dim 16384) need the opt-in shared-memory limit
+    static bool opted_in = false;
+    if (!opted_in) {
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<__nv_bfloat16, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      cudaFuncSetAttribute(rmsnorm_bwd_kernel<float, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      opted_in = true;
+    }
+  }
   if (D <= 1024) {
     if (dtype == 0) rmsnorm_bwd_kernel<__nv_bfloat16, 32><<<grid, 256, sm, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx, scratch, rows, D);
     else rmsnorm_bwd_kernel<float, 32><<<grid, 256, sm, st>>>((const float*)dy, (const float*)x, (const float*)w, rstd, (float*)dx, scratch, rows, D);

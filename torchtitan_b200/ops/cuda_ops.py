@@ -310,12 +310,32 @@ def _(q, k, v, causal, scale, row_lo=None, sinks=None):
     return torch.empty_like(q), q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32)
 
 
+# None: the fused backward kernel unless deterministic algorithms are requested; True / False force one form (tests)
+ATTN_BWD_FUSED: bool | None = None
+
+
+def _attn_bwd_fused() -> bool:
+    if ATTN_BWD_FUSED is not None:
+        return bool(ATTN_BWD_FUSED) and native.has("tt_attn_bwd_fused")
+    return native.has("tt_attn_bwd_fused") and not torch.are_deterministic_algorithms_enabled()
+
+
 @torch.library.custom_op("tt_b200::attention_bwd", mutates_args=())
 def attention_bwd(q: Tensor, k: Tensor, v: Tensor, o: Tensor, do: Tensor, lse: Tensor, causal: bool, scale: float,
                   row_lo: Tensor | None = None, col_hi: Tensor | None = None) -> tuple[Tensor, Tensor, Tensor]:
+    """Two forms: one fused kernel per key tile that also adds its share of dQ into an fp32 accumulator (default: fastest,
+    dQ not bitwise reproducible), or separate dK/dV and dQ kernels without atomics (``torch.use_deterministic_algorithms``)."""
     B, Sq, H, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if _attn_bwd_fused():
+        scratch = torch.empty((2, B, H, Sq), dtype=torch.float32, device=q.device)
+        dq_acc = torch.zeros((B, Sq, H, D), dtype=torch.float32, device=q.device)
+        _ck(_lib().tt_attn_bwd_fused(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                     scratch.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                     _p(row_lo), _p(col_hi), B, Sq, Sk, H, Hkv, D, int(causal), scale, _stream()),
+            "tt_attn_bwd_fused")
+        return dq, dk, dv
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
     _ck(_lib().tt_attn_bwd_range(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                                  delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _p(row_lo), _p(col_hi), B, Sq,

@@ -583,6 +583,9 @@ class FSDPUnit:
             first = next((p for p in self.params if p.param.requires_grad), None)
             self._slot_accumulate = first is not None and first.param.grad is not None
             self._slot_written = [False] * len(self.params)
+            guard = getattr(self.comm, "before_grad_writes", None)
+            if guard is not None:
+                guard(self)  # peers may still be reading the staging buffer of the previous micro-batch
             self.unshard()
             if self.prev is not None and self.prev.reshard_after_forward and not self.prev._in_backward:
                 self.prev.unshard(async_op=True)

@@ -14,9 +14,16 @@ buffer** in the gathered layout (written directly by the weight-gradient GEMMs t
 
 Cross-rank ordering: a rank publishes ``version`` in its flag after the producing work is
 queued on the same stream; consumers spin (bounded) until all flags reach the version they
-expect. Write-after-read hazards are excluded by the training step itself: a shadow shard is
-only rewritten by the optimizer after every reduce-scatter of the step, which needs every
-peer's backward (hence every peer's gathers) of that step to be done.
+expect. Write-after-read hazards:
+
+* a shadow shard is only rewritten by the optimizer after every reduce-scatter of the step, which
+  needs every peer's backward (hence every peer's gathers) of that step to be done;
+* a staging buffer is rewritten by the next backward of its unit. Across optimizer steps the
+  all-gather flags order that (a peer's next forward needs this rank's optimizer, which follows
+  all of this rank's reduce kernels). Within one optimizer step (gradient accumulation, pipeline
+  micro-batches) nothing else does, so every rank publishes a third flag, "my reduce kernel for
+  version v has read your staging", and :meth:`NvlinkComm.before_grad_writes` (called when a unit
+  enters backward) waits, bounded, for all peers' flags before the first gradient write.
 
 What the reference does for the same step: NCCL all-gather / reduce-scatter with copy-in,
 copy-out and fp32 casts around them (``torch.distributed.fsdp``), see
@@ -170,7 +177,7 @@ class NvlinkComm(ShardComm):
         if st is None:
             h = self.heap
             st = {"shadow_off": None, "staging_off": None, "flag_shadow": h.alloc_flag(), "flag_grad": h.alloc_flag(),
-                  "gather_version": 0, "grad_version": 0, "segs": None}
+                  "flag_done": h.alloc_flag(), "gather_version": 0, "grad_version": 0, "rs_params_version": None, "segs": None}
             self._units[id(unit)] = st
         return st
 
@@ -246,10 +253,29 @@ class NvlinkComm(ShardComm):
             out, acc = torch.empty_like(unit.grad_shard_flat), False
         native.check(L.tt_reduce_scatter_pull(ptrs, flags, st["segs"].data_ptr(), len(unit.params), out.data_ptr(), self.world,
                                               self.rank, version, int(acc), 64, _stream()), "tt_reduce_scatter_pull")
+        # "read done": the peers' staging buffers of this version may be overwritten from here on
+        native.check(L.tt_set_flag(h.base + st["flag_done"], version, _stream()), "tt_set_flag")
+        st["rs_params_version"] = unit.params_version
         if unit.replicate_group is not None:
             dist.all_reduce(out, group=unit.replicate_group)
             if out is not unit.grad_shard_flat:
                 unit.grad_shard_flat.add_(out)
+
+    def needs_staging_wait(self, unit: FSDPUnit) -> bool:
+        """True when this unit's staging buffer was reduced since the last optimizer step: a peer may still be reading it."""
+        st = self._units.get(id(unit))
+        return (st is not None and st.get("staging") is not None and st["grad_version"] > 0
+                and st["rs_params_version"] == unit.params_version)
+
+    def before_grad_writes(self, unit: FSDPUnit) -> None:
+        """Called on the compute stream when ``unit`` enters backward, before any weight-gradient GEMM writes staging.
+        Waits (bounded, error word on expiry) until every peer's reduce kernel of the previous micro-batch has read this
+        rank's staging buffer. Skipped when an optimizer step lies in between (see the module docstring)."""
+        if not self.needs_staging_wait(unit):
+            return
+        st = self._units[id(unit)]
+        flags, keep = self.heap.peer_ptrs(st["flag_done"])
+        native.check(native.lib().tt_wait_flags(flags, self.world, st["grad_version"], _stream()), "tt_wait_flags")
 
     def errors(self):
         out = (ctypes.c_int * 4)()

@@ -196,10 +196,21 @@ def bench_attention(args, timer):
     o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, True, scale)
     do = torch.randn_like(o)
     ms_f = timer.time(lambda: torch.ops.tt_b200.attention_fwd(q, k, v, True, scale), args.iters)
-    ms_b = timer.time(lambda: torch.ops.tt_b200.attention_bwd(q, k, v, o, do, lse, True, scale), args.iters)
-    res = {"case": "attention_causal", "B": B, "S": S, "H": H, "Hkv": Hkv, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9,
-           "bwd_ms": ms_b, "bwd_tflops_algorithmic(2.5x fwd)": 2.5 * fwd_flops / ms_b / 1e9,
-           "bwd_tflops_executed(3.5x fwd)": 3.5 * fwd_flops / ms_b / 1e9}
+    res = {"case": "attention_causal", "B": B, "S": S, "H": H, "Hkv": Hkv, "fwd_ms": ms_f, "fwd_tflops": fwd_flops / ms_f / 1e9}
+    from torchtitan_b200.ops import native
+
+    # one fused kernel (default; dQ added by bulk reduce copies) / deterministic dK,dV + dQ kernels; with --dq-modes also
+    # the fused kernel with per-element atomics and with dQ dropped (how much of its time the dQ traffic costs)
+    forms = [("fused", True, 0), ("split", False, 0)]
+    if args.dq_modes:
+        forms += [("fused_atomics", True, 1), ("fused_no_dq(timing aid)", True, 2)]
+    for form, fused, mode in forms:
+        cuda_ops.ATTN_BWD_FUSED = fused
+        native.lib().tt_attn_set_dq_mode(mode)
+        ms_b = timer.time(lambda: torch.ops.tt_b200.attention_bwd(q, k, v, o, do, lse, True, scale), args.iters)
+        res.update({f"bwd_{form}_ms": ms_b, f"bwd_{form}_tflops_algorithmic(2.5x fwd)": 2.5 * fwd_flops / ms_b / 1e9})
+    cuda_ops.ATTN_BWD_FUSED = None
+    native.lib().tt_attn_set_dq_mode(0)
     if args.compare:
         qt, kt, vt = (t.detach().transpose(1, 2).requires_grad_() for t in (q, k, v))
         f = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True)
@@ -254,6 +265,7 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--dq-modes", action="store_true", help="attention: also time the fused backward's other dQ modes")
     ap.add_argument("--single-cta", action="store_true", help="gemm: force the single-CTA tile kernel")
     args = ap.parse_args()
     timer = Timer()
