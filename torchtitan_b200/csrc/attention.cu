@@ -181,12 +181,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   } else if (warp == 1) {
     if (tt::elect_one()) {
       bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 13);
+      // descriptors are built once; an operand slice is one 32-bit add away (see tt::SmemDesc)
+      const tt::SmemDesc dQ = tt::make_smem_desc(base + F_Q, 1, 64), dK0 = tt::make_smem_desc(base + F_K, 1, 64);
+      const tt::SmemDesc dP = tt::make_smem_desc(base + F_P, 1, 64), dV = tt::make_smem_desc(base + F_V, (64 * 128) >> 4, 64);
       auto issue_s = [&](int j) {
         const int s = j & 1;
-        const uint32_t kb = base + F_K + s * 16384;
+        const tt::SmemDesc kd = dK0.at(s * 16384);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tS + s * 64, desc_kmajor_dh(base + F_Q, 128, kk), desc_kmajor_dh(kb, 64, kk),
+          tt::umma_f16_ss(tS + s * 64, dQ.at((kk >> 2) * 16384 + (kk & 3) * 32), kd.at((kk >> 2) * 8192 + (kk & 3) * 32),
                           IDESC_128x64_KK, kk != 0);
         tt::umma_commit(bar(9 + s));   // S ready
         tt::umma_commit(bar(3 + s));   // K stage free
@@ -206,11 +209,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         if (!tt::mbar_wait(bar(11), j & 1, abort_flag, &g_attn_error, 16)) break;
         if (!tt::mbar_wait(bar(5), j & 1, abort_flag, &g_attn_error, 17)) break;
         tt::tc_fence_after();
-        const uint32_t vb = base + F_V;
+        const uint32_t acc0 = j != 0;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tO, desc_kmajor_64(base + F_P, kk), desc_mnmajor(vb, 64, kk), IDESC_128x128_KM,
-                          (j | kk) != 0);
+          tt::umma_f16_ss(tO, dP.at(kk * 32), dV.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
         tt::umma_commit(bar(12));      // O updated, P free
         tt::umma_commit(bar(7));       // V buffer free
       }
@@ -678,14 +680,30 @@ constexpr int FB_KVFULL = 0, FB_QFULL = 1, FB_QEMPTY = FB_QFULL + K_NS, FB_STFUL
               FB_STFREE = FB_STFULL + 1, FB_PTREADY = FB_STFREE + 1, FB_PTFREE = FB_PTREADY + 2,
               FB_DQFULL = FB_PTFREE + 2, FB_DQFREE = FB_DQFULL + 1, FB_PFREE = FB_DQFREE + 1, FB_COUNT = FB_PFREE + 1;
 constexpr uint32_t K_DQS = K_PT + 16384;   // dQ staging tile (second half of the two-kernel form's P^T double buffer)
+constexpr uint32_t K_STAT = K_BAR + 256;   // per stage: 64 x (-lse * log2 e) then 64 x (-delta * scale), fp32
+constexpr size_t FUSED_SMEM = DKV_SMEM + K_NS * 512;
 constexpr uint32_t IDESC_128x64_MM = tt::umma_idesc_bf16(128, 64, 1, 1);
 constexpr int FUSED_THREADS = 448;   // TMA, MMA, 8 softmax warps, 4 drain warps
+
+// Optional timeline probe (compiled only with -DTT_ATTN_TRACE): block (0,0,0) records the SM clock at a few points of
+// steps [64, 72) into g_attn_trace[step - 64][slot].
+#ifdef TT_ATTN_TRACE
+__device__ long long g_attn_trace[8][16];
+#define TT_TRACE(st, slot)                                                                                     \
+  do {                                                                                                         \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (st) >= 64 && (st) < 72 && (threadIdx.x & 31) == 0) \
+      g_attn_trace[(st) - 64][slot] = clock64();                                                               \
+  } while (0)
+#else
+#define TT_TRACE(st, slot) do {} while (0)
+#endif
 
 struct FusedExtra {
   const float* lse2;     // [B,H,Sq] -lse * log2(e)
   const float* delta_s;  // [B,H,Sq] -delta * scale
   float* dq_acc;         // [B,Sq,H,D] fp32, zero on entry
   int dq_mode;           // 0: tiled TMA reduce-add through shared memory; 1: one atomic add per element; 2: dQ dropped (timing aid)
+  int a_tmem;            // 1: P^T and dS^T reach the dV / dK MMAs through tensor memory (no shared-memory reads for A)
 };
 
 // Tiled reduce-add of a shared-memory box into a 3-D fp32 tensor in global memory (one instruction per box).
@@ -761,6 +779,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   tt::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tST = tmem, tDPT = tmem + 64, tDQT = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
+  const uint32_t tPT = tmem + 192, tDST = tmem + 224;   // bf16 P^T / dS^T as A operands: 64 queries = 32 columns each
 
   if (warp == 0) {
     if (tt::elect_one()) {
@@ -773,7 +792,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         const int s = st % K_NS; const uint32_t ph = (st / K_NS) & 1;
         if (!tt::mbar_wait(bar(FB_QEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 41)) break;
         const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
-        tt::mbar_expect_tx(bar(FB_QFULL + s), 32768);
+        tt::mbar_expect_tx(bar(FB_QFULL + s), 32768 + 512);
+        {
+          // the 64 queries' softmax statistics ride on the same barrier (plain bulk copies, 256 bytes each)
+          const long long so = (static_cast<long long>(b) * p.H + h) * p.Sq + qt * 64;
+          tt::bulk_load(base + K_STAT + s * 512, x.lse2 + so, 256, bar(FB_QFULL + s));
+          tt::bulk_load(base + K_STAT + s * 512 + 256, x.delta_s + so, 256, bar(FB_QFULL + s));
+        }
         tt::tma_load_3d(qb, &tq, bar(FB_QFULL + s), 0, h, b * p.Sq + qt * 64);
         tt::tma_load_3d(qb + 8192, &tq, bar(FB_QFULL + s), 64, h, b * p.Sq + qt * 64);
         tt::tma_load_3d(dob, &tdo, bar(FB_QFULL + s), 0, h, b * p.Sq + qt * 64);
@@ -783,20 +808,34 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   } else if (warp == 1) {
     if (tt::elect_one()) {
       bool ok = tt::mbar_wait(bar(FB_KVFULL), 0, abort_flag, &g_attn_error, 42);
+      // descriptors are built once; inside the loop an operand slice is one 32-bit add away (see tt::SmemDesc)
+      const tt::SmemDesc dK_km = tt::make_smem_desc(base + K_K, 1, 64), dV_km = tt::make_smem_desc(base + K_V, 1, 64);
+      const tt::SmemDesc dK_mn = tt::make_smem_desc(base + K_K, (128 * 128) >> 4, 64);
+      const tt::SmemDesc dQ_km0 = tt::make_smem_desc(base + K_QDO, 1, 64);              // stage 0: Q; dO is 16 KB further
+      const tt::SmemDesc dQ_mn0 = tt::make_smem_desc(base + K_QDO, (64 * 128) >> 4, 64);
+      const tt::SmemDesc dPT_km = tt::make_smem_desc(base + K_PT, 1, 64);
+      const tt::SmemDesc dDS_km0 = tt::make_smem_desc(base + K_DST, 1, 64);
+      const tt::SmemDesc dDS_mn0 = tt::make_smem_desc(base + K_DST, (128 * 128) >> 4, 64);
       // S^T and dP^T of step st; the TMEM buffers must have been read out by the softmax warps of step st - 1
       auto issue_st = [&](int st) -> bool {
         const int s = st % K_NS;
         if (!tt::mbar_wait(bar(FB_QFULL + s), (st / K_NS) & 1, abort_flag, &g_attn_error, 43)) return false;
         if (st > 0 && !tt::mbar_wait(bar(FB_STFREE), (st - 1) & 1, abort_flag, &g_attn_error, 44)) return false;
         tt::tc_fence_after();
-        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
+        TT_TRACE(st, 0);   // S^T / dP^T issue begins
+        const tt::SmemDesc q = dQ_km0.at(s * 32768), dO = q.at(16384);
+        // K-major operands with two 64-wide halves of the head dimension: slice kk starts at
+        // (kk >> 2) * rows * 128 + (kk & 3) * 32 bytes (rows = 128 for K / V, 64 for Q / dO)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tST, desc_kmajor_dh(base + K_K, 128, kk), desc_kmajor_dh(qb, 64, kk), IDESC_128x64_KK, kk != 0);
+          tt::umma_f16_ss(tST, dK_km.at((kk >> 2) * 16384 + (kk & 3) * 32), q.at((kk >> 2) * 8192 + (kk & 3) * 32),
+                          IDESC_128x64_KK, kk != 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tDPT, desc_kmajor_dh(base + K_V, 128, kk), desc_kmajor_dh(dob, 64, kk), IDESC_128x64_KK, kk != 0);
+          tt::umma_f16_ss(tDPT, dV_km.at((kk >> 2) * 16384 + (kk & 3) * 32), dO.at((kk >> 2) * 8192 + (kk & 3) * 32),
+                          IDESC_128x64_KK, kk != 0);
         tt::umma_commit(bar(FB_STFULL));
+        TT_TRACE(st, 1);   // S^T / dP^T issued
         return true;
       };
       if (ok && n_steps > 0) ok = issue_st(0);
@@ -804,23 +843,39 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         if (st + 1 < n_steps && !issue_st(st + 1)) break;
         const int s = st % K_NS, t2 = st & 1;
         if (!tt::mbar_wait(bar(FB_PTREADY + t2), (st >> 1) & 1, abort_flag, &g_attn_error, 45)) break;
+        tt::tc_fence_after();
+        TT_TRACE(st, 2);   // P^T / dS^T seen ready
+        const tt::SmemDesc q_mn = dQ_mn0.at(s * 32768), dO_mn = q_mn.at(16384);
+        const tt::SmemDesc ds_km = dDS_km0.at(t2 * 16384), ds_mn = dDS_mn0.at(t2 * 16384);
+        const uint32_t acc0 = st != 0;
+        if (x.a_tmem) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tt::umma_f16_ts(tDV, tPT + kk * 8, dO_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tt::umma_f16_ts(tDK, tDST + kk * 8, q_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+          tt::umma_commit(bar(FB_PFREE));       // P^T and dS^T (tensor memory) free for the next step's softmax
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tt::umma_f16_ss(tDV, dPT_km.at(kk * 32), dO_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+          tt::umma_commit(bar(FB_PFREE));       // P^T buffer free for the next step's softmax
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            tt::umma_f16_ss(tDK, ds_km.at(kk * 32), q_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+        }
+        // dQ^T overwrites what the drain warps read for the previous step: wait for them as late as possible
         if (st > 0 && !tt::mbar_wait(bar(FB_DQFREE), (st - 1) & 1, abort_flag, &g_attn_error, 46)) break;
         tt::tc_fence_after();
-        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
-        const uint32_t ptb = base + K_PT, dstb = base + K_DST + t2 * 16384;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tDV, desc_kmajor_64(ptb, kk), desc_mnmajor(dob, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
-        tt::umma_commit(bar(FB_PFREE));         // P^T buffer free for the next step's softmax
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tDK, desc_kmajor_64(dstb, kk), desc_mnmajor(qb, 64, kk), IDESC_128x128_KM, (st | kk) != 0);
+        TT_TRACE(st, 3);   // dQ^T buffer seen free
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tDQT, desc_mnmajor(base + K_K, 128, kk), desc_mnmajor(dstb, 128, kk), IDESC_128x64_MM, kk != 0);
+          tt::umma_f16_ss(tDQT, dK_mn.at(kk * 2048), ds_mn.at(kk * 2048), IDESC_128x64_MM, kk != 0);
         tt::umma_commit(bar(FB_DQFULL));        // dQ^T of this step complete
         tt::umma_commit(bar(FB_PTFREE + t2));   // dS^T buffer free
         tt::umma_commit(bar(FB_QEMPTY + s));    // Q / dO stage free
+        TT_TRACE(st, 4);   // second group issued
       }
     }
   } else if (warp < 10) {
@@ -835,10 +890,16 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
     for (int st = 0; st < n_steps; ++st, next_step()) {
       const int t2 = st & 1;
       const int qbase = qt * 64 + half * 32;
-      const float* lse_g = x.lse2 + (static_cast<long long>(b) * p.H + h) * p.Sq + qbase;
-      const float* dl_g = x.delta_s + (static_cast<long long>(b) * p.H + h) * p.Sq + qbase;
+      // statistics of this step's queries: staged by the producer next to Q / dO (visible once S^T is: the MMA
+      // warp waited for the stage's barrier before it issued S^T)
+      const float4* lse_s = reinterpret_cast<const float4*>(gbase + K_STAT + (st % K_NS) * 512) + half * 8;
+      const float4* dl_s = lse_s + 16;
       if (!tt::mbar_wait(bar(FB_STFULL), st & 1, abort_flag, &g_attn_error, 47)) { ok = false; break; }
+      // the stage's own barrier completed before S^T was issued: this wait returns at once and orders the reads of
+      // the bulk-copied statistics after the copies
+      if (!tt::mbar_wait(bar(FB_QFULL + st % K_NS), (st / K_NS) & 1, abort_flag, &g_attn_error, 52)) { ok = false; break; }
       tt::tc_fence_after();
+      if (warp == 2) TT_TRACE(st, 5);   // S^T seen complete
       uint32_t rs[32], rp[32];
       tt::tmem_ld_32x32(tST + lane_off + half * 32, rs);
       tt::tmem_ld_32x32(tDPT + lane_off + half * 32, rp);
@@ -846,14 +907,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive(bar(FB_STFREE));      // the next step's S^T / dP^T may overwrite TMEM now
+      if (warp == 2) TT_TRACE(st, 6);   // TMEM read out
       // only tiles that touch the diagonal (or a range bound) need per-element masks: two versions of the loop
       const bool masked = (p.causal && kv0 + 127 > qt * 64 + off) || p.col_hi != nullptr;
       uint32_t pp[16], dd[16];   // packed bf16 pairs: P^T and dS^T of this thread's 32 queries
       if (!masked) {
 #pragma unroll
         for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_g) + e4);   // -lse * log2(e)
-          const float4 d4 = __ldg(reinterpret_cast<const float4*>(dl_g) + e4);    // -delta * scale
+          const float4 l4 = lse_s[e4];   // -lse * log2(e)
+          const float4 d4 = dl_s[e4];    // -delta * scale
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int e = e4 * 4 + 2 * u;
@@ -870,8 +932,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
       } else {
 #pragma unroll
         for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse_g) + e4);
-          const float4 d4 = __ldg(reinterpret_cast<const float4*>(dl_g) + e4);
+          const float4 l4 = lse_s[e4];
+          const float4 d4 = dl_s[e4];
           const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
           float pr[4], ds[4];
 #pragma unroll
@@ -885,23 +947,31 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
           dd[2 * e4] = tt::pack_bf16(ds[0], ds[1]); dd[2 * e4 + 1] = tt::pack_bf16(ds[2], ds[3]);
         }
       }
+      if (warp == 2) TT_TRACE(st, 7);   // arithmetic done
       if (st >= 1 && !tt::mbar_wait(bar(FB_PFREE), (st - 1) & 1, abort_flag, &g_attn_error, 51)) { ok = false; break; }
       if (st >= 2 && !tt::mbar_wait(bar(FB_PTFREE + t2), ((st - 2) >> 1) & 1, abort_flag, &g_attn_error, 48)) { ok = false; break; }
       {
         uint8_t* prow = gbase + K_PT + row * 128;
         uint8_t* drow = gbase + K_DST + t2 * 16384 + row * 128;
         const int xr = row & 7;
+        if (x.a_tmem) {
+          // A operands of dV / dK straight into tensor memory: this thread's key row = its lane, 32 queries = 16 columns
+          tt::tmem_st_32x16(tPT + lane_off + half * 16, pp);
+          tt::tmem_st_32x16(tDST + lane_off + half * 16, dd);
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int chunk = ((half * 4 + c) ^ xr) << 4;
-          *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
-          *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);
+          if (!x.a_tmem) *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+          *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);   // B operand of dQ^T
         }
+        if (x.a_tmem) tt::tc_wait_st();
       }
       tt::fence_proxy_async();
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive(bar(FB_PTREADY + t2));
+      if (warp == 2) TT_TRACE(st, 8);   // P^T / dS^T published
     }
     if (ok && n_steps > 0) ok = tt::mbar_wait(bar(FB_PTFREE + ((n_steps - 1) & 1)), ((n_steps - 1) >> 1) & 1, abort_flag, &g_attn_error, 49);
     tt::tc_fence_after();
@@ -937,17 +1007,19 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
     for (int st = 0; st < n_steps; ++st, next_step()) {
       if (!tt::mbar_wait(bar(FB_DQFULL), st & 1, abort_flag, &g_attn_error, 50)) break;
       tt::tc_fence_after();
+      if (warp == 10) TT_TRACE(st, 9);   // dQ^T seen complete
       float* dst0 = x.dq_acc + ((static_cast<long long>(b) * p.Sq + qt * 64) * p.H + h) * D + d;
-#pragma unroll 1
+      uint32_t r0[32], r1[32];
+      tt::tmem_ld_32x32(tDQT + lane_off, r0);
+      tt::tmem_ld_32x32(tDQT + lane_off + 32, r1);
+      tt::tc_wait_ld();
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive(bar(FB_DQFREE));       // dQ^T is in registers: the next step's MMA may overwrite it
+      if (warp == 10) TT_TRACE(st, 10);  // dQ^T read out
+#pragma unroll
       for (int hq = 0; hq < 2; ++hq) {
-        uint32_t r[32];
-        tt::tmem_ld_32x32(tDQT + lane_off + hq * 32, r);
-        tt::tc_wait_ld();
-        if (hq == 1) {
-          tt::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) tt::mbar_arrive(bar(FB_DQFREE));   // dQ^T is in registers: the next step's MMA may overwrite it
-        }
+        const uint32_t (&r)[32] = hq ? r1 : r0;
         if (x.dq_mode == 0) {
           if (issuer) tt::bulk_store_wait_read<0>();         // the previous half's copy has read the staging tile
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -967,6 +1039,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
           else red_rows<0>(dst, qstride, r);
         }
       }
+      if (warp == 10) TT_TRACE(st, 11);  // dQ handed to the memory system
     }
     if (issuer) tt::bulk_store_wait_all();                  // all additions have been performed before the kernel ends
     tt::tc_fence_before();
@@ -1065,12 +1138,13 @@ int make_map(CUtensorMap* m, const void* ptr, long long rows, int heads, int box
 
 bool g_attr_set = false;
 int g_dq_mode = 0;
+int g_a_tmem = 1;
 void set_attrs() {
   if (g_attr_set) return;
   cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FWD_SMEM));
   cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DQ_SMEM));
   cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DKV_SMEM));
-  cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DKV_SMEM));
+  cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FUSED_SMEM));
   g_attr_set = true;
 }
 
@@ -1164,8 +1238,9 @@ int tt_attn_bwd_range(const void* q, const void* k, const void* v, const void* o
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-// Debug / measurement knob: how the fused backward adds dQ (see FusedExtra::dq_mode). Mode 2 drops dQ.
-void tt_attn_set_dq_mode(int mode) { g_dq_mode = mode; }
+// Debug / measurement knob: bits 0-1 = how the fused backward adds dQ (see FusedExtra::dq_mode; 2 drops dQ), bit 2 = feed
+// P^T / dS^T to the dV / dK MMAs through tensor memory.
+void tt_attn_set_dq_mode(int mode) { g_dq_mode = mode & 3; g_a_tmem = (mode >> 2) & 1; }
 
 // Fused backward (see attn_bwd_fused_kernel). scratch: fp32 [2 * B*H*Sq] (written here); dq_acc: fp32 [B,Sq,H,D] that the
 // caller has zeroed (on the same stream). dQ's low bits are not reproducible from run to run.
@@ -1188,7 +1263,7 @@ int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o
   if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), nullptr, row_lo, col_hi, nullptr};
-  FusedExtra x{lse2, delta_s, dq_acc, g_dq_mode};
+  FusedExtra x{lse2, delta_s, dq_acc, g_dq_mode, g_a_tmem};
   // the fp32 dQ accumulator as a 3-D tensor (d, head, row); box = (128, 1, 32) fp32 rows, no swizzle
   CUtensorMap tdq;
   {
@@ -1202,7 +1277,7 @@ int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -static_cast<int>(r) - 1000;
   }
-  attn_bwd_fused_kernel<<<dim3(Hkv, Sk / 128, B), FUSED_THREADS, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, tdq, pk, x);
+  attn_bwd_fused_kernel<<<dim3(Hkv, Sk / 128, B), FUSED_THREADS, FUSED_SMEM, st>>>(tq64, tdo64, tk128, tv128, tdq, pk, x);
   const long long n8 = rows * D / 8;
   long long cblocks = (n8 + 255) / 256;
   if (cblocks > 148 * 16) cblocks = 148 * 16;
@@ -1210,6 +1285,10 @@ int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o
       dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+#ifdef TT_ATTN_TRACE
+int tt_attn_trace(long long* out) { return cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 8 * 16) == cudaSuccess ? 0 : -1; }
+#endif
 
 int tt_attn_error() {
   int v = 0, zero = 0;

@@ -247,6 +247,37 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   d |= 2ull << 61;  // SWIZZLE_128B
   return d;
 }
+// A shared-memory descriptor kept as two words: all MMAs of a loop share the high word (offsets, version, swizzle) and
+// differ only in the start address, so advancing to the next operand slice is one 32-bit add of (bytes >> 4) to `lo`
+// instead of rebuilding the 64-bit value in the single issuing thread.
+struct SmemDesc {
+  uint32_t lo, hi;
+  __device__ __forceinline__ SmemDesc at(uint32_t byte_off) const { return SmemDesc{lo + (byte_off >> 4), hi}; }
+};
+__device__ __forceinline__ SmemDesc make_smem_desc(uint32_t smem_addr, uint32_t lbo16, uint32_t sbo16) {
+  const uint64_t d = umma_smem_desc(smem_addr, lbo16, sbo16);
+  return SmemDesc{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
+}
+// D[tmem] (+)= A[smem] * B[smem] with two-word descriptors; `accumulate` is a compile-time 0 / 1 or a run-time flag.
+__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a.lo), "r"(a.hi), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: A is read from tensor memory (row m of A in lane m, two 16-bit elements per 32-bit
+// column, the lower contraction index in the low half), which costs no shared-memory bandwidth.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b.lo), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32-bit instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major) {
   return (1u << 4)      // D format: f32

@@ -101,6 +101,8 @@ def lib():
     if hasattr(L, "tt_attn_bwd_fused"):
         _sig(L.tt_attn_bwd_fused, [P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
         _sig(L.tt_attn_set_dq_mode, [I], None)
+        if os.environ.get("TT_ATTN_BWD_MODE"):      # measurement aid: see tt_attn_set_dq_mode in csrc/attention.cu
+            L.tt_attn_set_dq_mode(int(os.environ["TT_ATTN_BWD_MODE"]))
     if hasattr(L, "tt_gemm_rs_set_interleave"):
         L.tt_gemm_rs_set_interleave.argtypes = [I]
         L.tt_gemm_rs_set_interleave.restype = None

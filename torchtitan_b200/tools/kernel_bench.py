@@ -201,16 +201,16 @@ def bench_attention(args, timer):
 
     # one fused kernel (default; dQ added by bulk reduce copies) / deterministic dK,dV + dQ kernels; with --dq-modes also
     # the fused kernel with per-element atomics and with dQ dropped (how much of its time the dQ traffic costs)
-    forms = [("fused", True, 0), ("split", False, 0)]
+    forms = [("fused", True, 4), ("split", False, 4)]
     if args.dq_modes:
-        forms += [("fused_atomics", True, 1), ("fused_no_dq(timing aid)", True, 2)]
+        forms += [("fused_atomics", True, 5), ("fused_no_dq(timing aid)", True, 6), ("fused_A_from_smem", True, 0)]
     for form, fused, mode in forms:
         cuda_ops.ATTN_BWD_FUSED = fused
         native.lib().tt_attn_set_dq_mode(mode)
         ms_b = timer.time(lambda: torch.ops.tt_b200.attention_bwd(q, k, v, o, do, lse, True, scale), args.iters)
         res.update({f"bwd_{form}_ms": ms_b, f"bwd_{form}_tflops_algorithmic(2.5x fwd)": 2.5 * fwd_flops / ms_b / 1e9})
     cuda_ops.ATTN_BWD_FUSED = None
-    native.lib().tt_attn_set_dq_mode(0)
+    native.lib().tt_attn_set_dq_mode(4)
     if args.compare:
         qt, kt, vt = (t.detach().transpose(1, 2).requires_grad_() for t in (q, k, v))
         f = lambda: torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True)
