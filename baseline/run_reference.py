@@ -1,5 +1,5 @@
 """Runs the unmodified reference (installed under ``baseline/_ref``) on the benchmark config and
-reports the same JSON fields as ``bench.py``. Filled in once the offline install is recorded."""
+reports the same JSON fields as ``bench.py``."""
 
 
 def run(args) -> dict:

@@ -15,7 +15,9 @@ and ``torch.cuda.synchronize()`` and timed with CUDA events, max over ranks:
   * ``e2e``: the public ``Trainer.train_step`` path fed by the data loader's pinned host batches
     (host->device copy every step) plus a device->host read of the loss every step.
 ``--impl reference`` runs the unmodified reference installed under ``baseline/_ref`` on the same
-config and prints the same JSON line with ``"impl": "reference"``.
+config, eager and with its own ``--compile.enable``, and prints the faster build's JSON line with
+``"impl": "reference"`` (``config.compile`` says which). Both arms use the same selective-checkpoint
+policy (every second matmul output kept); ``--sac-mm-policy auto`` keeps all of them when memory allows.
 """
 
 from __future__ import annotations
@@ -89,7 +91,7 @@ def _dist_env():
 
 
 def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, layers: int | None = None,
-                  extra: list[str] | None = None):
+                  extra: list[str] | None = None, sac_mm_policy: str = "every_second"):
     from torchtitan_b200.config.manager import ConfigManager
     from torchtitan_b200.models.llama3 import llama3_configs
 
@@ -100,6 +102,9 @@ def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, lay
         "--module", "llama3", "--config", "llama3_8b_synthetic",
         "--training.steps", str(steps_total), "--metrics.log_freq", "1000000",
         "--dump_folder", "/tmp/tt_b200_bench", "--comm.train_timeout_seconds", "300",
+        # which matmul outputs per-op SAC keeps: "every_second" is the reference's policy (both arms then recompute the
+        # same share of the forward); "all" / "auto" trade memory for less recompute and are labelled in the output
+        "--activation_checkpoint.per_op_sac_mm_policy", sac_mm_policy,
     ]
     if ac_mode:
         args += ["--activation_checkpoint.mode", ac_mode]
@@ -174,10 +179,16 @@ def run_ours(args) -> dict:
     if rank == 0:
         init_logger()
     total_steps = args.warmup + 2 * args.steps + 4
-    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers, args.override)
+    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers, args.override, args.sac_mm_policy)
     dev = trainer.device
     local_bs = trainer.config.training.local_batch_size
-    tokens_per_step = local_bs * SEQ_LEN * world
+    pd = trainer.parallel_dims
+    # a step consumes local_bs sequences per rank of the batch (data-parallel) mesh; ranks of a tensor / context /
+    # pipeline group work on the same sequences
+    batch_degree = pd.dp_replicate * pd.dp_shard
+    tokens_per_step = local_bs * SEQ_LEN * batch_degree
+    dims = [("dp_replicate", pd.dp_replicate), ("fsdp", pd.dp_shard), ("cp", pd.cp), ("tp", pd.tp), ("pp", pd.pp), ("ep", pd.ep)]
+    parallelism = "x".join(f"{n}{d}" for n, d in dims if d > 1) or "single-gpu (fp32 master + bf16 compute copy)"
 
     host_iter = trainer.batch_generator(trainer.dataloader)
 
@@ -241,8 +252,9 @@ def run_ours(args) -> dict:
         "scaling": "weak", "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world), "dtype": "bf16",
         "data": "synthetic uniform tokens (seed 0), random-init weights",
         "config": {
-            "model": "Llama-3.1-8B", "global_batch": local_bs * world, "seq_len": SEQ_LEN,
-            "parallelism": f"fsdp{world}" if world > 1 else "single-gpu (fp32 master + bf16 compute copy)",
+            "model": "Llama-3.1-8B", "global_batch": local_bs * batch_degree, "seq_len": SEQ_LEN,
+            "parallelism": parallelism,
+            "per_op_sac_mm_policy": args.sac_mm_policy,
             "activation_checkpoint": f"{trainer.config.activation_checkpoint.mode}/{trainer.config.activation_checkpoint.selective_ac_option}"
                                      f" (matmul outputs kept: {_sac_mm_policy(trainer)})",
             "optimizer": "AdamW fused over flat shards, grad clip 1.0",
@@ -282,7 +294,11 @@ def main():
     ap.add_argument("--override", type=lambda v: v.split(), default=[], help="extra config flags for experiments as one "
                     "string, e.g. --override='--parallelism.fsdp_reshard_after_forward never' (recorded in the JSON line)")
     ap.add_argument("--layers", type=int, default=None, help="profiling aid: truncate the model (result is not a benchmark)")
-    ap.add_argument("--ref-compile", action="store_true", help="reference arm only: add --compile.enable")
+    ap.add_argument("--ref-compile", action="store_true", help="reference arm only: time the --compile.enable build alone")
+    ap.add_argument("--ref-build", default="both", choices=["both", "eager", "compile"],
+                    help="reference arm only: which build(s) to time; 'both' reports the faster one")
+    ap.add_argument("--sac-mm-policy", default="every_second", choices=["every_second", "all", "auto"],
+                    help="which matmul outputs per-op SAC keeps (every_second = the reference's policy)")
     ap.add_argument("--kernel-table", default=None, help="after the timed regions, run one more step under the PyTorch "
                     "profiler and write the device time per kernel name to this file")
     ap.add_argument("--ac", default=None, help="override activation_checkpoint.mode (selective|full|none)")

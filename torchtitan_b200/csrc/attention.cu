@@ -183,7 +183,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       bool ok = tt::mbar_wait(bar(0), 0, abort_flag, &g_attn_error, 13);
       // descriptors are built once; an operand slice is one 32-bit add away (see tt::SmemDesc)
       const tt::SmemDesc dQ = tt::make_smem_desc(base + F_Q, 1, 64), dK0 = tt::make_smem_desc(base + F_K, 1, 64);
-      const tt::SmemDesc dP = tt::make_smem_desc(base + F_P, 1, 64), dV = tt::make_smem_desc(base + F_V, (64 * 128) >> 4, 64);
+      const tt::SmemDesc dV = tt::make_smem_desc(base + F_V, (64 * 128) >> 4, 64);
       auto issue_s = [&](int j) {
         const int s = j & 1;
         const tt::SmemDesc kd = dK0.at(s * 16384);
@@ -210,9 +210,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         if (!tt::mbar_wait(bar(5), j & 1, abort_flag, &g_attn_error, 17)) break;
         tt::tc_fence_after();
         const uint32_t acc0 = j != 0;
+        // P (bf16) sits in the first 32 columns of the S buffer it was computed from: the A operand comes from tensor
+        // memory, so neither the softmax warps' stores nor this MMA's A reads touch shared memory
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tO, dP.at(kk * 32), dV.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+          tt::umma_f16_ts(tO, tS + s * 64 + kk * 8, dV.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
         tt::umma_commit(bar(12));      // O updated, P free
         tt::umma_commit(bar(7));       // V buffer free
       }
@@ -283,8 +285,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
       for (int e = 0; e < 64; ++e) { x[e] = fast_exp2(x[e] - m_use); sum += x[e]; }
       l += sum;
-      store_row_sw128(gbase + F_P, row, x);
-      tt::fence_proxy_async();
+      {
+        // P as bf16 pairs over this row's S columns (the MMA reads it from there as its A operand)
+        uint32_t pk[16];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) pk[e] = tt::pack_bf16(x[hh * 32 + 2 * e], x[hh * 32 + 2 * e + 1]);
+          tt::tmem_st_32x16(tS + lane_off + s * 64 + hh * 16, pk);
+        }
+        tt::tc_wait_st();
+      }
       tt::tc_fence_before();
       __syncwarp();
       if (lane == 0) tt::mbar_arrive(bar(11));

@@ -343,11 +343,23 @@ __global__ void sum_rows_kernel(const float* __restrict__ v, float* __restrict__
 // ============================================================================ AdamW / norms
 // p,g,m,v fp32 flat; shadow (optional) bf16 copy of the updated parameters.
 // gscale (optional) device scalar multiplying the gradient (folded gradient clipping).
-__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, __nv_bfloat16* __restrict__ shadow, long long n, float lr,
                              float beta1, float beta2, float eps, float wd, float bc1, float bc2_sqrt,
                              int decoupled, const float* __restrict__ gscale) {
   const float gs = gscale ? gscale[0] : 1.f;
+  const float decay = 1.f - lr * wd, omb1 = 1.f - beta1, omb2 = 1.f - beta2, inv_bc2_sqrt = 1.f / bc2_sqrt, step_size = lr / bc1;
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
     if (i + 4 <= n) {
@@ -358,11 +370,13 @@ __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float gr = gg[e] * gs;
-        if (decoupled) pp[e] *= (1.f - lr * wd); else gr += wd * pp[e];
-        mm[e] = mm[e] + (1.f - beta1) * (gr - mm[e]);
-        vq[e] = beta2 * vq[e] + (1.f - beta2) * gr * gr;
-        const float denom = sqrtf(vq[e]) / bc2_sqrt + eps;
-        pp[e] -= (lr / bc1) * (mm[e] / denom);
+        if (decoupled) pp[e] *= decay; else gr += wd * pp[e];
+        mm[e] = fmaf(omb1, gr - mm[e], mm[e]);
+        vq[e] = fmaf(beta2, vq[e], omb2 * gr * gr);
+        // the kernel is bound by memory only while its arithmetic stays short: special-function-unit square root and
+        // reciprocal (about 1e-7 relative error each) instead of the IEEE sequences
+        const float denom = fmaf(sqrt_approx(vq[e]), inv_bc2_sqrt, eps);
+        pp[e] = fmaf(-step_size * mm[e], rcp_approx(denom), pp[e]);
       }
       *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
       *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);

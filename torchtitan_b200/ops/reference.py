@@ -82,10 +82,20 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None,
     # SDPA's is_causal mask is top-left aligned; with Sq != Sk we need the bottom-right alignment
     plain = window is None and doc_ids is None and sinks is None and not return_lse and (not causal or S == Sk)
     if plain:
-        out = F.scaled_dot_product_attention(
-            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-            is_causal=causal, scale=scale, enable_gqa=H != Hkv,
-        )
+        def sdpa():
+            return F.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                is_causal=causal, scale=scale, enable_gqa=H != Hkv,
+            )
+
+        if q.is_cuda and torch.are_deterministic_algorithms_enabled():
+            # the fused library backends add dQ with atomics in backward; the math backend is reproducible bit for bit
+            from torch.nn.attention import SDPBackend, sdpa_kernel
+
+            with sdpa_kernel([SDPBackend.MATH]):
+                out = sdpa()
+        else:
+            out = sdpa()
         return out.transpose(1, 2)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     # the score matrix is materialised: bound it by walking the queries in chunks (recomputed in backward)
