@@ -1,6 +1,8 @@
 """The NVLink peer-memory FSDP transport against the c10d (NCCL) transport on 2 GPUs: same seed, same batches, five
 optimizer steps of two micro-batches each (gradient accumulation exercises the staging buffer's "read done" handshake).
-Losses and the gradient shards of the last step must agree to bf16 / fp32 rounding. Skipped with fewer than two GPUs."""
+The gradient shards of the first step (identical parameters on both sides) must agree to rounding; the losses of all
+steps must agree loosely (Adam turns rounding-level gradient differences into different steps for near-zero
+gradients, so later steps drift apart a little). Skipped with fewer than two GPUs."""
 
 import dataclasses
 
@@ -41,8 +43,8 @@ def _train(rank, world, fused: bool):
     transport = type(units[0].comm).__name__
     opt = OptimizersContainer.Config(lr=3e-3, beta1=0.9, beta2=0.95, weight_decay=0.1).build(model_parts=[model])
     g = torch.Generator().manual_seed(7 + rank)
-    losses = []
-    for _ in range(STEPS):
+    losses, grads = [], None
+    for step in range(STEPS):
         opt.zero_grad()
         total = torch.zeros((), device="cuda")
         for _ in range(MICRO):
@@ -50,7 +52,9 @@ def _train(rank, world, fused: bool):
             loss = cross_entropy_loss(model(x[:, :-1]), x[:, 1:]) / (BATCH * SEQ * MICRO * world)
             loss.backward()
             total += loss.detach()
-        grads = [u.grad_shard_flat.detach().clone() for u in units if u.params]
+        if step == 0:
+            torch.cuda.synchronize()
+            grads = [u.grad_shard_flat.detach().clone() for u in units if u.params]
         opt.step()
         dist.all_reduce(total)
         losses.append(total.item())
@@ -78,9 +82,10 @@ def test_nvlink_transport_matches_c10d_with_gradient_accumulation(tmp_path):
         assert nv["transport"] == "NvlinkComm" and c10["transport"] == "C10dComm"
         assert not nv["errs"] and nv["comm_err"] is None
         # bf16 gradients cross the wire in both (NCCL reduces them in fp32 after a cast): same sums up to ordering
+        assert abs(nv["losses"][0] - c10["losses"][0]) <= 1e-5 * abs(c10["losses"][0])
         for a, b in zip(nv["losses"], c10["losses"]):
-            assert abs(a - b) <= 2e-3 * abs(b), (nv["losses"], c10["losses"])
+            assert abs(a - b) <= 5e-3 * abs(b), (nv["losses"], c10["losses"])
         for ga, gb in zip(nv["grads"], c10["grads"]):
             scale = gb.abs().max().item() + 1e-12
-            assert (ga - gb).abs().max().item() <= 2e-2 * scale
+            assert (ga - gb).abs().max().item() <= 5e-3 * scale, ((ga - gb).abs().max().item(), scale)
         assert nv["losses"][-1] < nv["losses"][0]

@@ -98,14 +98,17 @@ class GradSlot:
     NVLink staging buffer that peers reduce from. The GEMM asks :meth:`begin` whether to
     accumulate and the unit learns through ``written`` that nothing is left to copy."""
 
-    __slots__ = ("tensor", "unit", "index")
+    __slots__ = ("tensor", "unit", "index", "staging")
 
-    def __init__(self, tensor, unit, index):
-        self.tensor, self.unit, self.index = tensor, unit, index
+    def __init__(self, tensor, unit, index, staging=False):
+        self.tensor, self.unit, self.index, self.staging = tensor, unit, index, staging
 
     def begin(self) -> bool:
+        """True when the GEMM must add to what the slot holds. A staging slot only ever holds the gradient of the
+        current backward (the reduce kernel adds earlier micro-batches in the fp32 shard), so it accumulates only for a
+        second use of the parameter inside one backward; the fp32 shard itself also accumulates across micro-batches."""
         u = self.unit
-        acc = u._slot_accumulate or u._slot_written[self.index]
+        acc = (u._slot_accumulate and not self.staging) or u._slot_written[self.index]
         u._slot_written[self.index] = True
         return acc
 
@@ -367,13 +370,13 @@ class FSDPUnit:
         for i, p in enumerate(self.params):
             if len(p.full_shape) != 2 or p.shard_dim != 0 or not p.param.requires_grad:
                 continue
-            t = None
+            t, staging = None, False
             if make is not None:
-                t = make(self, p)
+                t, staging = make(self, p), True
             elif self.shard_world == 1 and self.replicate_group is None and self.grad_shard_flat.dtype == torch.float32:
                 t = self._shard_view(self.grad_shard_flat, p)
             if t is not None:
-                self._slots[i] = GradSlot(t, self, i)
+                self._slots[i] = GradSlot(t, self, i, staging)
 
     def alloc_shard_buffer(self, dtype, kind: str):
         alloc = getattr(self.comm, "alloc_shard_buffer", None)
