@@ -91,7 +91,7 @@ def _dist_env():
 
 
 def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, layers: int | None = None,
-                  extra: list[str] | None = None, sac_mm_policy: str = "every_second"):
+                  extra: list[str] | None = None, sac_mm_policy: str = "every_second", config: str = "llama3_8b_synthetic"):
     from torchtitan_b200.config.manager import ConfigManager
     from torchtitan_b200.models.llama3 import llama3_configs
 
@@ -99,7 +99,7 @@ def build_trainer(n_gpus: int, steps_total: int, ac_mode: str | None = None, lay
         llama3_configs["8B"].n_layers = layers
 
     args = [
-        "--module", "llama3", "--config", "llama3_8b_synthetic",
+        "--module", "llama3", "--config", config,
         "--training.steps", str(steps_total), "--metrics.log_freq", "1000000",
         "--dump_folder", "/tmp/tt_b200_bench", "--comm.train_timeout_seconds", "300",
         # which matmul outputs per-op SAC keeps: "every_second" is the reference's policy (both arms then recompute the
@@ -179,7 +179,7 @@ def run_ours(args) -> dict:
     if rank == 0:
         init_logger()
     total_steps = args.warmup + 2 * args.steps + 4
-    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers, args.override, args.sac_mm_policy)
+    trainer = build_trainer(args.gpus, total_steps, args.ac, args.layers, args.override, args.sac_mm_policy, args.config)
     dev = trainer.device
     local_bs = trainer.config.training.local_batch_size
     pd = trainer.parallel_dims
@@ -275,6 +275,9 @@ def run_ours(args) -> dict:
         out["invalid_truncated_model_layers"] = args.layers
     if args.override:
         out["config"]["overrides"] = list(args.override)
+    if args.config != "llama3_8b_synthetic":
+        out["config"]["job_config"] = args.config
+        out["dtype"] = "mxfp8 linears (bf16 elsewhere)" if "mxfp8" in args.config else out["dtype"]
     trainer.close()
     return out
 
@@ -297,6 +300,8 @@ def main():
     ap.add_argument("--ref-compile", action="store_true", help="reference arm only: time the --compile.enable build alone")
     ap.add_argument("--ref-build", default="both", choices=["both", "eager", "compile"],
                     help="reference arm only: which build(s) to time; 'both' reports the faster one")
+    ap.add_argument("--config", default="llama3_8b_synthetic", help="job configuration of the llama3 module (e.g. "
+                    "llama3_8b_synthetic_mxfp8); anything but the default is an experiment and is labelled in the output")
     ap.add_argument("--sac-mm-policy", default="every_second", choices=["every_second", "all", "auto"],
                     help="which matmul outputs per-op SAC keeps (every_second = the reference's policy)")
     ap.add_argument("--kernel-table", default=None, help="after the timed regions, run one more step under the PyTorch "

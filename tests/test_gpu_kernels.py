@@ -488,3 +488,35 @@ def test_gemm_mxfp8_block_scaled(ops, M, N, K):
     assert _rel(got, want) < 1e-3, _rel(got, want)
     got16 = ops.gemm_mxfp8(qa, qb, sa, sb, torch.bfloat16)
     assert _rel(got16, want) < 1e-2
+
+
+@pytest.mark.parametrize("rows,K,N", [(256, 256, 512), (512, 1024, 768), (96, 160, 224)])
+def test_mx_linear_op_matches_definition(ops, rows, K, N):
+    """The MXFP8 linear as one op (quantise with scales in the MMA's layout + block-scaled GEMM, weight gradient into a
+    gradient slot) against the PyTorch definition of the same arithmetic (quantise, dequantise, fp32 matmul), forward,
+    input gradient and weight gradient; operands with block-dependent magnitudes so that a misplaced scale shows."""
+    from torchtitan_b200.ops import native, quant
+
+    if not native.has("tt_mxfp8_quant_rows_swz"):
+        pytest.skip("library built without the swizzled MXFP8 quantisers")
+    torch.manual_seed(0)
+    mag = lambda r, c: torch.exp2(torch.randint(-4, 5, (r, c // 32), device="cuda").float()).repeat_interleave(32, 1)
+    x = (torch.randn(rows, K, device="cuda") * mag(rows, K)).bfloat16().requires_grad_()
+    w = (torch.randn(N, K, device="cuda") * 0.05 * mag(N, K)).bfloat16().requires_grad_()
+    y = ops.mx_linear(x.view(1, rows, K), w)
+    assert y is not None and y.shape == (1, rows, N)
+    gy = (torch.randn(1, rows, N, device="cuda") * mag(rows, N).view(1, rows, N)).bfloat16()
+    y.backward(gy)
+    _no_kernel_errors()
+
+    def mm(a, b_t):           # the definition: both operands block-scaled along the contraction
+        qa, sa = quant.quantize_mxfp8(a.contiguous())
+        qb, sb = quant.quantize_mxfp8(b_t.contiguous())
+        return quant.dequantize_mxfp8(qa, sa) @ quant.dequantize_mxfp8(qb, sb).t()
+
+    xd, wd, g2 = x.detach(), w.detach(), gy.view(rows, N)
+    assert _rel(y.view(rows, N), mm(xd, wd)) < 1e-2
+    assert _rel(x.grad, mm(g2, wd.t())) < 1e-2
+    assert _rel(w.grad, mm(g2.t(), xd.t())) < 1e-2
+    # and close to the unquantised product (e4m3 keeps 3 mantissa bits)
+    assert _rel(y.view(rows, N), xd.float() @ wd.float().t()) < 8e-2

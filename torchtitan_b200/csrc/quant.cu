@@ -193,10 +193,17 @@ __device__ __forceinline__ int mx_exponent(float amax) {
   return max(-127, min(127, e));
 }
 
+// Where the scale of (row r, K block b) lives in the layout the block-scaled MMA wants (see gemm_mx.cu): one 512-byte
+// chunk per 128 rows and per 4 K blocks; inside it row r, block j sits at byte (r % 32) * 16 + ((r / 32) % 4) * 4 + j.
+// Writing this layout here saves the separate re-layout launch per operand.
+__device__ __forceinline__ long long mx_swizzled_index(long long r, int b, int kb4) {
+  return ((r >> 7) * kb4 + (b >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (b & 3);
+}
+
 // Rows: one thread per 32-element block (64 bytes in, 32 bytes + 1 scale byte out). K % 32 == 0.
 __global__ void __launch_bounds__(256)
 mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int K, uint8_t* __restrict__ q,
-                     uint8_t* __restrict__ scales) {
+                     uint8_t* __restrict__ scales, int kb4) {
   const int kb = K / 32;
   const long long total = static_cast<long long>(M) * kb;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -228,7 +235,7 @@ mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, i
     uint4* dst = reinterpret_cast<uint4*>(q + r * static_cast<long long>(K) + b * 32);
     dst[0] = *reinterpret_cast<const uint4*>(o);
     dst[1] = *reinterpret_cast<const uint4*>(o + 16);
-    scales[r * kb + b] = static_cast<uint8_t>(ex + 127);
+    scales[kb4 ? mx_swizzled_index(r, b, kb4) : r * kb + b] = static_cast<uint8_t>(ex + 127);
   }
 }
 
@@ -236,7 +243,7 @@ mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, i
 // scales [N, M/32]. Tile of 128 rows (m) x 64 columns (n): per column four 32-row blocks. M % 32 == 0, N % 8 == 0.
 __global__ void __launch_bounds__(256)
 mx_quant_cols_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N, uint8_t* __restrict__ qT,
-                     uint8_t* __restrict__ scales) {
+                     uint8_t* __restrict__ scales, int kb4) {
   __shared__ __nv_bfloat16 s_x[128][64 + 8];
   __shared__ uint8_t s_t[64][128 + 16];
   const int n0 = blockIdx.x * 64, m0 = blockIdx.y * 128;
@@ -262,7 +269,8 @@ mx_quant_cols_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, i
     s_t[n][blk * 32 + r] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
   }
   if (n0 + n < N && m0 + blk * 32 < M)
-    scales[(n0 + n) * static_cast<long long>(M / 32) + (m0 / 32 + blk)] = static_cast<uint8_t>(ex + 127);
+    scales[kb4 ? mx_swizzled_index(n0 + n, m0 / 32 + blk, kb4)
+               : (n0 + n) * static_cast<long long>(M / 32) + (m0 / 32 + blk)] = static_cast<uint8_t>(ex + 127);
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -342,7 +350,17 @@ int tt_mxfp8_quant_rows(const void* x, long long ld, int M, int K, void* q, void
   if (M <= 0 || K <= 0) return 0;
   if (K % 32 || ld % 8) return -2;
   mx_quant_rows_kernel<<<grid_for(static_cast<long long>(M) * (K / 32), 256), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(x), ld, M, K, static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales));
+      static_cast<const __nv_bfloat16*>(x), ld, M, K, static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales), 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Same, with the scales written straight into the block-scaled MMA's layout (buffer of tt_mx_scales_bytes(M, 256, K)
+// bytes; when M % 128 or (K / 32) % 4 is not zero the caller fills it with 127 = 2^0 first).
+int tt_mxfp8_quant_rows_swz(const void* x, long long ld, int M, int K, void* q, void* scales, cudaStream_t st) {
+  if (M <= 0 || K <= 0) return 0;
+  if (K % 32 || ld % 8) return -2;
+  mx_quant_rows_kernel<<<grid_for(static_cast<long long>(M) * (K / 32), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), ld, M, K, static_cast<uint8_t*>(q), static_cast<uint8_t*>(scales), (K + 127) / 128);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -352,7 +370,17 @@ int tt_mxfp8_quant_cols(const void* x, long long ld, int M, int N, void* qT, voi
   if (M % 32 || N % 8 || ld % 8) return -2;
   dim3 g((N + 63) / 64, (M + 127) / 128);
   mx_quant_cols_kernel<<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ld, M, N, static_cast<uint8_t*>(qT),
-                                          static_cast<uint8_t*>(scales));
+                                          static_cast<uint8_t*>(scales), 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Transposed operand with scales in the MMA's layout: rows of the operand = columns of x (N of them), contraction M.
+int tt_mxfp8_quant_cols_swz(const void* x, long long ld, int M, int N, void* qT, void* scales, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M % 32 || N % 8 || ld % 8) return -2;
+  dim3 g((N + 63) / 64, (M + 127) / 128);
+  mx_quant_cols_kernel<<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ld, M, N, static_cast<uint8_t*>(qT),
+                                          static_cast<uint8_t*>(scales), (M + 127) / 128);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

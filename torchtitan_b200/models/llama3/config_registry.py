@@ -106,6 +106,20 @@ def llama3_8b_synthetic() -> Trainer.Config:
     return cfg
 
 
+def llama3_8b_synthetic_mxfp8() -> Trainer.Config:
+    """The throughput job with every transformer Linear in MXFP8 (e4m3 data, one E8M0 scale per 32 elements along the
+    contraction, bf16 master copies, fp32 accumulation); the output projection stays bf16, as in
+    torchtitan docs/mxfp8.md. Add ``--parallelism.tensor_parallel_degree 2 --parallelism.enable_async_tensor_parallel``
+    for the FSDP x TP layout."""
+    from torchtitan_b200.components.quantization.mx import MXFP8Converter
+
+    cfg = llama3_8b_synthetic()
+    cfg.model_converters = ModelConvertersContainer.Config(converters=[
+        MXFP8Converter.Config(fqns=["attention", "feed_forward"]),
+    ])
+    return cfg
+
+
 def llama3_70b() -> Trainer.Config:
     return Trainer.Config(
         hf_assets_path="./assets/hf/Llama-3.1-70B",

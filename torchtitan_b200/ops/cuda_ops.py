@@ -524,6 +524,7 @@ def _scratch_buf(device, n: int) -> Tensor:
 def adamw_flat(param, grad, exp_avg, exp_avg_sq, shadow, *, lr, beta1, beta2, eps, weight_decay, step, decoupled=True,
                grad_scale=None):
     assert param.dtype == torch.float32 and grad.dtype == torch.float32
+    _MX_CACHE.clear()      # the kernel rewrites compute copies of the weights in place, behind the version counters
     if shadow is not None:
         assert shadow.dtype == torch.bfloat16 and shadow.numel() == param.numel()
     gs = None
@@ -876,6 +877,140 @@ def quantize_mxfp8_operand(x: Tensor):
         _ck(L.tt_mxfp8_quant_cols(x.data_ptr(), x.stride(1), K, R, q.data_ptr(), sc.data_ptr(), _stream()), "tt_mxfp8_quant_cols")
         return q, sc
     return None
+
+
+# ---- MXFP8 linear algebra as one dispatcher-visible op ------------------------------------------------------------
+# Recently quantised operands, keyed by the source's address, layout and version. The entry keeps the source tensor alive,
+# so its address cannot be handed to another tensor while the entry exists; an in-place write bumps the version. Serves
+# the activations that several linears share (wq / wk / wv, w1 / w3 and their weight-gradient GEMMs).
+_MX_CACHE: list = []
+_MX_CACHE_SIZE = 3
+
+
+def _mx_operand(x: Tensor, transposed: bool):
+    """MXFP8 operand of a GEMM whose contraction runs along the last dimension of ``x`` (or of ``x.t()`` when
+    ``transposed``): (e4m3 [R, K] contiguous, E8M0 scales in the block-scaled MMA's layout), or None when the layout is
+    not covered by the native kernels."""
+    key = (x.data_ptr(), tuple(x.shape), tuple(x.stride()), x._version, transposed)
+    for i, (k, _, out) in enumerate(_MX_CACHE):
+        if k == key:
+            _MX_CACHE.append(_MX_CACHE.pop(i))
+            return out
+    L = _lib()
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16:
+        return None
+    rows, cols = x.shape
+    if transposed:        # operand = x^T [cols, rows], contraction along x's rows
+        R, K = cols, rows
+        if K % 32 or R % 8:
+            return None
+    else:
+        R, K = rows, cols
+        if K % 32:
+            return None
+    q = torch.empty(R, K, dtype=torch.float8_e4m3fn, device=x.device)
+    sc = torch.empty(L.tt_mx_scales_bytes(R, 256, K), dtype=torch.uint8, device=x.device)
+    if R % 256 or (K // 32) % 4:
+        sc.fill_(127)     # rows / K blocks past the end carry the neutral scale 2^0 (their data is zero-filled by TMA)
+    if transposed:
+        _ck(L.tt_mxfp8_quant_cols_swz(x.data_ptr(), x.stride(0), rows, cols, q.data_ptr(), sc.data_ptr(), _stream()),
+            "tt_mxfp8_quant_cols_swz")
+    else:
+        _ck(L.tt_mxfp8_quant_rows_swz(x.data_ptr(), x.stride(0), rows, cols, q.data_ptr(), sc.data_ptr(), _stream()),
+            "tt_mxfp8_quant_rows_swz")
+    out = (q, sc)
+    _MX_CACHE.append((key, x, out))
+    if len(_MX_CACHE) > _MX_CACHE_SIZE:
+        _MX_CACHE.pop(0)
+    return out
+
+
+def mx_cache_clear() -> None:
+    _MX_CACHE.clear()
+
+
+def _mx_mm_into(a: Tensor, b: Tensor, a_t: bool, b_t: bool, out: Tensor) -> bool:
+    """``out = op(a) @ op(b)^T`` with both operands MXFP8-quantised along the contraction; False when a layout is not
+    covered (the caller then uses the PyTorch definition)."""
+    qa, qb = _mx_operand(a, a_t), _mx_operand(b, b_t)
+    if qa is None or qb is None or out.stride(1) != 1:
+        return False
+    (A, sa), (B, sb) = qa, qb
+    M, K = A.shape
+    N = B.shape[0]
+    assert B.shape[1] == K and out.shape == (M, N)
+    _ck(_lib().tt_gemm_mxfp8(A.data_ptr(), B.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), M, N, K, A.stride(0),
+                             B.stride(0), out.stride(0), int(out.dtype == torch.float32), _stream()), "tt_gemm_mxfp8")
+    return True
+
+
+@torch.library.custom_op("tt_b200::mx_mm", mutates_args=())
+def mx_mm(a: Tensor, b: Tensor, a_t: bool, b_t: bool, out_fp32: bool) -> Tensor:
+    """``op(a) [M,K] @ op(b) [N,K]^T`` (``op`` = transpose when the flag is set) with MXFP8 operands: both are quantised
+    here (e4m3 data, one E8M0 scale per 32 elements of K, RCEIL) and multiplied by the block-scaled tensor-core kernel.
+    One op, so per-op activation checkpointing can keep its output like any other matmul."""
+    M = a.shape[1] if a_t else a.shape[0]
+    N = b.shape[1] if b_t else b.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32 if out_fp32 else torch.bfloat16, device=a.device)
+    if not _mx_mm_into(a, b, a_t, b_t, out):
+        from .quant import _mx_mm
+
+        out.copy_(_mx_mm(a.t() if a_t else a, b.t() if b_t else b, out.dtype))
+    return out
+
+
+@mx_mm.register_fake
+def _(a, b, a_t, b_t, out_fp32):
+    M = a.shape[1] if a_t else a.shape[0]
+    N = b.shape[1] if b_t else b.shape[0]
+    return a.new_empty((M, N), dtype=torch.float32 if out_fp32 else torch.bfloat16)
+
+
+class _MxLinearFn(torch.autograd.Function):
+    """MXFP8 linear: forward ``x W^T``, input gradient ``dy W`` (W quantised down its columns) and weight gradient
+    ``dy^T x`` (both quantised down their rows, i.e. along the tokens), each through ``tt_b200::mx_mm``. The weight
+    gradient goes straight into the FSDP unit's gradient buffer when the weight carries a slot."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        x2 = _rows2d(x)
+        y = torch.ops.tt_b200.mx_mm(x2, w, False, False, False)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        ctx.grad_slot = getattr(w, "_grad_slot", None)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        g2 = _rows2d(gy)
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.ops.tt_b200.mx_mm(g2, w, False, True, False).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            slot = ctx.grad_slot
+            if slot is not None:
+                if not slot.begin() and _mx_mm_into(g2, x2, True, True, slot.tensor):
+                    pass                                            # first gradient of this backward: written in place
+                else:
+                    slot.tensor.add_(torch.ops.tt_b200.mx_mm(g2, x2, True, True, True))
+                gw = _placeholder(w)
+            else:
+                gw = torch.ops.tt_b200.mx_mm(g2, x2, True, True, False)
+        return gx, gw
+
+
+def mx_linear(x: Tensor, weight: Tensor) -> Tensor | None:
+    """The native MXFP8 linear, or None when dtype / shape / library do not allow it."""
+    if not (x.is_cuda and native.has("tt_mxfp8_quant_rows_swz") and native.has("tt_gemm_mxfp8")):
+        return None
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.dim() != 2 or weight.stride(1) != 1:
+        return None
+    K, N = x.shape[-1], weight.shape[0]
+    rows = x.numel() // max(K, 1)
+    if K % 32 or N % 32 or rows % 32 or weight.stride(0) % 8 or weight.data_ptr() % 16:
+        return None
+    return _MxLinearFn.apply(x, weight)
 
 
 def gemm_mxfp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:

@@ -90,6 +90,9 @@ def lib():
     if hasattr(L, "tt_mxfp8_quant_rows"):
         _sig(L.tt_mxfp8_quant_rows, [P, LL, I, I, P, P, P])
         _sig(L.tt_mxfp8_quant_cols, [P, LL, I, I, P, P, P])
+    if hasattr(L, "tt_mxfp8_quant_rows_swz"):
+        _sig(L.tt_mxfp8_quant_rows_swz, [P, LL, I, I, P, P, P])
+        _sig(L.tt_mxfp8_quant_cols_swz, [P, LL, I, I, P, P, P])
     if hasattr(L, "tt_sample_top_p"):
         _sig(L.tt_sample_top_p, [P, P, P, P, I, I, LL, F, F, I, P])
     if hasattr(L, "tt_fp8_quant_rows"):

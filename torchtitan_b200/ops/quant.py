@@ -161,7 +161,13 @@ class _MxLinear(torch.autograd.Function):
 
 def quant_linear(x: torch.Tensor, w: torch.Tensor, bias, recipe: QuantRecipe):
     w = w.to_local() if hasattr(w, "to_local") else w
-    y = _MxLinear.apply(x, w) if recipe.kind == "mxfp8" else _Fp8Linear.apply(x, w, recipe)
+    y = None
+    if recipe.kind == "mxfp8" and x.is_cuda and not recipe.emulate:
+        from .cuda_ops import mx_linear
+
+        y = mx_linear(x, w)            # one dispatcher-visible op per GEMM, gradient written into the FSDP slot
+    if y is None:
+        y = _MxLinear.apply(x, w) if recipe.kind == "mxfp8" else _Fp8Linear.apply(x, w, recipe)
     return y if bias is None else y + bias
 
 
