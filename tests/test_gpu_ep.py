@@ -130,14 +130,20 @@ def _worker(rank, world, score_before=False):
     base.init_weights(init_std=0.05, buffer_device=torch.device("cpu"))
     out = {"y": [], "dx": [], "dw1": [], "dgate": []}
     mods = []
-    for which in ("a2a", "nvlink"):
+    for which in ("a2a", "nvlink", "nvlink_small"):
         moe = MoE.Config(**kw).build(dim=128)
         moe.load_state_dict(base.state_dict())
         moe = moe.cuda().bfloat16()
         moe.router.gate.float()
         _shard_experts(moe.experts, ep_mesh)
-        moe.experts.dispatcher = (AllToAllDispatcher(ep_mesh, 8, alignment=64) if which == "a2a"
-                                  else NvlinkDispatcher(ep_mesh, 8, alignment=64))
+        if which == "a2a":
+            moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, 8, alignment=64)
+        else:
+            moe.experts.dispatcher = NvlinkDispatcher(ep_mesh, 8, alignment=64)
+            if which == "nvlink_small":
+                # lossless mode with a receive buffer far too small for the traffic: every call must notice that on
+                # the host and go through the collectives instead of dropping rows
+                moe.experts.dispatcher.capacity_factor = 0.05
         mods.append(moe)
     for it in range(3):                                            # several calls: both buffer parities, counters keep counting
         x = torch.randn(2, 96, 128, generator=torch.Generator().manual_seed(100 * it + rank)).cuda().bfloat16()
@@ -152,8 +158,11 @@ def _worker(rank, world, score_before=False):
         rel = lambda a, b: float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
         for key, (a, b) in zip(out, zip(res[1], res[0])):
             out[key].append(rel(a, b))
+        for key, (a, b) in zip(out, zip(res[2], res[0])):
+            out[key].append(rel(a, b))
     torch.cuda.synchronize()
     out["errors"] = native.kernel_errors()
+    out["fallbacks"] = (mods[1].experts.dispatcher.fallback_calls, mods[2].experts.dispatcher.fallback_calls)
     return out
 
 
@@ -165,3 +174,4 @@ def test_nvlink_dispatcher_matches_all_to_all_two_gpus(tmp_path, score_before):
         assert not o["errors"], o
         # same rows reach the same experts: results agree to bf16 rounding of the combine order
         assert max(o["y"]) < 2e-2 and max(o["dx"]) < 3e-2 and max(o["dw1"]) < 3e-2 and max(o["dgate"]) < 3e-2, o
+        assert o["fallbacks"][0] == 0 and o["fallbacks"][1] >= 3, o      # roomy buffer: never; tiny buffer: every forward

@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(256)
 build_maps_kernel(const int* __restrict__ table, const int* __restrict__ flags, int world, int rank, int E, int El, int align,
                   int n, int cap, int version, int* __restrict__ dst_rank, int* __restrict__ dst_row,
                   int* __restrict__ rev_rank, int* __restrict__ rev_row, int* __restrict__ offs, int* __restrict__ info,
-                  __nv_bfloat16* __restrict__ recv, int D) {
+                  __nv_bfloat16* __restrict__ recv, int D, int report_overflow) {
   __shared__ int s_ok;
   __shared__ int s_dst_start[kMaxExperts];     // receive row (on the owner) where this rank's rows of expert e begin
   __shared__ int s_my_cum[kMaxExperts + 1];    // exclusive prefix of this rank's counts
@@ -128,7 +128,9 @@ build_maps_kernel(const int* __restrict__ table, const int* __restrict__ flags, 
       int run = 0;
       for (int el = 0; el < El; ++el) { run = s_base[el] + (s_size[el] + align - 1) / align * align; offs[el] = min(run, cap); }
       info[0] = min(run, cap);
-      if (run > cap) set_error(2, rank, cap, run);
+      // more rows than the buffer holds: an error in the fixed-capacity mode (they will be dropped); in the lossless
+      // mode the host sees the same table and routes this call through the collectives, so nothing is lost
+      if (run > cap && report_overflow) set_error(2, rank, cap, run);
     }
   }
   if (threadIdx.x == 0) {
@@ -247,13 +249,21 @@ int tt_ep_publish_counts(const long long* counts, void* const* tables, void* con
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// report_overflow: 1 = rows beyond the capacity set error code 2 (they are dropped); 0 = the caller handles overflow itself.
+int tt_ep_build_maps_opt(const int* table, const int* flags, int world, int rank, int E, int align, int n, int cap,
+                         int version, int* dst_rank, int* dst_row, int* rev_rank, int* rev_row, int* offs, int* info,
+                         void* recv, int D, int report_overflow, cudaStream_t st) {
+  if (world < 1 || world > kMaxRanks || E > kMaxExperts || E % world || D % 8) return -6;
+  build_maps_kernel<<<1, 256, 0, st>>>(table, flags, world, rank, E, E / world, align, n, cap, version, dst_rank, dst_row,
+                                       rev_rank, rev_row, offs, info, static_cast<__nv_bfloat16*>(recv), D, report_overflow);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 int tt_ep_build_maps(const int* table, const int* flags, int world, int rank, int E, int align, int n, int cap, int version,
                      int* dst_rank, int* dst_row, int* rev_rank, int* rev_row, int* offs, int* info, void* recv, int D,
                      cudaStream_t st) {
-  if (world < 1 || world > kMaxRanks || E > kMaxExperts || E % world || D % 8) return -6;
-  build_maps_kernel<<<1, 256, 0, st>>>(table, flags, world, rank, E, E / world, align, n, cap, version, dst_rank, dst_row,
-                                       rev_rank, rev_row, offs, info, static_cast<__nv_bfloat16*>(recv), D);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return tt_ep_build_maps_opt(table, flags, world, rank, E, align, n, cap, version, dst_rank, dst_row, rev_rank, rev_row, offs,
+                              info, recv, D, 1, st);
 }
 
 int tt_ep_push(const void* in_rows, const int* in_index, int n_in, const int* to_rank, const int* to_row, void* const* bufs,

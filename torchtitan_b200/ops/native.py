@@ -76,6 +76,8 @@ def lib():
     if hasattr(L, "tt_ep_push"):
         _sig(L.tt_ep_publish_counts, [P, P, P, I, I, I, I, P])
         _sig(L.tt_ep_build_maps, [P, P, I, I, I, I, I, I, I, P, P, P, P, P, P, P, I, P])
+        if hasattr(L, "tt_ep_build_maps_opt"):
+            _sig(L.tt_ep_build_maps_opt, [P, P, I, I, I, I, I, I, I, P, P, P, P, P, P, P, I, I, P])
         _sig(L.tt_ep_push, [P, P, I, P, P, P, P, I, I, I, P])
         _sig(L.tt_ep_wait, [P, I, P])
         _sig(L.tt_ep_error, [P])

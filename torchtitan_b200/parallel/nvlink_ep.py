@@ -2,9 +2,17 @@
 counts exchanged through peer memory, group offsets kept on the device -- no collective library call and no device-to-host
 read on the path. Drop-in for :class:`parallel.ep.AllToAllDispatcher` (same ``dispatch`` / ``combine`` contract).
 
-The receive buffer has a fixed capacity of ``capacity_factor x`` the rows a rank sends (plus alignment padding); rows that
-do not fit are dropped and reported through ``native.kernel_errors()``. Received rows are copied out of the symmetric buffer
-(which is recycled two calls later) into an ordinary tensor, with the padding rows zeroed in the same pass.
+The receive buffer has a fixed capacity (plus alignment padding). Two modes:
+
+* default (``capacity_factor=None``): lossless. The buffer holds twice the rows a rank sends; after the counts are
+  exchanged every rank reads the (identical) count table on the host, and when any rank's experts would receive more
+  than the buffer holds, this call goes through the all-to-all dispatcher instead. One small device-to-host read per
+  dispatch, no token is ever dropped (what the reference's DeepEP backend guarantees by default);
+* ``hybridep_non_blocking_expert_capacity_factor`` set: no host read at all; rows beyond ``factor x`` the rows a rank sends
+  are dropped and reported through ``native.kernel_errors()`` (the reference's non-blocking HybridEP mode).
+
+Received rows are copied out of the symmetric buffer (which is recycled two calls later) into an ordinary tensor, with the
+padding rows zeroed in the same pass.
 Parity: the DeepEP / HybridEP backends of the reference (torchtitan/distributed/deepep, hybridep: NVLink buffers, fused
 permute, optional fixed-capacity non-blocking mode), without the external library."""
 
@@ -130,8 +138,10 @@ class NvlinkDispatcher:
         assert num_experts % self.ep == 0, f"ep ({self.ep}) must divide num_experts ({num_experts})"
         self.num_experts, self.local_experts = num_experts, num_experts // self.ep
         self.alignment = alignment
+        self.lossless = capacity_factor is None
         self.capacity_factor = capacity_factor if capacity_factor is not None else 2.0
         self.heap_bytes = heap_bytes
+        self.fallback_calls = 0
         self.device = torch.device("cuda", torch.cuda.current_device())
         self._mesh, self._fallback = ep_mesh, None
 
@@ -151,7 +161,7 @@ class NvlinkDispatcher:
         gid = id(self.group)
         if gid not in NvlinkDispatcher._heaps:
             NvlinkDispatcher._heaps[gid] = SymmetricHeap(self.group, self.heap_bytes, self.device)
-        key = (gid, n, D, self.num_experts)
+        key = (gid, n, D, self.num_experts, self.capacity_factor)
         if key not in NvlinkDispatcher._shared:
             cap = int(n * self.capacity_factor) + self.local_experts * self.alignment
             cap = (cap + self.alignment - 1) // self.alignment * self.alignment
@@ -159,14 +169,29 @@ class NvlinkDispatcher:
             dist.barrier(group=self.group)
         return NvlinkDispatcher._shared[key]
 
+    def _collective(self):
+        if self._fallback is None:
+            from .ep import AllToAllDispatcher
+
+            self._fallback = AllToAllDispatcher(self._mesh, self.num_experts, alignment=self.alignment)
+        return self._fallback
+
+    def _would_overflow(self, table: torch.Tensor, cap: int) -> bool:
+        """``table`` [W, E]: rows every rank sends to every expert (complete once the map kernel ran, which precedes this
+        read on the stream). True when some rank's padded expert groups exceed the receive capacity."""
+        from torch.utils._python_dispatch import _disable_current_modes
+
+        # the one host read of the lossless mode. Done outside any dispatch mode: activation checkpointing would
+        # otherwise record this copy in its per-op cache, and the replay in backward must read its own table
+        with _disable_current_modes():
+            per_expert = table.sum(0).cpu().view(self.ep, self.local_experts)
+        padded = (per_expert + self.alignment - 1) // self.alignment * self.alignment
+        return bool((padded.sum(1) > cap).any())
+
     def dispatch(self, x, order, counts, top_k: int):
         if x.dtype != torch.bfloat16 or x.shape[-1] % 8:
             # the peer-memory kernels move bf16 rows of a multiple of 8 elements: anything else takes the collectives
-            if self._fallback is None:
-                from .ep import AllToAllDispatcher
-
-                self._fallback = AllToAllDispatcher(self._mesh, self.num_experts, alignment=self.alignment)
-            rows, sizes, ctx = self._fallback.dispatch(x, order, counts, top_k)
+            rows, sizes, ctx = self._collective().dispatch(x, order, counts, top_k)
             ctx["fallback"] = True
             return rows, sizes, ctx
         L = native.lib()
@@ -182,11 +207,17 @@ class NvlinkDispatcher:
         maps = {"n": n, "dst_rank": torch.empty(n, dtype=_I32, device=dev), "dst_row": torch.empty(n, dtype=_I32, device=dev),
                 "rev_rank": torch.empty(sh.cap, dtype=_I32, device=dev), "rev_row": torch.empty(sh.cap, dtype=_I32, device=dev),
                 "offs": torch.empty(self.local_experts, dtype=_I32, device=dev), "info": torch.empty(2, dtype=_I32, device=dev)}
-        native.check(L.tt_ep_build_maps(sh.table[par]["ptr"], sh.flags[par]["ptr"], W, self.rank, E, self.alignment, n, sh.cap,
-                                        version, maps["dst_rank"].data_ptr(),
-                                        maps["dst_row"].data_ptr(), maps["rev_rank"].data_ptr(), maps["rev_row"].data_ptr(),
-                                        maps["offs"].data_ptr(), maps["info"].data_ptr(), None, D, _stream()),
-                     "tt_ep_build_maps")
+        native.check(L.tt_ep_build_maps_opt(sh.table[par]["ptr"], sh.flags[par]["ptr"], W, self.rank, E, self.alignment, n, sh.cap,
+                                            version, maps["dst_rank"].data_ptr(),
+                                            maps["dst_row"].data_ptr(), maps["rev_rank"].data_ptr(), maps["rev_row"].data_ptr(),
+                                            maps["offs"].data_ptr(), maps["info"].data_ptr(), None, D, int(not self.lossless),
+                                            _stream()), "tt_ep_build_maps")
+        if self.lossless and self._would_overflow(sh.table[par]["local"], sh.cap):
+            # every rank sees the same table, so all of them take the collective path for this call
+            self.fallback_calls += 1
+            rows, sizes, ctx = self._collective().dispatch(x, order, counts, top_k)
+            ctx["fallback"] = True
+            return rows, sizes, ctx
         src_index = (order // top_k).to(_I32).contiguous()
         recv = _Exchange.apply(x.contiguous(), src_index, maps, sh, "fwd")
         offs = maps["offs"].to(torch.int64)
