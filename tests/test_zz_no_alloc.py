@@ -35,6 +35,7 @@ def test_noalloc_matches_regular_entry_twice(dtype, code):
     L = _lib()
     dev = "cuda"
     stream = torch.cuda.current_stream().cuda_stream
+    calls_done = 0
     for trial, (rows, D) in enumerate([(777, 4096), (300, 1024)]):  # two calls in a row share the array
         torch.manual_seed(trial)
         x = torch.randn(rows, D, device=dev, dtype=dtype)
@@ -49,12 +50,19 @@ def test_noalloc_matches_regular_entry_twice(dtype, code):
                                 dw_ref.data_ptr(), scratch.data_ptr(), rows, D, code, stream) == 0
         # allocation-free entry point: outputs are allocated here, by the caller, before the call
         dx, dw = torch.empty_like(x), torch.empty_like(w)
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0] if calls_done else None
         rc = L.tt_rmsnorm_bwd_noalloc(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
                                       dw.data_ptr(), rows, D, code, stream)
         assert rc == 0, L.tt_noalloc_strerror(rc)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        # PyTorch's counter only sees its own allocator: from the second call on (the module and the scratch address are
+        # loaded by then) the driver's free-memory figure must not move either, so a cudaMalloc inside the library shows
+        if free_before is not None:
+            assert torch.cuda.mem_get_info()[0] >= free_before
+        calls_done += 1
         tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
         assert torch.allclose(dx.float(), dx_ref.float(), rtol=tol, atol=tol)
         assert torch.allclose(dw.float(), dw_ref.float(), rtol=tol, atol=tol * 10)

@@ -38,6 +38,7 @@ __all__ = ["pipeline_llm", "generate_llm_fqn_per_model_part", "pipeline_module_s
 SINGLE_STAGE = {"GPipe", "1F1B"}
 MULTI_STAGE = {"Interleaved1F1B", "LoopedBFS", "InterleavedZeroBubble", "ZBVZeroBubble", "DualPipeV"}
 V_STYLE = {"ZBVZeroBubble", "DualPipeV"}
+ZERO_BUBBLE = {"InterleavedZeroBubble", "ZBVZeroBubble", "DualPipeV"}
 SCHEDULES = SINGLE_STAGE | MULTI_STAGE
 
 
@@ -464,4 +465,11 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
         num_stages=num_stages, n_microbatches=n_mb, loss_fn=loss_fn, style=style, device=device,
     )
     logger.info(f"Using pipeline schedule {schedule if not csv_path else csv_path} with {n_mb} microbatches and {num_stages} stages.")
+    if not csv_path and schedule in ZERO_BUBBLE:
+        # said at start-up, not only in the documentation: the name selects the stage placement, not a zero-bubble order
+        logger.warning(
+            f"Pipeline schedule {schedule}: this runtime does not split a backward step into its input-gradient and "
+            f"weight-gradient halves, so the schedule runs as {'a V-shaped' if schedule in V_STYLE else 'an'} interleaved 1F1B "
+            "(same stage placement and results, the bubble of 1F1B)."
+        )
     return sched, parts, sched.has_first, sched.has_last
