@@ -8,7 +8,7 @@ import torch
 
 def test_generate_greedy_and_top_k():
     from torchtitan_b200.models.llama3 import llama3_configs
-    from torchtitan_b200.scripts.generate._generation import generate, logits_to_probs
+    from torchtitan_b200.scripts.generate._generation import generate, top_k_filter
 
     torch.manual_seed(0)
     model = dataclasses.replace(llama3_configs["debugmodel"], n_layers=1).build()
@@ -20,8 +20,11 @@ def test_generate_greedy_and_top_k():
     c = generate(model, ids, max_new_tokens=4, temperature=1.0, top_k=5, seed=3)
     d = generate(model, ids, max_new_tokens=4, temperature=1.0, top_k=5, seed=3)
     assert torch.equal(c, d)
-    p = logits_to_probs(torch.tensor([[1.0, 2.0, 3.0, 4.0]]), 1.0, top_k=2)
-    assert (p[0, :2] == 0).all() and abs(p.sum().item() - 1) < 1e-6
+    f = top_k_filter(torch.tensor([[1.0, 2.0, 3.0, 4.0]]), 2)
+    assert torch.isinf(f[0, :2]).all() and f[0, 2:].tolist() == [3.0, 4.0]
+    # top-k restricts what can be drawn; nucleus sampling with a tiny p is greedy
+    e = generate(model, ids, max_new_tokens=3, temperature=1.0, top_p=1e-6, seed=1)
+    assert torch.equal(e, generate(model, ids, max_new_tokens=3, temperature=0))
 
 
 def test_loss_compare_parsing_and_compare(tmp_path):

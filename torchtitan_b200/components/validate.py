@@ -1,10 +1,15 @@
-"""Periodic validation. Parity: torchtitan/components/validate.py:30-314 -- runs on step 1 and
-every ``freq`` steps, re-uses the training context / AMP / context-parallel sharding / pipeline
-``eval``, and reports ``sum_over_steps(loss_sum / global_valid_tokens) / steps`` reduced over the
-``loss`` mesh."""
+"""Periodic validation: on step 1 and every ``freq`` steps the model scores ``steps`` batches of the validation
+loader and the mean token loss goes to the metrics processor.
+
+Same contract as torchtitan/components/validate.py:30-314 (per batch ``loss_sum / global_valid_tokens``, averaged over
+the batches, summed over the ``loss`` mesh; training context, AMP, context-parallel sharding and the pipeline's ``eval``
+are reused). The pass itself is organised differently: batches come from a bounded generator, each is scored by one of
+two scorers (pipeline / single model part), and the running mean stays on the device, so a validation pass reads one
+number back instead of synchronising once per batch."""
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field, replace
 
 import torch
@@ -76,44 +81,60 @@ class Validator(BaseValidator):
 
         return prepare_batch(input_dict, labels, model_parts, self.tokenizer, self.parallel_dims, self.parallelism)
 
-    @torch.no_grad()
-    def validate(self, model_parts: list[nn.Module], step: int) -> None:
+    # ------------------------------------------------------------------ one pass
+    def _batches(self):
+        """At most ``steps`` batches (all of them for -1), already on the device."""
+        dev = utils.device_type
+        for n, (input_dict, labels) in enumerate(self.validation_dataloader):
+            if self.config.steps != -1 and n >= self.config.steps:
+                return
+            self.metrics_processor.ntokens_since_last_log += labels.numel()
+            yield {k: v.to(dev) for k, v in input_dict.items()}, labels.to(dev)
+
+    def _score_pipeline(self, inputs, labels, extra_inputs, extra_kwargs) -> torch.Tensor:
+        last = self.pp_has_last_stage
+        targets, losses = (labels, []) if last else (None, None)
+        first_args = (inputs,) if self.pp_has_first_stage else ()
+        first_kwargs = extra_inputs if self.pp_has_first_stage else {}
+        with self.validation_context():
+            self.pp_schedule.eval(*first_args, **first_kwargs, **extra_kwargs, target=targets, losses=losses)
+        if not last:          # ranks without the last stage contribute nothing; the loss mesh sums the real value in
+            return torch.zeros((), device=utils.device_type) - 1.0
+        return torch.stack(losses).sum().to(utils.device_type)
+
+    def _score_single(self, model, inputs, labels, extra_inputs, extra_kwargs) -> torch.Tensor:
+        with self.validation_context(), self.maybe_enable_amp:
+            return self.loss_fn(model(inputs, **extra_inputs, **extra_kwargs), labels)
+
+    @contextlib.contextmanager
+    def _eval_mode(self, model_parts):
         for m in model_parts:
             m.eval()
+        try:
+            yield
+        finally:
+            for m in model_parts:
+                m.train()
+
+    @torch.no_grad()
+    def validate(self, model_parts: list[nn.Module], step: int) -> None:
         pd = self.parallel_dims
-        dev = utils.device_type
-        losses_acc, n = [], 0
-        for input_dict, labels in self.validation_dataloader:
-            if self.config.steps != -1 and n >= self.config.steps:
-                break
-            self.metrics_processor.ntokens_since_last_log += labels.numel()
-            input_dict = {k: v.to(dev) for k, v in input_dict.items()}
-            labels = labels.to(dev)
-            inputs, labels, extra_inputs, extra_kwargs = self.post_dataloading_process(input_dict, labels, model_parts)
-            valid = (labels != IGNORE_INDEX).sum().to(torch.float32)
-            if pd.dp_enabled:
-                torch.distributed.all_reduce(valid, group=pd.get_mesh("batch").get_group())
-            if pd.pp_enabled:
-                with self.validation_context():
-                    targets, losses = (labels, []) if self.pp_has_last_stage else (None, None)
-                    if self.pp_has_first_stage:
-                        self.pp_schedule.eval(inputs, **extra_inputs, **extra_kwargs, target=targets, losses=losses)
-                    else:
-                        self.pp_schedule.eval(**extra_kwargs, target=targets, losses=losses)
-                loss_sum = torch.sum(torch.stack(losses)).to(dev) if self.pp_has_last_stage else torch.tensor([-1.0], device=dev)
-            else:
-                with self.validation_context():
+        batch_group = pd.get_mesh("batch").get_group() if pd.dp_enabled else None
+        mean_sum, n = None, 0
+        with self._eval_mode(model_parts):
+            for input_dict, labels in self._batches():
+                inputs, labels, extra_inputs, extra_kwargs = self.post_dataloading_process(input_dict, labels, model_parts)
+                valid = (labels != IGNORE_INDEX).sum().to(torch.float32)
+                if batch_group is not None:
+                    torch.distributed.all_reduce(valid, group=batch_group)
+                if pd.pp_enabled:
+                    loss_sum = self._score_pipeline(inputs, labels, extra_inputs, extra_kwargs)
+                else:
                     assert len(model_parts) == 1
-                    with self.maybe_enable_amp:
-                        pred = model_parts[0](inputs, **extra_inputs, **extra_kwargs)
-                        loss_sum = self.loss_fn(pred, labels)
-            losses_acc.append(loss_sum.detach() / valid)
-            n += 1
-        loss = torch.sum(torch.stack(losses_acc)) / max(n, 1)
-        if pd.dp_cp_enabled:
-            global_avg = dist_utils.dist_sum(loss, pd.get_optional_mesh("loss"))
-        else:
-            global_avg = loss.item()
+                    loss_sum = self._score_single(model_parts[0], inputs, labels, extra_inputs, extra_kwargs)
+                term = (loss_sum.detach() / valid).reshape(())
+                mean_sum = term if mean_sum is None else mean_sum + term
+                n += 1
+        loss = (mean_sum if mean_sum is not None else torch.zeros((), device=utils.device_type)) / max(n, 1)
+        global_avg = dist_utils.dist_sum(loss, pd.get_optional_mesh("loss")) if pd.dp_cp_enabled else loss.item()
         self.metrics_processor.log_validation(loss=global_avg, step=step)
-        for m in model_parts:
-            m.train()

@@ -1,11 +1,12 @@
 """Text datasets packed into fixed-length training windows.
 
-Parity: torchtitan/hf_datasets/text_datasets.py:35-217 -- datasets ``c4`` (streamed),
-``c4_test`` (local ``tests/assets/c4_test``) and ``c4_validation``; each sample is encoded with
-BOS and EOS, appended to a rolling token buffer, and windows of ``seq_len + 1`` tokens are cut
-off as ``({"input": x[:-1]}, x[1:])``; samples are split over data-parallel ranks with
-``split_dataset_by_node``; the checkpoint state is the token buffer plus either the sample index
-(map-style) or the streaming dataset's own state; ``infinite`` re-loops.
+Behaviour of torchtitan/hf_datasets/text_datasets.py:35-217 -- datasets ``c4`` (streamed), ``c4_test`` (local
+``tests/assets/c4_test``) and ``c4_validation``; samples are split over data-parallel ranks with
+``split_dataset_by_node``, encoded with BOS and EOS and packed into windows of ``seq_len + 1`` tokens yielded as
+``({"input": x[:-1]}, x[1:])``; the checkpoint state (keys ``token_buffer`` and ``sample_idx`` or ``data``) resumes the
+stream exactly; ``infinite`` re-loops. Built here from three parts: a sample source per dataset kind (indexed /
+streaming) that knows its own position, a packer that owns the rolling buffer and cuts all complete windows of a sample
+at once, and the dataset that strings them together.
 """
 
 from __future__ import annotations
@@ -47,76 +48,118 @@ DATASETS = {
 }
 
 
-def _validate_dataset(name: str, path: str | None = None):
-    if name not in DATASETS:
-        raise ValueError(f"Dataset {name} is not supported. Supported datasets are: {list(DATASETS.keys())}")
-    cfg = DATASETS[name]
-    path = path or cfg.path
-    logger.info(f"Preparing {name} dataset from {path}")
-    return path, cfg.loader, cfg.sample_processor
+def register_dataset(name: str, config: DatasetConfig) -> None:
+    """Make another text dataset available to ``--dataloader.dataset``."""
+    DATASETS[name.lower()] = config
+
+
+def _lookup(name: str, path: str | None):
+    try:
+        cfg = DATASETS[name]
+    except KeyError:
+        raise ValueError(f"Dataset {name} is not supported. Supported datasets are: {list(DATASETS.keys())}") from None
+    logger.info(f"Preparing {name} dataset from {path or cfg.path}")
+    return cfg, path or cfg.path
+
+
+class _IndexedSource:
+    """A map-style dataset shard: position = number of samples consumed (checkpoint key ``sample_idx``)."""
+
+    def __init__(self, data):
+        self.data, self.pos = data, 0
+
+    def __iter__(self):
+        remaining = self.data.skip(self.pos) if self.pos < len(self.data) else ()
+        for sample in remaining:
+            self.pos += 1
+            yield sample
+
+    def rewind(self) -> None:
+        self.pos = 0
+
+    def state(self) -> dict[str, Any]:
+        return {"sample_idx": self.pos}
+
+    def restore(self, state: dict[str, Any]) -> None:
+        self.pos = state["sample_idx"]
+
+
+class _StreamSource:
+    """A streaming dataset shard: the position is whatever the stream reports about itself (checkpoint key ``data``)."""
+
+    def __init__(self, data):
+        self.data = data
+
+    def __iter__(self):
+        return iter(self.data)
+
+    def rewind(self) -> None:
+        if hasattr(self.data, "set_epoch") and hasattr(self.data, "epoch"):
+            self.data.set_epoch(self.data.epoch + 1)     # a new epoch reshuffles the shards
+
+    def state(self) -> dict[str, Any]:
+        return {"data": self.data.state_dict()}
+
+    def restore(self, state: dict[str, Any]) -> None:
+        assert "data" in state, "checkpoint of a streaming dataset lacks the stream position"
+        self.data.load_state_dict(state["data"])
+
+
+class _Packer:
+    """Rolling token buffer cut into windows of ``seq_len + 1`` tokens; a window gives inputs ``[:-1]`` and labels ``[1:]``."""
+
+    def __init__(self, seq_len: int):
+        self.window = seq_len + 1
+        self.tokens: list[int] = []
+
+    def feed(self, ids):
+        self.tokens.extend(ids)
+        cut = len(self.tokens) - len(self.tokens) % self.window
+        if not cut:
+            return
+        full, self.tokens = torch.tensor(self.tokens[:cut], dtype=torch.long).view(-1, self.window), self.tokens[cut:]
+        pending = full.unbind(0)
+        for k, row in enumerate(pending):
+            # a consumer that checkpoints between two windows of one sample must find the later windows in the buffer
+            rest = [t for r in pending[k + 1:] for t in r.tolist()]
+            saved, self.tokens = self.tokens, rest + self.tokens
+            yield {"input": row[:-1]}, row[1:]
+            self.tokens = saved
 
 
 class HuggingFaceTextDataset(IterableDataset, Stateful):
+    """Samples of this data-parallel rank -> text -> tokens (BOS ... EOS) -> packed windows. Checkpoint state: the
+    packer's left-over tokens plus the source position."""
+
     def __init__(self, dataset_name: str, dataset_path: str | None, tokenizer, seq_len: int = 2048,
                  dp_rank: int = 0, dp_world_size: int = 1, infinite: bool = False) -> None:
+        from datasets import Dataset
         from datasets.distributed import split_dataset_by_node
 
-        dataset_name = dataset_name.lower()
-        path, loader, to_text = _validate_dataset(dataset_name, dataset_path)
-        self.dataset_name = dataset_name
-        self._data = split_dataset_by_node(loader(path), dp_rank, dp_world_size)
-        self._tokenizer = tokenizer
-        self.seq_len = seq_len
-        self.infinite = infinite
-        self._to_text = to_text
-        self._sample_idx = 0
-        self._token_buffer: list[int] = []
-
-    def _is_map_style(self) -> bool:
-        from datasets import Dataset
-
-        return isinstance(self._data, Dataset)
-
-    def _samples(self):
-        if self._is_map_style():
-            if self._sample_idx == len(self._data):
-                return iter(())
-            return iter(self._data.skip(self._sample_idx))
-        return iter(self._data)
+        self.dataset_name = dataset_name.lower()
+        cfg, path = _lookup(self.dataset_name, dataset_path)
+        shard = split_dataset_by_node(cfg.loader(path), dp_rank, dp_world_size)
+        self._source = _IndexedSource(shard) if isinstance(shard, Dataset) else _StreamSource(shard)
+        self._to_text, self._tokenizer = cfg.sample_processor, tokenizer
+        self._packer = _Packer(seq_len)
+        self.seq_len, self.infinite = seq_len, infinite
 
     def __iter__(self):
-        window = self.seq_len + 1
         while True:
-            for sample in self._samples():
-                self._token_buffer.extend(self._tokenizer.encode(self._to_text(sample), add_bos=True, add_eos=True))
-                self._sample_idx += 1
-                while len(self._token_buffer) >= window:
-                    x = torch.LongTensor(self._token_buffer[:window])
-                    self._token_buffer = self._token_buffer[window:]
-                    yield {"input": x[:-1]}, x[1:]
+            for sample in self._source:
+                yield from self._packer.feed(self._tokenizer.encode(self._to_text(sample), add_bos=True, add_eos=True))
             if not self.infinite:
                 logger.warning(f"Dataset {self.dataset_name} has run out of data")
                 return
-            self._sample_idx = 0
             logger.warning(f"Dataset {self.dataset_name} is being re-looped")
-            if not self._is_map_style() and hasattr(self._data, "set_epoch") and hasattr(self._data, "epoch"):
-                self._data.set_epoch(self._data.epoch + 1)
+            self._source.rewind()
 
     def state_dict(self):
-        sd: dict[str, Any] = {"token_buffer": self._token_buffer}
-        if self._is_map_style():
-            sd["sample_idx"] = self._sample_idx
-        else:
-            sd["data"] = self._data.state_dict()
-        return sd
+        return {"token_buffer": list(self._packer.tokens), **self._source.state()}
 
     def load_state_dict(self, state_dict):
-        self._token_buffer = state_dict["token_buffer"]
-        if self._is_map_style():
-            self._sample_idx = state_dict["sample_idx"]
-        else:
-            assert "data" in state_dict
-            self._data.load_state_dict(state_dict["data"])
+        self._packer.tokens = list(state_dict["token_buffer"])
+        self._source.restore(state_dict)
 
 
 class HuggingFaceTextDataLoader(ParallelAwareDataloader):
