@@ -359,3 +359,60 @@ def test_nvlink_staging_wait_is_needed_only_between_micro_batches_of_one_step():
     assert comm.needs_staging_wait(unit)                           # second micro-batch of the same optimizer step
     unit.params_version = 4                                        # the optimizer ran: all-gather flags order the reuse
     assert not comm.needs_staging_wait(unit)
+
+
+def _bucket_worker(rank, world, variant):
+    """Llama debug model through ``apply_fsdp`` with the plan knobs of the graph trainer; returns losses and unit count."""
+    import dataclasses
+    from types import SimpleNamespace
+
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.models.llama3 import llama3_configs
+    from torchtitan_b200.parallel import ParallelDims, fsdp
+    from torchtitan_b200.parallel.data_parallel import apply_fsdp
+
+    par = SimpleNamespace(fused_fsdp_collectives=False, fsdp_prefetch_depth=1, fsdp_bucket_bytes=0, fsdp_extra_process_group=False)
+    for k, v in variant.items():
+        setattr(par, k, v)
+    pd = ParallelDims(dp_replicate=1, dp_shard=world, cp=1, tp=1, pp=1, ep=1, etp=1, world_size=world)
+    cfg = dataclasses.replace(llama3_configs["debugmodel"])
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=64)
+    torch.manual_seed(5)
+    model = cfg.build()
+    model.init_weights()
+    apply_fsdp(model, pd.get_mesh("fsdp"), param_dtype=torch.float32, reduce_dtype=torch.float32, pp_enabled=False,
+               parallelism=par)
+    fsdp.materialize(model)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    g = torch.Generator().manual_seed(rank)
+    losses = []
+    for _ in range(3):
+        x = torch.randint(0, cfg.vocab_size, (2, 65), generator=g)
+        opt.zero_grad()
+        loss = cross_entropy_loss(model(x[:, :-1]), x[:, 1:]) / (2 * 64 * world)
+        loss.backward()
+        opt.step()
+        for u in fsdp.fsdp_units(model):
+            u.mark_params_updated()
+        l = loss.detach().clone()
+        dist.all_reduce(l)
+        losses.append(l.item())
+    units = fsdp.fsdp_units(model)
+    return losses, len(units), {u.prefetch_depth for u in units}
+
+
+def test_bucketed_units_prefetch_depth_and_gather_group_keep_the_numbers(tmp_path):
+    """What the graph trainer's plan sets on the FSDP runtime: grouping blocks into larger units, gathering two units
+    ahead and a separate process group for all-gathers change the schedule, not the arithmetic."""
+    for sub in "abc":
+        (tmp_path / sub).mkdir()
+    base = run_ranks(_bucket_worker, 2, {}, tmp_path=tmp_path / "a")[0]
+    big = run_ranks(_bucket_worker, 2, {"fsdp_bucket_bytes": 1 << 30, "fsdp_prefetch_depth": 2}, tmp_path=tmp_path / "b")[0]
+    pg = run_ranks(_bucket_worker, 2, {"fsdp_extra_process_group": True}, tmp_path=tmp_path / "c")[0]
+    assert base[1] == 6 + 3 and big[1] == 1 + 3                  # 6 blocks -> one bucket; embedding, [norm, output], root stay
+    assert base[2] == {1} and big[2] == {2}
+    assert big[0] == pytest.approx(base[0], rel=1e-6) and pg[0] == pytest.approx(base[0], rel=1e-6)
+    assert base[0][1] != base[0][0]                              # the optimizer steps in between did change the model

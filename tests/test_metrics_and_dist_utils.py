@@ -151,6 +151,7 @@ def test_trainer_raises_when_a_kernel_reports_an_expired_wait(monkeypatch):
     from torchtitan_b200.trainer import Trainer
 
     fake = types.SimpleNamespace(device=torch.device("cuda"), step=7)
+    fake._kernel_error_words = types.MethodType(Trainer._kernel_error_words, fake)
     monkeypatch.setattr(native, "available", lambda: True)
     monkeypatch.setattr(native, "kernel_errors", lambda: {})
     Trainer._raise_on_kernel_errors(fake)                         # nothing reported: no error

@@ -1,9 +1,12 @@
 """Plan passes of the graph trainer.
 
 Names follow torchtitan/experiments/graph_trainer/passes.py:38-408. Each pass receives the mutable
-:class:`StepPlan` and edits it; ``build_plan`` runs the configured passes in order. The plan is then honoured by
-``simple_fsdp.data_parallel`` (bucketing / prefetch / reshard / extra process group), by activation checkpointing
-(``apply_sac``) and by the trainer (``cudagraph``)."""
+:class:`StepPlan` and edits it; ``build_plan`` runs the configured passes in order. ``GraphTrainer`` then turns the plan
+into settings of the FSDP runtime that the job really runs with: ``parallelism.fsdp_bucket_bytes`` (auto bucketing:
+consecutive blocks grouped into one unit), ``fsdp_prefetch_depth`` (units gathered ahead), ``fsdp_reshard_after_forward``,
+``fsdp_extra_process_group`` (all-gathers on their own communicator with the c10d transport), per-op activation
+checkpointing (``apply_sac``) and CUDA-graph capture of the step (``cudagraph``). ``simple_fsdp.data_parallel`` applies the
+same plan to a bare module (the reference's entry point of that name)."""
 
 from __future__ import annotations
 

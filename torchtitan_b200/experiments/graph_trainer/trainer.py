@@ -25,6 +25,10 @@ class GraphTrainer(Trainer):
         if self.plan.reshard_after_forward != "default":
             config.parallelism.fsdp_reshard_after_forward = self.plan.reshard_after_forward
         config.parallelism.fsdp_prefetch_depth = max(getattr(config.parallelism, "fsdp_prefetch_depth", 1), self.plan.prefetch_depth)
+        if self.plan.bucketing == "auto":
+            config.parallelism.fsdp_bucket_bytes = self.plan.bucket_bytes      # consecutive blocks share one FSDP unit
+        if self.plan.extra_fsdp_pg:
+            config.parallelism.fsdp_extra_process_group = True
         if self.plan.sac_save_ops is not None and config.activation_checkpoint.mode == "none":
             config.activation_checkpoint.mode, config.activation_checkpoint.selective_ac_option = "selective", "op"
         super().__init__(config)

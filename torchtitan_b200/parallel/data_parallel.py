@@ -43,18 +43,61 @@ def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype
         reshard_after_forward_policy, pp_enabled, param_bytes=_compute_copy_bytes(model, param_dtype)
     )
     comm = make_comm(dp_mesh, parallelism, model=model, param_dtype=param_dtype)
+    if comm is None and getattr(parallelism, "fsdp_extra_process_group", False) and dp_mesh is not None:
+        import torch.distributed as dist
+
+        from .fsdp import C10dComm
+
+        shard_mesh = dp_mesh[dp_mesh.mesh_dim_names[-1]] if dp_mesh.ndim == 2 else dp_mesh
+        # new_group is collective over the whole job: every rank creates every shard group and keeps its own
+        ranks_mine = dist.get_process_group_ranks(shard_mesh.get_group())
+        all_sets = [None] * dist.get_world_size()
+        dist.all_gather_object(all_sets, tuple(ranks_mine))
+        own = None
+        for ranks in sorted(set(all_sets)):
+            g = dist.new_group(list(ranks))
+            if tuple(ranks_mine) == ranks:
+                own = g
+        comm = C10dComm(gather_group=own)
+        logger.info("FSDP all-gathers use a process group of their own")
     kw = dict(mesh=dp_mesh, mp_policy=mp, comm=comm)
     if getattr(model, "tok_embeddings", None) is not None:
         fully_shard(model.tok_embeddings, **kw, reshard_after_forward=reshard)
+    bucket_bytes = int(getattr(parallelism, "fsdp_bucket_bytes", 0) or 0)
+    elem = torch.empty((), dtype=param_dtype).element_size()
+    group, group_bytes = [], 0
+
+    def flush():
+        nonlocal group, group_bytes
+        if group:
+            fully_shard(group if len(group) > 1 else group[0], **kw, reshard_after_forward=reshard)
+        group, group_bytes = [], 0
+
     for block in model.layers.values():
         if efsdp_mesh is not None and getattr(block, "moe_enabled", False):
             # MoE-aware FSDP: expert-parallel weights are only replicated over the efsdp ranks
             fully_shard(block.moe.experts, mesh=efsdp_mesh, mp_policy=mp, reshard_after_forward=reshard)
-        fully_shard(block, **kw, reshard_after_forward=reshard)
+        if bucket_bytes <= 0:
+            fully_shard(block, **kw, reshard_after_forward=reshard)
+            continue
+        # bucketed units: consecutive blocks share one unit (one gather / one reduce for the whole group)
+        n = sum(p.numel() for p in block.parameters()) * elem
+        if group and group_bytes + n > bucket_bytes:
+            flush()
+        group.append(block)
+        group_bytes += n
+    flush()
     if getattr(model, "norm", None) is not None and getattr(model, "output", None) is not None:
         fully_shard([model.norm, model.output], **kw, reshard_after_forward=reshard_after_forward_policy == "always")
     fully_shard(model, **kw, reshard_after_forward=reshard)
-    logger.info(f"FSDP units: reshard_after_forward={reshard}, transport={'nvlink' if comm is not None else 'c10d'}")
+    from .fsdp import fsdp_units
+
+    depth = max(int(getattr(parallelism, "fsdp_prefetch_depth", 1) or 1), 1)
+    units = fsdp_units(model)
+    for u in units:
+        u.prefetch_depth = depth
+    logger.info(f"FSDP: {len(units)} units, reshard_after_forward={reshard}, prefetch depth {depth}, "
+                f"transport={'nvlink' if comm is not None and type(comm).__name__ == 'NvlinkComm' else 'c10d'}")
     return model
 
 

@@ -124,10 +124,14 @@ class ShardComm:
 
 
 class C10dComm(ShardComm):
-    """c10d collectives issued per parameter directly on the parameter-contiguous layout."""
+    """c10d collectives issued per parameter directly on the parameter-contiguous layout. ``gather_group``: an optional
+    second process group over the same ranks used by the all-gathers only."""
+
+    def __init__(self, gather_group=None):
+        self.gather_group = gather_group
 
     def all_gather(self, unit):
-        W, g = unit.shard_world, unit.shard_group
+        W, g = unit.shard_world, self.gather_group or unit.shard_group
         src_flat = unit.gather_source()
         works = []
         for p in unit.params:
@@ -306,6 +310,7 @@ class FSDPUnit:
         self._slot_written: list = []
         self._slot_accumulate = False
         self.is_root = False
+        self.prefetch_depth = 1  # units gathered ahead of the one that computes (forward: next, backward: prev)
         self.prev: FSDPUnit | None = None
         self.next: FSDPUnit | None = None
         modules[0].register_forward_pre_hook(self._pre_forward, with_kwargs=True, prepend=True)
@@ -535,8 +540,12 @@ class FSDPUnit:
             return cast_result  # recompute inside backward, a re-entrant call, or nothing to gather
         self._forward_active = True
         self.unshard()
-        if self.next is not None and not self.next._in_backward:
-            self.next.unshard(async_op=True)
+        ahead = self.next
+        for _ in range(max(self.prefetch_depth, 1)):
+            if ahead is None or ahead._in_backward:
+                break
+            ahead.unshard(async_op=True)
+            ahead = ahead.next
         if self._needs_grad():
             outs = _UnitGather.apply(self, self._anchor)
         else:
@@ -590,8 +599,12 @@ class FSDPUnit:
             if guard is not None:
                 guard(self)  # peers may still be reading the staging buffer of the previous micro-batch
             self.unshard()
-            if self.prev is not None and self.prev.reshard_after_forward and not self.prev._in_backward:
-                self.prev.unshard(async_op=True)
+            behind = self.prev
+            for _ in range(max(self.prefetch_depth, 1)):
+                if behind is None or not behind.reshard_after_forward or behind._in_backward:
+                    break
+                behind.unshard(async_op=True)
+                behind = behind.prev
             self._bind(fwd_params if fwd_params is not None else tuple(p.unsharded for p in self.params))
             _BackwardEnd.register(self)
         return grad
