@@ -520,3 +520,67 @@ def test_mx_linear_op_matches_definition(ops, rows, K, N):
     assert _rel(w.grad, mm(g2.t(), xd.t())) < 1e-2
     # and close to the unquantised product (e4m3 keeps 3 mantissa bits)
     assert _rel(y.view(rows, N), xd.float() @ wd.float().t()) < 8e-2
+
+
+@pytest.mark.parametrize("Dqk,Dv,H,Hkv", [(64, 64, 8, 2), (192, 128, 4, 4), (128, 128, 4, 2)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_forward_head_dims(ops, Dqk, Dv, H, Hkv, causal):
+    """Forward kernel instantiations for GPT-OSS (64/64) and multi-head latent attention (192 query/key, 128 value)."""
+    from torchtitan_b200.ops import native
+
+    if not native.has("tt_attn_fwd_dims"):
+        pytest.skip("library built without tt_attn_fwd_dims")
+    torch.manual_seed(0)
+    B, S = 2, 512
+    q = torch.randn(B, S, H, Dqk, device="cuda").bfloat16()
+    k = torch.randn(B, S, Hkv, Dqk, device="cuda").bfloat16()
+    v = torch.randn(B, S, Hkv, Dv, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(Dqk)
+    o, lse = torch.ops.tt_b200.attention_fwd(q, k, v, causal, scale)
+    _no_kernel_errors()
+    g = H // Hkv
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float().repeat_interleave(g, 2)) * scale
+    if causal:
+        s = s.masked_fill(torch.ones(S, S, device="cuda", dtype=torch.bool).triu(1), float("-inf"))
+    want = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v.float().repeat_interleave(g, 2))
+    assert o.shape == (B, S, H, Dv)
+    assert _rel(o, want) < 2e-2, _rel(o, want)
+    assert (lse - torch.logsumexp(s, -1)).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("Dqk,Dv,H,Hkv", [(64, 64, 8, 2), (192, 128, 4, 4), (192, 128, 8, 2)])
+@pytest.mark.parametrize("mask", ["causal", "full", "window"])
+def test_attention_other_head_dims_forward_and_backward(ops, Dqk, Dv, H, Hkv, mask):
+    """GPT-OSS (64/64, sliding window and sinks elsewhere) and latent-attention (192/128) head dimensions through the
+    kernels, forward and backward, against the fp32 definition."""
+    from torchtitan_b200.ops import native, reference as ref
+
+    if not native.has("tt_attn_bwd_dims"):
+        pytest.skip("library built without tt_attn_bwd_dims")
+    torch.manual_seed(3)
+    B, S = 2, 512
+    q = torch.randn(B, S, H, Dqk, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, S, Hkv, Dqk, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, S, Hkv, Dv, device="cuda").bfloat16().requires_grad_()
+    assert ops.attention_supported(q, k, v)
+    kw = dict(causal=mask != "full", window=100 if mask == "window" else None)
+    o = ops.attention(q, k, v, **kw)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _no_kernel_errors()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    # fp32 definition (masked path of the reference module; scale = 1/sqrt(Dqk))
+    g = H // Hkv
+    s = torch.einsum("bqhd,bkhd->bhqk", qr, kr.repeat_interleave(g, 2)) / math.sqrt(Dqk)
+    idx = torch.arange(S, device="cuda")
+    dead = torch.zeros(S, S, dtype=torch.bool, device="cuda")
+    if kw["causal"]:
+        dead |= idx.view(1, S) > idx.view(S, 1)
+    if kw["window"]:
+        dead |= idx.view(1, S) <= idx.view(S, 1) - kw["window"]
+    orf = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s.masked_fill(dead, float("-inf")), -1), vr.repeat_interleave(g, 2))
+    orf.backward(do.float())
+    assert _rel(o, orf) < 2e-2, _rel(o, orf)
+    assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)

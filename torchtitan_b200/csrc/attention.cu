@@ -115,13 +115,25 @@ constexpr uint32_t IDESC_128x64_KK = tt::umma_idesc_bf16(128, 64, 0, 0);
 constexpr uint32_t IDESC_128x128_KM = tt::umma_idesc_bf16(128, 128, 0, 1);
 
 // =================================================================================== forward
-// smem: Q 32K | K 2x16K | V 16K | P 16K | barriers  (small enough for two CTAs per SM)
-constexpr uint32_t F_Q = 0, F_K = 32768, F_V = F_K + 32768, F_P = F_V + 16384, F_BAR = F_P + 16384;
-constexpr size_t FWD_SMEM = 1024 + F_BAR + 256;
+// Head dimensions are template parameters: DQK for queries / keys, DV for values and the output (128/128 Llama and
+// Qwen, 64/64 GPT-OSS, 192/128 multi-head latent attention). An operand of width W lives in shared memory as W / 64
+// chunks of [rows][128 bytes] (one 128-byte swizzle atom wide), chunk c holding elements 64c .. 64c + 63.
+// smem: Q (DQK/64) x 16K | K 2 stages x (DQK/64) x 8K | V (DV/64) x 8K | barriers  (two CTAs per SM)
+template <int DQK, int DV>
+struct FwdLayout {
+  static constexpr int QC = DQK / 64, VC = DV / 64;
+  static constexpr uint32_t Q = 0, K = QC * 16384, KSTAGE = QC * 8192, V = K + 2 * KSTAGE, VBYTES = VC * 8192,
+                            BAR = V + VBYTES;
+  static constexpr size_t SMEM = 1024 + BAR + 256;
+};
 
+template <int DQK, int DV>
 __global__ void __launch_bounds__(192, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, AttnArgs p) {
+  using L = FwdLayout<DQK, DV>;
+  constexpr uint32_t F_Q = L::Q, F_K = L::K, F_V = L::V, F_BAR = L::BAR;
+  constexpr uint32_t IDESC_PV = tt::umma_idesc_bf16(128, DV, 0, 1);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
@@ -154,28 +166,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   tt::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;  // S buffers at cols 0 and 64, O at 128..255
+  const uint32_t tS = tmem, tO = tmem + 128;  // S buffers at cols 0 and 64, O at 128 .. 128 + DV
 
   if (warp == 0) {
     if (tt::elect_one()) {
-      tt::mbar_expect_tx(bar(0), 32768);
-      tt::tma_load_3d(base + F_Q, &tq, bar(0), 0, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + F_Q + 16384, &tq, bar(0), 64, h, b * p.Sq + q0);
+      tt::mbar_expect_tx(bar(0), L::QC * 16384);
+#pragma unroll
+      for (int c = 0; c < L::QC; ++c) tt::tma_load_3d(base + F_Q + c * 16384, &tq, bar(0), c * 64, h, b * p.Sq + q0);
       auto load_k = [&](int j) -> bool {
         const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
         if (!tt::mbar_wait(bar(3 + s), ph ^ 1, abort_flag, &g_attn_error, 11)) return false;
-        tt::mbar_expect_tx(bar(1 + s), 16384);
-        tt::tma_load_3d(base + F_K + s * 16384, &tk, bar(1 + s), 0, hk, b * p.Sk + (j0 + j) * 64);
-        tt::tma_load_3d(base + F_K + s * 16384 + 8192, &tk, bar(1 + s), 64, hk, b * p.Sk + (j0 + j) * 64);
+        tt::mbar_expect_tx(bar(1 + s), L::KSTAGE);
+#pragma unroll
+        for (int c = 0; c < L::QC; ++c)
+          tt::tma_load_3d(base + F_K + s * L::KSTAGE + c * 8192, &tk, bar(1 + s), c * 64, hk, b * p.Sk + (j0 + j) * 64);
         return true;
       };
       bool ok = n_kv > 0 ? load_k(0) : true;
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv && !load_k(j + 1)) break;  // K runs one tile ahead of V
         if (!tt::mbar_wait(bar(7), (j & 1) ^ 1, abort_flag, &g_attn_error, 12)) break;
-        tt::mbar_expect_tx(bar(5), 16384);
-        tt::tma_load_3d(base + F_V, &tv, bar(5), 0, hk, b * p.Sk + (j0 + j) * 64);
-        tt::tma_load_3d(base + F_V + 8192, &tv, bar(5), 64, hk, b * p.Sk + (j0 + j) * 64);
+        tt::mbar_expect_tx(bar(5), L::VBYTES);
+#pragma unroll
+        for (int c = 0; c < L::VC; ++c) tt::tma_load_3d(base + F_V + c * 8192, &tv, bar(5), c * 64, hk, b * p.Sk + (j0 + j) * 64);
       }
     }
   } else if (warp == 1) {
@@ -186,9 +199,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const tt::SmemDesc dV = tt::make_smem_desc(base + F_V, (64 * 128) >> 4, 64);
       auto issue_s = [&](int j) {
         const int s = j & 1;
-        const tt::SmemDesc kd = dK0.at(s * 16384);
+        const tt::SmemDesc kd = dK0.at(s * L::KSTAGE);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
+        for (int kk = 0; kk < DQK / 16; ++kk)
           tt::umma_f16_ss(tS + s * 64, dQ.at((kk >> 2) * 16384 + (kk & 3) * 32), kd.at((kk >> 2) * 8192 + (kk & 3) * 32),
                           IDESC_128x64_KK, kk != 0);
         tt::umma_commit(bar(9 + s));   // S ready
@@ -214,7 +227,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         // memory, so neither the softmax warps' stores nor this MMA's A reads touch shared memory
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ts(tO, tS + s * 64 + kk * 8, dV.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+          tt::umma_f16_ts(tO, tS + s * 64 + kk * 8, dV.at(kk * 2048), IDESC_PV, kk ? 1u : acc0);
         tt::umma_commit(bar(12));      // O updated, P free
         tt::umma_commit(bar(7));       // V buffer free
       }
@@ -270,7 +283,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         m_ref = m_new;
         l *= f;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < DV / 16; ++c) {
           uint32_t r[16];
           tt::tmem_ld_32x16(tO + lane_off + c * 16, r);
           tt::tc_wait_ld();
@@ -316,9 +329,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       const float inv = (l > 0.f) ? o_scale / l : 0.f;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) +
-                            ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * D;
+                            ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * DV;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < DV / 32; ++c) {
         uint32_t r[32];
         if (n_kv > 0) { tt::tmem_ld_32x32(tO + lane_off + c * 32, r); tt::tc_wait_ld(); }
         else {
@@ -345,18 +358,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 }
 
 // =================================================================================== backward: dQ
-// CTA = 128 query rows. smem: Q 32K | dO 32K | K/V ring NS x (16K + 16K) | dS 2x16K | barriers
-constexpr int Q_NS = 3;  // K/V stages: a stage is reloaded only after the dQ MMAs that read it have
-                         // completed, so the ring must cover TMA latency plus one full step
-constexpr uint32_t Q_Q = 0, Q_DO = 32768, Q_KV = 65536, Q_DS = Q_KV + Q_NS * 32768, Q_BAR = Q_DS + 32768;
-constexpr size_t DQ_SMEM = 1024 + Q_BAR + 256;
-// barriers
-constexpr int QB_QFULL = 0, QB_KVFULL = 1, QB_KVEMPTY = QB_KVFULL + Q_NS, QB_SPFULL = QB_KVEMPTY + Q_NS,
+// CTA = 128 query rows. smem: Q (DQK/64) x 16K | dO (DV/64) x 16K | K/V ring NS x ((DQK/64) x 8K + (DV/64) x 8K) |
+// dS 2 x 16K | barriers. A K/V stage is reloaded only after the dQ MMAs that read it have completed, so the ring must
+// cover TMA latency plus one full step: three stages where they fit (two for the 192/128 head dimensions).
+template <int DQK, int DV>
+struct DqLayout {
+  static constexpr int QC = DQK / 64, VC = DV / 64;
+  static constexpr int NS = (QC * 16384 + VC * 16384 + 3 * (QC + VC) * 8192 + 32768 <= 220 * 1024) ? 3 : 2;
+  static constexpr uint32_t Q = 0, DO = QC * 16384, KV = DO + VC * 16384, KBYTES = QC * 8192, STAGE = (QC + VC) * 8192,
+                            DS = KV + NS * STAGE, BAR = DS + 32768;
+  static constexpr size_t SMEM = 1024 + BAR + 256;
+};
+// barriers (sized for the largest ring)
+constexpr int QB_QFULL = 0, QB_KVFULL = 1, QB_KVEMPTY = QB_KVFULL + 3, QB_SPFULL = QB_KVEMPTY + 3,
               QB_DSREADY = QB_SPFULL + 2, QB_DSFREE = QB_DSREADY + 2, QB_COUNT = QB_DSFREE + 2;
 
+template <int DQK, int DV>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                    const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv, AttnArgs p) {
+  using L = DqLayout<DQK, DV>;
+  constexpr int Q_NS = L::NS;
+  constexpr uint32_t Q_Q = L::Q, Q_DO = L::DO, Q_KV = L::KV, Q_DS = L::DS, Q_BAR = L::BAR;
+  constexpr uint32_t IDESC_DQ = tt::umma_idesc_bf16(128, DQK, 0, 1);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
@@ -386,25 +410,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   __syncthreads();
   tt::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: S[2] at 0,64 | dP[2] at 128,192 | dQ at 256..383
+  // TMEM columns: S[2] at 0,64 | dP[2] at 128,192 | dQ at 256 .. 256 + DQK
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
 
   if (warp == 0) {
     if (tt::elect_one()) {
-      tt::mbar_expect_tx(bar(QB_QFULL), 65536);
-      tt::tma_load_3d(base + Q_Q, &tq, bar(QB_QFULL), 0, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + Q_Q + 16384, &tq, bar(QB_QFULL), 64, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + Q_DO, &tdo, bar(QB_QFULL), 0, h, b * p.Sq + q0);
-      tt::tma_load_3d(base + Q_DO + 16384, &tdo, bar(QB_QFULL), 64, h, b * p.Sq + q0);
+      tt::mbar_expect_tx(bar(QB_QFULL), (L::QC + L::VC) * 16384);
+#pragma unroll
+      for (int c = 0; c < L::QC; ++c) tt::tma_load_3d(base + Q_Q + c * 16384, &tq, bar(QB_QFULL), c * 64, h, b * p.Sq + q0);
+#pragma unroll
+      for (int c = 0; c < L::VC; ++c) tt::tma_load_3d(base + Q_DO + c * 16384, &tdo, bar(QB_QFULL), c * 64, h, b * p.Sq + q0);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % Q_NS; const uint32_t ph = (j / Q_NS) & 1;
         if (!tt::mbar_wait(bar(QB_KVEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 21)) break;
-        const uint32_t kb = base + Q_KV + s * 32768, vb = kb + 16384;
-        tt::mbar_expect_tx(bar(QB_KVFULL + s), 32768);
-        tt::tma_load_3d(kb, &tk, bar(QB_KVFULL + s), 0, hk, b * p.Sk + (j0 + j) * 64);
-        tt::tma_load_3d(kb + 8192, &tk, bar(QB_KVFULL + s), 64, hk, b * p.Sk + (j0 + j) * 64);
-        tt::tma_load_3d(vb, &tv, bar(QB_KVFULL + s), 0, hk, b * p.Sk + (j0 + j) * 64);
-        tt::tma_load_3d(vb + 8192, &tv, bar(QB_KVFULL + s), 64, hk, b * p.Sk + (j0 + j) * 64);
+        const uint32_t kb = base + Q_KV + s * L::STAGE, vb = kb + L::KBYTES;
+        tt::mbar_expect_tx(bar(QB_KVFULL + s), L::STAGE);
+#pragma unroll
+        for (int c = 0; c < L::QC; ++c) tt::tma_load_3d(kb + c * 8192, &tk, bar(QB_KVFULL + s), c * 64, hk, b * p.Sk + (j0 + j) * 64);
+#pragma unroll
+        for (int c = 0; c < L::VC; ++c) tt::tma_load_3d(vb + c * 8192, &tv, bar(QB_KVFULL + s), c * 64, hk, b * p.Sk + (j0 + j) * 64);
       }
     }
   } else if (warp == 1) {
@@ -414,12 +438,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         const int s = j % Q_NS, t2 = j & 1;
         if (!tt::mbar_wait(bar(QB_KVFULL + s), (j / Q_NS) & 1, abort_flag, &g_attn_error, 23)) return false;
         tt::tc_fence_after();
-        const uint32_t kb = base + Q_KV + s * 32768, vb = kb + 16384;
+        const uint32_t kb = base + Q_KV + s * L::STAGE, vb = kb + L::KBYTES;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
+        for (int kk = 0; kk < DQK / 16; ++kk)
           tt::umma_f16_ss(tS + t2 * 64, desc_kmajor_dh(base + Q_Q, 128, kk), desc_kmajor_dh(kb, 64, kk), IDESC_128x64_KK, kk != 0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
+        for (int kk = 0; kk < DV / 16; ++kk)
           tt::umma_f16_ss(tDP + t2 * 64, desc_kmajor_dh(base + Q_DO, 128, kk), desc_kmajor_dh(vb, 64, kk), IDESC_128x64_KK, kk != 0);
         tt::umma_commit(bar(QB_SPFULL + t2));
         return true;
@@ -430,10 +454,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         const int s = j % Q_NS, t2 = j & 1;
         if (!tt::mbar_wait(bar(QB_DSREADY + t2), (j >> 1) & 1, abort_flag, &g_attn_error, 25)) break;
         tt::tc_fence_after();
-        const uint32_t kb = base + Q_KV + s * 32768;
+        const uint32_t kb = base + Q_KV + s * L::STAGE;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          tt::umma_f16_ss(tDQ, desc_kmajor_64(base + Q_DS + t2 * 16384, kk), desc_mnmajor(kb, 64, kk), IDESC_128x128_KM, (j | kk) != 0);
+          tt::umma_f16_ss(tDQ, desc_kmajor_64(base + Q_DS + t2 * 16384, kk), desc_mnmajor(kb, 64, kk), IDESC_DQ, (j | kk) != 0);
         tt::umma_commit(bar(QB_DSFREE + t2));   // dS buffer free, dQ step done
         tt::umma_commit(bar(QB_KVEMPTY + s));   // K/V stage free
       }
@@ -477,9 +501,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     if (ok && n_kv > 0) ok = tt::mbar_wait(bar(QB_DSFREE + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag, &g_attn_error, 28);
     tt::tc_fence_after();
     if (ok) {
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * D;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + ((static_cast<long long>(b) * p.Sq + qi) * p.H + h) * DQK;
+      constexpr int CH = DQK / 64;    // 32-column chunks per warp half
 #pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
+      for (int c = half * CH; c < half * CH + CH; ++c) {
         uint32_t r[32];
         if (n_kv > 0) { tt::tmem_ld_32x32(tDQ + lane_off + c * 32, r); tt::tc_wait_ld(); }
         else {
@@ -690,9 +715,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 constexpr int FB_KVFULL = 0, FB_QFULL = 1, FB_QEMPTY = FB_QFULL + K_NS, FB_STFULL = FB_QEMPTY + K_NS,
               FB_STFREE = FB_STFULL + 1, FB_PTREADY = FB_STFREE + 1, FB_PTFREE = FB_PTREADY + 2,
               FB_DQFULL = FB_PTFREE + 2, FB_DQFREE = FB_DQFULL + 1, FB_PFREE = FB_DQFREE + 1, FB_COUNT = FB_PFREE + 1;
-constexpr uint32_t K_DQS = K_PT + 16384;   // dQ staging tile (second half of the two-kernel form's P^T double buffer)
-constexpr uint32_t K_STAT = K_BAR + 256;   // per stage: 64 x (-lse * log2 e) then 64 x (-delta * scale), fp32
-constexpr size_t FUSED_SMEM = DKV_SMEM + K_NS * 512;
+// Head dimensions are template parameters (see the forward kernel). WITH_DQ = false leaves dQ to the separate dQ kernel
+// (used for the head dimensions other than 128, where dQ^T would need an MMA with M = 64 or 192): the kernel is then
+// free of atomics, and the staging tile and the shared-memory P^T buffer are not allocated.
+template <int DQK, int DV, bool WITH_DQ>
+struct FusedLayout {
+  static constexpr int QC = DQK / 64, VC = DV / 64;
+  static constexpr uint32_t K = 0, V = QC * 16384, QDO = V + VC * 16384, DOOFF = QC * 8192, STAGE = (QC + VC) * 8192;
+  static constexpr uint32_t EXTRA = WITH_DQ ? 32768 : 0;   // P^T buffer + dQ staging tile
+  static constexpr int NS = (QDO + 3 * STAGE + EXTRA + 32768 <= 224 * 1024) ? 3 : 2;
+  static constexpr uint32_t PT = QDO + NS * STAGE, DQS = PT + 16384, DST = PT + EXTRA, BAR = DST + 32768,
+                            STAT = BAR + 256;   // per stage: 64 x (-lse * log2 e) then 64 x (-delta * scale), fp32
+  static constexpr size_t SMEM = 1024 + STAT + NS * 512;
+};
 constexpr uint32_t IDESC_128x64_MM = tt::umma_idesc_bf16(128, 64, 1, 1);
 constexpr int FUSED_THREADS = 448;   // TMA, MMA, 8 softmax warps, 4 drain warps
 
@@ -744,6 +779,7 @@ __device__ __forceinline__ void red_rows(float* dst, long long qstride, const ui
   for (int c = 0; c < 32; ++c) atomicAdd(dst + c * (QS ? static_cast<long long>(QS) : qstride), __uint_as_float(r[c]));
 }
 
+template <int DQK, int DV, bool WITH_DQ>
 __global__ void __launch_bounds__(FUSED_THREADS, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                       const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
@@ -751,6 +787,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - tt::smem_u32(smem_raw));
+  using L = FusedLayout<DQK, DV, WITH_DQ>;
+  constexpr int K_NS = L::NS;
+  constexpr uint32_t K_K = L::K, K_V = L::V, K_QDO = L::QDO, K_PT = L::PT, K_DQS = L::DQS, K_DST = L::DST, K_BAR = L::BAR,
+                     K_STAT = L::STAT;
+  constexpr uint32_t IDESC_DV = tt::umma_idesc_bf16(128, DV, 0, 1), IDESC_DK = tt::umma_idesc_bf16(128, DQK, 0, 1);
+  const bool a_tmem = !WITH_DQ || x.a_tmem;      // without the shared-memory P^T buffer the A operands must come from TMEM
   const uint32_t bar0 = base + K_BAR;
   auto bar = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + K_BAR + 8 * FB_COUNT);
@@ -789,31 +831,34 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
   __syncthreads();
   tt::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tST = tmem, tDPT = tmem + 64, tDQT = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
-  const uint32_t tPT = tmem + 192, tDST = tmem + 224;   // bf16 P^T / dS^T as A operands: 64 queries = 32 columns each
+  // with dQ: S^T 0 | dP^T 64 | dQ^T 128 | P^T 192 | dS^T 224 | dV 256 | dK 384; without: S^T 0 | dP^T 64 | P^T 128 |
+  // dS^T 160 | dV 192 | dK 192 + DV (bf16 P^T / dS^T as A operands: 64 queries = 32 columns each)
+  const uint32_t tST = tmem, tDPT = tmem + 64, tDQT = tmem + 128;
+  const uint32_t tPT = tmem + (WITH_DQ ? 192 : 128), tDST = tPT + 32;
+  const uint32_t tDV = tmem + (WITH_DQ ? 256 : 192), tDK = tDV + DV;
 
   if (warp == 0) {
     if (tt::elect_one()) {
-      tt::mbar_expect_tx(bar(FB_KVFULL), 65536);
-      tt::tma_load_3d(base + K_K, &tk, bar(FB_KVFULL), 0, hk, b * p.Sk + kv0);
-      tt::tma_load_3d(base + K_K + 16384, &tk, bar(FB_KVFULL), 64, hk, b * p.Sk + kv0);
-      tt::tma_load_3d(base + K_V, &tv, bar(FB_KVFULL), 0, hk, b * p.Sk + kv0);
-      tt::tma_load_3d(base + K_V + 16384, &tv, bar(FB_KVFULL), 64, hk, b * p.Sk + kv0);
+      tt::mbar_expect_tx(bar(FB_KVFULL), (L::QC + L::VC) * 16384);
+#pragma unroll
+      for (int c = 0; c < L::QC; ++c) tt::tma_load_3d(base + K_K + c * 16384, &tk, bar(FB_KVFULL), c * 64, hk, b * p.Sk + kv0);
+#pragma unroll
+      for (int c = 0; c < L::VC; ++c) tt::tma_load_3d(base + K_V + c * 16384, &tv, bar(FB_KVFULL), c * 64, hk, b * p.Sk + kv0);
       for (int st = 0; st < n_steps; ++st, next_step()) {
         const int s = st % K_NS; const uint32_t ph = (st / K_NS) & 1;
         if (!tt::mbar_wait(bar(FB_QEMPTY + s), ph ^ 1, abort_flag, &g_attn_error, 41)) break;
-        const uint32_t qb = base + K_QDO + s * 32768, dob = qb + 16384;
-        tt::mbar_expect_tx(bar(FB_QFULL + s), 32768 + 512);
+        const uint32_t qb = base + K_QDO + s * L::STAGE, dob = qb + L::DOOFF;
+        tt::mbar_expect_tx(bar(FB_QFULL + s), L::STAGE + 512);
         {
           // the 64 queries' softmax statistics ride on the same barrier (plain bulk copies, 256 bytes each)
           const long long so = (static_cast<long long>(b) * p.H + h) * p.Sq + qt * 64;
           tt::bulk_load(base + K_STAT + s * 512, x.lse2 + so, 256, bar(FB_QFULL + s));
           tt::bulk_load(base + K_STAT + s * 512 + 256, x.delta_s + so, 256, bar(FB_QFULL + s));
         }
-        tt::tma_load_3d(qb, &tq, bar(FB_QFULL + s), 0, h, b * p.Sq + qt * 64);
-        tt::tma_load_3d(qb + 8192, &tq, bar(FB_QFULL + s), 64, h, b * p.Sq + qt * 64);
-        tt::tma_load_3d(dob, &tdo, bar(FB_QFULL + s), 0, h, b * p.Sq + qt * 64);
-        tt::tma_load_3d(dob + 8192, &tdo, bar(FB_QFULL + s), 64, h, b * p.Sq + qt * 64);
+#pragma unroll
+        for (int c = 0; c < L::QC; ++c) tt::tma_load_3d(qb + c * 8192, &tq, bar(FB_QFULL + s), c * 64, h, b * p.Sq + qt * 64);
+#pragma unroll
+        for (int c = 0; c < L::VC; ++c) tt::tma_load_3d(dob + c * 8192, &tdo, bar(FB_QFULL + s), c * 64, h, b * p.Sq + qt * 64);
       }
     }
   } else if (warp == 1) {
@@ -822,7 +867,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
       // descriptors are built once; inside the loop an operand slice is one 32-bit add away (see tt::SmemDesc)
       const tt::SmemDesc dK_km = tt::make_smem_desc(base + K_K, 1, 64), dV_km = tt::make_smem_desc(base + K_V, 1, 64);
       const tt::SmemDesc dK_mn = tt::make_smem_desc(base + K_K, (128 * 128) >> 4, 64);
-      const tt::SmemDesc dQ_km0 = tt::make_smem_desc(base + K_QDO, 1, 64);              // stage 0: Q; dO is 16 KB further
+      const tt::SmemDesc dQ_km0 = tt::make_smem_desc(base + K_QDO, 1, 64);              // stage 0: Q; dO follows Q's chunks
       const tt::SmemDesc dQ_mn0 = tt::make_smem_desc(base + K_QDO, (64 * 128) >> 4, 64);
       const tt::SmemDesc dPT_km = tt::make_smem_desc(base + K_PT, 1, 64);
       const tt::SmemDesc dDS_km0 = tt::make_smem_desc(base + K_DST, 1, 64);
@@ -834,15 +879,15 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         if (st > 0 && !tt::mbar_wait(bar(FB_STFREE), (st - 1) & 1, abort_flag, &g_attn_error, 44)) return false;
         tt::tc_fence_after();
         TT_TRACE(st, 0);   // S^T / dP^T issue begins
-        const tt::SmemDesc q = dQ_km0.at(s * 32768), dO = q.at(16384);
+        const tt::SmemDesc q = dQ_km0.at(s * L::STAGE), dO = q.at(L::DOOFF);
         // K-major operands with two 64-wide halves of the head dimension: slice kk starts at
         // (kk >> 2) * rows * 128 + (kk & 3) * 32 bytes (rows = 128 for K / V, 64 for Q / dO)
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
+        for (int kk = 0; kk < DQK / 16; ++kk)
           tt::umma_f16_ss(tST, dK_km.at((kk >> 2) * 16384 + (kk & 3) * 32), q.at((kk >> 2) * 8192 + (kk & 3) * 32),
                           IDESC_128x64_KK, kk != 0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
+        for (int kk = 0; kk < DV / 16; ++kk)
           tt::umma_f16_ss(tDPT, dV_km.at((kk >> 2) * 16384 + (kk & 3) * 32), dO.at((kk >> 2) * 8192 + (kk & 3) * 32),
                           IDESC_128x64_KK, kk != 0);
         tt::umma_commit(bar(FB_STFULL));
@@ -856,34 +901,36 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         if (!tt::mbar_wait(bar(FB_PTREADY + t2), (st >> 1) & 1, abort_flag, &g_attn_error, 45)) break;
         tt::tc_fence_after();
         TT_TRACE(st, 2);   // P^T / dS^T seen ready
-        const tt::SmemDesc q_mn = dQ_mn0.at(s * 32768), dO_mn = q_mn.at(16384);
+        const tt::SmemDesc q_mn = dQ_mn0.at(s * L::STAGE), dO_mn = q_mn.at(L::DOOFF);
         const tt::SmemDesc ds_km = dDS_km0.at(t2 * 16384), ds_mn = dDS_mn0.at(t2 * 16384);
         const uint32_t acc0 = st != 0;
-        if (x.a_tmem) {
+        if (a_tmem) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tt::umma_f16_ts(tDV, tPT + kk * 8, dO_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+            tt::umma_f16_ts(tDV, tPT + kk * 8, dO_mn.at(kk * 2048), IDESC_DV, kk ? 1u : acc0);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tt::umma_f16_ts(tDK, tDST + kk * 8, q_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+            tt::umma_f16_ts(tDK, tDST + kk * 8, q_mn.at(kk * 2048), IDESC_DK, kk ? 1u : acc0);
           tt::umma_commit(bar(FB_PFREE));       // P^T and dS^T (tensor memory) free for the next step's softmax
         } else {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tt::umma_f16_ss(tDV, dPT_km.at(kk * 32), dO_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+            tt::umma_f16_ss(tDV, dPT_km.at(kk * 32), dO_mn.at(kk * 2048), IDESC_DV, kk ? 1u : acc0);
           tt::umma_commit(bar(FB_PFREE));       // P^T buffer free for the next step's softmax
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            tt::umma_f16_ss(tDK, ds_km.at(kk * 32), q_mn.at(kk * 2048), IDESC_128x128_KM, kk ? 1u : acc0);
+            tt::umma_f16_ss(tDK, ds_km.at(kk * 32), q_mn.at(kk * 2048), IDESC_DK, kk ? 1u : acc0);
         }
-        // dQ^T overwrites what the drain warps read for the previous step: wait for them as late as possible
-        if (st > 0 && !tt::mbar_wait(bar(FB_DQFREE), (st - 1) & 1, abort_flag, &g_attn_error, 46)) break;
-        tt::tc_fence_after();
-        TT_TRACE(st, 3);   // dQ^T buffer seen free
+        if constexpr (WITH_DQ) {
+          // dQ^T overwrites what the drain warps read for the previous step: wait for them as late as possible
+          if (st > 0 && !tt::mbar_wait(bar(FB_DQFREE), (st - 1) & 1, abort_flag, &g_attn_error, 46)) break;
+          tt::tc_fence_after();
+          TT_TRACE(st, 3);   // dQ^T buffer seen free
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tt::umma_f16_ss(tDQT, dK_mn.at(kk * 2048), ds_mn.at(kk * 2048), IDESC_128x64_MM, kk != 0);
-        tt::umma_commit(bar(FB_DQFULL));        // dQ^T of this step complete
+          for (int kk = 0; kk < 8; ++kk)
+            tt::umma_f16_ss(tDQT, dK_mn.at(kk * 2048), ds_mn.at(kk * 2048), IDESC_128x64_MM, kk != 0);
+          tt::umma_commit(bar(FB_DQFULL));      // dQ^T of this step complete
+        }
         tt::umma_commit(bar(FB_PTFREE + t2));   // dS^T buffer free
         tt::umma_commit(bar(FB_QEMPTY + s));    // Q / dO stage free
         TT_TRACE(st, 4);   // second group issued
@@ -965,18 +1012,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
         uint8_t* prow = gbase + K_PT + row * 128;
         uint8_t* drow = gbase + K_DST + t2 * 16384 + row * 128;
         const int xr = row & 7;
-        if (x.a_tmem) {
+        if (a_tmem) {
           // A operands of dV / dK straight into tensor memory: this thread's key row = its lane, 32 queries = 16 columns
           tt::tmem_st_32x16(tPT + lane_off + half * 16, pp);
           tt::tmem_st_32x16(tDST + lane_off + half * 16, dd);
         }
+        if (WITH_DQ || !a_tmem) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int chunk = ((half * 4 + c) ^ xr) << 4;
-          if (!x.a_tmem) *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
-          *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);   // B operand of dQ^T
+          for (int c = 0; c < 4; ++c) {
+            const int chunk = ((half * 4 + c) ^ xr) << 4;
+            if (!a_tmem) *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+            *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dd[4 * c], dd[4 * c + 1], dd[4 * c + 2], dd[4 * c + 3]);   // B operand of dQ^T
+          }
         }
-        if (x.a_tmem) tt::tc_wait_st();
+        if (a_tmem) tt::tc_wait_st();
       }
       tt::fence_proxy_async();
       tt::tc_fence_before();
@@ -987,15 +1036,16 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
     if (ok && n_steps > 0) ok = tt::mbar_wait(bar(FB_PTFREE + ((n_steps - 1) & 1)), ((n_steps - 1) >> 1) & 1, abort_flag, &g_attn_error, 49);
     tt::tc_fence_after();
     if (ok) {
-      const long long o = ((static_cast<long long>(b) * p.Sk + ki) * p.Hkv + hk) * D;
-      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
-      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.out2) + o;
+      const long long orow = (static_cast<long long>(b) * p.Sk + ki) * p.Hkv + hk;
+      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.out) + orow * DQK;
+      __nv_bfloat16* dv = reinterpret_cast<__nv_bfloat16*>(p.out2) + orow * DV;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dstp = which ? dk : dv;
         const uint32_t t = which ? tDK : tDV;
+        const int ch = (which ? DQK : DV) / 64;         // 32-column chunks per warp half
 #pragma unroll 1
-        for (int c = half * 2; c < half * 2 + 2; ++c) {
+        for (int c = half * ch; c < half * ch + ch; ++c) {
           uint32_t r[32];
           if (n_steps > 0) { tt::tmem_ld_32x32(t + lane_off + c * 32, r); tt::tc_wait_ld(); }
           else {
@@ -1007,7 +1057,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
       }
     }
     tt::tc_fence_before();
-  } else {
+  } else if constexpr (WITH_DQ) {
     // 4 drain warps: lane = head-dim index d of dQ^T; add this step's [64 queries x 128 d] to the fp32 accumulator
     const int lg = warp & 3, d = lg * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(lg * 32) << 16;
@@ -1061,16 +1111,18 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tq, const __grid_const
 }
 
 // -delta[b,h,s] * scale (delta = sum_d dO * O) and -lse * log2(e): the addends of the fused backward's two FMAs
+template <int DVT>
 __global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                  const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta_s,
-                                 float scale, int B, int S, int H) {
-  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x / 16) + threadIdx.x / 16;  // (b,s,h)
-  const int l16 = threadIdx.x & 15;
+                                 float* __restrict__ delta, float scale, int B, int S, int H) {
+  constexpr int LPR = DVT / 8;       // lanes per (b, s, h) row, 8 elements each
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x / LPR) + threadIdx.x / LPR;
+  const int l = threadIdx.x % LPR;
   const long long rows = static_cast<long long>(B) * S * H;
   float acc = 0.f;
   if (row < rows) {
-    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + l16 * 8);
-    const uint4 c = *reinterpret_cast<const uint4*>(dout + row * D + l16 * 8);
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * DVT + l * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dout + row * DVT + l * 8);
     const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
     const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
@@ -1080,8 +1132,8 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv
     }
   }
 #pragma unroll
-  for (int o2 = 8; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-  if (row < rows && l16 == 0) {
+  for (int o2 = LPR / 2; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (row < rows && l == 0) {
     const int hh = static_cast<int>(row % H);
     const long long bs = row / H;
     const int s = static_cast<int>(bs % S);
@@ -1089,6 +1141,7 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv
     const long long i = (bb * H + hh) * S + s;
     delta_s[i] = -acc * scale;
     lse2[i] = -lse[i] * kLog2e;
+    if (delta != nullptr) delta[i] = acc;    // plain form for the separate dQ kernel
   }
 }
 
@@ -1134,11 +1187,11 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 }
 
 // [B*S, heads, 128] bf16 viewed as a 3-D tensor (d, head, row); box = (64, 1, box_rows), 128B swizzle
-int make_map(CUtensorMap* m, const void* ptr, long long rows, int heads, int box_rows) {
+int make_map(CUtensorMap* m, const void* ptr, long long rows, int heads, int box_rows, int Dh = D) {
   tt::EncodeTiledFn fn = tt::encode_tiled_fn();
   if (!fn) return -1;
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(heads) * D * 2};
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(Dh), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(Dh) * 2, static_cast<cuuint64_t>(heads) * Dh * 2};
   cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t es[3] = {1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, es,
@@ -1152,15 +1205,24 @@ int g_dq_mode = 0;
 int g_a_tmem = 1;
 void set_attrs() {
   if (g_attr_set) return;
-  cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FWD_SMEM));
-  cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DQ_SMEM));
+  cudaFuncSetAttribute(attn_fwd_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FwdLayout<128, 128>::SMEM));
+  cudaFuncSetAttribute(attn_fwd_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FwdLayout<64, 64>::SMEM));
+  cudaFuncSetAttribute(attn_fwd_kernel<192, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FwdLayout<192, 128>::SMEM));
+  cudaFuncSetAttribute(attn_bwd_dq_kernel<128, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DqLayout<128, 128>::SMEM));
+  cudaFuncSetAttribute(attn_bwd_dq_kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DqLayout<64, 64>::SMEM));
+  cudaFuncSetAttribute(attn_bwd_dq_kernel<192, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DqLayout<192, 128>::SMEM));
   cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(DKV_SMEM));
-  cudaFuncSetAttribute(attn_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FUSED_SMEM));
+  cudaFuncSetAttribute(attn_bwd_fused_kernel<128, 128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FusedLayout<128, 128, true>::SMEM));
+  cudaFuncSetAttribute(attn_bwd_fused_kernel<64, 64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FusedLayout<64, 64, false>::SMEM));
+  cudaFuncSetAttribute(attn_bwd_fused_kernel<192, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FusedLayout<192, 128, false>::SMEM));
   g_attr_set = true;
 }
 
-int check_shapes(int Sq, int Sk, int H, int Hkv, int Dh) {
-  if (Dh != D) return -10;
+// Head dimensions the kernels are instantiated for: (query/key, value) = (128,128), (64,64), (192,128).
+bool dims_ok(int Dqk, int Dv) { return (Dqk == 128 && Dv == 128) || (Dqk == 64 && Dv == 64) || (Dqk == 192 && Dv == 128); }
+
+int check_shapes(int Sq, int Sk, int H, int Hkv, int Dh, int Dv = -1) {
+  if (!dims_ok(Dh, Dv < 0 ? Dh : Dv)) return -10;
   if (Sq % 128 || Sk % 128) return -11;
   if (Hkv <= 0 || H % Hkv) return -12;
   return 0;
@@ -1172,6 +1234,7 @@ extern "C" {
 
 // Shapes this build of the kernels accepts (0 = yes).
 int tt_attn_supported(int Sq, int Sk, int H, int Hkv, int Dh) { return check_shapes(Sq, Sk, H, Hkv, Dh); }
+int tt_attn_supported_dims(int Sq, int Sk, int H, int Hkv, int Dqk, int Dv) { return check_shapes(Sq, Sk, H, Hkv, Dqk, Dv); }
 
 // row_lo (nullable, int32 [B,Sq], non-decreasing along the sequence, needs Sq == Sk): see AttnArgs.
 int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo, int B, int Sq,
@@ -1192,21 +1255,30 @@ int tt_attn_fwd_range(const void* q, const void* k, const void* v, void* o, floa
 }
 
 // sinks (nullable, fp32 [H]): per-head logit added to the softmax denominator; lse includes it.
-int tt_attn_fwd_sinks(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
-                      const float* sinks, int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal, float scale,
-                      cudaStream_t st) {
-  int rc = check_shapes(Sq, Sk, H, Hkv, Dh);
+// General form: separate head dimensions for queries / keys (Dqk) and values (Dv); see dims_ok for the supported pairs.
+int tt_attn_fwd_dims(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                     const float* sinks, int B, int Sq, int Sk, int H, int Hkv, int Dqk, int Dv, int causal, float scale,
+                     cudaStream_t st) {
+  int rc = check_shapes(Sq, Sk, H, Hkv, Dqk, Dv);
   if (rc) return rc;
   if (row_lo && Sq != Sk) return -13;
   set_attrs();
   CUtensorMap tq, tk, tv;
-  if ((rc = make_map(&tq, q, static_cast<long long>(B) * Sq, H, 128))) return rc;
-  if ((rc = make_map(&tk, k, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
-  if ((rc = make_map(&tv, v, static_cast<long long>(B) * Sk, Hkv, 64))) return rc;
+  if ((rc = make_map(&tq, q, static_cast<long long>(B) * Sq, H, 128, Dqk))) return rc;
+  if ((rc = make_map(&tk, k, static_cast<long long>(B) * Sk, Hkv, 64, Dqk))) return rc;
+  if ((rc = make_map(&tv, v, static_cast<long long>(B) * Sk, Hkv, 64, Dv))) return rc;
   AttnArgs p{B, Sq, Sk, H, Hkv, causal, scale, o, nullptr, lse, nullptr, row_lo, nullptr, sinks};
   dim3 grid(Sq / 128, H, B);
-  attn_fwd_kernel<<<grid, 192, FWD_SMEM, st>>>(tq, tk, tv, p);
+  if (Dqk == 128) attn_fwd_kernel<128, 128><<<grid, 192, FwdLayout<128, 128>::SMEM, st>>>(tq, tk, tv, p);
+  else if (Dqk == 64) attn_fwd_kernel<64, 64><<<grid, 192, FwdLayout<64, 64>::SMEM, st>>>(tq, tk, tv, p);
+  else attn_fwd_kernel<192, 128><<<grid, 192, FwdLayout<192, 128>::SMEM, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int tt_attn_fwd_sinks(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                      const float* sinks, int B, int Sq, int Sk, int H, int Hkv, int Dh, int causal, float scale,
+                      cudaStream_t st) {
+  return tt_attn_fwd_dims(q, k, v, o, lse, row_lo, sinks, B, Sq, Sk, H, Hkv, Dh, Dh, causal, scale, st);
 }
 
 // delta is scratch [B,H,Sq] fp32 written by the first launch and read by the other two.
@@ -1243,7 +1315,7 @@ int tt_attn_bwd_range(const void* q, const void* k, const void* v, const void* o
   if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128))) return rc;
   AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta, row_lo, col_hi, nullptr};
-  attn_bwd_dq_kernel<<<dim3(Sq / 128, H, B), 320, DQ_SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
+  attn_bwd_dq_kernel<128, 128><<<dim3(Sq / 128, H, B), 320, DqLayout<128, 128>::SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
   AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), delta, row_lo, col_hi, nullptr};
   attn_bwd_dkv_kernel<<<dim3(Sk / 128, Hkv, B), 320, DKV_SMEM, st>>>(tq64, tdo64, tk128, tv128, pk);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -1266,8 +1338,8 @@ int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o
   const long long rows = static_cast<long long>(B) * Sq * H;
   float* lse2 = scratch;
   float* delta_s = scratch + rows;
-  attn_prep_kernel<<<static_cast<unsigned>((rows + 15) / 16), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, lse2, delta_s, scale, B, Sq, H);
+  attn_prep_kernel<128><<<static_cast<unsigned>((rows + 15) / 16), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, lse2, delta_s, nullptr, scale, B, Sq, H);
   CUtensorMap tq64, tdo64, tk128, tv128;
   if ((rc = make_map(&tq64, q, static_cast<long long>(B) * Sq, H, 64))) return rc;
   if ((rc = make_map(&tdo64, dout, static_cast<long long>(B) * Sq, H, 64))) return rc;
@@ -1288,12 +1360,58 @@ int tt_attn_bwd_fused(const void* q, const void* k, const void* v, const void* o
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -static_cast<int>(r) - 1000;
   }
-  attn_bwd_fused_kernel<<<dim3(Hkv, Sk / 128, B), FUSED_THREADS, FUSED_SMEM, st>>>(tq64, tdo64, tk128, tv128, tdq, pk, x);
+  attn_bwd_fused_kernel<128, 128, true><<<dim3(Hkv, Sk / 128, B), FUSED_THREADS, FusedLayout<128, 128, true>::SMEM, st>>>(
+      tq64, tdo64, tk128, tv128, tdq, pk, x);
   const long long n8 = rows * D / 8;
   long long cblocks = (n8 + 255) / 256;
   if (cblocks > 148 * 16) cblocks = 148 * 16;
   attn_dq_convert_kernel<<<static_cast<unsigned>(cblocks), 256, 0, st>>>(
       dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Backward for the head dimensions other than 128 (see dims_ok): the key-tile kernel forms dK and dV (no dQ, no atomics),
+// the query-tile kernel forms dQ. scratch: fp32 [3 * B*H*Sq] (written here). Deterministic.
+int tt_attn_bwd_dims(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                     float* scratch, void* dq, void* dk, void* dv, const int* row_lo, const int* col_hi, int B, int Sq, int Sk,
+                     int H, int Hkv, int Dqk, int Dv, int causal, float scale, cudaStream_t st) {
+  int rc = check_shapes(Sq, Sk, H, Hkv, Dqk, Dv);
+  if (rc) return rc;
+  if (Dqk == 128) return -15;     // use tt_attn_bwd_fused / tt_attn_bwd_range
+  if ((row_lo != nullptr) != (col_hi != nullptr)) return -14;
+  if (row_lo && Sq != Sk) return -13;
+  set_attrs();
+  const long long rows = static_cast<long long>(B) * Sq * H;
+  float* lse2 = scratch;
+  float* delta_s = scratch + rows;
+  float* delta = scratch + 2 * rows;
+  if (Dv == 128) {
+    attn_prep_kernel<128><<<static_cast<unsigned>((rows + 15) / 16), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, lse2, delta_s, delta, scale, B, Sq, H);
+  } else {
+    attn_prep_kernel<64><<<static_cast<unsigned>((rows + 31) / 32), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, lse2, delta_s, delta, scale, B, Sq, H);
+  }
+  CUtensorMap tq64, tdo64, tk128, tv128, tq128, tdo128, tk64, tv64;
+  if ((rc = make_map(&tq64, q, static_cast<long long>(B) * Sq, H, 64, Dqk))) return rc;
+  if ((rc = make_map(&tdo64, dout, static_cast<long long>(B) * Sq, H, 64, Dv))) return rc;
+  if ((rc = make_map(&tk128, k, static_cast<long long>(B) * Sk, Hkv, 128, Dqk))) return rc;
+  if ((rc = make_map(&tv128, v, static_cast<long long>(B) * Sk, Hkv, 128, Dv))) return rc;
+  if ((rc = make_map(&tq128, q, static_cast<long long>(B) * Sq, H, 128, Dqk))) return rc;
+  if ((rc = make_map(&tdo128, dout, static_cast<long long>(B) * Sq, H, 128, Dv))) return rc;
+  if ((rc = make_map(&tk64, k, static_cast<long long>(B) * Sk, Hkv, 64, Dqk))) return rc;
+  if ((rc = make_map(&tv64, v, static_cast<long long>(B) * Sk, Hkv, 64, Dv))) return rc;
+  AttnArgs pk{B, Sq, Sk, H, Hkv, causal, scale, dk, dv, const_cast<float*>(lse), nullptr, row_lo, col_hi, nullptr};
+  FusedExtra x{lse2, delta_s, nullptr, 2, 1};
+  AttnArgs pq{B, Sq, Sk, H, Hkv, causal, scale, dq, nullptr, const_cast<float*>(lse), delta, row_lo, col_hi, nullptr};
+  const dim3 gk(Hkv, Sk / 128, B), gq(Sq / 128, H, B);
+  if (Dqk == 64) {
+    attn_bwd_fused_kernel<64, 64, false><<<gk, FUSED_THREADS, FusedLayout<64, 64, false>::SMEM, st>>>(tq64, tdo64, tk128, tv128, tq64, pk, x);
+    attn_bwd_dq_kernel<64, 64><<<gq, 320, DqLayout<64, 64>::SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
+  } else {
+    attn_bwd_fused_kernel<192, 128, false><<<gk, FUSED_THREADS, FusedLayout<192, 128, false>::SMEM, st>>>(tq64, tdo64, tk128, tv128, tq64, pk, x);
+    attn_bwd_dq_kernel<192, 128><<<gq, 320, DqLayout<192, 128>::SMEM, st>>>(tq128, tdo128, tk64, tv64, pq);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

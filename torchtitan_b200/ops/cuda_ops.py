@@ -292,22 +292,29 @@ def swiglu(gate: Tensor, up: Tensor) -> Tensor:
 @torch.library.custom_op("tt_b200::attention_fwd", mutates_args=())
 def attention_fwd(q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float,
                   row_lo: Tensor | None = None, sinks: Tensor | None = None) -> tuple[Tensor, Tensor]:
+    """q [B,Sq,H,Dqk], k [B,Sk,Hkv,Dqk], v [B,Sk,Hkv,Dv] -> (o [B,Sq,H,Dv], lse [B,H,Sq])."""
     B, Sq, H, D = q.shape
-    Sk, Hkv = k.shape[1], k.shape[2]
-    o = torch.empty_like(q)
+    Sk, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
+    o = torch.empty((B, Sq, H, Dv), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
-    if sinks is not None:
-        _ck(_lib().tt_attn_fwd_sinks(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo),
-                                     sinks.data_ptr(), B, Sq, Sk, H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd_sinks")
+    L = _lib()
+    if hasattr(L, "tt_attn_fwd_dims"):
+        _ck(L.tt_attn_fwd_dims(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo), _p(sinks),
+                               B, Sq, Sk, H, Hkv, D, Dv, int(causal), scale, _stream()), "tt_attn_fwd_dims")
         return o, lse
-    _ck(_lib().tt_attn_fwd_range(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo), B, Sq, Sk,
-                                 H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd")
+    if sinks is not None:
+        _ck(L.tt_attn_fwd_sinks(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo),
+                                sinks.data_ptr(), B, Sq, Sk, H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd_sinks")
+        return o, lse
+    _ck(L.tt_attn_fwd_range(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _p(row_lo), B, Sq, Sk,
+                            H, Hkv, D, int(causal), scale, _stream()), "tt_attn_fwd")
     return o, lse
 
 
 @attention_fwd.register_fake
 def _(q, k, v, causal, scale, row_lo=None, sinks=None):
-    return torch.empty_like(q), q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32)
+    return (q.new_empty((q.shape[0], q.shape[1], q.shape[2], v.shape[3])),
+            q.new_empty((q.shape[0], q.shape[2], q.shape[1]), dtype=torch.float32))
 
 
 # None: the fused backward kernel unless deterministic algorithms are requested; True / False force one form (tests)
@@ -326,8 +333,15 @@ def attention_bwd(q: Tensor, k: Tensor, v: Tensor, o: Tensor, do: Tensor, lse: T
     """Two forms: one fused kernel per key tile that also adds its share of dQ into an fp32 accumulator (default: fastest,
     dQ not bitwise reproducible), or separate dK/dV and dQ kernels without atomics (``torch.use_deterministic_algorithms``)."""
     B, Sq, H, D = q.shape
-    Sk, Hkv = k.shape[1], k.shape[2]
+    Sk, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    if D != 128 or Dv != 128:
+        # other head dimensions: key-tile kernel for dK / dV plus query-tile kernel for dQ (no atomics, deterministic)
+        scratch = torch.empty((3, B, H, Sq), dtype=torch.float32, device=q.device)
+        _ck(_lib().tt_attn_bwd_dims(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                    scratch.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _p(row_lo), _p(col_hi),
+                                    B, Sq, Sk, H, Hkv, D, Dv, int(causal), scale, _stream()), "tt_attn_bwd_dims")
+        return dq, dk, dv
     if _attn_bwd_fused():
         scratch = torch.empty((2, B, H, Sq), dtype=torch.float32, device=q.device)
         dq_acc = torch.zeros((B, Sq, H, D), dtype=torch.float32, device=q.device)
@@ -393,9 +407,16 @@ def range_bounds(doc_ids: Tensor | None, window: int | None, B: int, S: int, dev
     return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
 
 
-def attention_supported(q: Tensor, k: Tensor) -> bool:
+def attention_supported(q: Tensor, k: Tensor, v: Tensor | None = None) -> bool:
     B, Sq, H, D = q.shape
-    return q.dtype == torch.bfloat16 and _lib().tt_attn_supported(Sq, k.shape[1], H, k.shape[2], D) == 0
+    Dv = D if v is None else v.shape[-1]
+    if q.dtype != torch.bfloat16:
+        return False
+    L = _lib()
+    if D == 128 and Dv == 128:
+        return L.tt_attn_supported(Sq, k.shape[1], H, k.shape[2], D) == 0
+    return (hasattr(L, "tt_attn_supported_dims") and hasattr(L, "tt_attn_bwd_dims")
+            and L.tt_attn_supported_dims(Sq, k.shape[1], H, k.shape[2], D, Dv) == 0)
 
 
 def attention(q, k, v, *, causal=True, scale=None, window=None, doc_ids=None, sinks=None, return_lse=False):
@@ -403,7 +424,7 @@ def attention(q, k, v, *, causal=True, scale=None, window=None, doc_ids=None, si
     sliding window (contiguous key ranges), with optional per-head attention sinks; unsupported shapes take the PyTorch
     definition."""
     ranged = window is not None or doc_ids is not None
-    ok = k.dtype == q.dtype and attention_supported(q, k)
+    ok = k.dtype == q.dtype and v.dtype == q.dtype and attention_supported(q, k, v)
     if ok and sinks is not None:
         ok = native.has("tt_attn_fwd_sinks")
     if ok and ranged:

@@ -103,6 +103,11 @@ def lib():
         _sig(L.tt_fp8_quant_tensor, [P, LL, I, I, P, P, I, I, P])
     if hasattr(L, "tt_attn_fwd_sinks"):
         _sig(L.tt_attn_fwd_sinks, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
+    if hasattr(L, "tt_attn_fwd_dims"):
+        _sig(L.tt_attn_fwd_dims, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
+        _sig(L.tt_attn_supported_dims, [I, I, I, I, I, I])
+    if hasattr(L, "tt_attn_bwd_dims"):
+        _sig(L.tt_attn_bwd_dims, [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P])
     if hasattr(L, "tt_attn_bwd_fused"):
         _sig(L.tt_attn_bwd_fused, [P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P])
         _sig(L.tt_attn_set_dq_mode, [I], None)
