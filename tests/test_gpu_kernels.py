@@ -469,13 +469,20 @@ def test_mxfp8_quantise_kernels(ops):
     _no_kernel_errors()
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 512), (384, 768, 1024), (200, 328, 224), (4096, 4096, 2048)])
-def test_gemm_mxfp8_block_scaled(ops, M, N, K):
-    """Block-scaled tcgen05 MXFP8 GEMM (scales applied by the MMA) vs the fp32 product of the dequantised operands."""
+@pytest.mark.parametrize("pair", [1, 0])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 512), (384, 768, 1024), (200, 328, 224), (4096, 4096, 2048),
+                                   (520, 1000, 384)])
+def test_gemm_mxfp8_block_scaled(ops, M, N, K, pair):
+    """Block-scaled tcgen05 MXFP8 GEMM (scales applied by the MMA) vs the fp32 product of the dequantised operands, with
+    CTA-pair tiles (the default for shapes of at least 256 x 256) and with the single-CTA kernel."""
     from torchtitan_b200.ops import native, quant
 
     if not native.has("tt_gemm_mxfp8"):
         pytest.skip("library built without tt_gemm_mxfp8")
+    if native.has("tt_gemm_mx_set_pair"):
+        native.lib().tt_gemm_mx_set_pair(pair)
+    elif pair == 0:
+        pytest.skip("library has one MXFP8 kernel only")
     torch.manual_seed(0)
     # rows and K blocks of very different magnitude, so that a misplaced scale shows
     a = torch.randn(M, K, device="cuda") * torch.exp2(torch.randint(-6, 7, (M, K // 32), device="cuda").float()).repeat_interleave(32, 1)
@@ -487,6 +494,8 @@ def test_gemm_mxfp8_block_scaled(ops, M, N, K):
     _no_kernel_errors()
     assert _rel(got, want) < 1e-3, _rel(got, want)
     got16 = ops.gemm_mxfp8(qa, qb, sa, sb, torch.bfloat16)
+    if native.has("tt_gemm_mx_set_pair"):
+        native.lib().tt_gemm_mx_set_pair(1)
     assert _rel(got16, want) < 1e-2
 
 

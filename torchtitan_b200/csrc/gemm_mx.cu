@@ -77,6 +77,37 @@ __device__ __forceinline__ void umma_mx_ss(uint32_t d_tmem, uint64_t adesc, uint
       : "memory");
 }
 
+// Write 32 consecutive accumulator columns of one output row (bf16 or fp32).
+__device__ __forceinline__ void store_acc_chunk(const MxArgs& p, int row, int col, const uint32_t (&r)[32]) {
+  const bool full_chunk = col + 32 <= p.N;
+  if (p.c_fp32) {
+    float* dst = static_cast<float*>(p.C) + row * p.ldc + col;
+    if (full_chunk && p.ldc % 4 == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<float4*>(dst)[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+    } else {
+      for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+    }
+  } else {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+    if (full_chunk && p.ldc % 8 == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 q;
+        q.x = tt::pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+        q.y = tt::pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        q.z = tt::pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        q.w = tt::pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        reinterpret_cast<uint4*>(dst)[j] = q;
+      }
+    } else {
+      for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, MxArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -191,33 +222,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         tt::tc_wait_ld();
         const int col = tn * BN + c * 32;
         if (row >= p.M || col >= p.N) continue;
-        const bool full_chunk = col + 32 <= p.N;
-        if (p.c_fp32) {
-          float* dst = static_cast<float*>(p.C) + row * p.ldc + col;
-          if (full_chunk && p.ldc % 4 == 0) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              reinterpret_cast<float4*>(dst)[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                              __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-          } else {
-            for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
-          }
-        } else {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
-          if (full_chunk && p.ldc % 8 == 0) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 q;
-              q.x = tt::pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-              q.y = tt::pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-              q.z = tt::pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-              q.w = tt::pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-              reinterpret_cast<uint4*>(dst)[j] = q;
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < p.N; ++j) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
-          }
-        }
+        store_acc_chunk(p, row, col, r);
       }
       tt::tc_fence_before();
       __syncwarp();
@@ -232,6 +237,162 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     tt::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): two CTAs on neighbouring SMs share one 256 x 256 output tile. Each CTA stages its own
+// 128 rows of A, *half* of the B tile and the scale factors it needs (its rows of A, all 256 columns of B), so every SM
+// pulls 33.5 KB instead of 49.5 KB per K step through the L2-to-SM fabric, which is what bounds the single-CTA kernel.
+// One elected thread of the leader issues the scale-factor copies (tcgen05.cp.cta_group::2 copies in both CTAs, each
+// from its own shared memory) and the M = 256 MMAs; each CTA's TMEM holds its 128 rows x 256 columns of the accumulator.
+// Scale factors travel as TMA tiles of the chunk array viewed as [chunks][128 x u32] (a bulk copy cannot credit the
+// partner's barrier, the cta_group::2 tensor copy can). No cluster multicast anywhere.
+namespace pairmx {
+constexpr int PSTAGES = 6;
+constexpr uint32_t PA = 128 * BK, PB = 128 * BK, PSF = 3 * SF_CHUNK;   // per CTA per stage
+constexpr uint32_t STAGE_BYTES = PA + PB + PSF;
+constexpr size_t PSMEM = 1024 + PSTAGES * STAGE_BYTES + 256;
+
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ uint32_t mx_idesc_pair(int j) {   // M = 256 across the pair, N = 256
+  return (static_cast<uint32_t>(j) << 4) | (static_cast<uint32_t>(256 >> 3) << 17) | (1u << 23) |
+         (static_cast<uint32_t>(256 >> 4) << 24) | (static_cast<uint32_t>(j) << 29);
+}
+__device__ __forceinline__ void umma_mx_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                                uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb, MxArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - tt::smem_u32(smem_raw));
+  const uint32_t sA = base, sB = sA + PSTAGES * PA, sSF = sB + PSTAGES * PB;
+  const uint32_t bars = sSF + PSTAGES * PSF;
+  uint8_t* bars_gen = gen_base + PSTAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };                      // used in the leader only
+  auto empty_bar = [&](int s) { return bars + 8u * (PSTAGES + s); };         // one per CTA
+  const uint32_t tfull_bar = bars + 8u * (2 * PSTAGES);                      // one per CTA
+  const uint32_t tempty_bar = bars + 8u * (2 * PSTAGES + 1);                 // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_gen + 8 * (2 * PSTAGES + 2));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * (2 * PSTAGES + 2) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tt::cluster_ctarank();   // 0 = leader
+  const int num_tiles = p.tiles_m * p.tiles_n;   // in 256 x 256 tiles
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) { tt::mbar_init(full_bar(s), 1); tt::mbar_init(empty_bar(s), 1); }
+    tt::mbar_init(tfull_bar, 1);
+    tt::mbar_init(tempty_bar, 8);                // four epilogue warps in each CTA
+    *abort_flag = 0;
+    tt::mbar_fence_init();
+    tt::tma_prefetch_desc(&tma_a); tt::tma_prefetch_desc(&tma_b);
+    tt::tma_prefetch_desc(&tma_sfa); tt::tma_prefetch_desc(&tma_sfb);
+  }
+  if (warp == 2) { tt::tmem_alloc_pair(tt::smem_u32(tmem_slot), TMEM_COLS); tt::tmem_relinquish_pair(); }
+  tt::tc_fence_before();
+  tt::cluster_sync();
+  tt::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (tt::elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        const int m0 = tm * 256 + rank * 128, n0 = tn * 256 + rank * 128;
+        const int ca = (2 * tm + static_cast<int>(rank)) * p.k_iters;          // chunk rows of this CTA's A scales
+        const int cb0 = (2 * tn) * p.k_iters, cb1 = (2 * tn + 1) * p.k_iters;  // both halves of the B scales
+        for (int k = 0; k < p.k_iters; ++k, ++it) {
+          const int s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1;
+          if (!tt::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, &g_mx_error, 11)) { ok = false; break; }
+          const uint32_t fb = tt::mapa(full_bar(s), 0);   // the leader's barrier collects both CTAs' bytes
+          if (rank == 0) tt::mbar_expect_tx(full_bar(s), 2 * STAGE_BYTES);
+          tt::tma_load_2d_pair(sA + s * PA, &tma_a, fb, k * BK, m0);
+          tt::tma_load_2d_pair(sB + s * PB, &tma_b, fb, k * BK, n0);
+          const uint32_t sf = sSF + s * PSF;
+          tt::tma_load_2d_pair(sf, &tma_sfa, fb, 0, ca + k);
+          tt::tma_load_2d_pair(sf + SF_CHUNK, &tma_sfb, fb, 0, cb0 + k);
+          tt::tma_load_2d_pair(sf + 2 * SF_CHUNK, &tma_sfb, fb, 0, cb1 + k);
+        }
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ------------------------------------------------------------ scale-factor copies + MMAs (leader only)
+    if (tt::elect_one()) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      const uint32_t sbo = 1024 >> 4;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++tile_it) {
+        if (!tt::mbar_wait(tempty_bar, (tile_it & 1) ^ 1, abort_flag, &g_mx_error, 12)) break;
+        tt::tc_fence_after();
+        for (int k = 0; k < p.k_iters; ++k, ++it) {
+          const int s = it % PSTAGES;
+          const uint32_t ph = (it / PSTAGES) & 1;
+          if (!tt::mbar_wait(full_bar(s), ph, abort_flag, &g_mx_error, 13)) { ok = false; break; }
+          tt::tc_fence_after();
+          const uint32_t sf = sSF + s * PSF;
+          const uint32_t t_sfa = tmem_base + ACC_COLS + s * SF_COLS_PER_STAGE, t_sfb = t_sfa + 4;
+          tmem_cp_sf_pair(t_sfa, sf_smem_desc(sf));
+          tmem_cp_sf_pair(t_sfb, sf_smem_desc(sf + SF_CHUNK));
+          tmem_cp_sf_pair(t_sfb + 4, sf_smem_desc(sf + 2 * SF_CHUNK));
+          const uint32_t aA = sA + s * PA, aB = sB + s * PB;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t ad = tt::umma_smem_desc(aA + kk * UMMA_K, 1, sbo);
+            const uint64_t bd = tt::umma_smem_desc(aB + kk * UMMA_K, 1, sbo);
+            umma_mx_ss_pair(tmem_base, ad, bd, mx_idesc_pair(kk), t_sfa + (static_cast<uint32_t>(kk) << 30),
+                            t_sfb + (static_cast<uint32_t>(kk) << 30), (k | kk) != 0);
+          }
+          tt::umma_commit_pair(empty_bar(s), 3);   // frees this stage in both CTAs
+        }
+        if (ok) tt::umma_commit_pair(tfull_bar, 3);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int ew = warp - 4;
+    uint32_t tile_it = 0;
+    const uint32_t leader_tempty = tt::mapa(tempty_bar, 0);
+    for (int t = cluster_id; t < num_tiles; t += num_clusters, ++tile_it) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      if (!tt::mbar_wait(tfull_bar, tile_it & 1, abort_flag, &g_mx_error, 14)) break;
+      tt::tc_fence_after();
+      const int row = tm * 256 + static_cast<int>(rank) * 128 + ew * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < 256 / 32; ++c) {
+        uint32_t r[32];
+        tt::tmem_ld_32x32(taddr + c * 32, r);
+        tt::tc_wait_ld();
+        const int col = tn * 256 + c * 32;
+        if (row >= p.M || col >= p.N) continue;
+        store_acc_chunk(p, row, col, r);
+      }
+      tt::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tt::mbar_arrive_cluster(leader_tempty);
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) tt::abort_drain();
+  tt::cluster_sync();   // nobody leaves while its partner may still touch its shared memory or TMEM
+  if (warp == 2) { tt::tc_fence_after(); tt::tmem_dealloc_pair(tmem_base, TMEM_COLS); }
+}
+}  // namespace pairmx
 
 // scales [R, KB] (row-major E8M0 bytes) -> chunks [ceil(R/128) rounded to row_blocks][kb4 = ceil(KB/4)][512]; missing rows
 // and K blocks get exponent 127 (2^0), their data is zero-filled by TMA.
@@ -252,10 +413,14 @@ __global__ void mx_swizzle_scales_kernel(const uint8_t* __restrict__ s, int R, i
 
 bool g_attr = false;
 int g_sms = 0;
+bool g_mx_pair = true;
 
 }  // namespace
 
 extern "C" {
+
+// 0 forces the single-CTA kernel (tests, comparisons); 1 (default) lets large shapes use CTA pairs.
+void tt_gemm_mx_set_pair(int on) { g_mx_pair = on != 0; }
 
 int tt_gemm_mx_error() {
   int v = 0;
@@ -303,7 +468,35 @@ int tt_gemm_mxfp8(const void* A, const void* B, const void* sfa, const void* sfb
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaFuncSetAttribute(gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    cudaFuncSetAttribute(pairmx::gemm_mx_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairmx::PSMEM));
     g_attr = true;
+  }
+  if (g_mx_pair && M >= 256 && N >= 256) {
+    // CTA-pair tiles of 256 x 256. Needs the scale buffers padded to 256 rows (tt_mx_scales_bytes(rows, 256, K)).
+    CUtensorMap ta, tb, tsa, tsb;
+    int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, 128, BK);
+    if (rc) return rc;
+    rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, 128, BK);
+    if (rc) return rc;
+    MxArgs p;
+    p.M = M; p.N = N; p.K = K;
+    p.k_iters = (K + BK - 1) / BK;
+    p.tiles_m = (M + 255) / 256;
+    p.tiles_n = (N + 255) / 256;
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb = static_cast<const uint8_t*>(sfb);
+    p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+    // scale chunks as rows of 128 32-bit words
+    rc = tt::make_tmap_2d(&tsa, sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(2) * p.tiles_m * p.k_iters, 128, 128, 1,
+                          128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = tt::make_tmap_2d(&tsb, sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, static_cast<uint64_t>(2) * p.tiles_n * p.k_iters, 128, 128, 1,
+                          128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    int clusters = p.tiles_m * p.tiles_n;
+    if (clusters > g_sms / 2) clusters = g_sms / 2;
+    pairmx::gemm_mx_pair_kernel<<<clusters * 2, NUM_THREADS, pairmx::PSMEM, stream>>>(ta, tb, tsa, tsb, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
   CUtensorMap ta, tb;
   int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, BM, BK);

@@ -52,64 +52,77 @@ class Attention(BaseAttention):
         super().__init__()
         if config.attn_backend == "varlen":
             raise ValueError("Varlen attention is not supported with Deepseek V3.")
-        self.dim, self.n_heads = dim, config.n_heads
-        self.q_lora_rank, self.kv_lora_rank = config.q_lora_rank, config.kv_lora_rank
-        self.qk_nope_head_dim, self.qk_rope_head_dim = config.qk_nope_head_dim, config.qk_rope_head_dim
-        self.qk_head_dim = config.qk_nope_head_dim + config.qk_rope_head_dim
-        self.v_head_dim = config.v_head_dim
-        lin = Linear.Config(bias=config.linear_bias)
+        c = config
+        self.dim, self.n_heads = dim, c.n_heads
+        self.q_lora_rank, self.kv_lora_rank = c.q_lora_rank, c.kv_lora_rank
+        self.qk_nope_head_dim, self.qk_rope_head_dim, self.v_head_dim = c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim
+        self.qk_head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
+        plain = Linear.Config(bias=c.linear_bias)
+        # projections as a table: name -> (config, in, out); the query side is either one matrix or a low-rank pair
+        q_out = self.n_heads * self.qk_head_dim
         if self.q_lora_rank == 0:
-            assert config.wq is not None, "wq is required when q_lora_rank == 0"
-            assert config.wq.bias == config.linear_bias
-            self.wq = config.wq.build(in_features=dim, out_features=self.n_heads * self.qk_head_dim)
+            table = {"wq": (c.wq, dim, q_out)}
         else:
-            assert config.wq_a is not None and config.wq_b is not None, "wq_a and wq_b are required when q_lora_rank > 0"
-            assert config.wq_a.bias == config.linear_bias and config.wq_b.bias == config.linear_bias
-            self.wq_a = config.wq_a.build(in_features=dim, out_features=self.q_lora_rank)
-            self.q_norm = config.q_norm.build(normalized_shape=self.q_lora_rank)
-            self.wq_b = config.wq_b.build(in_features=self.q_lora_rank, out_features=self.n_heads * self.qk_head_dim)
-        self.wkv_a = lin.build(in_features=dim, out_features=self.kv_lora_rank + self.qk_rope_head_dim)
-        self.kv_norm = config.kv_norm.build(normalized_shape=self.kv_lora_rank)
-        self.wkv_b = lin.build(in_features=self.kv_lora_rank,
-                               out_features=self.n_heads * (self.qk_nope_head_dim + self.v_head_dim))
-        self.wo = lin.build(in_features=self.n_heads * self.v_head_dim, out_features=dim)
-        self.softmax_scale = self.qk_head_dim**-0.5
-        if config.rope_max_seq_len > config.rope_original_seq_len:
-            m = 0.1 * config.mscale * math.log(config.rope_factor) + 1.0
-            self.softmax_scale *= m * m
-        self.attn_backend = config.attn_backend
+            table = {"wq_a": (c.wq_a, dim, self.q_lora_rank), "wq_b": (c.wq_b, self.q_lora_rank, q_out)}
+        for name, (cfg, _, _) in table.items():
+            if cfg is None:
+                raise AssertionError(f"{name} is required when q_lora_rank {'== 0' if name == 'wq' else '> 0'}")
+            assert cfg.bias == c.linear_bias, f"{name}.bias must equal linear_bias"
+        table.update({
+            "wkv_a": (plain, dim, self.kv_lora_rank + self.qk_rope_head_dim),
+            "wkv_b": (plain, self.kv_lora_rank, self.n_heads * (self.qk_nope_head_dim + self.v_head_dim)),
+            "wo": (plain, self.n_heads * self.v_head_dim, dim),
+        })
+        for name, (cfg, fin, fout) in table.items():
+            setattr(self, name, cfg.build(in_features=fin, out_features=fout))
+        if self.q_lora_rank > 0:
+            self.q_norm = c.q_norm.build(normalized_shape=self.q_lora_rank)
+        self.kv_norm = c.kv_norm.build(normalized_shape=self.kv_lora_rank)
+        self.softmax_scale = self._scale(c)
+        self.attn_backend = c.attn_backend
         self.inner_attention = InnerAttention()
 
-    def forward(self, x, freqs_cis, attention_masks, positions=None):
-        bsz, seqlen, _ = x.shape
+    def _scale(self, c) -> float:
+        """1 / sqrt(query width), times the YaRN attention factor squared once the context exceeds the original one."""
+        scale = self.qk_head_dim**-0.5
+        if c.rope_max_seq_len > c.rope_original_seq_len:
+            scale *= (0.1 * c.mscale * math.log(c.rope_factor) + 1.0) ** 2
+        return scale
+
+    def _queries(self, x, freqs_cis, positions):
+        """[B, S, heads, nope + rope]: the rope slice of every head is rotated (adjacent pairs), the rest passes through."""
         q = self.wq(x) if self.q_lora_rank == 0 else self.wq_b(self.q_norm(self.wq_a(x)))
-        q = q.view(bsz, seqlen, -1, self.qk_head_dim)  # -1: heads are sharded under tensor parallel
-        q_nope, q_pe = torch.split(q, [self.qk_nope_head_dim, self.qk_rope_head_dim], dim=-1)
-        q_pe = apply_rotary_emb_single(q_pe, freqs_cis, positions, "interleaved")
-        q = torch.cat((q_nope, q_pe), dim=-1)
-        kv = self.wkv_a(x)
-        kv, k_pe = torch.split(kv, [self.kv_lora_rank, self.qk_rope_head_dim], dim=-1)
-        k_pe = apply_rotary_emb_single(k_pe.unsqueeze(2), freqs_cis, positions, "interleaved")
-        kv = self.wkv_b(self.kv_norm(kv)).view(bsz, seqlen, -1, self.qk_nope_head_dim + self.v_head_dim)
-        k_nope, v = torch.split(kv, [self.qk_nope_head_dim, self.v_head_dim], dim=-1)
-        k = torch.cat((k_nope, k_pe.expand(-1, -1, k_nope.shape[2], -1)), dim=-1)
+        q = q.unflatten(-1, (-1, self.qk_head_dim))              # heads may be a tensor-parallel shard
+        rot = apply_rotary_emb_single(q[..., self.qk_nope_head_dim:], freqs_cis, positions, "interleaved")
+        return torch.cat((q[..., : self.qk_nope_head_dim], rot), dim=-1)
+
+    def _keys_values(self, x, freqs_cis, positions):
+        """Latent -> per-head keys [nope | shared rotated rope key] and values."""
+        latent, k_rope = self.wkv_a(x).split([self.kv_lora_rank, self.qk_rope_head_dim], dim=-1)
+        k_rope = apply_rotary_emb_single(k_rope.unsqueeze(2), freqs_cis, positions, "interleaved")   # one key for all heads
+        kv = self.wkv_b(self.kv_norm(latent)).unflatten(-1, (-1, self.qk_nope_head_dim + self.v_head_dim))
+        k_nope, v = kv.split([self.qk_nope_head_dim, self.v_head_dim], dim=-1)
+        return torch.cat((k_nope, k_rope.expand(-1, -1, k_nope.shape[2], -1)), dim=-1), v
+
+    def forward(self, x, freqs_cis, attention_masks, positions=None):
         if self.attn_backend == "flex":
             assert isinstance(attention_masks, AttentionMasks)
         else:
             assert attention_masks is None
-        out = self.inner_attention(q, k, v, masks=attention_masks, scale=self.softmax_scale)
-        return self.wo(out.reshape(bsz, seqlen, -1))
+        q = self._queries(x, freqs_cis, positions)
+        k, v = self._keys_values(x, freqs_cis, positions)
+        # 192-wide queries / keys and 128-wide values: the attention kernels have an instantiation for this pair
+        out = self.inner_attention(q, k, v.contiguous(), masks=attention_masks, scale=self.softmax_scale)
+        return self.wo(out.flatten(2))
 
     def init_weights(self, **kwargs) -> None:
         init_std = kwargs.get("init_std")
         assert init_std is not None
-        lins = [self.wkv_a, self.wkv_b] + ([self.wq_a, self.wq_b] if self.q_lora_rank > 0 else [self.wq])
-        for lin in lins:
-            lin.init_weights()
-        self.wo.init_weights(init_std=init_std)
-        self.kv_norm.init_weights()
-        if self.q_lora_rank > 0:
-            self.q_norm.init_weights()
+        for name, mod in self.named_children():
+            if name == "wo":
+                mod.init_weights(init_std=init_std)
+            elif name != "inner_attention":
+                mod.init_weights()
 
 
 class DeepSeekV3TransformerBlock(TransformerBlock):

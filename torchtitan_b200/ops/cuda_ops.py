@@ -1042,9 +1042,9 @@ def gemm_mxfp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.b
     L = _lib()
     qa, qb = qa.contiguous(), qb.contiguous()
     sa, sb = sa.contiguous(), sb.contiguous()
-    swa = torch.empty(L.tt_mx_scales_bytes(M, 128, K), dtype=torch.uint8, device=qa.device)
+    swa = torch.empty(L.tt_mx_scales_bytes(M, 256, K), dtype=torch.uint8, device=qa.device)   # 256-row padding: CTA-pair tiles
     swb = torch.empty(L.tt_mx_scales_bytes(N, 256, K), dtype=torch.uint8, device=qa.device)
-    _ck(L.tt_mx_swizzle_scales(sa.data_ptr(), M, K, 128, swa.data_ptr(), _stream()), "tt_mx_swizzle_scales")
+    _ck(L.tt_mx_swizzle_scales(sa.data_ptr(), M, K, 256, swa.data_ptr(), _stream()), "tt_mx_swizzle_scales")
     _ck(L.tt_mx_swizzle_scales(sb.data_ptr(), N, K, 256, swb.data_ptr(), _stream()), "tt_mx_swizzle_scales")
     c_fp32 = out_dtype == torch.float32
     out = torch.empty(M, N, dtype=torch.float32 if c_fp32 else torch.bfloat16, device=qa.device)

@@ -87,6 +87,8 @@ def lib():
     if hasattr(L, "tt_gemm_mxfp8"):
         _sig(L.tt_gemm_mxfp8, [P, P, P, P, P, I, I, I, LL, LL, LL, I, P])
         _sig(L.tt_mx_swizzle_scales, [P, I, I, I, P, P])
+        if hasattr(L, "tt_gemm_mx_set_pair"):
+            _sig(L.tt_gemm_mx_set_pair, [I], None)
         L.tt_mx_scales_bytes.argtypes = [I, I, I]
         L.tt_mx_scales_bytes.restype = LL
     if hasattr(L, "tt_mxfp8_quant_rows"):

@@ -90,10 +90,32 @@ def bench_gemm_mxfp8(args, timer):
     M, N, K = args.m, args.n, args.k
     a = torch.randn(M, K, device="cuda").bfloat16()
     b = torch.randn(N, K, device="cuda").bfloat16()
+    from torchtitan_b200.ops import native
+
     qa, sa = cuda_ops.quantize_mxfp8_operand(a)
     qb, sb = cuda_ops.quantize_mxfp8_operand(b)
+    # the GEMM alone: operands quantised once with their scales already in the MMA's layout
+    (A8, swa), (B8, swb) = cuda_ops._mx_operand(a, False), cuda_ops._mx_operand(b, False)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    L = native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def raw():
+        native.check(L.tt_gemm_mxfp8(A8.data_ptr(), B8.data_ptr(), swa.data_ptr(), swb.data_ptr(), out.data_ptr(), M, N, K,
+                                     A8.stride(0), B8.stride(0), out.stride(0), 0, stream), "tt_gemm_mxfp8")
+
+    res = {"case": "gemm_mxfp8_block_scaled", "M": M, "N": N, "K": K}
+    for name, pair in (("cta_pair", 1), ("single_cta", 0)):
+        if native.has("tt_gemm_mx_set_pair"):
+            L.tt_gemm_mx_set_pair(pair)
+        elif pair:
+            continue
+        ms = timer.time(raw, args.iters)
+        res.update({f"{name}_ms": ms, f"{name}_tflops": 2 * M * N * K / ms / 1e9})
+    if native.has("tt_gemm_mx_set_pair"):
+        L.tt_gemm_mx_set_pair(1)
     ms = timer.time(lambda: cuda_ops.gemm_mxfp8(qa, qb, sa, sb, torch.bfloat16), args.iters)
-    res = {"case": "gemm_mxfp8_block_scaled", "M": M, "N": N, "K": K, "ms": ms, "tflops": 2 * M * N * K / ms / 1e9}
+    res.update({"with_scale_relayout_launches_ms": ms})
     at = torch.randn(K, M, device="cuda").bfloat16().t()
     for name, fn in (("mx_quant_rows", lambda: cuda_ops.quantize_mxfp8_operand(a)),
                      ("mx_quant_transposed", lambda: cuda_ops.quantize_mxfp8_operand(at)),
