@@ -101,7 +101,7 @@ def test_gemm_accumulate_and_strided(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,D", [(64, 4096), (1000, 128), (33, 2048), (4096, 512), (16, 16384)])
+@pytest.mark.parametrize("rows,D", [(64, 4096), (1000, 128), (33, 2048), (4096, 512), (16, 16384), (300, 2048), (1025, 4096)])
 def test_rmsnorm(ops, dtype, rows, D):
     torch.manual_seed(0)
     x = torch.randn(rows, D, device="cuda", dtype=dtype, requires_grad=True)

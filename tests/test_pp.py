@@ -8,7 +8,8 @@ import torch
 
 from dist_utils import run_ranks
 from torchtitan_b200.parallel.pp import (
-    build_actions, generate_llm_fqn_per_model_part, stage_indices_for_rank, validate_actions,
+    Action, build_actions, estimate_makespan, fuse_split_backward, generate_llm_fqn_per_model_part, load_csv_actions,
+    stage_indices_for_rank, validate_actions,
 )
 
 
@@ -35,6 +36,47 @@ def test_schedules_are_complete_and_deadlock_free(schedule, pp, spr, style, n_mb
         stages = stage_indices_for_rank(r, pp, num_stages, style)
         assert sorted((a.stage, a.kind, a.mb) for a in acts) == sorted(
             (s, k, m) for s in stages for k in "FB" for m in range(n_mb))
+
+
+@pytest.mark.parametrize("schedule,pp,spr,style", [
+    ("InterleavedZeroBubble", 4, 2, "loop"), ("InterleavedZeroBubble", 2, 3, "loop"), ("ZBVZeroBubble", 2, 2, "v"),
+    ("ZBVZeroBubble", 4, 2, "v"), ("DualPipeV", 8, 2, "v"),
+])
+@pytest.mark.parametrize("n_mb", [4, 8, 5, 16])
+def test_zero_bubble_schedules_split_the_backward(schedule, pp, spr, style, n_mb):
+    num_stages = pp * spr
+    split = build_actions(schedule, pp, num_stages, n_mb, style, split=True)
+    validate_actions(split, pp, num_stages, n_mb, style)
+    for r, acts in enumerate(split):
+        stages = stage_indices_for_rank(r, pp, num_stages, style)
+        assert sorted((a.stage, a.kind, a.mb) for a in acts) == sorted(
+            (s, k, m) for s in stages for k in "FIW" for m in range(n_mb))
+        where = {(a.stage, a.kind, a.mb): i for i, a in enumerate(acts)}
+        assert all(where[(s, "W", m)] > where[(s, "I", m)] for s in stages for m in range(n_mb))
+    # the weight-gradient halves are really moved: on some rank one runs after a later micro-batch's input gradient
+    assert any(a.kind == "W" and any(b.kind == "I" and (b.stage, b.mb) != (a.stage, a.mb) for b in acts[i - 1:i])
+               for acts in split for i, a in enumerate(acts) if i)
+    whole = build_actions(schedule, pp, num_stages, n_mb, style)
+    validate_actions(whole, pp, num_stages, n_mb, style)
+    assert estimate_makespan(split, num_stages)[0] <= estimate_makespan(whole, num_stages)[0]
+    if n_mb >= 2 * pp:                                   # the idle share of a step, forward 1 / backward 2 units
+        assert estimate_makespan(split, num_stages)[1] < 0.15
+    fused = fuse_split_backward(split)
+    validate_actions(fused, pp, num_stages, n_mb, style)
+    assert all(a.kind in "FB" for acts in fused for a in acts)
+
+
+def test_schedule_checks_reject_a_weight_step_before_its_input_step(tmp_path):
+    path = tmp_path / "sched.csv"
+    path.write_text("0F0,0F1,0I0,0W0,0I1,0W1\n1F0,1I0,1F1,1I1,1W0,1W1\n")
+    ranks = load_csv_actions(str(path))
+    assert ranks[1][-1] == Action(1, "W", 1) and ranks[0][2].kind == "I"
+    validate_actions(ranks, 2, 2, 2, "loop")
+    bad = [ranks[0], [Action(1, "F", 0), Action(1, "W", 0), Action(1, "I", 0), Action(1, "F", 1), Action(1, "I", 1), Action(1, "W", 1)]]
+    with pytest.raises(RuntimeError, match="comes before"):
+        validate_actions(bad, 2, 2, 2, "loop")
+    with pytest.raises(RuntimeError, match="without a weight-gradient step"):
+        validate_actions([ranks[0], ranks[1][:-1]], 2, 2, 2, "loop")
 
 
 def _worker(rank, world, schedule):
@@ -85,12 +127,15 @@ def _worker(rank, world, schedule):
     else:
         sched.eval(target=lab if last else None, losses=ev)
     out["eval"] = float(torch.stack(ev).sum()) / lab.numel() if last else None
+    out["kinds"] = "".join(sorted({a.kind for a in sched.all_actions[rank]}))
     return out
 
 
-@pytest.mark.parametrize("schedule", ["1F1B", "Interleaved1F1B", "ZBVZeroBubble"])
+@pytest.mark.parametrize("schedule", ["1F1B", "Interleaved1F1B", "InterleavedZeroBubble", "ZBVZeroBubble", "DualPipeV"])
 def test_pp2_matches_single_process(tmp_path, schedule):
     res = run_ranks(_worker, 2, schedule, tmp_path=tmp_path)
+    # pipeline-only stages own their gradients, so the zero-bubble schedules run with separate I / W steps
+    assert all(o["kinds"] == ("FIW" if "Zero" in schedule or schedule == "DualPipeV" else "BF") for o in res), res
     got = [o for o in res if o["loss"] is not None]
     assert got, res
     for o in got:

@@ -105,6 +105,53 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
+// Register-resident form for bf16 rows of 256 * NV elements (NV <= 16, e.g. 4096): one warp per row, the row is read
+// once (NV 16-byte vectors per lane), reduced with shuffles only and written back; the weight vector (8 KB at most)
+// is re-read per row from L1. No block-level synchronisation, so many rows are in flight per SM.
+template <int NV>
+__global__ void __launch_bounds__(256, 2)
+rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, long long rows, float eps) {
+  constexpr int D = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const __nv_bfloat16* xr = x + row * D;
+    uint4 v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) v[j] = *reinterpret_cast<const uint4*>(xr + (j * 32 + lane) * 8);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); ss += f.x * f.x + f.y * f.y; }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    __nv_bfloat16* yr = y + row * D;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+      uint4 wq = make_uint4(0, 0, 0, 0);
+      if (w) wq = __ldg(reinterpret_cast<const uint4*>(w + (j * 32 + lane) * 8));
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wq);
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = __bfloat1622float2(h[e]);
+        f.x *= rstd; f.y *= rstd;
+        if (w) { const float2 g = __bfloat1622float2(wh[e]); f.x *= g.x; f.y *= g.y; }
+        oh[e] = __floats2bfloat162_rn(f.x, f.y);
+      }
+      *reinterpret_cast<uint4*>(yr + (j * 32 + lane) * 8) = o;
+    }
+  }
+}
+
 // dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw partials per block row-slice -> scratch[blk, D]
 template <typename T, int G>
 __global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
@@ -428,6 +475,17 @@ extern "C" {
 int tt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int D, float eps, int dtype,
                    cudaStream_t st) {
   if (D % 8) return -1;
+  if (dtype == 0 && rows >= 64 && (D == 4096 || D == 2048) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (w == nullptr || (reinterpret_cast<uintptr_t>(w) & 15) == 0)) {
+    long long blocks = (rows + 7) / 8;                 // 8 warps per block, one row per warp and pass
+    if (blocks > kSMs * 8) blocks = kSMs * 8;
+    const auto* xp = static_cast<const __nv_bfloat16*>(x);
+    const auto* wp = static_cast<const __nv_bfloat16*>(w);
+    auto* yp = static_cast<__nv_bfloat16*>(y);
+    if (D == 4096) rmsnorm_fwd_warp_kernel<16><<<static_cast<int>(blocks), 256, 0, st>>>(xp, wp, yp, rstd, rows, eps);
+    else rmsnorm_fwd_warp_kernel<8><<<static_cast<int>(blocks), 256, 0, st>>>(xp, wp, yp, rstd, rows, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   if (D <= 1024) {
     const int threads = 256, gpb = threads / 32;
     int grid = static_cast<int>((rows + gpb - 1) / gpb); if (grid > kSMs * 8) grid = kSMs * 8; if (grid < 1) grid = 1;

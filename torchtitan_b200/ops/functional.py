@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from . import reference as ref
+from .wgrad_store import WeightGradStore, split_linear
 
 
 def native_available() -> bool:
@@ -19,6 +20,8 @@ def _cuda(x) -> bool:
 
 
 def linear(x, weight, bias=None):
+    if WeightGradStore.enabled and weight.requires_grad and torch.is_grad_enabled():
+        return split_linear(x, weight, bias)   # a pipeline schedule with separate weight-gradient actions is running
     if _cuda(x):
         from . import cuda_ops
 

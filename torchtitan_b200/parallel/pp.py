@@ -13,9 +13,14 @@ The runtime is this framework's own (the reference uses ``torch.distributed.pipe
 schedule is a per-rank list of actions ``(stage, F|B, microbatch)``; activations and their gradients
 travel by asynchronous NCCL/gloo point-to-point messages; every stage output keeps its autograd graph
 until its backward action. Schedules: ``GPipe``, ``1F1B``, ``Interleaved1F1B`` / ``LoopedBFS`` (two or
-more stages per rank), ``ZBVZeroBubble`` and ``DualPipeV`` (V placement; input- and weight-gradient
-work is not split, so they run as a V-shaped interleaved 1F1B), and CSV files with one line of
-actions per rank (``0F0,0F1,0B0,...``).
+more stages per rank), ``InterleavedZeroBubble``, ``ZBVZeroBubble`` and ``DualPipeV`` (the last two with V
+placement), and CSV files with one line of actions per rank (``0F0,0F1,0I0,0W0,...``).
+
+Zero-bubble schedules split a backward step into ``I`` (gradient of the stage input, sent on at once) and ``W`` (the
+weight gradients of the stage's linear layers, parked by ``ops/wgrad_store.py`` and run where the rank would wait for
+a message). The split needs weights that own their ``.grad`` (pipeline-only or pipeline x tensor parallel); stages
+under FSDP or replicate units, whose reduce-scatter consumes the weight gradients inside the backward pass, run the
+same placement with whole ``B`` steps and say so at start-up.
 """
 
 from __future__ import annotations
@@ -30,6 +35,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from torchtitan_b200.ops.wgrad_store import WeightGradStore
 from torchtitan_b200.tools.logging import logger
 
 __all__ = ["pipeline_llm", "generate_llm_fqn_per_model_part", "pipeline_module_split", "PipelineSchedule",
@@ -123,7 +129,7 @@ def pipeline_module_split(whole: nn.Module, pp_rank: int, pp: int, schedule: str
 @dataclass(frozen=True)
 class Action:
     stage: int
-    kind: str  # "F" or "B"
+    kind: str  # "F" forward, "B" whole backward, "I" input-gradient half, "W" weight-gradient half
     mb: int
 
 
@@ -132,8 +138,8 @@ def _parse_action(tok: str) -> Action:
     if not m:
         raise ValueError(f"cannot parse pipeline action '{tok}'")
     kind = m.group(2)
-    if kind in ("I", "BW"):
-        kind = "B"  # input-gradient / fused backward both run the whole stage backward here
+    if kind == "BW":
+        kind = "B"
     return Action(int(m.group(1)), kind, int(m.group(3)))
 
 
@@ -141,13 +147,119 @@ def load_csv_actions(path: str) -> list[list[Action]]:
     rows = []
     with open(path, newline="") as f:
         for row in csv.reader(f):
-            acts = [_parse_action(t) for t in row if t.strip()]
-            rows.append([a for a in acts if a.kind in ("F", "B")])  # separate weight-grad steps are no-ops
+            rows.append([_parse_action(t) for t in row if t.strip()])
     return rows
 
 
-def build_actions(schedule: str, pp: int, num_stages: int, n_mb: int, style: str = "loop") -> list[list[Action]]:
-    """Per-rank ordered action lists."""
+def fuse_split_backward(ranks: list[list[Action]]) -> list[list[Action]]:
+    """The same schedule with whole backward steps: ``I`` becomes ``B`` and ``W`` is dropped."""
+    return [[Action(a.stage, "B", a.mb) if a.kind == "I" else a for a in acts if a.kind != "W"] for acts in ranks]
+
+
+def split_backward(ranks: list[list[Action]], pp: int, style: str) -> list[list[Action]]:
+    """Turn every ``B`` into ``I`` plus a later ``W``. A rank keeps up to ``lag`` weight-gradient steps in hand and
+    runs the oldest after each ``I`` beyond that, so in the cool-down (where a rank waits for the next gradient after
+    every ``I``) one ``W`` fills each wait, and the rest run at the end instead of the idle tail. ``lag`` is the number
+    of ranks behind this one in the backward direction (``pp - 1 - rank``) for loop placement and ``pp - 1`` for V
+    placement, where every rank holds both an early and a late stage."""
+    out = []
+    for r, acts in enumerate(ranks):
+        lag = (pp - 1 - r) if style == "loop" else (pp - 1)
+        res, backlog = [], []
+        for a in acts:
+            if a.kind != "B":
+                res.append(a)
+                continue
+            res.append(Action(a.stage, "I", a.mb))
+            backlog.append(Action(a.stage, "W", a.mb))
+            if len(backlog) > lag:
+                res.append(backlog.pop(0))
+        out.append(res + backlog)
+    return out
+
+
+def list_schedule(pp: int, num_stages: int, n_mb: int, style: str, slack: int = 1, split: bool = True) -> list[list[Action]]:
+    """Pipeline order by list scheduling on a unit-time grid: a forward and each backward half take one tick, a whole
+    backward two. With ``split`` a backward is an ``I`` step plus a parked ``W`` step (zero-bubble order), otherwise
+    one ``B`` step. A free rank prefers, in this order: a backward (input-gradient) step whose gradient has arrived (it
+    unblocks the rank before it; deepest local stage first), a weight-gradient step once more than ``pp`` of them are
+    parked (bounds the activations they hold), a forward step (deepest local stage first, so a micro-batch reaches the
+    loss as early as possible) while the stage has fewer than ``slack * ceil(2 (S - s) / (3 L)) + 1`` micro-batches
+    in flight (``S`` stages, ``L`` per rank: the round trip from stage ``s`` to the loss and back over the time a rank
+    spends per micro-batch), and otherwise a parked weight-gradient step: that is what fills the waits of the warm-up
+    and cool-down phases. The oldest micro-batch in flight is never held by a cap (a stage works in order, so the
+    stage it waits at holds nothing newer), hence the loop always makes progress."""
+    my_stages = [stage_indices_for_rank(r, pp, num_stages, style) for r in range(pp)]
+    n_local = len(my_stages[0])
+    done_at: dict = {}                                    # (stage, "F" | "B", mb) -> first tick at which the result exists
+    ranks: list[list[Action]] = [[] for _ in range(pp)]
+    next_f = [{s: 0 for s in my_stages[r]} for r in range(pp)]
+    next_b = [{s: 0 for s in my_stages[r]} for r in range(pp)]
+    parked: list[list[Action]] = [[] for _ in range(pp)]
+    busy_until = [0] * pp
+    inflight = {s: 0 for st in my_stages for s in st}
+    cap = {s: slack * math.ceil(2 * (num_stages - s) / (3 * n_local)) + 1 for s in inflight}
+    total = sum((3 if split else 2) * n_mb * len(st) for st in my_stages)
+    emitted, t = 0, 0
+    never = 1 << 60
+    while emitted < total:
+        for r in range(pp):
+            if busy_until[r] > t:
+                continue
+            pick = None
+            for st in sorted(my_stages[r], reverse=True):
+                m = next_b[r][st]
+                if m < n_mb and done_at.get((st, "F", m), never) <= t and \
+                        (st == num_stages - 1 or done_at.get((st + 1, "B", m), never) <= t):
+                    pick = Action(st, "I" if split else "B", m)
+                    break
+            if pick is None and len(parked[r]) > pp:
+                pick = parked[r][0]
+            if pick is None:
+                for st in sorted(my_stages[r], reverse=True):
+                    m = next_f[r][st]
+                    if m < n_mb and inflight[st] < cap[st] and (st == 0 or done_at.get((st - 1, "F", m), never) <= t):
+                        pick = Action(st, "F", m)
+                        break
+            if pick is None and parked[r]:
+                pick = parked[r][0]
+            if pick is None:
+                continue
+            ranks[r].append(pick)
+            emitted += 1
+            busy_until[r] = t + (2 if pick.kind == "B" else 1)
+            if pick.kind == "F":
+                done_at[(pick.stage, "F", pick.mb)] = busy_until[r]
+                next_f[r][pick.stage] += 1
+                inflight[pick.stage] += 1
+            elif pick.kind == "W":
+                parked[r].pop(0)
+            else:
+                done_at[(pick.stage, "B", pick.mb)] = busy_until[r]
+                next_b[r][pick.stage] += 1
+                inflight[pick.stage] -= 1
+                if split:
+                    parked[r].append(Action(pick.stage, "W", pick.mb))
+        t += 1
+        if t > 16 * total + 64:
+            raise RuntimeError("pipeline list scheduling made no progress")
+    return ranks
+
+
+def _shortest(candidates: list, num_stages: int):
+    return min(candidates, key=lambda acts: estimate_makespan(acts, num_stages)[0])     # ties: the earlier candidate
+
+
+def build_actions(schedule: str, pp: int, num_stages: int, n_mb: int, style: str = "loop",
+                  split: bool = False) -> list[list[Action]]:
+    """Per-rank ordered action lists. ``split`` gives a zero-bubble schedule separate I / W steps. The zero-bubble
+    schedules take the shortest (by :func:`estimate_makespan`) of the interleaved-1F1B-derived order and two list-scheduled
+    orders (in-flight slack 1 to 3; more slack holds more activations, and ties go to less)."""
+    if schedule in ZERO_BUBBLE:
+        base = build_actions("Interleaved1F1B", pp, num_stages, n_mb, style)
+        if split:
+            base = split_backward(base, pp, style)
+        return _shortest([base] + [list_schedule(pp, num_stages, n_mb, style, k, split) for k in (1, 2, 3)], num_stages)
     ranks: list[list[Action]] = [[] for _ in range(pp)]
     my_stages = [stage_indices_for_rank(r, pp, num_stages, style) for r in range(pp)]
     if schedule == "GPipe":
@@ -209,15 +321,55 @@ def validate_actions(ranks: list[list[Action]], pp: int, num_stages: int, n_mb: 
                 a = acts[pos[r]]
                 if a.kind == "F":
                     ready = a.stage == 0 or (a.stage - 1, "F", a.mb) in done
-                else:
+                elif a.kind == "W":
+                    if (a.stage, "I", a.mb) not in done:
+                        raise RuntimeError(f"pipeline schedule: {a.stage}W{a.mb} on rank {r} comes before its {a.stage}I{a.mb}")
+                    ready = True
+                else:                                    # "B" and "I" both deliver the input gradient, recorded as "B"
                     ready = (a.stage, "F", a.mb) in done and (a.stage == num_stages - 1 or (a.stage + 1, "B", a.mb) in done)
                 if not ready:
                     break
                 done.add((a.stage, a.kind, a.mb))
+                if a.kind == "I":
+                    done.add((a.stage, "B", a.mb))
                 pos[r] += 1
                 progressed = True
     if any(pos[r] < len(ranks[r]) for r in range(len(ranks))):
         raise RuntimeError(f"pipeline schedule deadlocks: progress {pos} of {[len(a) for a in ranks]}")
+    owed = {(a.stage, a.mb) for acts in ranks for a in acts if a.kind == "I"} - \
+           {(a.stage, a.mb) for acts in ranks for a in acts if a.kind == "W"}
+    if owed:
+        raise RuntimeError(f"pipeline schedule: input-gradient steps without a weight-gradient step: {sorted(owed)[:4]}")
+
+
+def estimate_makespan(ranks: list[list[Action]], num_stages: int, cost: dict | None = None) -> tuple[float, float]:
+    """Length of one step and the idle fraction of the busiest-possible timeline, from a dependency simulation with
+    per-action costs (default: a forward 1, a whole backward 2, each backward half 1; messages are free)."""
+    cost = cost or {"F": 1.0, "B": 2.0, "I": 1.0, "W": 1.0}
+    finish: dict = {}
+    pos, free = [0] * len(ranks), [0.0] * len(ranks)
+    progressed = True
+    while progressed:
+        progressed = False
+        for r, acts in enumerate(ranks):
+            while pos[r] < len(acts):
+                a = acts[pos[r]]
+                if a.kind == "F":
+                    deps = [(a.stage - 1, "F", a.mb)] if a.stage > 0 else []
+                elif a.kind == "W":
+                    deps = [(a.stage, "B", a.mb)]
+                else:
+                    deps = [(a.stage, "F", a.mb)] + ([(a.stage + 1, "B", a.mb)] if a.stage < num_stages - 1 else [])
+                if any(d not in finish for d in deps):
+                    break
+                end = max([free[r]] + [finish[d] for d in deps]) + cost[a.kind]
+                finish[(a.stage, "B" if a.kind == "I" else a.kind, a.mb)] = end
+                free[r] = end
+                pos[r] += 1
+                progressed = True
+    total = max(free)
+    busy = max(sum(cost[a.kind] for a in acts) for acts in ranks)
+    return total, 1.0 - busy / total if total else 0.0
 
 
 # ------------------------------------------------------------------------------------ runtime
@@ -290,7 +442,7 @@ class PipelineSchedule:
             for a in acts:
                 if a.kind == "F" and a.stage < self.num_stages - 1 and self._rank_of(a.stage + 1) == self.rank:
                     seq.append(("act", a.stage + 1, a.mb))
-                if a.kind == "B" and a.stage > 0 and self._rank_of(a.stage - 1) == self.rank:
+                if a.kind in ("B", "I") and a.stage > 0 and self._rank_of(a.stage - 1) == self.rank:
                     seq.append(("grad", a.stage - 1, a.mb))
             orders[r] = seq
         return orders
@@ -354,7 +506,11 @@ class PipelineSchedule:
             target_mb = list(torch.tensor_split(target, n, dim=0)) if n > 1 else [target]
         saved: dict = {}
         pending: list = []
+        parked: dict = {}                                # (stage, mb) -> weight-gradient closures of its "I" action
         for a in actions_per_rank[self.rank]:
+            if a.kind == "W":
+                WeightGradStore.run(parked.pop((a.stage, a.mb)))
+                continue
             mod = self.stages[a.stage]
             first, last = a.stage == 0, a.stage == self.num_stages - 1
             if a.kind == "F":
@@ -380,12 +536,16 @@ class PipelineSchedule:
             else:
                 x, out = saved.pop((a.stage, a.mb))
                 if last:
-                    out.backward()
+                    g = None
+                elif (a.stage + 1) in self.stages:
+                    g = self._local_grads.pop((a.stage, a.mb))
                 else:
-                    if (a.stage + 1) in self.stages:
-                        g = self._local_grads.pop((a.stage, a.mb))
-                    else:
-                        g = self._recv("grad", a.stage, a.mb, a.stage + 1)
+                    g = self._recv("grad", a.stage, a.mb, a.stage + 1)
+                if a.kind == "I":
+                    with WeightGradStore.collect() as queue:
+                        torch.autograd.backward(out, g)
+                    parked[(a.stage, a.mb)] = queue
+                else:
                     torch.autograd.backward(out, g)
                 if not first:
                     gx = x.grad
@@ -396,6 +556,7 @@ class PipelineSchedule:
             pending = [(w, t) for (w, t) in pending if not w.is_completed()]
         for w, _ in pending:
             w.wait()
+        assert not parked, f"weight-gradient steps never ran for {sorted(parked)}"
 
     def step(self, *args, target=None, losses=None, loss_scale=None, return_outputs: bool = False, **kwargs):
         self._run(self.all_actions, args, kwargs, target, losses, loss_scale, train=True)
@@ -454,22 +615,37 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
         logger.warning(
             f"Number of microbatches ({n_mb}) is less than the total number of stages ({num_stages}) which may result in a bubble in the pipeline."
         )
+    from .fsdp import fsdp_units
+
+    # weight gradients can be parked only where the weights own their .grad (no FSDP / replicate units on the stages)
+    can_split = not any(fsdp_units(m) for m in parts)
+    wanted_split = schedule in ZERO_BUBBLE
     if csv_path:
         all_actions = load_csv_actions(csv_path)
         assert len(all_actions) == pp, f"CSV schedule has {len(all_actions)} rows for {pp} pipeline ranks"
+        wanted_split = any(a.kind in ("I", "W") for acts in all_actions for a in acts)
+        if not can_split:
+            all_actions = fuse_split_backward(all_actions)
     else:
-        all_actions = build_actions(schedule, pp, num_stages, n_mb, style)
+        all_actions = build_actions(schedule, pp, num_stages, n_mb, style, split=can_split)
     validate_actions(all_actions, pp, num_stages, n_mb, style)
     sched = PipelineSchedule(
         stages=dict(zip(idx, parts)), all_actions=all_actions, pp_group=pp_mesh.get_group(), pp_rank=pp_rank, pp=pp,
         num_stages=num_stages, n_microbatches=n_mb, loss_fn=loss_fn, style=style, device=device,
     )
     logger.info(f"Using pipeline schedule {schedule if not csv_path else csv_path} with {n_mb} microbatches and {num_stages} stages.")
-    if not csv_path and schedule in ZERO_BUBBLE:
-        # said at start-up, not only in the documentation: the name selects the stage placement, not a zero-bubble order
+    has_split = any(a.kind in ("I", "W") for acts in all_actions for a in acts)
+    WeightGradStore.enabled = has_split
+    logger.info("Pipeline bubble estimate (forward 1, backward 2 units per stage and micro-batch): "
+                f"{estimate_makespan(all_actions, num_stages)[1]:.1%} of the step")
+    if has_split:
+        logger.info("Pipeline backward steps are split: input gradients are sent on first, the weight gradients of the "
+                    "linear layers run where the rank would wait")
+    elif wanted_split:
+        # said at start-up, not only in the documentation
         logger.warning(
-            f"Pipeline schedule {schedule}: this runtime does not split a backward step into its input-gradient and "
-            f"weight-gradient halves, so the schedule runs as {'a V-shaped' if schedule in V_STYLE else 'an'} interleaved 1F1B "
-            "(same stage placement and results, the bubble of 1F1B)."
-        )
+            f"Pipeline schedule {csv_path or schedule}: the stages are under FSDP / replicate units, whose gradient "
+            "reduction consumes the weight gradients inside the backward pass, so input- and weight-gradient work is not "
+            f"split and the schedule runs as {'a V-shaped' if style != 'loop' else 'an'} interleaved 1F1B "
+            "(same stage placement and results, the bubble of 1F1B).")
     return sched, parts, sched.has_first, sched.has_last
