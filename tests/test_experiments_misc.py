@@ -277,3 +277,121 @@ def test_vlm_loader_feeds_the_model_and_resumes():
     masks = model.get_attention_masks(inputs["input"], types.SimpleNamespace(eos_id=0))
     out = model(inputs["input"], inputs["pixel_values"], inputs["grid_thw"], inputs["special_tokens"], masks)
     assert out.shape == (2, 128, mc.vocab_size)
+
+
+class _ByteTokenizer:
+    """UTF-8 bytes as token ids, the four image tokens after them."""
+
+    eos_id = 256
+    _special = {"<|image|>": 300, "<|begin_of_image|>": 301, "<|end_of_image|>": 302, "<|pad|>": 303}
+
+    def encode(self, text, add_bos=False, add_eos=False):
+        return list(text.encode("utf-8")) + ([self.eos_id] if add_eos else [])
+
+    def token_to_id(self, tok):
+        return self._special.get(tok)
+
+
+def _jpeg(w, h, seed):
+    import io
+
+    from PIL import Image
+
+    g = torch.Generator().manual_seed(seed)
+    data = (torch.rand(h, w, 3, generator=g) * 255).to(torch.uint8).numpy()
+    buf = io.BytesIO()
+    Image.fromarray(data, "RGB").save(buf, format="JPEG")
+    return buf.getvalue()
+
+
+def _write_caption_shards(folder, n_shards=2, per_shard=6):
+    import io
+    import tarfile
+
+    for s in range(n_shards):
+        with tarfile.open(str(folder / f"shard-{s:03d}.tar"), "w") as tar:
+            for i in range(per_shard):
+                key = f"{s:03d}{i:04d}"
+                for ext, payload in (("jpg", _jpeg(32 + 16 * (i % 3), 48 + 16 * (i % 2), s * 100 + i)),
+                                     ("txt", f"caption number {s}-{i} " .encode() * (1 + i % 3))):
+                    info = tarfile.TarInfo(f"{key}.{ext}")
+                    info.size = len(payload)
+                    tar.addfile(info, io.BytesIO(payload))
+
+
+def test_vlm_caption_shards_pack_collate_shard_and_resume(tmp_path):
+    """CC12M-style WebDataset shards through the registry entry ``cc12m-test``: every row keeps image placeholders and
+    patches one to one, labels ignore image tokens and padding, two data-parallel ranks see different samples, packing
+    puts several samples into a row, and a restored loader continues with the batch the first one would have produced."""
+    from torchtitan_b200.experiments.vlm.datasets import MMDataLoader
+
+    _write_caption_shards(tmp_path)
+    tok = _ByteTokenizer()
+
+    def build(rank=0, world=1, buffer=0):
+        cfg = MMDataLoader.Config(dataset="cc12m-test", dataset_path=str(tmp_path), infinite=False, max_patches_per_image=16,
+                                  max_images_per_batch=16, packing_buffer_size=buffer)
+        return cfg.build(dp_world_size=world, dp_rank=rank, tokenizer=tok, seq_len=160, local_batch_size=2)
+
+    dl = build()
+    st = dl.special_tokens
+    assert (st.img_id, st.boi_id, st.eoi_id, st.pad_id) == (300, 301, 302, 303)
+    batches = list(dl)
+    assert len(batches) == 6                                      # 12 samples, one per row, two rows per batch
+    for inputs, labels in batches:
+        assert inputs["input"].shape == (2, 160) and labels.shape == (2, 160)
+        n_img = int((inputs["input"] == st.img_id).sum())
+        assert n_img > 0 and n_img == int((inputs["grid_thw"][:, :, 1:] != -1).all(-1).sum())
+        assert not any(int((labels == t).sum()) for t in (300, 301, 302, 303))
+        assert int((labels == tok.eos_id).sum()) == 2             # every document ends with the end-of-text token
+        assert inputs["pixel_values"].abs().max() <= 1.0 + 1e-6     # pixels scaled to [-1, 1]
+    # data-parallel ranks read disjoint shards
+    first = [b[0]["input"] for b in build(0, 2)]
+    second = [b[0]["input"] for b in build(1, 2)]
+    assert len(first) == len(second) == 3 and not any(torch.equal(a, b) for a in first for b in second)
+    # packing: fewer rows, several end-of-text tokens in one row
+    packed = list(build(buffer=4))
+    assert len(packed) < len(batches) and max(int((b[1] == tok.eos_id).sum(1).max()) for b in packed) > 1
+    # resume in the middle of a packing buffer
+    dl_a = build(buffer=4)
+    it = iter(dl_a)
+    next(it)
+    state = dl_a.state_dict()
+    expect = next(it)
+    dl_b = build(buffer=4)
+    dl_b.load_state_dict(state)
+    got = next(iter(dl_b))
+    assert torch.equal(got[0]["input"], expect[0]["input"]) and torch.equal(got[0]["pixel_values"], expect[0]["pixel_values"])
+
+
+def test_vlm_interleaved_documents_and_bad_samples():
+    """OBELICS-style documents (texts / images lists with None at the other modality's positions) through a registered
+    dataset; a document with an undecodable image or over the sequence length is dropped, the rest arrive in order."""
+    from torchtitan_b200.experiments.vlm.mm_datasets import InterleavedDataset, MMDatasetSpec, process_document, register_mm_dataset
+    from torchtitan_b200.experiments.vlm.model import SpecialTokens
+
+    tok = _ByteTokenizer()
+    st = SpecialTokens.from_tokenizer(tok)
+    docs = [
+        {"texts": ["before ", None, " between ", None, " after"], "images": [None, _jpeg(64, 32, 1), None, _jpeg(32, 32, 2), None]},
+        {"texts": ["broken ", None], "images": [None, b"not an image"]},
+        {"texts": ["x" * 500], "images": [None]},
+        {"texts": [None, "caption"], "images": [_jpeg(48, 48, 3), None]},
+        {"texts": ["mismatch"], "images": [None, None]},
+    ]
+    register_mm_dataset("unit-docs", MMDatasetSpec("memory", lambda path: docs, lambda s: (s["texts"], s["images"])))
+    ds = InterleavedDataset("unit-docs", None, tok, st, seq_len=128, patch=16, max_patches=16)
+    rows = list(ds)
+    assert len(rows) == 2 and ds.state_dict()["sample_idx"] == 5
+    ids, pats, grids = rows[0]
+    assert len(ids) == 129 and [p.shape[0] for p in pats] == [8, 4] and pats[0].shape[1] == 3 * 16 * 16
+    text = bytes(t for t in ids if t < 256).decode()
+    assert text == "before  between  after"
+    # order of the pieces: text, image, text, image, text, end of text, padding
+    kinds = "".join("T" if t < 256 else {300: "i", 301: "[", 302: "]", 256: "E", 303: "."}[t] for t in ids)
+    import re
+
+    assert re.fullmatch(r"T+\[i{8}\]T+\[i{4}\]T+E\.+", kinds)
+    assert process_document(["a", None], [None], tok, st, patch=16, max_patches=16) is None
+    with pytest.raises(ValueError, match="not supported"):
+        InterleavedDataset("nope", None, tok, st, seq_len=128, patch=16, max_patches=16)

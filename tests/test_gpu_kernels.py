@@ -530,6 +530,59 @@ def test_mx_linear_op_matches_definition(ops, rows, K, N):
     # and close to the unquantised product (e4m3 keeps 3 mantissa bits)
     assert _rel(y.view(rows, N), xd.float() @ wd.float().t()) < 8e-2
 
+@pytest.mark.parametrize("sizes,K,N", [
+    ([128, 0, 384, 256], 256, 384),          # an empty expert, N % 256 == 128 (the last tile hangs over the next expert)
+    ([256, 128, 128, 0, 0, 512, 128, 128], 768, 2048),   # Qwen3-30B-A3B down projection
+    ([640], 2048, 768),
+])
+def test_mx_grouped_linear_matches_definition(ops, sizes, K, N):
+    """Routed-expert linear in MXFP8 as three grouped launches (forward, input gradient, weight gradient) with the group
+    boundaries on the device, against the PyTorch definition expert by expert (quantise along each GEMM's contraction,
+    dequantise, fp32 matmul). Buffer rows past the last group stay zero."""
+    from torchtitan_b200.ops import native, quant
+
+    if not native.has("tt_grouped_gemm_mxfp8"):
+        pytest.skip("library built without the grouped MXFP8 GEMM")
+    torch.manual_seed(0)
+    G, used = len(sizes), sum(sizes)
+    R = used + 128                                            # the dispatcher's buffer is longer than the rows in use
+    mag = lambda r, c: torch.exp2(torch.randint(-3, 4, (r, c // 32), device="cuda").float()).repeat_interleave(32, 1)
+    x = torch.zeros(R, K, device="cuda")
+    x[:used] = torch.randn(used, K, device="cuda") * mag(used, K)
+    x = x.bfloat16().requires_grad_()
+    w = (torch.randn(G, N, K, device="cuda") * 0.05 * mag(G * N, K).view(G, N, K)).bfloat16().requires_grad_()
+    counts = torch.tensor(sizes, device="cuda", dtype=torch.int64)
+    counts._tt_aligned = 128
+    y = ops.mx_grouped_linear(x, w, counts)
+    assert y is not None and y.shape == (R, N)
+    gy = torch.zeros(R, N, device="cuda")
+    gy[:used] = torch.randn(used, N, device="cuda") * mag(used, N)
+    gy = gy.bfloat16()
+    y.backward(gy)
+    _no_kernel_errors()
+
+    def mm(a, b_t):
+        qa, sa = quant.quantize_mxfp8(a.contiguous())
+        qb, sb = quant.quantize_mxfp8(b_t.contiguous())
+        return quant.dequantize_mxfp8(qa, sa) @ quant.dequantize_mxfp8(qb, sb).t()
+
+    xd, wd = x.detach(), w.detach()
+    y_ref, gx_ref, gw_ref = torch.zeros(R, N, device="cuda"), torch.zeros(R, K, device="cuda"), torch.zeros(G, N, K, device="cuda")
+    s = 0
+    for g, n in enumerate(sizes):
+        if n:
+            y_ref[s:s + n] = mm(xd[s:s + n], wd[g])
+            gx_ref[s:s + n] = mm(gy[s:s + n], wd[g].t())
+            gw_ref[g] = mm(gy[s:s + n].t(), xd[s:s + n].t())
+        s += n
+    assert _rel(y, y_ref) < 1e-2
+    assert _rel(x.grad, gx_ref) < 1e-2
+    assert _rel(w.grad, gw_ref) < 1e-2
+    assert float(y[used:].abs().max()) == 0.0 and float(x.grad[used:].abs().max()) == 0.0
+    for g, n in enumerate(sizes):
+        if n == 0:
+            assert float(w.grad[g].abs().max()) == 0.0
+
 
 @pytest.mark.parametrize("Dqk,Dv,H,Hkv", [(64, 64, 8, 2), (192, 128, 4, 4), (128, 128, 4, 2)])
 @pytest.mark.parametrize("causal", [True, False])

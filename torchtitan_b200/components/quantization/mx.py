@@ -49,7 +49,11 @@ class MXFP8Converter(QuantizationConverter):
             if isinstance(mod, GroupedExperts):
                 mod.quant = self.recipe
                 if self.config.pad_token_groups_for_grouped_mm and hasattr(mod.dispatcher, "alignment"):
-                    mod.dispatcher.alignment = MXFP8_GROUP_ALIGNMENT_SIZE
+                    from torchtitan_b200.models.common.moe.moe import group_alignment
+
+                    # 32 rows for the definition; 128 where the native grouped kernel runs (its scale chunks cover
+                    # 128 rows). Dispatchers installed later by expert parallelism ask group_alignment() again.
+                    mod.dispatcher.alignment = group_alignment(mod, MXFP8_GROUP_ALIGNMENT_SIZE)
                 n += 1
             elif isinstance(mod, nn.Linear) and mod.weight.shape[0] % 32 == 0 and mod.weight.shape[1] % 32 == 0:
                 mod.quant = self.recipe

@@ -36,6 +36,7 @@ constexpr uint32_t SF_STAGE = 3 * SF_CHUNK;      // A, B rows 0..127, B rows 128
 constexpr uint32_t ACC_COLS = 256, SF_COLS_PER_STAGE = 16, TMEM_COLS = 512;
 constexpr int NUM_THREADS = 256;
 constexpr size_t SMEM_BYTES = 1024 + STAGES * (A_STAGE + B_STAGE + SF_STAGE) + 256;
+constexpr size_t SMEM_BYTES_GROUPED = SMEM_BYTES + (1024 + 1) * 4;   // + tiles-before-group table (MAX_GROUPS + 1 ints)
 
 __device__ int g_mx_error = 0;
 
@@ -47,6 +48,83 @@ struct MxArgs {
   long long ldc;
   int c_fp32;
 };
+
+// Grouped (mixture-of-experts) form: rows of the activation operand are grouped by expert, `offs[g]` (device memory) is
+// the end row of group g. Every group starts at a multiple of 128 rows (the dispatcher pads), so a tile's scale chunks
+// are whole chunks of the operand's scale array.
+//   mode 0  Y[r, :] = X[r, :] . W_g^T for rows r of group g. A = X [R, K]. B is either the weights as [G * N, K]
+//           (b_row_stride = N rows per group, b_k_stride = 0) or, for the input gradient, the transposed weights as
+//           [N, G * K] (b_row_stride = 0, b_k_stride = K / 128 steps per group along the contraction).
+//   mode 1  C_g = A[:, rows of g] . B[:, rows of g]^T, the weight gradient: A [M, R] and B [N, R] are the transposed
+//           operands, the contraction runs over the group's rows; C is [G * M, N]. Empty groups get no tile.
+constexpr int MAX_GROUPS = 1024;
+struct MxGroups {
+  int mode, G;
+  const int* offs;
+  int b_row_stride, b_k_stride;
+  int a_kb4, b_kb4;      // K steps per row block in the scale arrays of A and B
+  int b_row_blocks;      // 128-row blocks in B's scale array (the last one is reused for rows beyond it)
+};
+
+struct MxTile {
+  int a_row, b_row, a_k0, b_k0, k_iters;
+  long long c_row;       // first row of the tile in C
+  long long c_row_end;   // rows of C at or beyond this are not written
+  int c_col;
+  bool ok;
+};
+
+__device__ __forceinline__ void mx_build_prefix(const MxArgs& p, const MxGroups& g, int* prefix) {
+  if (threadIdx.x == 0) {
+    int acc = 0, prev = 0;
+    for (int i = 0; i < g.G; ++i) {
+      prefix[i] = acc;
+      const int end = __ldg(g.offs + i);
+      const int rows = end - prev;
+      prev = end;
+      if (g.mode == 0) acc += ((rows + BM - 1) / BM) * p.tiles_n;
+      else acc += rows > 0 ? p.tiles_m * p.tiles_n : 0;
+    }
+    prefix[g.G] = acc;
+  }
+}
+
+template <bool GROUPED>
+__device__ __forceinline__ MxTile mx_tile(const MxArgs& p, const MxGroups& g, const int* prefix, int t) {
+  MxTile tl;
+  if constexpr (!GROUPED) {
+    const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+    tl.a_row = tm * BM; tl.b_row = tn * BN; tl.a_k0 = 0; tl.b_k0 = 0; tl.k_iters = p.k_iters;
+    tl.c_row = tl.a_row; tl.c_row_end = p.M; tl.c_col = tl.b_row; tl.ok = true;
+  } else {
+    int lo = 0, hi = g.G - 1;                  // last group whose prefix is <= t (groups without tiles share a prefix
+    while (lo < hi) {                          // with the next group: the search lands on the last of equal entries)
+      const int mid = (lo + hi + 1) >> 1;
+      if (prefix[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    const int row0 = lo > 0 ? __ldg(g.offs + lo - 1) : 0;
+    const int rows = __ldg(g.offs + lo) - row0;
+    const int r = t - prefix[lo];
+    tl.ok = (row0 % BM) == 0 && (g.mode == 0 || (rows % BK) == 0);
+    if (g.mode == 0) {
+      const int tmg = (rows + BM - 1) / BM;    // m fastest: CTAs running together share one expert's weight panel
+      const int tm = r % tmg, tn = r / tmg;
+      tl.a_row = row0 + tm * BM; tl.a_k0 = 0;
+      tl.b_row = lo * g.b_row_stride + tn * BN; tl.b_k0 = lo * g.b_k_stride;
+      tl.k_iters = p.k_iters;
+      tl.c_row = tl.a_row; tl.c_row_end = min(row0 + rows, p.M); tl.c_col = tn * BN;
+    } else {
+      const int tm = r % p.tiles_m, tn = r / p.tiles_m;
+      tl.a_row = tm * BM; tl.b_row = tn * BN; tl.a_k0 = row0 / BK; tl.b_k0 = row0 / BK;
+      tl.k_iters = rows / BK;
+      tl.c_row = static_cast<long long>(lo) * p.M + tm * BM;
+      tl.c_row_end = static_cast<long long>(lo) * p.M + p.M;
+      tl.c_col = tn * BN;
+    }
+    if (!tl.ok) tl.k_iters = 0;
+  }
+  return tl;
+}
 
 // Shared-memory matrix descriptor without swizzle for the scale-factor chunk: 32 rows of 16 bytes, 8-row core matrices
 // 128 bytes apart.
@@ -78,7 +156,7 @@ __device__ __forceinline__ void umma_mx_ss(uint32_t d_tmem, uint64_t adesc, uint
 }
 
 // Write 32 consecutive accumulator columns of one output row (bf16 or fp32).
-__device__ __forceinline__ void store_acc_chunk(const MxArgs& p, int row, int col, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void store_acc_chunk(const MxArgs& p, long long row, int col, const uint32_t (&r)[32]) {
   const bool full_chunk = col + 32 <= p.N;
   if (p.c_fp32) {
     float* dst = static_cast<float*>(p.C) + row * p.ldc + col;
@@ -108,8 +186,9 @@ __device__ __forceinline__ void store_acc_chunk(const MxArgs& p, int row, int co
   }
 }
 
+template <bool GROUPED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, MxArgs p) {
+gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, MxArgs p, MxGroups grp) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (tt::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - tt::smem_u32(smem_raw));
@@ -123,9 +202,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const uint32_t tfull_bar = bars + 8u * (2 * STAGES), tempty_bar = bars + 8u * (2 * STAGES + 1);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars_gen + 8 * (2 * STAGES + 2));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_gen + 8 * (2 * STAGES + 2) + 8);
+  int* prefix = reinterpret_cast<int*>(bars_gen + 256);     // grouped form only: tiles before each group
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  if constexpr (GROUPED) mx_build_prefix(p, grp, prefix);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -147,6 +227,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   __syncthreads();
   tt::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  int num_tiles = p.tiles_m * p.tiles_n;
+  if constexpr (GROUPED) num_tiles = prefix[grp.G];
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
@@ -154,17 +236,21 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
-        const uint8_t* ga = p.sfa + static_cast<long long>(tm) * p.k_iters * SF_CHUNK;
-        const uint8_t* gb0 = p.sfb + static_cast<long long>(2 * tn) * p.k_iters * SF_CHUNK;
-        const uint8_t* gb1 = p.sfb + static_cast<long long>(2 * tn + 1) * p.k_iters * SF_CHUNK;
-        for (int k = 0; k < p.k_iters; ++k, ++it) {
+        const MxTile tl = mx_tile<GROUPED>(p, grp, prefix, t);
+        if (GROUPED && !tl.ok) atomicExch(&g_mx_error, 16);   // a group that does not start / end on a tile boundary
+        const int a_kb4 = GROUPED ? grp.a_kb4 : p.k_iters, b_kb4 = GROUPED ? grp.b_kb4 : p.k_iters;
+        const int brb0 = tl.b_row / 128;
+        const int brb1 = (GROUPED && brb0 + 1 >= grp.b_row_blocks) ? brb0 : brb0 + 1;
+        const uint8_t* ga = p.sfa + (static_cast<long long>(tl.a_row / 128) * a_kb4 + tl.a_k0) * SF_CHUNK;
+        const uint8_t* gb0 = p.sfb + (static_cast<long long>(brb0) * b_kb4 + tl.b_k0) * SF_CHUNK;
+        const uint8_t* gb1 = p.sfb + (static_cast<long long>(brb1) * b_kb4 + tl.b_k0) * SF_CHUNK;
+        for (int k = 0; k < tl.k_iters; ++k, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!tt::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, &g_mx_error, 1)) { ok = false; break; }
           tt::mbar_expect_tx(full_bar(s), A_STAGE + B_STAGE + SF_STAGE);
-          tt::tma_load_2d(sA + s * A_STAGE, &tma_a, full_bar(s), k * BK, tm * BM);
-          tt::tma_load_2d(sB + s * B_STAGE, &tma_b, full_bar(s), k * BK, tn * BN);
+          tt::tma_load_2d(sA + s * A_STAGE, &tma_a, full_bar(s), (tl.a_k0 + k) * BK, tl.a_row);
+          tt::tma_load_2d(sB + s * B_STAGE, &tma_b, full_bar(s), (tl.b_k0 + k) * BK, tl.b_row);
           const uint32_t sf = sSF + s * SF_STAGE;
           tt::bulk_load(sf, ga + static_cast<long long>(k) * SF_CHUNK, SF_CHUNK, full_bar(s));
           tt::bulk_load(sf + SF_CHUNK, gb0 + static_cast<long long>(k) * SF_CHUNK, SF_CHUNK, full_bar(s));
@@ -179,9 +265,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       bool ok = true;
       const uint32_t sbo = 1024 >> 4;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tile_it) {
+        const int k_iters = GROUPED ? mx_tile<GROUPED>(p, grp, prefix, t).k_iters : p.k_iters;
         if (!tt::mbar_wait(tempty_bar, (tile_it & 1) ^ 1, abort_flag, &g_mx_error, 2)) break;
         tt::tc_fence_after();
-        for (int k = 0; k < p.k_iters; ++k, ++it) {
+        for (int k = 0; k < k_iters; ++k, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!tt::mbar_wait(full_bar(s), ph, abort_flag, &g_mx_error, 3)) { ok = false; break; }
@@ -210,18 +297,18 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const int ew = warp - 4;
     uint32_t tile_it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_it) {
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const MxTile tl = mx_tile<GROUPED>(p, grp, prefix, t);
       if (!tt::mbar_wait(tfull_bar, tile_it & 1, abort_flag, &g_mx_error, 4)) break;
       tt::tc_fence_after();
-      const int row = tm * BM + ew * 32 + lane;
+      const long long row = tl.c_row + ew * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tt::tmem_ld_32x32(taddr + c * 32, r);
         tt::tc_wait_ld();
-        const int col = tn * BN + c * 32;
-        if (row >= p.M || col >= p.N) continue;
+        const int col = tl.c_col + c * 32;
+        if (!tl.ok || row >= tl.c_row_end || col >= p.N) continue;
         store_acc_chunk(p, row, col, r);
       }
       tt::tc_fence_before();
@@ -467,7 +554,8 @@ int tt_gemm_mxfp8(const void* A, const void* B, const void* sfa, const void* sfb
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    cudaFuncSetAttribute(gemm_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    cudaFuncSetAttribute(gemm_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES_GROUPED));
     cudaFuncSetAttribute(pairmx::gemm_mx_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairmx::PSMEM));
     g_attr = true;
   }
@@ -513,7 +601,56 @@ int tt_gemm_mxfp8(const void* A, const void* B, const void* sfa, const void* sfb
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
   int grid = p.tiles_m * p.tiles_n;
   if (grid > g_sms) grid = g_sms;
-  gemm_mx_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  gemm_mx_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p, MxGroups{});
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Grouped MXFP8 GEMM with the group boundaries on the device (see MxGroups). `A` is [a_rows, a_cols] and `B` is
+// [b_rows, b_cols] e4m3, both contiguous along the contraction, with swizzled scale arrays of a_rows / 128 and
+// ceil(b_rows / 128) row blocks; all of a_rows, a_cols, b_cols and the group boundaries are multiples of 128.
+//   mode 0: C [a_rows, N] rows grouped; `M` = a_rows, `K` = contraction per group; B rows of group g start at
+//           g * b_row_stride, its contraction at g * b_k_stride elements.
+//   mode 1: C [G * M, N]; contraction over the rows of group g (columns of A and B); the caller zero-fills C.
+int tt_grouped_gemm_mxfp8(const void* A, const void* B, const void* sfa, const void* sfb, void* C, const int* offs, int mode,
+                          int G, int M, int N, int K, long long a_rows, long long a_cols, long long b_rows, long long b_cols,
+                          int b_row_stride, int b_k_stride, long long ldc, int c_fp32, cudaStream_t stream) {
+  if (G <= 0 || a_rows <= 0 || N <= 0) return 0;
+  if (G > MAX_GROUPS || (mode != 0 && mode != 1)) return -2;
+  if ((a_rows % 128) || (a_cols % 128) || (b_cols % 128) || (b_row_stride % 128) || (b_k_stride % 128) || (K % 128)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(sfa) & 15) || (reinterpret_cast<uintptr_t>(sfb) & 15))
+    return -3;
+  if (!g_attr) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_mx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+    cudaFuncSetAttribute(gemm_mx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES_GROUPED));
+    cudaFuncSetAttribute(pairmx::gemm_mx_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pairmx::PSMEM));
+    g_attr = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = tt::make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_rows, a_cols, a_cols, BM, BK);
+  if (rc) return rc;
+  rc = tt::make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_rows, b_cols, b_cols, BN, BK);
+  if (rc) return rc;
+  MxArgs p;
+  p.M = M; p.N = N; p.K = K;
+  p.k_iters = K / BK;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+  MxGroups g;
+  g.mode = mode; g.G = G; g.offs = offs;
+  g.b_row_stride = b_row_stride; g.b_k_stride = b_k_stride / BK;
+  g.a_kb4 = static_cast<int>(a_cols / BK); g.b_kb4 = static_cast<int>(b_cols / BK);
+  g.b_row_blocks = static_cast<int>((b_rows + 127) / 128);
+  long long bound = mode == 0 ? (a_rows / BM + G) * p.tiles_n : static_cast<long long>(G) * p.tiles_m * p.tiles_n;
+  int grid = bound < g_sms ? static_cast<int>(bound) : g_sms;
+  if (grid < 1) grid = 1;
+  gemm_mx_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES_GROUPED, stream>>>(ta, tb, p, g);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -162,15 +162,17 @@ class MMDataLoader(BaseDataLoader):
     @dataclass(kw_only=True, slots=True)
     class Config(BaseDataLoader.Config):
         dataset: str = "synthetic"
+        dataset_path: str | None = None
+        infinite: bool = True
         patch_size: int = 16
+        spatial_merge_size: int = 1
         max_patches_per_image: int = 64
         max_images_per_batch: int = 32
+        packing_buffer_size: int = 0
         seed: int = 0
 
     def __init__(self, config: Config, *, dp_world_size: int, dp_rank: int, tokenizer=None, seq_len: int, local_batch_size: int,
                  model_vocab_size: int | None = None, **kwargs):
-        if config.dataset != "synthetic":
-            raise ValueError(f"vlm dataset {config.dataset!r} is not available offline; supported: ['synthetic']")
         self.config, self.batch_size = config, local_batch_size
         try:
             st = SpecialTokens.from_tokenizer(tokenizer)
@@ -178,25 +180,49 @@ class MMDataLoader(BaseDataLoader):
             v = model_vocab_size or 2048
             st = SpecialTokens("<|image|>", v - 4, "<|begin_of_image|>", v - 3, "<|end_of_image|>", v - 2, "<|pad|>", v - 1)
         self.special_tokens = st
-        vocab = min(i for i in (st.img_id, st.boi_id, st.eoi_id, st.pad_id))
-        self.dataset = SyntheticMultiModalDataset(st, vocab=vocab, seq_len=seq_len, patch=config.patch_size,
-                                                  max_patches=config.max_patches_per_image, seed=config.seed, dp_rank=dp_rank,
-                                                  dp_world_size=dp_world_size)
+        self.synthetic = config.dataset == "synthetic"
+        if self.synthetic:
+            vocab = min(i for i in (st.img_id, st.boi_id, st.eoi_id, st.pad_id))
+            self.dataset = SyntheticMultiModalDataset(st, vocab=vocab, seq_len=seq_len, patch=config.patch_size,
+                                                      max_patches=config.max_patches_per_image, seed=config.seed,
+                                                      dp_rank=dp_rank, dp_world_size=dp_world_size)
+        else:
+            from .mm_datasets import InterleavedDataset
+
+            assert tokenizer is not None, "image-text datasets need a tokenizer"
+            if config.spatial_merge_size != 1:
+                raise NotImplementedError("spatial_merge_size > 1: the projector of this model does not merge patches")
+            self.dataset = InterleavedDataset(config.dataset, config.dataset_path, tokenizer, st, seq_len=seq_len,
+                                              patch=config.patch_size, max_patches=config.max_patches_per_image,
+                                              merge=config.spatial_merge_size, packing_buffer_size=config.packing_buffer_size,
+                                              dp_rank=dp_rank, dp_world_size=dp_world_size, infinite=config.infinite)
         self.collate = MultiModalCollatorNLD(patch_dim=3 * config.patch_size ** 2, max_images_per_batch=config.max_images_per_batch,
                                              max_patches_per_image=config.max_patches_per_image, special_tokens=st)
         self._batches = 0
 
     def __iter__(self):
         it = iter(self.dataset)
-        for _ in range(self._batches * self.batch_size):          # resume: the stream is a pure function of (seed, rank)
-            next(it)
+        if self.synthetic:
+            for _ in range(self._batches * self.batch_size):      # resume: the stream is a pure function of (seed, rank)
+                next(it)
         while True:
-            batch = [next(it) for _ in range(self.batch_size)]
+            batch = []
+            for row in it:
+                batch.append(row)
+                if len(batch) == self.batch_size:
+                    break
+            if len(batch) < self.batch_size:                      # a finite dataset ran out: the last short batch is dropped
+                return
             self._batches += 1
             yield self.collate(batch)
 
     def state_dict(self):
-        return {"batches": self._batches}
+        state = {"batches": self._batches}
+        if not self.synthetic:
+            state["dataset"] = self.dataset.state_dict()
+        return state
 
     def load_state_dict(self, state_dict):
         self._batches = int(state_dict.get("batches", 0)) if state_dict else 0
+        if state_dict and not self.synthetic and "dataset" in state_dict:
+            self.dataset.load_state_dict(state_dict["dataset"])

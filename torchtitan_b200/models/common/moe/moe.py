@@ -41,6 +41,22 @@ def _moe_ops():
 
 
 GROUP_ALIGN_NATIVE = 64  # contraction tile of the grouped weight-gradient kernel
+GROUP_ALIGN_MX_NATIVE = 128  # row block of the block-scaled grouped GEMM's scale layout (and its contraction tile)
+
+
+def group_alignment(experts, base: int) -> int:
+    """Rows every expert's block is padded to: ``base`` from the dispatcher's own needs, raised to what the experts'
+    quantised grouped GEMM wants (MXFP8 on the native kernel: 128; otherwise the recipe's block along the tokens)."""
+    quant = getattr(experts, "quant", None)
+    if quant is None:
+        return base
+    if quant.kind == "mxfp8":
+        from torchtitan_b200.ops import native
+
+        need = GROUP_ALIGN_MX_NATIVE if (torch.cuda.is_available() and not quant.emulate and native.has("tt_grouped_gemm_mxfp8")) else 32
+    else:
+        need = 16
+    return max(base, need) if max(base, need) % min(base, need) == 0 else base * need
 
 
 class LocalDispatcher:

@@ -112,3 +112,16 @@ def qwen3_30b_a3b() -> Trainer.Config:
         activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op"),
     )
     return _synthetic(cfg)
+
+
+def qwen3_30b_a3b_mxfp8() -> Trainer.Config:
+    """The same job with the routed experts' three grouped GEMMs in MXFP8 (forward, input gradient and weight gradient,
+    each one grouped launch with the group boundaries on the device); attention, router and output stay bf16.
+    Parity: torchtitan/components/quantization/mx.py:91-134 (``MXFP8Converter`` on ``fqns = ["experts"]``)."""
+    from torchtitan_b200.components.quantization.mx import MXFP8Converter
+    from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
+
+    cfg = qwen3_30b_a3b()
+    cfg.model_converters = ModelConvertersContainer.Config(converters=[MXFP8Converter.Config(fqns=["experts"])])
+    return cfg
+

@@ -1034,6 +1034,62 @@ def mx_linear(x: Tensor, weight: Tensor) -> Tensor | None:
     return _MxLinearFn.apply(x, weight)
 
 
+def _mx_grouped_launch(A, sa, B, sb, out, offs, mode: int, G: int, M: int, N: int, K: int, b_row_stride: int, b_k_stride: int):
+    _ck(_lib().tt_grouped_gemm_mxfp8(A.data_ptr(), B.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), offs.data_ptr(),
+                                     mode, G, M, N, K, A.shape[0], A.shape[1], B.shape[0], B.shape[1], b_row_stride, b_k_stride,
+                                     out.stride(-2), int(out.dtype == torch.float32), _stream()), "tt_grouped_gemm_mxfp8")
+
+
+class _MxGroupedFn(torch.autograd.Function):
+    """Routed-expert linear ``y[r] = x[r] @ w[g(r)]^T`` in MXFP8, one launch per GEMM over all experts with the group
+    boundaries read on the device (``csrc/gemm_mx.cu``, grouped form). Operands are quantised along the contraction of
+    each of the three GEMMs: forward ``x`` and ``w`` along K; input gradient ``dy`` along N and ``w`` down its rows
+    (one transposing pass over the weights viewed as [G * N, K]); weight gradient ``dy`` and ``x`` down their rows, so
+    the 32-element blocks run along the tokens of one expert (groups start at multiples of 128 rows)."""
+
+    @staticmethod
+    def forward(ctx, x, w, offs):
+        G, N, K = w.shape
+        R = x.shape[0]
+        (xq, xs), (wq, ws) = _mx_operand(x, False), _mx_operand(w.view(G * N, K), False)
+        y = x.new_zeros(R, N)
+        _mx_grouped_launch(xq, xs, wq, ws, y, offs, 0, G, R, N, K, N, 0)
+        ctx.save_for_backward(x, w, offs)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, w, offs = ctx.saved_tensors
+        G, N, K = w.shape
+        R = x.shape[0]
+        gy = gy.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            (gq, gs), (wtq, wts) = _mx_operand(gy, False), _mx_operand(w.view(G * N, K), True)      # w^T: [K, G * N]
+            gx = torch.zeros_like(x)
+            _mx_grouped_launch(gq, gs, wtq, wts, gx, offs, 0, G, R, K, N, 0, N)
+        if ctx.needs_input_grad[1]:
+            (gtq, gts), (xtq, xts) = _mx_operand(gy, True), _mx_operand(x, True)                   # [N, R], [K, R]
+            gw = torch.zeros_like(w)
+            _mx_grouped_launch(gtq, gts, xtq, xts, gw, offs, 1, G, N, K, 128, 0, 0)
+        return gx, gw, None
+
+
+def mx_grouped_linear(x: Tensor, w: Tensor, counts: Tensor) -> Tensor | None:
+    """The native grouped MXFP8 linear, or None when alignment / shapes / library do not allow it: bf16 operands, every
+    group a multiple of 128 rows (``counts`` carries the dispatcher's alignment), N and K multiples of 128."""
+    if not (x.is_cuda and native.has("tt_grouped_gemm_mxfp8") and native.has("tt_mxfp8_quant_cols_swz")):
+        return None
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 3 or x.dim() != 2:
+        return None
+    aligned = getattr(counts, "_tt_aligned", 0)
+    G, N, K = w.shape
+    if not aligned or aligned % 128 or N % 128 or K % 128 or x.shape[0] % 128 or G > 1024 or x.shape[1] != K:
+        return None
+    offs = torch.cumsum(counts, 0).to(torch.int32)
+    return _MxGroupedFn.apply(x.contiguous(), w.contiguous(), offs)
+
+
 def gemm_mxfp8(qa: Tensor, qb: Tensor, sa: Tensor, sb: Tensor, out_dtype=torch.bfloat16) -> Tensor:
     """``qa [M,K] @ qb [N,K]^T`` for MXFP8 operands (e4m3 data, E8M0 scales [rows, K/32]) on the block-scaled tensor-core
     path: the scales are re-laid into the MMA's 512-byte chunks and applied by the MMA itself."""

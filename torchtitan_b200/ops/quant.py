@@ -173,7 +173,16 @@ def quant_linear(x: torch.Tensor, w: torch.Tensor, bias, recipe: QuantRecipe):
 
 def quant_grouped_linear(x: torch.Tensor, w: torch.Tensor, counts: torch.Tensor, recipe: QuantRecipe):
     """Per-expert ``x_e @ w[e]^T`` over row groups of sizes ``counts`` with quantised GEMMs; rows past
-    ``sum(counts)`` (alignment padding at the end) produce zeros."""
+    ``sum(counts)`` (alignment padding at the end) produce zeros. MXFP8 on CUDA with groups aligned to 128 rows runs as
+    one grouped launch per GEMM with the boundaries on the device; other cases go expert by expert (one host read of
+    the counts)."""
+    w = w.to_local() if hasattr(w, "to_local") else w
+    if recipe.kind == "mxfp8" and x.is_cuda and not recipe.emulate:
+        from .cuda_ops import mx_grouped_linear
+
+        y = mx_grouped_linear(x, w, counts)
+        if y is not None:
+            return y
     sizes = counts.tolist()
     outs, start = [], 0
     for e, n in enumerate(sizes):

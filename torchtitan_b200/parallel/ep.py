@@ -76,6 +76,7 @@ class AllToAllDispatcher:
         recv = all_to_all_rows(rows, out_splits, in_splits, self.group)
         n_recv = recv.shape[0]
         max_len = n_recv + self.local_experts * self.alignment
+        max_len = -(-max_len // self.alignment) * self.alignment      # the quantised grouped GEMM wants whole row blocks
         perm, m_sizes, _ = generate_permute_indices(
             recv_counts.to(torch.int32), self.local_experts, self.ep, max_len, self.alignment, use_cpu=not recv.is_cuda)
         perm = perm.to(recv.device).long()
@@ -212,7 +213,7 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
     etp_mesh = parallel_dims.get_optional_mesh("etp") if parallel_dims.etp_enabled else None
     if parallel_dims.etp_enabled and tp_mesh is None:
         raise ValueError("expert tensor parallel needs tensor parallel (etp must equal tp)")
-    from torchtitan_b200.models.common.moe.moe import GROUP_ALIGN_NATIVE
+    from torchtitan_b200.models.common.moe.moe import GROUP_ALIGN_NATIVE, group_alignment
     from torchtitan_b200.ops import native
 
     # 64-row groups let the device-side grouped GEMM (incl. its weight-gradient form) run without host-side sizes
@@ -247,10 +248,12 @@ def apply_moe_ep_tp(model: nn.Module, parallel_dims, parallelism) -> nn.Module:
             if nvlink_ep:
                 from .nvlink_ep import NvlinkDispatcher
 
-                moe.experts.dispatcher = NvlinkDispatcher(ep_mesh, moe.router.num_experts, alignment=GROUP_ALIGN_NATIVE,
+                moe.experts.dispatcher = NvlinkDispatcher(ep_mesh, moe.router.num_experts,
+                                                          alignment=group_alignment(moe.experts, GROUP_ALIGN_NATIVE),
                                                           capacity_factor=cf)
             else:
-                moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, moe.router.num_experts, alignment=alignment,
+                moe.experts.dispatcher = AllToAllDispatcher(ep_mesh, moe.router.num_experts,
+                                                            alignment=group_alignment(moe.experts, alignment),
                                                             capacity_factor=cf)
         if etp_mesh is not None:
             if moe.aux_loss_coeff > 0.0:

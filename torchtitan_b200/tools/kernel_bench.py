@@ -186,8 +186,27 @@ def bench_grouped_gemm(args, timer):
 
     ms_fb = timer.time(fb, args.iters)
     fl = 2.0 * rows * N * K
-    return {"case": "grouped_gemm", "experts": E, "rows": rows, "N": N, "K": K, "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9,
-            "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3 * fl / ms_fb / 1e9}
+    out = {"case": "grouped_gemm", "experts": E, "rows": rows, "N": N, "K": K, "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9,
+           "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3 * fl / ms_fb / 1e9}
+    # the same layer in MXFP8 (groups padded to 128 rows; times include quantising both operands of every GEMM)
+    sizes128 = (raw / raw.sum() * (R - 128 * E)).long() // 128 * 128 + 128
+    c128 = sizes128.clone()
+    c128._tt_aligned = 128
+    rows128 = int(sizes128.sum())
+    x8 = (torch.randn(rows128, K, device="cuda") * 0.5).bfloat16().requires_grad_()
+    if cuda_ops.mx_grouped_linear(x8, w, c128) is not None:
+        gy8 = torch.randn(rows128, N, device="cuda").bfloat16()
+        ms8_f = timer.time(lambda: cuda_ops.mx_grouped_linear(x8, w, c128), args.iters)
+
+        def fb8():
+            x8.grad = w.grad = None
+            cuda_ops.mx_grouped_linear(x8, w, c128).backward(gy8)
+
+        ms8_fb = timer.time(fb8, args.iters)
+        fl8 = 2.0 * rows128 * N * K
+        out.update(mxfp8_rows=rows128, mxfp8_fwd_ms=ms8_f, mxfp8_fwd_tflops=fl8 / ms8_f / 1e9, mxfp8_fwd_bwd_ms=ms8_fb,
+                   mxfp8_fwd_bwd_tflops=3 * fl8 / ms8_fb / 1e9)
+    return out
 
 
 def bench_paged_decode(args, timer):
