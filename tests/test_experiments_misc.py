@@ -395,3 +395,77 @@ def test_vlm_interleaved_documents_and_bad_samples():
     assert process_document(["a", None], [None], tok, st, patch=16, max_patches=16) is None
     with pytest.raises(ValueError, match="not supported"):
         InterleavedDataset("nope", None, tok, st, seq_len=128, patch=16, max_patches=16)
+
+
+def test_transformers_backend_pipeline_stages_chain_to_the_whole_model():
+    """Stages built from a wrapped Hugging Face decoder run its parts without the top-level forward; chained, they give
+    the whole model's logits, and their parameters keep the whole model's names."""
+    from torchtitan_b200.experiments.transformers_modeling_backend import model_registry
+    from torchtitan_b200.parallel.pp import generate_llm_fqn_per_model_part
+
+    spec = model_registry("debugmodel")
+    torch.manual_seed(0)
+    model = spec.model.build()
+    model.init_weights()
+    parts = generate_llm_fqn_per_model_part(3, 4, 1, 1)
+    stages = [model.build_pipeline_stage(f) for f in parts]
+    names = set()
+    for st in stages:
+        names |= {n for n, _ in st.named_parameters()}
+    assert names == {n for n, _ in model.named_parameters()}
+    assert stages[0].tok_embeddings is not None and stages[1].tok_embeddings is None and stages[2].output is not None
+    x = torch.randint(0, 2048, (2, 24))
+    h = x
+    for st in stages:
+        h = st(h)
+    assert torch.allclose(h, model(x), atol=1e-5, rtol=1e-5)
+    # a stage initialises its own modules with the architecture's initialiser
+    before = stages[1].model.model.layers["1"].mlp.up_proj.weight.clone()
+    stages[1].init_weights()
+    assert not torch.equal(before, stages[1].model.model.layers["1"].mlp.up_proj.weight)
+
+
+def _hf_pp_worker(rank, world):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.config import ActivationCheckpointConfig, CompileConfig, ParallelismConfig, TrainingConfig
+    from torchtitan_b200.experiments.transformers_modeling_backend import model_registry
+    from torchtitan_b200.parallel import ParallelDims
+    from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
+
+    spec = model_registry("debugmodel")
+    pd = ParallelDims(dp_replicate=1, dp_shard=1, cp=1, tp=1, pp=world, ep=1, etp=1, world_size=world)
+    torch.manual_seed(5)
+    ref = spec.model.build()
+    ref.init_weights()
+    B, S = 4, 16
+    x = torch.randint(0, 2048, (B, S + 1))
+    inp, lab = x[:, :-1], x[:, 1:]
+    sched, parts, first, last = spec.pipelining_fn(
+        ref, parallel_dims=pd, training=TrainingConfig(local_batch_size=B, seq_len=S),
+        model_converters=ModelConvertersContainer.Config(),
+        parallelism=ParallelismConfig(pipeline_parallel_degree=world, pipeline_parallel_schedule="Interleaved1F1B",
+                                      pipeline_parallel_microbatch_size=1),
+        compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="full"), dump_folder="/tmp",
+        device=torch.device("cpu"), model_config=spec.model, parallelize_fn=spec.parallelize_fn, loss_fn=cross_entropy_loss)
+    losses = [] if last else None
+    scale = torch.tensor(1.0 / lab.numel())
+    args = (inp,) if first else ()
+    sched.step(*args, target=lab if last else None, losses=losses, loss_scale=scale)
+    ref_loss = cross_entropy_loss(ref(inp), lab) / lab.numel()
+    ref_loss.backward()
+    want = {n: p.grad for n, p in ref.named_parameters()}
+    err = max((p.grad - want[n]).abs().max().item() for part in parts for n, p in part.named_parameters())
+    return {"ref": ref_loss.item(), "loss": float(torch.stack(losses).sum()) if last else None, "grad_err": err,
+            "stages": len(parts)}
+
+
+def test_transformers_backend_pipeline_parallel_matches_single_process(tmp_path):
+    from dist_utils import run_ranks
+
+    res = run_ranks(_hf_pp_worker, 2, tmp_path=tmp_path)
+    got = [o for o in res if o["loss"] is not None]
+    assert got and all(abs(o["loss"] - o["ref"]) < 1e-5 for o in got), res
+    assert all(o["stages"] == 2 for o in res) and max(o["grad_err"] for o in res) < 1e-5, res

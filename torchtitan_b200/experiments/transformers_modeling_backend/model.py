@@ -48,10 +48,12 @@ class HFTransformerModel(BaseModel):
             if os.path.exists(cand):
                 self.hf_config_path = cand
             par = trainer_config.parallelism
-            for name, deg in (("context", par.context_parallel_degree), ("pipeline", par.pipeline_parallel_degree)):
-                if deg > 1:
-                    raise NotImplementedError(f"{name} parallel is not available for wrapped Hugging Face models; "
-                                              "use FSDP / HSDP and tensor parallel")
+            if par.context_parallel_degree > 1:
+                raise NotImplementedError("context parallel is not available for wrapped Hugging Face models; "
+                                          "use FSDP / HSDP, tensor parallel and pipeline parallel")
+            if par.pipeline_parallel_degree > 1 and self.hf_config().tie_word_embeddings:
+                raise NotImplementedError("pipeline parallel cannot split a model whose output layer shares the embedding "
+                                          "weights (tie_word_embeddings)")
 
         def hf_config(self):
             from transformers import AutoConfig, CONFIG_MAPPING
@@ -119,15 +121,95 @@ class HFTransformerModel(BaseModel):
             kw["position_ids"] = positions.long()
         return self.model(input_ids=tokens, use_cache=False, **kw).logits
 
+    def build_pipeline_stage(self, fqns: list[str]) -> "HFPipelineStage":
+        """A pipeline stage holding the named parts (``tok_embeddings``, ``layers.<i>``, ``norm``, ``output``)."""
+        return HFPipelineStage(self, fqns)
+
     def init_weights(self, *args, **kwargs):
-        # buffers such as rotary inverse frequencies are rebuilt by the architecture's own modules
-        for m in self.model.modules():
-            if hasattr(m, "inv_freq") and hasattr(m, "rope_init_fn"):
-                inv, _ = m.rope_init_fn(m.config, m.inv_freq.device)
-                m.inv_freq = inv.to(m.inv_freq.device) if m.inv_freq.device.type != "meta" else inv
-                if hasattr(m, "original_inv_freq"):
-                    m.original_inv_freq = m.inv_freq
-        self.model.apply(self.model._init_weights)
+        _init_hf_weights(self.model)
+
+    def get_attention_masks(self, input_batch, tokenizer, extra_inputs=None):
+        raise TypeError("wrapped Hugging Face models use their own causal masking")
+
+
+def _init_hf_weights(root: nn.Module, init_fn=None) -> None:
+    # buffers such as rotary inverse frequencies are rebuilt by the architecture's own modules
+    for m in root.modules():
+        if hasattr(m, "inv_freq") and hasattr(m, "rope_init_fn"):
+            inv, _ = m.rope_init_fn(m.config, m.inv_freq.device)
+            m.inv_freq = inv.to(m.inv_freq.device) if m.inv_freq.device.type != "meta" else inv
+            if hasattr(m, "original_inv_freq"):
+                m.original_inv_freq = m.inv_freq
+    root.apply(init_fn or root._init_weights)
+
+
+class _Shell(nn.Module):
+    """Container that only gives its children the attribute path they have in the Hugging Face model."""
+
+
+class HFPipelineStage(nn.Module):
+    """Some consecutive parts of a wrapped decoder, run without the Hugging Face top-level ``forward``: embedding (first
+    stage), a run of decoder layers with the rotary tables computed by the architecture's own ``rotary_emb``, final norm
+    and output head (last stage). Parameters keep the names they have in the whole model
+    (``model.model.layers.<i>...``, ``model.lm_head.weight``), so checkpoints do not depend on the pipeline layout.
+    Layers are called without an explicit mask: the SDPA attention of the decoder then runs causal, which is what the
+    whole model's forward does for full-length sequences; architectures that mix sliding-window layers need their own
+    masks and are not covered. Counterpart of torchtitan/experiments/transformers_modeling_backend/pipeline.py:1-415."""
+
+    def __init__(self, whole: "HFTransformerModel", fqns: list[str]):
+        super().__init__()
+        import copy
+
+        keep = set(fqns)
+        self.config, self.hf_config = whole.config, whole.hf_config
+        if getattr(self.hf_config, "sliding_window", None) and getattr(self.hf_config, "layer_types", None) and \
+                any(t != "full_attention" for t in self.hf_config.layer_types):
+            raise NotImplementedError("pipeline stages call decoder layers with plain causal attention; this architecture "
+                                      "mixes sliding-window layers")
+        src = whole._decoder
+        dec = _Shell()
+        dec.embed_tokens = copy.deepcopy(src.embed_tokens) if "tok_embeddings" in keep else None
+        dec.layers = nn.ModuleDict({str(i): copy.deepcopy(m) for i, m in enumerate(src.layers) if f"layers.{i}" in keep})
+        dec.norm = copy.deepcopy(src.norm) if "norm" in keep else None
+        dec.rotary_emb = copy.deepcopy(src.rotary_emb)
+        top = _Shell()
+        top.model = dec
+        top.lm_head = copy.deepcopy(whole.model.lm_head) if "output" in keep else None
+        self.model = top
+        self._init_fn = whole.model._init_weights
+
+    @property
+    def tok_embeddings(self):
+        return self.model.model.embed_tokens
+
+    @property
+    def layers(self) -> dict[str, nn.Module]:
+        return dict(self.model.model.layers.items())
+
+    @property
+    def norm(self):
+        return self.model.model.norm
+
+    @property
+    def output(self):
+        return self.model.lm_head
+
+    def forward(self, x, attention_masks=None, positions=None):
+        dec = self.model.model
+        h = dec.embed_tokens(x) if dec.embed_tokens is not None else x
+        pos = positions.long() if positions is not None else torch.arange(h.shape[1], device=h.device).unsqueeze(0)
+        rope = dec.rotary_emb(h, pos)
+        for layer in dec.layers.values():
+            out = layer(h, attention_mask=None, position_ids=pos, position_embeddings=rope, use_cache=False)
+            h = out[0] if isinstance(out, tuple) else out
+        if dec.norm is not None:
+            h = dec.norm(h)
+        if self.model.lm_head is not None:
+            h = self.model.lm_head(h)
+        return h
+
+    def init_weights(self, *args, **kwargs):
+        _init_hf_weights(self.model, self._init_fn)      # the architecture's initialiser, on this stage's modules
 
     def get_attention_masks(self, input_batch, tokenizer, extra_inputs=None):
         raise TypeError("wrapped Hugging Face models use their own causal masking")

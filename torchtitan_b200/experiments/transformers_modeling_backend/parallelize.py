@@ -1,7 +1,8 @@
 """Activation checkpointing + FSDP/HSDP for wrapped Hugging Face decoders (one unit per decoder layer, one for
 [norm, lm_head], one for the rest). Parity: torchtitan/experiments/transformers_modeling_backend/parallelize.py:41-400,
-plus tensor parallel for the usual decoder layout (``self_attn.{q,k,v,o}_proj``, ``mlp.{gate,up,down}_proj``); context and
-pipeline plans are rejected in the model configuration."""
+plus tensor parallel for the usual decoder layout (``self_attn.{q,k,v,o}_proj``, ``mlp.{gate,up,down}_proj``). Works on
+the whole wrapper and on a pipeline stage alike (both expose ``layers`` / ``norm`` / ``output``); context parallel is
+rejected in the model configuration."""
 
 from __future__ import annotations
 

@@ -85,6 +85,8 @@ def generate_llm_fqn_per_model_part(num_stages: int, num_layers: int, input_weig
 
 
 def _build_stage(whole: nn.Module, fqns: list[str]) -> nn.Module:
+    if hasattr(whole, "build_pipeline_stage"):       # models whose parts are not direct children build their own stage
+        return whole.build_pipeline_stage(fqns)
     model = copy.deepcopy(whole)
     keep = set(fqns)
     for name, child in list(model.named_children()):
