@@ -72,6 +72,10 @@ def _sharded_worker(rank, world, mode, steps, mixed):
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16 if mixed else None, reduce_dtype=torch.float32)
     wrap = replicate if mode == "ddp" else fully_shard
     kw = {} if mode == "ddp" else {"reshard_after_forward": mode != "fsdp_noreshard"}
+    if mode == "fsdp_offload":
+        # shards "offloaded" with the CPU as compute device too: the same code path (separate master / gradient buffers,
+        # compute copy refreshed from the master before every gather, gradients stored across the two), no device needed
+        kw["compute_device"] = torch.device("cpu")
     for b in net.layers.values():
         wrap(b, mesh=mesh, mp_policy=mp, **kw)
     wrap(net, mesh=mesh, mp_policy=mp, **kw)
@@ -99,10 +103,13 @@ def _sharded_worker(rank, world, mode, steps, mixed):
     for name, p in net.named_parameters():
         full[name] = p.full_tensor().detach().clone() if hasattr(p, "full_tensor") else p.detach().clone()
     shard_numel = sum((p._local_tensor if hasattr(p, "_local_tensor") else p).numel() for p in net.parameters())
+    if mode == "fsdp_offload":
+        assert all(u.offloaded and u.shadow_flat is not None and not any(u._slots) for u in fsdp_units(net))
     return {"losses": losses, "full": full, "shard_numel": shard_numel, "units": len(fsdp_units(net))}
 
 
-@pytest.mark.parametrize("mode,world", [("fsdp", 2), ("fsdp_noreshard", 2), ("hsdp", 4), ("ddp", 2), ("fsdp", 3)])
+@pytest.mark.parametrize("mode,world", [("fsdp", 2), ("fsdp_noreshard", 2), ("hsdp", 4), ("ddp", 2), ("fsdp", 3),
+                                        ("fsdp_offload", 2)])
 def test_sharded_training_matches_single_process(tmp_path, mode, world):
     steps = 4
     ref_losses, ref_state = _reference_run(steps, world)

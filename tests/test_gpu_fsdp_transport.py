@@ -2,7 +2,9 @@
 optimizer steps of two micro-batches each (gradient accumulation exercises the staging buffer's "read done" handshake).
 The gradient shards of the first step (identical parameters on both sides) must agree to rounding; the losses of all
 steps must agree loosely (Adam turns rounding-level gradient differences into different steps for near-zero
-gradients, so later steps drift apart a little). Skipped with fewer than two GPUs."""
+gradients, so later steps drift apart a little). A third run keeps the shards, their gradients and the optimizer state
+in host memory (CPU offload): weights start from the same CPU initialisation, so its first-step gradients and its losses
+are held to the same bounds. Skipped with fewer than two GPUs."""
 
 import dataclasses
 
@@ -16,7 +18,7 @@ pytestmark = pytest.mark.gpu
 STEPS, MICRO, BATCH, SEQ = 5, 2, 2, 256
 
 
-def _train(rank, world, fused: bool):
+def _train(rank, world, fused: bool, offload: bool = False):
     import torch.distributed as dist
 
     from torchtitan_b200.components.loss import cross_entropy_loss
@@ -33,11 +35,13 @@ def _train(rank, world, fused: bool):
     cfg = dataclasses.replace(llama3_configs["debugmodel"])
     cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=SEQ)
     torch.manual_seed(1234)
-    with torch.device("cuda"):
+    with torch.device("cpu"):                         # CPU initialisation: the same weights with and without offload
         model = cfg.build()
-    model.init_weights()
+    model.init_weights(buffer_device=torch.device("cuda"))
+    if not offload:
+        model.cuda()
     apply_fsdp(model, pd.get_mesh("fsdp"), param_dtype=torch.bfloat16, reduce_dtype=torch.float32, pp_enabled=False,
-               parallelism=_Par())
+               parallelism=_Par(), cpu_offload=offload)
     fsdp.materialize(model)
     units = fsdp.fsdp_units(model)
     transport = type(units[0].comm).__name__
@@ -53,6 +57,8 @@ def _train(rank, world, fused: bool):
             loss.backward()
             total += loss.detach()
         if step == 0:
+            for u in units:
+                u.wait_for_reduce()
             torch.cuda.synchronize()
             grads = [u.grad_shard_flat.detach().clone() for u in units if u.params]
         opt.step()
@@ -61,7 +67,8 @@ def _train(rank, world, fused: bool):
     torch.cuda.synchronize()
     errs = native.kernel_errors()
     comm_err = units[0].comm.errors() if hasattr(units[0].comm, "errors") else None
-    return {"losses": losses, "grads": [t.cpu() for t in grads], "transport": transport, "errs": errs, "comm_err": comm_err}
+    return {"losses": losses, "grads": [t if offload else t.cpu() for t in grads], "transport": transport, "errs": errs,
+            "comm_err": comm_err}
 
 
 def _worker(rank, world):
@@ -71,14 +78,15 @@ def _worker(rank, world):
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     a = _train(rank, world, fused=True)
     b = _train(rank, world, fused=False)
-    return a, b
+    c = _train(rank, world, fused=False, offload=True)
+    return a, b, c
 
 
 def test_nvlink_transport_matches_c10d_with_gradient_accumulation(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     out = run_ranks(_worker, 2, tmp_path=tmp_path, timeout=900)
-    for nv, c10 in out:
+    for nv, c10, off in out:
         assert nv["transport"] == "NvlinkComm" and c10["transport"] == "C10dComm"
         assert not nv["errs"] and nv["comm_err"] is None
         # bf16 gradients cross the wire in both (NCCL reduces them in fp32 after a cast): same sums up to ordering
@@ -89,3 +97,12 @@ def test_nvlink_transport_matches_c10d_with_gradient_accumulation(tmp_path):
             scale = gb.abs().max().item() + 1e-12
             assert (ga - gb).abs().max().item() <= 5e-3 * scale, ((ga - gb).abs().max().item(), scale)
         assert nv["losses"][-1] < nv["losses"][0]
+        # CPU offload: same collectives as the c10d run, gradients land in host memory, torch's AdamW steps on the CPU
+        assert off["transport"] == "C10dComm" and not off["errs"]
+        assert abs(off["losses"][0] - c10["losses"][0]) <= 1e-5 * abs(c10["losses"][0])
+        for a, b in zip(off["losses"], c10["losses"]):
+            assert abs(a - b) <= 5e-3 * abs(b), (off["losses"], c10["losses"])
+        for ga, gb in zip(off["grads"], c10["grads"]):
+            assert not ga.is_cuda
+            scale = gb.abs().max().item() + 1e-12
+            assert (ga - gb).abs().max().item() <= 1e-5 * scale

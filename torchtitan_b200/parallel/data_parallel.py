@@ -37,12 +37,17 @@ def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype
                cpu_offload: bool = False, reshard_after_forward_policy: str = "default", parallelism=None,
                extra_groups: dict | None = None, efsdp_mesh=None):
     mp = MixedPrecisionPolicy(param_dtype=param_dtype, reduce_dtype=reduce_dtype)
-    if cpu_offload:
-        raise NotImplementedError("training.enable_cpu_offload is not supported by this FSDP runtime")
     reshard = get_fsdp_reshard_after_forward_policy(
         reshard_after_forward_policy, pp_enabled, param_bytes=_compute_copy_bytes(model, param_dtype)
     )
-    comm = make_comm(dp_mesh, parallelism, model=model, param_dtype=param_dtype)
+    compute_device = None
+    if cpu_offload:
+        # sharded parameters, gradients and optimizer state stay in (pinned) host memory; every gather starts with a
+        # host-to-device copy of the shard, every reduce-scatter ends with a device-to-host copy, the optimizer runs on
+        # the CPU (torchtitan/models/llama3/parallelize.py:334, ``CPUOffloadPolicy``). Collectives go through c10d.
+        compute_device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        logger.info(f"FSDP CPU offload: shards in host memory, compute on {compute_device}")
+    comm = None if cpu_offload else make_comm(dp_mesh, parallelism, model=model, param_dtype=param_dtype)
     if comm is None and getattr(parallelism, "fsdp_extra_process_group", False) and dp_mesh is not None:
         import torch.distributed as dist
 
@@ -60,7 +65,7 @@ def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype
                 own = g
         comm = C10dComm(gather_group=own)
         logger.info("FSDP all-gathers use a process group of their own")
-    kw = dict(mesh=dp_mesh, mp_policy=mp, comm=comm)
+    kw = dict(mesh=dp_mesh, mp_policy=mp, comm=comm, compute_device=compute_device)
     if getattr(model, "tok_embeddings", None) is not None:
         fully_shard(model.tok_embeddings, **kw, reshard_after_forward=reshard)
     bucket_bytes = int(getattr(parallelism, "fsdp_bucket_bytes", 0) or 0)
@@ -76,7 +81,8 @@ def apply_fsdp(model: nn.Module, dp_mesh, param_dtype: torch.dtype, reduce_dtype
     for block in model.layers.values():
         if efsdp_mesh is not None and getattr(block, "moe_enabled", False):
             # MoE-aware FSDP: expert-parallel weights are only replicated over the efsdp ranks
-            fully_shard(block.moe.experts, mesh=efsdp_mesh, mp_policy=mp, reshard_after_forward=reshard)
+            fully_shard(block.moe.experts, mesh=efsdp_mesh, mp_policy=mp, reshard_after_forward=reshard,
+                        compute_device=compute_device)
         if bucket_bytes <= 0:
             fully_shard(block, **kw, reshard_after_forward=reshard)
             continue

@@ -159,15 +159,14 @@ class C10dComm(ShardComm):
                 # the weight-gradient GEMM wrote (or accumulated) straight into the shard; what autograd
                 # delivered is a zero-stride placeholder unless the parameter had another use (tied weights)
                 if gr is not None and any(st != 0 for st in gr.stride()):
-                    dst.add_(gr.reshape(-1))
+                    _store(dst, gr.reshape(-1), True)
                 continue
             if gr is None:
                 if not accumulate:
                     dst.zero_()
                 continue
             if W == 1 and unit.replicate_group is None:
-                src = gr.reshape(-1)
-                dst.add_(src) if accumulate else dst.copy_(src)  # one fused cast-copy
+                _store(dst, gr.reshape(-1), accumulate)  # one fused cast-copy
                 continue
             full = unit.pack_grad(p, gr, rd)  # [W * n], reduce dtype, chunk-major
             if W == 1:
@@ -181,10 +180,17 @@ class C10dComm(ShardComm):
                 work.wait()
             if unit.replicate_group is not None:
                 dist.all_reduce(red, group=unit.replicate_group)
-            if accumulate:
-                dst.add_(red)
-            else:
-                dst.copy_(red)
+            _store(dst, red, accumulate)
+
+
+def _store(dst: torch.Tensor, src: torch.Tensor, accumulate: bool) -> None:
+    """``dst (+)= src``; with offloaded shards ``dst`` is pinned host memory and ``src`` comes off the device first."""
+    if src.device != dst.device:
+        src = src.to(dst.device, dtype=dst.dtype)
+    if accumulate:
+        dst.add_(src)
+    else:
+        dst.copy_(src)
 
 
 class _Streams:
@@ -224,8 +230,13 @@ class _UnitGather(torch.autograd.Function):
 class FSDPUnit:
     def __init__(self, modules: list[nn.Module], named: list, *, shard_mesh, replicate_mesh, mesh,
                  mp_policy: MixedPrecisionPolicy, reshard_after_forward: bool,
-                 shard_placement_fn: Callable | None = None, comm: ShardComm | None = None):
+                 shard_placement_fn: Callable | None = None, comm: ShardComm | None = None,
+                 compute_device: torch.device | None = None):
         self.modules = modules
+        # CPU offload: the sharded parameters, their gradients and (through them) the optimizer state live in host memory;
+        # ``compute_device`` holds the compute-dtype copy of the shard that the all-gather reads, the gathered parameters
+        # and all activations. None = parameters live where they compute.
+        self.compute_device = torch.device(compute_device) if compute_device is not None else None
         self.mp = mp_policy
         self.reshard_after_forward = reshard_after_forward
         self.mesh, self.shard_mesh, self.replicate_mesh = mesh, shard_mesh, replicate_mesh
@@ -319,7 +330,19 @@ class FSDPUnit:
     # ------------------------------------------------------------------ buffers
     @property
     def device(self):
+        """Where the unit computes (and gathers)."""
+        if self.compute_device is not None:
+            return self.compute_device
+        return self.storage_device
+
+    @property
+    def storage_device(self):
+        """Where the sharded parameters live."""
         return self._local(self.params[0].param).device if self.params else torch.device("cpu")
+
+    @property
+    def offloaded(self) -> bool:
+        return self.compute_device is not None
 
     @staticmethod
     def _local(param):
@@ -356,7 +379,7 @@ class FSDPUnit:
                 p.param._local_tensor = view
             else:
                 p.param.data = view
-        if self.param_dtype != self.orig_dtype:
+        if self.param_dtype != self.orig_dtype or self.offloaded:
             self.shadow_flat = self.alloc_shard_buffer(self.param_dtype, kind="shadow")
         for i, p in enumerate(self.params):
             p.param._tt_unit = (self, i)
@@ -369,7 +392,7 @@ class FSDPUnit:
         """Direct weight-gradient destinations for 2-D parameters on CUDA (see GradSlot)."""
         self._slots = [None] * len(self.params)
         self._slot_written = [False] * len(self.params)
-        if not self.uses_cuda:
+        if not self.uses_cuda or self.offloaded:      # a GEMM cannot write into a host-resident gradient shard
             return
         make = getattr(self.comm, "make_grad_slot", None)
         for i, p in enumerate(self.params):
@@ -384,6 +407,9 @@ class FSDPUnit:
                 self._slots[i] = GradSlot(t, self, i, staging)
 
     def alloc_shard_buffer(self, dtype, kind: str):
+        if self.offloaded and kind in ("master", "grad"):
+            buf = torch.zeros(self.shard_numel, dtype=dtype, device="cpu")
+            return buf.pin_memory() if torch.cuda.is_available() else buf
         alloc = getattr(self.comm, "alloc_shard_buffer", None)
         if alloc is not None:
             buf = alloc(self, dtype, kind)
@@ -403,7 +429,7 @@ class FSDPUnit:
         if self.shadow_flat is None:
             return self.shard_flat
         if self._shadow_stale:
-            self.shadow_flat.copy_(self.shard_flat)
+            self.shadow_flat.copy_(self.shard_flat, non_blocking=True)      # with offload: pinned host -> device, cast on the way
             self._shadow_stale = False
         return self.shadow_flat
 
@@ -723,20 +749,21 @@ def _split_mesh(mesh):
 
 def fully_shard(module, *, mesh, mp_policy: MixedPrecisionPolicy | None = None,
                 reshard_after_forward: bool = True, shard_placement_fn: Callable | None = None,
-                offload_policy=None, comm: ShardComm | None = None):
+                offload_policy=None, comm: ShardComm | None = None, compute_device=None):
     """Shard the parameters of ``module`` (a module, or a list of modules executed in list
     order and gathered together) that no nested unit already owns.
 
     ``mesh``: 1-D ``fsdp`` mesh, or 2-D ``[dp_replicate, fsdp]`` for HSDP.
     """
-    if offload_policy is not None:
-        raise NotImplementedError("CPU offload is not available in this FSDP runtime")
+    if offload_policy is not None and compute_device is None:
+        # torch's ``CPUOffloadPolicy()`` spelling: keep shards on the host, compute on the current accelerator
+        compute_device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     modules = list(module) if isinstance(module, (list, tuple)) else [module]
     named = _managed_params(modules)
     rep, shard = _split_mesh(mesh)
     unit = FSDPUnit(modules, named, shard_mesh=shard, replicate_mesh=rep, mesh=mesh,
                     mp_policy=mp_policy or MixedPrecisionPolicy(), reshard_after_forward=reshard_after_forward,
-                    shard_placement_fn=shard_placement_fn, comm=comm)
+                    shard_placement_fn=shard_placement_fn, comm=comm, compute_device=compute_device)
     for m in modules:
         m._fsdp_unit = unit
     return module
