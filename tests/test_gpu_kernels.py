@@ -583,6 +583,62 @@ def test_mx_grouped_linear_matches_definition(ops, sizes, K, N):
         if n == 0:
             assert float(w.grad[g].abs().max()) == 0.0
 
+@pytest.mark.parametrize("M,N,K", [(256, 512, 192), (200, 264, 136), (4096, 4096, 1024), (96, 128, 64)])
+def test_gemm_with_residual_in_the_epilogue(ops, M, N, K):
+    """``x W^T + r`` in one kernel (the block's skip connection added by the output projection) against the fp32
+    definition, forward and all three gradients; both the CTA-pair and the single-CTA kernel sizes."""
+    torch.manual_seed(0)
+    x = torch.randn(2, M // 2, K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    r = torch.randn(2, M // 2, N, device="cuda").bfloat16().requires_grad_()
+    y = ops.linear_residual(x, w, r)
+    assert y is not None and y.shape == r.shape
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    _no_kernel_errors()
+    want = x.detach().float() @ w.detach().float().t() + r.detach().float()
+    assert _rel(y, want) < 1e-2
+    # the addition happens in fp32 before the single rounding to bf16
+    assert (y.float() - want).abs().max() <= want.abs().max() * 2 ** -8 + 1e-6
+    assert torch.equal(r.grad, gy)
+    assert _rel(x.grad, gy.float() @ w.detach().float()) < 1e-2
+    assert _rel(w.grad, gy.flatten(0, 1).float().t() @ x.detach().flatten(0, 1).float()) < 1e-2
+
+
+def test_block_with_residual_epilogue_matches_separate_additions(ops, monkeypatch):
+    """A Llama block with the skip connections folded into ``wo`` / ``w2`` against the same block adding them afterwards:
+    outputs and every gradient agree to bf16 rounding."""
+    import dataclasses
+
+    from torchtitan_b200.models.common import linear as linear_mod
+    from torchtitan_b200.models.llama3 import llama3_configs
+
+    cfg = llama3_configs["debugmodel"]
+    attn = dataclasses.replace(cfg.layer.attention, n_heads=8, n_kv_heads=2)              # head dimension 128
+    cfg = dataclasses.replace(cfg, n_layers=1, dim=1024, layer=dataclasses.replace(cfg.layer, attention=attn),
+                              rope=dataclasses.replace(cfg.rope, dim=128, max_seq_len=256))
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = cfg.build()
+    model.init_weights()
+    model = model.bfloat16()
+    block = next(iter(model.layers.values()))
+    x = torch.randn(2, 256, cfg.dim, device="cuda").bfloat16()
+    gy = torch.randn_like(x)
+    results = []
+    for on in (True, False):
+        monkeypatch.setattr(linear_mod, "RESIDUAL_EPILOGUE", on)
+        block.zero_grad()
+        xi = x.clone().requires_grad_()
+        y = block(xi, model.freqs_cis, None)
+        y.backward(gy)
+        results.append((y.detach(), xi.grad, {n: p.grad.clone() for n, p in block.named_parameters()}))
+    _no_kernel_errors()
+    (ya, ga, pa), (yb, gb, pb) = results
+    assert _rel(ya, yb) < 1e-2 and _rel(ga, gb) < 1e-2
+    for n in pa:
+        assert _rel(pa[n], pb[n]) < 2e-2, n
+
 
 @pytest.mark.parametrize("Dqk,Dv,H,Hkv", [(64, 64, 8, 2), (192, 128, 4, 4), (128, 128, 4, 2)])
 @pytest.mark.parametrize("causal", [True, False])

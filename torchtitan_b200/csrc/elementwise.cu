@@ -281,7 +281,7 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__
     Vec8<T> gv, uv; gv.load(g + i * 8); uv.load(u + i * 8);
     float gf[8], uf[8], o[8]; gv.to_float(gf); uv.to_float(uf);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[e] = gf[e] / (1.f + __expf(-gf[e])) * uf[e];
+    for (int e = 0; e < 8; ++e) o[e] = __fdividef(gf[e], 1.f + __expf(-gf[e])) * uf[e];   // approximate divide: 2 ulp, issue-bound otherwise
     Vec8<T> ov; ov.from_float(o); ov.store(out + i * 8);
   }
 }
@@ -294,7 +294,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dout, const T* __restric
     float gf[8], uf[8], df[8], og[8], ou[8]; gv.to_float(gf); uv.to_float(uf); dv.to_float(df);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float sg = 1.f / (1.f + __expf(-gf[e]));
+      const float sg = __fdividef(1.f, 1.f + __expf(-gf[e]));
       const float silu = gf[e] * sg;
       ou[e] = df[e] * silu;
       og[e] = df[e] * uf[e] * (sg + silu * (1.f - sg));

@@ -39,7 +39,9 @@ struct GemmArgs {
   void* C;
   long long ldc;
   int c_fp32;
-  int accumulate;       // C += result
+  int accumulate;       // C = result + addend, where the addend is R when set and the previous content of C otherwise
+  const void* R;        // bf16 [M, N] with row stride ldr (residual input of the layer); bf16 output only
+  long long ldr;
   // fused all-gather variant: per n-tile readiness flags (nullptr = plain GEMM)
   const int* ready_flags;
   int ready_value;
@@ -206,7 +208,9 @@ __device__ __forceinline__ void store_chunk_to(const GemmArgs& p, void* Cbase, i
           }
         } else {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cbase) + static_cast<long long>(row) * p.ldc + col;
-          if (full_chunk && (p.ldc % 8 == 0)) {
+          const __nv_bfloat16* add = p.R ? reinterpret_cast<const __nv_bfloat16*>(p.R) + static_cast<long long>(row) * p.ldr + col
+                                         : dst;
+          if (full_chunk && (p.ldc % 8 == 0) && (p.ldr % 8 == 0)) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4* q = reinterpret_cast<uint4*>(dst) + j;
@@ -214,7 +218,7 @@ __device__ __forceinline__ void store_chunk_to(const GemmArgs& p, void* Cbase, i
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
               if (p.accumulate) {
-                uint4 o = *q;
+                uint4 o = *(reinterpret_cast<const uint4*>(add) + j);
                 const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -233,7 +237,7 @@ __device__ __forceinline__ void store_chunk_to(const GemmArgs& p, void* Cbase, i
           } else {
             for (int j = 0; j < 32 && col + j < p.N; ++j) {
               float v = __uint_as_float(r[j]);
-              if (p.accumulate) v += __bfloat162float(dst[j]);
+              if (p.accumulate) v += __bfloat162float(add[j]);
               dst[j] = __float2bfloat16(v);
             }
           }
@@ -794,12 +798,13 @@ extern "C" {
 
 // A: [M,K] (a_mn=0, row stride lda) or stored transposed [K,M] (a_mn=1). Same for B with N.
 // Returns 0 on success, a negative number on invalid arguments / descriptor failures.
-int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, long long lda, int b_mn,
-                 long long ldb, long long ldc, int c_fp32, int accumulate, const int* ready_flags, int ready_value,
-                 int max_ctas, cudaStream_t stream) {
+static int gemm_bf16_launch(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, long long lda, int b_mn,
+                            long long ldb, long long ldc, int c_fp32, int accumulate, const int* ready_flags, int ready_value,
+                            int max_ctas, const void* R, long long ldr, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8)) return -2;  // TMA needs 16-byte row strides
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (R && (c_fp32 || (reinterpret_cast<uintptr_t>(R) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))) return -3;
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -821,7 +826,8 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
   p.M = M; p.N = N; p.K = K;
   p.k_iters = (K + BK - 1) / BK;
   p.a_mn = a_mn; p.b_mn = b_mn;
-  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = accumulate; p.R = nullptr; p.ldr = 0;
+  if (R) { p.accumulate = 1; p.R = R; p.ldr = ldr; }
   p.ready_flags = ready_flags; p.ready_value = ready_value;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
   p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr; p.rs_world = 0;
@@ -845,6 +851,21 @@ int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
     gemm_bf16_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int tt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int a_mn, long long lda, int b_mn,
+                 long long ldb, long long ldc, int c_fp32, int accumulate, const int* ready_flags, int ready_value,
+                 int max_ctas, cudaStream_t stream) {
+  return gemm_bf16_launch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, c_fp32, accumulate, ready_flags, ready_value, max_ctas,
+                          nullptr, 0, stream);
+}
+
+// C[M,N] = A . B^T + R with R bf16 [M,N] (row stride ldr, 16-byte aligned): the residual connection of a transformer
+// block folded into the epilogue of its output projection (saves the separate add: one read and one write of C).
+int tt_gemm_bf16_res(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int a_mn, long long lda,
+                     int b_mn, long long ldb, long long ldc, long long ldr, cudaStream_t stream) {
+  if (!R || (ldr % 8)) return -2;
+  return gemm_bf16_launch(A, B, C, M, N, K, a_mn, lda, b_mn, ldb, ldc, 0, 0, nullptr, 0, 0, R, ldr, stream);
 }
 
 // C[M,N] = (A[M,K] . B[N,K]^T) * scales with 8-bit float operands (a_e5m2 / b_e5m2 select e5m2 instead of e4m3), both
@@ -874,7 +895,7 @@ int tt_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, long
   p.M = M; p.N = N; p.K = K;
   p.k_iters = (K + BK8 - 1) / BK8;
   p.a_mn = 0; p.b_mn = 0;
-  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0; p.R = nullptr; p.ldr = 0;
   p.ready_flags = nullptr; p.ready_value = 0;
   p.fp8 = 1; p.bk = BK8; p.scale_mode = scale_mode; p.scale_a = scale_a; p.scale_b = scale_b;
   p.flags_by_m = 0; p.m_rot = 0; p.copy_ctas = 0; p.panel_ready = nullptr; p.rs_world = 0;
@@ -930,7 +951,7 @@ int tt_gemm_allgather_a(const void* const* peer_bufs, const int* const* peer_fla
   p.M = M; p.N = N; p.K = K;
   p.k_iters = (K + BK - 1) / BK;
   p.a_mn = 0; p.b_mn = b_mn;
-  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32; p.accumulate = 0; p.R = nullptr; p.ldr = 0;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
   p.ready_flags = panel_ready; p.ready_value = ready_value; p.panel_ready = panel_ready;
   p.flags_by_m = 1; p.rs_world = 0;
@@ -995,7 +1016,7 @@ int tt_gemm_reduce_scatter(const void* A, const void* B, void* const* stages, in
   p.M = M; p.N = N; p.K = K;
   p.k_iters = (K + BK - 1) / BK;
   p.a_mn = 0; p.b_mn = b_mn;
-  p.C = nullptr; p.ldc = N; p.c_fp32 = 0; p.accumulate = 0;
+  p.C = nullptr; p.ldc = N; p.c_fp32 = 0; p.accumulate = 0; p.R = nullptr; p.ldr = 0;
   p.fp8 = 0; p.bk = BK; p.scale_mode = 0; p.scale_a = p.scale_b = nullptr;
   p.ready_flags = nullptr; p.ready_value = 0; p.panel_ready = nullptr; p.flags_by_m = 0;
   p.rs_world = world; p.rs_rank = rank; p.rs_out = out; p.rs_rows_per_rank = M / world;

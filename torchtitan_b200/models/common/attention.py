@@ -163,7 +163,8 @@ class GQAttention(BaseAttention):
         self.wo = lin.build(in_features=self.n_heads * self.head_dim, out_features=dim)
         self.inner_attention = InnerAttention()
 
-    def forward(self, x, rope_cache, attention_masks: AttentionMasksType | None, positions=None):
+    def forward(self, x, rope_cache, attention_masks: AttentionMasksType | None, positions=None, residual=None):
+        """``residual``: the block's skip connection, added to the output projection (inside its GEMM where possible)."""
         bs, seqlen, _ = x.shape
         # asynchronous tensor parallel (parallel/tp.py): ``x`` is this rank's sequence shard, the projections gather it
         # inside the GEMM and ``wo`` reduce-scatters inside its GEMM
@@ -189,8 +190,10 @@ class GQAttention(BaseAttention):
             assert isinstance(attention_masks, AttentionMasks), attention_masks
         out = self.inner_attention(xq, xk, xv, masks=attention_masks, scale=self.scaling)
         if fused_tp is not None:
-            return fused_tp.output(self, out.reshape(bs, seqlen, -1))
-        return self.wo(out.reshape(bs, seqlen, -1))
+            y = fused_tp.output(self, out.reshape(bs, seqlen, -1))
+            return y if residual is None else residual + y
+        out = out.reshape(bs, seqlen, -1)
+        return self.wo(out) if residual is None else self.wo.add_to(residual, out)
 
     def init_weights(self, init_std: float = 0.02, **kwargs) -> None:
         for lin in (self.wq, self.wk, self.wv):

@@ -33,8 +33,10 @@ class FeedForward(Module):
         self.w2 = lin.build(in_features=config.hidden_dim, out_features=config.dim)
         self.w3 = lin.build(in_features=config.dim, out_features=config.hidden_dim)
 
-    def forward(self, x):
-        return self.w2(ops.swiglu(self.w1(x), self.w3(x)))
+    def forward(self, x, residual=None):
+        """``w2(silu(w1 x) * w3 x)``, plus ``residual`` (the block's skip connection) when given."""
+        h = ops.swiglu(self.w1(x), self.w3(x))
+        return self.w2(h) if residual is None else self.w2.add_to(residual, h)
 
     def init_weights(self, init_std: float = 0.02, **kwargs):
         self.w1.init_weights()

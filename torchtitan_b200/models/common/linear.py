@@ -6,8 +6,15 @@ from dataclasses import dataclass, field
 
 import torch.nn as nn
 
+import os
+
 from torchtitan_b200 import ops
+from torchtitan_b200.ops.wgrad_store import WeightGradStore
 from torchtitan_b200.protocols.module import Module
+
+
+# residual additions inside the output projections' GEMM epilogues (``Linear.add_to``); TT_RESIDUAL_EPILOGUE=0 adds afterwards
+RESIDUAL_EPILOGUE = os.environ.get("TT_RESIDUAL_EPILOGUE", "0") == "1"
 
 
 class Linear(nn.Linear, Module):
@@ -36,8 +43,31 @@ class Linear(nn.Linear, Module):
             return quant_linear(x, self.weight, self.bias, self.quant)
         return ops.linear(x, self.weight, self.bias)
 
+    def add_to(self, residual, x):
+        """``residual + self(x)``. On CUDA in bf16 the addition runs in the epilogue of the GEMM (one kernel, no extra pass
+        over the output); a layer that is quantised, has a bias or had its forward replaced (tensor parallel) adds after
+        the call."""
+        if RESIDUAL_EPILOGUE and self.quant is None and self.bias is None and "forward" not in self.__dict__ and x.is_cuda \
+                and not WeightGradStore.enabled:
+            from torchtitan_b200.ops import cuda_ops
+
+            y = cuda_ops.linear_residual(x, self.weight, residual)
+            if y is not None:
+                return y
+        return residual + self(x)
+
     def init_weights(self, **kwargs) -> None:
         std = kwargs.get("init_std")
         nn.init.trunc_normal_(self.weight, mean=self._init_mean, std=self._init_std if std is None else std)
         if self.bias is not None:
             nn.init.zeros_(self.bias)
+
+
+def with_residual(module, residual, *args):
+    """``residual + module(*args)``. A module whose forward takes ``residual`` adds it in its output projection; one
+    whose forward was replaced (tensor parallel gathers / scatters around it) gets the addition after the call, where
+    the shapes match again."""
+    if "forward" in module.__dict__:
+        return residual + module(*args)
+    return module(*args, residual=residual)
+

@@ -10,6 +10,7 @@ from dataclasses import dataclass
 import torch.nn as nn
 
 from torchtitan_b200.models.common.decoder import Decoder, TransformerBlock
+from torchtitan_b200.models.common.linear import with_residual
 from torchtitan_b200.models.utils import get_dense_model_nparams_and_flops
 from torchtitan_b200.tools.logging import logger
 
@@ -30,8 +31,9 @@ class Llama3TransformerBlock(TransformerBlock):
         self.weight_init_std = 0.02 / (2 * depth) ** 0.5
 
     def forward(self, x, freqs_cis, attention_masks, positions=None):
-        h = x + self.attention(self.attention_norm(x), freqs_cis, attention_masks, positions)
-        return h + self.feed_forward(self.ffn_norm(h))
+        # the skip connections are handed to the output projections, which add them in their GEMM epilogues
+        h = with_residual(self.attention, x, self.attention_norm(x), freqs_cis, attention_masks, positions)
+        return with_residual(self.feed_forward, h, self.ffn_norm(h))
 
     def init_weights(self, **kwargs):
         self.attention_norm.init_weights()

@@ -119,6 +119,62 @@ class _LinearFn(torch.autograd.Function):
         return gx, gw, gb
 
 
+@torch.library.custom_op("tt_b200::gemm_res", mutates_args=())
+def gemm_res(a: Tensor, b: Tensor, r: Tensor) -> Tensor:
+    """``C[M,N] = A[M,K] · B[N,K]^T + R[M,N]`` (bf16): the residual addition runs in the GEMM's epilogue."""
+    M, K = a.shape
+    N = b.shape[0]
+    c = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _ck(_lib().tt_gemm_bf16_res(a.data_ptr(), b.data_ptr(), c.data_ptr(), r.data_ptr(), M, N, K, 0, a.stride(0), 0, b.stride(0),
+                                c.stride(0), r.stride(0), _stream()), "tt_gemm_bf16_res")
+    return c
+
+
+@gemm_res.register_fake
+def _(a, b, r):
+    return a.new_empty((a.shape[0], b.shape[0]), dtype=torch.bfloat16)
+
+
+class _LinearResFn(torch.autograd.Function):
+    """``y = x W^T + r``; backward as :class:`_LinearFn`, the residual's gradient is the output's."""
+
+    @staticmethod
+    def forward(ctx, x, w, res):
+        x2, r2 = _rows2d(x), _rows2d(res)
+        y = torch.ops.tt_b200.gemm_res(x2, w, r2)
+        ctx.save_for_backward(x2, w)
+        ctx.xshape = x.shape
+        ctx.grad_slot = getattr(w, "_grad_slot", None)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        g2 = _rows2d(gy)
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.ops.tt_b200.gemm(g2, w, False, True, False).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            slot = ctx.grad_slot
+            if slot is not None:
+                gemm_into(g2, x2, slot.tensor, a_mn=True, b_mn=True, accumulate=slot.begin())
+                gw = _placeholder(w)
+            else:
+                gw = torch.ops.tt_b200.gemm(g2, x2, True, True, False)
+        return gx, gw, (gy if ctx.needs_input_grad[2] else None)
+
+
+def linear_residual(x: Tensor, weight: Tensor, residual: Tensor) -> Tensor | None:
+    """``residual + x @ weight^T`` in one kernel, or None when dtype / layout / library do not allow it."""
+    if not (native.has("tt_gemm_bf16_res") and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and residual.dtype == torch.bfloat16 and weight.dim() == 2 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0
+            and weight.data_ptr() % 16 == 0 and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0
+            and residual.shape == (*x.shape[:-1], weight.shape[0]) and residual.is_contiguous()
+            and residual.data_ptr() % 16 == 0):
+        return None
+    return _LinearResFn.apply(x, weight, residual)
+
+
 _placeholders: dict = {}
 
 

@@ -84,6 +84,8 @@ def lib():
         L.tt_ep_set_wait_ns.argtypes = [ctypes.c_ulonglong]
         L.tt_ep_set_wait_ns.restype = None
         _sig(L.tt_ep_push_ctas, [])
+    if hasattr(L, "tt_gemm_bf16_res"):
+        _sig(L.tt_gemm_bf16_res, [P, P, P, P, I, I, I, I, LL, I, LL, LL, LL, P])
     if hasattr(L, "tt_grouped_gemm_mxfp8"):
         _sig(L.tt_grouped_gemm_mxfp8, [P, P, P, P, P, P, I, I, I, I, I, LL, LL, LL, LL, I, I, LL, I, P])
     if hasattr(L, "tt_gemm_mxfp8"):

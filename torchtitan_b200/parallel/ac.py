@@ -63,7 +63,8 @@ def default_op_sac_save_list() -> set:
     }
     ops |= _resolve([
         ("_c10d_functional", "reduce_scatter_tensor"), ("_c10d_functional", "all_to_all_single"),
-        ("tt_b200", "gemm"), ("tt_b200", "mx_mm"), ("tt_b200", "attention_fwd"), ("tt_b200", "grouped_gemm"),
+        ("tt_b200", "gemm"), ("tt_b200", "gemm_res"), ("tt_b200", "mx_mm"), ("tt_b200", "attention_fwd"),
+        ("tt_b200", "grouped_gemm"),
         ("tt_b200", "tp_reduce_scatter"), ("tt_b200", "ep_all_to_all"),
     ])
     return ops
@@ -72,7 +73,7 @@ def default_op_sac_save_list() -> set:
 def _mm_ops() -> set:
     _ensure_custom_ops_registered()
     aten = torch.ops.aten
-    return {aten.mm.default, aten.linear.default} | _resolve([("tt_b200", "gemm"), ("tt_b200", "mx_mm")])
+    return {aten.mm.default, aten.linear.default} | _resolve([("tt_b200", "gemm"), ("tt_b200", "gemm_res"), ("tt_b200", "mx_mm")])
 
 
 def _wrap_forward(module: nn.Module, ac_config, context_fn=None) -> nn.Module:
