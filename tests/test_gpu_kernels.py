@@ -605,9 +605,33 @@ def test_gemm_with_residual_in_the_epilogue(ops, M, N, K):
     assert _rel(w.grad, gy.flatten(0, 1).float().t() @ x.detach().flatten(0, 1).float()) < 1e-2
 
 
+def test_linears_of_one_input_share_their_input_gradient(ops):
+    """``wq / wk / wv`` as one autograd node: outputs as separate linears, the input gradient summed inside the GEMMs."""
+    torch.manual_seed(0)
+    x = torch.randn(2, 192, 512, device="cuda").bfloat16().requires_grad_()
+    ws = [(torch.randn(n, 512, device="cuda") * 0.05).bfloat16().requires_grad_() for n in (512, 128, 128)]
+    ys = ops.multi_linear(x, ws)
+    assert ys is not None and [y.shape[-1] for y in ys] == [512, 128, 128]
+    gys = [torch.randn_like(y) for y in ys]
+    torch.autograd.backward(ys, gys)
+    _no_kernel_errors()
+    xf = x.detach().float()
+    want_gx = sum(g.float() @ w.detach().float() for g, w in zip(gys, ws))
+    assert _rel(x.grad, want_gx) < 1.5e-2
+    for y, g, w in zip(ys, gys, ws):
+        assert _rel(y, xf @ w.detach().float().t()) < 1e-2
+        assert _rel(w.grad, g.flatten(0, 1).float().t() @ xf.flatten(0, 1)) < 1e-2
+    # one output unused: its weight gets no gradient, the others are unchanged
+    x2 = x.detach().clone().requires_grad_()
+    ya, yb, _ = ops.multi_linear(x2, [w.detach().requires_grad_() for w in ws])
+    torch.autograd.backward([ya, yb], gys[:2])
+    assert _rel(x2.grad, gys[0].float() @ ws[0].detach().float() + gys[1].float() @ ws[1].detach().float()) < 1.5e-2
+
+
 def test_block_with_residual_epilogue_matches_separate_additions(ops, monkeypatch):
-    """A Llama block with the skip connections folded into ``wo`` / ``w2`` against the same block adding them afterwards:
-    outputs and every gradient agree to bf16 rounding."""
+    """A Llama block with the skip connections folded into ``wo`` / ``w2`` and the input gradients of ``wq / wk / wv`` and
+    ``w1 / w3`` summed in GEMM epilogues, against the same block with separate additions: outputs and every gradient
+    agree to bf16 rounding."""
     import dataclasses
 
     from torchtitan_b200.models.common import linear as linear_mod
@@ -628,6 +652,7 @@ def test_block_with_residual_epilogue_matches_separate_additions(ops, monkeypatc
     results = []
     for on in (True, False):
         monkeypatch.setattr(linear_mod, "RESIDUAL_EPILOGUE", on)
+        monkeypatch.setattr(linear_mod, "FUSED_DGRAD", on)
         block.zero_grad()
         xi = x.clone().requires_grad_()
         y = block(xi, model.freqs_cis, None)

@@ -21,7 +21,7 @@ import torch
 from torchtitan_b200 import ops
 from torchtitan_b200.protocols.module import Module
 
-from .linear import Linear
+from .linear import Linear, project_together
 from .rmsnorm import RMSNorm
 from .rope import apply_rotary_emb
 
@@ -175,9 +175,7 @@ class GQAttention(BaseAttention):
             xq, xk, xv = (t.view(bs, seqlen, -1, self.head_dim) for t in (q2, k2, v2))
         else:
             # -1 for the head count: tensor parallel shards the projections by heads
-            xq = self.wq(x).view(bs, seqlen, -1, self.head_dim)
-            xk = self.wk(x).view(bs, seqlen, -1, self.head_dim)
-            xv = self.wv(x).view(bs, seqlen, -1, self.head_dim)
+            xq, xk, xv = (t.view(bs, seqlen, -1, self.head_dim) for t in project_together(x, self.wq, self.wk, self.wv))
         if self.q_norm is not None:
             xq, xk = self.q_norm(xq), self.k_norm(xk)
         if self.use_rope:

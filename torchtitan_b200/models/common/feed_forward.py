@@ -9,7 +9,7 @@ from dataclasses import dataclass, field
 from torchtitan_b200 import ops
 from torchtitan_b200.protocols.module import Module
 
-from .linear import Linear
+from .linear import Linear, project_together
 
 
 def compute_ffn_hidden_dim(dim: int, *, multiple_of: int = 1, ffn_dim_multiplier: float | None = None) -> int:
@@ -35,7 +35,7 @@ class FeedForward(Module):
 
     def forward(self, x, residual=None):
         """``w2(silu(w1 x) * w3 x)``, plus ``residual`` (the block's skip connection) when given."""
-        h = ops.swiglu(self.w1(x), self.w3(x))
+        h = ops.swiglu(*project_together(x, self.w1, self.w3))
         return self.w2(h) if residual is None else self.w2.add_to(residual, h)
 
     def init_weights(self, init_std: float = 0.02, **kwargs):

@@ -4,6 +4,7 @@ features, truncated-normal init with a per-call ``init_std`` override, zero bias
 
 from dataclasses import dataclass, field
 
+import torch
 import torch.nn as nn
 
 import os
@@ -15,6 +16,10 @@ from torchtitan_b200.protocols.module import Module
 
 # residual additions inside the output projections' GEMM epilogues (``Linear.add_to``); TT_RESIDUAL_EPILOGUE=0 adds afterwards
 RESIDUAL_EPILOGUE = os.environ.get("TT_RESIDUAL_EPILOGUE", "0") == "1"
+
+
+# input gradients of linears that share their input summed in GEMM epilogues (``project_together``); TT_FUSED_DGRAD=0: by autograd
+FUSED_DGRAD = os.environ.get("TT_FUSED_DGRAD", "0") == "1"
 
 
 class Linear(nn.Linear, Module):
@@ -71,3 +76,16 @@ def with_residual(module, residual, *args):
         return residual + module(*args)
     return module(*args, residual=residual)
 
+
+
+def project_together(x, *linears):
+    """``[lin(x) for lin in linears]``. Plain bf16 layers on CUDA run through one autograd node whose backward sums the
+    input gradients inside the GEMMs; anything else (quantised, biased, tensor-parallel wrapped) is called one by one."""
+    if FUSED_DGRAD and x.is_cuda and not WeightGradStore.enabled and torch.is_grad_enabled() and all(
+            type(lin) is Linear and lin.quant is None and lin.bias is None and "forward" not in lin.__dict__ for lin in linears):
+        from torchtitan_b200.ops import cuda_ops
+
+        ys = cuda_ops.multi_linear(x, [lin.weight for lin in linears])
+        if ys is not None:
+            return ys
+    return tuple(lin(x) for lin in linears)

@@ -164,6 +164,58 @@ class _LinearResFn(torch.autograd.Function):
         return gx, gw, (gy if ctx.needs_input_grad[2] else None)
 
 
+class _MultiLinearFn(torch.autograd.Function):
+    """Several bias-free linears of one input (``wq / wk / wv``, ``w1 / w3``): ``y_i = x W_i^T``. The input gradient
+    ``sum_i dy_i W_i`` is formed in one buffer, each GEMM after the first adding in its epilogue, instead of one tensor
+    per layer summed by autograd (two extra passes over ``dx`` per additional layer)."""
+
+    @staticmethod
+    def forward(ctx, x, *ws):
+        x2 = _rows2d(x)
+        ys = tuple(torch.ops.tt_b200.gemm(x2, w, False, False, False).view(*x.shape[:-1], w.shape[0]) for w in ws)
+        ctx.save_for_backward(x2, *ws)
+        ctx.xshape = x.shape
+        ctx.slots = [getattr(w, "_grad_slot", None) for w in ws]
+        return ys
+
+    @staticmethod
+    def backward(ctx, *gys):
+        x2, *ws = ctx.saved_tensors
+        gx = None
+        gws = []
+        for i, (gy, w) in enumerate(zip(gys, ws)):
+            if gy is None:
+                gws.append(None)
+                continue
+            g2 = _rows2d(gy)
+            if ctx.needs_input_grad[0]:
+                if gx is None:
+                    gx = torch.ops.tt_b200.gemm(g2, w, False, True, False)
+                else:
+                    gemm_into(g2, w, gx, b_mn=True, accumulate=True)
+            if ctx.needs_input_grad[1 + i]:
+                slot = ctx.slots[i]
+                if slot is not None:
+                    gemm_into(g2, x2, slot.tensor, a_mn=True, b_mn=True, accumulate=slot.begin())
+                    gws.append(_placeholder(w))
+                else:
+                    gws.append(torch.ops.tt_b200.gemm(g2, x2, True, True, False))
+            else:
+                gws.append(None)
+        return (gx.view(ctx.xshape) if gx is not None else None, *gws)
+
+
+def multi_linear(x: Tensor, weights: list) -> tuple | None:
+    """``[x @ w^T for w in weights]`` with a shared input-gradient buffer, or None when a dtype or layout is not covered."""
+    if x.dtype != torch.bfloat16 or x.shape[-1] % 8:
+        return None
+    for w in weights:
+        if w.dtype != torch.bfloat16 or w.dim() != 2 or w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16 \
+                or w.shape[0] % 8 or w.shape[1] != x.shape[-1]:
+            return None
+    return _MultiLinearFn.apply(x, *weights)
+
+
 def linear_residual(x: Tensor, weight: Tensor, residual: Tensor) -> Tensor | None:
     """``residual + x @ weight^T`` in one kernel, or None when dtype / layout / library do not allow it."""
     if not (native.has("tt_gemm_bf16_res") and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
