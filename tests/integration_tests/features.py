@@ -38,6 +38,8 @@ def build_features_test_list() -> list[T]:
           "Checkpoint: model-only save in bf16", "last_save_model_only_bf16"),
         T([[CKPT, "--checkpoint.async_mode async_with_pinned_mem"]], "Checkpoint: asynchronous save from pinned memory",
           "async_checkpoint", ngpu=2),
+        T([["--training.enable_cpu_offload"]], "FSDP with shards, gradients and optimizer state in host memory", "fsdp_cpu_offload",
+          ngpu=2),
         T([[f"{PP} 4", f"{SCHED} InterleavedZeroBubble"]], "PP looped zero bubble", "pp_looped_zero_bubble", ngpu=4),
         T([[f"{PP} 2", f"{SCHED} ZBVZeroBubble"]], "PP zero bubble (V-shaped)", "pp_zbv", ngpu=2),
         T([[f"{PP} 2", f"{SCHED} DualPipeV"]], "PP DualPipeV placement", "pp_dualpipev", ngpu=2),
