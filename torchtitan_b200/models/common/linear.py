@@ -15,11 +15,11 @@ from torchtitan_b200.protocols.module import Module
 
 
 # residual additions inside the output projections' GEMM epilogues (``Linear.add_to``); TT_RESIDUAL_EPILOGUE=0 adds afterwards
-RESIDUAL_EPILOGUE = os.environ.get("TT_RESIDUAL_EPILOGUE", "0") == "1"
+RESIDUAL_EPILOGUE = os.environ.get("TT_RESIDUAL_EPILOGUE", "1") == "1"
 
 
 # input gradients of linears that share their input summed in GEMM epilogues (``project_together``); TT_FUSED_DGRAD=0: by autograd
-FUSED_DGRAD = os.environ.get("TT_FUSED_DGRAD", "0") == "1"
+FUSED_DGRAD = os.environ.get("TT_FUSED_DGRAD", "1") == "1"
 
 
 class Linear(nn.Linear, Module):
