@@ -300,9 +300,18 @@ def test_attention_sinks(ops, window):
     (4, 256, 128, [64, 0, 192, 128]),
     (8, 768, 2048, [640, 64, 0, 128, 1024, 64, 320, 192]),
     (3, 192, 320, [128, 64, 64]),
+    (2, 512, 256, [448, 832]),
 ])
-def test_grouped_gemm_device_offsets(ops, E, N, K, sizes):
-    """Grouped GEMM with device-side group offsets (forward, input gradient, weight gradient) vs fp32 per-expert matmuls."""
+@pytest.mark.parametrize("pair", [True, False])
+def test_grouped_gemm_device_offsets(ops, E, N, K, sizes, pair):
+    """Grouped GEMM with device-side group offsets (forward, input gradient, weight gradient) vs fp32 per-expert matmuls;
+    256-row tiles on CTA pairs where the shape allows it, and the single-CTA kernel alone."""
+    from torchtitan_b200.ops import native
+
+    if native.has("tt_grouped_gemm_set_pair"):
+        native.lib().tt_grouped_gemm_set_pair(int(pair))
+    elif pair:
+        pytest.skip("library built without the CTA-pair grouped GEMM")
     torch.manual_seed(0)
     R = sum(sizes) + 64                      # trailing padding rows belong to no group
     x = (torch.randn(R, K, device="cuda") * 0.5).bfloat16().requires_grad_()
@@ -325,6 +334,8 @@ def test_grouped_gemm_device_offsets(ops, E, N, K, sizes):
     assert (y[s:] == 0).all()
     assert _rel(x.grad, xr.grad) < 2e-2, _rel(x.grad, xr.grad)
     assert _rel(w.grad, wr.grad) < 2e-2, _rel(w.grad, wr.grad)
+    if native.has("tt_grouped_gemm_set_pair"):
+        native.lib().tt_grouped_gemm_set_pair(1)
 
 
 def test_moe_layer_native_grouped_path(ops):

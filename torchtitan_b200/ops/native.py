@@ -62,6 +62,8 @@ def lib():
     _sig(L.tt_grouped_gemm, [P, P, P, P, LL, I, I, I, I, LL, LL, P])
     _sig(L.tt_grouped_gemm_wgrad, [P, P, P, P, LL, I, I, I, LL, LL, I, P])
     _sig(L.tt_grouped_gemm_error, [])
+    if hasattr(L, "tt_grouped_gemm_set_pair"):
+        _sig(L.tt_grouped_gemm_set_pair, [I], None)
     _sig(L.tt_kv_write, [P, P, P, P, P, LL, I, I, P])
     _sig(L.tt_paged_decode, [P, P, P, P, P, P, F, I, I, I, I, I, I, P])
     _sig(L.tt_sample, [P, P, P, P, I, I, LL, F, I, P])

@@ -176,18 +176,29 @@ def bench_grouped_gemm(args, timer):
     rows = int(sizes.sum())
     x = (torch.randn(rows, K, device="cuda") * 0.5).bfloat16().requires_grad_()
     w = (torch.randn(E, N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    from torchtitan_b200.ops import native as _native
+
+    has_pair = _native.has("tt_grouped_gemm_set_pair")
+    if has_pair:
+        _native.lib().tt_grouped_gemm_set_pair(1)
     y = cuda_ops.grouped_linear(x, w, counts)
     gy = torch.randn_like(y)
-    ms_f = timer.time(lambda: cuda_ops.grouped_linear(x, w, counts), args.iters)
 
     def fb():
         x.grad = w.grad = None
         cuda_ops.grouped_linear(x, w, counts).backward(gy)
 
+    ms_f = timer.time(lambda: cuda_ops.grouped_linear(x, w, counts), args.iters)
     ms_fb = timer.time(fb, args.iters)
     fl = 2.0 * rows * N * K
     out = {"case": "grouped_gemm", "experts": E, "rows": rows, "N": N, "K": K, "fwd_ms": ms_f, "fwd_tflops": fl / ms_f / 1e9,
-           "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3 * fl / ms_fb / 1e9}
+           "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": 3 * fl / ms_fb / 1e9, "cta_pairs": bool(has_pair)}
+    if has_pair:                                     # the single-CTA kernel alone, for comparison
+        _native.lib().tt_grouped_gemm_set_pair(0)
+        s_f = timer.time(lambda: cuda_ops.grouped_linear(x, w, counts), args.iters)
+        s_fb = timer.time(fb, args.iters)
+        out.update(single_cta_fwd_ms=s_f, single_cta_fwd_tflops=fl / s_f / 1e9, single_cta_fwd_bwd_ms=s_fb,
+                   single_cta_fwd_bwd_tflops=3 * fl / s_fb / 1e9)
     # the same layer in MXFP8 (groups padded to 128 rows; times include quantising both operands of every GEMM)
     sizes128 = (raw / raw.sum() * (R - 128 * E)).long() // 128 * 128 + 128
     c128 = sizes128.clone()
