@@ -26,6 +26,9 @@ def build_model_tests_list() -> list[T]:
           ngpu=4, **ds),
         T([[f"{PP} 2", f"{SCHED} Interleaved1F1B", f"{SHARD} 2", f"{EP} 2"]], "DeepSeek V3 PP + FSDP + EP",
           "deepseek_v3_pp+fsdp+ep", ngpu=4, **ds),
+        T([[f"{PP} 2", f"{SCHED} DualPipeV", f"{SHARD} 2", f"{EP} 2", "--training.local_batch_size 8"]],
+          "DeepSeek V3 DualPipeV (forward / backward slots overlapping the expert exchanges) + FSDP + EP",
+          "deepseek_v3_dualpipev+fsdp+ep", ngpu=4, **ds),
         T([[f"{SHARD} 2", f"{CP} 2"]], "DeepSeek V3 FSDP + CP", "deepseek_v3_fsdp+cp", ngpu=4, **ds),
         T([[]], "DeepSeek V3 with document masks", "deepseek_v3_flex", ngpu=2, module="deepseek_v3",
           config="deepseek_v3_debugmodel_flex_attn"),

@@ -79,7 +79,7 @@ def test_schedule_checks_reject_a_weight_step_before_its_input_step(tmp_path):
         validate_actions([ranks[0], ranks[1][:-1]], 2, 2, 2, "loop")
 
 
-def _worker(rank, world, schedule):
+def _worker(rank, world, schedule, overlap=False):
     import torch.distributed as dist
 
     dist.init_process_group("gloo")
@@ -107,6 +107,13 @@ def _worker(rank, world, schedule):
         compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode="none"), dump_folder="/tmp",
         device=torch.device("cpu"), model_config=cfg, parallelize_fn=parallelize_llama, loss_fn=cross_entropy_loss,
     )
+    if overlap:
+        # whole backward steps, neighbours of different micro-batches merged into slots that run both halves on two threads
+        sched.all_actions = build_actions(schedule, world, 2 * world, B, "v", split=False, overlap=True)
+        validate_actions(sched.all_actions, world, 2 * world, B, "v")
+        from torchtitan_b200.ops.wgrad_store import WeightGradStore
+
+        WeightGradStore.enabled = False
     losses = [] if last else None
     scale = torch.tensor(1.0 / lab.numel())
     if first:
@@ -142,6 +149,50 @@ def test_pp2_matches_single_process(tmp_path, schedule):
         assert abs(o["loss"] - o["ref"]) < 1e-5, o
         assert abs(o["eval"] - o["ref"]) < 1e-5, o
     assert max(o["grad_err"] for o in res) < 1e-5, res
+
+
+def test_overlapped_forward_backward_slots_match_single_process(tmp_path):
+    """DualPipeV slots that run a forward and a backward of different micro-batches on two threads: same loss and
+    gradients as the single-process model."""
+    res = run_ranks(_worker, 2, "DualPipeV", True, tmp_path=tmp_path)
+    assert any("O" in o["kinds"] for o in res), res
+    got = [o for o in res if o["loss"] is not None]
+    for o in got:
+        assert abs(o["loss"] - o["ref"]) < 1e-5, o
+    assert max(o["grad_err"] for o in res) < 1e-5, res
+
+
+def test_overlap_baton_alternates_at_yield_points():
+    from torchtitan_b200.parallel.overlap import active, run_overlapped, yield_point
+
+    log = []
+
+    def piece(name, n):
+        def run():
+            assert active()
+            for i in range(n):
+                log.append(f"{name}{i}")
+                yield_point()
+            return name
+        return run
+
+    assert run_overlapped(piece("a", 3), piece("b", 5)) == ("a", "b")
+    assert log == ["a0", "b0", "a1", "b1", "a2", "b2", "b3", "b4"] and not active()
+    with pytest.raises(ZeroDivisionError):
+        run_overlapped(lambda: 1 / 0, piece("c", 2))
+
+
+def test_overlapped_slot_syntax_and_checks(tmp_path):
+    path = tmp_path / "s.csv"
+    path.write_text("0F0,0F1,0B0,0B1\n1F0,1F1+1B0,1B1\n")
+    ranks = load_csv_actions(str(path))
+    assert ranks[1][1] == Action(1, "O", 1, ("B", 1, 0)) and [p.kind for p in ranks[1][1].parts()] == ["F", "B"]
+    validate_actions(ranks, 2, 2, 2, "loop")
+    # both halves wait for their inputs before either sends: pairing 0F1 with 0B0 would wait for a gradient that needs 0F1... of
+    # the same rank's later work only if the micro-batches were equal; an equal pair is rejected as a deadlock
+    bad = [[Action(0, "F", 0), Action(0, "O", 1, ("B", 0, 1))], [Action(1, "F", 0), Action(1, "B", 0), Action(1, "F", 1), Action(1, "B", 1)]]
+    with pytest.raises(RuntimeError):
+        validate_actions(bad, 2, 2, 2, "loop")
 
 
 def test_keyword_arguments_are_cut_per_micro_batch():

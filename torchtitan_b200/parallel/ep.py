@@ -30,6 +30,21 @@ from torchtitan_b200.tools.logging import logger
 __all__ = ["apply_moe_ep_tp", "AllToAllDispatcher", "all_to_all_rows"]
 
 
+def _exchange(out, x, out_splits, in_splits, group):
+    """The all-to-all itself. Inside a pipeline slot that runs a forward and a backward together
+    (``parallel/overlap.py``) it is issued in the background and the other piece of work gets the compute stream until
+    its own next exchange; the wait comes after the baton is back."""
+    from . import overlap
+
+    if overlap.active():
+        work = dist.all_to_all_single(out, x, out_splits, in_splits, group=group, async_op=True)
+        overlap.yield_point()
+        work.wait()
+    else:
+        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+    return out
+
+
 class _AllToAllRows(torch.autograd.Function):
     """Variable-split all-to-all of rows; backward runs the reverse exchange."""
 
@@ -37,14 +52,12 @@ class _AllToAllRows(torch.autograd.Function):
     def forward(ctx, x, out_splits, in_splits, group):
         ctx.group, ctx.out_splits, ctx.in_splits = group, out_splits, in_splits
         out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
-        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
-        return out
+        return _exchange(out, x.contiguous(), out_splits, in_splits, group)
 
     @staticmethod
     def backward(ctx, g):
         out = g.new_empty((sum(ctx.in_splits),) + tuple(g.shape[1:]))
-        dist.all_to_all_single(out, g.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
-        return out, None, None, None
+        return _exchange(out, g.contiguous(), ctx.in_splits, ctx.out_splits, ctx.group), None, None, None
 
 
 def all_to_all_rows(x, out_splits, in_splits, group):

@@ -131,12 +131,23 @@ def pipeline_module_split(whole: nn.Module, pp_rank: int, pp: int, schedule: str
 @dataclass(frozen=True)
 class Action:
     stage: int
-    kind: str  # "F" forward, "B" whole backward, "I" input-gradient half, "W" weight-gradient half
+    kind: str  # "F" forward, "B" whole backward, "I" input-gradient half, "W" weight-gradient half, "O" overlapped pair
     mb: int
+    other: tuple | None = None  # kind "O": (stage, mb) name the forward, ``other`` = (kind "B" | "I", stage, mb) the backward
+
+    def parts(self) -> list["Action"]:
+        """The plain actions this one stands for (an overlapped pair is its forward, then its backward)."""
+        if self.kind != "O":
+            return [self]
+        return [Action(self.stage, "F", self.mb), Action(self.other[1], self.other[0], self.other[2])]
 
 
 def _parse_action(tok: str) -> Action:
-    m = re.fullmatch(r"(\d+)([FBIW]|BW)(\d+)", tok.strip())
+    tok = tok.strip()
+    pair = re.fullmatch(r"(\d+)F(\d+)\+(\d+)([BI])(\d+)", tok)       # a forward and a backward in one slot: 0F4+7B1
+    if pair:
+        return Action(int(pair.group(1)), "O", int(pair.group(2)), (pair.group(4), int(pair.group(3)), int(pair.group(5))))
+    m = re.fullmatch(r"(\d+)([FBIW]|BW)(\d+)", tok)
     if not m:
         raise ValueError(f"cannot parse pipeline action '{tok}'")
     kind = m.group(2)
@@ -155,7 +166,44 @@ def load_csv_actions(path: str) -> list[list[Action]]:
 
 def fuse_split_backward(ranks: list[list[Action]]) -> list[list[Action]]:
     """The same schedule with whole backward steps: ``I`` becomes ``B`` and ``W`` is dropped."""
-    return [[Action(a.stage, "B", a.mb) if a.kind == "I" else a for a in acts if a.kind != "W"] for acts in ranks]
+    def whole(a):
+        if a.kind == "I":
+            return Action(a.stage, "B", a.mb)
+        if a.kind == "O" and a.other[0] == "I":
+            return Action(a.stage, "O", a.mb, ("B", a.other[1], a.other[2]))
+        return a
+
+    return [[whole(a) for a in acts if a.kind != "W"] for acts in ranks]
+
+
+def pair_forward_backward(ranks: list[list[Action]], pp: int, num_stages: int, n_mb: int, style: str,
+                          credit: float = 0.15) -> list[list[Action]]:
+    """DualPipeV's overlapped slots: a forward next to a backward (or input-gradient) step of a different micro-batch on
+    the same rank become one action whose two halves run together (``parallel/overlap.py``). Both halves take their
+    inputs before either sends its output (the two sends leave in a fixed order, whichever half finishes first), so a
+    pair is kept only if the dependency simulation still completes with it: candidates are tried one by one."""
+    out = [list(acts) for acts in ranks]
+    limit = estimate_makespan(out, num_stages)[0]          # a pairing must pay for the waiting it adds
+    for r in range(len(out)):
+        i = 0
+        while i + 1 < len(out[r]):
+            a, b = out[r][i], out[r][i + 1]
+            if a.mb != b.mb and {a.kind, b.kind} in ({"F", "B"}, {"F", "I"}):
+                f, bk = (a, b) if a.kind == "F" else (b, a)
+                trial = out[r][:i] + [Action(f.stage, "O", f.mb, (bk.kind, bk.stage, bk.mb))] + out[r][i + 2:]
+                keep = out[r]
+                out[r] = trial
+                try:
+                    validate_actions(out, pp, num_stages, n_mb, style)
+                    t = estimate_makespan(out, num_stages, pair_credit=credit)[0]
+                    if t > limit:
+                        out[r] = keep
+                    else:
+                        limit = t
+                except RuntimeError:
+                    out[r] = keep
+            i += 1
+    return out
 
 
 def split_backward(ranks: list[list[Action]], pp: int, style: str) -> list[list[Action]]:
@@ -253,15 +301,17 @@ def _shortest(candidates: list, num_stages: int):
 
 
 def build_actions(schedule: str, pp: int, num_stages: int, n_mb: int, style: str = "loop",
-                  split: bool = False) -> list[list[Action]]:
+                  split: bool = False, overlap: bool = False) -> list[list[Action]]:
     """Per-rank ordered action lists. ``split`` gives a zero-bubble schedule separate I / W steps. The zero-bubble
     schedules take the shortest (by :func:`estimate_makespan`) of the interleaved-1F1B-derived order and two list-scheduled
-    orders (in-flight slack 1 to 3; more slack holds more activations, and ties go to less)."""
+    orders (in-flight slack 1 to 3; more slack holds more activations, and ties go to less). ``overlap`` (DualPipeV
+    only) merges forward / backward neighbours of different micro-batches into slots that run both at once."""
     if schedule in ZERO_BUBBLE:
         base = build_actions("Interleaved1F1B", pp, num_stages, n_mb, style)
         if split:
             base = split_backward(base, pp, style)
-        return _shortest([base] + [list_schedule(pp, num_stages, n_mb, style, k, split) for k in (1, 2, 3)], num_stages)
+        best = _shortest([base] + [list_schedule(pp, num_stages, n_mb, style, k, split) for k in (1, 2, 3)], num_stages)
+        return pair_forward_backward(best, pp, num_stages, n_mb, style) if (overlap and schedule == "DualPipeV") else best
     ranks: list[list[Action]] = [[] for _ in range(pp)]
     my_stages = [stage_indices_for_rank(r, pp, num_stages, style) for r in range(pp)]
     if schedule == "GPipe":
@@ -321,6 +371,17 @@ def validate_actions(ranks: list[list[Action]], pp: int, num_stages: int, n_mb: 
         for r, acts in enumerate(ranks):
             while pos[r] < len(acts):
                 a = acts[pos[r]]
+                if a.kind == "O":
+                    # both halves take their inputs before either sends its output
+                    bk, bs, bm = a.other
+                    ready = (a.stage == 0 or (a.stage - 1, "F", a.mb) in done) and (bs, "F", bm) in done and \
+                        (bs == num_stages - 1 or (bs + 1, "B", bm) in done)
+                    if not ready:
+                        break
+                    done.update({(a.stage, "F", a.mb), (bs, bk, bm), (bs, "B", bm)})
+                    pos[r] += 1
+                    progressed = True
+                    continue
                 if a.kind == "F":
                     ready = a.stage == 0 or (a.stage - 1, "F", a.mb) in done
                 elif a.kind == "W":
@@ -338,39 +399,47 @@ def validate_actions(ranks: list[list[Action]], pp: int, num_stages: int, n_mb: 
                 progressed = True
     if any(pos[r] < len(ranks[r]) for r in range(len(ranks))):
         raise RuntimeError(f"pipeline schedule deadlocks: progress {pos} of {[len(a) for a in ranks]}")
-    owed = {(a.stage, a.mb) for acts in ranks for a in acts if a.kind == "I"} - \
-           {(a.stage, a.mb) for acts in ranks for a in acts if a.kind == "W"}
+    flat = [b for acts in ranks for a in acts for b in a.parts()]
+    owed = {(a.stage, a.mb) for a in flat if a.kind == "I"} - {(a.stage, a.mb) for a in flat if a.kind == "W"}
     if owed:
         raise RuntimeError(f"pipeline schedule: input-gradient steps without a weight-gradient step: {sorted(owed)[:4]}")
 
 
-def estimate_makespan(ranks: list[list[Action]], num_stages: int, cost: dict | None = None) -> tuple[float, float]:
+def estimate_makespan(ranks: list[list[Action]], num_stages: int, cost: dict | None = None,
+                      pair_credit: float = 0.0) -> tuple[float, float]:
     """Length of one step and the idle fraction of the busiest-possible timeline, from a dependency simulation with
-    per-action costs (default: a forward 1, a whole backward 2, each backward half 1; messages are free)."""
+    per-action costs (default: a forward 1, a whole backward 2, each backward half 1; messages are free). An overlapped
+    pair starts when the inputs of both halves are there, takes the sum of their costs less ``pair_credit`` of it (the
+    share of a slot that the overlapped exchanges are expected to hide) and delivers both outputs at its end."""
     cost = cost or {"F": 1.0, "B": 2.0, "I": 1.0, "W": 1.0}
     finish: dict = {}
+
+    def deps_of(a):
+        if a.kind == "F":
+            return [(a.stage - 1, "F", a.mb)] if a.stage > 0 else []
+        if a.kind == "W":
+            return [(a.stage, "B", a.mb)]
+        return [(a.stage, "F", a.mb)] + ([(a.stage + 1, "B", a.mb)] if a.stage < num_stages - 1 else [])
+
     pos, free = [0] * len(ranks), [0.0] * len(ranks)
     progressed = True
     while progressed:
         progressed = False
         for r, acts in enumerate(ranks):
             while pos[r] < len(acts):
-                a = acts[pos[r]]
-                if a.kind == "F":
-                    deps = [(a.stage - 1, "F", a.mb)] if a.stage > 0 else []
-                elif a.kind == "W":
-                    deps = [(a.stage, "B", a.mb)]
-                else:
-                    deps = [(a.stage, "F", a.mb)] + ([(a.stage + 1, "B", a.mb)] if a.stage < num_stages - 1 else [])
+                parts = acts[pos[r]].parts()
+                deps = [d for a in parts for d in deps_of(a)]
                 if any(d not in finish for d in deps):
                     break
-                end = max([free[r]] + [finish[d] for d in deps]) + cost[a.kind]
-                finish[(a.stage, "B" if a.kind == "I" else a.kind, a.mb)] = end
+                work = sum(cost[a.kind] for a in parts) * (1.0 - pair_credit if len(parts) > 1 else 1.0)
+                end = max([free[r]] + [finish[d] for d in deps]) + work
+                for a in parts:
+                    finish[(a.stage, "B" if a.kind == "I" else a.kind, a.mb)] = end
                 free[r] = end
                 pos[r] += 1
                 progressed = True
     total = max(free)
-    busy = max(sum(cost[a.kind] for a in acts) for acts in ranks)
+    busy = max(sum(cost[b.kind] for a in acts for b in a.parts()) for acts in ranks)
     return total, 1.0 - busy / total if total else 0.0
 
 
@@ -441,7 +510,7 @@ class PipelineSchedule:
             if r == self.rank:
                 continue
             seq = []
-            for a in acts:
+            for a in (b for a0 in acts for b in a0.parts()):
                 if a.kind == "F" and a.stage < self.num_stages - 1 and self._rank_of(a.stage + 1) == self.rank:
                     seq.append(("act", a.stage + 1, a.mb))
                 if a.kind in ("B", "I") and a.stage > 0 and self._rank_of(a.stage - 1) == self.rank:
@@ -509,52 +578,75 @@ class PipelineSchedule:
         saved: dict = {}
         pending: list = []
         parked: dict = {}                                # (stage, mb) -> weight-gradient closures of its "I" action
+        last_stage = self.num_stages - 1
+
+        def forward_input(a):
+            if a.stage == 0:
+                return inputs_mb[a.mb]
+            if (a.stage - 1) in self.stages:
+                return saved[(a.stage - 1, a.mb)][1].detach()
+            return self._recv("act", a.stage, a.mb, a.stage - 1)
+
+        def forward_compute(a, x):
+            if a.stage != 0 and train:
+                x.requires_grad_(True)
+            with torch.set_grad_enabled(train):
+                out = self.stages[a.stage](x, **kw_mb[a.mb])
+                if a.stage == last_stage:
+                    loss_sum = self.loss_fn(out, target_mb[a.mb])
+                    val = loss_sum * loss_scale if loss_scale is not None else loss_sum
+                    if losses is not None:
+                        losses.append(val.detach().reshape(()))
+                    out = val
+            saved[(a.stage, a.mb)] = (x, out)
+            return out
+
+        def forward_send(a, out):
+            if a.stage != last_stage and (a.stage + 1) not in self.stages:
+                self._send(out.detach(), "act", a.stage + 1, pending)
+
+        def backward_input(a):
+            if a.stage == last_stage:
+                return None
+            if (a.stage + 1) in self.stages:
+                return self._local_grads.pop((a.stage, a.mb))
+            return self._recv("grad", a.stage, a.mb, a.stage + 1)
+
+        def backward_compute(a, g):
+            x, out = saved.pop((a.stage, a.mb))
+            if a.kind == "I":
+                with WeightGradStore.collect() as queue:
+                    torch.autograd.backward(out, g)
+                parked[(a.stage, a.mb)] = queue
+            else:
+                torch.autograd.backward(out, g)
+            return x.grad if a.stage != 0 else None
+
+        def backward_send(a, gx):
+            if a.stage == 0:
+                return
+            if (a.stage - 1) in self.stages:
+                self._local_grads[(a.stage - 1, a.mb)] = gx
+            else:
+                self._send(gx, "grad", a.stage - 1, pending)
+
         for a in actions_per_rank[self.rank]:
             if a.kind == "W":
                 WeightGradStore.run(parked.pop((a.stage, a.mb)))
-                continue
-            mod = self.stages[a.stage]
-            first, last = a.stage == 0, a.stage == self.num_stages - 1
-            if a.kind == "F":
-                if first:
-                    x = inputs_mb[a.mb]
-                elif (a.stage - 1) in self.stages:
-                    x = saved[(a.stage - 1, a.mb)][1].detach()
-                else:
-                    x = self._recv("act", a.stage, a.mb, a.stage - 1)
-                if not first and train:
-                    x.requires_grad_(True)
-                with torch.set_grad_enabled(train):
-                    out = mod(x, **kw_mb[a.mb])
-                    if last:
-                        loss_sum = self.loss_fn(out, target_mb[a.mb])
-                        val = loss_sum * loss_scale if loss_scale is not None else loss_sum
-                        if losses is not None:
-                            losses.append(val.detach().reshape(()))
-                        out = val
-                saved[(a.stage, a.mb)] = (x, out)
-                if not last and (a.stage + 1) not in self.stages:
-                    self._send(out.detach(), "act", a.stage + 1, pending)
+            elif a.kind == "F":
+                forward_send(a, forward_compute(a, forward_input(a)))
+            elif a.kind == "O":
+                # a forward and a backward of different micro-batches in one slot: inputs first, then the two computations
+                # taking turns at their expert-parallel exchanges, then the outputs in the order the peers expect
+                from .overlap import run_overlapped
+
+                f, b = a.parts()
+                x, g = forward_input(f), backward_input(b)
+                out, gx = run_overlapped(lambda: forward_compute(f, x), lambda: backward_compute(b, g))
+                forward_send(f, out)
+                backward_send(b, gx)
             else:
-                x, out = saved.pop((a.stage, a.mb))
-                if last:
-                    g = None
-                elif (a.stage + 1) in self.stages:
-                    g = self._local_grads.pop((a.stage, a.mb))
-                else:
-                    g = self._recv("grad", a.stage, a.mb, a.stage + 1)
-                if a.kind == "I":
-                    with WeightGradStore.collect() as queue:
-                        torch.autograd.backward(out, g)
-                    parked[(a.stage, a.mb)] = queue
-                else:
-                    torch.autograd.backward(out, g)
-                if not first:
-                    gx = x.grad
-                    if (a.stage - 1) in self.stages:
-                        self._local_grads[(a.stage - 1, a.mb)] = gx
-                    else:
-                        self._send(gx, "grad", a.stage - 1, pending)
+                backward_send(a, backward_compute(a, backward_input(a)))
             pending = [(w, t) for (w, t) in pending if not w.is_completed()]
         for w, _ in pending:
             w.wait()
@@ -564,7 +656,7 @@ class PipelineSchedule:
         self._run(self.all_actions, args, kwargs, target, losses, loss_scale, train=True)
 
     def eval(self, *args, target=None, losses=None, **kwargs):
-        fwd_only = [[a for a in acts if a.kind == "F"] for acts in self.all_actions]
+        fwd_only = [[b for a in acts for b in a.parts() if b.kind == "F"] for acts in self.all_actions]
         with torch.no_grad():
             self._run(fwd_only, args, kwargs, target, losses, None, train=False)
 
@@ -629,7 +721,10 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
         if not can_split:
             all_actions = fuse_split_backward(all_actions)
     else:
-        all_actions = build_actions(schedule, pp, num_stages, n_mb, style, split=can_split)
+        # DualPipeV with expert parallel: forward / backward neighbours share a slot so that the token exchanges of one hide
+        # behind the compute of the other
+        all_actions = build_actions(schedule, pp, num_stages, n_mb, style, split=can_split,
+                                    overlap=bool(getattr(parallel_dims, "ep_enabled", False)))
     validate_actions(all_actions, pp, num_stages, n_mb, style)
     sched = PipelineSchedule(
         stages=dict(zip(idx, parts)), all_actions=all_actions, pp_group=pp_mesh.get_group(), pp_rank=pp_rank, pp=pp,
@@ -638,6 +733,9 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
     logger.info(f"Using pipeline schedule {schedule if not csv_path else csv_path} with {n_mb} microbatches and {num_stages} stages.")
     has_split = any(a.kind in ("I", "W") for acts in all_actions for a in acts)
     WeightGradStore.enabled = has_split
+    n_pairs = sum(1 for acts in all_actions for a in acts if a.kind == "O")
+    if n_pairs:
+        logger.info(f"{n_pairs} pipeline slots run a forward and a backward of different micro-batches together")
     logger.info("Pipeline bubble estimate (forward 1, backward 2 units per stage and micro-batch): "
                 f"{estimate_makespan(all_actions, num_stages)[1]:.1%} of the step")
     if has_split:
@@ -648,6 +746,6 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
         logger.warning(
             f"Pipeline schedule {csv_path or schedule}: the stages are under FSDP / replicate units, whose gradient "
             "reduction consumes the weight gradients inside the backward pass, so input- and weight-gradient work is not "
-            f"split and the schedule runs as {'a V-shaped' if style != 'loop' else 'an'} interleaved 1F1B "
-            "(same stage placement and results, the bubble of 1F1B).")
+            "split: the schedule keeps its stage placement and runs whole backward steps in a list-scheduled order "
+            "(same results, a larger bubble than the split order; see the estimate above).")
     return sched, parts, sched.has_first, sched.has_last
