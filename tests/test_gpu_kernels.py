@@ -541,6 +541,22 @@ def test_mx_linear_op_matches_definition(ops, rows, K, N):
     # and close to the unquantised product (e4m3 keeps 3 mantissa bits)
     assert _rel(y.view(rows, N), xd.float() @ wd.float().t()) < 8e-2
 
+def test_scale_rows_fused(ops):
+    """Rows times one fp32 factor each in one pass, with both gradients, against the fp32 definition."""
+    torch.manual_seed(0)
+    rows = torch.randn(1000, 2048, device="cuda").bfloat16().requires_grad_()
+    sc = torch.rand(1000, 1, device="cuda").requires_grad_()
+    out = ops.scale_rows(rows, sc)
+    g = torch.randn_like(out)
+    out.backward(g)
+    _no_kernel_errors()
+    rf, sf = rows.detach().float().requires_grad_(), sc.detach().clone().requires_grad_()
+    ref = rf * sf
+    ref.backward(g.float())
+    assert _rel(out, ref) < 1e-2 and _rel(rows.grad, rf.grad) < 1e-2
+    assert _rel(sc.grad, sf.grad) < 1e-2 and sc.grad.shape == sc.shape
+
+
 @pytest.mark.parametrize("sizes,K,N", [
     ([128, 0, 384, 256], 256, 384),          # an empty expert, N % 256 == 128 (the last tile hangs over the next expert)
     ([256, 128, 128, 0, 0, 512, 128, 128], 768, 2048),   # Qwen3-30B-A3B down projection

@@ -442,7 +442,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
 }  // namespace gpair
 
 bool g_attr = false;
-bool g_grouped_pair = false;   // tt_grouped_gemm_set_pair(1) turns the CTA-pair kernel on
+bool g_grouped_pair = true;
 
 void set_attrs() {
   if (g_attr) return;

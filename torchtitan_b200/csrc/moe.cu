@@ -217,7 +217,7 @@ __global__ void gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __
   const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= R) return;
-  const int s = src[row];
+  const int s = src ? src[row] : static_cast<int>(row);   // no index: rows in place (a plain per-row scaling)
   const float sc = scale ? scale[row] : 1.f;
   for (int c = lane; c < D / 8; c += 32) {
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -262,7 +262,7 @@ __global__ void rowdot_kernel(const __nv_bfloat16* __restrict__ rows, const int*
   const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (i >= TK) return;
-  const int p = pos[i];
+  const int p = pos ? pos[i] : static_cast<int>(i);       // no index: row i against row i / K of g
   float acc = 0.f;
   if (p >= 0) {
     const long long t = i / K;

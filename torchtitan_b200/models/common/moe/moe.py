@@ -108,6 +108,10 @@ class LocalDispatcher:
 
     def scale_rows(self, rows, scores_sorted, ctx):
         sc = rows.new_zeros(ctx["max_rows"], 1, dtype=torch.float32).index_copy(0, ctx["dest"], scores_sorted.reshape(-1, 1).float())
+        if rows.is_cuda:
+            from torchtitan_b200.ops.cuda_ops import scale_rows
+
+            return scale_rows(rows, sc)
         return (rows.float() * sc).to(rows.dtype)
 
     def combine(self, y, ctx):

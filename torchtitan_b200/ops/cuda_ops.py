@@ -783,6 +783,40 @@ class _CombinePos(torch.autograd.Function):
         return grows, None, None, gw, None, None
 
 
+class _ScaleRowsFn(torch.autograd.Function):
+    """``out[r, :] = rows[r, :] * scale[r]`` (bf16 rows, fp32 scales, one pass). Backward: the same pass on the output
+    gradient and one row-dot kernel for the scales' gradient."""
+
+    @staticmethod
+    def forward(ctx, rows, scale):
+        R, D = rows.shape
+        out = torch.empty_like(rows)
+        _ck(_lib().tt_moe_gather(rows.data_ptr(), None, scale.data_ptr(), out.data_ptr(), R, D, _stream()), "tt_moe_gather(scale)")
+        ctx.save_for_backward(rows, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        rows, scale = ctx.saved_tensors
+        R, D = rows.shape
+        g = g.contiguous()
+        g_rows = g_scale = None
+        if ctx.needs_input_grad[0]:
+            g_rows = torch.empty_like(rows)
+            _ck(_lib().tt_moe_gather(g.data_ptr(), None, scale.data_ptr(), g_rows.data_ptr(), R, D, _stream()), "tt_moe_gather(scale)")
+        if ctx.needs_input_grad[1]:
+            g_scale = torch.empty(R, dtype=torch.float32, device=rows.device)
+            _ck(_lib().tt_moe_rowdot(rows.data_ptr(), None, g.data_ptr(), g_scale.data_ptr(), R, 1, D, _stream()), "tt_moe_rowdot")
+        return g_rows, g_scale
+
+
+def scale_rows(rows: Tensor, scale: Tensor) -> Tensor:
+    """Rows times one fp32 factor each. bf16 rows of a multiple of 8 elements take the fused kernels."""
+    if rows.is_cuda and rows.dtype == torch.bfloat16 and rows.dim() == 2 and rows.shape[1] % 8 == 0 and rows.is_contiguous():
+        return _ScaleRowsFn.apply(rows, scale.reshape(-1).to(torch.float32).contiguous())
+    return (rows.float() * scale.reshape(-1, 1)).to(rows.dtype)
+
+
 def moe_gather_src(x, src, pos, top_k: int):
     return _GatherSrc.apply(x.contiguous(), src, pos, top_k)
 

@@ -36,6 +36,10 @@ def gather_rows(x, order, top_k: int):
 def scale_rows(rows, scores_sorted, dispatcher=None, ctx=None):
     if ctx is not None and hasattr(dispatcher, "scale_rows"):
         return dispatcher.scale_rows(rows, scores_sorted, ctx)
+    if rows.is_cuda:
+        from . import cuda_ops
+
+        return cuda_ops.scale_rows(rows, scores_sorted)
     return (rows.to(torch.float32) * scores_sorted.reshape(-1, 1)).to(rows.dtype)
 
 

@@ -104,6 +104,10 @@ class AllToAllDispatcher:
         # scores travel with the rows: exchange and permute them the same way
         sc = all_to_all_rows(scores_sorted.reshape(-1, 1).float(), ctx["out_splits"], ctx["in_splits"], self.group)
         sc = torch.vstack((sc, sc.new_zeros(1, 1)))[ctx["perm"]]
+        if rows.is_cuda:
+            from torchtitan_b200.ops.cuda_ops import scale_rows
+
+            return scale_rows(rows, sc)
         return (rows.float() * sc).to(rows.dtype)
 
     def combine(self, y, ctx):

@@ -231,7 +231,9 @@ class NvlinkDispatcher:
             return self._fallback.scale_rows(rows, scores_sorted, ctx)
         sh8 = self._state(ctx["maps"]["n"], 8)
         sc = _ExchangeScores.apply(scores_sorted.reshape(-1).float(), ctx["maps"], sh8)       # [cap] fp32, 0 on padding
-        return (rows.float() * sc.unsqueeze(1)).to(rows.dtype)
+        from torchtitan_b200.ops.cuda_ops import scale_rows
+
+        return scale_rows(rows, sc)
 
     def combine(self, y, ctx):
         if ctx.get("fallback"):
