@@ -541,6 +541,36 @@ def test_mx_linear_op_matches_definition(ops, rows, K, N):
     # and close to the unquantised product (e4m3 keeps 3 mantissa bits)
     assert _rel(y.view(rows, N), xd.float() @ wd.float().t()) < 8e-2
 
+@pytest.mark.parametrize("weighted", [True, False])
+def test_moe_gather_and_combine_kernels_match_indexing(ops, weighted):
+    """Routed-token gather (``x[order // k]``) and the un-sort + sum over a token's k copies through the fused row kernels,
+    against plain indexing in fp32, with gradients; and the masked copy used to leave a communication buffer."""
+    torch.manual_seed(0)
+    T, k, D = 300, 4, 256
+    order = torch.randperm(T * k, device="cuda")
+    x = torch.randn(T, D, device="cuda").bfloat16().requires_grad_()
+    w = torch.rand(T, k, device="cuda").requires_grad_() if weighted else None
+    rows = ops.moe_gather_rows(x, order, k)
+    out = ops.moe_scatter_combine(rows * 1.0, order, w, T, k)
+    g = torch.randn_like(out)
+    out.backward(g)
+    _no_kernel_errors()
+    xf = x.detach().float().requires_grad_()
+    wf = w.detach().clone().requires_grad_() if weighted else None
+    rf = xf[order // k]
+    uns = torch.zeros(T * k, D, device="cuda").index_copy(0, order, rf).view(T, k, D)
+    ref = (uns * wf.unsqueeze(-1)).sum(1) if weighted else uns.sum(1)
+    ref.backward(g.float())
+    assert torch.equal(rows.detach(), x.detach()[order // k])
+    assert _rel(out, ref) < 1e-2 and _rel(x.grad, xf.grad) < 2e-2
+    if weighted:
+        assert _rel(w.grad, wf.grad) < 2e-2
+    keep = torch.rand(T * k, device="cuda") > 0.3
+    got = ops.copy_rows_where(rows.detach(), keep)
+    assert torch.equal(got, torch.where(keep.unsqueeze(1), rows.detach(), torch.zeros((), dtype=torch.bfloat16, device="cuda")))
+
+
+
 def test_scale_rows_fused(ops):
     """Rows times one fp32 factor each in one pass, with both gradients, against the fp32 definition."""
     torch.manual_seed(0)

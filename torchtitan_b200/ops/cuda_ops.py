@@ -825,11 +825,48 @@ def moe_combine_pos(rows, pos, pair, weights, num_tokens: int, top_k: int):
     return _CombinePos.apply(rows.contiguous(), pos, pair, weights, num_tokens, top_k)
 
 
+def inverse_positions(order: Tensor) -> Tensor:
+    """``pos`` with ``pos[order[j]] = j`` (int32): where each (token, slot) pair sits in the expert-sorted order."""
+    n = order.numel()
+    return torch.empty(n, dtype=torch.int32, device=order.device).index_copy_(
+        0, order, torch.arange(n, dtype=torch.int32, device=order.device))
+
+
+def _rows_kernel_ok(x: Tensor) -> bool:
+    return x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[-1] % 8 == 0
+
+
+def copy_rows_where(rows: Tensor, keep: Tensor) -> Tensor:
+    """A copy of ``rows`` [R, D] with the rows where ``keep`` [R] is false set to zero, in one vectorised pass (also the
+    copy out of a communication buffer that the next exchange overwrites)."""
+    R = rows.shape[0]
+    if not (_rows_kernel_ok(rows) and rows.is_contiguous()):
+        return torch.where(keep.unsqueeze(1), rows, torch.zeros((), dtype=rows.dtype, device=rows.device))
+    src = torch.where(keep, torch.arange(R, dtype=torch.int32, device=rows.device), torch.full((), -1, dtype=torch.int32, device=rows.device))
+    out = torch.empty_like(rows)
+    _ck(_lib().tt_moe_gather(rows.data_ptr(), src.data_ptr(), None, out.data_ptr(), R, rows.shape[1], _stream()), "tt_moe_gather(copy)")
+    return out
+
+
+def sum_copies(rows: Tensor, pos: Tensor, num_tokens: int, top_k: int) -> Tensor:
+    """``out[t] = sum_s rows[pos[t * k + s]]``: the gradient of a token from the gradients of its k routed copies."""
+    out = torch.empty(num_tokens, rows.shape[-1], dtype=rows.dtype, device=rows.device)
+    _ck(_lib().tt_moe_combine(rows.contiguous().data_ptr(), pos.data_ptr(), None, out.data_ptr(), num_tokens, top_k, rows.shape[-1],
+                              _stream()), "tt_moe_combine")
+    return out
+
+
 def moe_gather_rows(x, order, top_k: int):
+    if _rows_kernel_ok(x) and order.numel() == x.shape[0] * top_k:
+        return _GatherSrc.apply(x.contiguous(), (order // top_k).to(torch.int32), inverse_positions(order), top_k)
     return x[order // top_k]
 
 
 def moe_scatter_combine(rows, order, weights, num_tokens: int, top_k: int):
+    n = order.numel()
+    if _rows_kernel_ok(rows) and n == num_tokens * top_k:
+        # one pass: every token reads its k rows through the inverse of the sort and sums them (weighted) in fp32
+        return _CombinePos.apply(rows[:n].contiguous(), inverse_positions(order), order, weights, num_tokens, top_k)
     D = rows.shape[-1]
     unsorted = rows.new_zeros(num_tokens * top_k, D)
     unsorted[order] = rows[: order.numel()]

@@ -80,7 +80,12 @@ class AllToAllDispatcher:
         self.alignment, self.capacity_factor = alignment, capacity_factor
 
     def dispatch(self, x, order, counts, top_k: int):
-        rows = x[order // top_k]  # sorted by global expert => contiguous per destination rank
+        if x.is_cuda:
+            from torchtitan_b200.ops.cuda_ops import moe_gather_rows
+
+            rows = moe_gather_rows(x, order, top_k)   # sorted by global expert => contiguous per destination rank
+        else:
+            rows = x[order // top_k]
         counts = counts.to(torch.int64)
         recv_counts = torch.empty_like(counts)
         dist.all_to_all_single(recv_counts, counts, group=self.group)  # [src rank][local expert]

@@ -27,6 +27,24 @@ from torchtitan_b200.ops import native
 
 from .nvlink_comm import _PP, SymmetricHeap, _stream
 
+
+def copy_rows_where(rows, keep):
+    from torchtitan_b200.ops.cuda_ops import copy_rows_where as f
+
+    return f(rows, keep)
+
+
+def sum_copies(rows, pos, num_tokens, top_k):
+    from torchtitan_b200.ops.cuda_ops import sum_copies as f
+
+    return f(rows, pos, num_tokens, top_k)
+
+
+def inverse_positions(order):
+    from torchtitan_b200.ops.cuda_ops import inverse_positions as f
+
+    return f(order)
+
 _I32 = torch.int32
 
 
@@ -61,9 +79,9 @@ class _Exchange(torch.autograd.Function):
     returns [n, D]. Backward is the opposite direction."""
 
     @staticmethod
-    def forward(ctx, rows, in_index, maps, sh: _Shared, direction: str):
+    def forward(ctx, rows, in_index, maps, sh: _Shared, direction: str, pos=None, top_k: int = 0):
         ctx.maps, ctx.sh, ctx.direction = maps, sh, direction
-        ctx.in_index, ctx.in_rows = in_index, rows.shape[0]
+        ctx.in_index, ctx.in_rows, ctx.pos, ctx.top_k = in_index, rows.shape[0], pos, top_k
         return _exchange(rows, in_index, maps, sh, direction)
 
     @staticmethod
@@ -73,10 +91,12 @@ class _Exchange(torch.autograd.Function):
         out = _exchange(g.contiguous(), None, maps, sh, back)
         if ctx.direction == "fwd" and ctx.in_index is not None:
             # rows were gathered through in_index: add the gradients of the copies of each source row
+            if ctx.pos is not None and out.dtype == torch.bfloat16:
+                return sum_copies(out, ctx.pos, ctx.in_rows, ctx.top_k), None, None, None, None, None, None
             gx = g.new_zeros(ctx.in_rows, g.shape[-1])
             gx.index_add_(0, ctx.in_index.long(), out)
-            return gx, None, None, None, None
-        return out, None, None, None, None
+            return gx, None, None, None, None, None, None
+        return out, None, None, None, None, None, None
 
 
 class _ExchangeScores(torch.autograd.Function):
@@ -117,14 +137,13 @@ def _exchange(rows, in_index, maps, sh: _Shared, direction: str):
                                   maps["dst_rank"].data_ptr(), maps["dst_row"].data_ptr(), sh.recv[par]["peers"],
                                   arrive["peers"], W, sh.D, sh.cap, _stream()), "tt_ep_push")
         native.check(L.tt_ep_wait(arrive["ptr"], per_parity_calls * W * sh.ctas, _stream()), "tt_ep_wait")
-        valid = (maps["rev_rank"] >= 0).unsqueeze(1)
-        return torch.where(valid, sh.recv[par]["local"], torch.zeros((), dtype=torch.bfloat16, device=rows.device))
+        # copied out of the symmetric buffer (the exchange after next overwrites it), padding rows zeroed, in one pass
+        return copy_rows_where(sh.recv[par]["local"], maps["rev_rank"] >= 0)
     native.check(L.tt_ep_push(rows.data_ptr(), None, sh.cap, maps["rev_rank"].data_ptr(), maps["rev_row"].data_ptr(),
                               sh.ret[par]["peers"], arrive["peers"], W, sh.D, sh.n, _stream()), "tt_ep_push")
     native.check(L.tt_ep_wait(arrive["ptr"], per_parity_calls * W * sh.ctas, _stream()), "tt_ep_wait")
-    dropped = maps["dst_rank"] < 0                      # rows that did not fit a receive buffer come back as zeros
-    ret = sh.ret[par]["local"]                          # copied out of the symmetric buffer in the same pass
-    return torch.where(dropped.unsqueeze(1), torch.zeros((), dtype=ret.dtype, device=ret.device), ret)
+    # rows that did not fit a receive buffer come back as zeros; copied out of the symmetric buffer in the same pass
+    return copy_rows_where(sh.ret[par]["local"], maps["dst_rank"] >= 0)
 
 
 class NvlinkDispatcher:
@@ -219,7 +238,7 @@ class NvlinkDispatcher:
             ctx["fallback"] = True
             return rows, sizes, ctx
         src_index = (order // top_k).to(_I32).contiguous()
-        recv = _Exchange.apply(x.contiguous(), src_index, maps, sh, "fwd")
+        recv = _Exchange.apply(x.contiguous(), src_index, maps, sh, "fwd", inverse_positions(order), top_k)
         offs = maps["offs"].to(torch.int64)
         sizes = offs - torch.cat((offs.new_zeros(1), offs[:-1]))
         sizes._tt_aligned = self.alignment
