@@ -160,3 +160,37 @@ def test_trainer_raises_when_a_kernel_reports_an_expired_wait(monkeypatch):
         Trainer._raise_on_kernel_errors(fake)
     fake.device = torch.device("cpu")
     Trainer._raise_on_kernel_errors(fake)                         # CPU runs have no kernels to ask
+
+
+def _fold_worker(rank, world):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.parallel import fsdp
+    from torchtitan_b200.parallel.utils import clip_grad_norm_
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.ReLU(), torch.nn.Linear(20, 7))
+    pd = _pd(world)
+    fsdp.fully_shard(net[0], mesh=pd.get_mesh("fsdp"))
+    fsdp.fully_shard(net, mesh=pd.get_mesh("fsdp"))
+    fsdp.materialize(net)
+    for p in net[0].parameters():                 # as for expert-parallel shards: the norm needs one more group
+        p._extra_norm_groups = (dist.group.WORLD,)
+    net(torch.randn(5, 12)).square().sum().backward()
+    units = fsdp.fsdp_units(net)
+    for u in units:
+        u.wait_for_reduce()
+    before = [u.grad_shard_flat.clone() for u in units]
+    total = clip_grad_norm_(list(net.parameters()), 1e-3, fold_into_optimizer=True)
+    coef = min(1.0, 1e-3 / (float(total) + 1e-6))
+    return {"scales": [float(u.pending_grad_scale) for u in units], "coef": coef,
+            "untouched": all(torch.equal(a, u.grad_shard_flat) for a, u in zip(before, units))}
+
+
+def test_clip_coefficient_rides_into_the_flat_optimizer_for_every_unit(tmp_path):
+    """With the clip folded into the flat-shard optimizer no gradient is scaled in place, also for units whose parameters
+    carry extra norm groups (expert-parallel shards)."""
+    for o in run_ranks(_fold_worker, 2, tmp_path=tmp_path):
+        assert o["untouched"] and len(o["scales"]) == 2
+        assert all(s == pytest.approx(o["coef"], rel=1e-5) for s in o["scales"])

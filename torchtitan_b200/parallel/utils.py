@@ -304,6 +304,23 @@ def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, error_i
             unit.pending_grad_scale = coef
         else:
             unit.grad_shard_flat.mul_(coef.to(unit.grad_shard_flat.dtype))
+    if fold_into_optimizer and loose:
+        # parameters with extra norm groups (expert-parallel shards) are reduced one by one above, but when a unit's
+        # parameters are all of that kind and their gradients are the unit's flat gradient shard, the coefficient can
+        # still ride into the flat-shard optimizer instead of one scaling pass per gradient
+        by_unit: dict[int, list] = {}
+        for p in loose:
+            ref = getattr(p, "_tt_unit", None)
+            if ref is not None:
+                by_unit.setdefault(id(ref[0]), [ref[0], []])[1].append(p)
+        folded = set()
+        for unit, plist in by_unit.values():
+            owned = [q.param for q in unit.params if q.param.requires_grad]
+            if len(plist) == len(owned) and unit.grad_shard_flat is not None and all(
+                    _local(q.grad).untyped_storage().data_ptr() == unit.grad_shard_flat.untyped_storage().data_ptr() for q in plist):
+                unit.pending_grad_scale = coef
+                folded.update(id(q) for q in plist)
+        loose = [p for p in loose if id(p) not in folded]
     seen = set()
     for p in loose:
         g = _local(p.grad)
