@@ -71,10 +71,9 @@ class ShardAdamW(Optimizer):
 
     def _wrap_like(self, param, local):
         if isinstance(param, DTensor):
-            from torchtitan_b200.parallel.fsdp import _contig_stride
+            from torchtitan_b200.parallel.fsdp import _contig_stride, dtensor_over
 
-            return DTensor.from_local(local, param.device_mesh, param.placements, run_check=False,
-                                      shape=param.shape, stride=_contig_stride(param.shape))
+            return dtensor_over(local, param.device_mesh, param.placements, param.shape, _contig_stride(param.shape))
         return local
 
     def _init_state(self):
@@ -268,8 +267,10 @@ class OptimizersContainer(Optimizer, Stateful, Configurable):
                     p = sharded.get(fqn)
                     if p is not None and v.dim() > 0:
                         local = local_of(v)
-                        state_dict[k] = (DTensor.from_local(local, p.device_mesh, p.placements, run_check=False, shape=p.shape,
-                                                            stride=p.stride()) if isinstance(p, DTensor) else local)
+                        from torchtitan_b200.parallel.fsdp import dtensor_over
+
+                        state_dict[k] = (dtensor_over(local, p.device_mesh, p.placements, p.shape, p.stride())
+                                         if isinstance(p, DTensor) else local)
         fn = functools.partial(
             set_optimizer_state_dict, optim_state_dict=state_dict,
             options=StateDictOptions(flatten_optimizer_state_dict=True),

@@ -92,6 +92,17 @@ def _contig_stride(shape):
     return tuple(reversed(st))
 
 
+def dtensor_over(local: torch.Tensor, mesh, placements, shape, stride, keep_device: bool = False) -> DTensor:
+    """A DTensor whose local shard is ``local`` itself. ``DTensor.from_local`` moves the shard to the mesh's device type;
+    CPU-offloaded shards must stay in host memory under a CUDA mesh, so for them the DTensor is built from its spec."""
+    if not keep_device and (local.device.type == mesh.device_type or local.is_meta):
+        return DTensor.from_local(local, mesh, placements, run_check=False, shape=shape, stride=stride)
+    from torch.distributed.tensor._dtensor_spec import DTensorSpec, TensorMeta
+
+    spec = DTensorSpec(mesh, tuple(placements), tensor_meta=TensorMeta(torch.Size(shape), tuple(stride), local.dtype))
+    return DTensor(local, spec, requires_grad=local.requires_grad)
+
+
 class GradSlot:
     """Where a weight-gradient GEMM may write its result directly (skipping the autograd-owned
     temporary): the fp32 gradient shard itself when the shard world is one, or a bf16 slice of the
@@ -283,8 +294,7 @@ class FSDPUnit:
                 new_param = nn.Parameter(local, requires_grad=param.requires_grad)
             else:
                 placements = [local_pl] if mesh.ndim == 1 else [Replicate(), local_pl]
-                dt = DTensor.from_local(local, mesh, placements, run_check=False, shape=shape,
-                                        stride=_contig_stride(shape))
+                dt = dtensor_over(local, mesh, placements, shape, _contig_stride(shape))
                 new_param = nn.Parameter(dt, requires_grad=param.requires_grad)
             for k, v in param.__dict__.items():  # carry user annotations (e.g. TP placement tags)
                 if not k.startswith("__") and k not in ("_local_tensor", "_spec"):
@@ -682,9 +692,8 @@ class FSDPUnit:
             p = self.params[i]
             local = self._shard_view(self.grad_shard_flat, p)
             if isinstance(p.param, DTensor):
-                self._grad_dtensors[i] = DTensor.from_local(
-                    local, self.mesh, p.param.placements, run_check=False, shape=p.full_shape,
-                    stride=_contig_stride(p.full_shape))
+                self._grad_dtensors[i] = dtensor_over(local, self.mesh, p.param.placements, p.full_shape,
+                                                      _contig_stride(p.full_shape))
             else:
                 self._grad_dtensors[i] = local
         return self._grad_dtensors[i]
