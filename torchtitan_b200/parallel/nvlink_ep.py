@@ -4,7 +4,7 @@ read on the path. Drop-in for :class:`parallel.ep.AllToAllDispatcher` (same ``di
 
 The receive buffer has a fixed capacity (plus alignment padding). Two modes:
 
-* default (``capacity_factor=None``): lossless. The buffer holds twice the rows a rank sends; after the counts are
+* default (``capacity_factor=None``): lossless. The buffer holds three times the rows a rank sends; after the counts are
   exchanged every rank reads the (identical) count table on the host, and when any rank's experts would receive more
   than the buffer holds, this call goes through the all-to-all dispatcher instead. One small device-to-host read per
   dispatch, no token is ever dropped (what the reference's DeepEP backend guarantees by default);
@@ -158,7 +158,9 @@ class NvlinkDispatcher:
         self.num_experts, self.local_experts = num_experts, num_experts // self.ep
         self.alignment = alignment
         self.lossless = capacity_factor is None
-        self.capacity_factor = capacity_factor if capacity_factor is not None else 2.0
+        # lossless mode: room for three times the average load before a call has to take the collective path (with random
+        # weights single ranks see more than twice the average in the first steps)
+        self.capacity_factor = capacity_factor if capacity_factor is not None else 3.0
         self.heap_bytes = heap_bytes
         self.fallback_calls = 0
         self.device = torch.device("cuda", torch.cuda.current_device())
