@@ -48,9 +48,9 @@ class HFTransformerModel(BaseModel):
             if os.path.exists(cand):
                 self.hf_config_path = cand
             par = trainer_config.parallelism
-            if par.context_parallel_degree > 1:
-                raise NotImplementedError("context parallel is not available for wrapped Hugging Face models; "
-                                          "use FSDP / HSDP, tensor parallel and pipeline parallel")
+            if par.context_parallel_degree > 1 and par.pipeline_parallel_degree > 1:
+                raise NotImplementedError("context parallel and pipeline parallel are not combined for wrapped Hugging Face "
+                                          "models")
             if par.pipeline_parallel_degree > 1 and self.hf_config().tie_word_embeddings:
                 raise NotImplementedError("pipeline parallel cannot split a model whose output layer shares the embedding "
                                           "weights (tie_word_embeddings)")
@@ -116,6 +116,11 @@ class HFTransformerModel(BaseModel):
         return self.model.lm_head
 
     def forward(self, tokens, attention_masks=None, positions=None):
+        if self.__dict__.get("_call_parts_directly"):
+            # context parallel: this rank holds a shard of the sequence, so the Hugging Face top-level forward (which
+            # builds a causal mask for the local length) is bypassed; the layers call the registered ring attention
+            dec = self._decoder
+            return _run_parts(dec.embed_tokens, dec.layers, dec.norm, self.model.lm_head, dec.rotary_emb, tokens, positions)
         kw = {}
         if positions is not None:
             kw["position_ids"] = positions.long()
@@ -141,6 +146,22 @@ def _init_hf_weights(root: nn.Module, init_fn=None) -> None:
             if hasattr(m, "original_inv_freq"):
                 m.original_inv_freq = m.inv_freq
     root.apply(init_fn or root._init_weights)
+
+
+def _run_parts(embed, layers, norm, head, rotary, x, positions):
+    """Embedding (if present) -> decoder layers with the architecture's rotary tables -> norm / head (if present). The
+    layers get no mask: their attention function runs causal."""
+    h = embed(x) if embed is not None else x
+    pos = positions.long() if positions is not None else torch.arange(h.shape[1], device=h.device).unsqueeze(0)
+    rope = rotary(h, pos)
+    for layer in layers:
+        out = layer(h, attention_mask=None, position_ids=pos, position_embeddings=rope, use_cache=False)
+        h = out[0] if isinstance(out, tuple) else out
+    if norm is not None:
+        h = norm(h)
+    if head is not None:
+        h = head(h)
+    return h
 
 
 class _Shell(nn.Module):
@@ -196,17 +217,7 @@ class HFPipelineStage(nn.Module):
 
     def forward(self, x, attention_masks=None, positions=None):
         dec = self.model.model
-        h = dec.embed_tokens(x) if dec.embed_tokens is not None else x
-        pos = positions.long() if positions is not None else torch.arange(h.shape[1], device=h.device).unsqueeze(0)
-        rope = dec.rotary_emb(h, pos)
-        for layer in dec.layers.values():
-            out = layer(h, attention_mask=None, position_ids=pos, position_embeddings=rope, use_cache=False)
-            h = out[0] if isinstance(out, tuple) else out
-        if dec.norm is not None:
-            h = dec.norm(h)
-        if self.model.lm_head is not None:
-            h = self.model.lm_head(h)
-        return h
+        return _run_parts(dec.embed_tokens, dec.layers.values(), dec.norm, self.model.lm_head, dec.rotary_emb, x, positions)
 
     def init_weights(self, *args, **kwargs):
         _init_hf_weights(self.model, self._init_fn)      # the architecture's initialiser, on this stage's modules

@@ -91,10 +91,56 @@ def apply_tp_to_hf_decoder(model: nn.Module, tp_mesh) -> None:
     logger.info(f"Applied tensor parallel (degree {W}) to the wrapped Hugging Face model")
 
 
+_RING_NAME = "tt_ring_attention"
+_rings: dict = {}
+
+
+def _ring_attention_fn(module, query, key, value, attention_mask=None, dropout=0.0, scaling=None, **kwargs):
+    """Attention function in the Hugging Face calling convention (``query`` [B, H, S, D], returns [B, S, H, D]) that runs
+    this framework's context-parallel attention over the sequence shards."""
+    ring = _rings[id(module.config)]
+    out = ring(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), scale=scaling)
+    return out.contiguous(), None
+
+
+def apply_cp_to_hf_decoder(model: nn.Module, cp_mesh, rotate_method: str, load_balancer) -> None:
+    """Context parallel for a wrapped decoder: the sequence is sharded head-tail by the trainer (inputs, labels, positions);
+    rotary embeddings follow the explicit positions; every layer's attention goes through ``RingAttention`` (registered
+    with Hugging Face's attention interface), and the model runs its parts directly instead of the top-level forward.
+    Plain causal attention only. Reference: torchtitan/experiments/transformers_modeling_backend/parallelize.py (its
+    context-parallel plan)."""
+    from transformers.modeling_utils import AttentionInterface
+
+    from torchtitan_b200.parallel.cp import RingAttention
+
+    cfg = model.hf_config
+    if getattr(cfg, "layer_types", None) and any(t != "full_attention" for t in cfg.layer_types):
+        raise NotImplementedError("context parallel for wrapped models covers plain causal attention; this architecture "
+                                  "mixes sliding-window layers")
+    AttentionInterface.register(_RING_NAME, _ring_attention_fn)
+    try:
+        from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
+
+        AttentionMaskInterface.register(_RING_NAME, sdpa_mask)
+    except ImportError:
+        pass
+    ring = RingAttention(cp_mesh, rotate_method, load_balancer)
+    from transformers import PretrainedConfig
+
+    for c in {id(m.config): m.config for m in model.modules() if isinstance(getattr(m, "config", None), PretrainedConfig)}.values():
+        c._attn_implementation = _RING_NAME
+        _rings[id(c)] = ring
+    model.__dict__["_call_parts_directly"] = True
+    logger.info(f"Applied context parallel (degree {cp_mesh.size()}) to the wrapped Hugging Face model")
+
+
 def parallelize_hf_transformers(model: nn.Module, *, parallel_dims, training, model_converters, parallelism, compile_config,
                                 ac_config, dump_folder: str):
     if parallel_dims.tp_enabled:
         apply_tp_to_hf_decoder(model, parallel_dims.get_mesh("tp"))
+    if parallel_dims.cp_enabled:
+        apply_cp_to_hf_decoder(model, parallel_dims.get_mesh("cp"), parallelism.context_parallel_rotate_method,
+                               parallelism.context_parallel_load_balancer)
     layers = list(model.layers.values())
     if ac_config.mode == "full":
         for layer in layers:
