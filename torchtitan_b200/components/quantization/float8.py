@@ -77,6 +77,12 @@ class Float8LinearConverter(QuantizationConverter):
             self.fp8_all_gather = parallel_dims.dp_shard_enabled and config.enable_fsdp_float8_all_gather
             self.precompute_scale = self.fp8_all_gather and config.precompute_float8_dynamic_scale_for_fsdp
             logger.info("Float8 tensorwise scaled training active")
+            if self.fp8_all_gather:
+                # said at start-up: the FSDP runtime gathers the bf16 compute copy of a shard (written by the fused
+                # AdamW in the same pass as the fp32 master) and the linears quantise after the gather
+                logger.warning("float8.enable_fsdp_float8_all_gather has no effect in this runtime: parameters are gathered "
+                               "in bf16 (the gather of the next unit runs on a side stream behind the current unit's compute); "
+                               "precompute_float8_dynamic_scale_for_fsdp is ignored with it")
         self.recipe = QuantRecipe(kind="float8", scaling=recipe, emulate=config.emulate)
         self.enabled = True
 
@@ -91,21 +97,10 @@ class Float8LinearConverter(QuantizationConverter):
         logger.info(f"Float8 ({self.recipe.scaling}) enabled on {n} linear layers, float8 all-gather={self.fp8_all_gather}")
 
     def post_optimizer_hook(self, model: nn.Module | list[nn.Module]):
-        """Tensorwise + float8 all-gather: refresh every converted weight's amax in one pass after
-        the optimizer step so the next gather can quantise without a second reduction."""
-        if not (self.enabled and self.precompute_scale):
-            return
-        for m in [model] if isinstance(model, nn.Module) else model:
-            ws = [mod.weight for mod in m.modules() if getattr(mod, "quant", None) is self.recipe]
-            if not ws:
-                continue
-            locs = [w.to_local() if hasattr(w, "to_local") else w for w in ws]
-            amax = torch.stack([t.detach().abs().amax().float() if t.numel() else t.new_zeros((), dtype=torch.float32)
-                                for t in locs])
-            if torch.distributed.is_initialized() and hasattr(ws[0], "device_mesh"):
-                torch.distributed.all_reduce(amax, op=torch.distributed.ReduceOp.MAX, group=ws[0].device_mesh.get_group())
-            for mod_w, a in zip(ws, amax):
-                mod_w._fp8_amax = a
+        """The reference refreshes every converted weight's amax here for its float8 all-gather
+        (torchtitan/components/quantization/float8.py:104-128). Parameters are gathered in bf16 in this runtime and
+        each linear takes the amax of the gathered weight when it quantises, so there is nothing to precompute."""
+        return
 
 
 class Float8GroupedMMConverter(QuantizationConverter):

@@ -212,6 +212,9 @@ class Trainer(Stateful, Configurable):
                 self._materialize(m)
             ensure_pp_loss_visible(pd, config.parallelism.pipeline_parallel_schedule, color)
         else:
+            from torchtitan_b200.ops.wgrad_store import WeightGradStore
+
+            WeightGradStore.enabled = False      # a pipeline job built earlier in this process may have left it on
             model = spec.parallelize_fn(
                 model, parallel_dims=pd, training=config.training, model_converters=config.model_converters,
                 parallelism=config.parallelism, compile_config=config.compile, ac_config=config.activation_checkpoint,
