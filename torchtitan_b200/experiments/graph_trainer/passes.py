@@ -5,8 +5,8 @@ Names follow torchtitan/experiments/graph_trainer/passes.py:38-408. Each pass re
 into settings of the FSDP runtime that the job really runs with: ``parallelism.fsdp_bucket_bytes`` (auto bucketing:
 consecutive blocks grouped into one unit), ``fsdp_prefetch_depth`` (units gathered ahead), ``fsdp_reshard_after_forward``,
 ``fsdp_extra_process_group`` (all-gathers on their own communicator with the c10d transport), per-op activation
-checkpointing (``apply_sac``) and CUDA-graph capture of the step (``cudagraph``). ``simple_fsdp.data_parallel`` applies the
-same plan to a bare module (the reference's entry point of that name)."""
+checkpointing (``apply_sac``) and CUDA-graph capture of the step (``cudagraph``). ``simple_fsdp.py`` lists the bucket
+layouts the two bucketing passes stand for."""
 
 from __future__ import annotations
 

@@ -1,18 +1,14 @@
-"""Data parallel modes of the graph trainer on top of the framework's FSDP runtime.
+"""Bucket layouts of the graph trainer's data parallelism.
 
 The reference implements ``replicate`` / ``fully_shard`` / ``hybrid_shard`` as DTensor parametrisations that a
 compiler later buckets and reorders (torchtitan/experiments/graph_trainer/simple_fsdp.py:28-317). Here the three modes
-select meshes for the same flat-buffer runtime, and the plan decides how parameters are bucketed into units."""
+are the meshes of the framework's flat-buffer FSDP runtime (chosen by the parallelism degrees, as for every trainer),
+and what the compiler passes decide is how blocks are grouped into units: ``GraphTrainer`` hands the plan's bucket size
+to ``parallel/data_parallel.py::apply_fsdp``, which groups consecutive blocks the way :func:`auto_buckets` lists them."""
 
 from __future__ import annotations
 
-import torch
 import torch.nn as nn
-
-from torchtitan_b200.parallel import fsdp
-from torchtitan_b200.parallel.fsdp import MixedPrecisionPolicy
-
-from .passes import StepPlan
 
 
 def get_transformer_block_buckets(model: nn.Module) -> list[list[str] | str]:
@@ -46,23 +42,3 @@ def auto_buckets(model: nn.Module, bucket_bytes: int, elem_size: int = 2) -> lis
     if tail:
         out.append(tail)
     return out
-
-
-def data_parallel(model: nn.Module, mesh, mode: str = "fully_shard", mp_policy: MixedPrecisionPolicy | None = None,
-                  plan: StepPlan | None = None) -> nn.Module:
-    assert mode in ("replicate", "fully_shard", "hybrid_shard"), f"Unsupported mode {mode}"
-    plan = plan or StepPlan()
-    mp = mp_policy or MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
-    if mode == "replicate":
-        fsdp.replicate(model, mesh=mesh, mp_policy=mp)
-        return model
-    if mode == "hybrid_shard":
-        assert mesh.ndim == 2, "hybrid_shard needs a (replicate, shard) mesh"
-    raf = {"default": None, "always": True, "never": False}[plan.reshard_after_forward]
-    buckets = auto_buckets(model, plan.bucket_bytes) if plan.bucketing == "auto" else get_transformer_block_buckets(model)
-    for b in buckets:
-        mods = [model.get_submodule(n) for n in ([b] if isinstance(b, str) else b)]
-        fsdp.fully_shard(mods if len(mods) > 1 else mods[0], mesh=mesh, mp_policy=mp,
-                         reshard_after_forward=True if raf is None else raf)
-    fsdp.fully_shard(model, mesh=mesh, mp_policy=mp, reshard_after_forward=True if raf is None else raf)
-    return model
