@@ -423,3 +423,31 @@ def test_bucketed_units_prefetch_depth_and_gather_group_keep_the_numbers(tmp_pat
     assert base[2] == {1} and big[2] == {2}
     assert big[0] == pytest.approx(base[0], rel=1e-6) and pg[0] == pytest.approx(base[0], rel=1e-6)
     assert base[0][1] != base[0][0]                              # the optimizer steps in between did change the model
+
+
+def _dtensor_worker(rank, world):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.parallel.fsdp import dtensor_over
+
+    mesh = init_device_mesh("cpu", (world,), mesh_dim_names=("fsdp",))
+    local = torch.arange(6, dtype=torch.float32).view(2, 3) + 10 * rank
+    shape, stride = (2 * world, 3), (3, 1)
+    kept = dtensor_over(local, mesh, [Shard(0)], shape, stride, keep_device=True)      # the path host-resident shards take
+    moved = dtensor_over(local, mesh, [Shard(0)], shape, stride)
+    same_storage = kept._local_tensor.data_ptr() == local.data_ptr()
+    p = torch.nn.Parameter(kept)
+    p.grad = dtensor_over(torch.ones(2, 3), mesh, [Shard(0)], shape, stride, keep_device=True)
+    torch.optim.AdamW([p], lr=0.1, foreach=True).step()
+    return {"equal": torch.equal(kept.full_tensor(), moved.full_tensor()), "same_storage": same_storage,
+            "shape": tuple(kept.shape), "stepped": bool((p.to_local() != 10 * rank + torch.arange(6.0).view(2, 3)).any())}
+
+
+def test_dtensor_built_from_its_spec_matches_from_local(tmp_path):
+    """Host-resident shards under a device mesh of another type are wrapped without ``DTensor.from_local`` (which would
+    move them): same global tensor, same storage, usable as a parameter with a gradient and an optimizer."""
+    for o in run_ranks(_dtensor_worker, 2, tmp_path=tmp_path):
+        assert o["equal"] and o["same_storage"] and o["shape"] == (4, 3) and o["stepped"]
