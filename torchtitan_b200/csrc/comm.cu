@@ -21,7 +21,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "protocol.h"
+
 namespace {
+
+using tt::proto::now_ns;
+using tt::proto::st_release_sys;
 
 #ifndef TT_COMM_WAIT_NS
 #define TT_COMM_WAIT_NS 20000000000ull  // 20 s: peers may legitimately lag by a whole (first) step
@@ -42,20 +47,6 @@ struct Seg {            // one parameter of a unit
   long long chunk;      // elements per rank chunk (unpadded rows * inner)
 };
 
-__device__ __forceinline__ uint64_t now_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
 // Thread 0 of the block waits until every peer's flag >= expected; result broadcast through smem.
 __device__ bool wait_peers(const Peers& peers, int world, int expected, int* ok_smem) {
   if (threadIdx.x == 0) {
@@ -64,15 +55,11 @@ __device__ bool wait_peers(const Peers& peers, int world, int expected, int* ok_
     for (int r = 0; r < world && ok; ++r) {
       if (peers.flag[r] == nullptr) continue;
       int seen;
-      while ((seen = ld_acquire_sys(peers.flag[r])) < expected) {
-        if (now_ns() - t0 > g_comm_wait_ns) {
-          if (atomicCAS(&g_comm_error[0], 0, 1) == 0) {
-            g_comm_error[1] = r; g_comm_error[2] = expected; g_comm_error[3] = seen;
-          }
-          ok = 0;
-          break;
+      if (!tt::proto::wait_flag_ge(peers.flag[r], expected, t0, g_comm_wait_ns, &seen)) {
+        if (atomicCAS(&g_comm_error[0], 0, 1) == 0) {
+          g_comm_error[1] = r; g_comm_error[2] = expected; g_comm_error[3] = seen;
         }
-        __nanosleep(500);
+        ok = 0;
       }
     }
     *ok_smem = ok;
