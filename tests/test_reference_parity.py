@@ -263,3 +263,39 @@ def test_hf_state_dict_adapters_match_the_reference_adapters(family, flavor):
     assert set(back_ours) == set(back_ref)
     for k, v in back_ref.items():
         assert torch.equal(back_ours[k], v) and torch.equal(v, state[k]), k
+
+
+def _config_tree(cls_or_obj, prefix="", out=None, depth=0):
+    out = {} if out is None else out
+    if depth > 6:
+        return out
+    for f in dataclasses.fields(cls_or_obj):
+        value = None
+        if f.default is not dataclasses.MISSING:
+            value = f.default
+        elif f.default_factory is not dataclasses.MISSING:
+            try:
+                value = f.default_factory()
+            except Exception:
+                value = None
+        if dataclasses.is_dataclass(value) and not isinstance(value, type):
+            _config_tree(value, prefix + f.name + ".", out, depth + 1)
+        else:
+            out[prefix + f.name] = value
+    return out
+
+
+def test_every_job_option_of_the_reference_exists_with_the_same_default():
+    """The trainer's configuration tree (what ``--section.option`` flags and job configurations address): no option of
+    the reference is missing and none has another default; options that only exist here are additions."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from torchtitan.trainer import Trainer as RefTrainer
+
+    from torchtitan_b200.trainer import Trainer
+
+    ref, ours = _config_tree(RefTrainer.Config), _config_tree(Trainer.Config)
+    assert sorted(set(ref) - set(ours)) == []
+    different = {k: (ref[k], ours[k]) for k in ref if not callable(ref[k]) and ref[k] != ours[k]}
+    assert different == {}
+    assert len(ref) > 100                                   # the walk really saw the whole tree
