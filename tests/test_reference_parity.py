@@ -299,3 +299,25 @@ def test_every_job_option_of_the_reference_exists_with_the_same_default():
     different = {k: (ref[k], ours[k]) for k in ref if not callable(ref[k]) and ref[k] != ours[k]}
     assert different == {}
     assert len(ref) > 100                                   # the walk really saw the whole tree
+
+
+@pytest.mark.parametrize("family", ["llama3", "llama4", "qwen3", "deepseek_v3", "gpt_oss", "flux"])
+def test_job_configurations_and_flavors_of_the_reference_exist(family):
+    """Every job configuration function and every model flavor the reference registers for a family is registered here
+    under the same name (``--module <family> --config <name>`` keeps working)."""
+    import importlib
+    import inspect
+
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    ref_reg = importlib.import_module(f"torchtitan.models.{family}.config_registry")
+    our_reg = importlib.import_module(f"torchtitan_b200.models.{family}.config_registry")
+    ref_jobs = {n for n, f in vars(ref_reg).items()
+                if inspect.isfunction(f) and f.__module__ == ref_reg.__name__ and not n.startswith("_")}
+    our_jobs = {n for n, f in vars(our_reg).items() if inspect.isfunction(f) and not n.startswith("_")}
+    assert sorted(ref_jobs - our_jobs) == []
+    ref_mod, our_mod = importlib.import_module(f"torchtitan.models.{family}"), importlib.import_module(f"torchtitan_b200.models.{family}")
+    names = [a for a in dir(ref_mod) if a.endswith("_configs")]
+    if names:
+        ours = next(a for a in dir(our_mod) if a.endswith("_configs"))
+        assert sorted(set(getattr(ref_mod, names[0])) - set(getattr(our_mod, ours))) == []
