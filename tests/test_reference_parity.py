@@ -321,3 +321,31 @@ def test_job_configurations_and_flavors_of_the_reference_exist(family):
     if names:
         ours = next(a for a in dir(our_mod) if a.endswith("_configs"))
         assert sorted(set(getattr(ref_mod, names[0])) - set(getattr(our_mod, ours))) == []
+
+
+def test_flux_debug_flavor_matches_the_reference_model():
+    """``flux-debug`` has the reference's dimensions (same parameter names and shapes) and, with the same weights, gives
+    the same velocity field as the reference's FLUX model (fp32, CPU)."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from torchtitan.models.flux import flux_configs as ref_configs
+
+    from torchtitan_b200.models.flux import flux_configs
+
+    cfg = flux_configs["flux-debug"]
+    torch.manual_seed(0)
+    ours = cfg.build()
+    ours.init_weights()
+    torch.nn.init.normal_(ours.final_layer.linear.weight, std=0.02)      # the zero-initialised last layer would hide everything
+    ref = ref_configs["flux-debug"].build()
+    state = ours.state_dict()
+    assert set(state) == set(ref.state_dict()) and all(v.shape == ref.state_dict()[k].shape for k, v in state.items())
+    ref.load_state_dict(state)
+    B, L, T = 2, 16, 8
+    ids = torch.zeros(B, L, 3)
+    ids[..., 1], ids[..., 2] = torch.arange(L).view(1, L) // 4, torch.arange(L).view(1, L) % 4
+    kw = dict(img=torch.randn(B, L, 64), img_ids=ids, txt=torch.randn(B, T, cfg.context_in_dim), txt_ids=torch.zeros(B, T, 3),
+              timesteps=torch.rand(B), y=torch.randn(B, cfg.vec_in_dim))
+    with torch.no_grad():
+        a, b = ours(**kw), ref(**kw)
+    assert b.abs().max() > 0.1 and (a - b).abs().max().item() <= 1e-5 * b.abs().max().item()
