@@ -349,3 +349,26 @@ def test_flux_debug_flavor_matches_the_reference_model():
     with torch.no_grad():
         a, b = ours(**kw), ref(**kw)
     assert b.abs().max() > 0.1 and (a - b).abs().max().item() <= 1e-5 * b.abs().max().item()
+
+
+@pytest.mark.parametrize("family", ["llama3", "llama4", "qwen3", "deepseek_v3", "gpt_oss", "flux"])
+def test_every_flavor_has_the_reference_parameters(family):
+    """Built on the meta device, every flavor of a family (debug models up to Llama-3.1-405B, DeepSeek-V3 671B, Qwen3
+    235B-A22B, GPT-OSS 120b, FLUX dev) has exactly the parameter and buffer names and shapes of the reference's model, so
+    checkpoints of either framework fit the other."""
+    import importlib
+
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+
+    def configs(mod):
+        return getattr(mod, next(a for a in dir(mod) if a.endswith("_configs")))
+
+    ours = configs(importlib.import_module(f"torchtitan_b200.models.{family}"))
+    ref = configs(importlib.import_module(f"torchtitan.models.{family}"))
+    for flavor in ref:
+        with torch.device("meta"):
+            a, b = ours[flavor].build().state_dict(), ref[flavor].build().state_dict()
+        assert set(a) == set(b), (family, flavor, sorted(set(a) ^ set(b))[:4])
+        wrong = [(k, tuple(a[k].shape), tuple(b[k].shape)) for k in a if a[k].shape != b[k].shape]
+        assert not wrong, (family, flavor, wrong[:3])
