@@ -372,3 +372,35 @@ def test_every_flavor_has_the_reference_parameters(family):
         assert set(a) == set(b), (family, flavor, sorted(set(a) ^ set(b))[:4])
         wrong = [(k, tuple(a[k].shape), tuple(b[k].shape)) for k in a if a[k].shape != b[k].shape]
         assert not wrong, (family, flavor, wrong[:3])
+
+
+def test_tokenizer_and_text_dataloader_give_the_reference_batches():
+    """Same token ids as the reference's tokenizer wrapper (begin / end tokens, unicode, empty text) and, on the checked-in
+    C4 sample, the same packed batches per data-parallel rank and the same loader state keys."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from torchtitan.components.tokenizer import HuggingFaceTokenizer as RefTokenizer
+    from torchtitan.hf_datasets.text_datasets import HuggingFaceTextDataLoader as RefLoader
+
+    from torchtitan_b200.components.tokenizer import HuggingFaceTokenizer
+    from torchtitan_b200.hf_datasets.text_datasets import HuggingFaceTextDataLoader
+
+    assets = os.path.join(_HERE, "assets")
+    ours_tok = HuggingFaceTokenizer(tokenizer_path=os.path.join(assets, "tokenizer"))
+    ref_tok = RefTokenizer(tokenizer_path=os.path.join(assets, "tokenizer"))
+    assert (ours_tok.get_vocab_size(), ours_tok.bos_id, ours_tok.eos_id) == (ref_tok.get_vocab_size(), ref_tok.bos_id, ref_tok.eos_id)
+    for text in ["Hello world! 123", "  leading spaces\nand a newline\ttab", "ünïcödé 你好 🙂", ""]:
+        for kw in (dict(add_bos=True, add_eos=True), dict(add_bos=False, add_eos=False), dict(add_bos=True, add_eos=False)):
+            assert ours_tok.encode(text, **kw) == ref_tok.encode(text, **kw), (text, kw)
+        assert ours_tok.decode(ours_tok.encode(text)) == ref_tok.decode(ref_tok.encode(text))
+    data = os.path.join(assets, "c4_test")
+    for world in (1, 2):
+        for rank in range(world):
+            kw = dict(dp_world_size=world, dp_rank=rank, seq_len=128, local_batch_size=2)
+            ours = HuggingFaceTextDataLoader(HuggingFaceTextDataLoader.Config(dataset="c4_test", dataset_path=data), tokenizer=ours_tok, **kw)
+            ref = RefLoader(RefLoader.Config(dataset="c4_test", dataset_path=data), tokenizer=ref_tok, **kw)
+            a, b = iter(ours), iter(ref)
+            for _ in range(6):
+                (xa, ya), (xb, yb) = next(a), next(b)
+                assert torch.equal(xa["input"], xb["input"]) and torch.equal(ya, yb), (world, rank)
+            assert sorted(ours.state_dict()) == sorted(ref.state_dict())
