@@ -404,3 +404,26 @@ def test_tokenizer_and_text_dataloader_give_the_reference_batches():
                 (xa, ya), (xb, yb) = next(a), next(b)
                 assert torch.equal(xa["input"], xb["input"]) and torch.equal(ya, yb), (world, rank)
             assert sorted(ours.state_dict()) == sorted(ref.state_dict())
+
+
+def test_pipeline_stage_layouts_match_the_reference():
+    """Automatic stage layouts (which layers, embedding and output go to which stage) for 1 - 8 stages, 1 - 39 layers and
+    input / output weights 0 - 2: the same lists as the reference's function, and an error exactly where it raises."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from torchtitan.distributed.pipeline_parallel import generate_llm_fqn_per_model_part as ref_layout
+
+    from torchtitan_b200.parallel.pp import generate_llm_fqn_per_model_part as our_layout
+
+    def run(fn, *a):
+        try:
+            return fn(*a)
+        except ValueError:
+            return "error"
+
+    for stages in range(1, 9):
+        for layers in range(1, 40):
+            for in_w in (0, 1, 2):
+                for out_w in (0, 1, 2):
+                    assert run(our_layout, stages, layers, in_w, out_w) == run(ref_layout, stages, layers, in_w, out_w), \\
+                        (stages, layers, in_w, out_w)

@@ -62,6 +62,8 @@ def generate_llm_fqn_per_model_part(num_stages: int, num_layers: int, input_weig
     base, extra = divmod(effective, num_stages)
     if base <= input_weight and num_stages > 1 and base < input_weight:
         raise ValueError(f"Not enough layers for the first stage: {base} per stage vs input weight {input_weight}")
+    if output_weight > base:
+        raise ValueError(f"output_weight ({output_weight}) exceeds minimum layers per stage ({base}).")
     out, cur = [], 0
     for s in range(num_stages):
         budget = base + (1 if s < extra else 0)
