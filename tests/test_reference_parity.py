@@ -425,5 +425,5 @@ def test_pipeline_stage_layouts_match_the_reference():
         for layers in range(1, 40):
             for in_w in (0, 1, 2):
                 for out_w in (0, 1, 2):
-                    assert run(our_layout, stages, layers, in_w, out_w) == run(ref_layout, stages, layers, in_w, out_w), \\
-                        (stages, layers, in_w, out_w)
+                    case = (stages, layers, in_w, out_w)
+                    assert run(our_layout, *case) == run(ref_layout, *case), case
