@@ -427,3 +427,25 @@ def test_pipeline_stage_layouts_match_the_reference():
                 for out_w in (0, 1, 2):
                     case = (stages, layers, in_w, out_w)
                     assert run(our_layout, *case) == run(ref_layout, *case), case
+
+
+@pytest.mark.parametrize("family", ["llama3", "llama4", "qwen3", "deepseek_v3", "gpt_oss"])
+def test_parameter_and_flop_counts_match_the_reference(family):
+    """The numbers behind the MFU / TFLOPs log line (parameters, FLOPs per token at sequence length 4096) equal the
+    reference's for every flavor: dense, tied-embedding and mixture-of-experts (active parameters) formulas."""
+    import importlib
+
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+
+    def configs(mod):
+        return getattr(mod, next(a for a in dir(mod) if a.endswith("_configs")))
+
+    ours = configs(importlib.import_module(f"torchtitan_b200.models.{family}"))
+    ref = configs(importlib.import_module(f"torchtitan.models.{family}"))
+    for flavor in ref:
+        with torch.device("meta"):
+            a, b = ours[flavor].build(), ref[flavor].build()
+        na, fa = ours[flavor].get_nparams_and_flops(a, 4096)
+        nb, fb = ref[flavor].get_nparams_and_flops(b, 4096)
+        assert na == nb and abs(fa - fb) <= 1e-9 * fb, (family, flavor, (na, fa), (nb, fb))

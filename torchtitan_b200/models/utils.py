@@ -17,13 +17,14 @@ def _numel(p) -> int:
 def get_dense_model_nparams_and_flops(model_config, model: nn.Module, n_heads: int, head_dims: int, seq_len: int):
     nparams = sum(_numel(p) for p in model.parameters())
     nparams_emb = sum(
-        sum(_numel(p) for p in m.parameters()) for m in model.modules() if isinstance(m, nn.Embedding)
+        sum(_numel(p) for p in m.parameters()) for m in model.children() if isinstance(m, nn.Embedding)
     )
     flops = 6 * (nparams - nparams_emb) + 6 * model_config.n_layers * n_heads * head_dims * seq_len
     if getattr(model_config, "enable_weight_tying", False):
-        # the tied output projection still does a matmul per token
-        nparams = nparams  # parameters are shared, counted once by .parameters()
-        flops += 6 * nparams_emb
+        # the reference's convention (torchtitan/models/utils.py:389-437): with tied embeddings the shared matrix is left
+        # out of the reported parameter count and the output projection's matmul is not added to the FLOPs, so throughput
+        # and MFU lines are comparable between the two frameworks
+        nparams = nparams - nparams_emb
     return nparams, flops
 
 
