@@ -23,6 +23,9 @@ class OverrideDefinitions:
     """The case exercises a CUDA-only path (float8 / MXFP8 kernels, peer-memory collectives): skipped on CPU runs."""
     module: str = "llama3"
     config: str = "llama3_debugmodel"
+    env: Sequence[dict] = ()
+    """Extra environment of override set ``i`` (``env[i]``), e.g. ``{"TRAIN_FILE": ...}`` to launch another entry point
+    such as the FLUX inference script on the checkpoint the first set saved."""
 
     def __repr__(self) -> str:
         return self.test_descr

@@ -37,6 +37,8 @@ def suites() -> dict:
 def command(case: OverrideDefinitions, i: int, dump: str, extra: list[str]) -> tuple[dict, list[str]]:
     """Environment additions and argv of override set ``i``; ``{dump}`` in a flag expands to the case's dump folder."""
     env = {"NGPU": str(case.ngpu), "MODULE": case.module, "CONFIG": case.config, "LOG_RANK": "0"}
+    if i < len(case.env):
+        env.update(case.env[i])
     flags = [f.replace("{dump}", dump) for f in case.flags(i)]
     return env, [os.path.join(_REPO, "run_train.sh"), "--dump_folder", dump, *flags, *_without(extra, flags)]
 

@@ -119,7 +119,8 @@ def test_gpt_oss_debugmodel_step_sinks_window_and_adapter():
 
     cfg = dataclasses.replace(gptoss_configs["debugmodel"], n_layers=2)
     cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=64)
-    cfg.layer.attention = dataclasses.replace(cfg.layer.attention, n_heads=8, n_kv_heads=2, head_dim=32, sliding_window_size=8)
+    cfg.layer = dataclasses.replace(cfg.layer, attention=dataclasses.replace(   # replace, not assign: the registry's object is shared
+        cfg.layer.attention, n_heads=8, n_kv_heads=2, head_dim=32, sliding_window_size=8))
     cfg.rope = dataclasses.replace(cfg.rope, dim=32)
     model = cfg.build()
     model.init_weights(buffer_device=torch.device("cpu"))

@@ -104,7 +104,7 @@ class ConfigManager:
                 last_err = e
         if module is None:
             raise ImportError(
-                f"Cannot import config registry for module '{module_name}'. "
+                f"Cannot import module '{module_name}' (no config registry found for it). "
                 f"Supported short names: {sorted(known)}"
             ) from last_err
         fn = getattr(module, config_name, None)

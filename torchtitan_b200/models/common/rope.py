@@ -123,3 +123,41 @@ def apply_rotary_emb(xq, xk, table, positions=None, layout: str = "interleaved")
 
 def apply_rotary_emb_single(x, table, positions=None, layout: str = "interleaved"):
     return ops.rope(x, table, positions, layout)
+
+
+# ------------------------------------------------------------------------------------ the reference's cache layouts
+# The models of this framework keep one table layout ([max_seq_len, head_dim / 2, 2] = cos, sin) and rotate through
+# ``ops.rope``. Code written against the reference passes its two cache layouts instead
+# (torchtitan/models/common/rope.py:293-360); the functions below take those, compute in fp32 and return the input dtype.
+def _rows_for(cache: torch.Tensor, x: torch.Tensor, positions: torch.Tensor | None) -> torch.Tensor:
+    """Cache rows for every token of ``x`` [B, S, H, D], shaped to broadcast over heads: [1 | B, S, 1, ...]."""
+    if positions is None:
+        return cache[: x.shape[1]].unsqueeze(0).unsqueeze(2)
+    rows = cache[positions.long()]                       # [1 | B, S, ...]
+    return rows.unsqueeze(2)
+
+
+def apply_rotary_emb_cos_sin(xq: torch.Tensor, xk: torch.Tensor, rope_cache: torch.Tensor, positions: torch.Tensor | None = None):
+    """Half-rotation RoPE with a ``[max_seq_len, 2 * head_dim]`` cache holding cos and sin side by side, each over the
+    whole head dimension (the two halves repeat)."""
+    d = xq.shape[-1]
+    tab = _rows_for(rope_cache, xq, positions).to(device=xq.device, dtype=torch.float32)
+    cos, sin = tab[..., :d], tab[..., d:]
+
+    def rotate(x):
+        xf = x.float()
+        half = torch.cat((-xf[..., d // 2:], xf[..., : d // 2]), dim=-1)
+        return (xf * cos + half * sin).type_as(x)
+
+    return rotate(xq), rotate(xk)
+
+
+def apply_rotary_emb_single_complex(x: torch.Tensor, freqs_cis: torch.Tensor, positions: torch.Tensor | None = None):
+    """Interleaved-pair RoPE with a complex ``[max_seq_len, head_dim / 2]`` cache (``exp(i * angle)``)."""
+    rows = _rows_for(freqs_cis, x, positions).to(x.device)
+    xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+    return torch.view_as_real(xc * rows).flatten(-2).type_as(x)
+
+
+def apply_rotary_emb_complex(xq: torch.Tensor, xk: torch.Tensor, freqs_cis: torch.Tensor, positions: torch.Tensor | None = None):
+    return apply_rotary_emb_single_complex(xq, freqs_cis, positions), apply_rotary_emb_single_complex(xk, freqs_cis, positions)

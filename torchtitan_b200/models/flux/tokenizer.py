@@ -10,6 +10,8 @@ import os
 
 import torch
 
+from torchtitan_b200.tools.logging import logger
+
 from torchtitan_b200.components.tokenizer import BaseTokenizer
 
 
@@ -69,6 +71,8 @@ def build_flux_tokenizer(*, t5_path: str | None, clip_path: str | None, t5_max_l
     """(t5 tokenizer, clip tokenizer); ``test_mode`` or missing folders select the asset-free tokenizer."""
     def one(path, length, vocab):
         if test_mode or path is None or not os.path.isdir(path):
+            if not test_mode and path is not None:
+                logger.warning(f"tokenizer folder {path!r} not found: using the asset-free test tokenizer")
             return FluxTestTokenizer(max_length=length, vocab_size=vocab)
         return FluxTokenizer(path, max_length=length)
 

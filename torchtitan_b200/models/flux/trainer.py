@@ -13,26 +13,19 @@ import torch
 from torchtitan_b200.parallel import utils as dist_utils
 from torchtitan_b200.trainer import Trainer
 
+from .configs import Encoder, Inference, Validation
 from .model.autoencoder import load_ae
 from .model.hf_embedder import FluxEmbedder
 from .utils import create_position_encoding_for_latents, pack_latents, preprocess_data
 from .validate import FluxValidator
 
 
-@dataclass(kw_only=True, slots=True)
-class Encoder:
-    t5_encoder: str = "google/t5-v1_1-small"
-    clip_encoder: str = "openai/clip-vit-large-patch14"
-    autoencoder_path: str = "assets/hf/FLUX.1-dev/ae.safetensors"
-    random_init: bool = False
-    """Build small randomly initialised encoders / autoencoder instead of loading checkpoints (tests, offline runs)."""
-    hidden: int = 64
-
-
 class FluxTrainer(Trainer):
     @dataclass(kw_only=True, slots=True)
     class Config(Trainer.Config):
         encoder: Encoder = field(default_factory=Encoder)
+        validation: Validation = field(default_factory=Validation)
+        inference: Inference = field(default_factory=Inference)
         validator: FluxValidator.Config = field(default_factory=FluxValidator.Config)
 
     def __init__(self, config: Config):
@@ -42,9 +35,15 @@ class FluxTrainer(Trainer):
         self._dtype = TORCH_DTYPE_MAP[config.training.mixed_precision_param] if self.device.type == "cuda" else torch.float32
         e = config.encoder
         self.autoencoder = load_ae(e.autoencoder_path, self.model_config.autoencoder_params, device=self.device, dtype=self._dtype,
-                                   random_init=e.random_init)
-        self.clip_encoder = FluxEmbedder(e.clip_encoder, random_init=e.random_init, hidden=self.model_config.vec_in_dim).to(self.device, self._dtype)
-        self.t5_encoder = FluxEmbedder(e.t5_encoder, random_init=e.random_init, hidden=self.model_config.context_in_dim).to(self.device, self._dtype)
+                                   random_init=e.offline)
+        self.clip_encoder = FluxEmbedder(e.clip_encoder, random_init=e.offline, hidden=self.model_config.vec_in_dim).to(self.device, self._dtype)
+        self.t5_encoder = FluxEmbedder(e.t5_encoder, random_init=e.offline, hidden=self.model_config.context_in_dim).to(self.device, self._dtype)
+        # Noise and noise levels must differ between data-parallel ranks (they see different images) and agree between
+        # the ranks that share a batch (context parallel): a generator of their own, seeded by the job's base seed and
+        # the data-parallel rank. The reference gets the same effect from distinct global seeds along the fsdp and
+        # dp_replicate mesh dimensions (torchtitan/models/flux/trainer.py:36-44).
+        self._noise_gen = torch.Generator(device=self.device)
+        self._noise_gen.manual_seed((int(self.base_seed) + 1_000_003 * (self.dp_rank + 1)) % 2**63)
         if self.validator is not None:
             self.validator.attach(self)
 
@@ -58,8 +57,8 @@ class FluxTrainer(Trainer):
         n_global = dist_utils.dist_sum(n_local, self.parallel_dims.get_mesh("batch")) if self.parallel_dims.dp_enabled else n_local
         bsz, _, lh, lw = target_latents.shape
         with torch.no_grad():
-            noise = torch.randn_like(target_latents)
-            t = torch.rand(bsz, device=self.device)
+            noise = torch.randn(target_latents.shape, dtype=target_latents.dtype, device=self.device, generator=self._noise_gen)
+            t = torch.rand(bsz, device=self.device, generator=self._noise_gen)
             sig = t.view(-1, 1, 1, 1).to(target_latents.dtype)
             latents = pack_latents((1 - sig) * target_latents + sig * noise)
             target = pack_latents(noise - target_latents)

@@ -25,9 +25,13 @@ class FluxValidator(BaseValidator):
         steps: int = 4
         """Held-out batches per validation run."""
         timesteps: int = 8
-        """Evenly spaced noise levels at which the loss is evaluated for every batch."""
+        """Evenly spaced noise levels at which the loss is evaluated for every batch (``all_timesteps``)."""
+        all_timesteps: bool = True
+        """Evaluate every sample at all ``timesteps`` levels. When False the loader deals one of the eight stratified
+        levels to each sample in turn (the reference's default, torchtitan/models/flux/validate.py:60-61, 103-107)."""
         save_img_count: int = 0
-        save_img_folder: str = "img"
+        """Images sampled from the validation prompts per validation run (-1: one for every prompt seen)."""
+        save_img_folder: str = "validation_images"
         dataloader: FluxDataLoader.Config = field(default_factory=lambda: FluxDataLoader.Config(dataset="synthetic"))
 
     def __init__(self, config=None, trainer=None, steps: int = 4, timesteps: int = 8, save_img_count: int = 0,
@@ -40,7 +44,11 @@ class FluxValidator(BaseValidator):
                                           save_img_folder=save_img_folder)
             self.dataloader = None
         else:
-            self.dataloader = config.dataloader.build(dp_world_size=dp_world_size, dp_rank=dp_rank, local_batch_size=local_batch_size)
+            import dataclasses
+
+            dl = dataclasses.replace(config.dataloader, generate_timesteps=not config.all_timesteps)
+            self.dataloader = dl.build(dp_world_size=dp_world_size, dp_rank=dp_rank, local_batch_size=local_batch_size)
+        self._tokenizers = None
         super().__init__(config)
         self.t, self.steps, self.n_t = trainer, config.steps, config.timesteps
         self.save_img_count, self.save_img_folder = config.save_img_count, config.save_img_folder
@@ -48,6 +56,20 @@ class FluxValidator(BaseValidator):
 
     def attach(self, trainer) -> None:
         self.t = trainer
+
+    def _prompt_tokenizers(self):
+        """(t5, clip) tokenizers of the validation loader: sampling with guidance encodes the empty prompt with them."""
+        if self._tokenizers is None:
+            ds = getattr(self.dataloader, "dataset", None)
+            self._tokenizers = (getattr(ds, "_t5", None), getattr(ds, "_clip", None))
+            if self._tokenizers[0] is None:
+                from .tokenizer import build_flux_tokenizer
+
+                c, e = self.config.dataloader, self.config.dataloader.encoder
+                self._tokenizers = build_flux_tokenizer(
+                    t5_path=c.t5_tokenizer_path or e.t5_encoder, clip_path=c.clip_tokenizer_path or e.clip_encoder,
+                    t5_max_length=c.t5_max_length, clip_max_length=c.clip_max_length, test_mode=c.test_tokenizer or e.test_mode)
+        return self._tokenizers
 
     def validate(self, model_parts_or_iterator, step: int) -> float:
         """Trainer protocol: ``validate(model_parts, step)`` draws from the validator's own loader and logs the loss;
@@ -69,27 +91,42 @@ class FluxValidator(BaseValidator):
         model = tr.model_parts[0]
         model.eval()
         total, count = 0.0, 0
+        self._images_left, self._saved = self.save_img_count, 0
         for _ in range(self.steps):
             inputs, images = next(data_iterator)
+            given_t = inputs.pop("timestep", None) if isinstance(inputs, dict) else None
             batch = preprocess_data(tr.device, tr._dtype, autoencoder=tr.autoencoder, clip_encoder=tr.clip_encoder,
                                     t5_encoder=tr.t5_encoder, batch={**inputs, "image": images})
             x = batch["img_encodings"]
             bsz, _, lh, lw = x.shape
             img_ids = create_position_encoding_for_latents(bsz, lh, lw).to(tr.device)
             txt_ids = torch.zeros(bsz, batch["t5_encodings"].shape[1], 3, device=tr.device)
-            for k in range(self.n_t):
-                t = torch.full((bsz,), (k + 0.5) / self.n_t, device=tr.device)
+            # a loader built with ``generate_timesteps`` assigns one stratified noise level to every sample; otherwise
+            # every batch is evaluated at all ``timesteps`` levels
+            levels = [torch.as_tensor(given_t, dtype=torch.float32, device=tr.device).reshape(bsz)] if given_t is not None else \
+                [torch.full((bsz,), (k + 0.5) / self.n_t, device=tr.device) for k in range(self.n_t)]
+            for t in levels:
                 noise = torch.randn_like(x)
                 sig = t.view(-1, 1, 1, 1).to(x.dtype)
                 pred = model(img=pack_latents((1 - sig) * x + sig * noise), img_ids=img_ids, txt=batch["t5_encodings"], txt_ids=txt_ids,
                              y=batch["clip_encodings"], timesteps=t.to(x.dtype))
                 total += float(torch.nn.functional.mse_loss(pred.float(), pack_latents(noise - x).float()))
                 count += 1
-            if self.save_img_count:
+            budget = self._images_left
+            if budget != 0:
+                prompts = inputs.get("prompt") if isinstance(inputs, dict) else None
+                n = images.shape[0] if budget < 0 else min(budget, images.shape[0])
+                t5_tok, clip_tok = self._prompt_tokenizers()
                 imgs = generate_image(tr.device, tr._dtype, model=model, autoencoder=tr.autoencoder, clip_encoder=tr.clip_encoder,
-                                      t5_encoder=tr.t5_encoder, clip_tokens=inputs["clip_tokens"][: self.save_img_count],
-                                      t5_tokens=inputs["t5_tokens"][: self.save_img_count], height=images.shape[-2], width=images.shape[-1])
+                                      t5_encoder=tr.t5_encoder, clip_tokens=inputs["clip_tokens"][:n], t5_tokens=inputs["t5_tokens"][:n],
+                                      clip_tokenizer=clip_tok, t5_tokenizer=t5_tok, job_config=tr.config,
+                                      height=16 * (images.shape[-2] // 16), width=16 * (images.shape[-1] // 16))
+                rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
                 for i, im in enumerate(imgs):
-                    save_image(im, os.path.join(tr.config.dump_folder, self.save_img_folder), f"step{step}_img{i}.png")
+                    save_image(im, os.path.join(tr.config.dump_folder, self.save_img_folder),
+                               f"image_rank{rank}_{step}_{self._saved}.png", prompt=prompts[i] if prompts else None)
+                    self._saved += 1
+                if budget > 0:
+                    self._images_left -= n
         model.train()
         return total / max(1, count)

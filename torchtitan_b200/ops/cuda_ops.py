@@ -968,13 +968,6 @@ def grouped_linear(x, w, counts):
     return _GroupedLinearRef.apply(x, w, counts)
 
 
-def moe_fill_indices(tokens_per_expert_group, start_index_values, write_offsets, experts_per_rank, num_ranks, max_len):
-    from torchtitan_b200.models.common.moe.permute import fill_indices_cpu
-
-    return fill_indices_cpu(tokens_per_expert_group.cpu(), start_index_values.cpu(), write_offsets.cpu(),
-                            experts_per_rank, num_ranks, max_len).to(tokens_per_expert_group.device)
-
-
 # =============================================================================== generation (see csrc/serving.cu)
 def kv_write(k_cache: Tensor, v_cache: Tensor, k: Tensor, v: Tensor, slots: Tensor) -> None:
     T, Hkv, D = k.shape

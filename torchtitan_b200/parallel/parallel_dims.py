@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from torchtitan_b200.tools.logging import logger
+from torchtitan_b200.tools.utils import device_type
 
 __all__ = ["ParallelDims", "RankGrid"]
 
@@ -170,8 +171,6 @@ class ParallelDims:
 
     # ------------------------------------------------------------------ process groups
     def _device_type(self) -> str:
-        from torchtitan_b200.tools.utils import device_type
-
         return device_type
 
     # A job may give the dims only a subset of its ranks (e.g. the trainer ranks of an RL job whose other ranks generate):

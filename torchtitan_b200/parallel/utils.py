@@ -53,8 +53,9 @@ def dist_mean(x: torch.Tensor, mesh, extra_pg=None) -> float:
     return _reduce(x, dist.ReduceOp.SUM, mesh, extra_pg) / n
 
 
-def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_seed_mesh_dims: list[str] | None = None) -> None:
-    """Same seed on all ranks except along ``distinct_seed_mesh_dims`` (default: pipeline)."""
+def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_seed_mesh_dims: list[str] | None = None) -> int:
+    """Same seed on all ranks except along ``distinct_seed_mesh_dims`` (default: pipeline). Returns the job's base seed
+    (the value every rank shares, before the per-dimension offsets)."""
     distinct_seed_mesh_dims = ["pp"] if distinct_seed_mesh_dims is None else distinct_seed_mesh_dims
     if debug_config.deterministic:
         logger.info("Deterministic algorithm enabled (expect perf degradation).")
@@ -71,13 +72,20 @@ def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_
         if world > 1 and dist.is_initialized():
             dist.broadcast(t, src=0)
         seed = int(t.to("cpu").view(torch.uint64).item() % (2**63))
+    base_seed = seed
     rank = dist.get_rank() if dist.is_initialized() else 0
     offset = 0
     mult = 1
-    for name in distinct_seed_mesh_dims:
-        size = parallel_dims.dim_size(name)
+    for name in (distinct_seed_mesh_dims if world > 1 else ()):
+        if hasattr(parallel_dims, "dim_size"):
+            size = parallel_dims.dim_size(name)
+            coord = parallel_dims.coordinate(name, rank) if size > 1 else 0
+        else:                                   # any object with the mesh accessors of ParallelDims
+            mesh = parallel_dims.get_optional_mesh(name)
+            size = mesh.size() if mesh is not None else 1
+            coord = mesh.get_local_rank() if mesh is not None else 0
         if size > 1:
-            offset += parallel_dims.coordinate(name, rank) * mult
+            offset += coord * mult
             mult *= size
     seed = (seed + offset) % 2**64
     logger.debug(f"rank {rank}: seed {seed}")
@@ -88,6 +96,7 @@ def set_determinism(parallel_dims, device: torch.device, debug_config, distinct_
             seed_dtensor_rng(parallel_dims.world_mesh, seed)
         except Exception as e:      # every rank of the job is here, so DTensor's own lazy start-up sync also works
             logger.warning(f"DTensor RNG tracker not pre-seeded ({type(e).__name__}: {e}); falling back to its start-up sync")
+    return base_seed
 
 
 def seed_dtensor_rng(mesh, seed: int) -> None:

@@ -10,7 +10,8 @@ from torchtitan_b200.config.configurable import Configurable
 
 class Module(nn.Module, Configurable):
     """Base of every model building block. ``init_weights`` must be callable on a module
-    whose parameters were just materialised with ``to_empty`` (built on ``meta``)."""
+    whose parameters were just materialised with ``to_empty`` (built on ``meta``). The default does nothing, which suits
+    modules without learnable parameters or with weights loaded from elsewhere; modules with parameters override it."""
 
     def init_weights(self, **kwargs) -> None:
-        raise NotImplementedError(f"{type(self).__name__} must implement init_weights()")
+        return None

@@ -151,7 +151,7 @@ class Trainer(Stateful, Configurable):
         # locally sharded (TP / EP) parameters are plain tensors: ranks along those dimensions need their
         # own random streams; replicated parameters are broadcast afterwards (tp.finalize_tp)
         seed_dims = ["pp"] + (["tp"] if pd.tp_enabled else []) + (["ep"] if pd.ep_enabled else [])
-        dist_utils.set_determinism(pd, self.device, config.debug, distinct_seed_mesh_dims=seed_dims)
+        self.base_seed = dist_utils.set_determinism(pd, self.device, config.debug, distinct_seed_mesh_dims=seed_dims)
         config.maybe_log()
 
         # ---- data ---------------------------------------------------------------------
