@@ -181,17 +181,44 @@ def _no_grouped(cfg):
     return cfg
 
 
+def _dense_flex_attention(q, k, v, block_mask=None, scale=None, enable_gqa=False, return_lse=False):
+    """Stand-in for the reference's compiled flex attention on the CPU: the plain definition of attention under the
+    reference's own ``mask_mod`` (taken from the block mask it built), with the log-sum-exp it asks for."""
+    from torch.nn.attention.flex_attention import create_mask
+
+    B, H, S, D = q.shape
+    if k.shape[1] != H:
+        k, v = k.repeat_interleave(H // k.shape[1], 1), v.repeat_interleave(H // v.shape[1], 1)
+    s = (q.float() @ k.float().transpose(-1, -2)) * (scale if scale is not None else D ** -0.5)
+    if block_mask is not None:
+        s = s.masked_fill(~create_mask(block_mask.mask_mod, B, 1, S, k.shape[2], device="cpu"), float("-inf"))
+    out = (torch.softmax(s, -1) @ v.float()).to(q.dtype)
+    return (out, torch.logsumexp(s, -1)) if return_lse else out
+
+
 @pytest.mark.parametrize("family,flavor", [("llama3", "debugmodel"), ("qwen3", "debugmodel"), ("qwen3", "debugmodel_moe"),
-                                           ("deepseek_v3", "debugmodel")])
+                                           ("deepseek_v3", "debugmodel"), ("gpt_oss", "debugmodel"), ("llama4", "debugmodel")])
 def test_model_families_match_the_reference_models(family, flavor, monkeypatch):
     """Same parameter names and shapes as the reference's model of the family; with this framework's weights loaded into
     the reference's own model code, logits and every parameter gradient agree (fp32, CPU): dense and MoE Qwen3 (q / k
-    norms, top-k softmax routing), DeepSeek-V3 (multi-head latent attention, sigmoid routing with shared experts).
-    GPT-OSS and Llama 4 are left out: the reference builds their masks with compiled flex attention, which needs a GPU."""
+    norms, top-k softmax routing), DeepSeek-V3 (multi-head latent attention, sigmoid routing with shared experts),
+    GPT-OSS (sinks, alternating sliding-window layers, biased experts with the clamped activation) and Llama 4 (layers
+    without rotary embedding, attention in fixed blocks, shared expert). The last two build document masks from
+    end-of-sequence tokens, planted here, over sequences longer than the window and the block; the reference's compiled
+    flex attention (GPU only) is replaced by the definition of attention under the reference's own mask function."""
     import importlib
 
     if REF not in sys.path:
         sys.path.insert(0, REF)
+    masked = family in ("gpt_oss", "llama4")
+    if masked:
+        from torch.nn.attention.flex_attention import create_block_mask
+
+        import torchtitan.models.common.attention as ref_attention
+
+        monkeypatch.setattr(ref_attention.FlexAttentionWrapper, "_compiled_flex_attn", staticmethod(_dense_flex_attention))
+        monkeypatch.setattr(ref_attention, "_compiled_create_block_mask",
+                            lambda *a, **k: create_block_mask(*a, **{**k, "device": "cpu"}))
     histc = torch.histc
     # the reference counts tokens per expert with histc on integer indices, which the CPU kernel does not take
     monkeypatch.setattr(torch, "histc", lambda x, *a, **k: histc(x.float(), *a, **k).to(x.dtype))
@@ -216,9 +243,19 @@ def test_model_families_match_the_reference_models(family, flavor, monkeypatch):
         with torch.no_grad():
             ref.init_weights(buffer_device=torch.device("cpu")) if family != "llama3" else ref.init_weights()
         ref.load_state_dict(state)
-    x = torch.randint(0, ours_cfg.vocab_size, (2, 65))
+    x = torch.randint(8, ours_cfg.vocab_size, (2, 321 if masked else 65))
+    kw_ours, kw_ref = {}, {}
+    if masked:
+        class _Tok:
+            eos_id = 3
+
+        x[0, [40, 41, 170]] = _Tok.eos_id                          # three documents in row 0 (one of a single token), two in row 1
+        x[1, 299] = _Tok.eos_id
     inp, lab = x[:, :-1], x[:, 1:]
-    lo, lr = ours(inp), ref(inp)
+    if masked:
+        kw_ours = {"attention_masks": ours.get_attention_masks(inp, _Tok())}
+        kw_ref = {"attention_masks": ref.get_attention_masks(inp, _Tok())}
+    lo, lr = ours(inp, **kw_ours), ref(inp, **kw_ref)
     assert (lo - lr).abs().max().item() < 2e-5 * max(lr.abs().max().item(), 1.0)
     torch.nn.functional.cross_entropy(lo.flatten(0, 1).float(), lab.flatten()).backward()
     torch.nn.functional.cross_entropy(lr.flatten(0, 1).float(), lab.flatten()).backward()
