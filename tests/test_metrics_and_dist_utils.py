@@ -194,3 +194,32 @@ def test_clip_coefficient_rides_into_the_flat_optimizer_for_every_unit(tmp_path)
     for o in run_ranks(_fold_worker, 2, tmp_path=tmp_path):
         assert o["untouched"] and len(o["scales"]) == 2
         assert all(s == pytest.approx(o["coef"], rel=1e-5) for s in o["scales"])
+
+
+def _node_worker(rank, world):
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.parallel import nvlink_comm
+
+    same = nvlink_comm.all_ranks_agree_on_one_node(dist.group.WORLD, True, "cpu")
+    one_says_no = nvlink_comm.all_ranks_agree_on_one_node(dist.group.WORLD, rank != 1, "cpu")
+    real = nvlink_comm.node_identity
+    nvlink_comm.node_identity = lambda: real() ^ (rank == 2)         # rank 2 pretends to sit on another machine
+    try:
+        split = nvlink_comm.all_ranks_agree_on_one_node(dist.group.WORLD, True, "cpu")
+    finally:
+        nvlink_comm.node_identity = real
+    no_gpu = nvlink_comm.peer_memory_group_ok(dist.group.WORLD)      # CPU ranks: never eligible, and nobody hangs
+    return same, one_says_no, split, no_gpu
+
+
+def test_peer_memory_groups_need_all_ranks_on_one_node(tmp_path):
+    """CUDA IPC handles only mean something on the machine that made them: a group whose ranks report different node
+    identities (a shard or tensor-parallel group that spans hosts in a multi-node job) must take the collectives, on
+    every rank alike."""
+    from torchtitan_b200.parallel.nvlink_comm import node_identity
+
+    assert node_identity() == node_identity() and 0 <= node_identity() < 2**62
+    for out in run_ranks(_node_worker, 3, tmp_path=tmp_path):
+        assert out == (True, False, False, False)

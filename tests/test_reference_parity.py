@@ -486,3 +486,79 @@ def test_parameter_and_flop_counts_match_the_reference(family):
         na, fa = ours[flavor].get_nparams_and_flops(a, 4096)
         nb, fb = ref[flavor].get_nparams_and_flops(b, 4096)
         assert na == nb and abs(fa - fb) <= 1e-9 * fb, (family, flavor, (na, fa), (nb, fb))
+
+
+def test_grpo_loss_matches_the_reference_loss():
+    """The GRPO objective (clipped ratio of per-sequence mean log-ratios, per-token KL estimate, entropy bonus) computed
+    over one packed forward pass equals the reference's, which runs one forward pass per sequence: loss, metrics,
+    per-token log-probabilities and parameter gradients; the log-probability identity report agrees as well."""
+    import importlib.util
+
+    # the file needs torch only; its package imports vLLM internals that this environment's vLLM does not have
+    path = os.path.join(REF, "torchtitan", "experiments", "rl", "unified", "actors", "utils.py")
+    if not os.path.exists(path):
+        pytest.skip("the reference install has no rl/unified/actors/utils.py")
+    spec = importlib.util.spec_from_file_location("_ref_rl_actor_utils", path)
+    ref_utils = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_utils)
+
+    from torchtitan_b200.experiments.rl import losses
+    from torchtitan_b200.models.llama3 import llama3_configs
+
+    cfg = dataclasses.replace(llama3_configs["debugmodel"], n_layers=2)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=64)
+    torch.manual_seed(3)
+    model = cfg.build()
+    model.init_weights()
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 9, 3, 7)]
+    gens = [torch.randint(1, cfg.vocab_size, (n,), generator=g).tolist() for n in (6, 2, 11, 4)]
+    adv = torch.tensor([0.7, -1.2, 0.1, 2.0])
+    ref_lps = [torch.randn(len(x), generator=g) * 0.05 - 7.6 for x in gens]
+    kw = dict(kl_coef=0.1, ppo_clip_eps=0.2, entropy_coef=0.01)
+
+    want, want_metrics, want_lps = ref_utils.compute_policy_gradient_loss(model, gens, prompts, adv, ref_lps, **kw)
+    want.backward()
+    want_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+    got, got_metrics, got_lps = losses.compute_policy_gradient_loss(model, gens, prompts, adv, ref_lps, **kw)
+    got.backward()
+    assert got.item() == pytest.approx(want.item(), rel=1e-5)
+    assert set(got_metrics) == set(want_metrics)
+    for k in want_metrics:
+        assert got_metrics[k] == pytest.approx(want_metrics[k], rel=1e-4, abs=1e-6), k
+    for a, b in zip(got_lps, want_lps):
+        assert torch.allclose(a, b, atol=1e-5)
+    for n, p in model.named_parameters():
+        assert torch.allclose(p.grad, want_grads[n], atol=1e-6 + 1e-4 * want_grads[n].abs().max().item()), n
+    # micro-batches with the step's totals add up to the full-batch loss
+    parts = [losses.compute_policy_gradient_loss(model, gens[i : i + 2], prompts[i : i + 2], adv[i : i + 2], ref_lps[i : i + 2],
+                                                 n_seqs_total=4, n_tokens_total=sum(map(len, gens)), **kw)[0] for i in (0, 2)]
+    assert (parts[0] + parts[1]).item() == pytest.approx(want.item(), rel=1e-5)
+    fake_gen = [[float(v) for v in t.detach()] for t in got_lps]
+    fake_gen[1][0] += 0.5
+    assert losses.verify_logprob_identity(fake_gen, got_lps) == pytest.approx(ref_utils.verify_logprob_identity(fake_gen, got_lps))
+
+
+def test_sum_digits_task_matches_the_reference_task():
+    """Same questions for the same seed, same answer protocol in the system prompt, same answer extraction and rewards on completions of every
+    kind the reward function distinguishes (tagged, prose, bare number, several tags, trailing text, wrong, empty)."""
+    import importlib.util
+
+    path = os.path.join(REF, "torchtitan", "experiments", "rl", "unified", "sum_digits.py")
+    if not os.path.exists(path):
+        pytest.skip("the reference install has no rl/unified/sum_digits.py")
+    spec = importlib.util.spec_from_file_location("_ref_sum_digits", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    from torchtitan_b200.experiments.rl import sum_digits as ours
+
+    a, b = ours.SumDigitsTask(seed=42), ref.SumDigitsTask(seed=42)
+    assert [a.create_question() for _ in range(50)] == [b.create_question() for _ in range(50)]
+    assert "[ANSWER] <number>" in a.get_system_prompt() and "[ANSWER] 28" in a.get_system_prompt()   # own wording, same protocol
+    texts = ["[ANSWER] 28", "so the sum is 28", "the answer is 28.", "Answer: 27 [ANSWER] 28", "[ANSWER] 27 [ANSWER] 28",
+             "[ANSWER] 28 and that is final", "1 + 2 = 28", "= 28. The answer", "[ANSWER] -28", "nothing here", "",
+             "[ANSWER]   28  \n", "[ANSWER] 28\n[ANSWER] 28"]
+    assert [ours.extract_answer(t) for t in texts] == [ref.extract_answer(t) for t in texts]
+    for expected in ("28", "27", ""):
+        assert torch.equal(a.reward_function(texts, expected), b.reward_function(texts, expected))

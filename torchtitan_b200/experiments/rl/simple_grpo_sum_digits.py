@@ -150,15 +150,13 @@ class RLTrainer(Configurable):
 
         from .weight_sync import NvlinkWeightSync, arena_layout
 
-        me = torch.cuda.current_device()
-        ok = native.available() and native.has("tt_push_cast") and dist.get_world_size() <= torch.cuda.device_count() and all(
-            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
+        from torchtitan_b200.parallel.nvlink_comm import peer_memory_group_ok
+
         # FSDP (or single-rank) trainers only: tensor-parallel shards are not dim-0 slices of the full parameter
         p = self.config.trainer.parallelism
-        ok = ok and p.tensor_parallel_degree == 1 and p.pipeline_parallel_degree == 1
-        flag = torch.tensor([1 if ok else 0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
+        ok = (native.available() and native.has("tt_push_cast") and p.tensor_parallel_degree == 1
+              and p.pipeline_parallel_degree == 1)
+        if not peer_memory_group_ok(dist.group.WORLD, extra_ok=ok):
             return None
         with torch.device("meta"):
             meta = self.config.model_spec.model.build()

@@ -34,7 +34,7 @@ import torch.distributed as dist
 from torchtitan_b200.ops import native
 from torchtitan_b200.tools.logging import logger
 
-from .nvlink_comm import _PP, SymmetricHeap, _stream
+from .nvlink_comm import _PP, SymmetricHeap, _stream, peer_memory_group_ok
 
 
 class AsyncTP:
@@ -58,13 +58,7 @@ class AsyncTP:
     def maybe_create(cls, tp_mesh):
         if not native.available() or not native.has("tt_gemm_allgather_a"):
             return None
-        W = tp_mesh.size()
-        me = torch.cuda.current_device()
-        ok = 2 <= W <= 16 and torch.cuda.device_count() >= W and all(
-            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
-        flag = torch.tensor([1 if ok else 0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=tp_mesh.get_group())
-        if int(flag.item()) == 0:
+        if not peer_memory_group_ok(tp_mesh.get_group()):
             return None
         return cls(tp_mesh)
 

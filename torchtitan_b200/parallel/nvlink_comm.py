@@ -77,6 +77,47 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def node_identity() -> int:
+    """62-bit number that is the same for all processes of one machine boot and differs between machines."""
+    import hashlib
+    import socket
+
+    ident = socket.gethostname()
+    try:
+        with open("/proc/sys/kernel/random/boot_id") as f:
+            ident += f.read().strip()
+    except OSError:
+        pass
+    return int.from_bytes(hashlib.md5(ident.encode()).digest()[:8], "little") >> 2
+
+
+def peer_memory_group_ok(group, extra_ok: bool = True, max_world: int = 16) -> bool:
+    """Collective over ``group``: True on every rank when the group can share memory through CUDA IPC, that is when
+    ``extra_ok`` holds on every rank, the group has 2..``max_world`` ranks, all of them run on this machine (a job over
+    several nodes can have groups of the right size whose ranks sit on different hosts, where the IPC handles mean
+    nothing) and this rank's GPU can map every other GPU of the machine. Otherwise False on every rank, and the callers
+    keep to the collectives."""
+    W = dist.get_world_size(group)
+    ok = bool(extra_ok) and 2 <= W <= max_world
+    if torch.cuda.is_available():
+        me = torch.cuda.current_device()
+        ok = ok and torch.cuda.device_count() >= W and all(
+            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
+        device = "cuda"
+    else:
+        ok, device = False, "cpu"
+    return all_ranks_agree_on_one_node(group, ok, device)
+
+
+def all_ranks_agree_on_one_node(group, ok: bool, device: str) -> bool:
+    """One all-reduce: every rank said ``ok`` and every rank reports the same node identity."""
+    h = node_identity()
+    t = torch.tensor([1 if ok else 0, h, -h], dtype=torch.int64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+    t = t.tolist()
+    return t[0] == 1 and t[1] == -t[2]
+
+
 class SymmetricHeap:
     """One IPC-shared arena per rank with a bump allocator that is replayed identically on every
     rank, so an offset names the same object everywhere."""
@@ -153,16 +194,9 @@ class NvlinkComm(ShardComm):
         W = shard_mesh.size()
         if W < 2 or W > 16:
             return None
-        group = shard_mesh.get_group()
         # all ranks of the group must be GPUs of this process's node with peer access
-        ok = torch.cuda.device_count() >= W
-        me = torch.cuda.current_device()
-        if ok:
-            ok = all(torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
-        flag = torch.tensor([1 if ok else 0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
-        if int(flag.item()) == 0:
-            logger.info("NVLink FSDP transport unavailable (no peer access); using c10d collectives")
+        if not peer_memory_group_ok(shard_mesh.get_group()):
+            logger.info("NVLink FSDP transport unavailable (ranks on several nodes or no peer access); using c10d collectives")
             return None
         # a tied weight is reachable from two wrapped units and each keeps its own flat buffers: count it twice
         nparams = sum(p.numel() for _, p in model.named_parameters(remove_duplicate=False)) if model is not None else 0

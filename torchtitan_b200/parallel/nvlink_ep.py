@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from torchtitan_b200.ops import native
 
-from .nvlink_comm import _PP, SymmetricHeap, _stream
+from .nvlink_comm import _PP, SymmetricHeap, _stream, peer_memory_group_ok
 
 
 def copy_rows_where(rows, keep):
@@ -170,13 +170,7 @@ class NvlinkDispatcher:
     def available(cls, ep_mesh) -> bool:
         if not (torch.cuda.is_available() and native.available() and native.has("tt_ep_push")):
             return False
-        W = ep_mesh.size()
-        me = torch.cuda.current_device()
-        ok = 2 <= W <= 16 and torch.cuda.device_count() >= W and all(
-            torch.cuda.can_device_access_peer(me, d) for d in range(torch.cuda.device_count()) if d != me)
-        flag = torch.tensor([1 if ok else 0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=ep_mesh.get_group())
-        return bool(int(flag.item()))
+        return peer_memory_group_ok(ep_mesh.get_group())
 
     def _state(self, n: int, D: int) -> _Shared:
         gid = id(self.group)
