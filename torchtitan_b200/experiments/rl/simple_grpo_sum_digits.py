@@ -148,9 +148,9 @@ class RLTrainer(Configurable):
         """One symmetric heap over all ranks of the job when every GPU can map every other one; else None (broadcast path)."""
         from torchtitan_b200.ops import native
 
-        from .weight_sync import NvlinkWeightSync, arena_layout
-
         from torchtitan_b200.parallel.nvlink_comm import peer_memory_group_ok
+
+        from .weight_sync import NvlinkWeightSync, arena_layout
 
         # FSDP (or single-rank) trainers only: tensor-parallel shards are not dim-0 slices of the full parameter
         p = self.config.trainer.parallelism
@@ -163,7 +163,7 @@ class RLTrainer(Configurable):
         if getattr(meta, "enable_weight_tying", False):
             meta.tok_embeddings.weight = meta.output.weight
         self._arena_offsets, numel = arena_layout(meta)
-        return NvlinkWeightSync(dist.group.WORLD, train_ranks, self.gen_ranks, numel, device or f"cuda:{me}")
+        return NvlinkWeightSync(dist.group.WORLD, train_ranks, self.gen_ranks, numel, device or f"cuda:{torch.cuda.current_device()}")
 
     def _sync_weights(self, version: int) -> None:
         """Trainer -> generator weights. Returns the time spent (seconds, host clock around a device sync)."""
