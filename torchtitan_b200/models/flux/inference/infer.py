@@ -69,10 +69,11 @@ def inference(config: FluxTrainer.Config) -> list[str]:
         filler = not ids                                   # keep the collectives of sharded models in step
         if filler:
             ids = mine[-bs:]
-        images = generate_image(trainer.device, trainer._dtype, model=model, autoencoder=trainer.autoencoder,
-                                clip_encoder=trainer.clip_encoder, t5_encoder=trainer.t5_encoder, prompt=[prompts[i] for i in ids],
-                                clip_tokenizer=clip_tok, t5_tokenizer=t5_tok, job_config=config, height=size, width=size,
-                                seed=None)
+        with trainer.maybe_enable_amp:
+            images = generate_image(trainer.device, trainer._dtype, model=model, autoencoder=trainer.autoencoder,
+                                    clip_encoder=trainer.clip_encoder, t5_encoder=trainer.t5_encoder,
+                                    prompt=[prompts[i] for i in ids], clip_tokenizer=clip_tok, t5_tokenizer=t5_tok,
+                                    job_config=config, height=size, width=size, seed=None)
         if filler:
             continue
         for img, i in zip(images, ids):

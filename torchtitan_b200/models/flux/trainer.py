@@ -32,7 +32,10 @@ class FluxTrainer(Trainer):
         super().__init__(config)
         from torchtitan_b200.config import TORCH_DTYPE_MAP
 
-        self._dtype = TORCH_DTYPE_MAP[config.training.mixed_precision_param] if self.device.type == "cuda" else torch.float32
+        # dtype of the frozen encoders and of their outputs: the mixed-precision parameter dtype when FSDP casts the
+        # model's parameters to it, float32 otherwise (then autocast, if any, does the casting inside the model)
+        self._dtype = (TORCH_DTYPE_MAP[config.training.mixed_precision_param]
+                       if self.device.type == "cuda" and self.parallel_dims.fsdp_enabled else torch.float32)
         e = config.encoder
         self.autoencoder = load_ae(e.autoencoder_path, self.model_config.autoencoder_params, device=self.device, dtype=self._dtype,
                                    random_init=e.offline)

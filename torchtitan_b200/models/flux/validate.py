@@ -108,8 +108,9 @@ class FluxValidator(BaseValidator):
             for t in levels:
                 noise = torch.randn_like(x)
                 sig = t.view(-1, 1, 1, 1).to(x.dtype)
-                pred = model(img=pack_latents((1 - sig) * x + sig * noise), img_ids=img_ids, txt=batch["t5_encodings"], txt_ids=txt_ids,
-                             y=batch["clip_encodings"], timesteps=t.to(x.dtype))
+                with tr.maybe_enable_amp:
+                    pred = model(img=pack_latents((1 - sig) * x + sig * noise), img_ids=img_ids, txt=batch["t5_encodings"],
+                                 txt_ids=txt_ids, y=batch["clip_encodings"], timesteps=t.to(x.dtype))
                 total += float(torch.nn.functional.mse_loss(pred.float(), pack_latents(noise - x).float()))
                 count += 1
             budget = self._images_left
@@ -117,10 +118,12 @@ class FluxValidator(BaseValidator):
                 prompts = inputs.get("prompt") if isinstance(inputs, dict) else None
                 n = images.shape[0] if budget < 0 else min(budget, images.shape[0])
                 t5_tok, clip_tok = self._prompt_tokenizers()
-                imgs = generate_image(tr.device, tr._dtype, model=model, autoencoder=tr.autoencoder, clip_encoder=tr.clip_encoder,
-                                      t5_encoder=tr.t5_encoder, clip_tokens=inputs["clip_tokens"][:n], t5_tokens=inputs["t5_tokens"][:n],
-                                      clip_tokenizer=clip_tok, t5_tokenizer=t5_tok, job_config=tr.config,
-                                      height=16 * (images.shape[-2] // 16), width=16 * (images.shape[-1] // 16))
+                with tr.maybe_enable_amp:
+                    imgs = generate_image(tr.device, tr._dtype, model=model, autoencoder=tr.autoencoder,
+                                          clip_encoder=tr.clip_encoder, t5_encoder=tr.t5_encoder,
+                                          clip_tokens=inputs["clip_tokens"][:n], t5_tokens=inputs["t5_tokens"][:n],
+                                          clip_tokenizer=clip_tok, t5_tokenizer=t5_tok, job_config=tr.config,
+                                          height=16 * (images.shape[-2] // 16), width=16 * (images.shape[-1] // 16))
                 rank = torch.distributed.get_rank() if torch.distributed.is_initialized() else 0
                 for i, im in enumerate(imgs):
                     save_image(im, os.path.join(tr.config.dump_folder, self.save_img_folder),
