@@ -243,7 +243,7 @@ def test_vlm_data_path_and_model_step():
     assert out.shape == (2, 256, cfg.vocab_size)
     loss = torch.nn.functional.cross_entropy(out.flatten(0, 1).float(), labels.flatten(), ignore_index=-100)
     loss.backward()
-    assert model.encoder.layers["0"].fc1.weight.grad.abs().sum() > 0 and model.projector.w2.weight.grad.abs().sum() > 0
+    assert model.encoder.layers["0"].mlp.fc1.weight.grad.abs().sum() > 0 and model.projector.w2.weight.grad.abs().sum() > 0
 
 
 def test_vlm_loader_feeds_the_model_and_resumes():

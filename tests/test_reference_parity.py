@@ -562,3 +562,66 @@ def test_sum_digits_task_matches_the_reference_task():
     assert [ours.extract_answer(t) for t in texts] == [ref.extract_answer(t) for t in texts]
     for expected in ("28", "27", ""):
         assert torch.equal(a.reward_function(texts, expected), b.reward_function(texts, expected))
+
+
+def test_vlm_model_matches_the_reference_model(monkeypatch):
+    """Llama 3 + SigLIP-2 vision-language model: same parameter names, and with the same weights the same logits and
+    gradients as the reference's model for a batch of two images of different grids scattered into two token rows (the
+    reference's compiled flex attention replaced by the definition of attention under its own mask functions)."""
+    if REF not in sys.path:
+        sys.path.insert(0, REF)
+    from torch.nn.attention.flex_attention import create_block_mask
+
+    import torchtitan.models.common.attention as ref_attention
+
+    monkeypatch.setattr(ref_attention.FlexAttentionWrapper, "_compiled_flex_attn", staticmethod(_dense_flex_attention))
+    monkeypatch.setattr(ref_attention, "_compiled_create_block_mask",
+                        lambda *a, **k: create_block_mask(*a, **{**k, "device": "cpu"}))
+    from torchtitan.experiments.vlm import llama3_siglip2_configs as ref_cfgs
+    from torchtitan.experiments.vlm.model.args import SpecialTokens as RefSpecialTokens
+
+    from torchtitan_b200.experiments.vlm import SpecialTokens, llama3_siglip2_configs as our_cfgs
+
+    torch.manual_seed(0)
+    cfg = our_cfgs["debugmodel"]
+    ours = cfg.build()
+    ours.init_weights()
+    ref = ref_cfgs["debugmodel"].build()
+    assert {k: v.shape for k, v in ours.state_dict().items()} == {k: v.shape for k, v in ref.state_dict().items()}
+    with torch.no_grad():
+        ref.init_weights(buffer_device=torch.device("cpu"))
+    ref.load_state_dict(ours.state_dict())
+    V, patch = cfg.vocab_size, cfg.encoder.patch_size
+    img, boi, eoi, pad = V - 1, V - 2, V - 3, V - 4
+    st = dict(img_token="<|image|>", img_id=img, boi_token="<|begin_of_image|>", boi_id=boi, eoi_token="<|end_of_image|>",
+              eoi_id=eoi, pad_token="<|pad|>", pad_id=pad)
+    B, S, N, L = 2, 96, 2, 16
+    pixel = torch.zeros(N, L, 3 * patch * patch)
+    grid = torch.full((N, L, 3), -1, dtype=torch.long)
+    for n, (h, w) in enumerate([(3, 4), (2, 5)]):                     # 12 and 10 patches, padded to 16
+        pixel[n, : h * w] = torch.randn(h * w, 3 * patch * patch)
+        grid[n, : h * w] = torch.tensor([[0, i, j] for i in range(h) for j in range(w)])
+    tokens = torch.randint(8, V - 8, (B, S))
+    tokens[0, 5], tokens[0, 6:18], tokens[0, 18] = boi, img, eoi
+    tokens[1, 30], tokens[1, 31:41], tokens[1, 41] = boi, img, eoi
+
+    class _Tok:
+        eos_id = 3
+
+    tokens[0, 50] = _Tok.eos_id                                        # two documents in row 0
+    lo = ours(tokens, pixel, grid, SpecialTokens(**st), attention_masks=ours.get_attention_masks(tokens, _Tok(), {"grid_thw": grid}))
+    # the reference leaves the positional embeddings of padding patches uninitialised (torch.empty); whatever is there
+    # reaches no real patch on a GPU kernel that skips masked keys, but 0 x NaN in the dense stand-in would: zero them
+    with monkeypatch.context() as m:
+        m.setattr(torch, "empty", torch.zeros)
+        lr = ref(tokens, pixel, grid, RefSpecialTokens(**st), attention_masks=ref.get_attention_masks(tokens, _Tok(), {"grid_thw": grid}))
+    assert (lo - lr).abs().max().item() < 2e-5 * max(lr.abs().max().item(), 1.0)
+    lab = torch.randint(0, V, (B, S))
+    torch.nn.functional.cross_entropy(lo.flatten(0, 1), lab.flatten()).backward()
+    torch.nn.functional.cross_entropy(lr.flatten(0, 1), lab.flatten()).backward()
+    ref_grads = dict(ref.named_parameters())
+    for name, p in ours.named_parameters():
+        g, w = p.grad, ref_grads[name].grad
+        assert (g is None) == (w is None), name
+        if g is not None:
+            assert (g - w).abs().max().item() <= 1e-4 * max(w.abs().max().item(), 1e-6) + 1e-7, name

@@ -51,6 +51,10 @@ class Siglip2Config:
     layer_norm_eps: float = 1e-6
     attn_backend: str = "flex"
     attn_mask_type: str = "causal"
+    """``causal`` / ``block_causal``: a patch attends to the patches before it in the image's row-major sequence, which is
+    what the reference's encoder computes (torchtitan/experiments/vlm/model/siglip2.py:211-238 builds its mask from the
+    causal mask function; its document variant splits at end-of-sequence ids, which a patch mask never holds);
+    ``bidirectional``: every real patch of the image, as in the published SigLIP-2 encoder."""
 
 
 def resize_positional_embeddings(pos_hwd: torch.Tensor, shapes_n2: torch.Tensor, max_length: int) -> torch.Tensor:
@@ -88,27 +92,61 @@ class VisionEmbeddings(Module):
         return x + resize_positional_embeddings(pos, shapes, pixels_nld.shape[1])
 
 
+class _EncoderAttention(Module):
+    """Bidirectional multi-head attention over the patches of one image (parameter names as in the Hugging Face
+    SigLIP-2 checkpoints and the reference's encoder: ``self_attn.{q,k,v,out}_proj``)."""
+
+    def __init__(self, a: Siglip2Config):
+        super().__init__()
+        if a.attn_mask_type not in ("causal", "block_causal", "bidirectional"):
+            raise ValueError(f"Unknown attention mask type: {a.attn_mask_type}")
+        self.n_heads, self.causal = a.n_heads, a.attn_mask_type != "bidirectional"
+        self.q_proj, self.k_proj, self.v_proj, self.out_proj = (nn.Linear(a.dim, a.dim) for _ in range(4))
+
+    def forward(self, h, key_mask):
+        N, L, D = h.shape
+        q, k, v = (p(h).view(N, L, self.n_heads, -1).transpose(1, 2) for p in (self.q_proj, self.k_proj, self.v_proj))
+        if self.causal:      # padding patches come last, so real patches never see them
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        else:
+            o = F.scaled_dot_product_attention(q, k, v, attn_mask=key_mask.view(N, 1, 1, L))
+        return self.out_proj(o.transpose(1, 2).reshape(N, L, D))
+
+    def init_weights(self, **kwargs) -> None:
+        for m in (self.q_proj, self.k_proj, self.v_proj, self.out_proj):
+            nn.init.trunc_normal_(m.weight, mean=0.0, std=0.02)
+            nn.init.zeros_(m.bias)
+
+
+class _EncoderMLP(Module):
+    def __init__(self, a: Siglip2Config):
+        super().__init__()
+        self.fc1, self.fc2 = nn.Linear(a.dim, a.ffn_dim), nn.Linear(a.ffn_dim, a.dim)
+
+    def forward(self, x):
+        return self.fc2(F.gelu(self.fc1(x), approximate="tanh"))
+
+    def init_weights(self, **kwargs) -> None:
+        for m in (self.fc1, self.fc2):
+            nn.init.trunc_normal_(m.weight, mean=0.0, std=0.02)
+            nn.init.zeros_(m.bias)
+
+
 class EncoderLayer(Module):
     def __init__(self, a: Siglip2Config):
         super().__init__()
-        self.n_heads = a.n_heads
         self.layer_norm1 = nn.LayerNorm(a.dim, eps=a.layer_norm_eps)
-        self.q_proj, self.k_proj, self.v_proj, self.out_proj = (nn.Linear(a.dim, a.dim) for _ in range(4))
+        self.self_attn = _EncoderAttention(a)
         self.layer_norm2 = nn.LayerNorm(a.dim, eps=a.layer_norm_eps)
-        self.fc1, self.fc2 = nn.Linear(a.dim, a.ffn_dim), nn.Linear(a.ffn_dim, a.dim)
+        self.mlp = _EncoderMLP(a)
 
     def forward(self, x, key_mask):
-        N, L, D = x.shape
-        h = self.layer_norm1(x)
-        q, k, v = (p(h).view(N, L, self.n_heads, -1).transpose(1, 2) for p in (self.q_proj, self.k_proj, self.v_proj))
-        o = F.scaled_dot_product_attention(q, k, v, attn_mask=key_mask.view(N, 1, 1, L))   # bidirectional inside an image
-        x = x + self.out_proj(o.transpose(1, 2).reshape(N, L, D))
-        return x + self.fc2(F.gelu(self.fc1(self.layer_norm2(x)), approximate="tanh"))
+        x = x + self.self_attn(self.layer_norm1(x), key_mask)
+        return x + self.mlp(self.layer_norm2(x))
 
     def init_weights(self, **kwargs) -> None:
-        for m in (self.q_proj, self.k_proj, self.v_proj, self.out_proj, self.fc1, self.fc2):
-            nn.init.trunc_normal_(m.weight, mean=0.0, std=0.02)
-            nn.init.zeros_(m.bias)
+        self.self_attn.init_weights()
+        self.mlp.init_weights()
         self.layer_norm1.reset_parameters()
         self.layer_norm2.reset_parameters()
 
