@@ -226,7 +226,7 @@ def test_image_caption_datasets_folder_and_webdataset(tmp_path):
         return FluxDataLoader(cfg, dp_world_size=world, dp_rank=rank, local_batch_size=2)
 
     batches = list(loader("coco-validation", folder))
-    assert len(batches) == 3                                             # 7 readable images -> 3 full batches of 2
+    assert [b[1].shape[0] for b in batches] == [2, 2, 2, 1]              # 7 readable images in batches of 2
     inp, img = batches[0]
     assert img.shape == (2, 3, 32, 32) and float(img.min()) >= -1 and float(img.max()) <= 1
     assert inp["t5_tokens"].shape == (2, 16) and inp["clip_tokens"].shape == (2, 8)
@@ -234,7 +234,7 @@ def test_image_caption_datasets_folder_and_webdataset(tmp_path):
     # web-dataset shards, split over two data-parallel ranks by shard
     r0 = [p for b in loader("cc12m-wds", wds, 0, 2) for p in b[0]["prompt"]]
     r1 = [p for b in loader("cc12m-wds", wds, 1, 2) for p in b[0]["prompt"]]
-    assert r0 == ["caption 0", "caption 2", "caption 4", "caption 6"] and r1 == ["caption 1", "caption 3"]
+    assert r0 == ["caption 0", "caption 2", "caption 4", "caption 6"] and r1 == ["caption 1", "caption 3", "caption 5"]
     # resume: the state counts consumed samples
     dl = loader("cc12m-test", folder)
     it = iter(dl)
@@ -274,7 +274,12 @@ def test_image_caption_datasets_folder_and_webdataset(tmp_path):
                                                clip_max_length=8, classifier_free_guidance_prob=0.0, test_tokenizer=True,
                                                infinite=False, generate_timesteps=True), dp_world_size=1, dp_rank=0, local_batch_size=2)
     ts = torch.cat([b[0]["timestep"] for b in val])
-    assert torch.allclose(ts, torch.tensor([(i + 0.5) / 8 for i in range(6)]))
+    assert torch.allclose(ts, torch.tensor([(i + 0.5) / 8 for i in range(7)]))
+    # loader workers: decoding runs in two worker processes that share the rank's samples between them
+    w2 = FluxDataLoader(FluxDataLoader.Config(dataset="cc12m-test", dataset_path=str(folder), img_size=32, t5_max_length=16,
+                                              clip_max_length=8, classifier_free_guidance_prob=0.0, test_tokenizer=True,
+                                              infinite=False, num_workers=2), dp_world_size=1, dp_rank=0, local_batch_size=1)
+    assert sorted(b[0]["prompt"][0] for b in w2) == [f"a picture number {i}" for i in range(7)]
     # images smaller than the target are skipped
     small = FluxDataLoader(FluxDataLoader.Config(dataset="cc12m-test", dataset_path=str(folder), img_size=48, t5_max_length=16,
                                                  clip_max_length=8, classifier_free_guidance_prob=0.0, test_tokenizer=True,
@@ -304,7 +309,7 @@ def test_image_caption_datasets_folder_and_webdataset(tmp_path):
     fd.DATASETS["mine"] = DatasetConfig(path=str(tmp_path), loader=Mine, sample_processor=mine_processor)
     try:
         got = [p for b in loader("mine", tmp_path, 1, 2) for p in b[0]["prompt"]]
-        assert got == ["mine 1", "mine 3"]                               # rank 1 of 2, batches of 2, grey images become RGB
+        assert got == ["mine 1", "mine 3", "mine 5"]                     # rank 1 of 2, grey images become RGB
     finally:
         del fd.DATASETS["mine"]
     import pytest

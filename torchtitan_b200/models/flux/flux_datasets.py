@@ -35,7 +35,7 @@ from typing import Any, Callable
 import torch
 from torch.utils.data import IterableDataset
 
-from torchtitan_b200.components.dataloader import BaseDataLoader
+from torchtitan_b200.components.dataloader import ParallelAwareDataloader
 from torchtitan_b200.hf_datasets import DatasetConfig
 from torchtitan_b200.tools.logging import logger
 
@@ -230,6 +230,12 @@ def _validate_dataset(dataset_name: str, dataset_path: str | None = None) -> tup
 
 
 # ------------------------------------------------------------------------------------------ datasets
+def _worker() -> tuple[int, int]:
+    """(index, count) of the loader worker process this code runs in; (0, 1) in the main process."""
+    info = torch.utils.data.get_worker_info()
+    return (info.id, info.num_workers) if info is not None else (0, 1)
+
+
 class FluxDataset(IterableDataset):
     """This data-parallel rank's share of a registered image-caption dataset, processed for FLUX."""
 
@@ -251,8 +257,10 @@ class FluxDataset(IterableDataset):
         self._t5, self._clip = t5_tokenizer, clip_tokenizer
         self._t5_empty, self._clip_empty = t5_tokenizer.encode(""), clip_tokenizer.encode("")
         self.classifier_free_guidance_prob, self.img_size, self.infinite = classifier_free_guidance_prob, img_size, infinite
-        self._gen = torch.Generator().manual_seed(seed * 7919 + dp_rank)
+        self._seed = seed * 7919 + dp_rank
+        self._gen = torch.Generator().manual_seed(self._seed)
         self._sample_idx = 0                                   # raw samples consumed in the current pass
+        self._restored = self._in_worker = False
 
     def _own_state(self) -> bool:
         """Hugging Face iterable datasets resume through their own ``state_dict``; everything else by skipping."""
@@ -266,7 +274,21 @@ class FluxDataset(IterableDataset):
             return iter(self._data.skip(self._sample_idx)) if self._sample_idx < len(self._data) else iter(())
         return itertools.islice(iter(self._data), self._sample_idx, None)
 
+    def _enter_worker(self) -> None:
+        """First iteration inside a loader worker: this copy of the dataset keeps every k-th local sample (Hugging Face
+        datasets deal their shards to the workers themselves) and draws from its own random stream."""
+        wid, workers = _worker()
+        if workers == 1 or self._in_worker:
+            return
+        self._in_worker = True
+        if isinstance(self._data, LocalSamples):
+            d = self._data
+            self._data = d.shard(d.rank * workers + wid, d.world * workers)
+        if not self._restored:
+            self._gen.manual_seed(self._seed * 1_000_003 + wid + 1)
+
     def __iter__(self):
+        self._enter_worker()
         it = self._raw()
         while True:
             sample = next(it, None)
@@ -310,6 +332,7 @@ class FluxDataset(IterableDataset):
         return state
 
     def load_state_dict(self, state_dict):
+        self._restored = True
         if "rng" in state_dict:
             self._gen.set_state(state_dict["rng"])
         if self._own_state():
@@ -337,29 +360,38 @@ class FluxValidationDataset(FluxDataset):
 
 class SyntheticFluxDataset(IterableDataset):
     """Random images and token ids, a different stream per data-parallel rank; both token rows are zeroed together with
-    probability ``cfg_prob``; ``generate_timesteps`` attaches the stratified validation noise levels in turn."""
+    probability ``cfg_prob``; ``generate_timesteps`` attaches the stratified validation noise levels in turn. A loader
+    that is not ``infinite`` gets 256 samples per rank."""
 
     def __init__(self, img_size: int, t5_len: int, clip_len: int, cfg_prob: float, rank: int, world: int, seed: int = 0,
-                 t5_vocab: int = 32128, clip_vocab: int = 49408, generate_timesteps: bool = False):
+                 t5_vocab: int = 32128, clip_vocab: int = 49408, generate_timesteps: bool = False, length: int | None = None):
+        self.length = length                                   # samples per rank before the stream ends; None = endless
         self.img_size, self.t5_len, self.clip_len, self.cfg_prob = img_size, t5_len, clip_len, cfg_prob
         self.rank, self.world, self.seed, self.t5_vocab, self.clip_vocab = rank, world, seed, t5_vocab, clip_vocab
         self.generate_timesteps = generate_timesteps
         self._n = 0
 
+    def _sample(self, n: int):
+        g = torch.Generator().manual_seed((self.seed * 7919 + self.rank) * 1_000_003 + n)
+        h = int(torch.randint(self.img_size, 2 * self.img_size, (1,), generator=g))
+        w = int(torch.randint(self.img_size, 2 * self.img_size, (1,), generator=g))
+        img = process_image(torch.rand(3, h, w, generator=g), self.img_size)
+        empty = bool(torch.rand((), generator=g) < self.cfg_prob)
+        t5 = torch.zeros(self.t5_len, dtype=torch.long) if empty else torch.randint(1, self.t5_vocab, (self.t5_len,), generator=g)
+        clip = torch.zeros(self.clip_len, dtype=torch.long) if empty else torch.randint(1, self.clip_vocab, (self.clip_len,), generator=g)
+        inputs = {"clip_tokens": clip, "t5_tokens": t5}
+        if self.generate_timesteps:
+            inputs["timestep"] = (n % 8 + 0.5) / 8
+        return inputs, img
+
     def __iter__(self):
-        g = torch.Generator().manual_seed(self.seed * 7919 + self.rank)
-        while True:
-            h = int(torch.randint(self.img_size, 2 * self.img_size, (1,), generator=g))
-            w = int(torch.randint(self.img_size, 2 * self.img_size, (1,), generator=g))
-            img = process_image(torch.rand(3, h, w, generator=g), self.img_size)
-            empty = bool(torch.rand((), generator=g) < self.cfg_prob)
-            t5 = torch.zeros(self.t5_len, dtype=torch.long) if empty else torch.randint(1, self.t5_vocab, (self.t5_len,), generator=g)
-            clip = torch.zeros(self.clip_len, dtype=torch.long) if empty else torch.randint(1, self.clip_vocab, (self.clip_len,), generator=g)
-            inputs = {"clip_tokens": clip, "t5_tokens": t5}
-            if self.generate_timesteps:
-                inputs["timestep"] = (self._n % 8 + 0.5) / 8
+        # sample n depends on (seed, rank, n) only: a restored loader continues exactly, loader workers take every k-th
+        wid, workers = _worker()
+        while self.length is None or self._n < self.length:
+            n = self._n
             self._n += 1
-            yield inputs, img
+            if n % workers == wid:
+                yield self._sample(n)
 
     def state_dict(self):
         return {"n": self._n}
@@ -383,9 +415,13 @@ def _collate(items):
     return inputs, torch.stack([i[1] for i in items])
 
 
-class FluxDataLoader(BaseDataLoader):
+class FluxDataLoader(ParallelAwareDataloader):
+    """The FLUX dataset behind the stateful, worker-capable loader of the text pipeline: ``--dataloader.num_workers``
+    moves image decoding and resizing into worker processes; the loader state (per data-parallel rank) is part of the
+    checkpoint (torchtitan/models/flux/flux_datasets.py:387-463)."""
+
     @dataclass(kw_only=True, slots=True)
-    class Config(BaseDataLoader.Config):
+    class Config(ParallelAwareDataloader.Config):
         dataset: str = "synthetic"
         """``synthetic`` or a name registered in ``DATASETS``."""
         dataset_path: str | None = None
@@ -411,9 +447,10 @@ class FluxDataLoader(BaseDataLoader):
     def __init__(self, config: Config, *, dp_world_size: int, dp_rank: int, local_batch_size: int, **kwargs):
         self.config = config
         if config.dataset == "synthetic":
-            self.dataset = SyntheticFluxDataset(config.img_size, config.t5_max_length, config.clip_max_length,
+            ds = SyntheticFluxDataset(config.img_size, config.t5_max_length, config.clip_max_length,
                                                 config.classifier_free_guidance_prob, dp_rank, dp_world_size, seed=config.seed,
-                                                generate_timesteps=config.generate_timesteps)
+                                                generate_timesteps=config.generate_timesteps,
+                                                length=None if config.infinite else 256)
         else:
             from .tokenizer import build_flux_tokenizer
 
@@ -423,23 +460,8 @@ class FluxDataLoader(BaseDataLoader):
                 t5_max_length=enc.max_t5_encoding_len if config.t5_max_length == 256 else config.t5_max_length,
                 clip_max_length=config.clip_max_length, test_mode=config.test_tokenizer or enc.test_mode)
             cls = FluxValidationDataset if config.generate_timesteps else FluxDataset
-            self.dataset = cls(config.dataset, config.dataset_path, t5, clip, config.classifier_free_guidance_prob,
+            ds = cls(config.dataset, config.dataset_path, t5, clip, config.classifier_free_guidance_prob,
                                config.img_size, dp_rank, dp_world_size, infinite=config.infinite, seed=config.seed)
-        self.batch_size = local_batch_size
-
-    def __iter__(self):
-        it = iter(self.dataset)
-        while True:
-            items = []
-            for _ in range(self.batch_size):
-                try:
-                    items.append(next(it))
-                except StopIteration:
-                    return
-            yield _collate(items)
-
-    def state_dict(self):
-        return self.dataset.state_dict()
-
-    def load_state_dict(self, sd):
-        self.dataset.load_state_dict(sd)
+        super().__init__(ds, dp_rank=dp_rank, dp_world_size=dp_world_size, batch_size=local_batch_size, collate_fn=_collate,
+                         num_workers=config.num_workers, persistent_workers=config.persistent_workers,
+                         pin_memory=config.pin_memory, prefetch_factor=config.prefetch_factor)

@@ -22,8 +22,8 @@ class FluxValidator(BaseValidator):
     @dataclass(kw_only=True, slots=True)
     class Config(BaseValidator.Config):
         enable: bool = False
-        steps: int = 4
-        """Held-out batches per validation run."""
+        steps: int = -1
+        """Held-out batches per validation run; -1 = until the (finite) validation loader is exhausted."""
         timesteps: int = 8
         """Evenly spaced noise levels at which the loss is evaluated for every batch (``all_timesteps``)."""
         all_timesteps: bool = True
@@ -46,7 +46,13 @@ class FluxValidator(BaseValidator):
         else:
             import dataclasses
 
-            dl = dataclasses.replace(config.dataloader, generate_timesteps=not config.all_timesteps)
+            dl = dataclasses.replace(config.dataloader, generate_timesteps=not config.all_timesteps,
+                                     infinite=config.steps != -1)
+            if config.steps == -1:
+                from torchtitan_b200.tools.logging import logger
+
+                logger.warning("Setting validation steps to -1 might cause hangs because of unequal sample counts across ranks "
+                               "when dataset is exhausted.")
             self.dataloader = dl.build(dp_world_size=dp_world_size, dp_rank=dp_rank, local_batch_size=local_batch_size)
         self._tokenizers = None
         super().__init__(config)
@@ -92,8 +98,13 @@ class FluxValidator(BaseValidator):
         model.eval()
         total, count = 0.0, 0
         self._images_left, self._saved = self.save_img_count, 0
-        for _ in range(self.steps):
-            inputs, images = next(data_iterator)
+        done = 0
+        while self.steps == -1 or done < self.steps:
+            nxt = next(data_iterator, None)
+            if nxt is None:
+                break
+            done += 1
+            inputs, images = nxt
             given_t = inputs.pop("timestep", None) if isinstance(inputs, dict) else None
             batch = preprocess_data(tr.device, tr._dtype, autoencoder=tr.autoencoder, clip_encoder=tr.clip_encoder,
                                     t5_encoder=tr.t5_encoder, batch={**inputs, "image": images})
