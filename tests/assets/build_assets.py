@@ -2,7 +2,10 @@
 
 * ``tokenizer/``  -- a byte-level BPE tokenizer with a 2048-entry vocabulary (``tokenizer.json`` +
   ``tokenizer_config.json``) trained on the synthetic corpus below;
-* ``c4_test/data.json`` -- 2000 JSON-lines documents with a ``text`` field (stand-in for the C4 test split).
+* ``c4_test/data.json`` -- 2000 JSON-lines documents with a ``text`` field (stand-in for the C4 test split);
+* ``cc12m_test/cc12m-train-0000.tar`` -- 32 image-caption pairs in WebDataset layout (``<key>.jpg``, ``<key>.txt``,
+  ``<key>.json``): drawn gradients and shapes of 256-400 pixels with captions that describe them (stand-in for a CC12M
+  shard; the ``cc12m-test`` dataset of the FLUX and vision-language loaders).
 
 The corpus is generated from a fixed word list with a seeded RNG, so the outputs are reproducible:
 ``python tests/assets/build_assets.py``.
@@ -79,6 +82,50 @@ def write_custom_schedule() -> None:
             f.write(",".join(f"{a.stage}{a.kind}{a.mb}" for a in acts) + "\n")
 
 
+def write_cc12m_test(n: int = 32, seed: int = 7) -> None:
+    import io
+    import tarfile
+
+    from PIL import Image, ImageDraw
+
+    rng = random.Random(seed)
+    colours = {"red": (200, 40, 40), "green": (40, 160, 60), "blue": (40, 70, 200), "yellow": (220, 200, 50),
+               "purple": (130, 60, 170), "orange": (230, 130, 40), "white": (235, 235, 235), "black": (25, 25, 25)}
+    shapes = ("circle", "square", "triangle", "bar")
+    os.makedirs(os.path.join(HERE, "cc12m_test"), exist_ok=True)
+    with tarfile.open(os.path.join(HERE, "cc12m_test", "cc12m-train-0000.tar"), "w") as tar:
+        for i in range(n):
+            w, h = rng.randint(256, 400), rng.randint(256, 400)
+            (bg_name, bg), (fg_name, fg) = rng.sample(sorted(colours.items()), 2)
+            shape = rng.choice(shapes)
+            img = Image.new("RGB", (w, h), bg)
+            px = img.load()
+            for y in range(h):                                   # vertical shading keeps the JPEG from being one flat block
+                k = 0.75 + 0.25 * y / h
+                for x in range(0, w):
+                    px[x, y] = tuple(int(c * k) for c in bg)
+            d = ImageDraw.Draw(img)
+            cx, cy, r = rng.randint(w // 4, 3 * w // 4), rng.randint(h // 4, 3 * h // 4), rng.randint(30, min(w, h) // 4)
+            if shape == "circle":
+                d.ellipse((cx - r, cy - r, cx + r, cy + r), fill=fg)
+            elif shape == "square":
+                d.rectangle((cx - r, cy - r, cx + r, cy + r), fill=fg)
+            elif shape == "triangle":
+                d.polygon([(cx, cy - r), (cx - r, cy + r), (cx + r, cy + r)], fill=fg)
+            else:
+                d.rectangle((0, cy - r // 3, w, cy + r // 3), fill=fg)
+            caption = f"a {fg_name} {shape} on a {bg_name} background"
+            buf = io.BytesIO()
+            img.save(buf, format="JPEG", quality=80)
+            key = f"{i:09d}"
+            meta = json.dumps({"key": key, "width": w, "height": h, "caption": caption}).encode()
+            for name, data in ((f"{key}.jpg", buf.getvalue()), (f"{key}.json", meta), (f"{key}.txt", caption.encode())):
+                info = tarfile.TarInfo(name)
+                info.size = len(data)
+                tar.addfile(info, io.BytesIO(data))
+
+
 if __name__ == "__main__":
     main()
     write_custom_schedule()
+    write_cc12m_test()

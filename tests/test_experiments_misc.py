@@ -252,17 +252,20 @@ def test_vlm_loader_feeds_the_model_and_resumes():
     from torchtitan_b200.experiments.vlm import llama3_siglip2_configs
     from torchtitan_b200.experiments.vlm.datasets import MMDataLoader
 
-    cfg = MMDataLoader.Config(max_patches_per_image=16, max_images_per_batch=64)
+    cfg = MMDataLoader.Config(dataset="synthetic", max_patches_per_image=16, max_images_per_batch=64)
     dl = cfg.build(dp_world_size=1, dp_rank=0, tokenizer=None, seq_len=128, local_batch_size=2, model_vocab_size=2048)
     it = iter(dl)
-    batches = [next(it) for _ in range(3)]
+    batches = [next(it) for _ in range(2)]
+    state = dl.state_dict()
+    assert set(state) == {"dp_rank_0", "world_size"}                  # the per-rank state format of the text loader
+    batches.append(next(it))
     st = dl.special_tokens
     assert (st.img_id, st.pad_id) == (2044, 2047)
     for inputs, labels in batches:
         assert inputs["input"].shape == (2, 128) and labels.shape == (2, 128)
         assert int((inputs["input"] == st.img_id).sum()) == int((inputs["grid_thw"][:, :, 1:] != -1).all(-1).sum())
     dl2 = cfg.build(dp_world_size=1, dp_rank=0, tokenizer=None, seq_len=128, local_batch_size=2, model_vocab_size=2048)
-    dl2.load_state_dict({"batches": 2})
+    dl2.load_state_dict(state)
     again, _ = next(iter(dl2))
     assert torch.equal(again["input"], batches[2][0]["input"])
     import dataclasses

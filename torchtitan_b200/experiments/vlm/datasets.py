@@ -7,7 +7,7 @@ from dataclasses import dataclass
 
 import torch
 
-from torchtitan_b200.components.dataloader import BaseDataLoader
+from torchtitan_b200.components.dataloader import ParallelAwareDataloader
 
 from .model import SpecialTokens
 
@@ -128,17 +128,23 @@ class MultiModalCollatorNLD:
 
 
 class SyntheticMultiModalDataset(torch.utils.data.IterableDataset):
-    """Random text and random images of varying aspect ratio (offline stand-in for OBELICS / CC12M streams)."""
+    """Random text and random images of varying aspect ratio (offline stand-in for OBELICS / CC12M streams). The stream
+    is a pure function of (seed, rank, loader worker); its state is the number of rows handed out, and a restored copy
+    regenerates and skips that many."""
 
     def __init__(self, st: SpecialTokens, vocab: int, seq_len: int, patch: int = 16, max_patches: int = 64, seed: int = 0,
                  dp_rank: int = 0, dp_world_size: int = 1):
         self.st, self.vocab, self.seq_len, self.patch, self.max_patches = st, vocab, seq_len, patch, max_patches
         self.seed, self.rank, self.world = seed, dp_rank, dp_world_size
+        self._rows = 0
 
     def __iter__(self):
-        g = torch.Generator().manual_seed(self.seed * 1000 + self.rank)
+        info = torch.utils.data.get_worker_info()
+        wid = info.id if info is not None else 0
+        g = torch.Generator().manual_seed((self.seed * 1000 + self.rank) * 64 + wid)
         packer = SamplePacker(self.seq_len, self.st)
         reserved = {self.st.img_id, self.st.boi_id, self.st.eoi_id, self.st.pad_id}
+        skip, self._rows = self._rows, 0
         while True:
             n_txt = int(torch.randint(8, 64, (1,), generator=g))
             ids = [t for t in torch.randint(0, self.vocab, (n_txt,), generator=g).tolist() if t not in reserved]
@@ -150,30 +156,44 @@ class SyntheticMultiModalDataset(torch.utils.data.IterableDataset):
             sample = process_sample(ids[: n_txt // 2], imgs, ids[n_txt // 2 :], self.st, self.patch, self.max_patches)
             out = packer.add(*sample)
             if out is not None:
-                yield out
+                self._rows += 1
+                if self._rows > skip:
+                    yield out
+
+    def state_dict(self):
+        return {"rows": self._rows}
+
+    def load_state_dict(self, state):
+        self._rows = int(state.get("rows", 0))
 
 
-class MMDataLoader(BaseDataLoader):
+class MMDataLoader(ParallelAwareDataloader):
     """Packed multimodal batches for the trainer: ``({"input", "pixel_values", "grid_thw", "special_tokens"}, labels)``.
 
-    Reference: torchtitan/experiments/vlm/datasets/mm_datasets.py (the loader built from the job configuration). The
-    ``synthetic`` dataset needs no files; its special tokens take the last four ids of the model's vocabulary."""
+    Reference: torchtitan/experiments/vlm/datasets/mm_datasets.py:370-453 (the loader built from the job configuration,
+    on the stateful loader of the text pipeline: ``num_workers`` moves image decoding into worker processes and the
+    loader state per data-parallel rank goes into the checkpoint). The ``synthetic`` dataset needs no files; when the
+    tokenizer has no image tokens the special tokens take the last four ids of the model's vocabulary."""
 
     @dataclass(kw_only=True, slots=True)
-    class Config(BaseDataLoader.Config):
-        dataset: str = "synthetic"
+    class Config(ParallelAwareDataloader.Config):
+        dataset: str = "cc12m-test"
+        """``synthetic``, or a name registered in ``mm_datasets.MM_DATASETS`` (``obelics``, ``cc12m``, ``cc12m-test``)."""
         dataset_path: str | None = None
         infinite: bool = True
+        max_images_per_batch: int = 10
+        """Vision encoder batch: images beyond it are dropped from the batch with a warning."""
+        max_patches_per_image: int = 256
+        """Larger images are scaled down keeping the aspect ratio."""
         patch_size: int = 16
         spatial_merge_size: int = 1
-        max_patches_per_image: int = 64
-        max_images_per_batch: int = 32
         packing_buffer_size: int = 0
+        """Samples buffered for packing several into one row; 0 = one sample per row."""
         seed: int = 0
 
     def __init__(self, config: Config, *, dp_world_size: int, dp_rank: int, tokenizer=None, seq_len: int, local_batch_size: int,
                  model_vocab_size: int | None = None, **kwargs):
-        self.config, self.batch_size = config, local_batch_size
+        self.config = config
         try:
             st = SpecialTokens.from_tokenizer(tokenizer)
         except Exception:
@@ -183,46 +203,26 @@ class MMDataLoader(BaseDataLoader):
         self.synthetic = config.dataset == "synthetic"
         if self.synthetic:
             vocab = min(i for i in (st.img_id, st.boi_id, st.eoi_id, st.pad_id))
-            self.dataset = SyntheticMultiModalDataset(st, vocab=vocab, seq_len=seq_len, patch=config.patch_size,
-                                                      max_patches=config.max_patches_per_image, seed=config.seed,
-                                                      dp_rank=dp_rank, dp_world_size=dp_world_size)
+            ds = SyntheticMultiModalDataset(st, vocab=vocab, seq_len=seq_len, patch=config.patch_size,
+                                            max_patches=config.max_patches_per_image, seed=config.seed,
+                                            dp_rank=dp_rank, dp_world_size=dp_world_size)
         else:
             from .mm_datasets import InterleavedDataset
 
             assert tokenizer is not None, "image-text datasets need a tokenizer"
             if config.spatial_merge_size != 1:
                 raise NotImplementedError("spatial_merge_size > 1: the projector of this model does not merge patches")
-            self.dataset = InterleavedDataset(config.dataset, config.dataset_path, tokenizer, st, seq_len=seq_len,
-                                              patch=config.patch_size, max_patches=config.max_patches_per_image,
-                                              merge=config.spatial_merge_size, packing_buffer_size=config.packing_buffer_size,
-                                              dp_rank=dp_rank, dp_world_size=dp_world_size, infinite=config.infinite)
+            ds = InterleavedDataset(config.dataset, config.dataset_path, tokenizer, st, seq_len=seq_len,
+                                    patch=config.patch_size, max_patches=config.max_patches_per_image,
+                                    merge=config.spatial_merge_size, packing_buffer_size=config.packing_buffer_size,
+                                    dp_rank=dp_rank, dp_world_size=dp_world_size, infinite=config.infinite)
         self.collate = MultiModalCollatorNLD(patch_dim=3 * config.patch_size ** 2, max_images_per_batch=config.max_images_per_batch,
                                              max_patches_per_image=config.max_patches_per_image, special_tokens=st)
-        self._batches = 0
+        # a finite dataset's last short batch is dropped: the collator pads to fixed image counts, not to a batch size
+        super().__init__(ds, dp_rank=dp_rank, dp_world_size=dp_world_size, batch_size=local_batch_size, collate_fn=self.collate,
+                         drop_last=True, num_workers=config.num_workers, persistent_workers=config.persistent_workers,
+                         pin_memory=config.pin_memory, prefetch_factor=config.prefetch_factor)
 
-    def __iter__(self):
-        it = iter(self.dataset)
-        if self.synthetic:
-            for _ in range(self._batches * self.batch_size):      # resume: the stream is a pure function of (seed, rank)
-                next(it)
-        while True:
-            batch = []
-            for row in it:
-                batch.append(row)
-                if len(batch) == self.batch_size:
-                    break
-            if len(batch) < self.batch_size:                      # a finite dataset ran out: the last short batch is dropped
-                return
-            self._batches += 1
-            yield self.collate(batch)
 
-    def state_dict(self):
-        state = {"batches": self._batches}
-        if not self.synthetic:
-            state["dataset"] = self.dataset.state_dict()
-        return state
-
-    def load_state_dict(self, state_dict):
-        self._batches = int(state_dict.get("batches", 0)) if state_dict else 0
-        if state_dict and not self.synthetic and "dataset" in state_dict:
-            self.dataset.load_state_dict(state_dict["dataset"])
+#: the reference's name for the loader class
+HuggingFaceMultiModalDataLoader = MMDataLoader

@@ -1,9 +1,10 @@
 """FLUX job configurations (torchtitan/models/flux/config_registry.py:24-195: the same batch sizes, step counts,
 guidance probability, sampling and validation settings).
 
-``flux_debugmodel`` runs without any downloaded asset: random images and token ids (``--dataloader.dataset cc12m-test
---dataloader.dataset_path <folder>`` switches to real files) and randomly initialised encoders of the model's input
-widths (``--encoder.random_init False`` loads the checkpoints the ``--encoder.*`` fields name)."""
+``flux_debugmodel`` runs without any downloaded asset: the image-caption shard under ``tests/assets/cc12m_test``
+(``--dataloader.dataset synthetic`` needs no files at all), the asset-free tokenizer when the tokenizer folders are
+absent, and randomly initialised encoders of the model's input widths (``--encoder.random_init False`` loads the
+checkpoints the ``--encoder.*`` fields name)."""
 
 from torchtitan_b200.components.checkpoint import CheckpointManager
 from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
@@ -26,7 +27,7 @@ def flux_debugmodel() -> FluxTrainer.Config:
     return FluxTrainer.Config(
         hf_assets_path="tests/assets/tokenizer", metrics=MetricsProcessor.Config(log_freq=1),
         model_spec=model_registry("flux-debug"), tokenizer=None,
-        dataloader=FluxDataLoader.Config(dataset="synthetic", classifier_free_guidance_prob=0.447, img_size=256, encoder=encoder),
+        dataloader=FluxDataLoader.Config(dataset="cc12m-test", classifier_free_guidance_prob=0.447, img_size=256, encoder=encoder),
         optimizer=OptimizersContainer.Config(lr=8e-4), lr_scheduler=LRSchedulersContainer.Config(warmup_steps=1, decay_ratio=0.0),
         training=TrainingConfig(local_batch_size=4, seq_len=512, steps=10, max_norm=2.0),
         encoder=encoder, checkpoint=CheckpointManager.Config(interval=10, last_save_model_only=False),
@@ -34,7 +35,7 @@ def flux_debugmodel() -> FluxTrainer.Config:
         validation=Validation(enable_classifier_free_guidance=True, classifier_free_guidance_scale=5.0, denoising_steps=4),
         validator=FluxValidator.Config(
             freq=5, steps=48, all_timesteps=False, save_img_count=1, save_img_folder="img",
-            dataloader=FluxDataLoader.Config(dataset="synthetic", classifier_free_guidance_prob=0.447, img_size=256,
+            dataloader=FluxDataLoader.Config(dataset="cc12m-test", classifier_free_guidance_prob=0.447, img_size=256,
                                              generate_timesteps=True, encoder=encoder)),
         inference=Inference(save_img_folder="inference_results",
                             prompts_path="./torchtitan_b200/models/flux/inference/prompts.txt", local_batch_size=2),

@@ -422,7 +422,7 @@ class FluxDataLoader(ParallelAwareDataloader):
 
     @dataclass(kw_only=True, slots=True)
     class Config(ParallelAwareDataloader.Config):
-        dataset: str = "synthetic"
+        dataset: str = "cc12m-test"
         """``synthetic`` or a name registered in ``DATASETS``."""
         dataset_path: str | None = None
         """Local copy (or another hub name); default: the registry entry's path."""

@@ -32,7 +32,7 @@ class FluxValidator(BaseValidator):
         save_img_count: int = 0
         """Images sampled from the validation prompts per validation run (-1: one for every prompt seen)."""
         save_img_folder: str = "validation_images"
-        dataloader: FluxDataLoader.Config = field(default_factory=lambda: FluxDataLoader.Config(dataset="synthetic"))
+        dataloader: FluxDataLoader.Config = field(default_factory=lambda: FluxDataLoader.Config(dataset="coco-validation", generate_timesteps=True))
 
     def __init__(self, config=None, trainer=None, steps: int = 4, timesteps: int = 8, save_img_count: int = 0,
                  save_img_folder: str = "img", *, dp_world_size: int = 1, dp_rank: int = 0, local_batch_size: int = 1,
