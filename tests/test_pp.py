@@ -210,3 +210,71 @@ def test_keyword_arguments_are_cut_per_micro_batch():
     assert got[0]["attention_masks"]["nope"].doc_ids is None
     assert got[0]["positions"].shape == (1, 6) and got[0]["flag"] is True
     assert _micro_batch_of(masks, 1, 0, 4) is masks
+
+
+def _fsdp_worker(rank, world, schedule, ac_mode):
+    """pp 2 x dp_shard 2: every pipeline stage is wrapped in FSDP units, the backward steps are split, and the units'
+    gradient reductions run at the end of the weight-gradient steps."""
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo")
+    from torchtitan_b200.components.loss import cross_entropy_loss
+    from torchtitan_b200.config import ActivationCheckpointConfig, CompileConfig, ParallelismConfig, TrainingConfig
+    from torchtitan_b200.models.llama3 import llama3_configs
+    from torchtitan_b200.models.llama3.parallelize import parallelize_llama
+    from torchtitan_b200.parallel import ParallelDims, fsdp
+    from torchtitan_b200.parallel.pp import pipeline_llm
+    from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
+
+    pd = ParallelDims(dp_replicate=1, dp_shard=2, cp=1, tp=1, pp=2, ep=1, etp=1, world_size=world)
+    dp_rank = pd.coordinate("fsdp", rank)
+    cfg = dataclasses.replace(llama3_configs["debugmodel_gqa"], n_layers=4)
+    cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=32)
+    torch.manual_seed(3)
+    ref = cfg.build()
+    ref.init_weights()
+    full_state = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    B = 4
+    x_all = torch.randint(0, cfg.vocab_size, (2 * B, 33), generator=torch.Generator().manual_seed(9))
+    x = x_all[dp_rank * B:(dp_rank + 1) * B]                    # the two data-parallel ranks see different rows
+    inp, lab = x[:, :-1], x[:, 1:]
+    training = TrainingConfig(local_batch_size=B, seq_len=32, mixed_precision_param="float32", mixed_precision_reduce="float32")
+    par = ParallelismConfig(pipeline_parallel_degree=2, data_parallel_shard_degree=2, pipeline_parallel_schedule=schedule,
+                            pipeline_parallel_microbatch_size=1)
+    model = cfg.build()
+    model.init_weights()                                         # also builds the rotary table, which is not part of the state
+    model.load_state_dict(full_state)
+    sched, parts, first, last = pipeline_llm(
+        model, parallel_dims=pd, training=training, model_converters=ModelConvertersContainer.Config(), parallelism=par,
+        compile_config=CompileConfig(), ac_config=ActivationCheckpointConfig(mode=ac_mode), dump_folder="/tmp",
+        device=torch.device("cpu"), model_config=cfg, parallelize_fn=parallelize_llama, loss_fn=cross_entropy_loss,
+    )
+    for part in parts:
+        assert fsdp.fsdp_units(part)
+        fsdp.materialize(part)
+    losses = [] if last else None
+    scale = torch.tensor(1.0 / (2 * lab.numel()))                # per global token: the units sum over data-parallel ranks
+    for _ in range(2):                                           # a second step accumulates onto the first one's gradients
+        if first:
+            sched.step(inp, target=lab if last else None, losses=losses, loss_scale=scale)
+        else:
+            sched.step(target=lab if last else None, losses=losses, loss_scale=scale)
+    inp_all, lab_all = x_all[:, :-1], x_all[:, 1:]
+    ref_loss = cross_entropy_loss(ref(inp_all), lab_all) / lab_all.numel()
+    (2 * ref_loss).backward()                                    # two identical steps, gradients add up
+    ref_grads = dict(ref.named_parameters())
+    err = 0.0
+    for part in parts:
+        for name, p in part.named_parameters():
+            g = p.grad.full_tensor() if hasattr(p.grad, "full_tensor") else p.grad
+            err = max(err, (g - ref_grads[name].grad).abs().max().item())
+    return {"grad_err": err, "kinds": "".join(sorted({a.kind for a in sched.all_actions[pd.coordinate("pp", rank)]})),
+            "loss": float(torch.stack(losses).sum()) if last else None}
+
+
+@pytest.mark.parametrize("schedule,ac_mode", [("ZBVZeroBubble", "none"), ("InterleavedZeroBubble", "full"), ("DualPipeV", "selective")])
+def test_split_backward_under_fsdp_matches_single_process(tmp_path, schedule, ac_mode):
+    res = run_ranks(_fsdp_worker, 4, schedule, ac_mode, tmp_path=tmp_path)
+    assert all("I" in o["kinds"] and "W" in o["kinds"] and "B" not in o["kinds"] for o in res), res
+    assert max(o["grad_err"] for o in res) < 1e-5, res
+    assert any(o["loss"] is not None for o in res)

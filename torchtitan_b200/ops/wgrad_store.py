@@ -9,10 +9,13 @@ independent GEMMs, ``dx = dy @ W`` and ``dW = dy^T @ x``. While the runtime is i
 (:meth:`WeightGradStore.collect`), :class:`_SplitLinearFn` computes ``dx`` only and parks a closure that holds ``dy``
 and ``x``; the ``W`` action runs the parked closures, which accumulate into ``weight.grad``.
 
-Only weights that are autograd leaves are deferred (plain ``nn.Parameter``s, also local tensor-parallel shards); a
-weight that reaches the layer through another autograd node (an FSDP unit's gathered copy) gets its gradient at once,
-because that node's own backward needs it. Everything that is not a linear layer (norm weights, embeddings, expert
-GEMMs, quantised linears) is also computed inside ``I``: those are a few percent of a dense transformer's backward.
+A weight is deferred when it is an autograd leaf (a plain ``nn.Parameter``, also a local tensor-parallel shard), or
+when it is the gathered copy an FSDP / replicate unit handed out: the unit tags its copies with ``_wgrad_sink = (unit,
+index)``, the parked closure puts its result into the unit's box for that backward pass, and the unit queues its
+reduce-scatter behind the closures (``parallel/fsdp.py::_park_post_backward``), so ``W`` ends with one reduction of the
+complete gradients. Any other non-leaf weight gets its gradient at once. Everything that is not a linear layer (norm
+weights, embeddings, expert GEMMs, quantised linears) is also computed inside ``I``: those are a few percent of a dense
+transformer's backward.
 """
 
 from __future__ import annotations
@@ -79,7 +82,7 @@ class _SplitLinearFn(torch.autograd.Function):
     ``w`` itself, or the fp32 parameter of which ``w`` is the autocast copy."""
 
     @staticmethod
-    def forward(ctx, x, w, bias, leaf):
+    def forward(ctx, x, w, bias, leaf, sink=None):
         x2 = _rows2d(x)
         native = _native(x2, w)
         if native:
@@ -88,7 +91,7 @@ class _SplitLinearFn(torch.autograd.Function):
         if bias is not None:
             y = y + bias
         ctx.save_for_backward(x2, w)
-        ctx.native, ctx.has_bias, ctx.xshape, ctx.leaf = native, bias is not None, x.shape, leaf
+        ctx.native, ctx.has_bias, ctx.xshape, ctx.leaf, ctx.sink = native, bias is not None, x.shape, leaf, sink
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -102,7 +105,15 @@ class _SplitLinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.float().sum(0).to(gy.dtype)
         if ctx.needs_input_grad[1]:
-            if leaf is not None and WeightGradStore.collecting():
+            if ctx.sink is not None and WeightGradStore.collecting():
+                unit, index = ctx.sink
+                box = unit.wgrad_box()
+
+                def weight_grad_to_unit(g2=g2, x2=x2, box=box, index=index, native=native):
+                    gw = _mm(g2, x2, True, True, native)
+                    box[index] = gw if index not in box else box[index] + gw
+                WeightGradStore.put(weight_grad_to_unit)
+            elif leaf is not None and WeightGradStore.collecting():
                 def weight_grad(g2=g2, x2=x2, leaf=leaf, native=native):
                     gw = _mm(g2, x2, True, True, native)
                     if leaf.grad is None:
@@ -112,14 +123,15 @@ class _SplitLinearFn(torch.autograd.Function):
                 WeightGradStore.put(weight_grad)
             else:
                 gw = _mm(g2, x2, True, True, native)
-        return gx, gw, gb, None
+        return gx, gw, gb, None, None
 
 
 def split_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """Linear layer for runs with :attr:`WeightGradStore.enabled`; same values as the ordinary path."""
     leaf = weight if (weight.is_leaf and weight.requires_grad and type(weight) in (torch.Tensor, torch.nn.Parameter)) else None
+    sink = getattr(weight, "_wgrad_sink", None) if leaf is None else None
     if x.is_cuda and torch.is_autocast_enabled() and weight.dtype == torch.float32:
         x, w = x.to(torch.bfloat16), weight.to(torch.bfloat16)
         bias = None if bias is None else bias.to(torch.bfloat16)
-        return _SplitLinearFn.apply(x, w, bias, leaf)
-    return _SplitLinearFn.apply(x, weight, bias, leaf)
+        return _SplitLinearFn.apply(x, w, bias, leaf, None)
+    return _SplitLinearFn.apply(x, weight, bias, leaf, sink)

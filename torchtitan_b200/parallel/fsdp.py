@@ -39,6 +39,8 @@ import torch.distributed as dist
 import torch.nn as nn
 from torch.distributed.tensor import DTensor, Replicate, Shard
 
+from torchtitan_b200.ops.wgrad_store import WeightGradStore
+
 __all__ = [
     "MixedPrecisionPolicy",
     "fully_shard",
@@ -226,6 +228,8 @@ class _UnitGather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, unit, anchor):
         ctx.unit = unit
+        if WeightGradStore.enabled:
+            ctx.set_materialize_grads(False)      # a parked weight gradient arrives later, not as a tensor of zeros now
         outs = tuple(p.unsharded.view_as(p.unsharded) for p in unit.params)
         frozen = [o for o, p in zip(outs, unit.params) if not p.param.requires_grad]
         if frozen:
@@ -234,7 +238,10 @@ class _UnitGather(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        ctx.unit._post_backward(list(grads))
+        if WeightGradStore.collecting():
+            ctx.unit._park_post_backward(list(grads))
+        else:
+            ctx.unit._post_backward(list(grads))
         return None, None
 
 
@@ -328,6 +335,7 @@ class FSDPUnit:
         self._fwd_params = None
         self.params_version = 0  # bumped (in lockstep on all ranks) whenever the master shard changes
         self._slots: list = []
+        self._wgrad_box: dict | None = None      # parked weight gradients of the backward pass in progress (index -> tensor)
         self._slot_written: list = []
         self._slot_accumulate = False
         self.is_root = False
@@ -589,7 +597,14 @@ class FSDPUnit:
         # the same tensor objects are re-bound for recompute in backward; with several forwards in flight before the
         # first backward (pipeline micro-batches) each backward needs ITS forward's tensors, so the output hooks carry them
         self._fwd_params = outs
-        if self._slots:
+        if WeightGradStore.enabled:
+            # split backward steps (zero-bubble pipeline schedules): linear layers park their weight-gradient GEMMs and
+            # hand the result to this unit later, see _park_post_backward. Gradient slots are not used then: several
+            # micro-batches can be between their two halves at once and would share one staging buffer
+            if self._needs_grad():
+                for i, o in enumerate(outs):
+                    o._wgrad_sink = (self, i)
+        elif self._slots:
             for o, slot in zip(outs, self._slots):
                 if slot is not None:
                     o._grad_slot = slot
@@ -645,7 +660,36 @@ class FSDPUnit:
             _BackwardEnd.register(self)
         return grad
 
+    def wgrad_box(self) -> dict:
+        """Where the parked weight-gradient closures of the backward pass in progress put their results."""
+        if self._wgrad_box is None:
+            self._wgrad_box = {}
+        return self._wgrad_box
+
+    def _park_post_backward(self, grads):
+        """Input-gradient half of a split backward step: keep what autograd delivered (norm weights, biases, everything
+        that is not a parked linear weight), leave backward mode, and queue the reduction behind the parked GEMMs of this
+        pass; the weight-gradient half runs the queue in order, so the reduction sees the complete set."""
+        box, self._wgrad_box = self.wgrad_box(), None
+
+        def reduce_parked(unit=self, grads=grads, box=box):
+            for i, gw in box.items():
+                grads[i] = gw if grads[i] is None else grads[i] + gw.to(grads[i].dtype)
+            box.clear()
+            guard = getattr(unit.comm, "before_grad_writes", None)
+            if guard is not None:
+                guard(unit)          # a reduction of another micro-batch may have run since this pass entered backward
+            unit._reduce_grads(grads)
+            unit.wait_for_reduce()
+
+        WeightGradStore.put(reduce_parked)
+        self._finish_backward()
+
     def _post_backward(self, grads):
+        self._reduce_grads(grads)
+        self._finish_backward()
+
+    def _reduce_grads(self, grads):
         # parameters replicated over tensor parallel saw only a sequence shard: sum their gradients
         for i, p in enumerate(self.params):
             if p.tp_spec is not None and p.tp_spec[0] == "replicate" and grads[i] is not None:
@@ -667,7 +711,6 @@ class FSDPUnit:
         for i, p in enumerate(self.params):
             if p.param.requires_grad and p.param.grad is None:
                 p.param.grad = self._grad_view(i)
-        self._finish_backward()
 
     def _finish_backward(self):
         self._in_backward = False
@@ -718,7 +761,12 @@ class _BackwardEnd:
         units, cls._pending, cls._queued = cls._pending, [], False
         for u in units:
             if u._in_backward:
-                u._finish_backward()
+                if WeightGradStore.collecting() and u._wgrad_box is not None:
+                    # every gradient of the unit was parked (a unit of bias-free linear layers): its gather node had
+                    # nothing to run on, the reduction still has to follow the parked GEMMs
+                    u._park_post_backward([None] * len(u.params))
+                else:
+                    u._finish_backward()
             u.wait_for_reduce()
 
 

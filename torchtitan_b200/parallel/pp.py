@@ -713,13 +713,13 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
         )
     from .fsdp import fsdp_units
 
-    # weight gradients can be parked only where the weights own their .grad (no FSDP / replicate units on the stages)
-    can_split = not any(fsdp_units(m) for m in parts)
-    wanted_split = schedule in ZERO_BUBBLE
+    # weight gradients of linear layers can be parked wherever the weight owns its .grad (pipeline-only, tensor parallel)
+    # or comes from an FSDP / replicate unit, which then queues its gradient reduction behind the parked GEMMs
+    can_split = True
+    sharded = any(fsdp_units(m) for m in parts)
     if csv_path:
         all_actions = load_csv_actions(csv_path)
         assert len(all_actions) == pp, f"CSV schedule has {len(all_actions)} rows for {pp} pipeline ranks"
-        wanted_split = any(a.kind in ("I", "W") for acts in all_actions for a in acts)
         if not can_split:
             all_actions = fuse_split_backward(all_actions)
     else:
@@ -742,12 +742,6 @@ def pipeline_llm(model: nn.Module, *, parallel_dims, training, model_converters,
                 f"{estimate_makespan(all_actions, num_stages)[1]:.1%} of the step")
     if has_split:
         logger.info("Pipeline backward steps are split: input gradients are sent on first, the weight gradients of the "
-                    "linear layers run where the rank would wait")
-    elif wanted_split:
-        # said at start-up, not only in the documentation
-        logger.warning(
-            f"Pipeline schedule {csv_path or schedule}: the stages are under FSDP / replicate units, whose gradient "
-            "reduction consumes the weight gradients inside the backward pass, so input- and weight-gradient work is not "
-            "split: the schedule keeps its stage placement and runs whole backward steps in a list-scheduled order "
-            "(same results, a larger bubble than the split order; see the estimate above).")
+                    "linear layers run where the rank would wait"
+                    + (" and end with the FSDP / replicate units' gradient reduction" if sharded else ""))
     return sched, parts, sched.has_first, sched.has_last
