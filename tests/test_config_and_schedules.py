@@ -189,3 +189,37 @@ def test_cross_entropy_is_a_token_sum_that_skips_ignored_labels():
     assert lb.dtype == torch.float32 and math.isfinite(float(lb))
     mse = build_mse_loss()(torch.ones(3, 4), torch.zeros(3, 4))
     assert float(mse) == 12.0
+
+
+def test_every_registered_job_configuration_parses(monkeypatch):
+    """``--module <m> --config <c>`` goes through the command-line parser for every job configuration of every model
+    family and experiment, including those whose converter list holds two converter kinds (both nested classes are
+    called ``Config``, which the parser could not tell apart), and an option of the second converter can be overridden."""
+    import importlib
+
+    from torchtitan_b200.config.manager import ConfigManager
+    from torchtitan_b200.experiments import _supported_experiments
+    from torchtitan_b200.models import _supported_models
+
+    monkeypatch.setenv("WORLD_SIZE", "8")           # the planner-driven configurations size themselves for the job
+    seen = 0
+    for kind, names in (("models", sorted(_supported_models)), ("experiments", sorted(_supported_experiments))):
+        for m in names:
+            try:
+                reg = importlib.import_module(f"torchtitan_b200.{kind}.{m}.config_registry")
+            except ModuleNotFoundError:
+                continue                             # an experiment without job configurations of its own
+            for c in sorted(n for n in dir(reg) if not n.startswith("_") and n[0].islower() and callable(getattr(reg, n))
+                            and getattr(getattr(reg, n), "__module__", "") == reg.__name__):
+                flat = m != "rl"                       # the RL job nests a trainer and a generator configuration
+                cfg = ConfigManager().parse_args(["--module", m, "--config", c] + (["--training.steps", "3"] if flat else []))
+                assert cfg is not None and (not flat or cfg.training.steps == 3), (m, c)
+                seen += 1
+    assert seen > 40
+    cfg = ConfigManager().parse_args([
+        "--module", "deepseek_v3", "--config", "deepseek_v3_671b",
+        "model-converters.converters.1:float8-grouped-mm-converter-config", "--model-converters.converters.1.fqns", "abc"])
+    kinds = [type(c).__qualname__ for c in cfg.model_converters.converters]
+    assert kinds == ["Float8LinearConverter.Config", "Float8GroupedMMConverter.Config"]
+    assert cfg.model_converters.converters[1].fqns == ["abc"]
+    assert type(cfg.model_converters.converters[0]).__name__ == "Config"        # the temporary names are gone again

@@ -9,6 +9,8 @@ treated as a fully-qualified module path, with or without ``.config_registry``),
 
 from __future__ import annotations
 
+import contextlib
+import dataclasses
 import importlib
 import os
 import sys
@@ -53,6 +55,40 @@ def _pop_flag(args: list[str], flag: str) -> tuple[str | None, list[str]]:
     return value, rest
 
 
+@contextlib.contextmanager
+def _distinct_element_names(config):
+    """While the command line is parsed, the element types of a heterogeneous list in the configuration carry distinct
+    class names. The parser offers the element types of a list such as ``model_converters.converters`` as alternatives
+    named after their classes; the nested ``Config`` classes of two converters are both called ``Config``, which it cannot
+    tell apart (a job configuration with a float8 linear converter and a float8 grouped-GEMM converter then fails to
+    parse at all). ``Float8LinearConverter.Config`` becomes ``Float8LinearConverterConfig`` for the duration."""
+    renamed: list[tuple[type, str]] = []
+
+    def walk(obj, depth=0):
+        if depth > 8 or not dataclasses.is_dataclass(obj) or isinstance(obj, type):
+            return
+        for f in dataclasses.fields(obj):
+            value = getattr(obj, f.name, None)
+            if isinstance(value, (list, tuple)):
+                types = {type(v) for v in value if dataclasses.is_dataclass(v)}
+                names = [t.__name__ for t in types]
+                for t in types:
+                    if names.count(t.__name__) > 1:
+                        renamed.append((t, t.__name__))
+                        t.__name__ = t.__qualname__.replace(".", "")
+                for v in value:
+                    walk(v, depth + 1)
+            else:
+                walk(value, depth + 1)
+
+    walk(config)
+    try:
+        yield
+    finally:
+        for t, name in renamed:
+            t.__name__ = name
+
+
 class ConfigManager:
     def __init__(self):
         self.config = None
@@ -64,9 +100,10 @@ class ConfigManager:
     def parse_args(self, args: list[str] | None = None):
         args = list(sys.argv[1:] if args is None else args)
         loaded, rest = self._load_config(args)
-        self.config = tyro.cli(
-            type(loaded), args=rest, default=loaded, registry=custom_registry
-        )
+        with _distinct_element_names(loaded):
+            self.config = tyro.cli(
+                type(loaded), args=rest, default=loaded, registry=custom_registry
+            )
         self._validate_config()
         return self.config
 

@@ -6,7 +6,7 @@ import os
 from torchtitan_b200.models.deepseek_v3 import config_registry as dsv3
 from torchtitan_b200.models.llama3 import config_registry as llama3
 
-from .planner import auto_plan
+from .planner import search, shape_of
 
 
 def _apply(cfg):
@@ -14,11 +14,17 @@ def _apply(cfg):
     m = cfg.model_spec.model
     with __import__("torch").device("meta"):
         model = m.build()
-    nparams, flops = m.get_nparams_and_flops(model, cfg.training.seq_len)
-    plan = auto_plan(nparams, flops, m.n_layers, m.dim, cfg.training.seq_len, cfg.training.local_batch_size, world)
-    cfg.parallelism.data_parallel_shard_degree = plan.dp_shard
-    cfg.parallelism.tensor_parallel_degree = plan.tp
-    cfg.parallelism.fsdp_reshard_after_forward = plan.reshard_after_forward
+    plans = search(shape_of(m, model, cfg.training.seq_len), cfg.training.seq_len, cfg.training.local_batch_size, world, keep=1)
+    if not plans:
+        raise RuntimeError(f"no parallel layout of {world} GPUs holds this model; add nodes")
+    plan = plans[0]
+    p = cfg.parallelism
+    p.data_parallel_replicate_degree, p.data_parallel_shard_degree = plan.dp_replicate, plan.dp_shard
+    p.tensor_parallel_degree, p.context_parallel_degree = plan.tp, plan.cp
+    p.pipeline_parallel_degree, p.expert_parallel_degree = plan.pp, plan.ep
+    if plan.pp > 1:
+        p.pipeline_parallel_schedule = plan.pp_schedule
+    p.fsdp_reshard_after_forward = plan.reshard_after_forward
     cfg.activation_checkpoint.mode = plan.ac_mode
     return cfg
 
