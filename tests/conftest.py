@@ -39,3 +39,27 @@ def _own_rendezvous_port(monkeypatch):
 
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
+
+
+def _registry_snapshot():
+    """repr of every model flavor registered by the model packages imported so far."""
+    out = {}
+    for name, mod in list(sys.modules.items()):
+        if mod is None or not (name.startswith("torchtitan_b200.models.") or name.startswith("torchtitan_b200.experiments.")):
+            continue
+        for attr, value in list(vars(mod).items()):
+            if attr.endswith("_configs") and isinstance(value, dict):
+                for flavor, cfg in value.items():
+                    out[(name, attr, flavor)] = repr(cfg)
+    return out
+
+
+@pytest.fixture(autouse=True)
+def _flavor_registries_stay_untouched():
+    """The flavor registries hold shared objects: a test that shrinks one in place changes what every later test builds.
+    Copy first (``dataclasses.replace``) and replace nested parts instead of assigning into them."""
+    before = _registry_snapshot()
+    yield
+    after = _registry_snapshot()
+    changed = [k for k, v in before.items() if after.get(k) != v]
+    assert not changed, f"this test modified registered model flavors in place: {changed}"

@@ -27,7 +27,7 @@ def _step(model, vocab, seq=64, bs=2, masks=True):
 def test_llama4_debugmodel_step_and_masks():
     from torchtitan_b200.models.llama4 import llama4_configs
 
-    cfg = llama4_configs["debugmodel"]
+    cfg = dataclasses.replace(llama4_configs["debugmodel"])          # a copy: the registry's object is shared by all tests
     cfg.layer = dataclasses.replace(cfg.layer, fixed_attn_block_size=16)
     cfg.rope = dataclasses.replace(cfg.rope, max_seq_len=64)
     model = cfg.build()
