@@ -27,9 +27,10 @@ def flux_debugmodel() -> FluxTrainer.Config:
     return FluxTrainer.Config(
         hf_assets_path="tests/assets/tokenizer", metrics=MetricsProcessor.Config(log_freq=1),
         model_spec=model_registry("flux-debug"), tokenizer=None,
-        dataloader=FluxDataLoader.Config(dataset="cc12m-test", classifier_free_guidance_prob=0.447, img_size=256, encoder=encoder),
+        dataloader=FluxDataLoader.Config(dataset="cc12m-test", classifier_free_guidance_prob=0.447, img_size=256, encoder=encoder,
+                                         hf_assets_path="tests/assets/tokenizer"),
         optimizer=OptimizersContainer.Config(lr=8e-4), lr_scheduler=LRSchedulersContainer.Config(warmup_steps=1, decay_ratio=0.0),
-        training=TrainingConfig(local_batch_size=4, seq_len=512, steps=10, max_norm=2.0),
+        training=TrainingConfig(local_batch_size=4, steps=10, max_norm=2.0),
         encoder=encoder, checkpoint=CheckpointManager.Config(interval=10, last_save_model_only=False),
         activation_checkpoint=ActivationCheckpointConfig(mode="full"),
         validation=Validation(enable_classifier_free_guidance=True, classifier_free_guidance_scale=5.0, denoising_steps=4),
@@ -50,7 +51,7 @@ def _full(flavor: str, *, batch: int, t5_len: int, val_steps: int) -> FluxTraine
         dataloader=FluxDataLoader.Config(dataset="cc12m-wds", classifier_free_guidance_prob=0.447, img_size=256,
                                          t5_max_length=t5_len, encoder=encoder),
         optimizer=OptimizersContainer.Config(lr=1e-4), lr_scheduler=LRSchedulersContainer.Config(warmup_steps=3000, decay_ratio=0.0),
-        training=TrainingConfig(local_batch_size=batch, seq_len=512, steps=30000),
+        training=TrainingConfig(local_batch_size=batch, steps=30000),
         encoder=encoder, checkpoint=CheckpointManager.Config(interval=1000),
         activation_checkpoint=ActivationCheckpointConfig(mode="full"),
         validation=Validation(enable_classifier_free_guidance=True, classifier_free_guidance_scale=5.0, denoising_steps=50),

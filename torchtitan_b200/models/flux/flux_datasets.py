@@ -441,6 +441,9 @@ class FluxDataLoader(ParallelAwareDataloader):
         encoder: Encoder = field(default_factory=Encoder)
         """The reference's way to name the tokenizer folders (``--dataloader.encoder.t5_encoder`` ...); used where the
         fields above are not set."""
+        hf_assets_path: str = "./tests/assets/tokenizer"
+        """Accepted for command lines written for the reference, which reads its test tokenizer from here; the asset-free
+        tokenizer of this framework needs no files."""
         infinite: bool = True
         seed: int = 0
 

@@ -36,34 +36,36 @@ def qwen3_debugmodel_flex() -> Trainer.Config:
     return _debug("debugmodel_flex")
 
 
-def _sized(flavor: str, hf: str, lr: float, bs: int, seq: int, steps: int, **par) -> Trainer.Config:
+def _sized(flavor: str, hf: str, lr: float, bs: int, seq: int, steps: int, *, warmup: int = 600, interval: int = 500,
+           ac: str = "selective", log_freq: int = 10, **par) -> Trainer.Config:
     return Trainer.Config(
         hf_assets_path=f"./assets/hf/{hf}",
+        metrics=MetricsProcessor.Config(log_freq=log_freq),
         model_spec=model_registry(flavor),
         dataloader=HuggingFaceTextDataLoader.Config(dataset="c4"),
         optimizer=OptimizersContainer.Config(lr=lr),
-        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2 if steps <= 10 else 600),
+        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=warmup),
         training=TrainingConfig(local_batch_size=bs, seq_len=seq, steps=steps),
         parallelism=ParallelismConfig(**par),
-        checkpoint=CheckpointManager.Config(interval=500, last_save_model_only=False, export_dtype="float16"),
-        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op"),
+        checkpoint=CheckpointManager.Config(interval=interval, last_save_model_only=False, export_dtype="float16"),
+        activation_checkpoint=ActivationCheckpointConfig(mode=ac, selective_ac_option="op"),
     )
 
 
 def qwen3_0_6b() -> Trainer.Config:
-    return _sized("0.6B", "Qwen3-0.6B", 3e-4, 4, 4096, 10)
+    return _sized("0.6B", "Qwen3-0.6B", 3e-4, 4, 4096, 10, warmup=2, log_freq=1)
 
 
 def qwen3_1_7b() -> Trainer.Config:
-    return _sized("1.7B", "Qwen3-1.7B", 8e-4, 4, 4096, 100)
+    return _sized("1.7B", "Qwen3-1.7B", 8e-4, 4, 4096, 100, warmup=20, interval=50)
 
 
 def qwen3_14b() -> Trainer.Config:
-    return _sized("14B", "Qwen3-14B", 8e-4, 4, 4096, 3000, tensor_parallel_degree=1)
+    return _sized("14B", "Qwen3-14B", 8e-4, 4, 4096, 3000, ac="full", tensor_parallel_degree=1)
 
 
 def qwen3_32b() -> Trainer.Config:
-    return _sized("32B", "Qwen3-32B", 8e-4, 2, 4096, 3000, tensor_parallel_degree=1)
+    return _sized("32B", "Qwen3-32B", 8e-4, 2, 4096, 3000, ac="full", tensor_parallel_degree=1)
 
 
 def qwen3_moe_debug() -> Trainer.Config:
