@@ -33,8 +33,15 @@ def build_transformers_backend_test_list() -> list[T]:
 
 
 def build_ft_test_list() -> list[T]:
-    return [T([["--fault_tolerance.enable", "--fault_tolerance.replica_id 0", "--fault_tolerance.group_size 1"]],
-              "Fault-tolerant trainer, one replica group", "ft_single_group", ngpu=2, module="ft", config="llama3_ft_debugmodel")]
+    # the job is a 100-step DiLoCo run over NCCL replica groups: a short one on whatever backend the ranks have
+    short = ["--training.steps 20", "--fault_tolerance.sync_steps 4", "--fault_tolerance.process_group gloo",
+             "--comm.train_timeout_seconds 100", "--profiling.no-enable-profiling"]
+    return [T([["--fault_tolerance.enable", "--fault_tolerance.replica_id 0", "--fault_tolerance.group_size 1", *short]],
+              "Fault-tolerant trainer, one replica group, DiLoCo", "ft_single_group", ngpu=2, module="ft", config="llama3_ft_debugmodel"),
+            T([["--fault_tolerance.enable", "--fault_tolerance.replica_id 0", "--fault_tolerance.group_size 1",
+                "--fault_tolerance.semi_sync_method None", *short]],
+              "Fault-tolerant trainer, one replica group, synchronous", "ft_single_group_sync", ngpu=2, module="ft",
+              config="llama3_ft_debugmodel")]
 
 
 def build_graph_trainer_test_list() -> list[T]:

@@ -657,7 +657,7 @@ _OWN_VALUES = {
 
 
 @pytest.mark.parametrize("package", ["models.llama3", "models.llama4", "models.qwen3", "models.deepseek_v3", "models.gpt_oss",
-                                     "models.flux", "experiments.vlm", "experiments.graph_trainer.llama3",
+                                     "models.flux", "experiments.vlm", "experiments.ft.llama3", "experiments.graph_trainer.llama3",
                                      "experiments.graph_trainer.deepseek_v3"])
 def test_job_configurations_resolve_to_the_reference_values(package):
     """Every job configuration function of the reference exists here and resolves, option by option, to the same values

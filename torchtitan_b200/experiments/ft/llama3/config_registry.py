@@ -1,27 +1,24 @@
-"""``llama3_ft_debugmodel``: the Llama-3 debug job with the fault-tolerant trainer
-(torchtitan/experiments/ft/llama3/config_registry.py:21-66)."""
+"""``llama3_ft_debugmodel``: the Llama-3 debug job with the fault-tolerant trainer, as a DiLoCo run of 100 steps that
+synchronises two model fragments every 10 steps (the settings of torchtitan/experiments/ft/llama3/config_registry.py:21-66).
+``--fault_tolerance.process_group gloo`` runs the replica groups' traffic on CPU ranks."""
 
-from torchtitan_b200.components.checkpoint import CheckpointManager
-from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
-from torchtitan_b200.components.metrics import MetricsProcessor
-from torchtitan_b200.components.optimizer import OptimizersContainer
-from torchtitan_b200.config import ActivationCheckpointConfig, TrainingConfig
+from torchtitan_b200.config import CommConfig
 from torchtitan_b200.experiments.ft.config import FaultTolerance
+from torchtitan_b200.experiments.ft.optimizer import FTOptimizersContainer
 from torchtitan_b200.experiments.ft.trainer import FaultTolerantTrainer
 from torchtitan_b200.hf_datasets.text_datasets import HuggingFaceTextDataLoader
+from torchtitan_b200.models.job_configs import debug_job
 from torchtitan_b200.models.llama3 import model_registry
+from torchtitan_b200.tools.profiling import ProfilingConfig
 
 
 def llama3_ft_debugmodel() -> FaultTolerantTrainer.Config:
-    return FaultTolerantTrainer.Config(
-        hf_assets_path="./tests/assets/tokenizer",
-        metrics=MetricsProcessor.Config(log_freq=1),
-        model_spec=model_registry("debugmodel"),
-        dataloader=HuggingFaceTextDataLoader.Config(dataset="c4_test"),
-        optimizer=OptimizersContainer.Config(lr=8e-4),
-        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2, decay_ratio=0.8, decay_type="linear", min_lr_factor=0.0),
-        training=TrainingConfig(local_batch_size=8, seq_len=2048, steps=10),
-        checkpoint=CheckpointManager.Config(interval=10, last_save_model_only=False),
-        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="2"),
-        fault_tolerance=FaultTolerance(enable=True, process_group="gloo", group_size=2, min_replica_size=1),
-    )
+    cfg = debug_job(
+        model_registry("debugmodel"), steps=100, validate=(5, 10), config_cls=FaultTolerantTrainer.Config,
+        profiling=ProfilingConfig(enable_profiling=True, profile_freq=10, profiler_active=10, profiler_warmup=0),
+        comm=CommConfig(train_timeout_seconds=15),
+        fault_tolerance=FaultTolerance(enable=True, semi_sync_method="diloco", process_group="nccl", process_group_timeout_ms=10000,
+                                       sync_steps=10, num_fragments=2))
+    cfg.optimizer = FTOptimizersContainer.Config(lr=8e-4)
+    cfg.dataloader = HuggingFaceTextDataLoader.Config()
+    return cfg

@@ -4,36 +4,32 @@ Function names and settings follow torchtitan/models/llama3/config_registry.py:3
 ``llama3_8b_synthetic`` and ``llama3_debugmodel_synthetic`` are additions that need no dataset
 or tokenizer (seeded random tokens)."""
 
-from torchtitan_b200.components.checkpoint import CheckpointManager
 from torchtitan_b200.components.dataloader import SyntheticDataLoader
 from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
 from torchtitan_b200.components.metrics import MetricsProcessor
-from torchtitan_b200.components.optimizer import OptimizersContainer, OptimizersInBackwardContainer
+from torchtitan_b200.components.optimizer import OptimizersInBackwardContainer
 from torchtitan_b200.components.quantization.float8 import Float8LinearConverter
 from torchtitan_b200.components.validate import Validator
-from torchtitan_b200.config import ActivationCheckpointConfig, CompileConfig, ParallelismConfig, TrainingConfig
-from torchtitan_b200.hf_datasets.text_datasets import HuggingFaceTextDataLoader
+from torchtitan_b200.models.job_configs import debug_job, text_job
 from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
 from torchtitan_b200.tools.profiling import ProfilingConfig
 from torchtitan_b200.trainer import Trainer
 
 from . import model_registry
 
+_FP8_ALL_GATHER = dict(enable_fsdp_float8_all_gather=True, precompute_float8_dynamic_scale_for_fsdp=True)
+
+
+def _pretrain(flavor: str, folder: str, **job) -> Trainer.Config:
+    """The C4 pre-training jobs: profiler every 100 steps, TensorBoard, checkpoints every 500 steps, validation every 500
+    steps over 1200 batches."""
+    job.setdefault("steps", 1000)
+    return text_job(model_registry(flavor), assets=f"./assets/hf/{folder}", dataset="c4", seq=8192, profile_every=100,
+                    metrics=dict(enable_tensorboard=True), checkpoint=dict(interval=500), validate=(500, 1200), **job)
+
 
 def llama3_debugmodel() -> Trainer.Config:
-    return Trainer.Config(
-        hf_assets_path="./tests/assets/tokenizer",
-        model_spec=model_registry("debugmodel"),
-        optimizer=OptimizersContainer.Config(lr=8e-4),
-        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2, decay_ratio=0.8, decay_type="linear", min_lr_factor=0.0),
-        training=TrainingConfig(local_batch_size=8, seq_len=2048, steps=10),
-        dataloader=HuggingFaceTextDataLoader.Config(dataset="c4_test"),
-        metrics=MetricsProcessor.Config(log_freq=1),
-        parallelism=ParallelismConfig(pipeline_parallel_schedule="Interleaved1F1B"),
-        checkpoint=CheckpointManager.Config(interval=10, last_save_model_only=False),
-        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="2"),
-        validator=Validator.Config(freq=5, steps=10),
-    )
+    return debug_job(model_registry("debugmodel"), parallel=dict(pipeline_parallel_schedule="Interleaved1F1B"), validate=(5, 10))
 
 
 def llama3_debugmodel_synthetic() -> Trainer.Config:
@@ -65,7 +61,7 @@ def llama3_debugmodel_opt_in_bwd() -> Trainer.Config:
 def llama3_debugmodel_float8() -> Trainer.Config:
     cfg = llama3_debugmodel()
     cfg.model_converters = ModelConvertersContainer.Config(converters=[
-        Float8LinearConverter.Config(enable_fsdp_float8_all_gather=True, precompute_float8_dynamic_scale_for_fsdp=True),
+        Float8LinearConverter.Config(**_FP8_ALL_GATHER),
     ])
     return cfg
 
@@ -73,24 +69,13 @@ def llama3_debugmodel_float8() -> Trainer.Config:
 def llama3_debugmodel_float8_emulate() -> Trainer.Config:
     cfg = llama3_debugmodel()
     cfg.model_converters = ModelConvertersContainer.Config(converters=[
-        Float8LinearConverter.Config(enable_fsdp_float8_all_gather=True, precompute_float8_dynamic_scale_for_fsdp=True, emulate=True),
+        Float8LinearConverter.Config(emulate=True, **_FP8_ALL_GATHER),
     ])
     return cfg
 
 
 def llama3_8b() -> Trainer.Config:
-    return Trainer.Config(
-        hf_assets_path="./assets/hf/Llama-3.1-8B",
-        profiling=ProfilingConfig(enable_profiling=True, profile_freq=100),
-        metrics=MetricsProcessor.Config(enable_tensorboard=True),
-        model_spec=model_registry("8B"),
-        optimizer=OptimizersContainer.Config(lr=3e-4),
-        training=TrainingConfig(local_batch_size=1, seq_len=8192, steps=1000),
-        dataloader=HuggingFaceTextDataLoader.Config(dataset="c4"),
-        checkpoint=CheckpointManager.Config(interval=500),
-        activation_checkpoint=ActivationCheckpointConfig(mode="selective", selective_ac_option="op"),
-        validator=Validator.Config(freq=500, steps=1200),
-    )
+    return _pretrain("8B", "Llama-3.1-8B", lr=3e-4, batch=1)
 
 
 def llama3_8b_synthetic() -> Trainer.Config:
@@ -121,39 +106,10 @@ def llama3_8b_synthetic_mxfp8() -> Trainer.Config:
 
 
 def llama3_70b() -> Trainer.Config:
-    return Trainer.Config(
-        hf_assets_path="./assets/hf/Llama-3.1-70B",
-        profiling=ProfilingConfig(enable_profiling=True, profile_freq=100),
-        metrics=MetricsProcessor.Config(enable_tensorboard=True),
-        model_spec=model_registry("70B"),
-        optimizer=OptimizersContainer.Config(lr=1.5e-4),
-        training=TrainingConfig(local_batch_size=8, seq_len=8192, steps=1000),
-        dataloader=HuggingFaceTextDataLoader.Config(dataset="c4"),
-        parallelism=ParallelismConfig(tensor_parallel_degree=8),
-        checkpoint=CheckpointManager.Config(interval=500),
-        activation_checkpoint=ActivationCheckpointConfig(mode="full"),
-        validator=Validator.Config(freq=500, steps=1200),
-    )
+    return _pretrain("70B", "Llama-3.1-70B", lr=1.5e-4, batch=8, ac="full", parallel=dict(tensor_parallel_degree=8))
 
 
 def llama3_405b() -> Trainer.Config:
-    return Trainer.Config(
-        hf_assets_path="./assets/hf/Llama-3.1-405B",
-        profiling=ProfilingConfig(enable_profiling=True, profile_freq=100),
-        metrics=MetricsProcessor.Config(enable_tensorboard=True),
-        model_spec=model_registry("405B"),
-        model_converters=ModelConvertersContainer.Config(converters=[
-            Float8LinearConverter.Config(
-                enable_fsdp_float8_all_gather=True, precompute_float8_dynamic_scale_for_fsdp=True, filter_fqns=["output"],
-            ),
-        ]),
-        optimizer=OptimizersContainer.Config(lr=8e-5),
-        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=600),
-        training=TrainingConfig(local_batch_size=2, seq_len=8192, steps=3000),
-        dataloader=HuggingFaceTextDataLoader.Config(dataset="c4"),
-        parallelism=ParallelismConfig(tensor_parallel_degree=8, enable_async_tensor_parallel=True),
-        checkpoint=CheckpointManager.Config(interval=500),
-        activation_checkpoint=ActivationCheckpointConfig(mode="full"),
-        compile=CompileConfig(enable=True),
-        validator=Validator.Config(freq=500, steps=1200),
-    )
+    return _pretrain("405B", "Llama-3.1-405B", lr=8e-5, batch=2, steps=3000, ac="full", schedule=dict(warmup_steps=600),
+                     parallel=dict(tensor_parallel_degree=8, enable_async_tensor_parallel=True), compile=dict(enable=True),
+                     converters=[Float8LinearConverter.Config(filter_fqns=["output"], **_FP8_ALL_GATHER)])

@@ -3,6 +3,7 @@
 Parity: torchtitan/protocols/model_spec.py:28-51.
 """
 
+import copy
 from collections.abc import Callable
 from dataclasses import dataclass
 from typing import Any
@@ -28,6 +29,11 @@ class ModelSpec:
     build_loss_fn: LossFunctionBuilder
     post_optimizer_build_fn: PostOptimizerBuildFn | None = None
     state_dict_adapter: type[BaseStateDictAdapter] | None = None
+
+    def __post_init__(self):
+        # a specification owns its model configuration: the trainer adapts it to the job (sequence length, vocabulary
+        # size ...), which must not change the flavor registered for everybody else in the process
+        self.model = copy.deepcopy(self.model)
 
 
 @dataclass
