@@ -7,13 +7,13 @@ from torchtitan_b200.experiments.ft.config import FaultTolerance
 from torchtitan_b200.experiments.ft.optimizer import FTOptimizersContainer
 from torchtitan_b200.experiments.ft.trainer import FaultTolerantTrainer
 from torchtitan_b200.hf_datasets.text_datasets import HuggingFaceTextDataLoader
-from torchtitan_b200.models.job_configs import debug_job
+from torchtitan_b200.models import job_configs as _jobs
 from torchtitan_b200.models.llama3 import model_registry
 from torchtitan_b200.tools.profiling import ProfilingConfig
 
 
 def llama3_ft_debugmodel() -> FaultTolerantTrainer.Config:
-    cfg = debug_job(
+    cfg = _jobs.debug_job(
         model_registry("debugmodel"), steps=100, validate=(5, 10), config_cls=FaultTolerantTrainer.Config,
         profiling=ProfilingConfig(enable_profiling=True, profile_freq=10, profiler_active=10, profiler_warmup=0),
         comm=CommConfig(train_timeout_seconds=15),

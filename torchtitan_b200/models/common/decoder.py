@@ -26,7 +26,7 @@ from .attention import (
 )
 from .embedding import Embedding
 from .feed_forward import FeedForward
-from .linear import Linear
+from .linear import Linear, with_residual
 from .moe import MoE
 from .rmsnorm import RMSNorm
 from .rope import RoPE
@@ -44,6 +44,39 @@ class TransformerBlock(Module):
         attention_norm: RMSNorm.Config
         ffn_norm: RMSNorm.Config
 
+    #: dense blocks hand their skip connections to the output projections, which add them in the GEMM epilogue
+    fuse_residual = False
+
+    def assemble(self, config, *, dim: int, layer_id: int, n_layers: int, attention=None, moe: bool = False,
+                 depth_init: bool = True) -> None:
+        """Sub-modules of the block: ``attention`` (built from ``attention`` when a family adjusts it per layer), either
+        ``moe`` or ``feed_forward``, the two norms; output projections are initialised with ``0.02 / sqrt(2 d)`` where ``d``
+        is the layer's depth (or the model's when ``depth_init`` is off)."""
+        self.attention = (attention if attention is not None else config.attention).build(dim=dim)
+        self.moe_enabled = moe
+        part = config.moe if moe else config.feed_forward
+        assert part is not None, "the block's configuration lacks its " + ("moe" if moe else "feed_forward") + " section"
+        setattr(self, "moe" if moe else "feed_forward", part.build(dim=dim))
+        self.attention_norm = config.attention_norm.build(normalized_shape=dim)
+        self.ffn_norm = config.ffn_norm.build(normalized_shape=dim)
+        self.weight_init_std = 0.02 / (2 * ((layer_id + 1) if depth_init else n_layers)) ** 0.5
+
+    def forward(self, x, freqs_cis, attention_masks, positions=None):
+        if self.fuse_residual and not self.moe_enabled:
+            h = with_residual(self.attention, x, self.attention_norm(x), freqs_cis, attention_masks, positions)
+            return with_residual(self.feed_forward, h, self.ffn_norm(h))
+        h = x + self.attention(self.attention_norm(x), freqs_cis, attention_masks, positions)
+        return h + (self.moe if self.moe_enabled else self.feed_forward)(self.ffn_norm(h))
+
+    def init_weights(self, **kwargs):
+        self.attention_norm.init_weights()
+        self.ffn_norm.init_weights()
+        self.attention.init_weights(self.weight_init_std)
+        if self.moe_enabled:
+            self.moe.init_weights(init_std=self.weight_init_std, buffer_device=kwargs.get("buffer_device"))
+        else:
+            self.feed_forward.init_weights(self.weight_init_std)
+
 
 class Decoder(BaseModel):
     @dataclass(kw_only=True, slots=True)
@@ -56,6 +89,30 @@ class Decoder(BaseModel):
         norm: RMSNorm.Config
         rope: RoPE.Config
         layer: TransformerBlock.Config
+
+        def fit_to_job(self, trainer_config, *, context_parallel: bool = True) -> None:
+            """What every decoder family adapts to a job: the rotary table covers the training sequence length, context
+            parallel is refused for variable-length attention (or altogether), tensor parallel divides the head counts."""
+            import dataclasses
+
+            from torchtitan_b200.tools.logging import logger
+
+            seq_len, par = trainer_config.training.seq_len, trainer_config.parallelism
+            if seq_len > self.rope.max_seq_len:
+                logger.warning(f"Sequence length {seq_len} exceeds original maximum {self.rope.max_seq_len}.")
+            self.rope = dataclasses.replace(self.rope, max_seq_len=seq_len)
+            backend = getattr(self.layer.attention, "attn_backend", None)
+            if par.context_parallel_degree > 1 and (not context_parallel or backend == "varlen"):
+                raise NotImplementedError(
+                    "Context Parallel only supports SDPA and FlexAttention. "
+                    f"Got attn_backend='{backend}'. Varlen attention is not supported with CP." if context_parallel else
+                    f"Context Parallel is not supported for {type(self).__qualname__.split('.')[0]}.")
+            tp, heads = par.tensor_parallel_degree, getattr(self.layer.attention, "n_heads", None)
+            if tp > 1 and heads:
+                kv = getattr(self.layer.attention, "n_kv_heads", None) or heads
+                for name, n in (("n_heads", heads), ("n_kv_heads", kv)):
+                    if n % tp != 0:
+                        raise ValueError(f"tensor_parallel_degree ({tp}) must divide {name} ({n}).")
 
     def __init__(self, config: Config):
         super().__init__()

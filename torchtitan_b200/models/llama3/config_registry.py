@@ -10,7 +10,7 @@ from torchtitan_b200.components.metrics import MetricsProcessor
 from torchtitan_b200.components.optimizer import OptimizersInBackwardContainer
 from torchtitan_b200.components.quantization.float8 import Float8LinearConverter
 from torchtitan_b200.components.validate import Validator
-from torchtitan_b200.models.job_configs import debug_job, text_job
+from torchtitan_b200.models import job_configs as _jobs
 from torchtitan_b200.protocols.model_converter import ModelConvertersContainer
 from torchtitan_b200.tools.profiling import ProfilingConfig
 from torchtitan_b200.trainer import Trainer
@@ -24,12 +24,12 @@ def _pretrain(flavor: str, folder: str, **job) -> Trainer.Config:
     """The C4 pre-training jobs: profiler every 100 steps, TensorBoard, checkpoints every 500 steps, validation every 500
     steps over 1200 batches."""
     job.setdefault("steps", 1000)
-    return text_job(model_registry(flavor), assets=f"./assets/hf/{folder}", dataset="c4", seq=8192, profile_every=100,
+    return _jobs.text_job(model_registry(flavor), assets=f"./assets/hf/{folder}", dataset="c4", seq=8192, profile_every=100,
                     metrics=dict(enable_tensorboard=True), checkpoint=dict(interval=500), validate=(500, 1200), **job)
 
 
 def llama3_debugmodel() -> Trainer.Config:
-    return debug_job(model_registry("debugmodel"), parallel=dict(pipeline_parallel_schedule="Interleaved1F1B"), validate=(5, 10))
+    return _jobs.debug_job(model_registry("debugmodel"), parallel=dict(pipeline_parallel_schedule="Interleaved1F1B"), validate=(5, 10))
 
 
 def llama3_debugmodel_synthetic() -> Trainer.Config:

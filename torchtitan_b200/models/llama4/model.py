@@ -16,9 +16,7 @@ import torch.nn as nn
 
 from torchtitan_b200.models.common.attention import AttentionMasks, document_ids
 from torchtitan_b200.models.common.decoder import Decoder, TransformerBlock
-from torchtitan_b200.models.llama3.model import validate_tp_heads
 from torchtitan_b200.models.utils import get_moe_model_nparams_and_flops
-from torchtitan_b200.tools.logging import logger
 
 
 def compute_moe_hidden_dim(dim: int, *, multiple_of: int = 256, ffn_dim_multiplier: float | None = None,
@@ -41,38 +39,14 @@ class Llama4TransformerBlock(TransformerBlock):
 
     def __init__(self, config: Config, *, layer_id: int, dim: int, n_layers: int):
         super().__init__()
-        attn_cfg = config.attention
+        attention = config.attention
         if config.every_n_layers_nope is not None:
             if config.every_n_layers_nope <= 1:
                 raise ValueError("every_n_layers_nope must be greater than 1")
             if layer_id % config.every_n_layers_nope == 0:
-                attn_cfg = dataclasses.replace(attn_cfg, use_rope=False)
-        self.attention = attn_cfg.build(dim=dim)
-        self.moe_enabled = (layer_id + 1) % config.interleave_moe_layer_step == 0
-        if self.moe_enabled:
-            assert config.moe is not None
-            self.moe = config.moe.build(dim=dim)
-        else:
-            assert config.feed_forward is not None
-            self.feed_forward = config.feed_forward.build(dim=dim)
-        self.attention_norm = config.attention_norm.build(normalized_shape=dim)
-        self.ffn_norm = config.ffn_norm.build(normalized_shape=dim)
-        depth = (layer_id + 1) if config.depth_init else n_layers
-        self.weight_init_std = 0.02 / (2 * depth) ** 0.5
-
-    def forward(self, x, freqs_cis, attention_masks, positions=None):
-        h = x + self.attention(self.attention_norm(x), freqs_cis, attention_masks, positions)
-        ff = self.moe if self.moe_enabled else self.feed_forward
-        return h + ff(self.ffn_norm(h))
-
-    def init_weights(self, **kwargs):
-        self.attention_norm.init_weights()
-        self.ffn_norm.init_weights()
-        self.attention.init_weights(self.weight_init_std)
-        if self.moe_enabled:
-            self.moe.init_weights(init_std=self.weight_init_std, buffer_device=kwargs.get("buffer_device"))
-        else:
-            self.feed_forward.init_weights(self.weight_init_std)
+                attention = dataclasses.replace(attention, use_rope=False)
+        self.assemble(config, dim=dim, layer_id=layer_id, n_layers=n_layers, attention=attention,
+                      moe=(layer_id + 1) % config.interleave_moe_layer_step == 0, depth_init=config.depth_init)
 
 
 class Llama4Model(Decoder):
@@ -84,19 +58,9 @@ class Llama4Model(Decoder):
         layer: TransformerBlock.Config
 
         def update_from_config(self, *, trainer_config, **kwargs) -> None:
-            seq_len = trainer_config.training.seq_len
-            par = trainer_config.parallelism
-            if seq_len > self.rope.max_seq_len:
-                logger.warning(f"Sequence length {seq_len} exceeds original maximum {self.rope.max_seq_len}.")
-            self.rope = dataclasses.replace(self.rope, max_seq_len=seq_len)
             assert self.layer.moe is not None
-            if par.context_parallel_degree > 1:
-                raise NotImplementedError(
-                    "Context Parallel is not supported for Llama4 "
-                    "(Llama4 requires FlexAttention, which is not supported with CP)."
-                )
+            self.fit_to_job(trainer_config, context_parallel=False)     # needs masks that context parallel does not carry
             self.layer.moe._debug_force_load_balance = trainer_config.debug.moe_force_load_balance
-            validate_tp_heads(self.layer.attention, par.tensor_parallel_degree)
 
         def get_nparams_and_flops(self, model: nn.Module, seq_len: int) -> tuple[int, int]:
             n_heads = self.layer.attention.n_heads
