@@ -204,3 +204,69 @@ def test_profiler_writes_traces_on_schedule_and_is_off_by_default(tmp_path):
             pass
     with maybe_enable_memory_snapshot(ProfilingConfig(enable_memory_snapshot=True), base_folder=str(tmp_path)) as snap:
         assert snap is None or torch.cuda.is_available()      # memory snapshots need a CUDA device
+
+
+def test_reference_names_of_building_blocks_and_mask_functions():
+    """Names that code written against the reference imports: the parallelize steps of every family, the mask functions
+    of the common attention module (checked against the documents / window they describe), loader and
+    fault-tolerance exports."""
+    import importlib
+
+    from torch.nn.attention.flex_attention import and_masks, create_mask
+
+    wanted = {f"torchtitan_b200.models.{f}.parallelize": ["apply_ac", "apply_fsdp", "apply_compile", "apply_non_moe_tp",
+                                                          "apply_moe_ep_tp", "disable_fsdp_gradient_division"]
+              for f in ("llama3", "llama4", "qwen3", "deepseek_v3", "gpt_oss")}
+    wanted.update({
+        "torchtitan_b200.models.flux.parallelize": ["apply_ac", "apply_fsdp", "parallelize_flux"],
+        "torchtitan_b200.models.common": ["MoE", "apply_rotary_emb_cos_sin", "apply_rotary_emb_complex", "create_attention_mask",
+                                          "get_causal_mask_mod", "get_document_mask_mod", "get_fixed_block_mask_mod",
+                                          "get_sliding_window_mask_mod", "create_varlen_metadata_for_document"],
+        "torchtitan_b200.models.common.moe.kernels": ["generate_permute_indices", "fill_indices_wrapper"],
+        "torchtitan_b200.components.quantization.module_utils": ["capture_module_attrs", "inject_module_protocol",
+                                                                 "verify_module_protocol"],
+        "torchtitan_b200.distributed": ["ParallelDims", "utils", "parallel_dims"],
+        "torchtitan_b200.distributed.utils": ["set_determinism", "clip_grad_norm_", "dist_mean", "init_distributed"],
+        "torchtitan_b200.distributed.tensor_parallel": ["maybe_enable_async_tp"],
+        "torchtitan_b200.distributed.activation_checkpoint": ["apply_ac"],
+        "torchtitan_b200.experiments.ft": ["has_torchft", "maybe_semi_sync_training"],
+        "torchtitan_b200.experiments.ft.llama3": ["model_registry"],
+        "torchtitan_b200.experiments.vlm": ["HuggingFaceMultiModalDataLoader"],
+        "torchtitan_b200.experiments.vlm.configs": ["MultiModalTrainerConfig"],
+        "torchtitan_b200.models.flux.configs": ["Encoder", "Validation", "Inference"],
+    })
+    for module, names in wanted.items():
+        mod = importlib.import_module(module)
+        for n in names:
+            assert getattr(mod, n, None) is not None, f"{module}.{n}"
+    from torchtitan_b200.models.common import (get_causal_mask_mod, get_document_mask_mod, get_fixed_block_mask_mod,
+                                               get_sliding_window_mask_mod)
+
+    x = torch.tensor([[5, 1, 7, 7, 1, 3, 4, 9]])                    # three documents ending with token 1
+    doc = torch.tensor([0, 0, 1, 1, 1, 2, 2, 2])
+    i = torch.arange(8)
+    causal = i[:, None] >= i[None, :]
+    got = create_mask(and_masks(get_causal_mask_mod(), get_document_mask_mod(x, 1), get_sliding_window_mask_mod(2)), 1, 1, 8, 8,
+                      device="cpu")[0, 0]
+    assert torch.equal(got, causal & (doc[:, None] == doc[None, :]) & (i[:, None] - i[None, :] < 2))
+    blocks = create_mask(and_masks(get_causal_mask_mod(), get_fixed_block_mask_mod(4)), 1, 1, 8, 8, device="cpu")[0, 0]
+    assert torch.equal(blocks, causal & (i[:, None] // 4 == i[None, :] // 4))
+    # a module swapped for another class keeps the Module protocol and its saved attributes
+    from torchtitan_b200.components.quantization.module_utils import (capture_module_attrs, inject_module_protocol,
+                                                                       verify_module_protocol)
+    from torchtitan_b200.models.common.linear import Linear
+
+    class Foreign(torch.nn.Linear):
+        pass
+
+    net = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.Linear(4, 2))
+    net[0].tag, net[1].tag = "first", "second"
+    saved = capture_module_attrs(net, ["tag"])
+    net[0], net[1] = Foreign(4, 4), Foreign(4, 2)
+    with pytest.raises(RuntimeError, match="do not satisfy"):
+        verify_module_protocol(net, Foreign, Linear)
+    inject_module_protocol(net, Linear, saved)
+    verify_module_protocol(net, Foreign, Linear)
+    assert (net[0].tag, net[1].tag) == ("first", "second") and type(net[0]) is type(net[1]) and isinstance(net[0], Foreign)
+    with pytest.raises(RuntimeError, match="should not be constructed directly"):
+        type(net[0])(4, 4)

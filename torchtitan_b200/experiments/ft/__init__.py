@@ -6,4 +6,16 @@ Counterpart of torchtitan/experiments/ft (which delegates these pieces to the ex
 from .lighthouse import Lighthouse, LighthouseClient, Quorum
 from .manager import FTManager, ReplicaManager
 
-__all__ = ["Lighthouse", "LighthouseClient", "Quorum", "FTManager", "ReplicaManager"]
+__all__ = ["Lighthouse", "LighthouseClient", "Quorum", "FTManager", "ReplicaManager", "has_torchft", "maybe_semi_sync_training"]
+
+#: the reference gates its fault-tolerance code on the external torchft package; the quorum service, replica manager and
+#: semi-synchronous methods of this framework are built in
+has_torchft = True
+
+
+def __getattr__(name):
+    if name == "maybe_semi_sync_training":
+        from .trainer import maybe_semi_sync_training
+
+        return maybe_semi_sync_training
+    raise AttributeError(name)

@@ -12,7 +12,16 @@ from torchtitan_b200.protocols.model_spec import ModelSpec
 from .model import Llama3Siglip2Transformer, Siglip2Config, SpecialTokens
 from .parallelize import parallelize_vlm
 
-__all__ = ["Llama3Siglip2Transformer", "Siglip2Config", "SpecialTokens", "model_registry", "llama3_siglip2_configs"]
+__all__ = ["Llama3Siglip2Transformer", "Siglip2Config", "SpecialTokens", "model_registry", "llama3_siglip2_configs",
+           "HuggingFaceMultiModalDataLoader"]
+
+
+def __getattr__(name):          # the loader pulls in the dataset stack: imported on first use
+    if name == "HuggingFaceMultiModalDataLoader":
+        from .datasets import MMDataLoader
+
+        return MMDataLoader
+    raise AttributeError(name)
 
 
 def _from_llama(flavor: str, encoder: Siglip2Config) -> Llama3Siglip2Transformer.Config:

@@ -200,3 +200,49 @@ class GQAttention(BaseAttention):
         if self.q_norm is not None:
             self.q_norm.init_weights()
             self.k_norm.init_weights()
+
+
+# ------------------------------------------------------------------------------------------ mask functions
+# The attention kernels of this framework take masks as per-row key ranges (``AttentionMasks``). Code written against the
+# reference describes them as FlexAttention mask functions ``(batch, head, query index, key index) -> bool`` and builds
+# block masks from them (torchtitan/models/common/attention.py:231-318); the same functions are offered here for models
+# that call ``torch.nn.attention.flex_attention`` themselves.
+def get_causal_mask_mod():
+    def causal(b, h, q_idx, kv_idx):
+        return q_idx >= kv_idx
+
+    return causal
+
+
+def get_document_mask_mod(batch: torch.Tensor, eos_id: int):
+    """Tokens attend inside their own document; documents end with ``eos_id``."""
+    docs = document_ids(batch, eos_id)
+
+    def same_document(b, h, q_idx, kv_idx):
+        return docs[b, q_idx] == docs[b, kv_idx]
+
+    return same_document
+
+
+def get_fixed_block_mask_mod(fixed_block_size: int):
+    def same_block(b, h, q_idx, kv_idx):
+        return (q_idx // fixed_block_size) == (kv_idx // fixed_block_size)
+
+    return same_block
+
+
+def get_sliding_window_mask_mod(window_size: int):
+    if window_size < 1:
+        raise ValueError(f"sliding window size must be at least 1, got {window_size}")
+
+    def in_window(b, h, q_idx, kv_idx):
+        return (kv_idx <= q_idx) & (q_idx - kv_idx < window_size)
+
+    return in_window
+
+
+def create_attention_mask(mask_mod, B, H, Q_LEN, KV_LEN, **kwargs):
+    """FlexAttention block mask of a mask function (eager construction)."""
+    from torch.nn.attention.flex_attention import create_block_mask
+
+    return create_block_mask(mask_mod, B, H, Q_LEN, KV_LEN, **kwargs)

@@ -33,3 +33,8 @@ def parallelize_flux(model: nn.Module, *, parallel_dims, training, model_convert
     elif parallel_dims.dp_replicate_enabled:
         fsdp.replicate(model, mesh=parallel_dims.get_mesh("dp_replicate"))
     return model
+
+
+# the steps of ``parallelize_flux`` under the reference's names, for custom parallelize functions written against it
+from torchtitan_b200.parallel.ac import apply_ac  # noqa: E402,F401
+from torchtitan_b200.parallel.data_parallel import apply_fsdp  # noqa: E402,F401

@@ -32,3 +32,26 @@ def parallelize_gptoss(model: nn.Module, *, parallel_dims, training, model_conve
         apply_ac(model, ac_config, model_compile_enabled=False, base_folder=dump_folder)
     apply_data_parallel(model, parallel_dims, training, parallelism)
     return model
+
+
+# ------------------------------------------------------------------------------------------ building blocks
+# the steps a family's parallelize function is made of, under the names the reference's modules give them, for custom
+# parallelize functions written against it
+from torchtitan_b200.parallel.ac import apply_ac  # noqa: E402,F401
+from torchtitan_b200.parallel.data_parallel import apply_fsdp  # noqa: E402,F401
+from torchtitan_b200.parallel.ep import apply_moe_ep_tp  # noqa: E402,F401
+from torchtitan_b200.parallel.tp import apply_tp_to_decoder as apply_tp  # noqa: E402,F401
+
+apply_non_moe_tp = apply_tp
+
+
+def apply_compile(model, compile_config=None, **kwargs):
+    """No tracing compiler runs in this framework: launch-bound loops are captured in CUDA graphs
+    (``experiments/graph_trainer``), the hot operators are kernels of their own."""
+    return model
+
+
+def disable_fsdp_gradient_division(model) -> None:
+    """The FSDP units of this framework sum gradients over the data-parallel ranks and never divide: the loss is
+    normalised by the global token count. Nothing to switch off."""
+    return None
