@@ -12,6 +12,7 @@ pipeline stages, :397-543), ``maybe_enable_amp`` (:228-248).
 from __future__ import annotations
 
 import contextlib
+from collections.abc import Callable
 import math
 import os
 from datetime import timedelta
@@ -130,14 +131,21 @@ def _flight_recorder_env(comm_config, base_folder: str) -> None:
         setdefault("TORCH_FR_DUMP_TEMP_FILE", os.path.join(dump_dir, comm_config.save_traces_file_prefix))
 
 
+def init_fake_mode(world_size: int, comm_mode: str = "fake_backend") -> int:
+    """One process standing in for ``world_size`` ranks: collectives of the ``fake`` backend return at once, so that
+    configuration, meshes and parallelisation of a large job can be checked without GPUs. ``local_tensor`` and
+    ``fake_backend`` are the same here: the parallel runtimes of this framework keep plain local shards and need no
+    tensor mode of their own (torchtitan/distributed/utils.py:251-275)."""
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+
+    dist.init_process_group("fake", rank=0, world_size=world_size, store=FakeStore())
+    return world_size
+
+
 def init_distributed(comm_config, enable_cpu_backend: bool = False, base_folder: str = "", ranks: list[int] | None = None) -> int:
     """Start the default process group and return the world size."""
     if comm_config.mode in ("fake_backend", "local_tensor"):
-        from torch.testing._internal.distributed.fake_pg import FakeStore
-
-        world = int(os.environ.get("NGPU", os.environ.get("WORLD_SIZE", "1")))
-        dist.init_process_group("fake", rank=0, world_size=world, store=FakeStore())
-        return world
+        return init_fake_mode(int(os.environ.get("NGPU", os.environ.get("WORLD_SIZE", "1"))), comm_config.mode)
     if not ("RANK" in os.environ and "WORLD_SIZE" in os.environ):
         # single process without a launcher
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -193,6 +201,10 @@ def maybe_enable_amp(parallel_dims, mixed_precision_param: str, dev_type: str):
 
     logger.info("Mixed precision training is handled by AMP")
     return torch.autocast(dev_type, dtype=TORCH_DTYPE_MAP[mixed_precision_param])
+
+
+#: what :func:`get_train_context` returns: a callable giving the context manager a training step runs under
+TrainContext = Callable[..., contextlib.AbstractContextManager]
 
 
 def get_train_context(enable_loss_parallel: bool):
