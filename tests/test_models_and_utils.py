@@ -270,3 +270,41 @@ def test_reference_names_of_building_blocks_and_mask_functions():
     assert (net[0].tag, net[1].tag) == ("first", "second") and type(net[0]) is type(net[1]) and isinstance(net[0], Foreign)
     with pytest.raises(RuntimeError, match="should not be constructed directly"):
         type(net[0])(4, 4)
+
+
+def test_token_group_padding_wrapper_and_alignment_floor():
+    """``indices_padding_wrapper`` hands a per-expert function padded, expert-major groups and restores the row order; the
+    alignment floor set by converters raises what the dispatchers pad to."""
+    from torchtitan_b200.models.common.moe import utils as u
+    from torchtitan_b200.models.common.moe.moe import group_alignment
+
+    torch.manual_seed(0)
+    E, D = 3, 4
+    w1, w2, w3 = torch.randn(E, 5, D), torch.randn(E, D, 5), torch.randn(E, 5, D)
+    counts = torch.tensor([2, 0, 3, 1, 4, 0], dtype=torch.int32)            # 2 source ranks x 3 local experts
+    x = torch.randn(int(counts.sum()), D)
+    seen = {}
+
+    def per_expert(w1, w2, w3, xp, c):
+        seen["counts"] = c.tolist()
+        out, off = torch.zeros(xp.shape[0], D), 0
+        for e, n in enumerate(c.tolist()):
+            h = xp[off:off + n]
+            out[off:off + n] = (torch.nn.functional.silu(h @ w1[e].t()) * (h @ w3[e].t())) @ w2[e].t()
+            off += n
+        return out
+
+    got = u.indices_padding_wrapper(per_expert)(w1, w2, w3, x, counts)
+    owner = torch.repeat_interleave(torch.arange(6) % 3, counts.long())
+    want = torch.stack([(torch.nn.functional.silu(x[i] @ w1[e].t()) * (x[i] @ w3[e].t())) @ w2[e].t()
+                        for i, e in enumerate(owner.tolist())])
+    assert torch.allclose(got, want, atol=1e-5) and seen["counts"] == [8, 8, 8]     # 3, 4, 3 rows padded to the alignment
+    try:
+        u.set_token_group_alignment_size_m(32)
+        assert u.get_mxfp8_pad_multiple() == 32 and u.maybe_align_num_tokens_for_mxfp8(33) == 64
+        assert group_alignment(object(), 8) == 32 and group_alignment(object(), 64) == 64
+        with pytest.raises(ValueError):
+            u.set_token_group_alignment_size_m(12)
+    finally:
+        u.set_token_group_alignment_size_m(8)
+    assert u.get_mxfp8_pad_multiple() is None and group_alignment(object(), 8) == 8

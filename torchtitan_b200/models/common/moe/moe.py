@@ -47,6 +47,9 @@ GROUP_ALIGN_MX_NATIVE = 128  # row block of the block-scaled grouped GEMM's scal
 def group_alignment(experts, base: int) -> int:
     """Rows every expert's block is padded to: ``base`` from the dispatcher's own needs, raised to what the experts'
     quantised grouped GEMM wants (MXFP8 on the native kernel: 128; otherwise the recipe's block along the tokens)."""
+    from . import utils as _utils
+
+    base = max(base, _utils.TOKEN_GROUP_ALIGN_SIZE_M)      # floor set through set_token_group_alignment_size_m
     quant = getattr(experts, "quant", None)
     if quant is None:
         return base
